@@ -1,0 +1,26 @@
+"""Generation engine: request/outputs types, executors, micro-batching, gathering."""
+
+from visionrl_b200.engine.batching import forward_batch_by_merging_prompts
+from visionrl_b200.engine.core.protocols import (
+    BatchedFamilyPipelineExecutor, ChunkedFamilyPipelineExecutor, FamilyPipelineExecutor,
+    PipelineChunkResult,
+)
+from visionrl_b200.engine.core.registry import ExecutorKey, FamilyPipelineRegistry
+from visionrl_b200.engine.core.runtime import GenerationRuntime, RolloutBackend
+from visionrl_b200.engine.core.runtime_spec import GenerationRuntimeSpec
+from visionrl_b200.engine.core.types import (
+    GenerationMetrics, GenerationRequest, GenerationSampleSpec, OutputBatch, RolloutDebugTensors,
+    RolloutDenoisingEnv, RolloutDitTrajectory, RolloutTrajectoryData, WorkloadSignature,
+)
+from visionrl_b200.engine.core.worker import GenerationIdFactory, GenerationWorker
+from visionrl_b200.engine.gather import gather_pipeline_chunks, require_chunked_executor
+
+__all__ = [
+    "BatchedFamilyPipelineExecutor", "ChunkedFamilyPipelineExecutor", "ExecutorKey",
+    "FamilyPipelineExecutor", "FamilyPipelineRegistry", "GenerationIdFactory", "GenerationMetrics",
+    "GenerationRequest", "GenerationRuntime", "GenerationRuntimeSpec", "GenerationSampleSpec",
+    "GenerationWorker", "OutputBatch", "PipelineChunkResult", "RolloutBackend",
+    "RolloutDebugTensors", "RolloutDenoisingEnv", "RolloutDitTrajectory", "RolloutTrajectoryData",
+    "WorkloadSignature", "forward_batch_by_merging_prompts", "gather_pipeline_chunks",
+    "require_chunked_executor",
+]

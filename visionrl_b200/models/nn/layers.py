@@ -1,0 +1,201 @@
+"""Building blocks of the native models.
+
+Every layer calls the functional operators in :mod:`visionrl_b200.ops`, which
+run hand-written sm_100a kernels for bf16 CUDA tensors and PyTorch formulas
+otherwise, so the same module definitions serve the CPU oracle runs and the
+B200 runs.
+"""
+
+from __future__ import annotations
+
+import contextlib
+import math
+
+import torch
+from torch import nn
+
+from visionrl_b200.ops import attention as attn_ops
+from visionrl_b200.ops import linear as linear_ops
+from visionrl_b200.ops import norm as norm_ops
+
+
+class Linear(nn.Module):
+    """``nn.Linear``-layout weight evaluated by :func:`visionrl_b200.ops.linear.linear`."""
+
+    def __init__(self, in_features: int, out_features: int, bias: bool = True,
+                 init_std: float | None = None):
+        super().__init__()
+        self.in_features, self.out_features = in_features, out_features
+        self.weight = nn.Parameter(torch.empty(out_features, in_features))
+        self.bias = nn.Parameter(torch.zeros(out_features)) if bias else None
+        std = init_std if init_std is not None else 1.0 / math.sqrt(in_features)
+        nn.init.normal_(self.weight, std=std)
+
+    def forward(self, x, act=None, gate=None, residual=None):
+        return linear_ops.linear(x, self.weight, self.bias, act=act, gate=gate, residual=residual)
+
+    def extra_repr(self) -> str:
+        return f"in={self.in_features}, out={self.out_features}, bias={self.bias is not None}"
+
+
+class LoRALinear(Linear):
+    """Linear with an optional low-rank adapter ``y += (alpha/r) * B(A x)``.
+
+    ``adapter_enabled`` is flipped by :func:`adapters_disabled`; the frozen
+    reference policy of LoRA training is the same module with the adapter off
+    (reference behaviour: ``vrl/rollouts/evaluators/diffusion/flow_matching.py:82-109``).
+    """
+
+    def __init__(self, in_features, out_features, bias=True, init_std=None):
+        super().__init__(in_features, out_features, bias, init_std)
+        self.lora_A: nn.Parameter | None = None
+        self.lora_B: nn.Parameter | None = None
+        self.lora_scale = 0.0
+        self.adapter_enabled = True
+        # extra names under which ``apply_lora`` targets address this layer, e.g. a fused
+        # QKV projection answers to ("to_q", "to_k", "to_v")
+        self.lora_aliases: tuple = ()
+
+    def add_adapter(self, rank: int, alpha: float, init: str = "gaussian") -> None:
+        dev, dt = self.weight.device, self.weight.dtype
+        a = torch.empty(rank, self.in_features, device=dev, dtype=dt)
+        if init == "gaussian":
+            nn.init.normal_(a, std=1.0 / rank)
+        else:
+            nn.init.kaiming_uniform_(a, a=math.sqrt(5))
+        self.lora_A = nn.Parameter(a)
+        self.lora_B = nn.Parameter(torch.zeros(self.out_features, rank, device=dev, dtype=dt))
+        self.lora_scale = float(alpha) / float(rank)
+
+    @property
+    def has_adapter(self) -> bool:
+        return self.lora_A is not None
+
+    def forward(self, x, act=None, gate=None, residual=None):
+        if not (self.has_adapter and self.adapter_enabled):
+            return super().forward(x, act=act, gate=gate, residual=residual)
+        y = linear_ops.linear(x, self.weight, self.bias)
+        low = linear_ops.linear(x, self.lora_A)
+        y = y + self.lora_scale * linear_ops.linear(low, self.lora_B)
+        return linear_ops.linear_epilogue(y, act, gate, residual)
+
+
+def iter_lora_layers(module: nn.Module):
+    for m in module.modules():
+        if isinstance(m, LoRALinear) and m.has_adapter:
+            yield m
+
+
+@contextlib.contextmanager
+def adapters_disabled(module: nn.Module):
+    layers = list(iter_lora_layers(module))
+    if not layers:
+        raise RuntimeError("disable_adapter() called on a model without LoRA adapters")
+    previous = [m.adapter_enabled for m in layers]
+    for m in layers:
+        m.adapter_enabled = False
+    try:
+        yield
+    finally:
+        for m, flag in zip(layers, previous):
+            m.adapter_enabled = flag
+
+
+def apply_lora(module: nn.Module, rank: int, alpha: float, target_modules, init="gaussian",
+               freeze_base: bool = True) -> list[str]:
+    """Attach adapters to every :class:`LoRALinear` whose qualified name ends with a target
+    or whose ``lora_aliases`` contain one.  A fused projection that answers to several
+    targets (q/k/v) receives a single adapter spanning the fused output."""
+    targets = tuple(target_modules)
+    hit: list[str] = []
+    if freeze_base:
+        for p in module.parameters():
+            p.requires_grad_(False)
+    for name, m in module.named_modules():
+        if not isinstance(m, LoRALinear):
+            continue
+        direct = any(name == t or name.endswith("." + t) for t in targets)
+        if direct or any(alias in targets for alias in m.lora_aliases):
+            m.add_adapter(rank, alpha, init)
+            hit.append(name)
+    if not hit:
+        raise ValueError(f"no LoRA target matched {list(targets)}")
+    return hit
+
+
+class AdapterMixin:
+    """Gives a network ``disable_adapter()`` / ``has_adapters`` over its LoRA layers."""
+
+    def disable_adapter(self):
+        return adapters_disabled(self)
+
+    @property
+    def has_adapters(self) -> bool:
+        return any(True for _ in iter_lora_layers(self))
+
+
+class RMSNorm(nn.Module):
+    def __init__(self, dim: int, eps: float = 1e-6):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(dim))
+        self.eps = eps
+
+    def forward(self, x):
+        return norm_ops.rmsnorm(x, self.weight, self.eps)
+
+
+class LayerNorm(nn.Module):
+    def __init__(self, dim: int, eps: float = 1e-5, affine: bool = True):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(dim)) if affine else None
+        self.bias = nn.Parameter(torch.zeros(dim)) if affine else None
+        self.eps = eps
+
+    def forward(self, x):
+        return norm_ops.layernorm(x, self.weight, self.bias, self.eps)
+
+
+def timestep_embedding(t: torch.Tensor, dim: int, max_period: float = 10000.0) -> torch.Tensor:
+    """Sinusoidal embedding of (possibly fractional) timesteps, fp32, ``[B, dim]``."""
+    half = dim // 2
+    freqs = torch.exp(-math.log(max_period) * torch.arange(half, device=t.device,
+                                                           dtype=torch.float32) / half)
+    args = t.float()[:, None] * freqs[None]
+    return torch.cat([torch.cos(args), torch.sin(args)], dim=-1)
+
+
+class TimestepEmbedder(nn.Module):
+    def __init__(self, hidden: int, freq_dim: int = 256):
+        super().__init__()
+        self.freq_dim = freq_dim
+        self.fc1 = Linear(freq_dim, hidden)
+        self.fc2 = Linear(hidden, hidden)
+
+    def forward(self, t, dtype):
+        e = timestep_embedding(t, self.freq_dim).to(dtype)
+        return self.fc2(self.fc1(e, act="silu"))
+
+
+class MLP(nn.Module):
+    def __init__(self, dim: int, hidden: int, act: str = "gelu_tanh"):
+        super().__init__()
+        self.fc1 = Linear(dim, hidden)
+        self.fc2 = Linear(hidden, dim)
+        self.act = act
+
+    def forward(self, x, gate=None, residual=None):
+        return self.fc2(self.fc1(x, act=self.act), gate=gate, residual=residual)
+
+
+def split_heads(x: torch.Tensor, heads: int) -> torch.Tensor:
+    b, s, d = x.shape
+    return x.view(b, s, heads, d // heads).transpose(1, 2)
+
+
+def merge_heads(x: torch.Tensor) -> torch.Tensor:
+    b, h, s, d = x.shape
+    return x.transpose(1, 2).reshape(b, s, h * d)
+
+
+def sdpa(q, k, v, causal: bool = False):
+    return attn_ops.attention(q, k, v, causal=causal)

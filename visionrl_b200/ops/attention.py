@@ -1,0 +1,82 @@
+"""Attention entry points (kernels K2 and K8) with a PyTorch oracle.
+
+``attention(q, k, v)`` takes ``[B, H, S, D]`` tensors and returns ``[B, H, S, D]``.
+The oracle is ``softmax(q k^T / sqrt(D)) v`` in fp32.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn.functional as F
+
+
+def attention_reference(q, k, v, causal: bool = False, scale: float | None = None):
+    scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+    s = torch.matmul(q.float(), k.float().transpose(-1, -2)) * scale
+    if causal:
+        sq, sk = s.shape[-2:]
+        mask = torch.ones(sq, sk, dtype=torch.bool, device=s.device).tril(sk - sq)
+        s = s.masked_fill(~mask, float("-inf"))
+    return torch.matmul(torch.softmax(s, dim=-1), v.float()).to(q.dtype)
+
+
+class _FlashFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, scale):
+        from visionrl_b200.ops import _ext
+
+        o, lse = _ext.load().flash_attn_fwd(q.contiguous(), k.contiguous(), v.contiguous(),
+                                            float(scale))
+        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.scale = scale
+        return o
+
+    @staticmethod
+    def backward(ctx, go):
+        from visionrl_b200.ops import _ext
+
+        q, k, v, o, lse = ctx.saved_tensors
+        gq, gk, gv = _ext.load().flash_attn_bwd(go.contiguous(), q, k, v, o, lse, float(ctx.scale))
+        return gq, gk, gv, None
+
+
+def _native_ok(q, k) -> bool:
+    from visionrl_b200.ops import _ext
+
+    return (q.is_cuda and q.dtype == torch.bfloat16 and q.shape[-1] in (64, 128)
+            and _ext.available() and hasattr(_ext.load(), "flash_attn_fwd"))
+
+
+def attention(q, k, v, causal: bool = False, scale: float | None = None):
+    scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+    if not causal and _native_ok(q, k):
+        return _FlashFn.apply(q, k, v, scale)
+    if q.is_cuda:
+        return F.scaled_dot_product_attention(q, k, v, is_causal=causal, scale=scale)
+    return attention_reference(q, k, v, causal, scale)
+
+
+def decode_attention_reference(q, k_cache, v_cache, valid, length: int, scale: float | None = None):
+    """One query position per row against a static cache.
+
+    ``q[R, H, 1, D]``, ``k_cache``/``v_cache`` ``[R, H, max_len, D]``, ``valid[R, max_len]`` marks
+    usable key positions, ``length`` is the number of filled positions.
+    """
+    scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+    k = k_cache[:, :, :length].float()
+    v = v_cache[:, :, :length].float()
+    s = torch.matmul(q.float(), k.transpose(-1, -2)) * scale
+    s = s.masked_fill(~valid[:, None, None, :length], float("-inf"))
+    return torch.matmul(torch.softmax(s, dim=-1), v).to(q.dtype)
+
+
+def decode_attention(q, k_cache, v_cache, valid, length: int, scale: float | None = None):
+    if q.is_cuda and q.dtype == torch.bfloat16 and q.shape[-1] == 128:
+        from visionrl_b200.ops import _ext
+
+        scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+        return _ext.load().decode_attention(q.contiguous(), k_cache, v_cache, valid, int(length),
+                                            float(scale))
+    return decode_attention_reference(q, k_cache, v_cache, valid, length, scale)

@@ -1,0 +1,124 @@
+"""Linear layer on the tcgen05 GEMM (kernel K1) with fused epilogues.
+
+``y = epilogue(x @ w.T + bias)`` where ``w`` is ``[N, K]`` (``nn.Linear`` layout).
+Epilogues: ``act`` ∈ {None, "gelu_tanh", "silu"} and the adaLN gate-residual
+``y = residual + gate[b] * y`` with a per-sample ``gate[B, N]``.  bf16 CUDA inputs
+run the hand-written sm_100a kernel (TMA → shared memory → ``tcgen05.mma`` with
+the accumulator in tensor memory → epilogue from ``tcgen05.ld``); anything else
+(CPU, fp32) takes the PyTorch oracle below.  The backward pass forms ``dX`` and
+``dW`` with the same kernel through its transposed-operand variants.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+_ACTS = {None: 0, "none": 0, "gelu_tanh": 1, "silu": 2}
+
+
+def linear_reference(x, w, bias=None, act=None, gate=None, residual=None):
+    y = F.linear(x, w, bias)
+    if act == "gelu_tanh":
+        y = F.gelu(y, approximate="tanh")
+    elif act == "silu":
+        y = F.silu(y)
+    if gate is not None:
+        y = residual + gate.unsqueeze(1) * y if y.dim() == 3 else residual + gate * y
+    return y
+
+
+def linear_epilogue(y, act=None, gate=None, residual=None):
+    """The epilogue alone, for callers that add a side product before it."""
+    if act == "gelu_tanh":
+        y = F.gelu(y, approximate="tanh")
+    elif act == "silu":
+        y = F.silu(y)
+    if gate is not None:
+        y = residual + (gate.unsqueeze(1) if y.dim() == 3 else gate) * y
+    return y
+
+
+def _use_kernel(x, w) -> bool:
+    return (x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+            and x.shape[-1] % 8 == 0 and w.shape[0] % 8 == 0)
+
+
+def gemm_nt(a, b, bias=None, act=None, gate=None, residual=None, rows_per_gate: int = 0,
+            out_dtype=None):
+    """``a[M,K] @ b[N,K].T`` on the sm_100a kernel (no autograd)."""
+    from visionrl_b200.ops import _ext
+
+    return _ext.load().gemm_bf16(
+        a, b, bias, gate, residual, _ACTS[act], int(rows_per_gate), False, False,
+        out_dtype == torch.float32,
+    )
+
+
+def gemm_nn(a, b):
+    """``a[M,K] @ b[K,N]`` (``b`` row-major, i.e. MN-major operand)."""
+    from visionrl_b200.ops import _ext
+
+    return _ext.load().gemm_bf16(a, b, None, None, None, 0, 0, False, True, False)
+
+
+def gemm_tn(a, b, out_fp32: bool = False):
+    """``a[K,M].T @ b[K,N]`` — both operands MN-major (weight gradients)."""
+    from visionrl_b200.ops import _ext
+
+    return _ext.load().gemm_bf16(a, b, None, None, None, 0, 0, True, True, out_fp32)
+
+
+class _LinearFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, bias):
+        x2 = x.reshape(-1, x.shape[-1])
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        y = gemm_nt(x2, w, bias)
+        ctx.save_for_backward(x2, w)
+        ctx.has_bias = bias is not None
+        ctx.x_shape = x.shape
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, gy):
+        x2, w = ctx.saved_tensors
+        gy2 = gy.reshape(-1, gy.shape[-1])
+        if not gy2.is_contiguous():
+            gy2 = gy2.contiguous()
+        gx = gw = gb = None
+        if ctx.needs_input_grad[0]:
+            gx = gemm_nn(gy2, w).view(ctx.x_shape)
+        if ctx.needs_input_grad[1]:
+            gw = gemm_tn(gy2, x2)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            gb = gy2.float().sum(0).to(gy2.dtype)
+        return gx, gw, gb
+
+
+def linear(x, w, bias=None, act=None, gate=None, residual=None):
+    """Differentiable linear with optional fused epilogue (fused only without grad)."""
+    if not _use_kernel(x, w):
+        return linear_reference(x, w, bias, act, gate, residual)
+    needs_grad = torch.is_grad_enabled() and (
+        x.requires_grad or w.requires_grad or (bias is not None and bias.requires_grad)
+        or (gate is not None and gate.requires_grad)
+        or (residual is not None and residual.requires_grad)
+    )
+    if not needs_grad:
+        x2 = x.reshape(-1, x.shape[-1])
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        rows = x.shape[-2] if (gate is not None and x.dim() == 3) else (1 if gate is not None else 0)
+        res2 = None if residual is None else residual.reshape(-1, w.shape[0])
+        y = gemm_nt(x2, w, bias, act, gate, res2, rows)
+        return y.view(*x.shape[:-1], w.shape[0])
+    y = _LinearFn.apply(x, w, bias)
+    if act == "gelu_tanh":
+        y = F.gelu(y, approximate="tanh")
+    elif act == "silu":
+        y = F.silu(y)
+    if gate is not None:
+        y = residual + (gate.unsqueeze(1) if y.dim() == 3 else gate) * y
+    return y
