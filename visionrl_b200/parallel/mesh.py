@@ -1,0 +1,129 @@
+"""Process mesh ``(dp, sp)`` over ``torch.distributed``.
+
+Ranks are laid out ``rank = dp_rank * sp + sp_rank`` so a sequence-parallel group is
+a run of adjacent ranks (adjacent GPUs).  Parameters are sharded over the whole
+world when ``fsdp`` is on.  One process owns one GPU; with no initialised process
+group everything degenerates to a single rank.
+"""
+
+from __future__ import annotations
+
+import datetime
+import os
+from dataclasses import dataclass
+from typing import Any
+
+import torch
+import torch.distributed as dist
+
+
+def dist_ready() -> bool:
+    return dist.is_available() and dist.is_initialized()
+
+
+def init_distributed(backend: str | None = None, timeout_s: float = 1800.0) -> tuple[int, int, int]:
+    """Initialise from the ``RANK`` / ``WORLD_SIZE`` / ``MASTER_*`` environment (torchrun).
+
+    Returns ``(rank, world_size, local_rank)``.  Without those variables nothing is
+    initialised and ``(0, 1, 0)`` is returned.
+    """
+    if dist_ready():
+        return dist.get_rank(), dist.get_world_size(), int(os.environ.get("LOCAL_RANK", 0))
+    if "RANK" not in os.environ or "WORLD_SIZE" not in os.environ:
+        return 0, 1, 0
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29500")
+    use_cuda = torch.cuda.is_available()
+    if backend is None:
+        backend = "nccl" if use_cuda else "gloo"
+    kwargs: dict[str, Any] = {}
+    if use_cuda:
+        torch.cuda.set_device(local)
+        if backend == "nccl":
+            kwargs["device_id"] = torch.device("cuda", local)
+    dist.init_process_group(backend=backend, init_method="env://", rank=rank, world_size=world,
+                            timeout=datetime.timedelta(seconds=timeout_s), **kwargs)
+    return rank, world, local
+
+
+@dataclass
+class ProcessMesh:
+    rank: int = 0
+    world_size: int = 1
+    dp: int = 1
+    sp: int = 1
+    fsdp: bool = True
+    sp_group: Any = None
+    dp_group: Any = None
+
+    @classmethod
+    def build(cls, sp: int = 1, dp: int = -1, fsdp: bool = True) -> "ProcessMesh":
+        if not dist_ready():
+            if sp not in (1, None):
+                raise ValueError(f"sp={sp} needs an initialised process group")
+            return cls(fsdp=fsdp)
+        rank, world = dist.get_rank(), dist.get_world_size()
+        sp = int(sp or 1)
+        if world % sp != 0:
+            raise ValueError(f"world_size={world} is not divisible by sp={sp}")
+        if dp in (-1, None):
+            dp = world // sp
+        if dp * sp != world:
+            raise ValueError(f"dp*sp = {dp}*{sp} != world_size {world}")
+        sp_group = dp_group = None
+        if sp > 1:
+            for d in range(dp):
+                ranks = list(range(d * sp, (d + 1) * sp))
+                g = dist.new_group(ranks)
+                if rank in ranks:
+                    sp_group = g
+            for s in range(sp):
+                ranks = list(range(s, world, sp))
+                g = dist.new_group(ranks)
+                if rank in ranks:
+                    dp_group = g
+        return cls(rank=rank, world_size=world, dp=dp, sp=sp, fsdp=fsdp, sp_group=sp_group,
+                   dp_group=dp_group)
+
+    @property
+    def dp_rank(self) -> int:
+        return self.rank // self.sp
+
+    @property
+    def sp_rank(self) -> int:
+        return self.rank % self.sp
+
+    @property
+    def is_main(self) -> bool:
+        return self.rank == 0
+
+    def barrier(self) -> None:
+        if dist_ready():
+            dist.barrier()
+
+    def all_gather_1d(self, t: torch.Tensor, group: Any = None) -> torch.Tensor:
+        """Concatenate equally sized 1-D tensors from every rank of ``group``."""
+        if not dist_ready():
+            return t
+        n = dist.get_world_size(group)
+        out = torch.empty(n * t.numel(), dtype=t.dtype, device=t.device)
+        dist.all_gather_into_tensor(out, t.contiguous(), group=group)
+        return out
+
+    def all_gather_varlen(self, t: torch.Tensor, group: Any = None) -> list[torch.Tensor]:
+        """Gather 1-D tensors whose lengths differ between ranks."""
+        if not dist_ready():
+            return [t]
+        n = dist.get_world_size(group)
+        size = torch.tensor([t.numel()], dtype=torch.long, device=t.device)
+        sizes = [torch.zeros_like(size) for _ in range(n)]
+        dist.all_gather(sizes, size, group=group)
+        lens = [int(s.item()) for s in sizes]
+        pad = max(lens) if lens else 0
+        buf = torch.zeros(pad, dtype=t.dtype, device=t.device)
+        buf[: t.numel()] = t
+        outs = [torch.zeros_like(buf) for _ in range(n)]
+        dist.all_gather(outs, buf, group=group)
+        return [o[:k] for o, k in zip(outs, lens)]

@@ -1,0 +1,139 @@
+"""Sharded data-parallel optimiser step: gradient reduce-scatter ⊕ clip ⊕ AdamW ⊕ parameter
+all-gather over flat buffers.
+
+Every rank holds the full bf16 parameters (180 GB of HBM makes that cheap) but only
+``1/world`` of the fp32 master weights and Adam moments.  After backward the flat bf16
+gradient buffer of every rank holds that rank's partial sum.  ``reduce_clip_step`` then
+
+1. reduces the partials so that rank ``r`` owns the mean gradient of slice ``r``
+   (reduce-scatter),
+2. forms the global gradient norm from the per-slice sums of squares (one tiny all-reduce)
+   and the clip coefficient, on the device,
+3. updates slice ``r`` of master weights / moments / bf16 parameters, and
+4. publishes the updated bf16 slice to every rank (all-gather).
+
+``collectives="fused"`` runs steps 1, 3 and 4 inside hand-written kernels that read the
+peers' gradient slices and write the peers' parameter slices directly over NVLink
+(symmetric memory, :mod:`visionrl_b200.parallel.symm`); ``"nccl"`` is the library
+baseline (``reduce_scatter_tensor`` / ``all_gather_into_tensor``), and on CPU/gloo an
+all-reduce based variant keeps the same semantics for tests.
+"""
+
+from __future__ import annotations
+
+from typing import Any
+
+import torch
+import torch.distributed as dist
+
+from visionrl_b200.parallel.mesh import ProcessMesh, dist_ready
+
+
+class ShardedGradSync:
+    def __init__(self, mesh: ProcessMesh, shard_optimizer: bool = True,
+                 collectives: str = "fused") -> None:
+        self.mesh = mesh
+        self.shard_optimizer = shard_optimizer and mesh.world_size > 1
+        self.collectives = collectives
+        self._symm = None
+        self.kernel_launches = 0
+
+    # -- set-up ----------------------------------------------------------------------------
+    def prepare(self, optimizer: Any) -> None:
+        """Configure ``optimizer`` (a flat ``FusedAdamW``) before its buffers are built."""
+        if self.mesh.world_size <= 1:
+            return
+        if self.shard_optimizer and hasattr(optimizer, "set_shard") and not optimizer._built:
+            optimizer.set_shard(self.mesh.rank, self.mesh.world_size)
+        if self.collectives == "fused" and torch.cuda.is_available() and not optimizer._built:
+            from visionrl_b200.parallel.symm import SymmetricPool
+
+            self._symm = SymmetricPool(self.mesh)
+            optimizer.set_allocator(self._symm.allocate)
+
+    # -- the step ----------------------------------------------------------------------------
+    @torch.no_grad()
+    def reduce_clip_step(self, optimizer: Any, max_norm: float) -> torch.Tensor:
+        world = self.mesh.world_size
+        flat = optimizer.flat_buffers()
+        if world <= 1 or not dist_ready():
+            norm = optimizer.grad_norm()
+            coef = (max_norm / (norm + 1e-6)).clamp(max=1.0) if max_norm > 0 else None
+            optimizer.step(clip_coef=coef)
+            optimizer.zero_grad()
+            return norm
+        if self._symm is not None and all(e["param"].is_cuda for e in flat):
+            return self._fused_step(optimizer, flat, max_norm)
+        return self._library_step(optimizer, flat, max_norm)
+
+    def _library_step(self, optimizer, flat, max_norm: float) -> torch.Tensor:
+        world, rank = self.mesh.world_size, self.mesh.rank
+        sq_total = None
+        for e in flat:
+            n, lo = e["shard"], e["lo"]
+            g = e["grad"]
+            if g.is_cuda and self.shard_optimizer:
+                shard = torch.empty(n, dtype=g.dtype, device=g.device)
+                dist.reduce_scatter_tensor(shard, g, op=dist.ReduceOp.AVG)
+            else:
+                dist.all_reduce(g, op=dist.ReduceOp.SUM)
+                g.div_(world)
+                shard = g[lo:lo + n] if self.shard_optimizer else g
+            e["grad_shard"] = shard if self.shard_optimizer else None
+            sq = shard.float().pow(2).sum()
+            if not self.shard_optimizer:
+                sq = sq / world     # every rank holds the whole gradient
+            sq_total = sq if sq_total is None else sq_total + sq
+        dist.all_reduce(sq_total, op=dist.ReduceOp.SUM)
+        norm = sq_total.sqrt()
+        coef = (max_norm / (norm + 1e-6)).clamp(max=1.0) if max_norm > 0 else None
+        optimizer.step(clip_coef=coef)
+        if self.shard_optimizer:
+            for e in flat:
+                p = e["param"]
+                own = p[e["lo"]:e["lo"] + e["shard"]].contiguous()
+                if p.is_cuda:
+                    dist.all_gather_into_tensor(p, own)
+                else:
+                    parts = [torch.empty_like(own) for _ in range(world)]
+                    dist.all_gather(parts, own)
+                    p.copy_(torch.cat(parts))
+                e["grad_shard"] = None
+        optimizer.zero_grad()
+        return norm
+
+    def _fused_step(self, optimizer, flat, max_norm: float) -> torch.Tensor:
+        from visionrl_b200.ops import _ext
+
+        ext = _ext.load()
+        symm = self._symm
+        sq_total = None
+        # phase 1: every rank sums the peers' partials of its own slice (P2P loads), writes the
+        # fp32 mean gradient slice and its sum of squares
+        symm.barrier()
+        for e in flat:
+            peers = symm.peer_pointers(e["grad"])
+            if "grad_f32" not in e:
+                e["grad_f32"] = torch.empty(e["shard"], dtype=torch.float32, device=e["grad"].device)
+            sq = ext.rs_sum_slice(peers, e["grad_f32"], e["lo"], e["shard"], self.mesh.world_size,
+                                  e["grad"].dtype == torch.bfloat16)
+            self.kernel_launches += 1
+            sq_total = sq if sq_total is None else sq_total + sq
+        dist.all_reduce(sq_total, op=dist.ReduceOp.SUM)
+        norm = sq_total.sqrt()
+        coef = (max_norm / (norm + 1e-6)).clamp(max=1.0) if max_norm > 0 \
+            else torch.ones((), device=norm.device)
+        # phase 2: AdamW on the slice, new bf16 values stored into every rank's parameter buffer
+        for e in flat:
+            e["step"] += 1
+            g = e["group"]
+            b1, b2 = g["betas"]
+            ext.adamw_slice_broadcast(
+                symm.peer_pointers(e["param"]), e["grad_f32"], e["master"], e["exp_avg"],
+                e["exp_avg_sq"], e["lo"], e["shard"], self.mesh.world_size, float(g["lr"]),
+                float(b1), float(b2), float(g["eps"]), float(g["weight_decay"]), int(e["step"]),
+                coef, e["param"].dtype == torch.bfloat16)
+            self.kernel_launches += 1
+        symm.barrier()      # peers' stores into our parameter buffer are complete
+        optimizer.zero_grad()
+        return norm

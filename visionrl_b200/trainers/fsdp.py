@@ -1,0 +1,116 @@
+"""Sharded-training utilities under the reference's ``vrl.trainers.fsdp`` names
+(``vrl/trainers/fsdp.py:35-183``).
+
+``fsdp_wrapper`` attaches the native sharded runtime of
+:mod:`visionrl_b200.parallel.sharded` (flat bf16 parameters, fp32 master weights and
+Adam moments sharded over the ranks, gradient reduce-scatter fused with the optimiser
+step) instead of wrapping modules in ``torch.distributed.fsdp``.
+``save_fsdp_checkpoint`` writes rank 0's full state dict to
+``checkpoint-<step>/model.safetensors`` and then barriers.
+"""
+
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass
+from typing import Any
+
+import torch
+import torch.distributed as dist
+from torch import nn
+
+from visionrl_b200.parallel.mesh import ProcessMesh, dist_ready
+from visionrl_b200.parallel.mesh import init_distributed as _init_distributed
+
+
+@dataclass
+class FSDPConfig:
+    sharding_strategy: str = "FULL_SHARD"       # FULL_SHARD | SHARD_GRAD_OP | HYBRID_SHARD | NO_SHARD
+    backward_prefetch: str = "BACKWARD_PRE"
+    cpu_offload: bool = False
+    num_replicate: int = 1
+    num_shard: int = 8
+    mixed_precision_dtype: torch.dtype = torch.bfloat16
+    use_activation_checkpointing: bool = False
+    use_device_mesh: bool = False
+
+
+def fsdp_wrapper(model: nn.Module, config: FSDPConfig | None = None, *,
+                 mesh: ProcessMesh | None = None, collectives: str = "fused") -> nn.Module:
+    """Prepare ``model`` for sharded training and return it (same object).
+
+    The returned module carries ``model.sharded_runtime`` — the object trainers pass as
+    ``grad_sync`` so that gradient reduction, clipping and the sharded AdamW update run
+    as one fused step.
+    """
+    from visionrl_b200.parallel.sharded import ShardedGradSync
+
+    config = config or FSDPConfig()
+    mesh = mesh or ProcessMesh.build()
+    if config.use_activation_checkpointing:
+        enable = getattr(model, "enable_gradient_checkpointing", None)
+        inner = getattr(model, "transformer", None)
+        if callable(enable):
+            enable(True)
+        elif inner is not None and callable(getattr(inner, "enable_gradient_checkpointing", None)):
+            inner.enable_gradient_checkpointing(True)
+    shard = config.sharding_strategy != "NO_SHARD"
+    model.sharded_runtime = ShardedGradSync(mesh, shard_optimizer=shard, collectives=collectives)
+    return model
+
+
+def save_fsdp_checkpoint(model: nn.Module, step: int, output_dir: str, rank: int | None = None) -> str:
+    if rank is None:
+        rank = dist.get_rank() if dist_ready() else 0
+    path = os.path.join(output_dir, f"checkpoint-{step}")
+    if rank == 0:
+        from safetensors.torch import save_file
+
+        os.makedirs(path, exist_ok=True)
+        state = {k: v.detach().cpu().contiguous() for k, v in model.state_dict().items()}
+        save_file(state, os.path.join(path, "model.safetensors"))
+    if dist_ready():
+        dist.barrier()
+    return path
+
+
+class OptimizerOffloadHook:
+    """Keeps optimiser state in host memory between steps: a pre-step hook brings it to
+    the device, a post-step hook returns it."""
+
+    def __init__(self, optimizer: torch.optim.Optimizer, device: torch.device | str = "cuda"):
+        self.optimizer = optimizer
+        self.device = torch.device(device)
+
+    def _move(self, device: torch.device) -> None:
+        for state in self.optimizer.state.values():
+            for k, v in state.items():
+                if isinstance(v, torch.Tensor):
+                    state[k] = v.to(device, non_blocking=True)
+        for entry in getattr(self.optimizer, "_flat", []):
+            for k in ("exp_avg", "exp_avg_sq"):
+                entry[k] = entry[k].to(device, non_blocking=True)
+
+    def pre_step(self, *_: Any) -> None:
+        self._move(self.device)
+
+    def post_step(self, *_: Any) -> None:
+        self._move(torch.device("cpu"))
+
+
+def register_optimizer_offload_hooks(optimizer: torch.optim.Optimizer,
+                                     device: torch.device | str = "cuda") -> OptimizerOffloadHook:
+    hook = OptimizerOffloadHook(optimizer, device)
+    optimizer.register_step_pre_hook(hook.pre_step)
+    optimizer.register_step_post_hook(hook.post_step)
+    hook.post_step()
+    return hook
+
+
+def init_distributed(backend: str | None = None) -> tuple[int, int, int]:
+    """``env://`` rendezvous (NCCL on GPUs, gloo otherwise) → ``(rank, world, local_rank)``."""
+    return _init_distributed(backend)
+
+
+__all__ = ["FSDPConfig", "OptimizerOffloadHook", "fsdp_wrapper", "init_distributed",
+           "register_optimizer_offload_hooks", "save_fsdp_checkpoint"]

@@ -65,8 +65,11 @@ class _AliasFinder(importlib.abc.MetaPathFinder):
         spec = importlib.util.spec_from_loader(
             fullname,
             _AliasLoader(real),
+            origin=real_spec.origin,
             is_package=real_spec.submodule_search_locations is not None,
         )
+        if spec is not None:
+            spec.has_location = real_spec.has_location
         if spec is not None and real_spec.submodule_search_locations is not None:
             spec.submodule_search_locations = list(real_spec.submodule_search_locations)
         return spec
