@@ -1,0 +1,233 @@
+"""Headline benchmark: GRPO samples/sec (rollout + train) of the SD3.5-medium-shape MMDiT.
+
+    python bench.py --gpus N --steps K --warmup W [--impl native|torch_baseline|reference]
+
+Workload: 24 joint blocks, hidden 1536, 24 heads, 16x64x64 latents (1024 image tokens), 154 x 4096
+context + 2048 pooled (synthetic, seeded), 10 SDE steps with CFG 4.5, 8 prompts x group 8 = 64
+samples per step in total (strong scaling: the global batch is fixed, rank r takes prompts
+r, r+N, ...), ViT-L/14 scalar reward on the 512x512 image from a 16-channel VAE decoder,
+full-parameter bf16 training with the flat sharded AdamW.  Every step runs rollout, reward,
+advantages, the per-timestep replay forward/backward and the optimiser update.
+
+Two timings, both through ``OnlineTrainer.step`` (the call a training run makes):
+  * ``value``  — K steps between CUDA events, conditioning already resident on the device;
+  * ``e2e``    — K steps in which the step's prompt conditioning is copied from pinned host
+                 memory and the step's metrics are read back to the host.
+Every rank times on its device; the slowest rank defines the result.  The step's working set
+(4 GB of weights plus activations) is far larger than the 126 MB L2, so no explicit flush is used.
+"""
+
+from __future__ import annotations
+
+import argparse
+import asyncio
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "GRPO samples/sec (rollout+train, device-timed, max over ranks)"
+MODEL = "SD3.5-medium-shape MMDiT (24 blocks, hidden 1536, 24 heads, 1024+154 tokens)"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int) -> None:
+        self.gpu_index = gpu_index
+        self.rows: list[list[str]] = []
+        self._proc = None
+        self._thread = None
+
+    def start(self) -> None:
+        try:
+            self._proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "200", "-i", str(self.gpu_index)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self._proc = None
+            return
+
+        def pump():
+            for line in self._proc.stdout:
+                parts = [x.strip() for x in line.split(",")]
+                if len(parts) >= 9:
+                    self.rows.append(parts)
+
+        self._thread = threading.Thread(target=pump, daemon=True)
+        self._thread.start()
+
+    def stop(self) -> dict:
+        if self._proc is not None:
+            self._proc.terminate()
+            try:
+                self._proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self._proc.kill()
+        sm, sm_max, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[1]))
+                sm_max.append(float(r[2]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, r[5:9]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(sm_max) if sm_max else None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def reference_arm() -> None:
+    """The reference installs offline only with --no-deps; its training path cannot run here."""
+    print(json.dumps({
+        "impl": "reference",
+        "unavailable": "reference stock path needs ray + diffusers + peft + omegaconf and HF "
+                       "checkpoints (none installed, no network); it defines no model in-tree",
+    }))
+
+
+def run(args) -> None:
+    import torch
+    import torch.distributed as dist
+
+    from visionrl_b200.config.loader import load_config
+    from visionrl_b200.ops import _ext
+    from visionrl_b200.scripts.flagship import build_flagship_trainer
+
+    baseline = args.impl == "torch_baseline"
+    if baseline:
+        _ext.set_kernels_enabled(False)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}; launch with torchrun")
+    overrides = [
+        f"distributed.collectives={'nccl' if baseline else args.collectives}",
+        "trainer.output_dir=/tmp/vrl_bench", f"rollout.rollout_batch_size={args.prompts}",
+        f"rollout.n={args.group}", f"rollout.sample_batch_size={args.group}",
+    ] + list(args.override)
+    cfg = load_config("experiment/sd3_5_shape_grpo", overrides=overrides)
+    trainer, prompts = build_flagship_trainer(cfg)
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    device = trainer.device
+    policy = trainer.model
+    text = policy.backend_handle.text
+    samples_per_step = args.prompts * args.group
+
+    def barrier():
+        if dist.is_initialized():
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    async def one_step():
+        return await trainer.step(prompts)
+
+    loop = asyncio.new_event_loop()
+    for _ in range(args.warmup):
+        loop.run_until_complete(one_step())
+    ext_status = _ext.load().gemm_last_status() if not baseline else 0
+    if ext_status:
+        raise RuntimeError(f"GEMM kernel status {ext_status} during warm-up")
+
+    def timed(clear_device_cache: bool):
+        barrier()
+        launches0 = _ext.launch_count
+        text.reset_transfer_stats()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        wall0 = time.perf_counter()
+        start.record()
+        d2h = 0
+        for _ in range(args.steps):
+            if clear_device_cache:
+                text.drop_device_cache()
+            m = loop.run_until_complete(one_step())
+            d2h += trainer.last_d2h_bytes
+        end.record()
+        barrier()
+        wall = time.perf_counter() - wall0
+        ms = start.elapsed_time(end)
+        return ms, wall, _ext.launch_count - launches0, text.h2d_bytes, d2h, m
+
+    sampler = ClockSampler(torch.cuda.current_device())
+    sampler.start()
+    dev_ms, _, launches, _, _, metrics = timed(clear_device_cache=False)
+    clocks = sampler.stop()
+    e2e_ms, e2e_wall, _, h2d, d2h, _ = timed(clear_device_cache=True)
+
+    def max_over_ranks(value: float) -> float:
+        t = torch.tensor([value], device=device, dtype=torch.float64)
+        if dist.is_initialized():
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    dev_ms = max_over_ranks(dev_ms)
+    e2e_s = max_over_ranks(max(e2e_ms / 1e3, e2e_wall))
+    launches = int(max_over_ranks(float(launches)))
+    value = samples_per_step * args.steps / (dev_ms / 1e3)
+    e2e_value = samples_per_step * args.steps / e2e_s
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": round(value, 4), "unit": "samples/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(dev_ms / args.steps, 3), "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "impl": args.impl,
+            "config": {
+                "model": MODEL, "global_batch": samples_per_step, "seq_len": 1024 + 154,
+                "parallelism": f"dp{args.gpus}+sharded-optimizer" if args.gpus > 1 else "single",
+                "prompts": args.prompts, "group_size": args.group, "sde_steps": 10, "cfg": 4.5,
+                "train_timesteps": 9, "reward": "ViT-L/14 scalar head on VAE-decoded 512x512",
+                "l2_policy": "working set (4 GB weights + activations) exceeds the 126 MB L2",
+                "collectives": "nccl" if baseline else args.collectives,
+            },
+            "clocks": clocks,
+            "e2e": {"value": round(e2e_value, 4), "unit": "samples/s",
+                    "h2d_bytes_per_step": int(h2d // max(args.steps, 1)),
+                    "d2h_bytes_per_step": int(d2h // max(args.steps, 1))},
+            "gpu_launches": launches,
+            "last_metrics": {"loss": metrics.loss, "reward_mean": metrics.reward_mean,
+                             "grad_norm": metrics.grad_norm},
+        }
+        print(json.dumps(line))
+    if dist.is_initialized():
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser(description=__doc__.split("\n")[0])
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=2)
+    parser.add_argument("--warmup", type=int, default=3)
+    parser.add_argument("--impl", default="native", choices=["native", "torch_baseline", "reference"])
+    parser.add_argument("--collectives", default="fused", choices=["fused", "nccl"])
+    parser.add_argument("--prompts", type=int, default=8)
+    parser.add_argument("--group", type=int, default=8)
+    parser.add_argument("--override", action="append", default=[],
+                        help="extra config override, e.g. model.arch.num_layers=4")
+    args = parser.parse_args()
+    if args.warmup < 3:
+        print("note: fewer than 3 warm-up steps; the number is not a valid headline", file=sys.stderr)
+    if args.impl == "reference":
+        reference_arm()
+        return
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    run(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,292 @@
+"""Numerics of every sm_100a kernel against a plain PyTorch fp32 reference of the same op."""
+
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ext():
+    from visionrl_b200.ops import _ext
+
+    return _ext.load()
+
+
+def _rel(a, b):
+    return ((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-12)).item()
+
+
+# ---------------------------------------------------------------------------------- GEMM
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (256, 512, 256), (1000, 1536, 1536),
+                                   (77, 264, 200), (4096, 6144, 1536), (16, 9216, 1536)])
+def test_gemm_nt_matches_fp32(ext, m, n, k):
+    torch.manual_seed(0)
+    a = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(n, k, device="cuda", dtype=torch.bfloat16)
+    out = ext.gemm_bf16(a, b, None, None, None, 0, 0, False, False, False)
+    assert ext.gemm_last_status() == 0
+    ref = a.float() @ b.float().t()
+    assert _rel(out, ref) < 5e-3
+
+
+def test_gemm_fp32_output_and_epilogues(ext):
+    torch.manual_seed(1)
+    bsz, s, k, n = 3, 160, 512, 768
+    a = torch.randn(bsz * s, k, device="cuda", dtype=torch.bfloat16) * 0.5
+    w = torch.randn(n, k, device="cuda", dtype=torch.bfloat16) * 0.05
+    bias = torch.randn(n, device="cuda", dtype=torch.bfloat16)
+    gate = torch.randn(bsz, n, device="cuda", dtype=torch.bfloat16)
+    res = torch.randn(bsz * s, n, device="cuda", dtype=torch.bfloat16)
+    base = a.float() @ w.float().t() + bias.float()
+    out32 = ext.gemm_bf16(a, w, bias, None, None, 0, 0, False, False, True)
+    assert out32.dtype == torch.float32 and _rel(out32, base) < 2e-3
+    gelu = ext.gemm_bf16(a, w, bias, None, None, 1, 0, False, False, False)
+    assert _rel(gelu, torch.nn.functional.gelu(base, approximate="tanh")) < 1e-2
+    silu = ext.gemm_bf16(a, w, bias, None, None, 2, 0, False, False, False)
+    assert _rel(silu, torch.nn.functional.silu(base)) < 1e-2
+    gated = ext.gemm_bf16(a, w, bias, gate, res, 0, s, False, False, False)
+    ref = res.float() + gate.float().repeat_interleave(s, 0) * base
+    assert _rel(gated, ref) < 1e-2
+    assert ext.gemm_last_status() == 0
+
+
+@pytest.mark.parametrize("m,n,k", [(256, 256, 128), (1178, 1536, 4608), (300, 520, 136)])
+def test_gemm_transposed_operands(ext, m, n, k):
+    """dX = dY @ W (B stored [K, N]) and dW = dY^T @ X (both operands stored [K, *])."""
+    torch.manual_seed(2)
+    a = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
+    b_kn = torch.randn(k, n, device="cuda", dtype=torch.bfloat16)
+    out = ext.gemm_bf16(a, b_kn, None, None, None, 0, 0, False, True, False)
+    assert _rel(out, a.float() @ b_kn.float()) < 5e-3
+    a_km = torch.randn(k, m, device="cuda", dtype=torch.bfloat16)
+    out2 = ext.gemm_bf16(a_km, b_kn, None, None, None, 0, 0, True, True, False)
+    assert _rel(out2, a_km.float().t() @ b_kn.float()) < 5e-3
+    assert ext.gemm_last_status() == 0
+
+
+def test_linear_autograd_matches_fp32():
+    from visionrl_b200.ops.linear import linear
+
+    torch.manual_seed(3)
+    x = torch.randn(4, 96, 256, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = (torch.randn(512, 256, device="cuda", dtype=torch.bfloat16) * 0.05).requires_grad_()
+    b = torch.randn(512, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    y = linear(x, w, b)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xf, wf, bf = (t.detach().float().requires_grad_() for t in (x, w, b))
+    yf = torch.nn.functional.linear(xf, wf, bf)
+    yf.backward(g.float())
+    assert _rel(y, yf) < 5e-3 and _rel(x.grad, xf.grad) < 1e-2
+    assert _rel(w.grad, wf.grad) < 1e-2 and _rel(b.grad, bf.grad) < 1e-2
+
+
+# ------------------------------------------------------------------------------ SDE step
+@pytest.mark.parametrize("gaussian", [True, False])
+@pytest.mark.parametrize("shape", [(3, 16, 64, 64), (2, 16, 3, 20, 28), (5, 7)])
+def test_sde_step_matches_reference(ext, gaussian, shape):
+    from visionrl_b200.ops.sde import sde_step, sde_step_reference
+
+    torch.manual_seed(4)
+    b = shape[0]
+    v, x, noise = (torch.randn(shape, device="cuda") for _ in range(3))
+    a = 1 + 0.1 * torch.randn(b, device="cuda")
+    bb = -0.1 + 0.02 * torch.randn(b, device="cuda")
+    scale = 0.05 + 0.1 * torch.rand(b, device="cuda")
+    dt = -0.1 * torch.ones(b, device="cuda")
+    got = sde_step(v, x, a, bb, scale, dt, noise=noise, gaussian=gaussian)
+    ref = sde_step_reference(v, x, a, bb, scale, dt, noise=noise, gaussian=gaussian)
+    for g, r in zip(got, ref):
+        assert torch.allclose(g, r, rtol=2e-4, atol=2e-4)
+    # replay with the recorded sample reproduces the rollout log-prob bit for bit
+    again = sde_step(v, x, a, bb, scale, dt, prev_sample=got[0], gaussian=gaussian)
+    assert torch.equal(again[1], got[1])
+    det = sde_step(v, x, a, bb, scale, dt, noise=noise, deterministic=True, gaussian=gaussian)
+    assert torch.allclose(det[0], x + dt.view(-1, *([1] * (len(shape) - 1))) * v, atol=1e-5)
+
+
+def test_sde_step_backward(ext):
+    from visionrl_b200.ops.sde import sde_step, sde_step_reference
+
+    torch.manual_seed(5)
+    shape = (3, 4, 8, 8)
+    x, prev = torch.randn(shape, device="cuda"), torch.randn(shape, device="cuda")
+    a = torch.full((3,), 0.97, device="cuda")
+    b = torch.full((3,), -0.08, device="cuda")
+    scale = torch.full((3,), 0.2, device="cuda")
+    dt = torch.full((3,), -0.1, device="cuda")
+    w_lp, w_mu = torch.randn(3, device="cuda"), torch.randn(shape, device="cuda")
+    grads = []
+    for fn in (sde_step, sde_step_reference):
+        v = torch.randn(shape, device="cuda", generator=torch.Generator("cuda").manual_seed(9),
+                        requires_grad=True)
+        _, lp, mu = fn(v, x, a, b, scale, dt, prev_sample=prev)
+        ((lp * w_lp).sum() + (mu * w_mu).sum()).backward()
+        grads.append(v.grad)
+    assert torch.allclose(grads[0], grads[1], rtol=1e-4, atol=1e-5)
+
+
+# --------------------------------------------------------------------------------- losses
+def test_token_loss_matches_reference(ext):
+    from visionrl_b200.ops.losses import token_grpo_loss, token_grpo_loss_reference
+
+    torch.manual_seed(6)
+    bsz, length = 6, 97
+    old = torch.randn(bsz, length, device="cuda") * 0.1
+    ref = old + 0.05 * torch.randn_like(old)
+    adv = torch.randn(bsz, device="cuda")
+    mask = (torch.rand(bsz, length, device="cuda") > 0.2).float()
+    for kl in ("k3", "k1"):
+        outs = []
+        for fn in (token_grpo_loss, token_grpo_loss_reference):
+            lp = (old + 0.02 * torch.randn(bsz, length, device="cuda",
+                                           generator=torch.Generator("cuda").manual_seed(1))
+                  ).requires_grad_()
+            pol, klv, clip, akl = fn(lp, old, adv, mask, ref, 0.01, kl)
+            (pol + 0.3 * klv).backward()
+            outs.append((pol, klv, clip, akl, lp.grad))
+        for g, r in zip(*outs):
+            assert torch.allclose(g, r, rtol=1e-4, atol=1e-6)
+
+
+def test_grpo_sample_loss_matches_reference(ext):
+    from visionrl_b200.ops.losses import grpo_clipped_loss, grpo_clipped_loss_reference
+
+    torch.manual_seed(7)
+    old = torch.randn(16, device="cuda")
+    adv = torch.randn(16, device="cuda")
+    res = []
+    for fn in (grpo_clipped_loss, grpo_clipped_loss_reference):
+        lp = (old + 1e-4 * torch.arange(16, device="cuda").float() - 5e-4).requires_grad_()
+        loss, clip, akl = fn(lp, old, adv, 1e-4)
+        loss.backward()
+        res.append((loss, clip, akl, lp.grad))
+    for g, r in zip(*res):
+        assert torch.allclose(g, r, rtol=1e-4, atol=1e-7)
+
+
+def test_per_sample_mse_and_sum_squares(ext):
+    torch.manual_seed(8)
+    for dtype in (torch.float32, torch.bfloat16):
+        p = torch.randn(5, 16, 9, 20, 26, device="cuda", dtype=dtype)
+        t = torch.randn_like(p)
+        got = ext.per_sample_mse(p, t)
+        ref = (p.float() - t.float()).pow(2).mean(dim=(1, 2, 3, 4))
+        assert torch.allclose(got, ref, rtol=1e-4)
+        flat = torch.randn(1_000_003 if dtype == torch.float32 else 1_000_008, device="cuda",
+                           dtype=dtype)
+        assert torch.allclose(ext.sum_squares(flat), flat.float().pow(2).sum(), rtol=1e-4)
+
+
+def test_fused_adamw_matches_torch(ext):
+    import copy
+
+    from visionrl_b200.ops.optim import FusedAdamW
+
+    torch.manual_seed(9)
+    net = torch.nn.Sequential(torch.nn.Linear(64, 96), torch.nn.Linear(96, 32)).cuda()
+    ref = copy.deepcopy(net)
+    ours = FusedAdamW(net.parameters(), lr=1e-2, weight_decay=0.05)
+    theirs = torch.optim.AdamW(ref.parameters(), lr=1e-2, weight_decay=0.05)
+    for _ in range(5):
+        x = torch.randn(8, 64, device="cuda")
+        for m, o in ((net, ours), (ref, theirs)):
+            o.zero_grad()
+            m(x).pow(2).mean().backward()
+            o.step()
+    for a, b in zip(net.parameters(), ref.parameters()):
+        assert torch.allclose(a, b, rtol=1e-4, atol=1e-6)
+    assert torch.allclose(ours.grad_norm(), torch.sqrt(sum(p.grad.pow(2).sum()
+                                                         for p in net.parameters())), rtol=1e-4)
+
+
+# ---------------------------------------------------------------------------------- norms
+@pytest.mark.parametrize("d", [64, 1536, 5120])
+def test_adaln_forward_backward(ext, d):
+    from visionrl_b200.ops.norm import adaln_layernorm, adaln_layernorm_reference
+
+    torch.manual_seed(10)
+    b, s = 2, 37
+    res = []
+    for fn in (adaln_layernorm, adaln_layernorm_reference):
+        gen = torch.Generator("cuda").manual_seed(3)
+        x = torch.randn(b, s, d, device="cuda", generator=gen).bfloat16().requires_grad_()
+        sh = (0.1 * torch.randn(b, d, device="cuda", generator=gen)).bfloat16().requires_grad_()
+        sc = (0.1 * torch.randn(b, d, device="cuda", generator=gen)).bfloat16().requires_grad_()
+        y = fn(x, sh, sc)
+        y.backward(torch.randn(y.shape, device="cuda", generator=gen).bfloat16())
+        res.append((y, x.grad, sh.grad, sc.grad))
+    for g, r in zip(*res):
+        assert _rel(g, r) < 2e-2
+
+
+@pytest.mark.parametrize("d", [128, 2048])
+def test_rmsnorm_forward_backward(ext, d):
+    from visionrl_b200.ops.norm import rmsnorm, rmsnorm_reference
+
+    res = []
+    for fn in (rmsnorm, rmsnorm_reference):
+        gen = torch.Generator("cuda").manual_seed(4)
+        x = torch.randn(3, 19, d, device="cuda", generator=gen).bfloat16().requires_grad_()
+        w = (1 + 0.1 * torch.randn(d, device="cuda", generator=gen)).bfloat16().requires_grad_()
+        y = fn(x, w)
+        y.backward(torch.randn(y.shape, device="cuda", generator=gen).bfloat16())
+        res.append((y, x.grad, w.grad))
+    for g, r in zip(*res):
+        assert _rel(g, r) < 2e-2
+
+
+@pytest.mark.parametrize("heads,dh,across,use_rope", [(24, 64, False, False), (12, 128, True, True),
+                                                      (4, 64, False, True), (40, 128, True, True)])
+def test_qkv_prepare_forward_backward(ext, heads, dh, across, use_rope):
+    from visionrl_b200.ops.qkv import qkv_prepare, qkv_prepare_reference
+
+    b, s, d = 2, 21, heads * dh
+    wn = d if across else dh
+    rope = None
+    if use_rope:
+        ang = torch.rand(s, dh // 2, device="cuda") * 6.28
+        rope = (torch.cos(ang), torch.sin(ang))
+    res = []
+    for fn in (qkv_prepare, qkv_prepare_reference):
+        gen = torch.Generator("cuda").manual_seed(5)
+        qkv = torch.randn(b, s, 3 * d, device="cuda", generator=gen).bfloat16().requires_grad_()
+        qw = (1 + 0.1 * torch.randn(wn, device="cuda", generator=gen)).bfloat16().requires_grad_()
+        kw = (1 + 0.1 * torch.randn(wn, device="cuda", generator=gen)).bfloat16().requires_grad_()
+        q, k, v = fn(qkv, heads, qw, kw, rope=rope)
+        gq, gk, gv = (torch.randn(q.shape, device="cuda", generator=gen).bfloat16() for _ in range(3))
+        torch.autograd.backward([q, k, v], [gq, gk, gv])
+        res.append((q, k, v, qkv.grad, qw.grad, kw.grad))
+    for g, r in zip(*res):
+        assert _rel(g, r) < 3e-2
+
+
+# ------------------------------------------------------------------------- model-level parity
+def test_mmdit_forward_backward_kernels_vs_torch_ops():
+    from visionrl_b200.models.nn.mmdit import MMDiT, MMDiTConfig
+    from visionrl_b200.ops import _ext
+
+    torch.manual_seed(11)
+    cfg = MMDiTConfig(num_layers=2, hidden_size=256, num_heads=4, in_channels=16, context_dim=128,
+                      pooled_dim=64, max_grid=32)
+    net = MMDiT(cfg).cuda().bfloat16()
+    lat = torch.randn(2, 16, 16, 16, device="cuda")
+    t = torch.tensor([800.0, 300.0], device="cuda")
+    ctx = torch.randn(2, 24, 128, device="cuda")
+    pooled = torch.randn(2, 64, device="cuda")
+    outs = []
+    for flag in (True, False):
+        _ext.set_kernels_enabled(flag)
+        try:
+            net.zero_grad()
+            y = net(lat, t, ctx, pooled)
+            y.float().pow(2).mean().backward()
+            outs.append((y.detach().clone(), net.blocks[0].attn_x.qkv.weight.grad.clone()))
+        finally:
+            _ext.set_kernels_enabled(True)
+    assert _rel(outs[0][0], outs[1][0]) < 3e-2
+    assert _rel(outs[0][1], outs[1][1]) < 6e-2
+    assert _ext.load().gemm_last_status() == 0

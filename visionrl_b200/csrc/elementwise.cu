@@ -1,0 +1,450 @@
+// Fused element-wise / reduction kernels: SDE step + Gaussian log-prob (K5), GRPO and
+// TokenGRPO losses (K6), per-sample MSE (K14), flat AdamW and gradient norm (K11).
+// All reductions are two-stage with a fixed summation order, so results are bitwise
+// reproducible between the rollout and the training replay of the same step.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include "common.cuh"
+#include "ops.h"
+
+namespace vrl {
+
+// ------------------------------------------------------------------------------------------
+// K5: mu = a x + b v ; x' = mu + scale * eps (or given, or x + dt v) ; sum (x' - mu)^2
+// ------------------------------------------------------------------------------------------
+constexpr int kSdeThreads = 256;
+constexpr int kSdeElemsPerBlock = kSdeThreads * 4 * 4;   // 4 float4 per thread
+
+__global__ void __launch_bounds__(kSdeThreads)
+sde_step_fwd_kernel(const float* __restrict__ v, const float* __restrict__ x,
+                    const float* __restrict__ a, const float* __restrict__ b,
+                    const float* __restrict__ scale, const float* __restrict__ dt,
+                    const float* __restrict__ prev_in, const float* __restrict__ noise,
+                    float* __restrict__ prev_out, float* __restrict__ mean_out,
+                    float* __restrict__ partial, int64_t n, int blocks_per_sample,
+                    int deterministic) {
+  __shared__ float red[32];
+  const int sample = blockIdx.y;
+  const float ca = a[sample], cb = b[sample], cs = scale[sample], cdt = dt[sample];
+  const int64_t base = (int64_t)sample * n;
+  const int64_t start = (int64_t)blockIdx.x * kSdeElemsPerBlock;
+  float acc = 0.f;
+#pragma unroll
+  for (int it = 0; it < 4; ++it) {
+    const int64_t i = start + ((int64_t)it * kSdeThreads + threadIdx.x) * 4;
+    if (i + 3 < n) {
+      const float4 vv = *reinterpret_cast<const float4*>(v + base + i);
+      const float4 xx = *reinterpret_cast<const float4*>(x + base + i);
+      float4 mu, pr;
+      mu.x = ca * xx.x + cb * vv.x; mu.y = ca * xx.y + cb * vv.y;
+      mu.z = ca * xx.z + cb * vv.z; mu.w = ca * xx.w + cb * vv.w;
+      if (prev_in != nullptr) {
+        pr = *reinterpret_cast<const float4*>(prev_in + base + i);
+      } else {
+        const float4 e = *reinterpret_cast<const float4*>(noise + base + i);
+        pr.x = mu.x + cs * e.x; pr.y = mu.y + cs * e.y; pr.z = mu.z + cs * e.z; pr.w = mu.w + cs * e.w;
+      }
+      if (deterministic) {
+        pr.x = xx.x + cdt * vv.x; pr.y = xx.y + cdt * vv.y;
+        pr.z = xx.z + cdt * vv.z; pr.w = xx.w + cdt * vv.w;
+      }
+      *reinterpret_cast<float4*>(mean_out + base + i) = mu;
+      *reinterpret_cast<float4*>(prev_out + base + i) = pr;
+      const float d0 = pr.x - mu.x, d1 = pr.y - mu.y, d2 = pr.z - mu.z, d3 = pr.w - mu.w;
+      acc += d0 * d0 + d1 * d1 + d2 * d2 + d3 * d3;
+    } else {
+      for (int64_t j = i; j < n && j < i + 4; ++j) {
+        const float vv = v[base + j], xx = x[base + j];
+        const float mu = ca * xx + cb * vv;
+        float pr = (prev_in != nullptr) ? prev_in[base + j] : mu + cs * noise[base + j];
+        if (deterministic) pr = xx + cdt * vv;
+        mean_out[base + j] = mu;
+        prev_out[base + j] = pr;
+        acc += (pr - mu) * (pr - mu);
+      }
+    }
+  }
+  const float total = block_sum(acc, red);
+  if (threadIdx.x == 0) partial[(int64_t)sample * blocks_per_sample + blockIdx.x] = total;
+}
+
+__global__ void sde_logprob_finalize_kernel(const float* __restrict__ partial,
+                                            const float* __restrict__ scale,
+                                            float* __restrict__ logp, int blocks_per_sample,
+                                            int64_t n, int gaussian, int batch) {
+  const int sample = blockIdx.x * blockDim.x + threadIdx.x;
+  if (sample >= batch) return;
+  float s = 0.f;
+  for (int i = 0; i < blocks_per_sample; ++i) s += partial[(int64_t)sample * blocks_per_sample + i];
+  const float mean_sq = s / (float)n;
+  if (gaussian) {
+    const float nu = scale[sample];
+    logp[sample] = -mean_sq / (2.f * nu * nu) - logf(nu) - 0.9189385332046727f;
+  } else {
+    logp[sample] = -mean_sq;
+  }
+}
+
+void sde_step_launch(const float* v, const float* x, const float* a, const float* b,
+                     const float* scale, const float* dt, const float* prev_in,
+                     const float* noise, float* prev_out, float* mean_out, float* logp,
+                     float* partial, int batch, int64_t n, bool deterministic, bool gaussian,
+                     cudaStream_t stream) {
+  const int bps = sde_blocks_per_sample(n);
+  dim3 grid(bps, batch);
+  sde_step_fwd_kernel<<<grid, kSdeThreads, 0, stream>>>(v, x, a, b, scale, dt, prev_in, noise,
+                                                        prev_out, mean_out, partial, n, bps,
+                                                        deterministic ? 1 : 0);
+  sde_logprob_finalize_kernel<<<(batch + 127) / 128, 128, 0, stream>>>(partial, scale, logp, bps,
+                                                                       n, gaussian ? 1 : 0, batch);
+}
+
+int sde_blocks_per_sample(int64_t n) {
+  return (int)((n + kSdeElemsPerBlock - 1) / kSdeElemsPerBlock);
+}
+
+std::vector<torch::Tensor> sde_step_fwd(torch::Tensor v, torch::Tensor x, torch::Tensor a,
+                                        torch::Tensor b, torch::Tensor scale, torch::Tensor dt,
+                                        c10::optional<torch::Tensor> prev_sample,
+                                        c10::optional<torch::Tensor> noise, bool deterministic,
+                                        bool gaussian) {
+  TORCH_CHECK(v.is_cuda() && v.scalar_type() == torch::kFloat32 && v.is_contiguous());
+  TORCH_CHECK(x.scalar_type() == torch::kFloat32 && x.is_contiguous() && x.sizes() == v.sizes());
+  TORCH_CHECK(prev_sample.has_value() || noise.has_value(), "need prev_sample or noise");
+  const c10::cuda::CUDAGuard guard(v.device());
+  const int batch = (int)v.size(0);
+  const int64_t n = v.numel() / batch;
+  TORCH_CHECK(n % 4 == 0 || true);
+  auto prev_out = torch::empty_like(v);
+  auto mean_out = torch::empty_like(v);
+  auto logp = torch::empty({batch}, v.options());
+  auto partial = torch::empty({batch, sde_blocks_per_sample(n)}, v.options());
+  const float* prev_ptr = nullptr;
+  const float* noise_ptr = nullptr;
+  torch::Tensor prev_c, noise_c;
+  if (prev_sample.has_value()) {
+    prev_c = prev_sample->contiguous();
+    TORCH_CHECK(prev_c.scalar_type() == torch::kFloat32 && prev_c.numel() == v.numel());
+    prev_ptr = prev_c.data_ptr<float>();
+  } else {
+    noise_c = noise->contiguous();
+    TORCH_CHECK(noise_c.scalar_type() == torch::kFloat32 && noise_c.numel() == v.numel());
+    noise_ptr = noise_c.data_ptr<float>();
+  }
+  auto f = [](torch::Tensor& t) { t = t.to(torch::kFloat32).contiguous(); return t.data_ptr<float>(); };
+  sde_step_launch(v.data_ptr<float>(), x.data_ptr<float>(), f(a), f(b), f(scale), f(dt), prev_ptr,
+                  noise_ptr, prev_out.data_ptr<float>(), mean_out.data_ptr<float>(),
+                  logp.data_ptr<float>(), partial.data_ptr<float>(), batch, n, deterministic,
+                  gaussian, at::cuda::getCurrentCUDAStream());
+  return {prev_out, logp, mean_out};
+}
+
+__global__ void sde_step_bwd_kernel(const float* __restrict__ prev, const float* __restrict__ mean,
+                                    const float* __restrict__ a, const float* __restrict__ b,
+                                    const float* __restrict__ scale,
+                                    const float* __restrict__ g_logp,
+                                    const float* __restrict__ g_mean, float* __restrict__ g_v,
+                                    float* __restrict__ g_x, int64_t n, int gaussian) {
+  const int sample = blockIdx.y;
+  const float ca = a[sample], cb = b[sample], nu = scale[sample];
+  // d logp / d mu_i = (x'_i - mu_i) * k
+  const float k = g_logp[sample] * (gaussian ? 1.f / (nu * nu * (float)n) : 2.f / (float)n);
+  const int64_t base = (int64_t)sample * n;
+  for (int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < n;
+       i += (int64_t)gridDim.x * blockDim.x * 4) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (i + j < n) {
+        float gm = (prev[base + i + j] - mean[base + i + j]) * k;
+        if (g_mean != nullptr) gm += g_mean[base + i + j];
+        g_v[base + i + j] = gm * cb;
+        g_x[base + i + j] = gm * ca;
+      }
+    }
+  }
+}
+
+std::vector<torch::Tensor> sde_step_bwd(torch::Tensor prev, torch::Tensor mean, torch::Tensor a,
+                                        torch::Tensor b, torch::Tensor scale, torch::Tensor g_logp,
+                                        c10::optional<torch::Tensor> g_mean, bool gaussian) {
+  const c10::cuda::CUDAGuard guard(prev.device());
+  const int batch = (int)prev.size(0);
+  const int64_t n = prev.numel() / batch;
+  auto g_v = torch::empty_like(prev);
+  auto g_x = torch::empty_like(prev);
+  torch::Tensor gm;
+  const float* gm_ptr = nullptr;
+  if (g_mean.has_value()) {
+    gm = g_mean->to(torch::kFloat32).contiguous();
+    gm_ptr = gm.data_ptr<float>();
+  }
+  a = a.to(torch::kFloat32).contiguous();
+  b = b.to(torch::kFloat32).contiguous();
+  scale = scale.to(torch::kFloat32).contiguous();
+  g_logp = g_logp.to(torch::kFloat32).contiguous();
+  const int bx = (int)std::min<int64_t>((n / 4 + 255) / 256, 64);
+  sde_step_bwd_kernel<<<dim3(std::max(bx, 1), batch), 256, 0, at::cuda::getCurrentCUDAStream()>>>(
+      prev.data_ptr<float>(), mean.data_ptr<float>(), a.data_ptr<float>(), b.data_ptr<float>(),
+      scale.data_ptr<float>(), g_logp.data_ptr<float>(), gm_ptr, g_v.data_ptr<float>(),
+      g_x.data_ptr<float>(), n, gaussian ? 1 : 0);
+  return {g_v, g_x};
+}
+
+// ------------------------------------------------------------------------------------------
+// K6: clipped surrogate over [B, L] tokens (L = 1 gives the per-sample GRPO loss)
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024)
+token_loss_kernel(const float* __restrict__ lp, const float* __restrict__ old,
+                  const float* __restrict__ adv, const float* __restrict__ mask,
+                  const float* __restrict__ ref, float* __restrict__ out,
+                  float* __restrict__ g_pol, float* __restrict__ g_kl, int batch, int len,
+                  float eps_clip, int k3) {
+  __shared__ float red[32];
+  const int total = batch * len;
+  float s_loss = 0.f, s_kl = 0.f, s_clip = 0.f, s_akl = 0.f, s_mask = 0.f, s_valid = 0.f;
+  for (int i = threadIdx.x; i < total; i += blockDim.x) {
+    const float m = mask ? mask[i] : 1.f;
+    const float a = adv[i / len];
+    const float d = lp[i] - old[i];
+    const float r = __expf(d);
+    const float rc = fminf(fmaxf(r, 1.f - eps_clip), 1.f + eps_clip);
+    const float un = -a * r, cl = -a * rc;
+    s_loss += fmaxf(un, cl) * m;
+    if (ref) {
+      const float dr = lp[i] - ref[i];
+      s_kl += (k3 ? (__expf(dr) * (dr - 1.f) + 1.f) : dr) * m;
+    }
+    const float valid = m > 0.f ? 1.f : 0.f;
+    s_clip += (fabsf(r - 1.f) > eps_clip ? 1.f : 0.f) * valid;
+    s_akl += 0.5f * d * d * valid;
+    s_mask += m;
+    s_valid += valid;
+  }
+  s_loss = block_sum(s_loss, red);
+  s_kl = block_sum(s_kl, red);
+  s_clip = block_sum(s_clip, red);
+  s_akl = block_sum(s_akl, red);
+  s_mask = block_sum(s_mask, red);
+  s_valid = block_sum(s_valid, red);
+  const float denom = fmaxf(s_mask, 1.f), nvalid = fmaxf(s_valid, 1.f);
+  if (threadIdx.x == 0) {
+    out[0] = s_loss / denom;
+    out[1] = s_kl / denom;
+    out[2] = s_clip / nvalid;
+    out[3] = s_akl / nvalid;
+  }
+  for (int i = threadIdx.x; i < total; i += blockDim.x) {
+    const float m = mask ? mask[i] : 1.f;
+    const float a = adv[i / len];
+    const float r = __expf(lp[i] - old[i]);
+    const bool inside = (r >= 1.f - eps_clip) && (r <= 1.f + eps_clip);
+    const float rc = fminf(fmaxf(r, 1.f - eps_clip), 1.f + eps_clip);
+    const bool unclipped_active = inside || (-a * r > -a * rc);
+    g_pol[i] = unclipped_active ? (-a * r) * m / denom : 0.f;
+    if (ref) {
+      const float dr = lp[i] - ref[i];
+      g_kl[i] = (k3 ? __expf(dr) * dr : 1.f) * m / denom;
+    } else {
+      g_kl[i] = 0.f;
+    }
+  }
+}
+
+std::vector<torch::Tensor> token_loss_fwd(torch::Tensor lp, torch::Tensor old, torch::Tensor adv,
+                                          c10::optional<torch::Tensor> mask,
+                                          c10::optional<torch::Tensor> ref, double eps_clip,
+                                          bool k3) {
+  TORCH_CHECK(lp.is_cuda() && lp.dim() == 2 && lp.scalar_type() == torch::kFloat32);
+  const c10::cuda::CUDAGuard guard(lp.device());
+  const int batch = (int)lp.size(0), len = (int)lp.size(1);
+  old = old.to(torch::kFloat32).contiguous();
+  adv = adv.to(torch::kFloat32).contiguous();
+  TORCH_CHECK(old.numel() == lp.numel() && adv.numel() == batch);
+  torch::Tensor m, r;
+  const float* mp = nullptr;
+  const float* rp = nullptr;
+  if (mask.has_value()) { m = mask->to(torch::kFloat32).contiguous(); mp = m.data_ptr<float>(); }
+  if (ref.has_value()) { r = ref->to(torch::kFloat32).contiguous(); rp = r.data_ptr<float>(); }
+  auto out = torch::empty({4}, lp.options());
+  auto g_pol = torch::empty_like(lp);
+  auto g_kl = torch::empty_like(lp);
+  token_loss_kernel<<<1, 1024, 0, at::cuda::getCurrentCUDAStream()>>>(
+      lp.data_ptr<float>(), old.data_ptr<float>(), adv.data_ptr<float>(), mp, rp,
+      out.data_ptr<float>(), g_pol.data_ptr<float>(), g_kl.data_ptr<float>(), batch, len,
+      (float)eps_clip, k3 ? 1 : 0);
+  return {out, g_pol, g_kl};
+}
+
+// ------------------------------------------------------------------------------------------
+// K14 helper: per-sample mean squared error, any of fp32 / bf16 inputs
+// ------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void mse_partial_kernel(const T* __restrict__ p, const T* __restrict__ t,
+                                   float* __restrict__ partial, int64_t n, int bps) {
+  __shared__ float red[32];
+  const int sample = blockIdx.y;
+  const int64_t base = (int64_t)sample * n;
+  float acc = 0.f;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const float d = to_f<T>(p[base + i]) - to_f<T>(t[base + i]);
+    acc += d * d;
+  }
+  const float s = block_sum(acc, red);
+  if (threadIdx.x == 0) partial[(int64_t)sample * bps + blockIdx.x] = s;
+}
+
+__global__ void mean_finalize_kernel(const float* __restrict__ partial, float* __restrict__ out,
+                                     int bps, float inv_n, int batch) {
+  const int sample = blockIdx.x * blockDim.x + threadIdx.x;
+  if (sample >= batch) return;
+  float s = 0.f;
+  for (int i = 0; i < bps; ++i) s += partial[(int64_t)sample * bps + i];
+  out[sample] = s * inv_n;
+}
+
+torch::Tensor per_sample_mse(torch::Tensor pred, torch::Tensor target) {
+  TORCH_CHECK(pred.is_cuda() && pred.sizes() == target.sizes() && pred.dtype() == target.dtype());
+  const c10::cuda::CUDAGuard guard(pred.device());
+  pred = pred.contiguous();
+  target = target.contiguous();
+  const int batch = (int)pred.size(0);
+  const int64_t n = pred.numel() / batch;
+  const int bps = (int)std::min<int64_t>((n + 4095) / 4096, 128);
+  auto partial = torch::empty({batch, bps}, pred.options().dtype(torch::kFloat32));
+  auto out = torch::empty({batch}, pred.options().dtype(torch::kFloat32));
+  auto stream = at::cuda::getCurrentCUDAStream();
+  if (pred.scalar_type() == torch::kFloat32) {
+    mse_partial_kernel<float><<<dim3(bps, batch), 256, 0, stream>>>(
+        pred.data_ptr<float>(), target.data_ptr<float>(), partial.data_ptr<float>(), n, bps);
+  } else {
+    TORCH_CHECK(pred.scalar_type() == torch::kBFloat16, "per_sample_mse: fp32 or bf16");
+    mse_partial_kernel<__nv_bfloat16><<<dim3(bps, batch), 256, 0, stream>>>(
+        reinterpret_cast<const __nv_bfloat16*>(pred.data_ptr()),
+        reinterpret_cast<const __nv_bfloat16*>(target.data_ptr()), partial.data_ptr<float>(), n, bps);
+  }
+  mean_finalize_kernel<<<(batch + 127) / 128, 128, 0, stream>>>(
+      partial.data_ptr<float>(), out.data_ptr<float>(), bps, 1.f / (float)n, batch);
+  return out;
+}
+
+// ------------------------------------------------------------------------------------------
+// K11: sum of squares of a flat gradient buffer and the flat AdamW update
+// ------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void sumsq_partial_kernel(const T* __restrict__ g, float* __restrict__ partial,
+                                     int64_t n) {
+  __shared__ float red[32];
+  float acc = 0.f;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const float x = to_f<T>(g[i]);
+    acc += x * x;
+  }
+  const float s = block_sum(acc, red);
+  if (threadIdx.x == 0) partial[blockIdx.x] = s;
+}
+
+__global__ void sumsq_partial_bf16x8_kernel(const bf16x8* __restrict__ g,
+                                            float* __restrict__ partial, int64_t nvec) {
+  __shared__ float red[32];
+  float acc = 0.f;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    float f[8];
+    unpack8(g[i], f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc += f[j] * f[j];
+  }
+  const float s = block_sum(acc, red);
+  if (threadIdx.x == 0) partial[blockIdx.x] = s;
+}
+
+__global__ void sum_finalize_kernel(const float* __restrict__ partial, float* __restrict__ out,
+                                    int count) {
+  __shared__ float red[32];
+  float acc = 0.f;
+  for (int i = threadIdx.x; i < count; i += blockDim.x) acc += partial[i];
+  const float s = block_sum(acc, red);
+  if (threadIdx.x == 0) out[0] = s;
+}
+
+torch::Tensor sum_squares(torch::Tensor g) {
+  TORCH_CHECK(g.is_cuda() && g.is_contiguous());
+  const c10::cuda::CUDAGuard guard(g.device());
+  const int64_t n = g.numel();
+  const int blocks = (int)std::max<int64_t>(1, std::min<int64_t>((n + 8191) / 8192, 148 * 8));
+  auto partial = torch::empty({blocks}, g.options().dtype(torch::kFloat32));
+  auto out = torch::empty({}, g.options().dtype(torch::kFloat32));
+  auto stream = at::cuda::getCurrentCUDAStream();
+  if (g.scalar_type() == torch::kBFloat16 && n % 8 == 0 &&
+      reinterpret_cast<uintptr_t>(g.data_ptr()) % 16 == 0) {
+    sumsq_partial_bf16x8_kernel<<<blocks, 256, 0, stream>>>(
+        reinterpret_cast<const bf16x8*>(g.data_ptr()), partial.data_ptr<float>(), n / 8);
+  } else if (g.scalar_type() == torch::kBFloat16) {
+    sumsq_partial_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(
+        reinterpret_cast<const __nv_bfloat16*>(g.data_ptr()), partial.data_ptr<float>(), n);
+  } else {
+    TORCH_CHECK(g.scalar_type() == torch::kFloat32, "sum_squares: fp32 or bf16");
+    sumsq_partial_kernel<float><<<blocks, 256, 0, stream>>>(g.data_ptr<float>(),
+                                                           partial.data_ptr<float>(), n);
+  }
+  sum_finalize_kernel<<<1, 256, 0, stream>>>(partial.data_ptr<float>(), out.data_ptr<float>(), blocks);
+  return out;
+}
+
+template <typename TP, typename TG>
+__global__ void adamw_flat_kernel(TP* __restrict__ p, const TG* __restrict__ g,
+                                  float* __restrict__ master, float* __restrict__ m,
+                                  float* __restrict__ v, int64_t n, float lr, float b1, float b2,
+                                  float eps, float wd, float bc1, float bc2,
+                                  const float* __restrict__ clip, int master_is_param) {
+  const float coef = clip ? clip[0] : 1.f;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const float grad = to_f<TG>(g[i]) * coef;
+    const float mi = b1 * m[i] + (1.f - b1) * grad;
+    const float vi = b2 * v[i] + (1.f - b2) * grad * grad;
+    m[i] = mi;
+    v[i] = vi;
+    float w = master[i];
+    w = w * (1.f - lr * wd) - lr * (mi / bc1) / (sqrtf(vi / bc2) + eps);
+    master[i] = w;
+    if (!master_is_param) p[i] = from_f<TP>(w);
+  }
+}
+
+void adamw_flat(torch::Tensor p, torch::Tensor g, torch::Tensor master, torch::Tensor m,
+                torch::Tensor v, double lr, double b1, double b2, double eps, double wd,
+                int64_t step, c10::optional<torch::Tensor> clip) {
+  TORCH_CHECK(p.is_cuda() && p.is_contiguous() && g.is_contiguous());
+  TORCH_CHECK(master.scalar_type() == torch::kFloat32 && m.scalar_type() == torch::kFloat32);
+  const c10::cuda::CUDAGuard guard(p.device());
+  const int64_t n = p.numel();
+  TORCH_CHECK(g.numel() == n && master.numel() == n && m.numel() == n && v.numel() == n);
+  const float bc1 = 1.f - (float)std::pow(b1, (double)step);
+  const float bc2 = 1.f - (float)std::pow(b2, (double)step);
+  torch::Tensor c;
+  const float* cp = nullptr;
+  if (clip.has_value()) { c = clip->to(torch::kFloat32).contiguous(); cp = c.data_ptr<float>(); }
+  const int blocks = (int)std::max<int64_t>(1, std::min<int64_t>((n + 1023) / 1024, 148 * 16));
+  auto stream = at::cuda::getCurrentCUDAStream();
+  const int same = master.data_ptr() == p.data_ptr() ? 1 : 0;
+#define LAUNCH(TP, TG)                                                                         \
+  adamw_flat_kernel<TP, TG><<<blocks, 256, 0, stream>>>(                                       \
+      reinterpret_cast<TP*>(p.data_ptr()), reinterpret_cast<const TG*>(g.data_ptr()),          \
+      master.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(), n, (float)lr,        \
+      (float)b1, (float)b2, (float)eps, (float)wd, bc1, bc2, cp, same)
+  const bool pb = p.scalar_type() == torch::kBFloat16, gb = g.scalar_type() == torch::kBFloat16;
+  TORCH_CHECK(pb || p.scalar_type() == torch::kFloat32);
+  TORCH_CHECK(gb || g.scalar_type() == torch::kFloat32);
+  if (pb && gb) LAUNCH(__nv_bfloat16, __nv_bfloat16);
+  else if (pb && !gb) LAUNCH(__nv_bfloat16, float);
+  else if (!pb && gb) LAUNCH(float, __nv_bfloat16);
+  else LAUNCH(float, float);
+#undef LAUNCH
+}
+
+}  // namespace vrl

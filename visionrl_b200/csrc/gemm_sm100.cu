@@ -1,0 +1,487 @@
+// K1: persistent bf16 GEMM for sm_100a.  C[M,N] = epilogue(A · B^T) with fp32 accumulation.
+//
+//   * operands reach shared memory through TMA (cp.async.bulk.tensor, 128-byte swizzle,
+//     no cluster multicast), four pipeline stages of a 128x64 A tile and a 256x64 B tile;
+//   * one elected thread issues tcgen05.mma (cta_group::1, kind::f16, M=128, N=256, K=16);
+//     the accumulator lives in tensor memory, double-buffered (2 x 256 columns) so the
+//     epilogue of tile i overlaps the main loop of tile i+1;
+//   * four epilogue warps read the accumulator with tcgen05.ld (32 lanes x 32 columns),
+//     apply bias / GELU-tanh / SiLU / adaLN gate-residual in registers and store bf16 or fp32;
+//   * either operand may be "MN-major" (stored [K, M] resp. [K, N] with the non-contracted
+//     dimension contiguous), which is what the backward GEMMs dX = dY·W and dW = dY^T·X need;
+//   * every mbarrier wait is bounded: on expiry the kernel records where it gave up in a
+//     status word, drains its own TMA copies (bounded as well), frees its tensor memory and
+//     returns; the host raises after the launch completes.
+//
+// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer and TMEM owner,
+// warps 2..5 = epilogue (warp w may only touch TMEM lanes 32*(w%4) .. 32*(w%4)+31).
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <cuda.h>
+#include <cudaTypedefs.h>
+#include <torch/extension.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "common.cuh"
+#include "ops.h"
+
+namespace vrl {
+namespace gemm {
+
+constexpr int BM = 128, BN = 256, BK = 64;
+constexpr int UMMA_K = 16;
+constexpr int kStages = 4;
+constexpr int kThreads = 192;
+constexpr uint32_t kABytes = BM * BK * 2;          // 16 KiB
+constexpr uint32_t kBBytes = BN * BK * 2;          // 32 KiB
+constexpr uint32_t kStageBytes = kABytes + kBBytes;
+constexpr uint32_t kTmemCols = 512;                // two 256-column fp32 accumulators
+constexpr uint32_t kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+constexpr uint32_t kSpinLimit = 1u << 26;          // ~ a second of polling at most
+
+enum Status : int { kOk = 0, kTimeoutProducer = 1, kTimeoutMma = 2, kTimeoutEpilogue = 3 };
+
+struct Params {
+  void* c;
+  const __nv_bfloat16* bias;       // [N] or null
+  const __nv_bfloat16* gate;       // [M / rows_per_gate, N] or null
+  const __nv_bfloat16* residual;   // [M, N] or null
+  int* status;
+  int m, n, k;
+  int act;                         // 0 none, 1 gelu-tanh, 2 silu
+  int rows_per_gate;
+  int a_mn, b_mn;
+  int out_fp32;
+};
+
+// ------------------------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+               "r"(bytes)
+               : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Bounded wait.  Returns false when the limit ran out or another role already gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+    if (mbar_try(bar, parity)) return true;
+    if ((spin & 1023u) == 1023u && *abort_flag) return false;
+  }
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar,
+                                            int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];" ::"r"(smem_u32(dst)),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                   smem_u32(slot)),
+               "r"(cols));
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+}
+
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols));
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_c, uint64_t desc_a, uint64_t desc_b,
+                                          uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_c),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   smem_u32(bar))
+               : "memory");
+}
+
+__device__ __forceinline__ void tmem_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, "
+      "%20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle.  Addresses and offsets are in 16-byte
+// units.  K-major tile: rows of 128 bytes, 8-row groups 1024 bytes apart (SBO), LBO unused (1).
+// MN-major tile: 64-element chunks of the non-contracted dimension `lbo_bytes` apart, rows of
+// the contracted dimension 128 bytes apart, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_bytes,
+                                              uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 46;          // descriptor version for sm_100
+  d |= (uint64_t)2 << 61;          // SWIZZLE_128B
+  return d;
+}
+
+__host__ __device__ constexpr uint32_t make_idesc(int a_mn, int b_mn) {
+  return (1u << 4)                       // accumulator fp32
+         | (1u << 7) | (1u << 10)        // A, B = bf16
+         | ((uint32_t)a_mn << 15) | ((uint32_t)b_mn << 16)
+         | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+// ------------------------------------------------------------------------------------- kernel
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                 const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
+  uint64_t* full = bars;                       // [kStages]
+  uint64_t* empty = bars + kStages;            // [kStages]
+  uint64_t* acc_full = bars + 2 * kStages;     // [2]
+  uint64_t* acc_empty = bars + 2 * kStages + 2;  // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m_tiles = (p.m + BM - 1) / BM, n_tiles = (p.n + BN - 1) / BN;
+  const int num_tiles = m_tiles * n_tiles;
+  const int k_blocks = (p.k + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, kTmemCols);
+  tmem_fence_before();
+  __syncthreads();
+  tmem_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0 && lane == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    uint32_t it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      const int m0 = (tile / n_tiles) * BM, n0 = (tile % n_tiles) * BN;
+      for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        const int s = it % kStages;
+        const uint32_t parity = ((it / kStages) & 1u) ^ 1u;
+        if (!mbar_wait(&empty[s], parity, abort_flag)) { ok = false; break; }
+        uint8_t* sa = smem + s * kStageBytes;
+        uint8_t* sb = sa + kABytes;
+        mbar_expect_tx(&full[s], kStageBytes);
+        const int k0 = kb * BK;
+        if (!p.a_mn) {
+          tma_load_2d(sa, &map_a, &full[s], k0, m0);
+        } else {
+#pragma unroll
+          for (int c = 0; c < BM / 64; ++c)
+            tma_load_2d(sa + c * (BK * 128), &map_a, &full[s], m0 + c * 64, k0);
+        }
+        if (!p.b_mn) {
+          tma_load_2d(sb, &map_b, &full[s], k0, n0);
+        } else {
+#pragma unroll
+          for (int c = 0; c < BN / 64; ++c)
+            tma_load_2d(sb + c * (BK * 128), &map_b, &full[s], n0 + c * 64, k0);
+        }
+      }
+    }
+    if (!ok) {
+      if (atomicCAS(const_cast<int*>(abort_flag), 0, 1) == 0) atomicExch(p.status, kTimeoutProducer);
+    }
+    // copies still in flight target this CTA's shared memory: give them time to land
+    if (*abort_flag) {
+      const uint32_t issued = it;
+      for (uint32_t j = issued > (uint32_t)kStages ? issued - kStages : 0; j < issued; ++j) {
+        const int s = j % kStages;
+        for (uint32_t spin = 0; spin < (1u << 20); ++spin)
+          if (mbar_try(&full[s], (j / kStages) & 1u)) break;
+      }
+    }
+  } else if (warp == 1 && lane == 0) {
+    // -------------------------------------------------------------------- MMA issuer
+    const uint32_t idesc = make_idesc(p.a_mn, p.b_mn);
+    uint32_t it = 0, tile_it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_it) {
+      const uint32_t buf = tile_it & 1u;
+      if (!mbar_wait(&acc_empty[buf], ((tile_it >> 1) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+      tmem_fence_after();
+      const uint32_t tmem_c = tmem_base + buf * BN;
+      for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        const int s = it % kStages;
+        if (!mbar_wait(&full[s], (it / kStages) & 1u, abort_flag)) { ok = false; break; }
+        tmem_fence_after();
+        const uint32_t sa = smem_u32(smem + s * kStageBytes), sb = sa + kABytes;
+#pragma unroll
+        for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+          const uint64_t da = p.a_mn ? make_desc(sa + kk * UMMA_K * 128, BK * 128, 1024)
+                                     : make_desc(sa + kk * UMMA_K * 2, 16, 1024);
+          const uint64_t db = p.b_mn ? make_desc(sb + kk * UMMA_K * 128, BK * 128, 1024)
+                                     : make_desc(sb + kk * UMMA_K * 2, 16, 1024);
+          umma_bf16(tmem_c, da, db, idesc, (kb | kk) ? 1u : 0u);
+        }
+        umma_commit(&empty[s]);           // frees the stage once these MMAs have read it
+      }
+      if (ok) umma_commit(&acc_full[buf]);
+    }
+    if (!ok) {
+      if (atomicCAS(const_cast<int*>(abort_flag), 0, 1) == 0) atomicExch(p.status, kTimeoutMma);
+    }
+  } else if (warp >= 2) {
+    // ---------------------------------------------------------------------- epilogue
+    const int quarter = warp & 3;                 // TMEM lane quarter this warp may read
+    uint32_t tile_it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_it) {
+      const uint32_t buf = tile_it & 1u;
+      const int m0 = (tile / n_tiles) * BM, n0 = (tile % n_tiles) * BN;
+      if (!mbar_wait(&acc_full[buf], (tile_it >> 1) & 1u, abort_flag)) { ok = false; break; }
+      tmem_fence_after();
+      const int row = m0 + quarter * 32 + lane;
+      const bool row_ok = row < p.m;
+      const int64_t gate_row = p.gate ? (row / p.rows_per_gate) : 0;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN + c * 32, r);
+        const int col0 = n0 + c * 32;
+        if (!row_ok || col0 >= p.n) continue;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const int col = col0 + g * 8;
+          if (col >= p.n) break;
+          float v[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[g * 8 + j]);
+          if (p.bias) {
+            float b[8];
+            unpack8(*reinterpret_cast<const bf16x8*>(p.bias + col), b);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] += b[j];
+          }
+          if (p.act == 1) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = gelu_tanh(v[j]);
+          } else if (p.act == 2) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = silu(v[j]);
+          }
+          if (p.gate) {
+            float gt[8], rs[8];
+            unpack8(*reinterpret_cast<const bf16x8*>(p.gate + gate_row * p.n + col), gt);
+            unpack8(*reinterpret_cast<const bf16x8*>(p.residual + (int64_t)row * p.n + col), rs);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = rs[j] + gt[j] * v[j];
+          } else if (p.residual) {
+            float rs[8];
+            unpack8(*reinterpret_cast<const bf16x8*>(p.residual + (int64_t)row * p.n + col), rs);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] += rs[j];
+          }
+          if (p.out_fp32) {
+            float* dst = reinterpret_cast<float*>(p.c) + (int64_t)row * p.n + col;
+            *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+            *reinterpret_cast<float4*>(dst + 4) = make_float4(v[4], v[5], v[6], v[7]);
+          } else {
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.c) + (int64_t)row * p.n + col;
+            *reinterpret_cast<bf16x8*>(dst) = pack8(v);
+          }
+        }
+      }
+      tmem_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[buf]);
+    }
+    if (!ok && lane == 0) {
+      if (atomicCAS(const_cast<int*>(abort_flag), 0, 1) == 0) atomicExch(p.status, kTimeoutEpilogue);
+    }
+  }
+
+  tmem_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tmem_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// --------------------------------------------------------------------------------- host side
+using EncodeFn = PFN_cuTensorMapEncodeTiled_v12000;
+
+static EncodeFn encode_fn() {
+  static EncodeFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    C10_CUDA_CHECK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q));
+    TORCH_CHECK(ptr != nullptr && q == cudaDriverEntryPointSuccess,
+                "cuTensorMapEncodeTiled is not available from this driver");
+    fn = reinterpret_cast<EncodeFn>(ptr);
+  });
+  return fn;
+}
+
+// 2-D bf16 tensor map: `inner` contiguous elements, `outer` rows of pitch `pitch_elems`.
+static CUtensorMap make_map(const void* base, uint64_t inner, uint64_t outer, uint64_t pitch_elems,
+                            uint32_t box_inner, uint32_t box_outer) {
+  CUtensorMap map;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {pitch_elems * 2};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t elem[2] = {1, 1};
+  CUresult rc = encode_fn()(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims,
+                            strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  TORCH_CHECK(rc == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with code ", (int)rc,
+              " (base must be 16-byte aligned, pitch a multiple of 16 bytes)");
+  return map;
+}
+
+static int* status_word(int device) {
+  static std::map<int, int*> words;
+  static std::mutex mu;
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = words.find(device);
+  if (it != words.end()) return it->second;
+  int* w = nullptr;
+  C10_CUDA_CHECK(cudaMalloc(&w, sizeof(int)));
+  C10_CUDA_CHECK(cudaMemset(w, 0, sizeof(int)));
+  words[device] = w;
+  return w;
+}
+
+}  // namespace gemm
+
+int64_t gemm_last_status() {
+  int device = 0;
+  C10_CUDA_CHECK(cudaGetDevice(&device));
+  int host = 0;
+  C10_CUDA_CHECK(cudaMemcpy(&host, gemm::status_word(device), sizeof(int), cudaMemcpyDeviceToHost));
+  if (host != 0) C10_CUDA_CHECK(cudaMemset(gemm::status_word(device), 0, sizeof(int)));
+  return host;
+}
+
+torch::Tensor gemm_bf16(torch::Tensor a, torch::Tensor b, c10::optional<torch::Tensor> bias,
+                        c10::optional<torch::Tensor> gate, c10::optional<torch::Tensor> residual,
+                        int64_t act, int64_t rows_per_gate, bool a_mn_major, bool b_mn_major,
+                        bool out_fp32) {
+  using namespace gemm;
+  TORCH_CHECK(a.is_cuda() && b.is_cuda() && a.dim() == 2 && b.dim() == 2);
+  TORCH_CHECK(a.scalar_type() == torch::kBFloat16 && b.scalar_type() == torch::kBFloat16);
+  TORCH_CHECK(a.stride(1) == 1 && b.stride(1) == 1, "gemm_bf16: innermost dimension must be contiguous");
+  const c10::cuda::CUDAGuard guard(a.device());
+  // logical sizes: A is [M, K] (or stored [K, M] when MN-major), B is [N, K] (or stored [K, N])
+  const int64_t m = a_mn_major ? a.size(1) : a.size(0);
+  const int64_t k = a_mn_major ? a.size(0) : a.size(1);
+  const int64_t n = b_mn_major ? b.size(1) : b.size(0);
+  const int64_t kb = b_mn_major ? b.size(0) : b.size(1);
+  TORCH_CHECK(k == kb, "gemm_bf16: contraction sizes differ: ", k, " vs ", kb);
+  TORCH_CHECK(n % 8 == 0, "gemm_bf16: N must be a multiple of 8");
+  TORCH_CHECK(a.stride(0) % 8 == 0 && b.stride(0) % 8 == 0, "gemm_bf16: row pitch must be a multiple of 8");
+  TORCH_CHECK(reinterpret_cast<uintptr_t>(a.data_ptr()) % 16 == 0 &&
+              reinterpret_cast<uintptr_t>(b.data_ptr()) % 16 == 0, "gemm_bf16: 16-byte alignment");
+  auto out = torch::empty({m, n}, a.options().dtype(out_fp32 ? torch::kFloat32 : torch::kBFloat16));
+  if (m == 0 || n == 0) return out;
+  TORCH_CHECK(k > 0, "gemm_bf16: empty contraction");
+
+  CUtensorMap map_a = a_mn_major ? make_map(a.data_ptr(), m, k, a.stride(0), 64, BK)
+                                 : make_map(a.data_ptr(), k, m, a.stride(0), BK, BM);
+  CUtensorMap map_b = b_mn_major ? make_map(b.data_ptr(), n, k, b.stride(0), 64, BK)
+                                 : make_map(b.data_ptr(), k, n, b.stride(0), BK, BN);
+  Params p{};
+  p.c = out.data_ptr();
+  torch::Tensor bias_c, gate_c, res_c;
+  if (bias.has_value()) {
+    bias_c = bias->to(torch::kBFloat16).contiguous();
+    TORCH_CHECK(bias_c.numel() == n);
+    p.bias = reinterpret_cast<const __nv_bfloat16*>(bias_c.data_ptr());
+  }
+  if (gate.has_value()) {
+    TORCH_CHECK(residual.has_value() && rows_per_gate > 0, "gate needs residual and rows_per_gate");
+    gate_c = gate->to(torch::kBFloat16).contiguous();
+    TORCH_CHECK(gate_c.numel() == (m / rows_per_gate) * n && m % rows_per_gate == 0);
+    p.gate = reinterpret_cast<const __nv_bfloat16*>(gate_c.data_ptr());
+  }
+  if (residual.has_value()) {
+    res_c = residual->to(torch::kBFloat16).contiguous();
+    TORCH_CHECK(res_c.numel() == m * n);
+    p.residual = reinterpret_cast<const __nv_bfloat16*>(res_c.data_ptr());
+  }
+  p.status = status_word(a.get_device());
+  p.m = (int)m; p.n = (int)n; p.k = (int)k;
+  p.act = (int)act;
+  p.rows_per_gate = (int)std::max<int64_t>(rows_per_gate, 1);
+  p.a_mn = a_mn_major ? 1 : 0;
+  p.b_mn = b_mn_major ? 1 : 0;
+  p.out_fp32 = out_fp32 ? 1 : 0;
+
+  static std::once_flag attr_once;
+  std::call_once(attr_once, [] {
+    C10_CUDA_CHECK(cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        kSmemBytes));
+  });
+  const int tiles = (int)(((m + BM - 1) / BM) * ((n + BN - 1) / BN));
+  const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+  const int grid = std::min(tiles, sms);
+  gemm_bf16_kernel<<<grid, kThreads, kSmemBytes, at::cuda::getCurrentCUDAStream()>>>(map_a, map_b, p);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return out;
+}
+
+}  // namespace vrl

@@ -1,0 +1,587 @@
+// Normalisation kernels (K3/K4): adaLN-modulated LayerNorm, RMSNorm and the fused QKV
+// post-processing (head split + per-head or full-width RMS norm of q/k + rotary embedding),
+// forward and backward.  One thread block handles one token row (forward) or a short run of
+// rows (backward, so per-column parameter gradients are accumulated in registers / shared
+// memory before touching global atomics).  Statistics are fp32; data is bf16.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include "common.cuh"
+#include "ops.h"
+
+namespace vrl {
+
+constexpr int kNormThreads = 256;
+constexpr int kMaxVec = 4;          // vectors of 8 per thread  => D <= 8192
+constexpr int kBwdRows = 16;
+
+using bf16 = __nv_bfloat16;
+
+// ------------------------------------------------------------------------------ adaLN forward
+__global__ void __launch_bounds__(kNormThreads)
+adaln_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ shift,
+                 const bf16* __restrict__ scale, bf16* __restrict__ y, float* __restrict__ mean_o,
+                 float* __restrict__ rstd_o, int rows_per_sample, int d, float eps) {
+  __shared__ float red[32];
+  const int64_t row = blockIdx.x;
+  const int sample = (int)(row / rows_per_sample);
+  const int nvec = d / 8;
+  const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + row * d);
+  float f[kMaxVec][8];
+  float s = 0.f;
+#pragma unroll
+  for (int k = 0; k < kMaxVec; ++k) {
+    const int i = threadIdx.x + k * kNormThreads;
+    if (i < nvec) {
+      unpack8(xr[i], f[k]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) s += f[k][j];
+    }
+  }
+  const float mu = block_sum(s, red) / (float)d;
+  float q = 0.f;
+#pragma unroll
+  for (int k = 0; k < kMaxVec; ++k) {
+    const int i = threadIdx.x + k * kNormThreads;
+    if (i < nvec) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { const float c = f[k][j] - mu; q += c * c; }
+    }
+  }
+  const float rstd = rsqrtf(block_sum(q, red) / (float)d + eps);
+  if (threadIdx.x == 0) { mean_o[row] = mu; rstd_o[row] = rstd; }
+  const bf16x8* sh = reinterpret_cast<const bf16x8*>(shift + (int64_t)sample * d);
+  const bf16x8* sc = reinterpret_cast<const bf16x8*>(scale + (int64_t)sample * d);
+  bf16x8* yr = reinterpret_cast<bf16x8*>(y + row * d);
+#pragma unroll
+  for (int k = 0; k < kMaxVec; ++k) {
+    const int i = threadIdx.x + k * kNormThreads;
+    if (i < nvec) {
+      float a[8], b[8], o[8];
+      unpack8(sh[i], a);
+      unpack8(sc[i], b);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = (f[k][j] - mu) * rstd * (1.f + b[j]) + a[j];
+      yr[i] = pack8(o);
+    }
+  }
+}
+
+std::vector<torch::Tensor> adaln_fwd(torch::Tensor x, torch::Tensor shift, torch::Tensor scale,
+                                     double eps) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 3 && x.scalar_type() == torch::kBFloat16 && x.is_contiguous());
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int b = (int)x.size(0), s = (int)x.size(1), d = (int)x.size(2);
+  TORCH_CHECK(d % 8 == 0 && d <= 8 * kMaxVec * kNormThreads, "adaln: D must be a multiple of 8, <= 8192");
+  shift = shift.to(torch::kBFloat16).contiguous();
+  scale = scale.to(torch::kBFloat16).contiguous();
+  TORCH_CHECK(shift.numel() == (int64_t)b * d && scale.numel() == (int64_t)b * d);
+  auto y = torch::empty_like(x);
+  auto mean = torch::empty({(int64_t)b * s}, x.options().dtype(torch::kFloat32));
+  auto rstd = torch::empty_like(mean);
+  adaln_fwd_kernel<<<b * s, kNormThreads, 0, at::cuda::getCurrentCUDAStream()>>>(
+      reinterpret_cast<const bf16*>(x.data_ptr()), reinterpret_cast<const bf16*>(shift.data_ptr()),
+      reinterpret_cast<const bf16*>(scale.data_ptr()), reinterpret_cast<bf16*>(y.data_ptr()),
+      mean.data_ptr<float>(), rstd.data_ptr<float>(), s, d, (float)eps);
+  return {y, mean, rstd};
+}
+
+// ----------------------------------------------------------------------------- adaLN backward
+__global__ void __launch_bounds__(kNormThreads)
+adaln_bwd_kernel(const bf16* __restrict__ gy, const bf16* __restrict__ x,
+                 const bf16* __restrict__ scale, const float* __restrict__ mean,
+                 const float* __restrict__ rstd, bf16* __restrict__ gx, float* __restrict__ gshift,
+                 float* __restrict__ gscale, int rows_per_sample, int d) {
+  __shared__ float red[32];
+  const int sample = blockIdx.y;
+  const int nvec = d / 8;
+  const int row0 = blockIdx.x * kBwdRows;
+  const bf16x8* sc = reinterpret_cast<const bf16x8*>(scale + (int64_t)sample * d);
+  float one_plus[kMaxVec][8], acc_sh[kMaxVec][8], acc_sc[kMaxVec][8];
+#pragma unroll
+  for (int k = 0; k < kMaxVec; ++k) {
+    const int i = threadIdx.x + k * kNormThreads;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { acc_sh[k][j] = 0.f; acc_sc[k][j] = 0.f; one_plus[k][j] = 1.f; }
+    if (i < nvec) {
+      float t[8];
+      unpack8(sc[i], t);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) one_plus[k][j] = 1.f + t[j];
+    }
+  }
+  for (int r = row0; r < row0 + kBwdRows && r < rows_per_sample; ++r) {
+    const int64_t row = (int64_t)sample * rows_per_sample + r;
+    const float mu = mean[row], rs = rstd[row];
+    const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + row * d);
+    const bf16x8* gr = reinterpret_cast<const bf16x8*>(gy + row * d);
+    float xh[kMaxVec][8], gp[kMaxVec][8];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int k = 0; k < kMaxVec; ++k) {
+      const int i = threadIdx.x + k * kNormThreads;
+      if (i < nvec) {
+        float xv[8], gv[8];
+        unpack8(xr[i], xv);
+        unpack8(gr[i], gv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          xh[k][j] = (xv[j] - mu) * rs;
+          gp[k][j] = gv[j] * one_plus[k][j];
+          acc_sh[k][j] += gv[j];
+          acc_sc[k][j] += gv[j] * xh[k][j];
+          s1 += gp[k][j];
+          s2 += gp[k][j] * xh[k][j];
+        }
+      }
+    }
+    const float m1 = block_sum(s1, red) / (float)d;
+    const float m2 = block_sum(s2, red) / (float)d;
+    bf16x8* gxr = reinterpret_cast<bf16x8*>(gx + row * d);
+#pragma unroll
+    for (int k = 0; k < kMaxVec; ++k) {
+      const int i = threadIdx.x + k * kNormThreads;
+      if (i < nvec) {
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = rs * (gp[k][j] - m1 - xh[k][j] * m2);
+        gxr[i] = pack8(o);
+      }
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < kMaxVec; ++k) {
+    const int i = threadIdx.x + k * kNormThreads;
+    if (i < nvec) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        atomicAdd(gshift + (int64_t)sample * d + i * 8 + j, acc_sh[k][j]);
+        atomicAdd(gscale + (int64_t)sample * d + i * 8 + j, acc_sc[k][j]);
+      }
+    }
+  }
+}
+
+std::vector<torch::Tensor> adaln_bwd(torch::Tensor gy, torch::Tensor x, torch::Tensor scale,
+                                     torch::Tensor mean, torch::Tensor rstd) {
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int b = (int)x.size(0), s = (int)x.size(1), d = (int)x.size(2);
+  gy = gy.to(torch::kBFloat16).contiguous();
+  scale = scale.to(torch::kBFloat16).contiguous();
+  auto gx = torch::empty_like(x);
+  auto gshift = torch::zeros({b, d}, x.options().dtype(torch::kFloat32));
+  auto gscale = torch::zeros({b, d}, x.options().dtype(torch::kFloat32));
+  dim3 grid((s + kBwdRows - 1) / kBwdRows, b);
+  adaln_bwd_kernel<<<grid, kNormThreads, 0, at::cuda::getCurrentCUDAStream()>>>(
+      reinterpret_cast<const bf16*>(gy.data_ptr()), reinterpret_cast<const bf16*>(x.data_ptr()),
+      reinterpret_cast<const bf16*>(scale.data_ptr()), mean.data_ptr<float>(),
+      rstd.data_ptr<float>(), reinterpret_cast<bf16*>(gx.data_ptr()), gshift.data_ptr<float>(),
+      gscale.data_ptr<float>(), s, d);
+  return {gx, gshift, gscale};
+}
+
+// ----------------------------------------------------------------------------------- RMSNorm
+__global__ void __launch_bounds__(kNormThreads)
+rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16* __restrict__ y,
+                   float* __restrict__ rstd_o, int d, float eps) {
+  __shared__ float red[32];
+  const int64_t row = blockIdx.x;
+  const int nvec = d / 8;
+  const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + row * d);
+  const bf16x8* wr = reinterpret_cast<const bf16x8*>(w);
+  float f[kMaxVec][8];
+  float q = 0.f;
+#pragma unroll
+  for (int k = 0; k < kMaxVec; ++k) {
+    const int i = threadIdx.x + k * kNormThreads;
+    if (i < nvec) {
+      unpack8(xr[i], f[k]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) q += f[k][j] * f[k][j];
+    }
+  }
+  const float rstd = rsqrtf(block_sum(q, red) / (float)d + eps);
+  if (threadIdx.x == 0) rstd_o[row] = rstd;
+  bf16x8* yr = reinterpret_cast<bf16x8*>(y + row * d);
+#pragma unroll
+  for (int k = 0; k < kMaxVec; ++k) {
+    const int i = threadIdx.x + k * kNormThreads;
+    if (i < nvec) {
+      float ww[8], o[8];
+      unpack8(wr[i], ww);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = f[k][j] * rstd * ww[j];
+      yr[i] = pack8(o);
+    }
+  }
+}
+
+std::vector<torch::Tensor> rmsnorm_fwd(torch::Tensor x, torch::Tensor w, double eps) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == torch::kBFloat16 && x.is_contiguous());
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int d = (int)x.size(-1);
+  const int64_t rows = x.numel() / d;
+  TORCH_CHECK(d % 8 == 0 && d <= 8 * kMaxVec * kNormThreads);
+  w = w.to(torch::kBFloat16).contiguous();
+  auto y = torch::empty_like(x);
+  auto rstd = torch::empty({rows}, x.options().dtype(torch::kFloat32));
+  rmsnorm_fwd_kernel<<<(unsigned)rows, kNormThreads, 0, at::cuda::getCurrentCUDAStream()>>>(
+      reinterpret_cast<const bf16*>(x.data_ptr()), reinterpret_cast<const bf16*>(w.data_ptr()),
+      reinterpret_cast<bf16*>(y.data_ptr()), rstd.data_ptr<float>(), d, (float)eps);
+  return {y, rstd};
+}
+
+__global__ void __launch_bounds__(kNormThreads)
+rmsnorm_bwd_kernel(const bf16* __restrict__ gy, const bf16* __restrict__ x,
+                   const bf16* __restrict__ w, const float* __restrict__ rstd,
+                   bf16* __restrict__ gx, float* __restrict__ gw, int64_t rows, int d) {
+  __shared__ float red[32];
+  const int nvec = d / 8;
+  const bf16x8* wr = reinterpret_cast<const bf16x8*>(w);
+  float ww[kMaxVec][8], acc[kMaxVec][8];
+#pragma unroll
+  for (int k = 0; k < kMaxVec; ++k) {
+    const int i = threadIdx.x + k * kNormThreads;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { acc[k][j] = 0.f; ww[k][j] = 0.f; }
+    if (i < nvec) unpack8(wr[i], ww[k]);
+  }
+  const int64_t row0 = (int64_t)blockIdx.x * kBwdRows;
+  for (int64_t row = row0; row < row0 + kBwdRows && row < rows; ++row) {
+    const float rs = rstd[row];
+    const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + row * d);
+    const bf16x8* gr = reinterpret_cast<const bf16x8*>(gy + row * d);
+    float xh[kMaxVec][8], gn[kMaxVec][8];
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < kMaxVec; ++k) {
+      const int i = threadIdx.x + k * kNormThreads;
+      if (i < nvec) {
+        float xv[8], gv[8];
+        unpack8(xr[i], xv);
+        unpack8(gr[i], gv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          xh[k][j] = xv[j] * rs;
+          gn[k][j] = gv[j] * ww[k][j];
+          acc[k][j] += gv[j] * xh[k][j];
+          s += gn[k][j] * xh[k][j];
+        }
+      }
+    }
+    const float m = block_sum(s, red) / (float)d;
+    bf16x8* gxr = reinterpret_cast<bf16x8*>(gx + row * d);
+#pragma unroll
+    for (int k = 0; k < kMaxVec; ++k) {
+      const int i = threadIdx.x + k * kNormThreads;
+      if (i < nvec) {
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = rs * (gn[k][j] - xh[k][j] * m);
+        gxr[i] = pack8(o);
+      }
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < kMaxVec; ++k) {
+    const int i = threadIdx.x + k * kNormThreads;
+    if (i < nvec) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) atomicAdd(gw + i * 8 + j, acc[k][j]);
+    }
+  }
+}
+
+std::vector<torch::Tensor> rmsnorm_bwd(torch::Tensor gy, torch::Tensor x, torch::Tensor w,
+                                       torch::Tensor rstd) {
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int d = (int)x.size(-1);
+  const int64_t rows = x.numel() / d;
+  gy = gy.to(torch::kBFloat16).contiguous();
+  w = w.to(torch::kBFloat16).contiguous();
+  auto gx = torch::empty_like(x);
+  auto gw = torch::zeros({d}, x.options().dtype(torch::kFloat32));
+  rmsnorm_bwd_kernel<<<(unsigned)((rows + kBwdRows - 1) / kBwdRows), kNormThreads, 0,
+                       at::cuda::getCurrentCUDAStream()>>>(
+      reinterpret_cast<const bf16*>(gy.data_ptr()), reinterpret_cast<const bf16*>(x.data_ptr()),
+      reinterpret_cast<const bf16*>(w.data_ptr()), rstd.data_ptr<float>(),
+      reinterpret_cast<bf16*>(gx.data_ptr()), gw.data_ptr<float>(), rows, d);
+  return {gx, gw};
+}
+
+// ------------------------------------------------------------------------- QKV post-processing
+// qkv[b, s, which, h, :] -> out_which[b, h, s, :].  Norm modes: 0 none, 1 per head (weights of
+// Dh elements), 2 full width (weights of H*Dh elements).  rstd layout: [b, s, 2, H] (mode 1)
+// or [b, s, 2] (mode 2).  Rotary tables are [S, Dh/2]; pairs are (2i, 2i+1).
+constexpr int kQkvMaxVec = 8;      // 3*H*Dh/8 <= 8*256  => H*Dh <= 5461
+
+__device__ __forceinline__ float group_sum(float v, int lanes) {
+  for (int o = lanes >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__global__ void __launch_bounds__(kNormThreads)
+qkv_prepare_fwd_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ qw,
+                       const bf16* __restrict__ kw, const float* __restrict__ cosT,
+                       const float* __restrict__ sinT, bf16* __restrict__ q, bf16* __restrict__ k,
+                       bf16* __restrict__ v, float* __restrict__ rstd_o, int seq, int heads,
+                       int dh, int mode, float eps) {
+  __shared__ float red[32];
+  const int64_t tok = blockIdx.x;
+  const int b = (int)(tok / seq), s = (int)(tok % seq);
+  const int dmodel = heads * dh;
+  const int vec_per_head = dh / 8, vec_per_which = dmodel / 8, nvec = 3 * vec_per_which;
+  const bf16x8* src = reinterpret_cast<const bf16x8*>(qkv + tok * 3 * dmodel);
+  float f[kQkvMaxVec][8];
+  float ssq[kQkvMaxVec];
+  float tot_q = 0.f, tot_k = 0.f;
+#pragma unroll
+  for (int t = 0; t < kQkvMaxVec; ++t) {
+    const int i = threadIdx.x + t * kNormThreads;
+    ssq[t] = 0.f;
+    if (i < nvec) {
+      unpack8(src[i], f[t]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ssq[t] += f[t][j] * f[t][j];
+      const int which = i / vec_per_which;
+      if (which == 0) tot_q += ssq[t];
+      if (which == 1) tot_k += ssq[t];
+    }
+  }
+  float full_q = 0.f, full_k = 0.f;
+  if (mode == 2) {
+    full_q = rsqrtf(block_sum(tot_q, red) / (float)dmodel + eps);
+    full_k = rsqrtf(block_sum(tot_k, red) / (float)dmodel + eps);
+    if (threadIdx.x == 0) { rstd_o[tok * 2] = full_q; rstd_o[tok * 2 + 1] = full_k; }
+  }
+#pragma unroll
+  for (int t = 0; t < kQkvMaxVec; ++t) {
+    const int i = threadIdx.x + t * kNormThreads;
+    // the whole head group takes part in the shuffle, so no early exit before it
+    float head_ssq = (mode == 1) ? group_sum(ssq[t], vec_per_head) : 0.f;
+    if (i >= nvec) continue;
+    const int which = i / vec_per_which;
+    const int rem = i - which * vec_per_which;
+    const int h = rem / vec_per_head, j8 = rem - h * vec_per_head;
+    float o[8];
+    if (which < 2 && mode != 0) {
+      float rs;
+      if (mode == 1) {
+        rs = rsqrtf(head_ssq / (float)dh + eps);
+        if (j8 == 0) rstd_o[(tok * 2 + which) * heads + h] = rs;
+      } else {
+        rs = which == 0 ? full_q : full_k;
+      }
+      const bf16* wsrc = (which == 0 ? qw : kw) + (mode == 1 ? j8 * 8 : rem * 8);
+      float ww[8];
+      unpack8(*reinterpret_cast<const bf16x8*>(wsrc), ww);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = f[t][j] * rs * ww[j];
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = f[t][j];
+    }
+    if (which < 2 && cosT != nullptr) {
+      const float* c = cosT + (int64_t)s * (dh / 2) + j8 * 4;
+      const float* sn = sinT + (int64_t)s * (dh / 2) + j8 * 4;
+#pragma unroll
+      for (int p = 0; p < 4; ++p) {
+        const float x0 = o[2 * p], x1 = o[2 * p + 1];
+        o[2 * p] = x0 * c[p] - x1 * sn[p];
+        o[2 * p + 1] = x0 * sn[p] + x1 * c[p];
+      }
+    }
+    bf16* dst = which == 0 ? q : (which == 1 ? k : v);
+    *reinterpret_cast<bf16x8*>(dst + (((int64_t)b * heads + h) * seq + s) * dh + j8 * 8) = pack8(o);
+  }
+}
+
+std::vector<torch::Tensor> qkv_prepare_fwd(torch::Tensor qkv, c10::optional<torch::Tensor> qw,
+                                           c10::optional<torch::Tensor> kw,
+                                           c10::optional<torch::Tensor> cos,
+                                           c10::optional<torch::Tensor> sin, int64_t heads,
+                                           double eps) {
+  TORCH_CHECK(qkv.is_cuda() && qkv.dim() == 3 && qkv.scalar_type() == torch::kBFloat16 &&
+              qkv.is_contiguous());
+  const c10::cuda::CUDAGuard guard(qkv.device());
+  const int b = (int)qkv.size(0), s = (int)qkv.size(1);
+  const int dmodel = (int)(qkv.size(2) / 3), dh = dmodel / (int)heads;
+  TORCH_CHECK(dh % 8 == 0 && kNormThreads % (dh / 8) == 0 && (dh / 8) <= 32, "unsupported head dim");
+  TORCH_CHECK(3 * dmodel / 8 <= kQkvMaxVec * kNormThreads, "model width too large for qkv_prepare");
+  int mode = 0;
+  torch::Tensor qwc, kwc;
+  if (qw.has_value()) {
+    qwc = qw->to(torch::kBFloat16).contiguous();
+    kwc = kw->to(torch::kBFloat16).contiguous();
+    mode = (qwc.numel() == dh && heads > 1) || (heads == 1) ? 1 : 2;
+    TORCH_CHECK(qwc.numel() == (mode == 1 ? dh : dmodel));
+  }
+  torch::Tensor cosc, sinc;
+  if (cos.has_value()) {
+    cosc = cos->to(torch::kFloat32).contiguous();
+    sinc = sin->to(torch::kFloat32).contiguous();
+    TORCH_CHECK(cosc.size(0) == s && cosc.size(1) == dh / 2);
+  }
+  auto opt = qkv.options();
+  auto q = torch::empty({b, (int64_t)heads, s, dh}, opt);
+  auto k = torch::empty_like(q);
+  auto v = torch::empty_like(q);
+  auto rstd = torch::empty({(int64_t)b * s * 2 * (mode == 1 ? heads : 1)},
+                           opt.dtype(torch::kFloat32));
+  qkv_prepare_fwd_kernel<<<b * s, kNormThreads, 0, at::cuda::getCurrentCUDAStream()>>>(
+      reinterpret_cast<const bf16*>(qkv.data_ptr()),
+      mode ? reinterpret_cast<const bf16*>(qwc.data_ptr()) : nullptr,
+      mode ? reinterpret_cast<const bf16*>(kwc.data_ptr()) : nullptr,
+      cos.has_value() ? cosc.data_ptr<float>() : nullptr,
+      cos.has_value() ? sinc.data_ptr<float>() : nullptr, reinterpret_cast<bf16*>(q.data_ptr()),
+      reinterpret_cast<bf16*>(k.data_ptr()), reinterpret_cast<bf16*>(v.data_ptr()),
+      rstd.data_ptr<float>(), s, (int)heads, dh, mode, (float)eps);
+  return {q, k, v, rstd};
+}
+
+constexpr int kQkvBwdTokens = 8;
+
+__global__ void __launch_bounds__(kNormThreads)
+qkv_prepare_bwd_kernel(const bf16* __restrict__ gq, const bf16* __restrict__ gk,
+                       const bf16* __restrict__ gv, const bf16* __restrict__ qkv,
+                       const bf16* __restrict__ qw, const bf16* __restrict__ kw,
+                       const float* __restrict__ cosT, const float* __restrict__ sinT,
+                       const float* __restrict__ rstd, bf16* __restrict__ gqkv,
+                       float* __restrict__ gqw, float* __restrict__ gkw, int64_t tokens, int seq,
+                       int heads, int dh, int mode) {
+  extern __shared__ float wacc[];          // [2][wlen] parameter-gradient accumulators
+  __shared__ float red[32];
+  const int dmodel = heads * dh;
+  const int wlen = mode == 1 ? dh : dmodel;
+  const int vec_per_head = dh / 8, vec_per_which = dmodel / 8, nvec = 3 * vec_per_which;
+  if (mode != 0) {
+    for (int i = threadIdx.x; i < 2 * wlen; i += blockDim.x) wacc[i] = 0.f;
+  }
+  __syncthreads();
+  const int64_t tok0 = (int64_t)blockIdx.x * kQkvBwdTokens;
+  for (int64_t tok = tok0; tok < tok0 + kQkvBwdTokens && tok < tokens; ++tok) {
+    const int b = (int)(tok / seq), s = (int)(tok % seq);
+    const bf16x8* src = reinterpret_cast<const bf16x8*>(qkv + tok * 3 * dmodel);
+    bf16x8* dst = reinterpret_cast<bf16x8*>(gqkv + tok * 3 * dmodel);
+    float gn[kQkvMaxVec][8], xh[kQkvMaxVec][8];
+    float dot[kQkvMaxVec];
+    float tot_q = 0.f, tot_k = 0.f;
+#pragma unroll
+    for (int t = 0; t < kQkvMaxVec; ++t) {
+      const int i = threadIdx.x + t * kNormThreads;
+      dot[t] = 0.f;
+      if (i >= nvec) continue;
+      const int which = i / vec_per_which;
+      const int rem = i - which * vec_per_which;
+      const int h = rem / vec_per_head, j8 = rem - h * vec_per_head;
+      const bf16* gsrc = which == 0 ? gq : (which == 1 ? gk : gv);
+      float g[8];
+      unpack8(*reinterpret_cast<const bf16x8*>(gsrc + (((int64_t)b * heads + h) * seq + s) * dh + j8 * 8), g);
+      if (which == 2) {
+        dst[i] = pack8(g);
+        continue;
+      }
+      if (cosT != nullptr) {     // transpose of the rotation
+        const float* c = cosT + (int64_t)s * (dh / 2) + j8 * 4;
+        const float* sn = sinT + (int64_t)s * (dh / 2) + j8 * 4;
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+          const float g0 = g[2 * p], g1 = g[2 * p + 1];
+          g[2 * p] = g0 * c[p] + g1 * sn[p];
+          g[2 * p + 1] = -g0 * sn[p] + g1 * c[p];
+        }
+      }
+      if (mode == 0) {
+        dst[i] = pack8(g);
+        continue;
+      }
+      float xv[8], ww[8];
+      unpack8(src[i], xv);
+      const float rs = mode == 1 ? rstd[(tok * 2 + which) * heads + h] : rstd[tok * 2 + which];
+      const int woff = mode == 1 ? j8 * 8 : rem * 8;
+      unpack8(*reinterpret_cast<const bf16x8*>((which == 0 ? qw : kw) + woff), ww);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        xh[t][j] = xv[j] * rs;
+        gn[t][j] = g[j] * ww[j];
+        dot[t] += gn[t][j] * xh[t][j];
+        atomicAdd(&wacc[which * wlen + woff + j], g[j] * xh[t][j]);
+      }
+      if (which == 0) tot_q += dot[t]; else tot_k += dot[t];
+    }
+    float mean_q = 0.f, mean_k = 0.f;
+    if (mode == 2) {
+      mean_q = block_sum(tot_q, red) / (float)dmodel;
+      mean_k = block_sum(tot_k, red) / (float)dmodel;
+    }
+#pragma unroll
+    for (int t = 0; t < kQkvMaxVec; ++t) {
+      const int i = threadIdx.x + t * kNormThreads;
+      const float head_dot = (mode == 1) ? group_sum(dot[t], vec_per_head) : 0.f;
+      if (i >= nvec || mode == 0) continue;
+      const int which = i / vec_per_which;
+      if (which == 2) continue;
+      const int rem = i - which * vec_per_which;
+      const int h = rem / vec_per_head;
+      const float rs = mode == 1 ? rstd[(tok * 2 + which) * heads + h] : rstd[tok * 2 + which];
+      const float m = mode == 1 ? head_dot / (float)dh : (which == 0 ? mean_q : mean_k);
+      float o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = rs * (gn[t][j] - xh[t][j] * m);
+      dst[i] = pack8(o);
+    }
+  }
+  __syncthreads();
+  if (mode != 0) {
+    for (int i = threadIdx.x; i < wlen; i += blockDim.x) {
+      atomicAdd(gqw + i, wacc[i]);
+      atomicAdd(gkw + i, wacc[wlen + i]);
+    }
+  }
+}
+
+std::vector<torch::Tensor> qkv_prepare_bwd(torch::Tensor gq, torch::Tensor gk, torch::Tensor gv,
+                                           torch::Tensor qkv, c10::optional<torch::Tensor> qw,
+                                           c10::optional<torch::Tensor> kw,
+                                           c10::optional<torch::Tensor> cos,
+                                           c10::optional<torch::Tensor> sin, torch::Tensor rstd,
+                                           int64_t heads) {
+  const c10::cuda::CUDAGuard guard(qkv.device());
+  const int b = (int)qkv.size(0), s = (int)qkv.size(1);
+  const int dmodel = (int)(qkv.size(2) / 3), dh = dmodel / (int)heads;
+  gq = gq.to(torch::kBFloat16).contiguous();
+  gk = gk.to(torch::kBFloat16).contiguous();
+  gv = gv.to(torch::kBFloat16).contiguous();
+  int mode = 0;
+  torch::Tensor qwc, kwc;
+  if (qw.has_value()) {
+    qwc = qw->to(torch::kBFloat16).contiguous();
+    kwc = kw->to(torch::kBFloat16).contiguous();
+    mode = (qwc.numel() == dh && heads > 1) || (heads == 1) ? 1 : 2;
+  }
+  torch::Tensor cosc, sinc;
+  if (cos.has_value()) {
+    cosc = cos->to(torch::kFloat32).contiguous();
+    sinc = sin->to(torch::kFloat32).contiguous();
+  }
+  const int wlen = mode == 1 ? dh : dmodel;
+  auto gqkv = torch::empty_like(qkv);
+  auto gqw = torch::zeros({mode ? wlen : 1}, qkv.options().dtype(torch::kFloat32));
+  auto gkw = torch::zeros_like(gqw);
+  const int64_t tokens = (int64_t)b * s;
+  const size_t smem = mode ? sizeof(float) * 2 * wlen : 0;
+  qkv_prepare_bwd_kernel<<<(unsigned)((tokens + kQkvBwdTokens - 1) / kQkvBwdTokens), kNormThreads,
+                           smem, at::cuda::getCurrentCUDAStream()>>>(
+      reinterpret_cast<const bf16*>(gq.data_ptr()), reinterpret_cast<const bf16*>(gk.data_ptr()),
+      reinterpret_cast<const bf16*>(gv.data_ptr()), reinterpret_cast<const bf16*>(qkv.data_ptr()),
+      mode ? reinterpret_cast<const bf16*>(qwc.data_ptr()) : nullptr,
+      mode ? reinterpret_cast<const bf16*>(kwc.data_ptr()) : nullptr,
+      cos.has_value() ? cosc.data_ptr<float>() : nullptr,
+      cos.has_value() ? sinc.data_ptr<float>() : nullptr, rstd.data_ptr<float>(),
+      reinterpret_cast<bf16*>(gqkv.data_ptr()), gqw.data_ptr<float>(), gkw.data_ptr<float>(),
+      tokens, s, (int)heads, dh, mode);
+  return {gqkv, gqw, gkw};
+}
+
+}  // namespace vrl

@@ -1,0 +1,63 @@
+// Host entry points of the visionrl_b200 extension.
+#pragma once
+
+#include <cuda_runtime_api.h>
+#include <torch/extension.h>
+
+#include <vector>
+
+namespace vrl {
+
+// elementwise.cu
+int sde_blocks_per_sample(int64_t n);
+void sde_step_launch(const float* v, const float* x, const float* a, const float* b,
+                     const float* scale, const float* dt, const float* prev_in,
+                     const float* noise, float* prev_out, float* mean_out, float* logp,
+                     float* partial, int batch, int64_t n, bool deterministic, bool gaussian,
+                     cudaStream_t stream);
+std::vector<torch::Tensor> sde_step_fwd(torch::Tensor v, torch::Tensor x, torch::Tensor a,
+                                        torch::Tensor b, torch::Tensor scale, torch::Tensor dt,
+                                        c10::optional<torch::Tensor> prev_sample,
+                                        c10::optional<torch::Tensor> noise, bool deterministic,
+                                        bool gaussian);
+std::vector<torch::Tensor> sde_step_bwd(torch::Tensor prev, torch::Tensor mean, torch::Tensor a,
+                                        torch::Tensor b, torch::Tensor scale, torch::Tensor g_logp,
+                                        c10::optional<torch::Tensor> g_mean, bool gaussian);
+std::vector<torch::Tensor> token_loss_fwd(torch::Tensor lp, torch::Tensor old, torch::Tensor adv,
+                                          c10::optional<torch::Tensor> mask,
+                                          c10::optional<torch::Tensor> ref, double eps_clip,
+                                          bool k3);
+torch::Tensor per_sample_mse(torch::Tensor pred, torch::Tensor target);
+torch::Tensor sum_squares(torch::Tensor g);
+void adamw_flat(torch::Tensor p, torch::Tensor g, torch::Tensor master, torch::Tensor m,
+                torch::Tensor v, double lr, double b1, double b2, double eps, double wd,
+                int64_t step, c10::optional<torch::Tensor> clip);
+
+// norm.cu
+std::vector<torch::Tensor> adaln_fwd(torch::Tensor x, torch::Tensor shift, torch::Tensor scale,
+                                     double eps);
+std::vector<torch::Tensor> adaln_bwd(torch::Tensor gy, torch::Tensor x, torch::Tensor scale,
+                                     torch::Tensor mean, torch::Tensor rstd);
+std::vector<torch::Tensor> rmsnorm_fwd(torch::Tensor x, torch::Tensor w, double eps);
+std::vector<torch::Tensor> rmsnorm_bwd(torch::Tensor gy, torch::Tensor x, torch::Tensor w,
+                                       torch::Tensor rstd);
+std::vector<torch::Tensor> qkv_prepare_fwd(torch::Tensor qkv, c10::optional<torch::Tensor> qw,
+                                           c10::optional<torch::Tensor> kw,
+                                           c10::optional<torch::Tensor> cos,
+                                           c10::optional<torch::Tensor> sin, int64_t heads,
+                                           double eps);
+std::vector<torch::Tensor> qkv_prepare_bwd(torch::Tensor gq, torch::Tensor gk, torch::Tensor gv,
+                                           torch::Tensor qkv, c10::optional<torch::Tensor> qw,
+                                           c10::optional<torch::Tensor> kw,
+                                           c10::optional<torch::Tensor> cos,
+                                           c10::optional<torch::Tensor> sin, torch::Tensor rstd,
+                                           int64_t heads);
+
+// gemm_sm100.cu
+torch::Tensor gemm_bf16(torch::Tensor a, torch::Tensor b, c10::optional<torch::Tensor> bias,
+                        c10::optional<torch::Tensor> gate, c10::optional<torch::Tensor> residual,
+                        int64_t act, int64_t rows_per_gate, bool a_mn_major, bool b_mn_major,
+                        bool out_fp32);
+int64_t gemm_last_status();
+
+}  // namespace vrl

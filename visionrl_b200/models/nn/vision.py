@@ -195,28 +195,54 @@ def _seed_from_text(text: str, salt: str = "") -> int:
 
 class SyntheticTextEncoder:
     """Deterministic stand-in for T5/CLIP text towers: every prompt maps to seeded
-    ``N(0, 1)`` token embeddings ``[L, context_dim]`` and a pooled vector."""
+    ``N(0, 1)`` token embeddings ``[L, context_dim]`` and a pooled vector.
+
+    Embeddings are generated once into (pinned, when CUDA is present) host memory and copied
+    to the device on demand; a per-device cache avoids repeated copies.  ``h2d_bytes`` counts
+    the bytes moved since :meth:`reset_transfer_stats`.
+    """
 
     def __init__(self, context_dim: int, pooled_dim: int = 0, salt: str = "text"):
         self.context_dim, self.pooled_dim, self.salt = context_dim, pooled_dim, salt
-        self._cache: dict = {}
+        self._host: dict = {}
+        self._device: dict = {}
+        self.h2d_bytes = 0
+
+    def reset_transfer_stats(self) -> None:
+        self.h2d_bytes = 0
+
+    def drop_device_cache(self) -> None:
+        self._device.clear()
+
+    def _host_entry(self, prompt: str, length: int, dtype):
+        key = (prompt, length, dtype)
+        if key not in self._host:
+            g = torch.Generator().manual_seed(_seed_from_text(prompt, self.salt))
+            c = torch.randn(length, self.context_dim, generator=g).to(dtype)
+            v = torch.randn(max(self.pooled_dim, 1), generator=g).to(dtype)
+            if torch.cuda.is_available():
+                c, v = c.pin_memory(), v.pin_memory()
+            self._host[key] = (c, v)
+        return self._host[key]
 
     def __call__(self, prompts, length: int, device, dtype):
         if isinstance(prompts, str):
             prompts = [prompts]
+        device = torch.device(device)
         ctx, pooled = [], []
         for p in prompts:
-            key = (p, length)
-            if key not in self._cache:
-                g = torch.Generator().manual_seed(_seed_from_text(p, self.salt))
-                c = torch.randn(length, self.context_dim, generator=g)
-                v = torch.randn(max(self.pooled_dim, 1), generator=g)
-                self._cache[key] = (c, v)
-            c, v = self._cache[key]
+            key = (p, length, dtype, str(device))
+            if key not in self._device:
+                c, v = self._host_entry(p, length, dtype)
+                if device.type == "cuda":
+                    self.h2d_bytes += c.numel() * c.element_size() + v.numel() * v.element_size()
+                    c, v = c.to(device, non_blocking=True), v.to(device, non_blocking=True)
+                self._device[key] = (c, v)
+            c, v = self._device[key]
             ctx.append(c)
             pooled.append(v)
-        ctx_t = torch.stack(ctx).to(device=device, dtype=dtype)
-        pooled_t = torch.stack(pooled).to(device=device, dtype=dtype) if self.pooled_dim else None
+        ctx_t = torch.stack(ctx)
+        pooled_t = torch.stack(pooled) if self.pooled_dim else None
         return ctx_t, pooled_t
 
 

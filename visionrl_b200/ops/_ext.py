@@ -9,11 +9,62 @@ binary is missing, so a GPU run can never fall back to eager PyTorch silently.
 from __future__ import annotations
 
 import importlib
+import os
 import threading
 
 _lock = threading.Lock()
 _module = None
+_proxy = None
 _error: Exception | None = None
+
+# kernels launched per extension call (used for launch accounting in benchmarks)
+_LAUNCHES = {
+    "sde_step_fwd": 2, "sde_step_bwd": 1, "token_loss_fwd": 1, "per_sample_mse": 2,
+    "sum_squares": 2, "adamw_flat": 1, "adaln_fwd": 1, "adaln_bwd": 1, "rmsnorm_fwd": 1,
+    "rmsnorm_bwd": 1, "qkv_prepare_fwd": 1, "qkv_prepare_bwd": 1, "gemm_bf16": 1,
+    "flash_attn_fwd": 1, "flash_attn_bwd": 2, "token_logprob_fwd": 1, "token_logprob_bwd": 1,
+    "decode_attention": 1, "rs_sum_slice": 1, "adamw_slice_broadcast": 1, "int4_gemv": 1,
+    "sample_tokens": 1, "peer_copy": 1, "moe_route": 1,
+}
+launch_count = 0
+_kernels_enabled = os.environ.get("VRL_FORCE_TORCH_OPS", "0") != "1"
+
+
+def kernels_enabled() -> bool:
+    """False while the PyTorch-library baseline mode is active (benchmark comparison arm)."""
+    return _kernels_enabled
+
+
+def set_kernels_enabled(flag: bool) -> None:
+    global _kernels_enabled
+    _kernels_enabled = bool(flag)
+
+
+class _CountingProxy:
+    """Forwards attribute access to the extension and counts kernel launches per call."""
+
+    def __init__(self, module):
+        self._module = module
+        self._wrapped: dict = {}
+
+    def __getattr__(self, name):
+        fn = self._wrapped.get(name)
+        if fn is None:
+            raw = getattr(self._module, name)
+            n = _LAUNCHES.get(name, 0)
+            if n == 0 or not callable(raw):
+                return raw
+
+            def fn(*args, _raw=raw, _n=n, **kwargs):
+                global launch_count
+                launch_count += _n
+                return _raw(*args, **kwargs)
+
+            self._wrapped[name] = fn
+        return fn
+
+    def __dir__(self):
+        return dir(self._module)
 
 
 class ExtensionUnavailable(RuntimeError):
@@ -22,12 +73,12 @@ class ExtensionUnavailable(RuntimeError):
 
 def load():
     """Import ``visionrl_b200._C`` once; raise :class:`ExtensionUnavailable` otherwise."""
-    global _module, _error
-    if _module is not None:
-        return _module
+    global _module, _error, _proxy
+    if _proxy is not None:
+        return _proxy
     with _lock:
-        if _module is not None:
-            return _module
+        if _proxy is not None:
+            return _proxy
         try:
             import torch  # noqa: F401  (libtorch must be loaded before the extension)
 
@@ -38,7 +89,16 @@ def load():
                 "visionrl_b200._C is not built; run `python -c \"import __graft_entry__ as g; "
                 "g.build()\"` (or `python -m visionrl_b200.ops.build`) first"
             ) from exc
-    return _module
+        _proxy = _CountingProxy(_module)
+    return _proxy
+
+
+def has(name: str) -> bool:
+    """True when the built extension exports ``name``."""
+    try:
+        return hasattr(load()._module, name)
+    except ExtensionUnavailable:
+        return False
 
 
 def available() -> bool:

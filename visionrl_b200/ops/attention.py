@@ -46,7 +46,7 @@ def _native_ok(q, k) -> bool:
     from visionrl_b200.ops import _ext
 
     return (q.is_cuda and q.dtype == torch.bfloat16 and q.shape[-1] in (64, 128)
-            and _ext.available() and hasattr(_ext.load(), "flash_attn_fwd"))
+            and _ext.kernels_enabled() and _ext.has("flash_attn_fwd"))
 
 
 def attention(q, k, v, causal: bool = False, scale: float | None = None):
@@ -73,9 +73,10 @@ def decode_attention_reference(q, k_cache, v_cache, valid, length: int, scale: f
 
 
 def decode_attention(q, k_cache, v_cache, valid, length: int, scale: float | None = None):
-    if q.is_cuda and q.dtype == torch.bfloat16 and q.shape[-1] == 128:
-        from visionrl_b200.ops import _ext
+    from visionrl_b200.ops import _ext
 
+    if (q.is_cuda and q.dtype == torch.bfloat16 and q.shape[-1] == 128 and _ext.kernels_enabled()
+            and _ext.has("decode_attention")):
         scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
         return _ext.load().decode_attention(q.contiguous(), k_cache, v_cache, valid, int(length),
                                             float(scale))

@@ -40,8 +40,10 @@ def linear_epilogue(y, act=None, gate=None, residual=None):
 
 
 def _use_kernel(x, w) -> bool:
+    from visionrl_b200.ops import _ext
+
     return (x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
-            and x.shape[-1] % 8 == 0 and w.shape[0] % 8 == 0)
+            and x.shape[-1] % 8 == 0 and w.shape[0] % 8 == 0 and _ext.kernels_enabled())
 
 
 def gemm_nt(a, b, bias=None, act=None, gate=None, residual=None, rows_per_gate: int = 0,

@@ -41,7 +41,10 @@ class _TokenLogProbFn(torch.autograd.Function):
 
 
 def token_log_probs(logits, ids, temperature: float = 1.0):
-    if logits.is_cuda and logits.dtype in (torch.bfloat16, torch.float32):
+    from visionrl_b200.ops import _ext
+
+    if (logits.is_cuda and logits.dtype in (torch.bfloat16, torch.float32)
+            and _ext.kernels_enabled() and _ext.has("token_logprob_fwd")):
         return _TokenLogProbFn.apply(logits, ids, temperature)
     return token_log_probs_reference(logits, ids, temperature)
 

@@ -9,6 +9,8 @@ from __future__ import annotations
 import torch
 import torch.nn.functional as F
 
+from visionrl_b200.ops import _ext
+
 
 def grpo_clipped_loss_reference(log_prob, old_log_prob, advantages, eps_clip: float):
     ratio = torch.exp(log_prob - old_log_prob)
@@ -71,7 +73,8 @@ class _FusedTokenLoss(torch.autograd.Function):
 
 def grpo_clipped_loss(log_prob, old_log_prob, advantages, eps_clip: float):
     """``log_prob[B]`` → ``(policy_loss, clip_fraction, approx_kl)``."""
-    if log_prob.is_cuda and log_prob.dim() == 1 and log_prob.dtype == torch.float32:
+    if (log_prob.is_cuda and log_prob.dim() == 1 and log_prob.dtype == torch.float32
+            and _ext.kernels_enabled()):
         b = log_prob.shape[0]
         pol, _kl, clip, akl = _FusedTokenLoss.apply(
             log_prob.view(b, 1), old_log_prob.view(b, 1).float(), advantages.float(), None, None,
@@ -85,7 +88,7 @@ def token_grpo_loss(log_prob, old_log_prob, advantages, mask, ref_log_prob, eps_
                     kl_estimator: str = "k3"):
     """``log_prob[B, L]`` → ``(policy_loss, kl_loss, clip_fraction, approx_kl)``."""
     if (log_prob.is_cuda and log_prob.dim() == 2 and advantages.dim() == 1
-            and log_prob.dtype == torch.float32):
+            and log_prob.dtype == torch.float32 and _ext.kernels_enabled()):
         pol, kl, clip, akl = _FusedTokenLoss.apply(
             log_prob, old_log_prob.float(), advantages.float(), mask, ref_log_prob, eps_clip,
             kl_estimator == "k3",
@@ -98,9 +101,8 @@ def token_grpo_loss(log_prob, old_log_prob, advantages, mask, ref_log_prob, eps_
 
 def per_sample_mse(pred, target):
     """``mean((pred - target)^2)`` over all non-batch dims, fp32 accumulation."""
-    if pred.is_cuda and not (pred.requires_grad or target.requires_grad):
-        from visionrl_b200.ops import _ext
-
+    if (pred.is_cuda and not (pred.requires_grad or target.requires_grad)
+            and _ext.kernels_enabled()):
         return _ext.load().per_sample_mse(pred.contiguous(), target.contiguous())
     return (pred.float() - target.float()).pow(2).mean(dim=tuple(range(1, pred.ndim)))
 

@@ -5,7 +5,7 @@
 * :func:`rmsnorm` — ``y = x / sqrt(mean(x^2) + eps) * weight`` over the last dim.
 * :func:`layernorm` — affine LayerNorm over the last dim.
 
-CUDA bf16/fp32 inputs run one-row-per-warp sm_100a kernels (single pass over the
+CUDA bf16 inputs run one-row-per-warp sm_100a kernels (single pass over the
 row in registers, fp32 statistics); CPU tensors use the PyTorch formulas.
 """
 
@@ -68,8 +68,10 @@ class _RMSNormFn(torch.autograd.Function):
 
 
 def _kernel_ok(x) -> bool:
-    return x.is_cuda and x.dtype in (torch.bfloat16, torch.float32) and x.shape[-1] % 8 == 0 \
-        and x.shape[-1] <= 8192
+    from visionrl_b200.ops import _ext
+
+    return (x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0
+            and x.shape[-1] <= 8192 and _ext.kernels_enabled())
 
 
 def adaln_layernorm(x, shift, scale, eps: float = 1e-6):

@@ -22,6 +22,8 @@ from typing import Any
 
 import torch
 
+from visionrl_b200.ops import _ext
+
 
 def adamw_flat_reference(param, grad, master, exp_avg, exp_avg_sq, *, lr, beta1, beta2, eps,
                          weight_decay, step, clip_coef=None):
@@ -144,9 +146,7 @@ class FusedAdamW(torch.optim.Optimizer):
         total = None
         for e in self._flat:
             g = e["grad"]
-            if g.is_cuda:
-                from visionrl_b200.ops import _ext
-
+            if g.is_cuda and _ext.kernels_enabled():
                 sq = _ext.load().sum_squares(g)
             else:
                 sq = g.float().pow(2).sum()
@@ -170,9 +170,7 @@ class FusedAdamW(torch.optim.Optimizer):
             g_own = e.get("grad_shard")
             if g_own is None:
                 g_own = e["grad"][lo:lo + n]
-            if p_own.is_cuda:
-                from visionrl_b200.ops import _ext
-
+            if p_own.is_cuda and _ext.kernels_enabled():
                 _ext.load().adamw_flat(p_own, g_own, e["master"], e["exp_avg"],
                                        e["exp_avg_sq"], kw["lr"], kw["beta1"], kw["beta2"],
                                        kw["eps"], kw["weight_decay"], kw["step"], clip_coef)

@@ -68,7 +68,10 @@ class _QKVPrepFn(torch.autograd.Function):
 
 def qkv_prepare(qkv, heads: int, q_weight=None, k_weight=None, eps: float = 1e-6, rope=None):
     dh = qkv.shape[-1] // (3 * heads)
-    if qkv.is_cuda and qkv.dtype == torch.bfloat16 and dh in (64, 128):
+    from visionrl_b200.ops import _ext
+
+    if (qkv.is_cuda and qkv.dtype == torch.bfloat16 and dh in (64, 128)
+            and qkv.shape[-1] <= 16384 and _ext.kernels_enabled()):
         cos, sin = rope if rope is not None else (None, None)
         return _QKVPrepFn.apply(qkv, q_weight, k_weight, cos, sin, heads, eps)
     return qkv_prepare_reference(qkv, heads, q_weight, k_weight, eps, rope)

@@ -72,7 +72,9 @@ class _FusedSDEStep(torch.autograd.Function):
 def sde_step(v, x, a, b, scale, dt, prev_sample=None, noise=None,
              deterministic=False, gaussian=True):
     """Returns ``(prev_sample, log_prob[B], prev_sample_mean)``."""
-    if v.is_cuda:
+    from visionrl_b200.ops import _ext
+
+    if v.is_cuda and _ext.kernels_enabled():
         return _FusedSDEStep.apply(v, x, a, b, scale, dt, prev_sample, noise,
                                    deterministic, gaussian)
     return sde_step_reference(v, x, a, b, scale, dt, prev_sample, noise, deterministic, gaussian)

@@ -130,13 +130,11 @@ def default_csv_row(epoch: int, m: Any) -> str:
             f"{m.trained_prompt_num}")
 
 
-async def run_online_recipe(ctx: RunContext, parts: RecipeParts, reward_fn: Any,
-                            reward_names: list[str], *,
-                            on_epoch_end: Callable[[int, Any, Any], Any] | None = None) -> Any:
+def build_online_trainer(ctx: RunContext, parts: RecipeParts, reward_fn: Any):
+    """Collector + rollout runtime + weight syncer + (sharded) ``OnlineTrainer`` of a recipe."""
     from visionrl_b200.rollouts.collector import build_rollout_collector
     from visionrl_b200.rollouts.runtime.backend import build_rollout_backend_from_cfg
     from visionrl_b200.rollouts.runtime.launch_inputs import build_rollout_runtime_inputs
-    from visionrl_b200.trainers.data import load_prompt_manifest
     from visionrl_b200.trainers.online import OnlineTrainer
     from visionrl_b200.trainers.weight_sync import build_runtime_weight_syncer
 
@@ -171,6 +169,16 @@ async def run_online_recipe(ctx: RunContext, parts: RecipeParts, reward_fn: Any,
                                     strict=tc.resume_strict)
         logger.info("Resuming from %s, start_epoch=%d", ctx.resume.checkpoint_dir,
                     ctx.resume.next_epoch)
+    return trainer, collector
+
+
+async def run_online_recipe(ctx: RunContext, parts: RecipeParts, reward_fn: Any,
+                            reward_names: list[str], *,
+                            on_epoch_end: Callable[[int, Any, Any], Any] | None = None) -> Any:
+    from visionrl_b200.trainers.data import load_prompt_manifest
+
+    cfg, tc, bundle, mesh = ctx.cfg, ctx.trainer_config, parts.bundle, ctx.mesh
+    trainer, collector = build_online_trainer(ctx, parts, reward_fn)
 
     manifest = str(require(cfg, "data.manifest"))
     if not manifest.startswith("synthetic:") and not Path(manifest).exists():

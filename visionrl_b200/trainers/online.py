@@ -170,6 +170,7 @@ class OnlineTrainer(Trainer):
         self._ema: EMAModuleWrapper | None = None
         self._rollout_weights_initialized = False
         self.last_step_samples = 0
+        self.last_d2h_bytes = 0
         if self.config.optim.allow_tf32:
             torch.backends.cuda.matmul.allow_tf32 = True
 
@@ -502,6 +503,8 @@ class OnlineTrainer(Trainer):
         packed = torch.cat([means.to(adv_stats.device), adv_stats.float(),
                             gn.reshape(1).to(adv_stats.device)]).tolist()
         loss_v, pol_v, kl_v, clip_v, akl_v, zero_v, sat_v, r_mean, r_std, a_mean, gn_v = packed
+        self.last_d2h_bytes = 4 * len(packed)
+        self._check_kernel_status()
 
         phase_times = dict(timer.times)
         if cfg.profile:
@@ -525,6 +528,20 @@ class OnlineTrainer(Trainer):
         if self.weight_syncer is not None:
             await self.weight_syncer.push(self.model.state_dict())
         return out
+
+    def _check_kernel_status(self) -> None:
+        """Bounded device-side waits report here instead of hanging; raise if one gave up."""
+        if self.device.type != "cuda":
+            return
+        from visionrl_b200.ops import _ext
+
+        if not (_ext.kernels_enabled() and _ext.available()):
+            return
+        status = int(_ext.load().gemm_last_status())
+        self.last_d2h_bytes += 4
+        if status != 0:
+            raise RuntimeError(f"a GEMM kernel gave up waiting on a barrier (status {status}: "
+                               "1 = TMA producer, 2 = MMA issuer, 3 = epilogue)")
 
     # -- state -------------------------------------------------------------------------------------
     def state_dict(self) -> dict:
