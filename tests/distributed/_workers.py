@@ -1,0 +1,151 @@
+"""Worker bodies for multi-process tests (spawned with torch.multiprocessing)."""
+
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def _init(rank: int, world: int, port: int, backend: str) -> None:
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank),
+                      WORLD_SIZE=str(world), LOCAL_RANK=str(rank))
+    if backend == "nccl":
+        torch.cuda.set_device(rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world,
+                                device_id=torch.device("cuda", rank))
+    else:
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+
+
+def sharded_adamw_matches_single(rank, world, port, backend, collectives, out):
+    """Sharded reduce+clip+AdamW over `world` ranks equals one AdamW on the mean gradient."""
+    import copy
+
+    from visionrl_b200.ops.optim import FusedAdamW
+    from visionrl_b200.parallel.mesh import ProcessMesh
+    from visionrl_b200.parallel.sharded import ShardedGradSync
+
+    _init(rank, world, port, backend)
+    dev = torch.device("cuda", rank) if backend == "nccl" else torch.device("cpu")
+    dtype = torch.bfloat16 if backend == "nccl" else torch.float32
+    torch.manual_seed(0)
+    net = torch.nn.Sequential(torch.nn.Linear(24, 40), torch.nn.Linear(40, 8)).to(dev, dtype)
+    ref = copy.deepcopy(net).float()
+    mesh = ProcessMesh.build()
+    sync = ShardedGradSync(mesh, collectives=collectives)
+    opt = FusedAdamW(net.parameters(), lr=1e-2, weight_decay=0.01)
+    sync.prepare(opt)
+    ref_opt = torch.optim.AdamW(ref.parameters(), lr=1e-2, weight_decay=0.01)
+    norms = []
+    for step in range(3):
+        grads_all = []
+        for r in range(world):
+            g = torch.Generator().manual_seed(100 * step + r)
+            grads_all.append([torch.randn(p.shape, generator=g) for p in ref.parameters()])
+        opt.flat_buffers()
+        for p, g in zip(net.parameters(), grads_all[rank]):
+            p.grad.copy_(g.to(dev, dtype))
+        if dev.type == "cuda":
+            torch.cuda.synchronize()
+        norm = sync.reduce_clip_step(opt, max_norm=1.0)
+        norms.append(float(norm))
+        mean = [sum(gs[i].to(dtype).float() for gs in grads_all) / world
+                for i in range(len(grads_all[0]))]
+        for p, g in zip(ref.parameters(), mean):
+            p.grad = g.clone()
+        ref_norm = torch.nn.utils.clip_grad_norm_(ref.parameters(), 1.0)
+        ref_opt.step()
+        tol = 3e-2 if dtype == torch.bfloat16 else 1e-5
+        assert abs(float(ref_norm) - norms[-1]) <= tol * max(1.0, float(ref_norm)), (ref_norm, norm)
+    if dev.type == "cuda":
+        torch.cuda.synchronize()
+    err = max((a.detach().float().cpu() - b.detach()).abs().max().item()
+              for a, b in zip(net.parameters(), ref.parameters()))
+    # every rank must hold identical parameters after the all-gather
+    flat = torch.cat([p.detach().float().reshape(-1) for p in net.parameters()]).to(dev)
+    gathered = [torch.empty_like(flat) for _ in range(world)]
+    dist.all_gather(gathered, flat)
+    same = all(torch.equal(gathered[0], t) for t in gathered)
+    state = opt.state_dict()      # collective when sharded
+    if rank == 0:
+        out.put({"err": err, "same": same, "norms": norms,
+                 "state_keys": sorted(state["state"].keys()),
+                 "launches": getattr(sync, "kernel_launches", 0)})
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def ulysses_attention_matches_dense(rank, world, port, backend, use_kernels, out):
+    from visionrl_b200.ops.attention import attention_reference
+    from visionrl_b200.parallel.mesh import ProcessMesh
+    from visionrl_b200.parallel.ulysses import SequenceParallel
+
+    _init(rank, world, port, backend)
+    dev = torch.device("cuda", rank) if backend == "nccl" else torch.device("cpu")
+    dtype = torch.bfloat16 if backend == "nccl" else torch.float32
+    mesh = ProcessMesh.build(sp=world)
+    pool = None
+    if use_kernels:
+        from visionrl_b200.parallel.symm import SymmetricPool
+
+        pool = SymmetricPool(mesh, group=mesh.sp_group)
+    sp = SequenceParallel(mesh, pool)
+    torch.manual_seed(1)
+    b, h, s, d = 2, 4 * world, 16 * world, 64
+    q, k, v = (torch.randn(b, h, s, d).to(dev, dtype) for _ in range(3))
+    sl = slice(rank * s // world, (rank + 1) * s // world)
+    ql, kl, vl = (t[:, :, sl].clone().requires_grad_() for t in (q, k, v))
+    o = sp.attention(ql, kl, vl)
+    w = torch.randn(b, h, s, d, generator=torch.Generator().manual_seed(5)).to(dev, dtype)
+    (o.float() * w[:, :, sl].float()).sum().backward()
+    qf, kf, vf = (t.float().requires_grad_() for t in (q, k, v))
+    of = attention_reference(qf, kf, vf)
+    (of * w.float()).sum().backward()
+    tol = 3e-2 if dtype == torch.bfloat16 else 1e-4
+    ok_fwd = torch.allclose(o.float(), of[:, :, sl], atol=tol, rtol=tol)
+    ok_bwd = all(torch.allclose(a.grad.float(), b_.grad[:, :, sl], atol=tol * 4, rtol=tol * 4)
+                 for a, b_ in ((ql, qf), (kl, kf), (vl, vf)))
+    flags = torch.tensor([float(ok_fwd), float(ok_bwd)], device=dev)
+    dist.all_reduce(flags, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        out.put({"fwd": bool(flags[0]), "bwd": bool(flags[1]), "launches": sp.kernel_launches})
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def weight_broadcast_and_timeout(rank, world, port, out):
+    """Owner publishes a versioned buffer to every replica; a wait on a version nobody
+    publishes runs out and reports instead of hanging."""
+    from visionrl_b200.parallel.mesh import ProcessMesh
+    from visionrl_b200.parallel.symm import CollectiveTimeout, SymmetricPool
+    from visionrl_b200.parallel.weight_broadcast import DeviceWeightBroadcaster
+
+    _init(rank, world, port, "nccl")
+    dev = torch.device("cuda", rank)
+    mesh = ProcessMesh.build()
+    pool = SymmetricPool(mesh)
+    n = 1 << 16
+    bc = DeviceWeightBroadcaster(pool, n * world, torch.bfloat16, dev)
+    shard = torch.full((n,), float(rank + 1), device=dev, dtype=torch.bfloat16)
+    version = bc.publish(shard, offset_elems=rank * n)
+    for owner in range(world):
+        bc.wait_version(owner, version, timeout_s=5.0)
+    torch.cuda.synchronize()
+    want = torch.cat([torch.full((n,), float(r + 1)) for r in range(world)])
+    ok = torch.equal(bc.replica.float().cpu(), want)
+    timed_out = False
+    try:
+        bc.wait_version((rank + 1) % world, version + 7, timeout_s=0.2)
+    except CollectiveTimeout:
+        timed_out = True
+    flags = torch.tensor([float(ok), float(timed_out)], device=dev)
+    dist.all_reduce(flags, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        out.put({"ok": bool(flags[0]), "timed_out": bool(flags[1])})
+    dist.barrier()
+    dist.destroy_process_group()

@@ -1,0 +1,70 @@
+"""Multi-rank behaviour: gloo ranks on CPU (always), NCCL + in-kernel NVLink paths on >= 2 GPUs."""
+
+import socket
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+from tests.distributed import _workers
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _run(fn, world, *args, timeout=240):
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=fn, args=(r, world, port, *args, out)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout)
+    for p in procs:
+        if p.is_alive():
+            p.kill()
+            raise AssertionError("worker timed out")
+    assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+    return out.get(timeout=10)
+
+
+def test_sharded_adamw_gloo_world2():
+    res = _run(_workers.sharded_adamw_matches_single, 2, "gloo", "nccl")
+    assert res["err"] < 1e-5 and res["same"]
+    assert res["state_keys"] == [0, 1, 2, 3]
+
+
+def test_ulysses_attention_gloo_world2():
+    res = _run(_workers.ulysses_attention_matches_dense, 2, "gloo", False)
+    assert res["fwd"] and res["bwd"]
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+@pytest.mark.parametrize("collectives", ["nccl", "fused"])
+def test_sharded_adamw_gpu(collectives):
+    world = min(torch.cuda.device_count(), 4)
+    res = _run(_workers.sharded_adamw_matches_single, world, "nccl", collectives)
+    assert res["err"] < 2e-2 and res["same"]
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+@pytest.mark.parametrize("use_kernels", [False, True])
+def test_ulysses_attention_gpu(use_kernels):
+    world = 2
+    res = _run(_workers.ulysses_attention_matches_dense, world, "nccl", use_kernels)
+    assert res["fwd"] and res["bwd"]
+    assert (res["launches"] > 0) == use_kernels
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+def test_weight_broadcast_versions_and_bounded_wait():
+    world = min(torch.cuda.device_count(), 4)
+    res = _run(_workers.weight_broadcast_and_timeout, world)
+    assert res["ok"] and res["timed_out"]

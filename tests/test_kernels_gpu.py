@@ -53,7 +53,7 @@ def test_gemm_fp32_output_and_epilogues(ext):
     assert ext.gemm_last_status() == 0
 
 
-@pytest.mark.parametrize("m,n,k", [(256, 256, 128), (1178, 1536, 4608), (300, 520, 136)])
+@pytest.mark.parametrize("m,n,k", [(256, 256, 128), (1184, 1536, 4608), (296, 520, 136)])
 def test_gemm_transposed_operands(ext, m, n, k):
     """dX = dY @ W (B stored [K, N]) and dW = dY^T @ X (both operands stored [K, *])."""
     torch.manual_seed(2)
@@ -65,6 +65,15 @@ def test_gemm_transposed_operands(ext, m, n, k):
     out2 = ext.gemm_bf16(a_km, b_kn, None, None, None, 0, 0, True, True, False)
     assert _rel(out2, a_km.float().t() @ b_kn.float()) < 5e-3
     assert ext.gemm_last_status() == 0
+
+
+def test_gemm_rejects_unaligned_pitch(ext):
+    a = torch.randn(64, 300, device="cuda", dtype=torch.bfloat16)      # stored [K, M], M % 8 != 0
+    b = torch.randn(64, 256, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="pitch"):
+        ext.gemm_bf16(a, b, None, None, None, 0, 0, True, True, False)
+    ok = ext.gemm_bf16(a[:, :296].contiguous(), b, None, None, None, 0, 0, True, True, False)
+    assert ok.shape == (296, 256)
 
 
 def test_linear_autograd_matches_fp32():

@@ -1,10 +1,34 @@
 // Python bindings of the visionrl_b200 extension (module visionrl_b200._C).
 #include <torch/extension.h>
 
+#include <execinfo.h>
+#include <signal.h>
+#include <unistd.h>
+
+#include <cstdlib>
+
 #include "ops.h"
+
+namespace {
+// With VRL_SEGV_TRACE=1 a native backtrace is written to stderr before a SIGSEGV ends the
+// process (debugging aid; off by default).
+void segv_handler(int sig) {
+  void* frames[64];
+  const int n = backtrace(frames, 64);
+  const char msg[] = "\n[visionrl_b200] SIGSEGV, native frames:\n";
+  ssize_t ignored = write(STDERR_FILENO, msg, sizeof(msg) - 1);
+  (void)ignored;
+  backtrace_symbols_fd(frames, n, STDERR_FILENO);
+  signal(sig, SIG_DFL);
+  raise(sig);
+}
+}  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.doc() = "visionrl_b200 sm_100a kernels";
+  if (const char* flag = std::getenv("VRL_SEGV_TRACE")) {
+    if (flag[0] == '1') signal(SIGSEGV, segv_handler);
+  }
   m.def("sde_step_fwd", &vrl::sde_step_fwd);
   m.def("sde_step_bwd", &vrl::sde_step_bwd);
   m.def("token_loss_fwd", &vrl::token_loss_fwd);
@@ -17,6 +41,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("rmsnorm_bwd", &vrl::rmsnorm_bwd);
   m.def("qkv_prepare_fwd", &vrl::qkv_prepare_fwd);
   m.def("qkv_prepare_bwd", &vrl::qkv_prepare_bwd);
+  m.def("rs_sum_slice", &vrl::rs_sum_slice);
+  m.def("adamw_slice_broadcast", &vrl::adamw_slice_broadcast);
+  m.def("p2p_broadcast_versioned", &vrl::p2p_broadcast_versioned);
+  m.def("wait_flag", &vrl::wait_flag);
+  m.def("ulysses_scatter", &vrl::ulysses_scatter);
   m.def("gemm_bf16", &vrl::gemm_bf16);
   m.def("gemm_last_status", &vrl::gemm_last_status);
 }

@@ -24,7 +24,7 @@ sde_step_fwd_kernel(const float* __restrict__ v, const float* __restrict__ x,
                     const float* __restrict__ prev_in, const float* __restrict__ noise,
                     float* __restrict__ prev_out, float* __restrict__ mean_out,
                     float* __restrict__ partial, int64_t n, int blocks_per_sample,
-                    int deterministic) {
+                    int deterministic, int vec_ok) {
   __shared__ float red[32];
   const int sample = blockIdx.y;
   const float ca = a[sample], cb = b[sample], cs = scale[sample], cdt = dt[sample];
@@ -34,7 +34,7 @@ sde_step_fwd_kernel(const float* __restrict__ v, const float* __restrict__ x,
 #pragma unroll
   for (int it = 0; it < 4; ++it) {
     const int64_t i = start + ((int64_t)it * kSdeThreads + threadIdx.x) * 4;
-    if (i + 3 < n) {
+    if (vec_ok && i + 3 < n) {
       const float4 vv = *reinterpret_cast<const float4*>(v + base + i);
       const float4 xx = *reinterpret_cast<const float4*>(x + base + i);
       float4 mu, pr;
@@ -87,6 +87,14 @@ __global__ void sde_logprob_finalize_kernel(const float* __restrict__ partial,
   }
 }
 
+// float4 accesses need every sample's base (sample * n floats) on a 16-byte boundary
+static int sde_vector_ok(const float* v, const float* x, const float* prev_in, const float* noise,
+                         const float* prev_out, const float* mean_out, int64_t n) {
+  auto aligned = [](const void* p) { return p == nullptr || reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+  return (n % 4 == 0 && aligned(v) && aligned(x) && aligned(prev_in) && aligned(noise) &&
+          aligned(prev_out) && aligned(mean_out)) ? 1 : 0;
+}
+
 void sde_step_launch(const float* v, const float* x, const float* a, const float* b,
                      const float* scale, const float* dt, const float* prev_in,
                      const float* noise, float* prev_out, float* mean_out, float* logp,
@@ -96,7 +104,9 @@ void sde_step_launch(const float* v, const float* x, const float* a, const float
   dim3 grid(bps, batch);
   sde_step_fwd_kernel<<<grid, kSdeThreads, 0, stream>>>(v, x, a, b, scale, dt, prev_in, noise,
                                                         prev_out, mean_out, partial, n, bps,
-                                                        deterministic ? 1 : 0);
+                                                        deterministic ? 1 : 0,
+                                                        sde_vector_ok(v, x, prev_in, noise, prev_out,
+                                                                      mean_out, n));
   sde_logprob_finalize_kernel<<<(batch + 127) / 128, 128, 0, stream>>>(partial, scale, logp, bps,
                                                                        n, gaussian ? 1 : 0, batch);
 }
@@ -116,7 +126,6 @@ std::vector<torch::Tensor> sde_step_fwd(torch::Tensor v, torch::Tensor x, torch:
   const c10::cuda::CUDAGuard guard(v.device());
   const int batch = (int)v.size(0);
   const int64_t n = v.numel() / batch;
-  TORCH_CHECK(n % 4 == 0 || true);
   auto prev_out = torch::empty_like(v);
   auto mean_out = torch::empty_like(v);
   auto logp = torch::empty({batch}, v.options());

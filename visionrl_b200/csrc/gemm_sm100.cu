@@ -40,7 +40,7 @@ constexpr uint32_t kBBytes = BN * BK * 2;          // 32 KiB
 constexpr uint32_t kStageBytes = kABytes + kBBytes;
 constexpr uint32_t kTmemCols = 512;                // two 256-column fp32 accumulators
 constexpr uint32_t kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
-constexpr uint32_t kSpinLimit = 1u << 26;          // ~ a second of polling at most
+constexpr uint32_t kSpinLimit = 1u << 22;          // bounded polling (order of a second)
 
 enum Status : int { kOk = 0, kTimeoutProducer = 1, kTimeoutMma = 2, kTimeoutEpilogue = 3 };
 
@@ -362,17 +362,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 // --------------------------------------------------------------------------------- host side
 using EncodeFn = PFN_cuTensorMapEncodeTiled_v12000;
 
+static EncodeFn lookup_encode_fn() {
+  void* ptr = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  C10_CUDA_CHECK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q));
+  TORCH_CHECK(ptr != nullptr && q == cudaDriverEntryPointSuccess,
+              "cuTensorMapEncodeTiled is not available from this driver");
+  return reinterpret_cast<EncodeFn>(ptr);
+}
+
 static EncodeFn encode_fn() {
-  static EncodeFn fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    C10_CUDA_CHECK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q));
-    TORCH_CHECK(ptr != nullptr && q == cudaDriverEntryPointSuccess,
-                "cuTensorMapEncodeTiled is not available from this driver");
-    fn = reinterpret_cast<EncodeFn>(ptr);
-  });
+  static EncodeFn fn = lookup_encode_fn();     // thread-safe function-local static
   return fn;
 }
 
@@ -426,6 +426,13 @@ torch::Tensor gemm_bf16(torch::Tensor a, torch::Tensor b, c10::optional<torch::T
   TORCH_CHECK(a.scalar_type() == torch::kBFloat16 && b.scalar_type() == torch::kBFloat16);
   TORCH_CHECK(a.stride(1) == 1 && b.stride(1) == 1, "gemm_bf16: innermost dimension must be contiguous");
   const c10::cuda::CUDAGuard guard(a.device());
+  // The tensor-map encoder is a driver entry point.  A thread that has made no runtime call yet
+  // (a fresh autograd worker) has no context bound, so bind the primary context once per thread.
+  static thread_local bool context_bound = false;
+  if (!context_bound) {
+    C10_CUDA_CHECK(cudaFree(nullptr));
+    context_bound = true;
+  }
   // logical sizes: A is [M, K] (or stored [K, M] when MN-major), B is [N, K] (or stored [K, N])
   const int64_t m = a_mn_major ? a.size(1) : a.size(0);
   const int64_t k = a_mn_major ? a.size(0) : a.size(1);
@@ -471,11 +478,12 @@ torch::Tensor gemm_bf16(torch::Tensor a, torch::Tensor b, c10::optional<torch::T
   p.b_mn = b_mn_major ? 1 : 0;
   p.out_fp32 = out_fp32 ? 1 : 0;
 
-  static std::once_flag attr_once;
-  std::call_once(attr_once, [] {
+  static const bool attr_set = [] {
     C10_CUDA_CHECK(cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         kSmemBytes));
-  });
+    return true;
+  }();
+  (void)attr_set;
   const int tiles = (int)(((m + BM - 1) / BM) * ((n + BN - 1) / BN));
   const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
   const int grid = std::min(tiles, sms);

@@ -53,6 +53,20 @@ std::vector<torch::Tensor> qkv_prepare_bwd(torch::Tensor gq, torch::Tensor gk, t
                                            c10::optional<torch::Tensor> sin, torch::Tensor rstd,
                                            int64_t heads);
 
+// collective.cu
+torch::Tensor rs_sum_slice(torch::Tensor peers, torch::Tensor out, int64_t lo, int64_t n,
+                           int64_t world, int64_t rank, bool is_bf16, double scale);
+void adamw_slice_broadcast(torch::Tensor peers, torch::Tensor g, torch::Tensor master,
+                           torch::Tensor m, torch::Tensor v, int64_t lo, int64_t n, int64_t world,
+                           int64_t rank, double lr, double b1, double b2, double eps, double wd,
+                           int64_t step, c10::optional<torch::Tensor> clip, bool is_bf16);
+void p2p_broadcast_versioned(torch::Tensor src, torch::Tensor dst_peers, int64_t dst_offset_bytes,
+                             torch::Tensor flag_peers, int64_t flag_slot, int64_t world,
+                             int64_t rank, int64_t version, bool include_self);
+torch::Tensor wait_flag(torch::Tensor flags, int64_t slot, int64_t expected, double timeout_s);
+void ulysses_scatter(torch::Tensor src, torch::Tensor dst_peers, int64_t batch, int64_t heads,
+                     int64_t s_loc, int64_t head_dim, int64_t world, int64_t rank, bool to_heads);
+
 // gemm_sm100.cu
 torch::Tensor gemm_bf16(torch::Tensor a, torch::Tensor b, c10::optional<torch::Tensor> bias,
                         c10::optional<torch::Tensor> gate, c10::optional<torch::Tensor> residual,

@@ -1,0 +1,68 @@
+"""Wan variant with two timestep experts and sequential CFG.
+
+A high-noise and a low-noise transformer are switched at a boundary timestep
+(``boundary * num_train_timesteps``); conditional and unconditional branches run as two
+forwards; encoded prompts are cached by a SHA-256 key.  As in the reference
+(``vrl/models/families/wan_2_1/official_policy.py:65-602``) this variant is rollout-only:
+it has no adapter path and ``restore_eval_state`` raises.
+"""
+
+from __future__ import annotations
+
+import copy
+import hashlib
+from typing import Any
+
+import torch
+
+from visionrl_b200.models.families.wan_2_1.diffusers_policy import WanT2VDiffusersPolicy
+
+
+class WanT2VOfficialPolicy(WanT2VDiffusersPolicy):
+    family = "wan_2_1"
+
+    def __init__(self, *args: Any, boundary: float = 0.875, **kwargs: Any) -> None:
+        super().__init__(*args, **kwargs)
+        self.boundary = boundary
+        object.__setattr__(self, "_low_noise", None)
+        self._prompt_cache: dict[str, dict[str, Any]] = {}
+
+    def attach_low_noise_expert(self, module: torch.nn.Module | None = None) -> None:
+        expert = module if module is not None else copy.deepcopy(self.transformer)
+        object.__setattr__(self, "_low_noise", expert.requires_grad_(False).eval())
+
+    def _expert(self, t: torch.Tensor):
+        low = self._low_noise
+        if low is None:
+            return self.transformer
+        threshold = self.boundary * self._scheduler.num_train_timesteps
+        return self.transformer if float(t.flatten()[0]) >= threshold else low
+
+    def encode_prompt(self, prompt, negative_prompt=None, **kwargs: Any) -> dict[str, Any]:
+        key = hashlib.sha256(repr((prompt, negative_prompt, kwargs.get("max_sequence_length"),
+                                   kwargs.get("guidance_scale"))).encode()).hexdigest()
+        if key not in self._prompt_cache:
+            self._prompt_cache[key] = super().encode_prompt(prompt, negative_prompt, **kwargs)
+        return dict(self._prompt_cache[key])
+
+    def forward_step(self, state, step_idx: int) -> dict[str, Any]:
+        t = state.timesteps[step_idx]
+        b = state.latents.shape[0]
+        t_batch = t.expand(b) if t.ndim == 0 else t
+        net = self._expert(t_batch)
+        cond = net(state.latents, t_batch, state.prompt_embeds).float()
+        if state.do_cfg:
+            uncond = net(state.latents, t_batch, state.negative_prompt_embeds).float()
+            noise_pred = uncond + state.guidance_scale * (cond - uncond)
+        else:
+            uncond, noise_pred = torch.zeros_like(cond), cond
+        return {"noise_pred": noise_pred, "noise_pred_cond": cond, "noise_pred_uncond": uncond}
+
+    def apply_lora(self, spec: Any) -> None:
+        raise NotImplementedError("the two-expert Wan variant has no adapter path")
+
+    def restore_eval_state(self, batch_extras, batch_context, latents, step_idx):
+        raise NotImplementedError("the two-expert Wan variant is rollout-only (no replay path)")
+
+
+__all__ = ["WanT2VOfficialPolicy"]

@@ -109,16 +109,23 @@ class LlamaLayer(nn.Module):
         x = x + self.attn.out(merge_heads(o))
         return x + self.mlp(self.mlp_norm(x))
 
-    def decode(self, x, cos, sin, cache: KVCache, layer_idx: int):
-        """``x[R, 1, D]`` at position ``cache.length`` (already marked valid)."""
+    def decode(self, x, cos, sin, cache: KVCache, layer_idx: int, rows=None, pos=None):
+        """``x[R, 1, D]`` at position ``pos`` (already marked valid) of cache rows ``rows``."""
         q, k, v = self.attn._split(self.attn.qkv(self.attn_norm(x)))
         q = apply_rope_reference(q, cos, sin)
         k = apply_rope_reference(k, cos, sin)
-        pos = cache.length
-        cache.data[layer_idx, 0, :, :, pos] = k[:, :, 0]
-        cache.data[layer_idx, 1, :, :, pos] = v[:, :, 0]
-        o = attn_ops.decode_attention(q, cache.data[layer_idx, 0], cache.data[layer_idx, 1],
-                                      cache.valid, pos + 1)
+        pos = cache.length if pos is None else pos
+        if rows is None:
+            cache.data[layer_idx, 0, :, :, pos] = k[:, :, 0]
+            cache.data[layer_idx, 1, :, :, pos] = v[:, :, 0]
+            o = attn_ops.decode_attention(q, cache.data[layer_idx, 0], cache.data[layer_idx, 1],
+                                          cache.valid, pos + 1)
+        else:
+            cache.data[layer_idx, 0, rows, :, pos] = k[:, :, 0]
+            cache.data[layer_idx, 1, rows, :, pos] = v[:, :, 0]
+            o = attn_ops.decode_attention_reference(
+                q, cache.data[layer_idx, 0][rows], cache.data[layer_idx, 1][rows],
+                cache.valid[rows], pos + 1)
         x = x + self.attn.out(merge_heads(o))
         return x + self.mlp(self.mlp_norm(x))
 
@@ -165,16 +172,27 @@ class LlamaDecoder(AdapterMixin, nn.Module):
                 x = layer(x, cos, sin, bias, cache, i, 0)
         return self.norm(x)
 
-    def decode_step(self, embeds, cache: KVCache):
-        """``embeds[R, D]`` for the next position of every row → hidden ``[R, D]``."""
-        pos = cache.length
+    def decode_step(self, embeds, cache: KVCache, rows=None, position: int | None = None):
+        """``embeds[R, D]`` for the next position → hidden ``[R, D]``.
+
+        Without ``rows`` every cache row advances together from ``cache.length``.  With ``rows``
+        (a long tensor) only those rows are stepped, at the explicit ``position``; rows may then
+        sit at different lengths, which token-level scheduling needs.
+        """
+        pos = cache.length if position is None else int(position)
         if pos >= cache.max_len:
             raise RuntimeError(f"KV cache is full ({cache.max_len} positions)")
-        cache.valid[:, pos] = True
+        if rows is None:
+            cache.valid[:, pos] = True
+        else:
+            cache.valid[rows, pos] = True
         cos, sin = rope_tables(torch.tensor([pos], device=embeds.device), self.head_dim,
                                self.cfg.rope_theta)
         x = embeds.unsqueeze(1)
         for i, layer in enumerate(self.layers):
-            x = layer.decode(x, cos, sin, cache, i)
-        cache.length = pos + 1
+            x = layer.decode(x, cos, sin, cache, i, rows, pos)
+        if rows is None:
+            cache.length = pos + 1
+        else:
+            cache.length = max(cache.length, pos + 1)
         return self.norm(x)[:, 0]

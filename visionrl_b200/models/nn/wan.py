@@ -45,6 +45,8 @@ class WanConfig:
         out = {k: d[k] for k in keys if k in d}
         if "patch_size" in out:
             out["patch_size"] = tuple(out["patch_size"])
+        if "in_channels" in out and "out_channels" not in out:
+            out["out_channels"] = out["in_channels"]
         return cls(**out)
 
 

@@ -37,6 +37,9 @@ class ShardedGradSync:
         self.collectives = collectives
         self._symm = None
         self.kernel_launches = 0
+        # ranks of one sequence-parallel group hold partial sums of the same samples' gradient
+        # (sum them), data-parallel ranks hold different samples (average them)
+        self.grad_scale = float(mesh.sp) / float(max(mesh.world_size, 1))
 
     # -- set-up ----------------------------------------------------------------------------
     def prepare(self, optimizer: Any) -> None:
@@ -45,11 +48,14 @@ class ShardedGradSync:
             return
         if self.shard_optimizer and hasattr(optimizer, "set_shard") and not optimizer._built:
             optimizer.set_shard(self.mesh.rank, self.mesh.world_size)
-        if self.collectives == "fused" and torch.cuda.is_available() and not optimizer._built:
+        if (self.collectives == "fused" and torch.cuda.is_available() and not optimizer._built
+                and self.shard_optimizer):
+            from visionrl_b200.ops import _ext
             from visionrl_b200.parallel.symm import SymmetricPool
 
-            self._symm = SymmetricPool(self.mesh)
-            optimizer.set_allocator(self._symm.allocate)
+            if _ext.kernels_enabled():
+                self._symm = SymmetricPool(self.mesh)
+                optimizer.set_allocator(self._symm.allocate)
 
     # -- the step ----------------------------------------------------------------------------
     @torch.no_grad()
@@ -74,10 +80,11 @@ class ShardedGradSync:
             g = e["grad"]
             if g.is_cuda and self.shard_optimizer:
                 shard = torch.empty(n, dtype=g.dtype, device=g.device)
-                dist.reduce_scatter_tensor(shard, g, op=dist.ReduceOp.AVG)
+                dist.reduce_scatter_tensor(shard, g, op=dist.ReduceOp.SUM)
+                shard.mul_(self.grad_scale)
             else:
                 dist.all_reduce(g, op=dist.ReduceOp.SUM)
-                g.div_(world)
+                g.mul_(self.grad_scale)
                 shard = g[lo:lo + n] if self.shard_optimizer else g
             e["grad_shard"] = shard if self.shard_optimizer else None
             sq = shard.float().pow(2).sum()
@@ -107,33 +114,33 @@ class ShardedGradSync:
 
         ext = _ext.load()
         symm = self._symm
+        world, rank = self.mesh.world_size, self.mesh.rank
         sq_total = None
-        # phase 1: every rank sums the peers' partials of its own slice (P2P loads), writes the
-        # fp32 mean gradient slice and its sum of squares
+        # every rank's backward (which wrote its partial gradients) must be complete
         symm.barrier()
+        # phase 1: sum the peers' partials of the owned slice with P2P loads -> fp32 mean gradient
         for e in flat:
-            peers = symm.peer_pointers(e["grad"])
             if "grad_f32" not in e:
                 e["grad_f32"] = torch.empty(e["shard"], dtype=torch.float32, device=e["grad"].device)
-            sq = ext.rs_sum_slice(peers, e["grad_f32"], e["lo"], e["shard"], self.mesh.world_size,
-                                  e["grad"].dtype == torch.bfloat16)
-            self.kernel_launches += 1
+            sq = ext.rs_sum_slice(symm.peer_pointers(e["grad"]), e["grad_f32"], e["lo"], e["shard"],
+                                  world, rank, e["grad"].dtype == torch.bfloat16,
+                                  self.grad_scale)
             sq_total = sq if sq_total is None else sq_total + sq
         dist.all_reduce(sq_total, op=dist.ReduceOp.SUM)
         norm = sq_total.sqrt()
-        coef = (max_norm / (norm + 1e-6)).clamp(max=1.0) if max_norm > 0 \
-            else torch.ones((), device=norm.device)
-        # phase 2: AdamW on the slice, new bf16 values stored into every rank's parameter buffer
+        coef = (max_norm / (norm + 1e-6)).clamp(max=1.0) if max_norm > 0 else None
+        # phase 2: AdamW on the slice; the new bf16 values go straight into every rank's buffer
         for e in flat:
             e["step"] += 1
             g = e["group"]
             b1, b2 = g["betas"]
             ext.adamw_slice_broadcast(
                 symm.peer_pointers(e["param"]), e["grad_f32"], e["master"], e["exp_avg"],
-                e["exp_avg_sq"], e["lo"], e["shard"], self.mesh.world_size, float(g["lr"]),
-                float(b1), float(b2), float(g["eps"]), float(g["weight_decay"]), int(e["step"]),
-                coef, e["param"].dtype == torch.bfloat16)
-            self.kernel_launches += 1
-        symm.barrier()      # peers' stores into our parameter buffer are complete
+                e["exp_avg_sq"], e["lo"], e["shard"], world, rank, float(g["lr"]), float(b1),
+                float(b2), float(g["eps"]), float(g["weight_decay"]), int(e["step"]), coef,
+                e["param"].dtype == torch.bfloat16)
+        # peers' stores into this rank's parameters are complete, and nobody still reads the
+        # gradients that are zeroed next
+        symm.barrier()
         optimizer.zero_grad()
         return norm
