@@ -299,3 +299,35 @@ def test_mmdit_forward_backward_kernels_vs_torch_ops():
     assert _rel(outs[0][0], outs[1][0]) < 3e-2
     assert _rel(outs[0][1], outs[1][1]) < 6e-2
     assert _ext.load().gemm_last_status() == 0
+
+
+@pytest.mark.gpu
+def test_colsum_matches_fp32():
+    from visionrl_b200.ops import _ext
+
+    x = torch.randn(4712, 1536, device="cuda", dtype=torch.bfloat16)
+    got = _ext.load().colsum(x)
+    ref = x.float().sum(0)
+    assert torch.allclose(got, ref, atol=2e-2, rtol=1e-3)
+    x = torch.randn(37, 72, device="cuda", dtype=torch.bfloat16)
+    assert torch.allclose(_ext.load().colsum(x), x.float().sum(0), atol=1e-3, rtol=1e-3)
+
+
+@pytest.mark.gpu
+def test_adaln_accepts_strided_modulation_views():
+    from visionrl_b200.ops.norm import adaln_layernorm
+
+    b, s, d = 3, 77, 256
+    x = torch.randn(b, s, d, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    mod = torch.randn(b, 6 * d, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    shift, scale = mod[:, d:2 * d], mod[:, 3 * d:4 * d]
+    y = adaln_layernorm(x, shift, scale, 1e-6)
+    xf, mf = x.detach().float().requires_grad_(), mod.detach().float().requires_grad_()
+    ref = torch.nn.functional.layer_norm(xf, (d,), eps=1e-6) * (1 + mf[:, None, 3 * d:4 * d]) \
+        + mf[:, None, d:2 * d]
+    assert torch.allclose(y.float(), ref, atol=3e-2, rtol=3e-2)
+    g = torch.randn_like(y)
+    y.backward(g)
+    ref.backward(g.float())
+    assert torch.allclose(x.grad.float(), xf.grad, atol=5e-2, rtol=5e-2)
+    assert torch.allclose(mod.grad.float(), mf.grad, atol=0.15, rtol=5e-2)

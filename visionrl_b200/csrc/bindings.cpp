@@ -34,6 +34,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("token_loss_fwd", &vrl::token_loss_fwd);
   m.def("per_sample_mse", &vrl::per_sample_mse);
   m.def("sum_squares", &vrl::sum_squares);
+  m.def("colsum", &vrl::colsum);
   m.def("adamw_flat", &vrl::adamw_flat);
   m.def("adaln_fwd", &vrl::adaln_fwd);
   m.def("adaln_bwd", &vrl::adaln_bwd);

@@ -456,4 +456,55 @@ void adamw_flat(torch::Tensor p, torch::Tensor g, torch::Tensor master, torch::T
 #undef LAUNCH
 }
 
+// ------------------------------------------------------------------------------------------
+// Column sums of a [rows, cols] bf16 matrix (bias gradients): fp32 accumulation, bf16 result.
+// Each block owns 64 columns x a slab of rows; slabs are combined with fp32 atomics.
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+colsum_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ out, int64_t rows, int cols,
+              int rows_per_block) {
+  __shared__ float tile[32][8 * 8 + 1];
+  const int cvec = threadIdx.x & 7;               // 8 vectors of 8 columns = 64 columns
+  const int rlane = threadIdx.x >> 3;             // 32 row lanes
+  const int col = blockIdx.x * 64 + cvec * 8;
+  const int64_t r0 = (int64_t)blockIdx.y * rows_per_block;
+  const int64_t r1 = min(rows, r0 + rows_per_block);
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (col < cols) {
+    for (int64_t r = r0 + rlane; r < r1; r += 32) {
+      float f[8];
+      unpack8(*reinterpret_cast<const bf16x8*>(x + r * cols + col), f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += f[j];
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) tile[rlane][cvec * 8 + j] = acc[j];
+  __syncthreads();
+  if (threadIdx.x < 64) {
+    float s = 0.f;
+#pragma unroll
+    for (int r = 0; r < 32; ++r) s += tile[r][threadIdx.x];
+    const int c = blockIdx.x * 64 + threadIdx.x;
+    if (c < cols) atomicAdd(out + c, s);
+  }
+}
+
+torch::Tensor colsum(torch::Tensor x) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.scalar_type() == torch::kBFloat16 && x.is_contiguous());
+  TORCH_CHECK(x.size(1) % 8 == 0 && reinterpret_cast<uintptr_t>(x.data_ptr()) % 16 == 0);
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int64_t rows = x.size(0);
+  const int cols = (int)x.size(1);
+  auto out = torch::zeros({cols}, x.options().dtype(torch::kFloat32));
+  const int col_blocks = (cols + 63) / 64;
+  const int row_blocks = (int)std::max<int64_t>(1, std::min<int64_t>((rows + 511) / 512, 1184 / col_blocks + 1));
+  const int rows_per_block = (int)((rows + row_blocks - 1) / row_blocks);
+  colsum_kernel<<<dim3(col_blocks, row_blocks), 256, 0, at::cuda::getCurrentCUDAStream()>>>(
+      reinterpret_cast<const __nv_bfloat16*>(x.data_ptr()), out.data_ptr<float>(), rows, cols,
+      rows_per_block);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return out;
+}
+
 }  // namespace vrl

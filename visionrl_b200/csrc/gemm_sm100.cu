@@ -13,8 +13,9 @@
 //     status word, drains its own TMA copies (bounded as well), frees its tensor memory and
 //     returns; the host raises after the launch completes.
 //
-// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer and TMEM owner,
-// warps 2..5 = epilogue (warp w may only touch TMEM lanes 32*(w%4) .. 32*(w%4)+31).
+// Warp roles (320 threads): warp 0 = TMA producer, warp 1 = MMA issuer and TMEM owner,
+// warps 2..9 = epilogue.  Warp w may only touch TMEM lanes 32*(w%4) .. 32*(w%4)+31, so two
+// warps share every lane quarter and split the 256 accumulator columns between them.
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <cuda.h>
@@ -34,7 +35,7 @@ namespace gemm {
 constexpr int BM = 128, BN = 256, BK = 64;
 constexpr int UMMA_K = 16;
 constexpr int kStages = 4;
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;      // TMA warp, MMA warp, 8 epilogue warps
 constexpr uint32_t kABytes = BM * BK * 2;          // 16 KiB
 constexpr uint32_t kBBytes = BN * BK * 2;          // 32 KiB
 constexpr uint32_t kStageBytes = kABytes + kBBytes;
@@ -53,6 +54,7 @@ struct Params {
   int m, n, k;
   int act;                         // 0 none, 1 gelu-tanh, 2 silu
   int rows_per_gate;
+  int64_t gate_ld;                 // elements between consecutive gate rows
   int a_mn, b_mn;
   int out_fp32;
 };
@@ -198,7 +200,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 8); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -284,6 +286,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   } else if (warp >= 2) {
     // ---------------------------------------------------------------------- epilogue
     const int quarter = warp & 3;                 // TMEM lane quarter this warp may read
+    const int half = (warp - 2) >> 2;             // which 128 accumulator columns it handles
     uint32_t tile_it = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_it) {
@@ -295,7 +298,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       const bool row_ok = row < p.m;
       const int64_t gate_row = p.gate ? (row / p.rows_per_gate) : 0;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = half * (BN / 64); c < (half + 1) * (BN / 64); ++c) {
         uint32_t r[32];
         tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN + c * 32, r);
         const int col0 = n0 + c * 32;
@@ -322,7 +325,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           }
           if (p.gate) {
             float gt[8], rs[8];
-            unpack8(*reinterpret_cast<const bf16x8*>(p.gate + gate_row * p.n + col), gt);
+            unpack8(*reinterpret_cast<const bf16x8*>(p.gate + gate_row * p.gate_ld + col), gt);
             unpack8(*reinterpret_cast<const bf16x8*>(p.residual + (int64_t)row * p.n + col), rs);
 #pragma unroll
             for (int j = 0; j < 8; ++j) v[j] = rs[j] + gt[j] * v[j];
@@ -461,9 +464,15 @@ torch::Tensor gemm_bf16(torch::Tensor a, torch::Tensor b, c10::optional<torch::T
   }
   if (gate.has_value()) {
     TORCH_CHECK(residual.has_value() && rows_per_gate > 0, "gate needs residual and rows_per_gate");
-    gate_c = gate->to(torch::kBFloat16).contiguous();
-    TORCH_CHECK(gate_c.numel() == (m / rows_per_gate) * n && m % rows_per_gate == 0);
+    gate_c = *gate;
+    const bool strided_ok = gate_c.dim() == 2 && gate_c.scalar_type() == torch::kBFloat16 &&
+                            gate_c.stride(1) == 1 && gate_c.stride(0) % 8 == 0 &&
+                            reinterpret_cast<uintptr_t>(gate_c.data_ptr()) % 16 == 0;
+    if (!strided_ok) gate_c = gate_c.to(torch::kBFloat16).contiguous().view({-1, n});
+    TORCH_CHECK(gate_c.size(0) == m / rows_per_gate && gate_c.size(1) == n && m % rows_per_gate == 0,
+                "gate must be [M / rows_per_gate, N]");
     p.gate = reinterpret_cast<const __nv_bfloat16*>(gate_c.data_ptr());
+    p.gate_ld = gate_c.stride(0);
   }
   if (residual.has_value()) {
     res_c = residual->to(torch::kBFloat16).contiguous();

@@ -18,11 +18,21 @@ constexpr int kBwdRows = 16;
 
 using bf16 = __nv_bfloat16;
 
+// A [B, D] bf16 operand whose rows may sit `stride(0)` apart (a column slice of a wider
+// modulation tensor); copied only when it is not row-strided with 16-byte aligned rows.
+static torch::Tensor strided_rows(torch::Tensor t, int64_t b, int64_t d) {
+  TORCH_CHECK(t.dim() == 2 && t.size(0) == b && t.size(1) == d, "expected a [B, D] tensor");
+  const bool ok = t.scalar_type() == torch::kBFloat16 && t.stride(1) == 1 && t.stride(0) % 8 == 0 &&
+                  reinterpret_cast<uintptr_t>(t.data_ptr()) % 16 == 0;
+  return ok ? t : t.to(torch::kBFloat16).contiguous();
+}
+
 // ------------------------------------------------------------------------------ adaLN forward
 __global__ void __launch_bounds__(kNormThreads)
 adaln_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ shift,
                  const bf16* __restrict__ scale, bf16* __restrict__ y, float* __restrict__ mean_o,
-                 float* __restrict__ rstd_o, int rows_per_sample, int d, float eps) {
+                 float* __restrict__ rstd_o, int rows_per_sample, int d, float eps,
+                 int64_t shift_ld, int64_t scale_ld) {
   __shared__ float red[32];
   const int64_t row = blockIdx.x;
   const int sample = (int)(row / rows_per_sample);
@@ -51,8 +61,8 @@ adaln_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ shift,
   }
   const float rstd = rsqrtf(block_sum(q, red) / (float)d + eps);
   if (threadIdx.x == 0) { mean_o[row] = mu; rstd_o[row] = rstd; }
-  const bf16x8* sh = reinterpret_cast<const bf16x8*>(shift + (int64_t)sample * d);
-  const bf16x8* sc = reinterpret_cast<const bf16x8*>(scale + (int64_t)sample * d);
+  const bf16x8* sh = reinterpret_cast<const bf16x8*>(shift + (int64_t)sample * shift_ld);
+  const bf16x8* sc = reinterpret_cast<const bf16x8*>(scale + (int64_t)sample * scale_ld);
   bf16x8* yr = reinterpret_cast<bf16x8*>(y + row * d);
 #pragma unroll
   for (int k = 0; k < kMaxVec; ++k) {
@@ -74,16 +84,16 @@ std::vector<torch::Tensor> adaln_fwd(torch::Tensor x, torch::Tensor shift, torch
   const c10::cuda::CUDAGuard guard(x.device());
   const int b = (int)x.size(0), s = (int)x.size(1), d = (int)x.size(2);
   TORCH_CHECK(d % 8 == 0 && d <= 8 * kMaxVec * kNormThreads, "adaln: D must be a multiple of 8, <= 8192");
-  shift = shift.to(torch::kBFloat16).contiguous();
-  scale = scale.to(torch::kBFloat16).contiguous();
-  TORCH_CHECK(shift.numel() == (int64_t)b * d && scale.numel() == (int64_t)b * d);
+  shift = strided_rows(shift, b, d);
+  scale = strided_rows(scale, b, d);
   auto y = torch::empty_like(x);
   auto mean = torch::empty({(int64_t)b * s}, x.options().dtype(torch::kFloat32));
   auto rstd = torch::empty_like(mean);
   adaln_fwd_kernel<<<b * s, kNormThreads, 0, at::cuda::getCurrentCUDAStream()>>>(
       reinterpret_cast<const bf16*>(x.data_ptr()), reinterpret_cast<const bf16*>(shift.data_ptr()),
       reinterpret_cast<const bf16*>(scale.data_ptr()), reinterpret_cast<bf16*>(y.data_ptr()),
-      mean.data_ptr<float>(), rstd.data_ptr<float>(), s, d, (float)eps);
+      mean.data_ptr<float>(), rstd.data_ptr<float>(), s, d, (float)eps, shift.stride(0),
+      scale.stride(0));
   return {y, mean, rstd};
 }
 
@@ -92,12 +102,12 @@ __global__ void __launch_bounds__(kNormThreads)
 adaln_bwd_kernel(const bf16* __restrict__ gy, const bf16* __restrict__ x,
                  const bf16* __restrict__ scale, const float* __restrict__ mean,
                  const float* __restrict__ rstd, bf16* __restrict__ gx, float* __restrict__ gshift,
-                 float* __restrict__ gscale, int rows_per_sample, int d) {
+                 float* __restrict__ gscale, int rows_per_sample, int d, int64_t scale_ld) {
   __shared__ float red[32];
   const int sample = blockIdx.y;
   const int nvec = d / 8;
   const int row0 = blockIdx.x * kBwdRows;
-  const bf16x8* sc = reinterpret_cast<const bf16x8*>(scale + (int64_t)sample * d);
+  const bf16x8* sc = reinterpret_cast<const bf16x8*>(scale + (int64_t)sample * scale_ld);
   float one_plus[kMaxVec][8], acc_sh[kMaxVec][8], acc_sc[kMaxVec][8];
 #pragma unroll
   for (int k = 0; k < kMaxVec; ++k) {
@@ -168,7 +178,7 @@ std::vector<torch::Tensor> adaln_bwd(torch::Tensor gy, torch::Tensor x, torch::T
   const c10::cuda::CUDAGuard guard(x.device());
   const int b = (int)x.size(0), s = (int)x.size(1), d = (int)x.size(2);
   gy = gy.to(torch::kBFloat16).contiguous();
-  scale = scale.to(torch::kBFloat16).contiguous();
+  scale = strided_rows(scale, b, d);
   auto gx = torch::empty_like(x);
   auto gshift = torch::zeros({b, d}, x.options().dtype(torch::kFloat32));
   auto gscale = torch::zeros({b, d}, x.options().dtype(torch::kFloat32));
@@ -177,7 +187,7 @@ std::vector<torch::Tensor> adaln_bwd(torch::Tensor gy, torch::Tensor x, torch::T
       reinterpret_cast<const bf16*>(gy.data_ptr()), reinterpret_cast<const bf16*>(x.data_ptr()),
       reinterpret_cast<const bf16*>(scale.data_ptr()), mean.data_ptr<float>(),
       rstd.data_ptr<float>(), reinterpret_cast<bf16*>(gx.data_ptr()), gshift.data_ptr<float>(),
-      gscale.data_ptr<float>(), s, d);
+      gscale.data_ptr<float>(), s, d, scale.stride(0));
   return {gx, gshift, gscale};
 }
 
@@ -440,7 +450,7 @@ std::vector<torch::Tensor> qkv_prepare_fwd(torch::Tensor qkv, c10::optional<torc
   return {q, k, v, rstd};
 }
 
-constexpr int kQkvBwdTokens = 8;
+constexpr int kQkvBwdTokens = 16;
 
 __global__ void __launch_bounds__(kNormThreads)
 qkv_prepare_bwd_kernel(const bf16* __restrict__ gq, const bf16* __restrict__ gk,
@@ -459,6 +469,11 @@ qkv_prepare_bwd_kernel(const bf16* __restrict__ gq, const bf16* __restrict__ gk,
     for (int i = threadIdx.x; i < 2 * wlen; i += blockDim.x) wacc[i] = 0.f;
   }
   __syncthreads();
+  float wg[kQkvMaxVec][8];
+#pragma unroll
+  for (int t = 0; t < kQkvMaxVec; ++t)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) wg[t][j] = 0.f;
   const int64_t tok0 = (int64_t)blockIdx.x * kQkvBwdTokens;
   for (int64_t tok = tok0; tok < tok0 + kQkvBwdTokens && tok < tokens; ++tok) {
     const int b = (int)(tok / seq), s = (int)(tok % seq);
@@ -506,7 +521,7 @@ qkv_prepare_bwd_kernel(const bf16* __restrict__ gq, const bf16* __restrict__ gk,
         xh[t][j] = xv[j] * rs;
         gn[t][j] = g[j] * ww[j];
         dot[t] += gn[t][j] * xh[t][j];
-        atomicAdd(&wacc[which * wlen + woff + j], g[j] * xh[t][j]);
+        wg[t][j] += g[j] * xh[t][j];
       }
       if (which == 0) tot_q += dot[t]; else tot_k += dot[t];
     }
@@ -530,6 +545,20 @@ qkv_prepare_bwd_kernel(const bf16* __restrict__ gq, const bf16* __restrict__ gk,
 #pragma unroll
       for (int j = 0; j < 8; ++j) o[j] = rs * (gn[t][j] - xh[t][j] * m);
       dst[i] = pack8(o);
+    }
+  }
+  if (mode != 0) {
+#pragma unroll
+    for (int t = 0; t < kQkvMaxVec; ++t) {
+      const int i = threadIdx.x + t * kNormThreads;
+      if (i >= nvec) continue;
+      const int which = i / vec_per_which;
+      if (which == 2) continue;
+      const int rem = i - which * vec_per_which;
+      const int j8 = rem % vec_per_head;
+      const int woff = mode == 1 ? j8 * 8 : rem * 8;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) atomicAdd(&wacc[which * wlen + woff + j], wg[t][j]);
     }
   }
   __syncthreads();

@@ -29,6 +29,7 @@ std::vector<torch::Tensor> token_loss_fwd(torch::Tensor lp, torch::Tensor old, t
                                           bool k3);
 torch::Tensor per_sample_mse(torch::Tensor pred, torch::Tensor target);
 torch::Tensor sum_squares(torch::Tensor g);
+torch::Tensor colsum(torch::Tensor x);
 void adamw_flat(torch::Tensor p, torch::Tensor g, torch::Tensor master, torch::Tensor m,
                 torch::Tensor v, double lr, double b1, double b2, double eps, double wd,
                 int64_t step, c10::optional<torch::Tensor> clip);

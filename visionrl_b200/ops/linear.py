@@ -95,7 +95,9 @@ class _LinearFn(torch.autograd.Function):
         if ctx.needs_input_grad[1]:
             gw = gemm_tn(gy2, x2)
         if ctx.has_bias and ctx.needs_input_grad[2]:
-            gb = gy2.float().sum(0).to(gy2.dtype)
+            from visionrl_b200.ops import _ext
+
+            gb = _ext.load().colsum(gy2).to(gy2.dtype)
         return gx, gw, gb
 
 
@@ -113,6 +115,8 @@ def linear(x, w, bias=None, act=None, gate=None, residual=None):
         if not x2.is_contiguous():
             x2 = x2.contiguous()
         rows = x.shape[-2] if (gate is not None and x.dim() == 3) else (1 if gate is not None else 0)
+        if gate is not None and gate.dim() != 2:
+            gate = gate.reshape(-1, w.shape[0])
         res2 = None if residual is None else residual.reshape(-1, w.shape[0])
         y = gemm_nt(x2, w, bias, act, gate, res2, rows)
         return y.view(*x.shape[:-1], w.shape[0])

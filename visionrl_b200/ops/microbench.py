@@ -1,0 +1,188 @@
+"""Per-kernel micro-benchmarks: ``python -m visionrl_b200.ops.microbench <kernel> [options]``.
+
+Every case times the sm_100a kernel with CUDA events on the launching stream (warm-up first,
+synchronise on both sides, a buffer larger than L2 rewritten between iterations) and prints one
+JSON line with the achieved throughput, the same figure for the library / eager counterpart,
+and the fraction of the roofline denominator passed with ``--peak-tflops`` / ``--peak-gbs``.
+The same entry points are what the profiler captures are taken from (``--iters 1 --warmup 1``).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+
+import torch
+
+_L2_FLUSH_BYTES = 256 << 20
+
+
+def _time(fn, iters: int, warmup: int, flush: torch.Tensor | None) -> float:
+    """Median milliseconds of ``fn`` over ``iters`` runs."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    samples = []
+    for _ in range(iters):
+        if flush is not None:
+            flush.add_(1)
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        fn()
+        stop.record()
+        torch.cuda.synchronize()
+        samples.append(start.elapsed_time(stop))
+    samples.sort()
+    return samples[len(samples) // 2]
+
+
+def _flush_buffer(enabled: bool) -> torch.Tensor | None:
+    return torch.zeros(_L2_FLUSH_BYTES // 4, device="cuda", dtype=torch.int32) if enabled else None
+
+
+def bench_gemm(args) -> dict:
+    from visionrl_b200.ops import _ext
+
+    ext = _ext.load()
+    m, n, k = args.m, args.n, args.k
+    a = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(n, k, device="cuda", dtype=torch.bfloat16) * 0.02
+    bias = torch.randn(n, device="cuda", dtype=torch.bfloat16) if args.bias else None
+    flush = _flush_buffer(not args.no_flush)
+    act = {"none": 0, "gelu": 1, "silu": 2}[args.act]
+
+    def own():
+        return ext.gemm_bf16(a, w, bias, None, None, act, 1, False, False, False)
+
+    def lib():
+        return torch.nn.functional.linear(a, w, bias)
+
+    out = {"kernel": "gemm_bf16", "m": m, "n": n, "k": k, "act": args.act, "bias": bool(args.bias)}
+    flops = 2.0 * m * n * k
+    if not args.skip_lib:
+        t_lib = _time(lib, args.iters, args.warmup, flush)
+        out["cublas_ms"] = round(t_lib, 4)
+        out["cublas_tflops"] = round(flops / t_lib / 1e9, 1)
+    t_own = _time(own, args.iters, args.warmup, flush)
+    out["ms"] = round(t_own, 4)
+    out["tflops"] = round(flops / t_own / 1e9, 1)
+    if args.peak_tflops:
+        out["frac_of_measured_peak"] = round(out["tflops"] / args.peak_tflops, 3)
+    status = ext.gemm_last_status() if hasattr(ext, "gemm_last_status") else 0
+    out["status"] = int(status)
+    if not args.skip_check:
+        ref = torch.nn.functional.linear(a.float(), w.float(), bias.float() if bias is not None else None)
+        if act == 1:
+            ref = torch.nn.functional.gelu(ref, approximate="tanh")
+        elif act == 2:
+            ref = torch.nn.functional.silu(ref)
+        err = (own().float() - ref).abs().max().item() / max(ref.abs().max().item(), 1e-6)
+        out["max_rel_err"] = round(err, 5)
+    return out
+
+
+def bench_sde(args) -> dict:
+    from visionrl_b200.ops import _ext
+
+    ext = _ext.load()
+    b, n = args.batch, args.elems
+    v = torch.randn(b, n, device="cuda")
+    x = torch.randn(b, n, device="cuda")
+    noise = torch.randn(b, n, device="cuda")
+    a, bb, scale, dt = (torch.rand(b, device="cuda") + 0.1 for _ in range(4))
+    flush = _flush_buffer(not args.no_flush)
+
+    def own():
+        return ext.sde_step_fwd(v, x, a, bb, scale, dt, None, noise, False, True)
+
+    t = _time(own, args.iters, args.warmup, flush)
+    moved = b * n * 4 * 5   # velocity, sample, noise in; next sample, mean out
+    out = {"kernel": "sde_step_fwd", "batch": b, "elems": n, "ms": round(t, 4),
+           "gbs": round(moved / t / 1e6, 1)}
+    if args.peak_gbs:
+        out["frac_of_measured_peak"] = round(out["gbs"] / args.peak_gbs, 3)
+    return out
+
+
+def bench_adaln(args) -> dict:
+    from visionrl_b200.ops.norm import adaln_layernorm
+
+    b, s, d = args.batch, args.seq, args.dim
+    x = torch.randn(b, s, d, device="cuda", dtype=torch.bfloat16)
+    mod = torch.randn(b, 2 * d, device="cuda", dtype=torch.bfloat16)
+    shift, scale = mod[:, :d], mod[:, d:]
+    flush = _flush_buffer(not args.no_flush)
+    t = _time(lambda: adaln_layernorm(x, shift, scale, 1e-6), args.iters, args.warmup, flush)
+    moved = 2 * x.numel() * 2
+    out = {"kernel": "adaln_fwd", "batch": b, "seq": s, "dim": d, "ms": round(t, 4),
+           "gbs": round(moved / t / 1e6, 1)}
+    if args.peak_gbs:
+        out["frac_of_measured_peak"] = round(out["gbs"] / args.peak_gbs, 3)
+    return out
+
+
+def bench_attention(args) -> dict:
+    from visionrl_b200.ops.attention import attention
+
+    b, h, s, d = args.batch, args.heads, args.seq, args.head_dim
+    q, k, v = (torch.randn(b, h, s, d, device="cuda", dtype=torch.bfloat16) for _ in range(3))
+    flush = _flush_buffer(not args.no_flush)
+    flops = 4.0 * b * h * s * s * d
+    out = {"kernel": "attention_fwd", "batch": b, "heads": h, "seq": s, "head_dim": d}
+    with torch.no_grad():
+        t_lib = _time(lambda: torch.nn.functional.scaled_dot_product_attention(q, k, v),
+                      args.iters, args.warmup, flush)
+        t = _time(lambda: attention(q, k, v), args.iters, args.warmup, flush)
+        ref = torch.nn.functional.scaled_dot_product_attention(q.float(), k.float(), v.float())
+        out["max_abs_err"] = round((attention(q, k, v).float() - ref).abs().max().item(), 5)
+    out.update({"sdpa_ms": round(t_lib, 4), "sdpa_tflops": round(flops / t_lib / 1e9, 1),
+                "ms": round(t, 4), "tflops": round(flops / t / 1e9, 1)})
+    if args.peak_tflops:
+        out["frac_of_measured_peak"] = round(out["tflops"] / args.peak_tflops, 3)
+    return out
+
+
+def main(argv=None) -> int:
+    parser = argparse.ArgumentParser(prog="visionrl_b200.ops.microbench")
+    parser.add_argument("--iters", type=int, default=20)
+    parser.add_argument("--warmup", type=int, default=5)
+    parser.add_argument("--no-flush", action="store_true")
+    parser.add_argument("--peak-tflops", type=float, default=0.0)
+    parser.add_argument("--peak-gbs", type=float, default=0.0)
+    sub = parser.add_subparsers(dest="kernel", required=True)
+    g = sub.add_parser("gemm")
+    g.add_argument("--m", type=int, default=9424)
+    g.add_argument("--n", type=int, default=6144)
+    g.add_argument("--k", type=int, default=1536)
+    g.add_argument("--act", default="none", choices=["none", "gelu", "silu"])
+    g.add_argument("--bias", action="store_true")
+    g.add_argument("--skip-lib", action="store_true")
+    g.add_argument("--skip-check", action="store_true")
+    g.set_defaults(fn=bench_gemm)
+    s = sub.add_parser("sde")
+    s.add_argument("--batch", type=int, default=64)
+    s.add_argument("--elems", type=int, default=898560)
+    s.set_defaults(fn=bench_sde)
+    n = sub.add_parser("adaln")
+    n.add_argument("--batch", type=int, default=16)
+    n.add_argument("--seq", type=int, default=1024)
+    n.add_argument("--dim", type=int, default=1536)
+    n.set_defaults(fn=bench_adaln)
+    t = sub.add_parser("attention")
+    t.add_argument("--batch", type=int, default=16)
+    t.add_argument("--heads", type=int, default=24)
+    t.add_argument("--seq", type=int, default=1178)
+    t.add_argument("--head-dim", type=int, default=64)
+    t.set_defaults(fn=bench_attention)
+    args = parser.parse_args(argv)
+    if not torch.cuda.is_available():
+        print(json.dumps({"error": "no CUDA device"}))
+        return 1
+    print(json.dumps(args.fn(args)))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -34,8 +34,7 @@ class _AdaLNFn(torch.autograd.Function):
     def forward(ctx, x, shift, scale, eps):
         from visionrl_b200.ops import _ext
 
-        y, mean, rstd = _ext.load().adaln_fwd(x.contiguous(), shift.contiguous(),
-                                              scale.contiguous(), float(eps))
+        y, mean, rstd = _ext.load().adaln_fwd(x.contiguous(), shift, scale, float(eps))
         ctx.save_for_backward(x, scale, mean, rstd)
         return y
 
@@ -44,8 +43,8 @@ class _AdaLNFn(torch.autograd.Function):
         from visionrl_b200.ops import _ext
 
         x, scale, mean, rstd = ctx.saved_tensors
-        gx, gshift, gscale = _ext.load().adaln_bwd(gy.contiguous(), x.contiguous(),
-                                                   scale.contiguous(), mean, rstd)
+        gx, gshift, gscale = _ext.load().adaln_bwd(gy.contiguous(), x.contiguous(), scale, mean,
+                                                   rstd)
         return gx, gshift.to(scale.dtype), gscale.to(scale.dtype), None
 
 
