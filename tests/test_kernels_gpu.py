@@ -331,3 +331,168 @@ def test_adaln_accepts_strided_modulation_views():
     ref.backward(g.float())
     assert torch.allclose(x.grad.float(), xf.grad, atol=5e-2, rtol=5e-2)
     assert torch.allclose(mod.grad.float(), mf.grad, atol=0.15, rtol=5e-2)
+
+
+# ----------------------------------------------------------------------------- AR-path kernels
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_token_logprob_fwd_bwd(dtype):
+    from visionrl_b200.ops.logprob import token_log_probs, token_log_probs_reference
+
+    torch.manual_seed(0)
+    logits = (torch.randn(37, 16384, device="cuda") * 3).to(dtype).requires_grad_()
+    ids = torch.randint(0, 16384, (37,), device="cuda")
+    lp = token_log_probs(logits, ids, 0.7)
+    ref_in = logits.detach().float().requires_grad_()
+    ref = token_log_probs_reference(ref_in, ids, 0.7)
+    assert torch.allclose(lp, ref, atol=2e-4, rtol=1e-4)
+    g = torch.randn_like(lp)
+    lp.backward(g)
+    ref.backward(g)
+    tol = 2e-2 if dtype == torch.bfloat16 else 1e-5
+    assert torch.allclose(logits.grad.float(), ref_in.grad, atol=tol, rtol=tol)
+
+
+@pytest.mark.gpu
+def test_fused_head_log_probs_matches_reference():
+    from visionrl_b200.ops.logprob import fused_head_log_probs, fused_head_log_probs_reference
+
+    torch.manual_seed(1)
+    rows, hid, vocab = 300, 256, 4096 + 1024
+    h = (torch.randn(rows, hid, device="cuda") * 0.5).bfloat16().requires_grad_()
+    w = (torch.randn(vocab, hid, device="cuda") * 0.05).bfloat16().requires_grad_()
+    b = (torch.randn(vocab, device="cuda") * 0.1).bfloat16().requires_grad_()
+    ids = torch.randint(0, vocab, (rows,), device="cuda")
+    lp = fused_head_log_probs(h, w, b, ids, 1.0, chunk=2048)
+    hf, wf, bf = (t.detach().float().requires_grad_() for t in (h, w, b))
+    ref = fused_head_log_probs_reference(hf, wf, bf, ids, 1.0)
+    assert torch.allclose(lp, ref, atol=5e-3, rtol=1e-3)
+    g = torch.randn_like(lp)
+    lp.backward(g)
+    ref.backward(g)
+    assert torch.allclose(h.grad.float(), hf.grad, atol=2e-2, rtol=5e-2)
+    assert torch.allclose(w.grad.float(), wf.grad, atol=2e-2, rtol=5e-2)
+    assert torch.allclose(b.grad.float(), bf.grad, atol=2e-2, rtol=5e-2)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_sample_tokens_inverse_cdf(dtype):
+    from visionrl_b200.ops.sampling import sample_cfg_tokens
+
+    torch.manual_seed(2)
+    rows, vocab, w, t = 32, 16384, 5.0, 0.9
+    cond = (torch.randn(rows, vocab, device="cuda") * 2).to(dtype)
+    uncond = (torch.randn(rows, vocab, device="cuda") * 2).to(dtype)
+    u = torch.rand(rows, device="cuda")
+    tokens, logp = sample_cfg_tokens(cond, uncond, u, w, t)
+    tokens2, logp2 = sample_cfg_tokens(cond, uncond, u, w, t)
+    assert torch.equal(tokens, tokens2) and torch.equal(logp, logp2)
+    guided = uncond.double() + w * (cond.double() - uncond.double())
+    cdf = torch.softmax(guided / t, dim=-1).cumsum(-1)
+    hi = cdf.gather(-1, tokens[:, None])[:, 0]
+    lo = torch.where(tokens > 0, cdf.gather(-1, (tokens - 1).clamp_min(0)[:, None])[:, 0],
+                     torch.zeros_like(hi))
+    target = u.double()
+    assert bool(((target >= lo - 1e-4) & (target <= hi + 1e-4)).all())
+    ref_lp = torch.log_softmax(cond.float() / t, dim=-1).gather(-1, tokens[:, None])[:, 0]
+    assert torch.allclose(logp, ref_lp, atol=2e-4, rtol=1e-4)
+
+
+@pytest.mark.gpu
+def test_decode_attention_matches_reference():
+    from visionrl_b200.ops.attention import decode_attention, decode_attention_reference
+
+    torch.manual_seed(3)
+    rows, heads, max_len, d, length = 6, 16, 96, 128, 77
+    cache = torch.randn(2, rows, heads, max_len, d, device="cuda").bfloat16()
+    q = torch.randn(rows, heads, 1, d, device="cuda").bfloat16()
+    valid = torch.rand(rows, max_len, device="cuda") > 0.2
+    valid[:, 0] = True
+    got = decode_attention(q, cache[0], cache[1], valid, length)
+    ref = decode_attention_reference(q.float(), cache[0].float(), cache[1].float(), valid, length)
+    assert torch.allclose(got.float(), ref, atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("global_std", [False, True])
+def test_group_advantages_kernel(global_std):
+    from visionrl_b200.algorithms.grpo import (group_normalized_advantages,
+                                                group_normalized_advantages_reference)
+
+    torch.manual_seed(4)
+    rewards = torch.randn(67, device="cuda")
+    gids = torch.randint(0, 9, (67,), device="cuda") * 7 + 3
+    gids[-1] = 1000          # singleton group
+    got = group_normalized_advantages(rewards, gids, 1e-8, 5.0, global_std)
+    ref = group_normalized_advantages_reference(rewards.cpu(), gids.cpu(), 1e-8, 5.0, global_std)
+    assert torch.allclose(got.cpu(), ref, atol=1e-5, rtol=1e-5)
+    assert got[-1].item() == 0.0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("m", [1, 16, 32])
+def test_int4_gemv_matches_dequantised_matmul(m):
+    from visionrl_b200.ops.quant import int4_linear, int4_linear_reference, quantize_int4
+
+    torch.manual_seed(5)
+    n, k = 2048 + 24, 2048
+    w = torch.randn(n, k, device="cuda") * 0.05
+    packed, scales = quantize_int4(w)
+    x = torch.randn(m, k, device="cuda").bfloat16()
+    bias = torch.randn(n, device="cuda").bfloat16()
+    got = int4_linear(x, packed, scales, bias)
+    ref = int4_linear_reference(x.float(), packed, scales, bias)
+    assert torch.allclose(got.float(), ref, atol=3e-2, rtol=2e-2)
+
+
+@pytest.mark.gpu
+def test_moe_routing_kernels_and_block():
+    from visionrl_b200.ops import moe
+
+    torch.manual_seed(6)
+    tokens, experts, k, dim = 1000, 8, 2, 256
+    logits = torch.randn(tokens, experts, device="cuda")
+    w, idx = moe.route(logits, k)
+    rw, ridx = moe.route_reference(logits, k)
+    assert torch.equal(idx, ridx) and torch.allclose(w, rw, atol=1e-5)
+    perm, inv, offsets = moe.permute(idx, experts)
+    rperm, rinv, roff = moe.permute_reference(idx, experts)
+    assert torch.equal(perm, rperm) and torch.equal(inv, rinv) and torch.equal(offsets, roff)
+    block = moe.MoEFFN(dim, 512, experts, k).cuda().bfloat16()
+    x = torch.randn(4, 250, dim, device="cuda").bfloat16()
+    with torch.no_grad():
+        got = block(x)
+        ref = moe.moe_ffn_reference(block, x)
+    assert torch.allclose(got.float(), ref.float(), atol=6e-2, rtol=6e-2)
+    xg = x.clone().requires_grad_()
+    block(xg).float().pow(2).mean().backward()
+    assert xg.grad is not None and torch.isfinite(xg.grad.float()).all()
+    assert block.w1.grad is not None and block.gate.weight.grad is not None
+
+
+@pytest.mark.gpu
+def test_gemm_tma_store_epilogue_tails_with_gate_residual():
+    from visionrl_b200.ops import _ext
+
+    torch.manual_seed(7)
+    ext = _ext.load()
+    batch, seq, k, n = 3, 77, 192, 200          # M = 231 (not a multiple of 32), N % 64 != 0
+    m = batch * seq
+    a = torch.randn(m, k, device="cuda").bfloat16()
+    w = (torch.randn(n, k, device="cuda") * 0.1).bfloat16()
+    bias = torch.randn(n, device="cuda").bfloat16()
+    mod = torch.randn(batch, 3 * n, device="cuda").bfloat16()
+    gate = mod[:, n:2 * n]                       # strided view
+    res = torch.randn(m, n, device="cuda").bfloat16()
+    poison = torch.full((m, n), float("nan"), device="cuda", dtype=torch.bfloat16)
+    del poison
+    got = ext.gemm_bf16(a, w, bias, gate, res, 0, seq, False, False, False)
+    lin = a.float() @ w.float().t() + bias.float()
+    ref = res.float() + gate.float().repeat_interleave(seq, 0) * lin
+    assert ext.gemm_last_status() == 0
+    assert torch.isfinite(got.float()).all()
+    assert torch.allclose(got.float(), ref, atol=6e-2, rtol=3e-2)
+    got2 = ext.gemm_bf16(a, w, bias, None, res, 1, 1, False, False, False)
+    ref2 = torch.nn.functional.gelu(lin, approximate="tanh") + res.float()
+    assert torch.allclose(got2.float(), ref2, atol=6e-2, rtol=3e-2)

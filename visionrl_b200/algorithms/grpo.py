@@ -35,6 +35,21 @@ def group_normalized_advantages(rewards, group_ids, eps: float, adv_clip_max: fl
     """Vectorised group mean/std normalisation (kernel K13's oracle)."""
     import torch
 
+    if rewards.is_cuda and rewards.dim() == 1 and 0 < rewards.numel() <= 16384:
+        from visionrl_b200.ops import _ext
+
+        if _ext.kernels_enabled() and _ext.has("group_advantages"):
+            adv = _ext.load().group_advantages(rewards.detach(), group_ids, float(eps),
+                                               float(adv_clip_max), bool(global_std))
+            return adv.to(rewards.dtype)
+    return group_normalized_advantages_reference(rewards, group_ids, eps, adv_clip_max, global_std)
+
+
+def group_normalized_advantages_reference(rewards, group_ids, eps: float, adv_clip_max: float,
+                                          global_std: bool = False):
+    """Segment-sum restatement in PyTorch (CPU path and oracle of the kernel)."""
+    import torch
+
     rewards_f = rewards.float()
     _, inverse = torch.unique(group_ids, return_inverse=True)
     n_groups = int(inverse.max().item()) + 1 if inverse.numel() else 0

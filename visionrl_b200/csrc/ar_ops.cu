@@ -1,0 +1,476 @@
+// Autoregressive-path kernels: token log-probabilities over a large vocabulary (whole-row and
+// vocabulary-chunked online forms), guided categorical sampling, single-position attention
+// against a static KV cache, and group-normalised advantages.
+//
+// Reduction orders are fixed by the launch shape (no atomics on results), so two calls with the
+// same inputs return bit-identical values: the rollout's recorded log-probability and the
+// trainer's replayed one must agree exactly for the first policy-ratio to be 1.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+
+#include "common.cuh"
+#include "ops.h"
+
+namespace vrl {
+
+namespace {
+
+constexpr int kRowThreads = 256;
+
+template <typename T>
+__device__ __forceinline__ void load8(const T* p, float* f);
+template <>
+__device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float* f) {
+  unpack8(*reinterpret_cast<const bf16x8*>(p), f);
+}
+template <>
+__device__ __forceinline__ void load8<float>(const float* p, float* f) {
+  const float4 a = *reinterpret_cast<const float4*>(p);
+  const float4 b = *reinterpret_cast<const float4*>(p + 4);
+  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w;
+  f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+
+// (max, sum of exp(x - max)) pairs combine associatively.
+__device__ __forceinline__ void lse_merge(float& m, float& s, float m2, float s2) {
+  const float mn = fmaxf(m, m2);
+  const float a = (m == -INFINITY) ? 0.f : s * __expf(m - mn);
+  const float b = (m2 == -INFINITY) ? 0.f : s2 * __expf(m2 - mn);
+  m = mn;
+  s = a + b;
+}
+
+__device__ __forceinline__ void block_lse(float& m, float& s, float* sm, float* ss) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float m2 = __shfl_xor_sync(0xffffffffu, m, o), s2 = __shfl_xor_sync(0xffffffffu, s, o);
+    lse_merge(m, s, m2, s2);
+  }
+  __syncthreads();
+  if (lane == 0) { sm[warp] = m; ss[warp] = s; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float mm = sm[0], sv = ss[0];
+    for (int w = 1; w < (int)(blockDim.x >> 5); ++w) lse_merge(mm, sv, sm[w], ss[w]);
+    sm[0] = mm; ss[0] = sv;
+  }
+  __syncthreads();
+  m = sm[0]; s = ss[0];
+  __syncthreads();
+}
+
+// ------------------------------------------------------------------------------------------
+// log_softmax(logits / T)[id] for every row.  One block per row, one pass over the row.
+// ------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(kRowThreads)
+token_logprob_fwd_kernel(const T* __restrict__ logits, const int64_t* __restrict__ ids,
+                         float* __restrict__ lp, float* __restrict__ lse, int vocab, float inv_t) {
+  __shared__ float sm[32], ss[32];
+  const int64_t row = blockIdx.x;
+  const T* x = logits + row * vocab;
+  float m = -INFINITY, s = 0.f;
+  const int vec_end = (vocab / 8) * 8;
+  for (int i = threadIdx.x * 8; i < vec_end; i += kRowThreads * 8) {
+    float f[8];
+    load8<T>(x + i, f);
+    float cm = f[0];
+#pragma unroll
+    for (int j = 1; j < 8; ++j) cm = fmaxf(cm, f[j]);
+    cm *= inv_t;
+    float cs = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) cs += __expf(f[j] * inv_t - cm);
+    lse_merge(m, s, cm, cs);
+  }
+  for (int i = vec_end + threadIdx.x; i < vocab; i += kRowThreads) lse_merge(m, s, to_f<T>(x[i]) * inv_t, 1.f);
+  block_lse(m, s, sm, ss);
+  if (threadIdx.x == 0) {
+    const float l = m + __logf(s);
+    lse[row] = l;
+    int64_t id = ids[row];
+    id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+    lp[row] = to_f<T>(x[id]) * inv_t - l;
+  }
+}
+
+// grad_logits = g / T * (onehot(id) - softmax(logits / T))
+template <typename T>
+__global__ void __launch_bounds__(kRowThreads)
+token_logprob_bwd_kernel(const T* __restrict__ logits, const int64_t* __restrict__ ids,
+                         const float* __restrict__ lse, const float* __restrict__ g,
+                         T* __restrict__ grad, int vocab, float inv_t) {
+  const int64_t row = blockIdx.x;
+  const T* x = logits + row * vocab;
+  T* o = grad + row * vocab;
+  const float l = lse[row], gs = g[row] * inv_t;
+  const int id = (int)ids[row];
+  for (int i = threadIdx.x; i < vocab; i += kRowThreads) {
+    const float p = __expf(to_f<T>(x[i]) * inv_t - l);
+    o[i] = from_f<T>(gs * ((i == id ? 1.f : 0.f) - p));
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// Vocabulary-chunked form.  `chunk` is the fp32 head output for columns [col0, col0 + width);
+// the running (max, sum) and the target logit are updated in place, so the full [rows, vocab]
+// logits never exist at once.
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kRowThreads)
+lse_chunk_update_kernel(const float* __restrict__ chunk, const int64_t* __restrict__ ids,
+                        float* __restrict__ run_max, float* __restrict__ run_sum,
+                        float* __restrict__ target, int width, int col0, float inv_t) {
+  __shared__ float sm[32], ss[32];
+  const int64_t row = blockIdx.x;
+  const float* x = chunk + row * width;
+  float m = -INFINITY, s = 0.f;
+  for (int i = threadIdx.x; i < width; i += kRowThreads) lse_merge(m, s, x[i] * inv_t, 1.f);
+  block_lse(m, s, sm, ss);
+  if (threadIdx.x == 0) {
+    float rm = run_max[row], rs = run_sum[row];
+    lse_merge(rm, rs, m, s);
+    run_max[row] = rm;
+    run_sum[row] = rs;
+    const int64_t id = ids[row] - col0;
+    if (id >= 0 && id < width) target[row] = x[id] * inv_t;
+  }
+}
+
+// dlogits chunk (bf16) = g / T * (onehot - softmax) for columns [col0, col0 + width)
+__global__ void __launch_bounds__(kRowThreads)
+softmax_grad_chunk_kernel(const float* __restrict__ chunk, const int64_t* __restrict__ ids,
+                          const float* __restrict__ lse, const float* __restrict__ g,
+                          __nv_bfloat16* __restrict__ out, int width, int col0, float inv_t) {
+  const int64_t row = blockIdx.x;
+  const float* x = chunk + row * width;
+  __nv_bfloat16* o = out + row * width;
+  const float l = lse[row], gs = g[row] * inv_t;
+  const int id = (int)(ids[row] - col0);
+  for (int i = threadIdx.x; i < width; i += kRowThreads) {
+    const float p = __expf(x[i] * inv_t - l);
+    o[i] = __float2bfloat16_rn(gs * ((i == id ? 1.f : 0.f) - p));
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// Guided sampling.  One block per row.  The token is the first index whose inclusive cumulative
+// probability under softmax((u + w (c - u)) / T) exceeds `uniform * total`; the recorded
+// log-probability is log_softmax(c / T)[token].  Threads own contiguous index ranges so the
+// cumulative sum is taken in index order.
+// ------------------------------------------------------------------------------------------
+constexpr int kSampleThreads = 512;
+
+template <typename T>
+__global__ void __launch_bounds__(kSampleThreads)
+sample_tokens_kernel(const T* __restrict__ cond, const T* __restrict__ uncond,
+                     const float* __restrict__ uniform, int64_t* __restrict__ tokens,
+                     float* __restrict__ logp, int vocab, float w, float inv_t) {
+  __shared__ float sm[32], ss[32];
+  __shared__ float part[kSampleThreads];
+  const int64_t row = blockIdx.x;
+  const T* c = cond + row * vocab;
+  const T* u = uncond + row * vocab;
+  const int per = (vocab + kSampleThreads - 1) / kSampleThreads;
+  const int lo = min(vocab, (int)threadIdx.x * per), hi = min(vocab, lo + per);
+
+  // pass 1: maxima and sums of both distributions
+  float gm = -INFINITY, gsum = 0.f, cm = -INFINITY, csum = 0.f;
+  for (int i = lo; i < hi; ++i) {
+    const float cv = to_f<T>(c[i]), uv = to_f<T>(u[i]);
+    lse_merge(gm, gsum, (uv + w * (cv - uv)) * inv_t, 1.f);
+    lse_merge(cm, csum, cv * inv_t, 1.f);
+  }
+  float gmax = gm, gtot = gsum;
+  block_lse(gmax, gtot, sm, ss);
+  float cmax = cm, ctot = csum;
+  block_lse(cmax, ctot, sm, ss);
+
+  // pass 2: per-thread mass relative to the row maximum, then the owning thread scans its range
+  float mass = 0.f;
+  for (int i = lo; i < hi; ++i) {
+    const float cv = to_f<T>(c[i]), uv = to_f<T>(u[i]);
+    mass += __expf((uv + w * (cv - uv)) * inv_t - gmax);
+  }
+  part[threadIdx.x] = mass;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float total = 0.f;
+    for (int t = 0; t < kSampleThreads; ++t) total += part[t];
+    const float uu = fminf(fmaxf(uniform[row], 0.f), 1.f - 1e-7f);
+    const float tgt = uu * total;
+    float acc = 0.f;
+    int owner = kSampleThreads - 1;
+    for (int t = 0; t < kSampleThreads; ++t) {
+      if (acc + part[t] > tgt) { owner = t; break; }
+      acc += part[t];
+    }
+    // sequential scan inside the owner's range
+    const int olo = min(vocab, owner * per), ohi = min(vocab, olo + per);
+    int tok = max(0, min(vocab, ohi) - 1);      // rounding may leave the target just out of reach
+    for (int i = olo; i < ohi; ++i) {
+      const float cv = to_f<T>(c[i]), uv = to_f<T>(u[i]);
+      acc += __expf((uv + w * (cv - uv)) * inv_t - gmax);
+      if (acc > tgt) { tok = i; break; }
+    }
+    tokens[row] = tok;
+    logp[row] = to_f<T>(c[tok]) * inv_t - (cmax + __logf(ctot));
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// Decode attention: one query position per (row, head) against a static cache.
+// q [R, H, D], caches [R, H, L, D] (strided), valid [R, L]; D = 128.  One block of 4 warps per
+// (row, head); every warp walks keys w, w+4, ... with an online softmax, lanes own 4 dims.
+// ------------------------------------------------------------------------------------------
+constexpr int kDecodeWarps = 4;
+
+__global__ void __launch_bounds__(kDecodeWarps * 32)
+decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kc,
+                        const __nv_bfloat16* __restrict__ vc, const bool* __restrict__ valid,
+                        __nv_bfloat16* __restrict__ out, int heads, int length, int64_t k_sr,
+                        int64_t k_sh, int64_t k_sl, int64_t v_sr, int64_t v_sh, int64_t v_sl,
+                        int64_t valid_sr, float scale) {
+  __shared__ float sm_m[kDecodeWarps], sm_s[kDecodeWarps];
+  __shared__ float sm_o[kDecodeWarps][128];
+  const int r = blockIdx.x / heads, h = blockIdx.x % heads;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const __nv_bfloat16* qp = q + ((int64_t)r * heads + h) * 128 + lane * 4;
+  const uint2 qraw = *reinterpret_cast<const uint2*>(qp);
+  const float2 q01 = bf16pair_to_float2(qraw.x), q23 = bf16pair_to_float2(qraw.y);
+  const __nv_bfloat16* kbase = kc + r * k_sr + h * k_sh + lane * 4;
+  const __nv_bfloat16* vbase = vc + r * v_sr + h * v_sh + lane * 4;
+  const bool* vrow = valid + r * valid_sr;
+  float m = -INFINITY, s = 0.f, o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+  for (int j = warp; j < length; j += kDecodeWarps) {
+    if (!vrow[j]) continue;                                   // warp-uniform
+    const uint2 kraw = *reinterpret_cast<const uint2*>(kbase + j * k_sl);
+    const float2 k01 = bf16pair_to_float2(kraw.x), k23 = bf16pair_to_float2(kraw.y);
+    float dot = q01.x * k01.x + q01.y * k01.y + q23.x * k23.x + q23.y * k23.y;
+    dot = warp_sum(dot) * scale;
+    const float mn = fmaxf(m, dot);
+    const float corr = (m == -INFINITY) ? 0.f : __expf(m - mn);
+    const float p = __expf(dot - mn);
+    const uint2 vraw = *reinterpret_cast<const uint2*>(vbase + j * v_sl);
+    const float2 v01 = bf16pair_to_float2(vraw.x), v23 = bf16pair_to_float2(vraw.y);
+    o0 = o0 * corr + p * v01.x; o1 = o1 * corr + p * v01.y;
+    o2 = o2 * corr + p * v23.x; o3 = o3 * corr + p * v23.y;
+    s = s * corr + p;
+    m = mn;
+  }
+  if (lane == 0) { sm_m[warp] = m; sm_s[warp] = s; }
+  __syncthreads();
+  float gm = -INFINITY;
+#pragma unroll
+  for (int w2 = 0; w2 < kDecodeWarps; ++w2) gm = fmaxf(gm, sm_m[w2]);
+  const float mine = (m == -INFINITY) ? 0.f : __expf(m - gm);
+  sm_o[warp][lane * 4 + 0] = o0 * mine; sm_o[warp][lane * 4 + 1] = o1 * mine;
+  sm_o[warp][lane * 4 + 2] = o2 * mine; sm_o[warp][lane * 4 + 3] = o3 * mine;
+  __syncthreads();
+  if (threadIdx.x < 128) {
+    float tot = 0.f, acc = 0.f;
+#pragma unroll
+    for (int w2 = 0; w2 < kDecodeWarps; ++w2) {
+      tot += (sm_m[w2] == -INFINITY) ? 0.f : sm_s[w2] * __expf(sm_m[w2] - gm);
+      acc += sm_o[w2][threadIdx.x];
+    }
+    out[((int64_t)r * heads + h) * 128 + threadIdx.x] = __float2bfloat16_rn(tot > 0.f ? acc / tot : 0.f);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// Group-normalised advantages: a = clamp((r - mean_g) / max(std_g, eps), +-clip), unbiased std,
+// singleton groups -> 0.  One block; every thread owns samples i, i + blockDim, ...
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+group_advantages_kernel(const float* __restrict__ rewards, const int64_t* __restrict__ gids,
+                        float* __restrict__ adv, int n, float eps, float clip, int global_std) {
+  __shared__ float scratch[32];
+  float gstd = 0.f;
+  if (global_std) {
+    float s = 0.f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) s += rewards[i];
+    const float mean = block_sum(s, scratch) / (float)max(n, 1);
+    float q = 0.f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) { const float d = rewards[i] - mean; q += d * d; }
+    gstd = n > 1 ? sqrtf(block_sum(q, scratch) / (float)(n - 1)) : 0.f;
+  }
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int64_t g = gids[i];
+    float sum = 0.f;
+    int cnt = 0;
+    for (int j = 0; j < n; ++j)
+      if (gids[j] == g) { sum += rewards[j]; ++cnt; }
+    const float mean = sum / (float)cnt;
+    float sq = 0.f;
+    for (int j = 0; j < n; ++j)
+      if (gids[j] == g) { const float d = rewards[j] - mean; sq += d * d; }
+    const float std = global_std ? gstd : sqrtf(sq / (float)max(cnt - 1, 1));
+    float a = (rewards[i] - mean) / fmaxf(std, eps);
+    a = fminf(fmaxf(a, -clip), clip);
+    adv[i] = cnt > 1 ? a : 0.f;
+  }
+}
+
+}  // namespace
+
+// ============================================================================== host wrappers
+std::vector<torch::Tensor> token_logprob_fwd(torch::Tensor logits, torch::Tensor ids, double temperature) {
+  TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.is_contiguous());
+  TORCH_CHECK(ids.is_cuda() && ids.scalar_type() == torch::kInt64 && ids.numel() == logits.size(0));
+  const c10::cuda::CUDAGuard guard(logits.device());
+  const int64_t rows = logits.size(0);
+  const int vocab = (int)logits.size(1);
+  auto opts = logits.options().dtype(torch::kFloat32);
+  auto lp = torch::empty({rows}, opts), lse = torch::empty({rows}, opts);
+  if (rows == 0) return {lp, lse};
+  auto stream = at::cuda::getCurrentCUDAStream();
+  const float inv_t = (float)(1.0 / temperature);
+  ids = ids.contiguous();
+  if (logits.scalar_type() == torch::kBFloat16) {
+    TORCH_CHECK(vocab % 8 == 0, "token_logprob_fwd: bf16 vocabulary must be a multiple of 8");
+    token_logprob_fwd_kernel<__nv_bfloat16><<<rows, kRowThreads, 0, stream>>>(
+        reinterpret_cast<const __nv_bfloat16*>(logits.data_ptr()), ids.data_ptr<int64_t>(),
+        lp.data_ptr<float>(), lse.data_ptr<float>(), vocab, inv_t);
+  } else {
+    TORCH_CHECK(logits.scalar_type() == torch::kFloat32 && vocab % 4 == 0);
+    token_logprob_fwd_kernel<float><<<rows, kRowThreads, 0, stream>>>(
+        logits.data_ptr<float>(), ids.data_ptr<int64_t>(), lp.data_ptr<float>(),
+        lse.data_ptr<float>(), vocab, inv_t);
+  }
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return {lp, lse};
+}
+
+torch::Tensor token_logprob_bwd(torch::Tensor logits, torch::Tensor ids, torch::Tensor lse,
+                                torch::Tensor g, double temperature) {
+  TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.is_contiguous());
+  const c10::cuda::CUDAGuard guard(logits.device());
+  const int64_t rows = logits.size(0);
+  const int vocab = (int)logits.size(1);
+  auto grad = torch::empty_like(logits);
+  if (rows == 0) return grad;
+  auto stream = at::cuda::getCurrentCUDAStream();
+  const float inv_t = (float)(1.0 / temperature);
+  ids = ids.contiguous();
+  lse = lse.contiguous();
+  g = g.to(torch::kFloat32).contiguous();
+  if (logits.scalar_type() == torch::kBFloat16) {
+    token_logprob_bwd_kernel<__nv_bfloat16><<<rows, kRowThreads, 0, stream>>>(
+        reinterpret_cast<const __nv_bfloat16*>(logits.data_ptr()), ids.data_ptr<int64_t>(),
+        lse.data_ptr<float>(), g.data_ptr<float>(),
+        reinterpret_cast<__nv_bfloat16*>(grad.data_ptr()), vocab, inv_t);
+  } else {
+    TORCH_CHECK(logits.scalar_type() == torch::kFloat32);
+    token_logprob_bwd_kernel<float><<<rows, kRowThreads, 0, stream>>>(
+        logits.data_ptr<float>(), ids.data_ptr<int64_t>(), lse.data_ptr<float>(),
+        g.data_ptr<float>(), grad.data_ptr<float>(), vocab, inv_t);
+  }
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return grad;
+}
+
+void lse_chunk_update(torch::Tensor chunk, torch::Tensor ids, torch::Tensor run_max,
+                      torch::Tensor run_sum, torch::Tensor target, int64_t col0, double temperature) {
+  TORCH_CHECK(chunk.is_cuda() && chunk.dim() == 2 && chunk.is_contiguous() &&
+              chunk.scalar_type() == torch::kFloat32);
+  TORCH_CHECK(run_max.scalar_type() == torch::kFloat32 && run_sum.scalar_type() == torch::kFloat32 &&
+              target.scalar_type() == torch::kFloat32 && ids.scalar_type() == torch::kInt64);
+  const c10::cuda::CUDAGuard guard(chunk.device());
+  const int64_t rows = chunk.size(0);
+  if (rows == 0) return;
+  lse_chunk_update_kernel<<<rows, kRowThreads, 0, at::cuda::getCurrentCUDAStream()>>>(
+      chunk.data_ptr<float>(), ids.data_ptr<int64_t>(), run_max.data_ptr<float>(),
+      run_sum.data_ptr<float>(), target.data_ptr<float>(), (int)chunk.size(1), (int)col0,
+      (float)(1.0 / temperature));
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
+torch::Tensor softmax_grad_chunk(torch::Tensor chunk, torch::Tensor ids, torch::Tensor lse,
+                                 torch::Tensor g, int64_t col0, double temperature) {
+  TORCH_CHECK(chunk.is_cuda() && chunk.dim() == 2 && chunk.is_contiguous() &&
+              chunk.scalar_type() == torch::kFloat32);
+  const c10::cuda::CUDAGuard guard(chunk.device());
+  auto out = torch::empty(chunk.sizes(), chunk.options().dtype(torch::kBFloat16));
+  const int64_t rows = chunk.size(0);
+  if (rows == 0) return out;
+  softmax_grad_chunk_kernel<<<rows, kRowThreads, 0, at::cuda::getCurrentCUDAStream()>>>(
+      chunk.data_ptr<float>(), ids.data_ptr<int64_t>(), lse.data_ptr<float>(), g.data_ptr<float>(),
+      reinterpret_cast<__nv_bfloat16*>(out.data_ptr()), (int)chunk.size(1), (int)col0,
+      (float)(1.0 / temperature));
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return out;
+}
+
+std::vector<torch::Tensor> sample_tokens(torch::Tensor cond, torch::Tensor uncond, torch::Tensor u,
+                                         double cfg_weight, double temperature) {
+  TORCH_CHECK(cond.is_cuda() && cond.dim() == 2 && cond.is_contiguous() && uncond.is_contiguous());
+  TORCH_CHECK(cond.sizes() == uncond.sizes() && cond.scalar_type() == uncond.scalar_type());
+  TORCH_CHECK(u.scalar_type() == torch::kFloat32 && u.numel() == cond.size(0) && u.is_contiguous());
+  const c10::cuda::CUDAGuard guard(cond.device());
+  const int64_t rows = cond.size(0);
+  auto tokens = torch::empty({rows}, cond.options().dtype(torch::kInt64));
+  auto logp = torch::empty({rows}, cond.options().dtype(torch::kFloat32));
+  if (rows == 0) return {tokens, logp};
+  auto stream = at::cuda::getCurrentCUDAStream();
+  const float inv_t = (float)(1.0 / temperature);
+  if (cond.scalar_type() == torch::kBFloat16) {
+    sample_tokens_kernel<__nv_bfloat16><<<rows, kSampleThreads, 0, stream>>>(
+        reinterpret_cast<const __nv_bfloat16*>(cond.data_ptr()),
+        reinterpret_cast<const __nv_bfloat16*>(uncond.data_ptr()), u.data_ptr<float>(),
+        tokens.data_ptr<int64_t>(), logp.data_ptr<float>(), (int)cond.size(1), (float)cfg_weight, inv_t);
+  } else {
+    TORCH_CHECK(cond.scalar_type() == torch::kFloat32);
+    sample_tokens_kernel<float><<<rows, kSampleThreads, 0, stream>>>(
+        cond.data_ptr<float>(), uncond.data_ptr<float>(), u.data_ptr<float>(),
+        tokens.data_ptr<int64_t>(), logp.data_ptr<float>(), (int)cond.size(1), (float)cfg_weight, inv_t);
+  }
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return {tokens, logp};
+}
+
+torch::Tensor decode_attention(torch::Tensor q, torch::Tensor k_cache, torch::Tensor v_cache,
+                               torch::Tensor valid, int64_t length, double scale) {
+  TORCH_CHECK(q.is_cuda() && q.scalar_type() == torch::kBFloat16 && q.dim() == 4 && q.size(2) == 1 &&
+              q.size(3) == 128 && q.is_contiguous(), "decode_attention: q must be [R, H, 1, 128] bf16");
+  TORCH_CHECK(k_cache.dim() == 4 && v_cache.dim() == 4 && k_cache.stride(3) == 1 && v_cache.stride(3) == 1 &&
+              k_cache.scalar_type() == torch::kBFloat16 && v_cache.scalar_type() == torch::kBFloat16);
+  TORCH_CHECK(valid.scalar_type() == torch::kBool && valid.dim() == 2 && valid.stride(1) == 1);
+  TORCH_CHECK(length <= k_cache.size(2) && length <= valid.size(1));
+  TORCH_CHECK(k_cache.stride(0) % 4 == 0 && k_cache.stride(1) % 4 == 0 && k_cache.stride(2) % 4 == 0 &&
+              v_cache.stride(0) % 4 == 0 && v_cache.stride(1) % 4 == 0 && v_cache.stride(2) % 4 == 0 &&
+              reinterpret_cast<uintptr_t>(k_cache.data_ptr()) % 8 == 0 &&
+              reinterpret_cast<uintptr_t>(v_cache.data_ptr()) % 8 == 0, "decode_attention: cache alignment");
+  const c10::cuda::CUDAGuard guard(q.device());
+  const int64_t rows = q.size(0), heads = q.size(1);
+  auto out = torch::empty_like(q);
+  if (rows == 0) return out;
+  decode_attention_kernel<<<rows * heads, kDecodeWarps * 32, 0, at::cuda::getCurrentCUDAStream()>>>(
+      reinterpret_cast<const __nv_bfloat16*>(q.data_ptr()),
+      reinterpret_cast<const __nv_bfloat16*>(k_cache.data_ptr()),
+      reinterpret_cast<const __nv_bfloat16*>(v_cache.data_ptr()), valid.data_ptr<bool>(),
+      reinterpret_cast<__nv_bfloat16*>(out.data_ptr()), (int)heads, (int)length, k_cache.stride(0),
+      k_cache.stride(1), k_cache.stride(2), v_cache.stride(0), v_cache.stride(1), v_cache.stride(2),
+      valid.stride(0), (float)scale);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return out;
+}
+
+torch::Tensor group_advantages(torch::Tensor rewards, torch::Tensor group_ids, double eps, double clip,
+                               bool global_std) {
+  TORCH_CHECK(rewards.is_cuda() && rewards.dim() == 1 && group_ids.numel() == rewards.numel());
+  const c10::cuda::CUDAGuard guard(rewards.device());
+  auto r = rewards.to(torch::kFloat32).contiguous();
+  auto g = group_ids.to(torch::kInt64).contiguous();
+  auto adv = torch::empty_like(r);
+  const int n = (int)r.numel();
+  if (n == 0) return adv;
+  TORCH_CHECK(n <= 16384, "group_advantages: batch larger than the single-block kernel supports");
+  group_advantages_kernel<<<1, 256, 0, at::cuda::getCurrentCUDAStream()>>>(
+      r.data_ptr<float>(), g.data_ptr<int64_t>(), adv.data_ptr<float>(), n, (float)eps, (float)clip,
+      global_std ? 1 : 0);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return adv;
+}
+
+}  // namespace vrl

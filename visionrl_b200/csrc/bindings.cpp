@@ -47,6 +47,18 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("p2p_broadcast_versioned", &vrl::p2p_broadcast_versioned);
   m.def("wait_flag", &vrl::wait_flag);
   m.def("ulysses_scatter", &vrl::ulysses_scatter);
+  m.def("token_logprob_fwd", &vrl::token_logprob_fwd);
+  m.def("token_logprob_bwd", &vrl::token_logprob_bwd);
+  m.def("lse_chunk_update", &vrl::lse_chunk_update);
+  m.def("softmax_grad_chunk", &vrl::softmax_grad_chunk);
+  m.def("sample_tokens", &vrl::sample_tokens);
+  m.def("decode_attention", &vrl::decode_attention);
+  m.def("group_advantages", &vrl::group_advantages);
+  m.def("int4_gemv", &vrl::int4_gemv);
+  m.def("moe_gate_topk", &vrl::moe_gate_topk);
+  m.def("moe_permute", &vrl::moe_permute);
+  m.def("moe_gather_rows", &vrl::moe_gather_rows);
+  m.def("moe_combine", &vrl::moe_combine);
   m.def("gemm_bf16", &vrl::gemm_bf16);
   m.def("gemm_last_status", &vrl::gemm_last_status);
 }

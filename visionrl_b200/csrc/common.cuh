@@ -64,23 +64,39 @@ template <> __device__ __forceinline__ float from_f<float>(float v) { return v; 
 template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
 // 16-byte vector of 8 bf16 values.
+// Eight bf16 values moved as ONE 128-bit access.  The payload is a single uint4 member so that
+// copying the struct through a pointer compiles to one LDG.128 / STG.128 (a struct of four
+// 32-bit members is copied member by member, i.e. four 4-byte accesses per thread).
 struct alignas(16) bf16x8 {
-  __nv_bfloat162 v[4];
+  uint4 u;
 };
 
+__device__ __forceinline__ float2 bf16pair_to_float2(uint32_t w) {
+  __nv_bfloat162 h;
+  memcpy(&h, &w, sizeof(w));
+  return __bfloat1622float2(h);
+}
+
+__device__ __forceinline__ uint32_t float2_to_bf16pair(float a, float b) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  uint32_t w;
+  memcpy(&w, &h, sizeof(w));
+  return w;
+}
+
 __device__ __forceinline__ void unpack8(const bf16x8& p, float* f) {
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    float2 t = __bfloat1622float2(p.v[i]);
-    f[2 * i] = t.x;
-    f[2 * i + 1] = t.y;
-  }
+  const uint4 u = p.u;
+  float2 t;
+  t = bf16pair_to_float2(u.x); f[0] = t.x; f[1] = t.y;
+  t = bf16pair_to_float2(u.y); f[2] = t.x; f[3] = t.y;
+  t = bf16pair_to_float2(u.z); f[4] = t.x; f[5] = t.y;
+  t = bf16pair_to_float2(u.w); f[6] = t.x; f[7] = t.y;
 }
 
 __device__ __forceinline__ bf16x8 pack8(const float* f) {
   bf16x8 p;
-#pragma unroll
-  for (int i = 0; i < 4; ++i) p.v[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  p.u = make_uint4(float2_to_bf16pair(f[0], f[1]), float2_to_bf16pair(f[2], f[3]),
+                   float2_to_bf16pair(f[4], f[5]), float2_to_bf16pair(f[6], f[7]));
   return p;
 }
 

@@ -40,7 +40,11 @@ constexpr uint32_t kABytes = BM * BK * 2;          // 16 KiB
 constexpr uint32_t kBBytes = BN * BK * 2;          // 32 KiB
 constexpr uint32_t kStageBytes = kABytes + kBBytes;
 constexpr uint32_t kTmemCols = 512;                // two 256-column fp32 accumulators
-constexpr uint32_t kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int kEpiWarps = 8;
+constexpr uint32_t kStoreBytes = 32 * 128;         // one warp's 32-row x 64-column bf16 staging tile
+constexpr uint32_t kStagingBytes = kEpiWarps * kStoreBytes;
+constexpr uint32_t kSmemBytes =
+    kStages * kStageBytes + kStagingBytes + 1024 /*align*/ + 256 /*barriers*/;
 constexpr uint32_t kSpinLimit = 1u << 22;          // bounded polling (order of a second)
 
 enum Status : int { kOk = 0, kTimeoutProducer = 1, kTimeoutMma = 2, kTimeoutEpilogue = 3 };
@@ -108,6 +112,25 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, u
       : "memory");
 }
 
+__device__ __forceinline__ void tma_store_2d(const void* src, const CUtensorMap* map, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+          reinterpret_cast<uint64_t>(map)),
+      "r"(smem_u32(src)), "r"(x), "r"(y)
+      : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// The staging tile may be overwritten once earlier bulk stores have finished READING it.
+__device__ __forceinline__ void tma_store_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+__device__ __forceinline__ void tma_store_wait_all() {
+  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
+__device__ __forceinline__ void fence_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
 __device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t cols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                    smem_u32(slot)),
@@ -153,6 +176,8 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
         "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
         "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
@@ -181,16 +206,19 @@ __host__ __device__ constexpr uint32_t make_idesc(int a_mn, int b_mn) {
 // ------------------------------------------------------------------------------------- kernel
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                 const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_r,
                  const Params p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
+  uint8_t* staging = smem + kStages * kStageBytes;      // 1024-byte aligned (stage size is 48 KiB)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + kStagingBytes);
   uint64_t* full = bars;                       // [kStages]
   uint64_t* empty = bars + kStages;            // [kStages]
   uint64_t* acc_full = bars + 2 * kStages;     // [2]
   uint64_t* acc_empty = bars + 2 * kStages + 2;  // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+  uint64_t* res_full = bars + 2 * kStages + 4;   // [kEpiWarps] residual tile landed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4 + kEpiWarps);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -200,7 +228,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 8); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], kEpiWarps); }
+    for (int w = 0; w < kEpiWarps; ++w) mbar_init(&res_full[w], 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -285,32 +314,61 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     }
   } else if (warp >= 2) {
     // ---------------------------------------------------------------------- epilogue
+    // bf16 results leave through shared memory: each warp converts a 32-row x 64-column piece,
+    // writes it 128-byte-swizzled into its own staging tile and lane 0 hands that tile to a TMA
+    // store (full-line writes, rows and columns past the matrix edge clipped by the tensor map).
+    // The residual operand arrives the same way (TMA load into the staging tile, combined in
+    // place).  fp32 results are rare (final projections) and use plain 16-byte stores.
     const int quarter = warp & 3;                 // TMEM lane quarter this warp may read
-    const int half = (warp - 2) >> 2;             // which 128 accumulator columns it handles
-    uint32_t tile_it = 0;
+    const int ew = warp - 2;                      // epilogue warp index 0..7
+    const int half = ew >> 2;                     // which 128 accumulator columns it handles
+    uint8_t* stage = staging + ew * kStoreBytes;
+    const uint32_t stage_row = smem_u32(stage) + lane * 128;
+    const int swz = lane & 7;
+    uint32_t tile_it = 0, res_it = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_it) {
       const uint32_t buf = tile_it & 1u;
       const int m0 = (tile / n_tiles) * BM, n0 = (tile % n_tiles) * BN;
       if (!mbar_wait(&acc_full[buf], (tile_it >> 1) & 1u, abort_flag)) { ok = false; break; }
       tmem_fence_after();
-      const int row = m0 + quarter * 32 + lane;
+      const int row0 = m0 + quarter * 32;
+      const int row = row0 + lane;
       const bool row_ok = row < p.m;
-      const int64_t gate_row = p.gate ? (row / p.rows_per_gate) : 0;
+      const int64_t gate_row = p.gate ? ((row_ok ? row : 0) / p.rows_per_gate) : 0;
 #pragma unroll 1
-      for (int c = half * (BN / 64); c < (half + 1) * (BN / 64); ++c) {
-        uint32_t r[32];
-        tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN + c * 32, r);
-        const int col0 = n0 + c * 32;
-        if (!row_ok || col0 >= p.n) continue;
+      for (int cc = 0; cc < 2 && ok; ++cc) {
+        const int colbase = n0 + half * 128 + cc * 64;
+        if (colbase >= p.n) break;                // warp-uniform
+        const uint32_t taddr =
+            tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN + half * 128 + cc * 64;
+        uint32_t r[64];
+        tmem_ld32(taddr, r);
+        tmem_ld32(taddr + 32, r + 32);
+        if (!p.out_fp32) {
+          if (lane == 0) {
+            tma_store_wait_read();                // the previous store has drained this tile
+            if (p.residual) {
+              mbar_expect_tx(&res_full[ew], kStoreBytes);
+              tma_load_2d(stage, &map_r, &res_full[ew], colbase, row0);
+            }
+          }
+          __syncwarp();
+          if (p.residual) {
+            if (!mbar_wait(&res_full[ew], res_it & 1u, abort_flag)) { ok = false; }
+            ++res_it;
+          }
+        }
+        tmem_ld_wait();
+        if (!ok) break;
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          const int col = col0 + g * 8;
-          if (col >= p.n) break;
+        for (int g = 0; g < 8; ++g) {
+          const int col = colbase + g * 8;
+          const bool col_ok = col < p.n;
           float v[8];
 #pragma unroll
           for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[g * 8 + j]);
-          if (p.bias) {
+          if (p.bias && col_ok) {
             float b[8];
             unpack8(*reinterpret_cast<const bf16x8*>(p.bias + col), b);
 #pragma unroll
@@ -323,32 +381,60 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 #pragma unroll
             for (int j = 0; j < 8; ++j) v[j] = silu(v[j]);
           }
-          if (p.gate) {
-            float gt[8], rs[8];
-            unpack8(*reinterpret_cast<const bf16x8*>(p.gate + gate_row * p.gate_ld + col), gt);
-            unpack8(*reinterpret_cast<const bf16x8*>(p.residual + (int64_t)row * p.n + col), rs);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = rs[j] + gt[j] * v[j];
-          } else if (p.residual) {
+          const uint32_t saddr = stage_row + ((uint32_t)(g ^ swz) << 4);
+          if (p.residual) {
             float rs[8];
-            unpack8(*reinterpret_cast<const bf16x8*>(p.residual + (int64_t)row * p.n + col), rs);
+            if (!p.out_fp32) {
+              bf16x8 t;
+              asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                           : "=r"(t.u.x), "=r"(t.u.y), "=r"(t.u.z), "=r"(t.u.w)
+                           : "r"(saddr));
+              unpack8(t, rs);
+            } else if (row_ok && col_ok) {
+              unpack8(*reinterpret_cast<const bf16x8*>(p.residual + (int64_t)row * p.n + col), rs);
+            } else {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] += rs[j];
+              for (int j = 0; j < 8; ++j) rs[j] = 0.f;
+            }
+            if (p.gate) {
+              float gt[8];
+              if (col_ok) {
+                unpack8(*reinterpret_cast<const bf16x8*>(p.gate + gate_row * p.gate_ld + col), gt);
+              } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) gt[j] = 0.f;
+              }
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v[j] = rs[j] + gt[j] * v[j];
+            } else {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v[j] += rs[j];
+            }
           }
           if (p.out_fp32) {
-            float* dst = reinterpret_cast<float*>(p.c) + (int64_t)row * p.n + col;
-            *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
-            *reinterpret_cast<float4*>(dst + 4) = make_float4(v[4], v[5], v[6], v[7]);
+            if (row_ok && col_ok) {
+              float* dst = reinterpret_cast<float*>(p.c) + (int64_t)row * p.n + col;
+              *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+              *reinterpret_cast<float4*>(dst + 4) = make_float4(v[4], v[5], v[6], v[7]);
+            }
           } else {
-            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.c) + (int64_t)row * p.n + col;
-            *reinterpret_cast<bf16x8*>(dst) = pack8(v);
+            const bf16x8 o = pack8(v);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(saddr), "r"(o.u.x),
+                         "r"(o.u.y), "r"(o.u.z), "r"(o.u.w)
+                         : "memory");
           }
+        }
+        if (!p.out_fp32) {
+          fence_async_smem();                     // generic-proxy writes -> visible to the TMA unit
+          __syncwarp();
+          if (lane == 0) tma_store_2d(stage, &map_c, colbase, row0);
         }
       }
       tmem_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[buf]);
     }
+    if (lane == 0) tma_store_wait_all();          // staging must outlive the stores reading it
     if (!ok && lane == 0) {
       if (atomicCAS(const_cast<int*>(abort_flag), 0, 1) == 0) atomicExch(p.status, kTimeoutEpilogue);
     }
@@ -477,6 +563,7 @@ torch::Tensor gemm_bf16(torch::Tensor a, torch::Tensor b, c10::optional<torch::T
   if (residual.has_value()) {
     res_c = residual->to(torch::kBFloat16).contiguous();
     TORCH_CHECK(res_c.numel() == m * n);
+    if (reinterpret_cast<uintptr_t>(res_c.data_ptr()) % 16 != 0) res_c = res_c.clone();
     p.residual = reinterpret_cast<const __nv_bfloat16*>(res_c.data_ptr());
   }
   p.status = status_word(a.get_device());
@@ -496,7 +583,11 @@ torch::Tensor gemm_bf16(torch::Tensor a, torch::Tensor b, c10::optional<torch::T
   const int tiles = (int)(((m + BM - 1) / BM) * ((n + BN - 1) / BN));
   const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
   const int grid = std::min(tiles, sms);
-  gemm_bf16_kernel<<<grid, kThreads, kSmemBytes, at::cuda::getCurrentCUDAStream()>>>(map_a, map_b, p);
+  // output / residual maps: 64-column x 32-row boxes matching one epilogue warp's staging tile
+  CUtensorMap map_c = out_fp32 ? map_a : make_map(out.data_ptr(), n, m, n, 64, 32);
+  CUtensorMap map_r = (p.residual && !out_fp32) ? make_map(p.residual, n, m, n, 64, 32) : map_c;
+  gemm_bf16_kernel<<<grid, kThreads, kSmemBytes, at::cuda::getCurrentCUDAStream()>>>(map_a, map_b, map_c,
+                                                                                    map_r, p);
   C10_CUDA_KERNEL_LAUNCH_CHECK();
   return out;
 }

@@ -68,6 +68,29 @@ torch::Tensor wait_flag(torch::Tensor flags, int64_t slot, int64_t expected, dou
 void ulysses_scatter(torch::Tensor src, torch::Tensor dst_peers, int64_t batch, int64_t heads,
                      int64_t s_loc, int64_t head_dim, int64_t world, int64_t rank, bool to_heads);
 
+// ar_ops.cu
+std::vector<torch::Tensor> token_logprob_fwd(torch::Tensor logits, torch::Tensor ids, double temperature);
+torch::Tensor token_logprob_bwd(torch::Tensor logits, torch::Tensor ids, torch::Tensor lse,
+                                torch::Tensor g, double temperature);
+void lse_chunk_update(torch::Tensor chunk, torch::Tensor ids, torch::Tensor run_max,
+                      torch::Tensor run_sum, torch::Tensor target, int64_t col0, double temperature);
+torch::Tensor softmax_grad_chunk(torch::Tensor chunk, torch::Tensor ids, torch::Tensor lse,
+                                 torch::Tensor g, int64_t col0, double temperature);
+std::vector<torch::Tensor> sample_tokens(torch::Tensor cond, torch::Tensor uncond, torch::Tensor u,
+                                         double cfg_weight, double temperature);
+torch::Tensor decode_attention(torch::Tensor q, torch::Tensor k_cache, torch::Tensor v_cache,
+                               torch::Tensor valid, int64_t length, double scale);
+torch::Tensor group_advantages(torch::Tensor rewards, torch::Tensor group_ids, double eps, double clip,
+                               bool global_std);
+
+// quant_moe.cu
+torch::Tensor int4_gemv(torch::Tensor x, torch::Tensor qweight, torch::Tensor scales,
+                        c10::optional<torch::Tensor> bias, int64_t group);
+std::vector<torch::Tensor> moe_gate_topk(torch::Tensor logits, int64_t topk);
+std::vector<torch::Tensor> moe_permute(torch::Tensor experts, int64_t num_experts);
+torch::Tensor moe_gather_rows(torch::Tensor x, torch::Tensor perm, int64_t topk);
+torch::Tensor moe_combine(torch::Tensor yp, torch::Tensor inv, torch::Tensor weights);
+
 // gemm_sm100.cu
 torch::Tensor gemm_bf16(torch::Tensor a, torch::Tensor b, c10::optional<torch::Tensor> bias,
                         c10::optional<torch::Tensor> gate, c10::optional<torch::Tensor> residual,

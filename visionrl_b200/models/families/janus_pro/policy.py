@@ -100,6 +100,23 @@ class JanusNetwork(nn.Module):
     def image_logits(self, hidden: torch.Tensor) -> torch.Tensor:
         return self.gen_head.fc2(self.head_hidden(hidden))
 
+    def image_logits_fp32(self, hidden: torch.Tensor) -> torch.Tensor:
+        """Logits kept in the GEMM's fp32 accumulator precision.
+
+        Sampling records ``log_softmax`` of these values; the training replay forms the same
+        quantity from fp32 head outputs tile by tile, so both sides must skip the bf16 rounding
+        of the logits to agree.
+        """
+        from visionrl_b200.ops import linear as linear_ops
+
+        hh = self.head_hidden(hidden)
+        head = self.gen_head.fc2
+        h2 = hh.reshape(-1, hh.shape[-1])
+        if linear_ops._use_kernel(h2, head.weight):
+            out = linear_ops.gemm_nt(h2.contiguous(), head.weight, head.bias, out_dtype=torch.float32)
+            return out.view(*hh.shape[:-1], -1)
+        return head(hh).float()
+
 
 def image_token_logits_from_hidden(network: JanusNetwork, hidden: torch.Tensor) -> torch.Tensor:
     """Image-vocabulary logits from trunk hidden states (always through ``gen_head``)."""
@@ -145,6 +162,20 @@ class JanusProPolicy(nn.Module):
         if self.config.use_lora:
             self._apply_lora()
         self.fused_logprob = True
+        self._int4_layers = -1          # -1: int4 copies not built yet
+
+    def _int4_context(self):
+        """Context under which the trunk's decode-sized linears read int4 weights.
+
+        Active only when ``int4_decode`` is configured, the model sits on a CUDA device and the
+        trunk's base weights are frozen (LoRA training); the copies are built on first use.
+        """
+        from visionrl_b200.models.nn.layers import attach_int4_shadows, int4_decode
+
+        enabled = bool(self.config.int4_decode) and self.device.type == "cuda"
+        if enabled and self._int4_layers < 0:
+            self._int4_layers = attach_int4_shadows(self.policy.language_model)
+        return int4_decode(enabled and self._int4_layers > 0)
 
     @staticmethod
     def _load_checkpoint(network: nn.Module, path: str) -> None:
@@ -289,7 +320,7 @@ class JanusProPolicy(nn.Module):
         else:
             hidden = state.last_hidden[torch.cat([rows, rows + b])]
             u = state.uniforms[rows, position]
-        logits = self.policy.image_logits(hidden)
+        logits = self.policy.image_logits_fp32(hidden)
         n = logits.shape[0] // 2
         tokens, log_probs = sampling_ops.sample_cfg_tokens(
             logits[:n], logits[n:], u, state.cfg_weight, state.temperature)
@@ -302,7 +333,10 @@ class JanusProPolicy(nn.Module):
         if position + 1 < state.image_token_num:
             nxt = self.policy.align(tokens)
             lm = self.policy.language_model
-            if rows is None:
+            if rows is None and self.config.int4_decode:
+                with self._int4_context():
+                    state.last_hidden = lm.decode_step(torch.cat([nxt, nxt], dim=0), state.cache)
+            elif rows is None:
                 state.last_hidden = lm.decode_step(torch.cat([nxt, nxt], dim=0), state.cache)
             else:
                 both = torch.cat([rows, rows + b])

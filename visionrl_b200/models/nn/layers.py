@@ -31,8 +31,19 @@ class Linear(nn.Module):
         std = init_std if init_std is not None else 1.0 / math.sqrt(in_features)
         nn.init.normal_(self.weight, std=std)
 
-    def forward(self, x, act=None, gate=None, residual=None):
+    # Int4 copy of ``weight`` used for decode-sized inputs while :func:`int4_decode` is active.
+    int4_shadow = None
+
+    def _base(self, x, act=None, gate=None, residual=None):
+        shadow = self.int4_shadow
+        if (shadow is not None and _INT4_DECODE_ACTIVE and not torch.is_grad_enabled()
+                and x.numel() // x.shape[-1] <= 32):
+            y = shadow(x)
+            return linear_ops.linear_epilogue(y, act, gate, residual)
         return linear_ops.linear(x, self.weight, self.bias, act=act, gate=gate, residual=residual)
+
+    def forward(self, x, act=None, gate=None, residual=None):
+        return self._base(x, act=act, gate=gate, residual=residual)
 
     def extra_repr(self) -> str:
         return f"in={self.in_features}, out={self.out_features}, bias={self.bias is not None}"
@@ -74,10 +85,42 @@ class LoRALinear(Linear):
     def forward(self, x, act=None, gate=None, residual=None):
         if not (self.has_adapter and self.adapter_enabled):
             return super().forward(x, act=act, gate=gate, residual=residual)
-        y = linear_ops.linear(x, self.weight, self.bias)
+        y = self._base(x)
         low = linear_ops.linear(x, self.lora_A)
         y = y + self.lora_scale * linear_ops.linear(low, self.lora_B)
         return linear_ops.linear_epilogue(y, act, gate, residual)
+
+
+_INT4_DECODE_ACTIVE = False
+
+
+@contextlib.contextmanager
+def int4_decode(active: bool = True):
+    """While active, layers holding an ``int4_shadow`` serve decode-sized calls from it."""
+    global _INT4_DECODE_ACTIVE
+    previous = _INT4_DECODE_ACTIVE
+    _INT4_DECODE_ACTIVE = bool(active)
+    try:
+        yield
+    finally:
+        _INT4_DECODE_ACTIVE = previous
+
+
+def attach_int4_shadows(module: nn.Module, group: int = 128) -> int:
+    """Quantise the frozen base weight of every eligible linear under ``module`` to int4.
+
+    Only weights that do not receive gradients are shadowed (LoRA leaves the base frozen, so
+    the copy stays valid for the whole run); returns the number of layers covered.
+    """
+    from visionrl_b200.ops.quant import Int4Linear
+
+    count = 0
+    for sub in module.modules():
+        if isinstance(sub, Linear) and not sub.weight.requires_grad and sub.in_features % 256 == 0:
+            # plain attribute, not a registered submodule: the copy must stay out of state_dict()
+            object.__setattr__(sub, "int4_shadow", Int4Linear(sub, group))
+            count += 1
+    return count
 
 
 def iter_lora_layers(module: nn.Module):

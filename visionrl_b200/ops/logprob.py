@@ -58,5 +58,71 @@ def fused_head_log_probs_reference(hidden, weight, bias, ids, temperature: float
     return token_log_probs_reference(logits, flat_ids, 1.0).view(ids.shape)
 
 
-def fused_head_log_probs(hidden, weight, bias, ids, temperature: float = 1.0):
+class _FusedHeadLogProbFn(torch.autograd.Function):
+    """Head GEMM tiled over the vocabulary with an online log-sum-exp.
+
+    Forward: for every vocabulary chunk the tcgen05 GEMM writes fp32 logits ``[rows, chunk]``,
+    one kernel folds them into the running (max, sum) and picks up the target logit.  Backward
+    recomputes each chunk, turns it into ``g/T (onehot - softmax)`` in bf16 and feeds the two
+    gradient GEMMs, so neither pass ever holds ``[rows, vocab]`` logits.
+    """
+
+    @staticmethod
+    def forward(ctx, hidden, weight, bias, ids, temperature, chunk):
+        from visionrl_b200.ops import _ext
+        from visionrl_b200.ops.linear import gemm_nt
+
+        ext = _ext.load()
+        h = hidden.reshape(-1, hidden.shape[-1]).contiguous()
+        flat_ids = ids.reshape(-1).contiguous()
+        rows, vocab = h.shape[0], weight.shape[0]
+        run_max = torch.full((rows,), float("-inf"), device=h.device, dtype=torch.float32)
+        run_sum = torch.zeros(rows, device=h.device, dtype=torch.float32)
+        target = torch.zeros(rows, device=h.device, dtype=torch.float32)
+        for c0 in range(0, vocab, chunk):
+            c1 = min(vocab, c0 + chunk)
+            logits = gemm_nt(h, weight[c0:c1], None if bias is None else bias[c0:c1],
+                             out_dtype=torch.float32)
+            ext.lse_chunk_update(logits, flat_ids, run_max, run_sum, target, c0, float(temperature))
+        lse = run_max + torch.log(run_sum)
+        ctx.save_for_backward(h, weight, bias if bias is not None else h.new_zeros(0), flat_ids, lse)
+        ctx.has_bias = bias is not None
+        ctx.temperature, ctx.chunk = float(temperature), int(chunk)
+        ctx.hidden_shape = hidden.shape
+        return (target - lse).view(ids.shape)
+
+    @staticmethod
+    def backward(ctx, g):
+        from visionrl_b200.ops import _ext
+        from visionrl_b200.ops.linear import gemm_nn, gemm_nt, gemm_tn
+
+        ext = _ext.load()
+        h, weight, bias, flat_ids, lse = ctx.saved_tensors
+        bias = bias if ctx.has_bias else None
+        gflat = g.reshape(-1).contiguous().float()
+        vocab = weight.shape[0]
+        need_w = ctx.needs_input_grad[1]
+        gh = torch.zeros(h.shape, device=h.device, dtype=torch.float32)
+        gw = torch.empty_like(weight) if need_w else None
+        gb = torch.empty_like(bias) if (bias is not None and ctx.needs_input_grad[2]) else None
+        for c0 in range(0, vocab, ctx.chunk):
+            c1 = min(vocab, c0 + ctx.chunk)
+            logits = gemm_nt(h, weight[c0:c1], None if bias is None else bias[c0:c1],
+                             out_dtype=torch.float32)
+            dl = ext.softmax_grad_chunk(logits, flat_ids, lse, gflat, c0, ctx.temperature)
+            gh += gemm_nn(dl, weight[c0:c1]).float()
+            if need_w:
+                gw[c0:c1] = gemm_tn(dl, h)
+            if gb is not None:
+                gb[c0:c1] = ext.colsum(dl).to(gb.dtype)
+        return gh.to(h.dtype).view(ctx.hidden_shape), gw, gb, None, None, None
+
+
+def fused_head_log_probs(hidden, weight, bias, ids, temperature: float = 1.0, chunk: int = 4096):
+    from visionrl_b200.ops import _ext
+
+    if (hidden.is_cuda and hidden.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
+            and hidden.shape[-1] % 8 == 0 and weight.shape[0] % 8 == 0 and chunk % 8 == 0
+            and _ext.kernels_enabled() and _ext.has("lse_chunk_update")):
+        return _FusedHeadLogProbFn.apply(hidden, weight, bias, ids, temperature, chunk)
     return fused_head_log_probs_reference(hidden, weight, bias, ids, temperature)
