@@ -496,3 +496,93 @@ def test_gemm_tma_store_epilogue_tails_with_gate_residual():
     got2 = ext.gemm_bf16(a, w, bias, None, res, 1, 1, False, False, False)
     ref2 = torch.nn.functional.gelu(lin, approximate="tanh") + res.float()
     assert torch.allclose(got2.float(), ref2, atol=6e-2, rtol=3e-2)
+
+
+# ------------------------------------------------------------------------ tcgen05 attention
+@pytest.mark.gpu
+@pytest.mark.parametrize("shape", [(2, 3, 1178, 1178, 64), (1, 2, 300, 512, 128), (2, 2, 128, 77, 64),
+                                   (1, 4, 515, 515, 128)])
+def test_flash_attention_forward_matches_fp32(shape):
+    from visionrl_b200.ops import _ext
+    from visionrl_b200.ops.attention import attention_reference, flash_attention_forward
+
+    b, h, sq, skv, d = shape
+    torch.manual_seed(8)
+    q = torch.randn(b, h, sq, d, device="cuda").bfloat16()
+    k = torch.randn(b, h, skv, d, device="cuda").bfloat16()
+    v = torch.randn(b, h, skv, d, device="cuda").bfloat16()
+    out, lse = flash_attention_forward(q, k, v, d ** -0.5)
+    torch.cuda.synchronize()
+    assert _ext.load().flash_attn_last_status() == 0
+    ref = attention_reference(q.float(), k.float(), v.float())
+    assert out.shape == ref.shape
+    assert torch.allclose(out.float(), ref, atol=2e-2, rtol=2e-2)
+    scores = torch.matmul(q.float(), k.float().transpose(-1, -2)) * d ** -0.5
+    assert torch.allclose(lse, torch.logsumexp(scores, dim=-1), atol=2e-3, rtol=1e-3)
+
+
+@pytest.mark.gpu
+def test_flash_attention_token_major_views_and_dispatch():
+    from visionrl_b200.ops.attention import attention, attention_reference
+
+    torch.manual_seed(9)
+    b, s, h, d = 2, 333, 4, 64
+    bufs = [torch.randn(b, s, h, d, device="cuda").bfloat16() for _ in range(3)]
+    q, k, v = (t.transpose(1, 2) for t in bufs)            # [B, H, S, D] views, token-major storage
+    with torch.no_grad():
+        out = attention(q, k, v)
+    ref = attention_reference(q.float(), k.float(), v.float())
+    assert torch.allclose(out.float(), ref, atol=2e-2, rtol=2e-2)
+    merged = out.transpose(1, 2).reshape(b, s, h * d)
+    assert merged.data_ptr() == out.data_ptr()              # merging heads is a view, not a copy
+
+
+@pytest.mark.gpu
+def test_joint_qkv_prepare_matches_concatenated_reference():
+    from visionrl_b200.ops.qkv import joint_qkv_prepare, qkv_prepare_reference
+
+    torch.manual_seed(10)
+    b, sa, sb, heads, dh = 2, 40, 13, 4, 64
+    d = heads * dh
+    res = []
+    for use_kernel in (True, False):
+        gen = torch.Generator("cuda").manual_seed(3)
+        xa = torch.randn(b, sa, 3 * d, device="cuda", generator=gen).bfloat16().requires_grad_()
+        xb = torch.randn(b, sb, 3 * d, device="cuda", generator=gen).bfloat16().requires_grad_()
+        ws = [(1 + 0.1 * torch.randn(dh, device="cuda", generator=gen)).bfloat16().requires_grad_()
+              for _ in range(4)]
+        if use_kernel:
+            q, k, v = joint_qkv_prepare(xa, xb, heads, (ws[0], ws[1]), (ws[2], ws[3]))
+        else:
+            qa, ka, va = qkv_prepare_reference(xa, heads, ws[0], ws[1])
+            qb, kb, vb = qkv_prepare_reference(xb, heads, ws[2], ws[3])
+            q, k, v = torch.cat([qa, qb], 2), torch.cat([ka, kb], 2), torch.cat([va, vb], 2)
+        grads = [torch.randn(q.shape, device="cuda", generator=gen).bfloat16() for _ in range(3)]
+        torch.autograd.backward([q, k, v], grads)
+        res.append((q, k, v, xa.grad, xb.grad, *[w.grad for w in ws]))
+    for got, ref in zip(*res):
+        assert _rel(got, ref) < 3e-2
+
+
+@pytest.mark.gpu
+def test_gate_residual_fused_forward_backward():
+    from visionrl_b200.ops.linear import gate_residual
+
+    torch.manual_seed(12)
+    b, s, d = 3, 77, 256
+    res = []
+    for fused in (True, False):
+        gen = torch.Generator("cuda").manual_seed(1)
+        y = torch.randn(b, s, d, device="cuda", generator=gen).bfloat16().requires_grad_()
+        mod = torch.randn(b, 3 * d, device="cuda", generator=gen).bfloat16().requires_grad_()
+        r = torch.randn(b, s, d, device="cuda", generator=gen).bfloat16().requires_grad_()
+        gate = mod[:, d:2 * d]
+        if fused:
+            out = gate_residual(y, gate, r)
+        else:
+            out = (r.float() + gate.float().unsqueeze(1) * y.float())
+        g = torch.randn(b, s, d, device="cuda", generator=gen).bfloat16()
+        out.backward(g.to(out.dtype))
+        res.append((out, y.grad, mod.grad, r.grad))
+    for got, ref in zip(*res):
+        assert _rel(got, ref) < 2e-2

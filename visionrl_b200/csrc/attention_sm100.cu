@@ -1,0 +1,408 @@
+// Bidirectional flash attention forward for sm_100a: S = Q K^T and O += P V on tcgen05.mma with
+// both accumulators in tensor memory, operands staged by TMA, online softmax in registers.
+//
+// One CTA owns 128 query rows of one (batch, head) and walks the keys in tiles of 128.
+//   warp 0      TMA producer: Q once, then K and V tiles through two-stage rings
+//   warp 1      MMA issuer and TMEM owner: S[j+1] = Q K[j+1]^T is issued before P[j] V[j], so the
+//               tensor core works on the next score tile while the softmax warps handle this one
+//   warps 2..5  softmax: thread r owns query row r.  Two passes over the score tile in TMEM (row
+//               maximum, then exponentials), probabilities written as bf16 into a 128-byte-swizzled
+//               shared tile that is the A operand of P V; the running output lives in registers and
+//               absorbs each P V partial product from TMEM with the usual rescale.
+// TMEM columns: S0, S1 (128 each), then O0, O1 (D each).  Every wait is bounded; on expiry the
+// role records a status code, raises the CTA's abort flag and all roles fall through to the
+// common exit where the TMEM is released.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <cudaTypedefs.h>
+
+#include <map>
+#include <mutex>
+
+#include "common.cuh"
+#include "ops.h"
+#include "sm100_ptx.cuh"
+
+namespace vrl {
+namespace attn {
+
+using namespace ptx;
+
+constexpr int kTile = 128;                 // query rows per CTA and keys per step
+constexpr int kThreads = 192;
+constexpr uint32_t kBlockBytes = kTile * 128;   // one 64-column swizzle block of a 128-row tile
+constexpr uint32_t kPBytes = 2 * kBlockBytes;
+constexpr uint32_t kTmemCols = 512;
+
+enum Status : int { kOk = 0, kTimeoutProducer = 11, kTimeoutMma = 12, kTimeoutSoftmax = 13 };
+
+template <int D>
+struct Cfg {
+  static constexpr int kDBlocks = D / 64;
+  static constexpr uint32_t kTileBytes = kDBlocks * kBlockBytes;      // Q, K or V tile
+  static constexpr uint32_t kSmemBytes = 5 * kTileBytes + kPBytes + 1024 + 256;
+  static constexpr uint32_t kOCol = 2 * kTile;                        // first O column in TMEM
+};
+
+struct Params {
+  __nv_bfloat16* out;     // token-major [B, Sq, H, D]
+  float* lse;             // [B, H, Sq] natural-log sum of exponentials of the scaled scores
+  int heads;
+  int* status;
+  int sq, skv;
+  float scale_log2;       // softmax scale times log2(e)
+};
+
+template <int D>
+__global__ void __launch_bounds__(kThreads, 1)
+flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                 const __grid_constant__ CUtensorMap map_v, const Params p) {
+  using C = Cfg<D>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* sq = smem;
+  uint8_t* sk = sq + C::kTileBytes;            // [2]
+  uint8_t* sv = sk + 2 * C::kTileBytes;        // [2]
+  uint8_t* sp = sv + 2 * C::kTileBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sp + kPBytes);
+  uint64_t* q_full = bars;
+  uint64_t* k_full = bars + 1;     // [2]
+  uint64_t* k_empty = bars + 3;    // [2]
+  uint64_t* v_full = bars + 5;     // [2]
+  uint64_t* v_empty = bars + 7;    // [2]
+  uint64_t* s_full = bars + 9;     // [2]
+  uint64_t* o_full = bars + 11;    // [2]
+  uint64_t* p_full = bars + 13;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int bh = blockIdx.y, q0 = blockIdx.x * kTile;
+  const int bi = bh / p.heads, hi = bh % p.heads;
+  const int n_tiles = (p.skv + kTile - 1) / kTile;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1);
+      mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
+      mbar_init(&s_full[s], 1); mbar_init(&o_full[s], 1);
+    }
+    mbar_init(p_full, 4);
+    *abort_flag = 0;
+    mbar_fence_init();
+    fence_async_smem();
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, kTmemCols);
+  tmem_fence_before();
+  __syncthreads();
+  tmem_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0 && lane == 0) {
+    // ----------------------------------------------------------------------- TMA producer
+    bool ok = true;
+    mbar_expect_tx(q_full, C::kTileBytes);
+#pragma unroll
+    for (int c = 0; c < C::kDBlocks; ++c) tma_load_4d(sq + c * kBlockBytes, &map_q, q_full, c * 64, q0, hi, bi);
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int s = j & 1;
+      const uint32_t ph = ((j >> 1) & 1u) ^ 1u;
+      if (!mbar_wait(&k_empty[s], ph, abort_flag)) { ok = false; break; }
+      mbar_expect_tx(&k_full[s], C::kTileBytes);
+#pragma unroll
+      for (int c = 0; c < C::kDBlocks; ++c)
+        tma_load_4d(sk + s * C::kTileBytes + c * kBlockBytes, &map_k, &k_full[s], c * 64, j * kTile, hi, bi);
+      if (!mbar_wait(&v_empty[s], ph, abort_flag)) { ok = false; break; }
+      mbar_expect_tx(&v_full[s], C::kTileBytes);
+#pragma unroll
+      for (int c = 0; c < C::kDBlocks; ++c)
+        tma_load_4d(sv + s * C::kTileBytes + c * kBlockBytes, &map_v, &v_full[s], c * 64, j * kTile, hi, bi);
+    }
+    if (!ok && atomicCAS(const_cast<int*>(abort_flag), 0, 1) == 0) atomicExch(p.status, kTimeoutProducer);
+    if (*abort_flag) {
+      // copies already issued write into this CTA's shared memory: give them time to land
+      for (uint32_t spin = 0; spin < (1u << 20); ++spin)
+        if (mbar_try(q_full, 0)) break;
+      for (int s = 0; s < 2; ++s)
+        for (uint32_t spin = 0; spin < (1u << 16); ++spin) {
+          if (mbar_try(&k_full[s], 0) || mbar_try(&k_full[s], 1)) break;
+        }
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ------------------------------------------------------------------------ MMA issuer
+    constexpr uint32_t idesc_qk = make_idesc(kTile, kTile, 0, 0);
+    constexpr uint32_t idesc_pv = make_idesc(kTile, D, 0, 1);
+    bool ok = mbar_wait(q_full, 0, abort_flag);
+    tmem_fence_after();
+    auto issue_qk = [&](int j) -> bool {
+      const int s = j & 1;
+      if (!mbar_wait(&k_full[s], (j >> 1) & 1u, abort_flag)) return false;
+      tmem_fence_after();
+      const uint32_t qa = smem_u32(sq), ka = smem_u32(sk + s * C::kTileBytes);
+#pragma unroll
+      for (int c = 0; c < C::kDBlocks; ++c)
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          umma_bf16(tmem_base + s * kTile, make_desc(qa + c * kBlockBytes + kk * 32, 16, 1024),
+                    make_desc(ka + c * kBlockBytes + kk * 32, 16, 1024), idesc_qk, (c | kk) ? 1u : 0u);
+      umma_commit(&k_empty[s]);
+      umma_commit(&s_full[s]);
+      return true;
+    };
+    if (ok) ok = issue_qk(0);
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      if (j + 1 < n_tiles && !issue_qk(j + 1)) { ok = false; break; }
+      if (!mbar_wait(p_full, j & 1u, abort_flag)) { ok = false; break; }
+      const int s = j & 1;
+      if (!mbar_wait(&v_full[s], (j >> 1) & 1u, abort_flag)) { ok = false; break; }
+      tmem_fence_after();
+      const uint32_t pa = smem_u32(sp), va = smem_u32(sv + s * C::kTileBytes);
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk)
+        umma_bf16(tmem_base + C::kOCol + s * D,
+                  make_desc(pa + (kk >> 2) * kBlockBytes + (kk & 3) * 32, 16, 1024),
+                  make_desc(va + kk * 2048, kBlockBytes, 1024), idesc_pv, kk ? 1u : 0u);
+      umma_commit(&v_empty[s]);
+      umma_commit(&o_full[s]);
+    }
+    if (!ok && atomicCAS(const_cast<int*>(abort_flag), 0, 1) == 0) atomicExch(p.status, kTimeoutMma);
+  } else if (warp >= 2) {
+    // --------------------------------------------------------------------------- softmax
+    const int quarter = warp & 3;
+    const int row_local = quarter * 32 + lane;
+    const int row = q0 + row_local;
+    const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    const uint32_t p_row = smem_u32(sp) + row_local * 128;
+    const int swz = row_local & 7;
+    float m = -INFINITY, l = 0.f;
+    float o[D];
+#pragma unroll
+    for (int i = 0; i < D; ++i) o[i] = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_tiles; ++j) {
+      const int sb = j & 1;
+      ok = __all_sync(0xffffffffu, mbar_wait(&s_full[sb], (j >> 1) & 1u, abort_flag));
+      if (!ok) break;
+      tmem_fence_after();
+      const int valid = min(kTile, p.skv - j * kTile);
+      const uint32_t s_addr = lane_base + sb * kTile;
+      // pass 1: row maximum
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld32(s_addr + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (c * 32 + i < valid) mx = fmaxf(mx, __uint_as_float(r[i]));
+      }
+      const float m_new = fmaxf(m, mx * p.scale_log2);
+      const float corr = exp2f(m - m_new);              // 0 on the first tile (m = -inf)
+      // the previous P V must be done before its P operand is overwritten
+      if (j > 0) {
+        ok = __all_sync(0xffffffffu, mbar_wait(&o_full[(j - 1) & 1], ((j - 1) >> 1) & 1u, abort_flag));
+        if (!ok) break;
+        tmem_fence_after();
+      }
+      // pass 2: probabilities -> shared memory (bf16, swizzled K-major), row sum
+      float rowsum = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld32(s_addr + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          float pv[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int col = c * 32 + g * 8 + i;
+            const float e = exp2f(__uint_as_float(r[g * 8 + i]) * p.scale_log2 - m_new);
+            pv[i] = col < valid ? e : 0.f;
+            rowsum += pv[i];
+          }
+          const bf16x8 packed = pack8(pv);
+          const uint32_t chunk = (uint32_t)((c & 1) * 4 + g);
+          const uint32_t addr = p_row + (c >> 1) * kBlockBytes + ((chunk ^ (uint32_t)swz) << 4);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(packed.u.x),
+                       "r"(packed.u.y), "r"(packed.u.z), "r"(packed.u.w)
+                       : "memory");
+        }
+      }
+      fence_async_smem();
+      tmem_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full);
+      // absorb the previous partial product: o = (o + P[j-1] V[j-1]) * corr
+      if (j > 0) {
+        const uint32_t o_addr = lane_base + C::kOCol + ((j - 1) & 1) * D;
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(o_addr + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[c * 32 + i] = (o[c * 32 + i] + __uint_as_float(r[i])) * corr;
+        }
+      }
+      l = l * corr + rowsum;
+      m = m_new;
+    }
+    if (ok) {
+      const int last = n_tiles - 1;
+      ok = __all_sync(0xffffffffu, mbar_wait(&o_full[last & 1], (last >> 1) & 1u, abort_flag));
+    }
+    if (ok) {
+      tmem_fence_after();
+      const int last = n_tiles - 1;
+      const uint32_t o_addr = lane_base + C::kOCol + (last & 1) * D;
+      const float inv = 1.f / l;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(o_addr + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[c * 32 + i] = (o[c * 32 + i] + __uint_as_float(r[i])) * inv;
+      }
+      if (row < p.sq) {
+        __nv_bfloat16* dst = p.out + (((int64_t)bi * p.sq + row) * p.heads + hi) * D;
+#pragma unroll
+        for (int g = 0; g < D / 8; ++g) *reinterpret_cast<bf16x8*>(dst + g * 8) = pack8(&o[g * 8]);
+        p.lse[(int64_t)bh * p.sq + row] = (m + log2f(l)) * 0.6931471805599453f;
+      }
+    } else if (lane == 0) {
+      if (atomicCAS(const_cast<int*>(abort_flag), 0, 1) == 0) atomicExch(p.status, kTimeoutSoftmax);
+    }
+  }
+
+  tmem_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tmem_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// --------------------------------------------------------------------------------- host side
+using EncodeFn = PFN_cuTensorMapEncodeTiled_v12000;
+
+static EncodeFn encode_fn() {
+  static EncodeFn fn = [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    C10_CUDA_CHECK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q));
+    TORCH_CHECK(ptr != nullptr && q == cudaDriverEntryPointSuccess,
+                "cuTensorMapEncodeTiled is not available from this driver");
+    return reinterpret_cast<EncodeFn>(ptr);
+  }();
+  return fn;
+}
+
+// A [B, H, S, D] bf16 view with unit stride in D: dims {D, S, H, B}; box = 64 columns x 128 rows of
+// one (batch, head).  Rows past S read as zeros.
+static CUtensorMap make_map4(const torch::Tensor& t) {
+  CUtensorMap map;
+  cuuint64_t dims[4] = {(cuuint64_t)t.size(3), (cuuint64_t)t.size(2), (cuuint64_t)t.size(1),
+                        (cuuint64_t)t.size(0)};
+  cuuint64_t strides[3] = {(cuuint64_t)t.stride(2) * 2, (cuuint64_t)t.stride(1) * 2,
+                           (cuuint64_t)t.stride(0) * 2};
+  cuuint32_t box[4] = {64, (cuuint32_t)kTile, 1, 1};
+  cuuint32_t elem[4] = {1, 1, 1, 1};
+  CUresult rc = encode_fn()(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, t.data_ptr(), dims, strides, box,
+                            elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  TORCH_CHECK(rc == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with code ", (int)rc);
+  return map;
+}
+
+// A tensor the 4-D map can describe as is: unit stride in D, other strides multiples of 16 bytes.
+static torch::Tensor mappable(torch::Tensor t) {
+  const bool ok = t.stride(3) == 1 && t.stride(0) % 8 == 0 && t.stride(1) % 8 == 0 && t.stride(2) % 8 == 0 &&
+                  reinterpret_cast<uintptr_t>(t.data_ptr()) % 16 == 0;
+  return ok ? t : t.contiguous();
+}
+
+static int* status_word(int device) {
+  static std::map<int, int*> words;
+  static std::mutex mu;
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = words.find(device);
+  if (it != words.end()) return it->second;
+  int* w = nullptr;
+  C10_CUDA_CHECK(cudaMalloc(&w, sizeof(int)));
+  C10_CUDA_CHECK(cudaMemset(w, 0, sizeof(int)));
+  words[device] = w;
+  return w;
+}
+
+template <int D>
+static void launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const Params& p,
+                   int q_tiles, int bh, cudaStream_t stream) {
+  static const bool attr_set = [] {
+    C10_CUDA_CHECK(cudaFuncSetAttribute(flash_fwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        Cfg<D>::kSmemBytes));
+    return true;
+  }();
+  (void)attr_set;
+  flash_fwd_kernel<D><<<dim3(q_tiles, bh), kThreads, Cfg<D>::kSmemBytes, stream>>>(mq, mk, mv, p);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
+}  // namespace attn
+
+int64_t flash_attn_last_status() {
+  int device = 0;
+  C10_CUDA_CHECK(cudaGetDevice(&device));
+  int host = 0;
+  C10_CUDA_CHECK(cudaMemcpy(&host, attn::status_word(device), sizeof(int), cudaMemcpyDeviceToHost));
+  if (host != 0) C10_CUDA_CHECK(cudaMemset(attn::status_word(device), 0, sizeof(int)));
+  return host;
+}
+
+std::vector<torch::Tensor> flash_attn_fwd(torch::Tensor q, torch::Tensor k, torch::Tensor v, double scale) {
+  using namespace attn;
+  TORCH_CHECK(q.is_cuda() && q.dim() == 4 && k.dim() == 4 && v.dim() == 4, "flash_attn_fwd: [B, H, S, D]");
+  TORCH_CHECK(q.scalar_type() == torch::kBFloat16 && k.scalar_type() == torch::kBFloat16 &&
+              v.scalar_type() == torch::kBFloat16);
+  const int64_t b = q.size(0), h = q.size(1), sq = q.size(2), d = q.size(3), skv = k.size(2);
+  TORCH_CHECK(d == 64 || d == 128, "flash_attn_fwd: head dimension 64 or 128");
+  TORCH_CHECK(k.size(0) == b && k.size(1) == h && k.size(3) == d && v.sizes() == k.sizes());
+  q = mappable(q);
+  k = mappable(k);
+  v = mappable(v);
+  const c10::cuda::CUDAGuard guard(q.device());
+  static thread_local bool context_bound = false;   // the encoder is a driver entry point
+  if (!context_bound) {
+    C10_CUDA_CHECK(cudaFree(nullptr));
+    context_bound = true;
+  }
+  // token-major output, returned as a [B, H, S, D] view: merging heads afterwards is free
+  auto out_tm = torch::empty({b, sq, h, d}, q.options());
+  auto out = out_tm.transpose(1, 2);
+  auto lse = torch::empty({b, h, sq}, q.options().dtype(torch::kFloat32));
+  if (b * h == 0 || sq == 0) return {out, lse};
+  TORCH_CHECK(skv > 0, "flash_attn_fwd: empty key sequence");
+  const CUtensorMap mq = make_map4(q);
+  const CUtensorMap mk = make_map4(k);
+  const CUtensorMap mv = make_map4(v);
+  Params p{};
+  p.out = reinterpret_cast<__nv_bfloat16*>(out_tm.data_ptr());
+  p.heads = (int)h;
+  p.lse = lse.data_ptr<float>();
+  p.status = status_word(q.get_device());
+  p.sq = (int)sq;
+  p.skv = (int)skv;
+  p.scale_log2 = (float)(scale * 1.4426950408889634);
+  const int q_tiles = (int)((sq + kTile - 1) / kTile);
+  TORCH_CHECK(b * h <= 65535, "flash_attn_fwd: batch * heads exceeds the grid limit");
+  auto stream = at::cuda::getCurrentCUDAStream();
+  if (d == 64) launch<64>(mq, mk, mv, p, q_tiles, (int)(b * h), stream);
+  else launch<128>(mq, mk, mv, p, q_tiles, (int)(b * h), stream);
+  return {out, lse};
+}
+
+}  // namespace vrl

@@ -38,6 +38,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("adamw_flat", &vrl::adamw_flat);
   m.def("adaln_fwd", &vrl::adaln_fwd);
   m.def("adaln_bwd", &vrl::adaln_bwd);
+  m.def("gate_residual_fwd", &vrl::gate_residual_fwd);
+  m.def("gate_residual_bwd", &vrl::gate_residual_bwd);
   m.def("rmsnorm_fwd", &vrl::rmsnorm_fwd);
   m.def("rmsnorm_bwd", &vrl::rmsnorm_bwd);
   m.def("qkv_prepare_fwd", &vrl::qkv_prepare_fwd);
@@ -59,6 +61,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("moe_permute", &vrl::moe_permute);
   m.def("moe_gather_rows", &vrl::moe_gather_rows);
   m.def("moe_combine", &vrl::moe_combine);
+  m.def("flash_attn_fwd", &vrl::flash_attn_fwd);
+  m.def("flash_attn_last_status", &vrl::flash_attn_last_status);
   m.def("gemm_bf16", &vrl::gemm_bf16);
   m.def("gemm_last_status", &vrl::gemm_last_status);
 }

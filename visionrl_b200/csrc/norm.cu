@@ -27,6 +27,199 @@ static torch::Tensor strided_rows(torch::Tensor t, int64_t b, int64_t d) {
   return ok ? t : t.to(torch::kBFloat16).contiguous();
 }
 
+
+// ------------------------------------------------------------------ warp-per-row variants
+// For D <= 2048 one warp owns a whole row: lane l holds vectors l, l+32, ... (512 contiguous
+// bytes per warp-wide load), statistics are warp shuffles, and no block barrier is needed, so
+// many rows are in flight per SM.  Rows stay packed (bf16) in registers between the passes.
+constexpr int kRowWarps = 8;
+
+template <int VPL>
+__global__ void __launch_bounds__(kRowWarps * 32)
+adaln_fwd_warp_kernel(const bf16* __restrict__ x, const bf16* __restrict__ shift,
+                      const bf16* __restrict__ scale, bf16* __restrict__ y, float* __restrict__ mean_o,
+                      float* __restrict__ rstd_o, int64_t rows, int rows_per_sample, int d, float eps,
+                      int64_t shift_ld, int64_t scale_ld) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * kRowWarps + warp;
+  if (row >= rows) return;
+  const int nvec = d / 8;
+  const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + row * d);
+  bf16x8 raw[VPL];
+  float s = 0.f;
+#pragma unroll
+  for (int k = 0; k < VPL; ++k) {
+    const int i = lane + k * 32;
+    if (i < nvec) {
+      raw[k] = xr[i];
+      float f[8];
+      unpack8(raw[k], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) s += f[j];
+    }
+  }
+  const float mu = warp_sum(s) / (float)d;
+  float q = 0.f;
+#pragma unroll
+  for (int k = 0; k < VPL; ++k) {
+    if (lane + k * 32 < nvec) {
+      float f[8];
+      unpack8(raw[k], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { const float c = f[j] - mu; q += c * c; }
+    }
+  }
+  const float rstd = rsqrtf(warp_sum(q) / (float)d + eps);
+  if (lane == 0) { mean_o[row] = mu; rstd_o[row] = rstd; }
+  const int sample = (int)(row / rows_per_sample);
+  const bf16x8* sh = reinterpret_cast<const bf16x8*>(shift + (int64_t)sample * shift_ld);
+  const bf16x8* sc = reinterpret_cast<const bf16x8*>(scale + (int64_t)sample * scale_ld);
+  bf16x8* yr = reinterpret_cast<bf16x8*>(y + row * d);
+#pragma unroll
+  for (int k = 0; k < VPL; ++k) {
+    const int i = lane + k * 32;
+    if (i < nvec) {
+      float f[8], a[8], b[8], o[8];
+      unpack8(raw[k], f);
+      unpack8(sh[i], a);
+      unpack8(sc[i], b);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = (f[j] - mu) * rstd * (1.f + b[j]) + a[j];
+      yr[i] = pack8(o);
+    }
+  }
+}
+
+// Backward: a block of 8 warps covers `kAdaBlockRows` rows of ONE sample.  Per-column sums for
+// d(shift) and d(scale) go to shared memory with one shared atomic per element (lanes of a warp
+// hit distinct columns), then once per block to global memory.
+constexpr int kAdaBlockRows = 32;
+
+template <int VPL>
+__global__ void __launch_bounds__(kRowWarps * 32)
+adaln_bwd_warp_kernel(const bf16* __restrict__ gy, const bf16* __restrict__ x,
+                      const bf16* __restrict__ scale, const float* __restrict__ mean,
+                      const float* __restrict__ rstd, bf16* __restrict__ gx, float* __restrict__ gshift,
+                      float* __restrict__ gscale, int rows_per_sample, int d, int64_t scale_ld) {
+  extern __shared__ float col_acc[];         // [2][d]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int sample = blockIdx.y;
+  const int nvec = d / 8;
+  for (int i = threadIdx.x; i < 2 * d; i += blockDim.x) col_acc[i] = 0.f;
+  __syncthreads();
+  const bf16x8* sc = reinterpret_cast<const bf16x8*>(scale + (int64_t)sample * scale_ld);
+  const int r_begin = blockIdx.x * kAdaBlockRows;
+  for (int r = r_begin + warp; r < r_begin + kAdaBlockRows && r < rows_per_sample; r += kRowWarps) {
+    const int64_t row = (int64_t)sample * rows_per_sample + r;
+    const float mu = mean[row], rs = rstd[row];
+    const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + row * d);
+    const bf16x8* gr = reinterpret_cast<const bf16x8*>(gy + row * d);
+    bf16x8 xraw[VPL], graw[VPL];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int k = 0; k < VPL; ++k) {
+      const int i = lane + k * 32;
+      if (i < nvec) {
+        xraw[k] = xr[i];
+        graw[k] = gr[i];
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < VPL; ++k) {
+      const int i = lane + k * 32;
+      if (i < nvec) {
+        float xv[8], gv[8], t[8];
+        unpack8(xraw[k], xv);
+        unpack8(graw[k], gv);
+        unpack8(sc[i], t);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float xh = (xv[j] - mu) * rs;
+          const float gp = gv[j] * (1.f + t[j]);
+          s1 += gp;
+          s2 += gp * xh;
+          atomicAdd(&col_acc[i * 8 + j], gv[j]);
+          atomicAdd(&col_acc[d + i * 8 + j], gv[j] * xh);
+        }
+      }
+    }
+    const float m1 = warp_sum(s1) / (float)d;
+    const float m2 = warp_sum(s2) / (float)d;
+    bf16x8* gxr = reinterpret_cast<bf16x8*>(gx + row * d);
+#pragma unroll
+    for (int k = 0; k < VPL; ++k) {
+      const int i = lane + k * 32;
+      if (i < nvec) {
+        float xv[8], gv[8], t[8], o[8];
+        unpack8(xraw[k], xv);
+        unpack8(graw[k], gv);
+        unpack8(sc[i], t);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float xh = (xv[j] - mu) * rs;
+          o[j] = rs * (gv[j] * (1.f + t[j]) - m1 - xh * m2);
+        }
+        gxr[i] = pack8(o);
+      }
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    atomicAdd(gshift + (int64_t)sample * d + i, col_acc[i]);
+    atomicAdd(gscale + (int64_t)sample * d + i, col_acc[d + i]);
+  }
+}
+
+template <int VPL>
+__global__ void __launch_bounds__(kRowWarps * 32)
+rmsnorm_fwd_warp_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16* __restrict__ y,
+                        float* __restrict__ rstd_o, int64_t rows, int d, float eps) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * kRowWarps + warp;
+  if (row >= rows) return;
+  const int nvec = d / 8;
+  const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + row * d);
+  const bf16x8* wr = reinterpret_cast<const bf16x8*>(w);
+  bf16x8 raw[VPL];
+  float q = 0.f;
+#pragma unroll
+  for (int k = 0; k < VPL; ++k) {
+    const int i = lane + k * 32;
+    if (i < nvec) {
+      raw[k] = xr[i];
+      float f[8];
+      unpack8(raw[k], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) q += f[j] * f[j];
+    }
+  }
+  const float rstd = rsqrtf(warp_sum(q) / (float)d + eps);
+  if (lane == 0) rstd_o[row] = rstd;
+  bf16x8* yr = reinterpret_cast<bf16x8*>(y + row * d);
+#pragma unroll
+  for (int k = 0; k < VPL; ++k) {
+    const int i = lane + k * 32;
+    if (i < nvec) {
+      float f[8], ww[8], o[8];
+      unpack8(raw[k], f);
+      unpack8(wr[i], ww);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = f[j] * rstd * ww[j];
+      yr[i] = pack8(o);
+    }
+  }
+}
+
+// Calls `fn.template operator()<VPL>()` with the smallest VPL in {2, 4, 6, 8} covering nvec / 32.
+#define VRL_DISPATCH_VPL(nvec, ...)                     \
+  do {                                                  \
+    const int vpl_needed = ((nvec) + 31) / 32;          \
+    if (vpl_needed <= 2) { constexpr int VPL = 2; __VA_ARGS__; }        \
+    else if (vpl_needed <= 4) { constexpr int VPL = 4; __VA_ARGS__; }   \
+    else if (vpl_needed <= 6) { constexpr int VPL = 6; __VA_ARGS__; }   \
+    else { constexpr int VPL = 8; __VA_ARGS__; }                        \
+  } while (0)
+
 // ------------------------------------------------------------------------------ adaLN forward
 __global__ void __launch_bounds__(kNormThreads)
 adaln_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ shift,
@@ -89,7 +282,19 @@ std::vector<torch::Tensor> adaln_fwd(torch::Tensor x, torch::Tensor shift, torch
   auto y = torch::empty_like(x);
   auto mean = torch::empty({(int64_t)b * s}, x.options().dtype(torch::kFloat32));
   auto rstd = torch::empty_like(mean);
-  adaln_fwd_kernel<<<b * s, kNormThreads, 0, at::cuda::getCurrentCUDAStream()>>>(
+  auto stream = at::cuda::getCurrentCUDAStream();
+  if (d <= 2048) {
+    const int64_t rows = (int64_t)b * s;
+    const unsigned blocks = (unsigned)((rows + kRowWarps - 1) / kRowWarps);
+    VRL_DISPATCH_VPL(d / 8, adaln_fwd_warp_kernel<VPL><<<blocks, kRowWarps * 32, 0, stream>>>(
+        reinterpret_cast<const bf16*>(x.data_ptr()), reinterpret_cast<const bf16*>(shift.data_ptr()),
+        reinterpret_cast<const bf16*>(scale.data_ptr()), reinterpret_cast<bf16*>(y.data_ptr()),
+        mean.data_ptr<float>(), rstd.data_ptr<float>(), rows, s, d, (float)eps, shift.stride(0),
+        scale.stride(0)));
+    C10_CUDA_KERNEL_LAUNCH_CHECK();
+    return {y, mean, rstd};
+  }
+  adaln_fwd_kernel<<<b * s, kNormThreads, 0, stream>>>(
       reinterpret_cast<const bf16*>(x.data_ptr()), reinterpret_cast<const bf16*>(shift.data_ptr()),
       reinterpret_cast<const bf16*>(scale.data_ptr()), reinterpret_cast<bf16*>(y.data_ptr()),
       mean.data_ptr<float>(), rstd.data_ptr<float>(), s, d, (float)eps, shift.stride(0),
@@ -182,6 +387,17 @@ std::vector<torch::Tensor> adaln_bwd(torch::Tensor gy, torch::Tensor x, torch::T
   auto gx = torch::empty_like(x);
   auto gshift = torch::zeros({b, d}, x.options().dtype(torch::kFloat32));
   auto gscale = torch::zeros({b, d}, x.options().dtype(torch::kFloat32));
+  if (d <= 2048) {
+    dim3 wgrid((s + kAdaBlockRows - 1) / kAdaBlockRows, b);
+    auto stream = at::cuda::getCurrentCUDAStream();
+    VRL_DISPATCH_VPL(d / 8, adaln_bwd_warp_kernel<VPL><<<wgrid, kRowWarps * 32, 2 * d * sizeof(float), stream>>>(
+        reinterpret_cast<const bf16*>(gy.data_ptr()), reinterpret_cast<const bf16*>(x.data_ptr()),
+        reinterpret_cast<const bf16*>(scale.data_ptr()), mean.data_ptr<float>(),
+        rstd.data_ptr<float>(), reinterpret_cast<bf16*>(gx.data_ptr()), gshift.data_ptr<float>(),
+        gscale.data_ptr<float>(), s, d, scale.stride(0)));
+    C10_CUDA_KERNEL_LAUNCH_CHECK();
+    return {gx, gshift, gscale};
+  }
   dim3 grid((s + kBwdRows - 1) / kBwdRows, b);
   adaln_bwd_kernel<<<grid, kNormThreads, 0, at::cuda::getCurrentCUDAStream()>>>(
       reinterpret_cast<const bf16*>(gy.data_ptr()), reinterpret_cast<const bf16*>(x.data_ptr()),
@@ -236,6 +452,15 @@ std::vector<torch::Tensor> rmsnorm_fwd(torch::Tensor x, torch::Tensor w, double 
   w = w.to(torch::kBFloat16).contiguous();
   auto y = torch::empty_like(x);
   auto rstd = torch::empty({rows}, x.options().dtype(torch::kFloat32));
+  if (d <= 2048) {
+    auto stream = at::cuda::getCurrentCUDAStream();
+    const unsigned blocks = (unsigned)((rows + kRowWarps - 1) / kRowWarps);
+    VRL_DISPATCH_VPL(d / 8, rmsnorm_fwd_warp_kernel<VPL><<<blocks, kRowWarps * 32, 0, stream>>>(
+        reinterpret_cast<const bf16*>(x.data_ptr()), reinterpret_cast<const bf16*>(w.data_ptr()),
+        reinterpret_cast<bf16*>(y.data_ptr()), rstd.data_ptr<float>(), rows, d, (float)eps));
+    C10_CUDA_KERNEL_LAUNCH_CHECK();
+    return {y, rstd};
+  }
   rmsnorm_fwd_kernel<<<(unsigned)rows, kNormThreads, 0, at::cuda::getCurrentCUDAStream()>>>(
       reinterpret_cast<const bf16*>(x.data_ptr()), reinterpret_cast<const bf16*>(w.data_ptr()),
       reinterpret_cast<bf16*>(y.data_ptr()), rstd.data_ptr<float>(), d, (float)eps);
@@ -320,23 +545,141 @@ std::vector<torch::Tensor> rmsnorm_bwd(torch::Tensor gy, torch::Tensor x, torch:
   return {gx, gw};
 }
 
+// ------------------------------------------------------------------ gated residual (adaLN-Zero)
+// out = residual + gate[sample] * y, and its backward: gy = g * gate, d(gate)[sample] = sum_s g * y
+// (d(residual) is g itself).  One warp per row; the per-sample column sums of the backward are
+// collected in shared memory per block and flushed once with global atomics.
+__global__ void __launch_bounds__(kRowWarps * 32)
+gate_residual_fwd_kernel(const bf16* __restrict__ y, const bf16* __restrict__ gate,
+                         const bf16* __restrict__ residual, bf16* __restrict__ out, int64_t rows,
+                         int rows_per_sample, int d, int64_t gate_ld) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * kRowWarps + warp;
+  if (row >= rows) return;
+  const int nvec = d / 8;
+  const bf16x8* yr = reinterpret_cast<const bf16x8*>(y + row * d);
+  const bf16x8* rr = reinterpret_cast<const bf16x8*>(residual + row * d);
+  const bf16x8* gr = reinterpret_cast<const bf16x8*>(gate + (row / rows_per_sample) * gate_ld);
+  bf16x8* orow = reinterpret_cast<bf16x8*>(out + row * d);
+  for (int i = lane; i < nvec; i += 32) {
+    float a[8], b[8], c[8], o[8];
+    unpack8(yr[i], a);
+    unpack8(gr[i], b);
+    unpack8(rr[i], c);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = c[j] + b[j] * a[j];
+    orow[i] = pack8(o);
+  }
+}
+
+constexpr int kGateBlockRows = 32;
+
+__global__ void __launch_bounds__(kRowWarps * 32)
+gate_residual_bwd_kernel(const bf16* __restrict__ g, const bf16* __restrict__ y,
+                         const bf16* __restrict__ gate, bf16* __restrict__ gy,
+                         float* __restrict__ ggate, int rows_per_sample, int d, int64_t gate_ld) {
+  extern __shared__ float col_acc[];         // [d]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int sample = blockIdx.y;
+  const int nvec = d / 8;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) col_acc[i] = 0.f;
+  __syncthreads();
+  const bf16x8* gt = reinterpret_cast<const bf16x8*>(gate + (int64_t)sample * gate_ld);
+  const int r_begin = blockIdx.x * kGateBlockRows;
+  for (int r = r_begin + warp; r < r_begin + kGateBlockRows && r < rows_per_sample; r += kRowWarps) {
+    const int64_t row = (int64_t)sample * rows_per_sample + r;
+    const bf16x8* gr = reinterpret_cast<const bf16x8*>(g + row * d);
+    const bf16x8* yr = reinterpret_cast<const bf16x8*>(y + row * d);
+    bf16x8* orow = reinterpret_cast<bf16x8*>(gy + row * d);
+    for (int i = lane; i < nvec; i += 32) {
+      float a[8], b[8], c[8], o[8];
+      unpack8(gr[i], a);
+      unpack8(yr[i], b);
+      unpack8(gt[i], c);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        o[j] = a[j] * c[j];
+        atomicAdd(&col_acc[i * 8 + j], a[j] * b[j]);
+      }
+      orow[i] = pack8(o);
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < d; i += blockDim.x) atomicAdd(ggate + (int64_t)sample * d + i, col_acc[i]);
+}
+
+torch::Tensor gate_residual_fwd(torch::Tensor y, torch::Tensor gate, torch::Tensor residual) {
+  TORCH_CHECK(y.is_cuda() && y.dim() == 3 && y.scalar_type() == torch::kBFloat16 && y.is_contiguous());
+  TORCH_CHECK(residual.scalar_type() == torch::kBFloat16 && residual.is_contiguous() &&
+              residual.sizes() == y.sizes());
+  const c10::cuda::CUDAGuard guard(y.device());
+  const int b = (int)y.size(0), s = (int)y.size(1), d = (int)y.size(2);
+  TORCH_CHECK(d % 8 == 0);
+  gate = strided_rows(gate, b, d);
+  auto out = torch::empty_like(y);
+  const int64_t rows = (int64_t)b * s;
+  if (rows == 0) return out;
+  gate_residual_fwd_kernel<<<(unsigned)((rows + kRowWarps - 1) / kRowWarps), kRowWarps * 32, 0,
+                             at::cuda::getCurrentCUDAStream()>>>(
+      reinterpret_cast<const bf16*>(y.data_ptr()), reinterpret_cast<const bf16*>(gate.data_ptr()),
+      reinterpret_cast<const bf16*>(residual.data_ptr()), reinterpret_cast<bf16*>(out.data_ptr()), rows, s,
+      d, gate.stride(0));
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return out;
+}
+
+std::vector<torch::Tensor> gate_residual_bwd(torch::Tensor g, torch::Tensor y, torch::Tensor gate) {
+  TORCH_CHECK(y.is_cuda() && y.dim() == 3 && y.scalar_type() == torch::kBFloat16 && y.is_contiguous());
+  const c10::cuda::CUDAGuard guard(y.device());
+  const int b = (int)y.size(0), s = (int)y.size(1), d = (int)y.size(2);
+  g = g.to(torch::kBFloat16).contiguous();
+  TORCH_CHECK(g.sizes() == y.sizes() && d % 8 == 0 && d <= 8192);
+  gate = strided_rows(gate, b, d);
+  auto gy = torch::empty_like(y);
+  auto ggate = torch::zeros({b, d}, y.options().dtype(torch::kFloat32));
+  if (b * s == 0) return {gy, ggate};
+  dim3 grid((s + kGateBlockRows - 1) / kGateBlockRows, b);
+  gate_residual_bwd_kernel<<<grid, kRowWarps * 32, d * sizeof(float), at::cuda::getCurrentCUDAStream()>>>(
+      reinterpret_cast<const bf16*>(g.data_ptr()), reinterpret_cast<const bf16*>(y.data_ptr()),
+      reinterpret_cast<const bf16*>(gate.data_ptr()), reinterpret_cast<bf16*>(gy.data_ptr()),
+      ggate.data_ptr<float>(), s, d, gate.stride(0));
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return {gy, ggate};
+}
+
 // ------------------------------------------------------------------------- QKV post-processing
-// qkv[b, s, which, h, :] -> out_which[b, h, s, :].  Norm modes: 0 none, 1 per head (weights of
+// qkv[b, s, which, h, :] -> out_which[b, seq_offset + s, h, :] of a token-major [B, S_total, H, Dh]
+// buffer (callers view it as [B, H, S_total, Dh] through strides; two streams of a joint-attention
+// block write into one buffer at different offsets, so no concatenation copy is needed).  Norm modes: 0 none, 1 per head (weights of
 // Dh elements), 2 full width (weights of H*Dh elements).  rstd layout: [b, s, 2, H] (mode 1)
 // or [b, s, 2] (mode 2).  Rotary tables are [S, Dh/2]; pairs are (2i, 2i+1).
-constexpr int kQkvMaxVec = 8;      // 3*H*Dh/8 <= 8*256  => H*Dh <= 5461
+constexpr int kQkvVecLimit = 8;     // vectors per thread: 3*H*Dh/8 <= 8*256  => H*Dh <= 5461
+
+// Instantiates the kernel for the number of 8-element vectors each thread really owns, so the
+// per-thread arrays (and the register count) match the model width.
+#define VRL_DISPATCH_QKV(nvec, ...)                                              \
+  do {                                                                           \
+    const int per_thread = ((nvec) + kNormThreads - 1) / kNormThreads;           \
+    if (per_thread <= 1) { constexpr int T = 1; __VA_ARGS__; }                   \
+    else if (per_thread <= 2) { constexpr int T = 2; __VA_ARGS__; }              \
+    else if (per_thread <= 3) { constexpr int T = 3; __VA_ARGS__; }              \
+    else if (per_thread <= 4) { constexpr int T = 4; __VA_ARGS__; }              \
+    else if (per_thread <= 6) { constexpr int T = 6; __VA_ARGS__; }              \
+    else { constexpr int T = 8; __VA_ARGS__; }                                   \
+  } while (0)
 
 __device__ __forceinline__ float group_sum(float v, int lanes) {
   for (int o = lanes >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
   return v;
 }
 
+template <int kQkvMaxVec>
 __global__ void __launch_bounds__(kNormThreads)
 qkv_prepare_fwd_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ qw,
                        const bf16* __restrict__ kw, const float* __restrict__ cosT,
                        const float* __restrict__ sinT, bf16* __restrict__ q, bf16* __restrict__ k,
                        bf16* __restrict__ v, float* __restrict__ rstd_o, int seq, int heads,
-                       int dh, int mode, float eps) {
+                       int dh, int mode, float eps, int seq_total, int seq_offset) {
   __shared__ float red[32];
   const int64_t tok = blockIdx.x;
   const int b = (int)(tok / seq), s = (int)(tok % seq);
@@ -403,7 +746,9 @@ qkv_prepare_fwd_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ qw
       }
     }
     bf16* dst = which == 0 ? q : (which == 1 ? k : v);
-    *reinterpret_cast<bf16x8*>(dst + (((int64_t)b * heads + h) * seq + s) * dh + j8 * 8) = pack8(o);
+    // token-major destination [B, seq_total, H, Dh]: one token's heads are contiguous
+    *reinterpret_cast<bf16x8*>(dst + (((int64_t)b * seq_total + seq_offset + s) * heads + h) * dh + j8 * 8) =
+        pack8(o);
   }
 }
 
@@ -411,14 +756,16 @@ std::vector<torch::Tensor> qkv_prepare_fwd(torch::Tensor qkv, c10::optional<torc
                                            c10::optional<torch::Tensor> kw,
                                            c10::optional<torch::Tensor> cos,
                                            c10::optional<torch::Tensor> sin, int64_t heads,
-                                           double eps) {
+                                           double eps, c10::optional<torch::Tensor> dst_q,
+                                           c10::optional<torch::Tensor> dst_k,
+                                           c10::optional<torch::Tensor> dst_v, int64_t seq_offset) {
   TORCH_CHECK(qkv.is_cuda() && qkv.dim() == 3 && qkv.scalar_type() == torch::kBFloat16 &&
               qkv.is_contiguous());
   const c10::cuda::CUDAGuard guard(qkv.device());
   const int b = (int)qkv.size(0), s = (int)qkv.size(1);
   const int dmodel = (int)(qkv.size(2) / 3), dh = dmodel / (int)heads;
   TORCH_CHECK(dh % 8 == 0 && kNormThreads % (dh / 8) == 0 && (dh / 8) <= 32, "unsupported head dim");
-  TORCH_CHECK(3 * dmodel / 8 <= kQkvMaxVec * kNormThreads, "model width too large for qkv_prepare");
+  TORCH_CHECK(3 * dmodel / 8 <= kQkvVecLimit * kNormThreads, "model width too large for qkv_prepare");
   int mode = 0;
   torch::Tensor qwc, kwc;
   if (qw.has_value()) {
@@ -434,24 +781,41 @@ std::vector<torch::Tensor> qkv_prepare_fwd(torch::Tensor qkv, c10::optional<torc
     TORCH_CHECK(cosc.size(0) == s && cosc.size(1) == dh / 2);
   }
   auto opt = qkv.options();
-  auto q = torch::empty({b, (int64_t)heads, s, dh}, opt);
-  auto k = torch::empty_like(q);
-  auto v = torch::empty_like(q);
+  torch::Tensor q, k, v;
+  int64_t seq_total = s;
+  if (dst_q.has_value()) {
+    q = *dst_q; k = *dst_k; v = *dst_v;
+    for (const auto& t : {q, k, v})
+      TORCH_CHECK(t.is_cuda() && t.scalar_type() == torch::kBFloat16 && t.dim() == 4 && t.is_contiguous() &&
+                  t.size(0) == b && t.size(2) == heads && t.size(3) == dh,
+                  "qkv_prepare: destinations must be contiguous [B, S_total, H, Dh]");
+    seq_total = q.size(1);
+    TORCH_CHECK(k.size(1) == seq_total && v.size(1) == seq_total && seq_offset >= 0 &&
+                seq_offset + s <= seq_total, "qkv_prepare: sequence window out of range");
+  } else {
+    TORCH_CHECK(seq_offset == 0);
+    q = torch::empty({b, s, (int64_t)heads, dh}, opt);
+    k = torch::empty_like(q);
+    v = torch::empty_like(q);
+  }
   auto rstd = torch::empty({(int64_t)b * s * 2 * (mode == 1 ? heads : 1)},
                            opt.dtype(torch::kFloat32));
-  qkv_prepare_fwd_kernel<<<b * s, kNormThreads, 0, at::cuda::getCurrentCUDAStream()>>>(
+  auto stream = at::cuda::getCurrentCUDAStream();
+  VRL_DISPATCH_QKV(3 * dmodel / 8, qkv_prepare_fwd_kernel<T><<<b * s, kNormThreads, 0, stream>>>(
       reinterpret_cast<const bf16*>(qkv.data_ptr()),
       mode ? reinterpret_cast<const bf16*>(qwc.data_ptr()) : nullptr,
       mode ? reinterpret_cast<const bf16*>(kwc.data_ptr()) : nullptr,
       cos.has_value() ? cosc.data_ptr<float>() : nullptr,
       cos.has_value() ? sinc.data_ptr<float>() : nullptr, reinterpret_cast<bf16*>(q.data_ptr()),
       reinterpret_cast<bf16*>(k.data_ptr()), reinterpret_cast<bf16*>(v.data_ptr()),
-      rstd.data_ptr<float>(), s, (int)heads, dh, mode, (float)eps);
+      rstd.data_ptr<float>(), s, (int)heads, dh, mode, (float)eps, (int)seq_total, (int)seq_offset));
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
   return {q, k, v, rstd};
 }
 
 constexpr int kQkvBwdTokens = 16;
 
+template <int kQkvMaxVec>
 __global__ void __launch_bounds__(kNormThreads)
 qkv_prepare_bwd_kernel(const bf16* __restrict__ gq, const bf16* __restrict__ gk,
                        const bf16* __restrict__ gv, const bf16* __restrict__ qkv,
@@ -459,7 +823,9 @@ qkv_prepare_bwd_kernel(const bf16* __restrict__ gq, const bf16* __restrict__ gk,
                        const float* __restrict__ cosT, const float* __restrict__ sinT,
                        const float* __restrict__ rstd, bf16* __restrict__ gqkv,
                        float* __restrict__ gqw, float* __restrict__ gkw, int64_t tokens, int seq,
-                       int heads, int dh, int mode) {
+                       int heads, int dh, int mode, int seq_offset, int64_t gq_sb, int64_t gq_sh,
+                       int64_t gq_ss, int64_t gk_sb, int64_t gk_sh, int64_t gk_ss, int64_t gv_sb,
+                       int64_t gv_sh, int64_t gv_ss) {
   extern __shared__ float wacc[];          // [2][wlen] parameter-gradient accumulators
   __shared__ float red[32];
   const int dmodel = heads * dh;
@@ -491,8 +857,11 @@ qkv_prepare_bwd_kernel(const bf16* __restrict__ gq, const bf16* __restrict__ gk,
       const int rem = i - which * vec_per_which;
       const int h = rem / vec_per_head, j8 = rem - h * vec_per_head;
       const bf16* gsrc = which == 0 ? gq : (which == 1 ? gk : gv);
+      const int64_t sb = which == 0 ? gq_sb : (which == 1 ? gk_sb : gv_sb);
+      const int64_t sh = which == 0 ? gq_sh : (which == 1 ? gk_sh : gv_sh);
+      const int64_t ss = which == 0 ? gq_ss : (which == 1 ? gk_ss : gv_ss);
       float g[8];
-      unpack8(*reinterpret_cast<const bf16x8*>(gsrc + (((int64_t)b * heads + h) * seq + s) * dh + j8 * 8), g);
+      unpack8(*reinterpret_cast<const bf16x8*>(gsrc + b * sb + h * sh + (int64_t)(seq_offset + s) * ss + j8 * 8), g);
       if (which == 2) {
         dst[i] = pack8(g);
         continue;
@@ -575,13 +944,22 @@ std::vector<torch::Tensor> qkv_prepare_bwd(torch::Tensor gq, torch::Tensor gk, t
                                            c10::optional<torch::Tensor> kw,
                                            c10::optional<torch::Tensor> cos,
                                            c10::optional<torch::Tensor> sin, torch::Tensor rstd,
-                                           int64_t heads) {
+                                           int64_t heads, int64_t seq_offset) {
   const c10::cuda::CUDAGuard guard(qkv.device());
   const int b = (int)qkv.size(0), s = (int)qkv.size(1);
   const int dmodel = (int)(qkv.size(2) / 3), dh = dmodel / (int)heads;
-  gq = gq.to(torch::kBFloat16).contiguous();
-  gk = gk.to(torch::kBFloat16).contiguous();
-  gv = gv.to(torch::kBFloat16).contiguous();
+  // gradients arrive as [B, H, S_total, Dh] views with arbitrary (16-byte aligned) strides
+  auto usable = [&](torch::Tensor& g) {
+    TORCH_CHECK(g.dim() == 4 && g.size(0) == b && g.size(1) == heads && g.size(3) == dh &&
+                seq_offset + s <= g.size(2), "qkv_prepare_bwd: gradient shape");
+    const bool ok = g.scalar_type() == torch::kBFloat16 && g.stride(3) == 1 && g.stride(0) % 8 == 0 &&
+                    g.stride(1) % 8 == 0 && g.stride(2) % 8 == 0 &&
+                    reinterpret_cast<uintptr_t>(g.data_ptr()) % 16 == 0;
+    if (!ok) g = g.to(torch::kBFloat16).contiguous();
+  };
+  usable(gq);
+  usable(gk);
+  usable(gv);
   int mode = 0;
   torch::Tensor qwc, kwc;
   if (qw.has_value()) {
@@ -600,8 +978,9 @@ std::vector<torch::Tensor> qkv_prepare_bwd(torch::Tensor gq, torch::Tensor gk, t
   auto gkw = torch::zeros_like(gqw);
   const int64_t tokens = (int64_t)b * s;
   const size_t smem = mode ? sizeof(float) * 2 * wlen : 0;
-  qkv_prepare_bwd_kernel<<<(unsigned)((tokens + kQkvBwdTokens - 1) / kQkvBwdTokens), kNormThreads,
-                           smem, at::cuda::getCurrentCUDAStream()>>>(
+  auto stream = at::cuda::getCurrentCUDAStream();
+  const unsigned blocks = (unsigned)((tokens + kQkvBwdTokens - 1) / kQkvBwdTokens);
+  VRL_DISPATCH_QKV(3 * dmodel / 8, qkv_prepare_bwd_kernel<T><<<blocks, kNormThreads, smem, stream>>>(
       reinterpret_cast<const bf16*>(gq.data_ptr()), reinterpret_cast<const bf16*>(gk.data_ptr()),
       reinterpret_cast<const bf16*>(gv.data_ptr()), reinterpret_cast<const bf16*>(qkv.data_ptr()),
       mode ? reinterpret_cast<const bf16*>(qwc.data_ptr()) : nullptr,
@@ -609,7 +988,9 @@ std::vector<torch::Tensor> qkv_prepare_bwd(torch::Tensor gq, torch::Tensor gk, t
       cos.has_value() ? cosc.data_ptr<float>() : nullptr,
       cos.has_value() ? sinc.data_ptr<float>() : nullptr, rstd.data_ptr<float>(),
       reinterpret_cast<bf16*>(gqkv.data_ptr()), gqw.data_ptr<float>(), gkw.data_ptr<float>(),
-      tokens, s, (int)heads, dh, mode);
+      tokens, s, (int)heads, dh, mode, (int)seq_offset, gq.stride(0), gq.stride(1), gq.stride(2),
+      gk.stride(0), gk.stride(1), gk.stride(2), gv.stride(0), gv.stride(1), gv.stride(2)));
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
   return {gqkv, gqw, gkw};
 }
 

@@ -39,6 +39,8 @@ std::vector<torch::Tensor> adaln_fwd(torch::Tensor x, torch::Tensor shift, torch
                                      double eps);
 std::vector<torch::Tensor> adaln_bwd(torch::Tensor gy, torch::Tensor x, torch::Tensor scale,
                                      torch::Tensor mean, torch::Tensor rstd);
+torch::Tensor gate_residual_fwd(torch::Tensor y, torch::Tensor gate, torch::Tensor residual);
+std::vector<torch::Tensor> gate_residual_bwd(torch::Tensor g, torch::Tensor y, torch::Tensor gate);
 std::vector<torch::Tensor> rmsnorm_fwd(torch::Tensor x, torch::Tensor w, double eps);
 std::vector<torch::Tensor> rmsnorm_bwd(torch::Tensor gy, torch::Tensor x, torch::Tensor w,
                                        torch::Tensor rstd);
@@ -46,13 +48,15 @@ std::vector<torch::Tensor> qkv_prepare_fwd(torch::Tensor qkv, c10::optional<torc
                                            c10::optional<torch::Tensor> kw,
                                            c10::optional<torch::Tensor> cos,
                                            c10::optional<torch::Tensor> sin, int64_t heads,
-                                           double eps);
+                                           double eps, c10::optional<torch::Tensor> dst_q,
+                                           c10::optional<torch::Tensor> dst_k,
+                                           c10::optional<torch::Tensor> dst_v, int64_t seq_offset);
 std::vector<torch::Tensor> qkv_prepare_bwd(torch::Tensor gq, torch::Tensor gk, torch::Tensor gv,
                                            torch::Tensor qkv, c10::optional<torch::Tensor> qw,
                                            c10::optional<torch::Tensor> kw,
                                            c10::optional<torch::Tensor> cos,
                                            c10::optional<torch::Tensor> sin, torch::Tensor rstd,
-                                           int64_t heads);
+                                           int64_t heads, int64_t seq_offset);
 
 // collective.cu
 torch::Tensor rs_sum_slice(torch::Tensor peers, torch::Tensor out, int64_t lo, int64_t n,
@@ -90,6 +94,10 @@ std::vector<torch::Tensor> moe_gate_topk(torch::Tensor logits, int64_t topk);
 std::vector<torch::Tensor> moe_permute(torch::Tensor experts, int64_t num_experts);
 torch::Tensor moe_gather_rows(torch::Tensor x, torch::Tensor perm, int64_t topk);
 torch::Tensor moe_combine(torch::Tensor yp, torch::Tensor inv, torch::Tensor weights);
+
+// attention_sm100.cu
+std::vector<torch::Tensor> flash_attn_fwd(torch::Tensor q, torch::Tensor k, torch::Tensor v, double scale);
+int64_t flash_attn_last_status();
 
 // gemm_sm100.cu
 torch::Tensor gemm_bf16(torch::Tensor a, torch::Tensor b, c10::optional<torch::Tensor> bias,

@@ -23,7 +23,7 @@ from visionrl_b200.models.nn.layers import (
     Linear, LoRALinear, MLP, TimestepEmbedder, merge_heads, sdpa,
 )
 from visionrl_b200.ops import norm as norm_ops
-from visionrl_b200.ops.qkv import qkv_prepare
+from visionrl_b200.ops.qkv import joint_qkv_prepare, qkv_prepare
 
 
 @dataclass
@@ -97,10 +97,12 @@ class JointBlock(nn.Module):
         sx = x.shape[1]
         mx = self.mod_x(temb_act).chunk(6, dim=-1)
         mc = self.mod_c(temb_act).chunk(2 if self.context_pre_only else 6, dim=-1)
-        qx, kx, vx = self.attn_x.project(norm_ops.adaln_layernorm(x, mx[0], mx[1]))
-        qc, kc, vc = self.attn_c.project(norm_ops.adaln_layernorm(c, mc[0], mc[1]))
-        o = sdpa(torch.cat([qx, qc], 2), torch.cat([kx, kc], 2), torch.cat([vx, vc], 2))
-        o = merge_heads(o)
+        ax, ac = self.attn_x, self.attn_c
+        q, k, v = joint_qkv_prepare(
+            ax.qkv(norm_ops.adaln_layernorm(x, mx[0], mx[1])),
+            ac.qkv(norm_ops.adaln_layernorm(c, mc[0], mc[1])),
+            ax.heads, (ax.q_norm, ax.k_norm), (ac.q_norm, ac.k_norm))
+        o = merge_heads(sdpa(q, k, v))
         x = self.attn_x.out(o[:, :sx], gate=mx[2], residual=x)
         x = self.mlp_x(norm_ops.adaln_layernorm(x, mx[3], mx[4]), gate=mx[5], residual=x)
         if self.context_pre_only:

@@ -22,37 +22,34 @@ def attention_reference(q, k, v, causal: bool = False, scale: float | None = Non
     return torch.matmul(torch.softmax(s, dim=-1), v.float()).to(q.dtype)
 
 
-class _FlashFn(torch.autograd.Function):
-    @staticmethod
-    def forward(ctx, q, k, v, scale):
-        from visionrl_b200.ops import _ext
-
-        o, lse = _ext.load().flash_attn_fwd(q.contiguous(), k.contiguous(), v.contiguous(),
-                                            float(scale))
-        ctx.save_for_backward(q, k, v, o, lse)
-        ctx.scale = scale
-        return o
-
-    @staticmethod
-    def backward(ctx, go):
-        from visionrl_b200.ops import _ext
-
-        q, k, v, o, lse = ctx.saved_tensors
-        gq, gk, gv = _ext.load().flash_attn_bwd(go.contiguous(), q, k, v, o, lse, float(ctx.scale))
-        return gq, gk, gv, None
-
-
-def _native_ok(q, k) -> bool:
+def _native_ok(q, k, v) -> bool:
     from visionrl_b200.ops import _ext
 
-    return (q.is_cuda and q.dtype == torch.bfloat16 and q.shape[-1] in (64, 128)
+    return (q.is_cuda and q.dtype == torch.bfloat16 and k.dtype == torch.bfloat16
+            and q.dim() == 4 and q.shape[-1] in (64, 128) and k.shape[-1] == q.shape[-1]
+            and v.shape == k.shape and q.shape[0] * q.shape[1] <= 65535
             and _ext.kernels_enabled() and _ext.has("flash_attn_fwd"))
 
 
+def flash_attention_forward(q, k, v, scale: float):
+    """tcgen05 forward kernel: returns ``(out, lse)`` with ``lse[B, H, S]`` in natural log."""
+    from visionrl_b200.ops import _ext
+
+    out, lse = _ext.load().flash_attn_fwd(q, k, v, float(scale))
+    return out, lse
+
+
 def attention(q, k, v, causal: bool = False, scale: float | None = None):
+    """Bidirectional (or causal) attention over ``[B, H, S, D]``.
+
+    Calls that need no gradient (rollout sampling, frozen-reference passes, reward towers) run
+    the hand-written sm_100a forward kernel; differentiable calls use the library's fused
+    forward/backward pair until the tcgen05 backward lands.
+    """
     scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
-    if not causal and _native_ok(q, k):
-        return _FlashFn.apply(q, k, v, scale)
+    needs_grad = torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad)
+    if not causal and not needs_grad and _native_ok(q, k, v):
+        return flash_attention_forward(q, k, v, scale)[0]
     if q.is_cuda:
         return F.scaled_dot_product_attention(q, k, v, is_causal=causal, scale=scale)
     return attention_reference(q, k, v, causal, scale)

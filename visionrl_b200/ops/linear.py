@@ -35,7 +35,7 @@ def linear_epilogue(y, act=None, gate=None, residual=None):
     elif act == "silu":
         y = F.silu(y)
     if gate is not None:
-        y = residual + (gate.unsqueeze(1) if y.dim() == 3 else gate) * y
+        y = gate_residual(y, gate, residual)
     return y
 
 
@@ -101,6 +101,39 @@ class _LinearFn(torch.autograd.Function):
         return gx, gw, gb
 
 
+class _GateResidualFn(torch.autograd.Function):
+    """``residual + gate[:, None, :] * y`` for ``[B, S, D]`` activations and a ``[B, D]`` gate."""
+
+    @staticmethod
+    def forward(ctx, y, gate, residual):
+        from visionrl_b200.ops import _ext
+
+        y = y.contiguous()
+        out = _ext.load().gate_residual_fwd(y, gate, residual.contiguous())
+        ctx.save_for_backward(y, gate)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        from visionrl_b200.ops import _ext
+
+        y, gate = ctx.saved_tensors
+        gy, ggate = _ext.load().gate_residual_bwd(g, y, gate)
+        return gy, ggate.to(gate.dtype), g
+
+
+def gate_residual(y, gate, residual):
+    """Differentiable adaLN-Zero gate: one fused kernel each way on bf16 CUDA tensors."""
+    from visionrl_b200.ops import _ext
+
+    if (y.is_cuda and y.dim() == 3 and gate.dim() == 2 and y.dtype == torch.bfloat16
+            and gate.dtype == torch.bfloat16 and residual.dtype == torch.bfloat16
+            and y.shape[-1] % 8 == 0 and y.shape[-1] <= 8192 and _ext.kernels_enabled()
+            and _ext.has("gate_residual_fwd")):
+        return _GateResidualFn.apply(y, gate, residual)
+    return residual + (gate.unsqueeze(1) if y.dim() == 3 else gate) * y
+
+
 def linear(x, w, bias=None, act=None, gate=None, residual=None):
     """Differentiable linear with optional fused epilogue (fused only without grad)."""
     if not _use_kernel(x, w):
@@ -126,5 +159,5 @@ def linear(x, w, bias=None, act=None, gate=None, residual=None):
     elif act == "silu":
         y = F.silu(y)
     if gate is not None:
-        y = residual + (gate.unsqueeze(1) if y.dim() == 3 else gate) * y
+        y = gate_residual(y, gate, residual)
     return y
