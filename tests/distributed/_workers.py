@@ -57,14 +57,14 @@ def sharded_adamw_matches_single(rank, world, port, backend, collectives, out):
         mean = [sum(gs[i].to(dtype).float() for gs in grads_all) / world
                 for i in range(len(grads_all[0]))]
         for p, g in zip(ref.parameters(), mean):
-            p.grad = g.clone()
+            p.grad = g.clone().to(p.device)
         ref_norm = torch.nn.utils.clip_grad_norm_(ref.parameters(), 1.0)
         ref_opt.step()
         tol = 3e-2 if dtype == torch.bfloat16 else 1e-5
         assert abs(float(ref_norm) - norms[-1]) <= tol * max(1.0, float(ref_norm)), (ref_norm, norm)
     if dev.type == "cuda":
         torch.cuda.synchronize()
-    err = max((a.detach().float().cpu() - b.detach()).abs().max().item()
+    err = max((a.detach().float().cpu() - b.detach().float().cpu()).abs().max().item()
               for a, b in zip(net.parameters(), ref.parameters()))
     # every rank must hold identical parameters after the all-gather
     flat = torch.cat([p.detach().float().reshape(-1) for p in net.parameters()]).to(dev)

@@ -9,7 +9,10 @@
 //               maximum, then exponentials), probabilities written as bf16 into a 128-byte-swizzled
 //               shared tile that is the A operand of P V; the running output lives in registers and
 //               absorbs each P V partial product from TMEM with the usual rescale.
-// TMEM columns: S0, S1 (128 each), then O0, O1 (D each).  Every wait is bounded; on expiry the
+// TMEM columns: the score buffers (128 each), then O0, O1 (D each).  Head dimension 128 double-buffers
+// the scores (512 columns, one CTA per SM); head dimension 64 keeps one score buffer (256 columns)
+// so that two CTAs share an SM and overlap each other's softmax and MMA phases.  Every wait is
+// bounded; on expiry the
 // role records a status code, raises the CTA's abort flag and all roles fall through to the
 // common exit where the TMEM is released.
 #include <ATen/cuda/CUDAContext.h>
@@ -32,16 +35,19 @@ constexpr int kTile = 128;                 // query rows per CTA and keys per st
 constexpr int kThreads = 192;
 constexpr uint32_t kBlockBytes = kTile * 128;   // one 64-column swizzle block of a 128-row tile
 constexpr uint32_t kPBytes = 2 * kBlockBytes;
-constexpr uint32_t kTmemCols = 512;
 
-enum Status : int { kOk = 0, kTimeoutProducer = 11, kTimeoutMma = 12, kTimeoutSoftmax = 13 };
+enum Status : int { kOk = 0, kTimeoutProducer = 11, kTimeoutMma = 12, kTimeoutSoftmax = 13,
+                    kMisalignedSmem = 14 };
 
 template <int D>
 struct Cfg {
   static constexpr int kDBlocks = D / 64;
   static constexpr uint32_t kTileBytes = kDBlocks * kBlockBytes;      // Q, K or V tile
-  static constexpr uint32_t kSmemBytes = 5 * kTileBytes + kPBytes + 1024 + 256;
-  static constexpr uint32_t kOCol = 2 * kTile;                        // first O column in TMEM
+  static constexpr uint32_t kSmemBytes = 5 * kTileBytes + kPBytes + 256;
+  static constexpr int kSBufs = D == 64 ? 1 : 2;                      // score buffers in TMEM
+  static constexpr uint32_t kOCol = kSBufs * kTile;                   // first O column in TMEM
+  static constexpr uint32_t kTmemCols = kOCol + 2 * D;                // 256 or 512
+  static constexpr int kCtasPerSm = D == 64 ? 2 : 1;
 };
 
 struct Params {
@@ -54,13 +60,15 @@ struct Params {
 };
 
 template <int D>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, Cfg<D>::kCtasPerSm)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                  const __grid_constant__ CUtensorMap map_v, const Params p) {
   using C = Cfg<D>;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
-                                             ~static_cast<uintptr_t>(1023));
+  extern __shared__ __align__(1024) uint8_t smem[];
+  if ((smem_u32(smem) & 1023u) != 0u) {          // the swizzled tiles need 1024-byte alignment
+    if (threadIdx.x == 0) atomicExch(p.status, kMisalignedSmem);
+    return;
+  }
   uint8_t* sq = smem;
   uint8_t* sk = sq + C::kTileBytes;            // [2]
   uint8_t* sv = sk + 2 * C::kTileBytes;        // [2]
@@ -94,7 +102,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     mbar_fence_init();
     fence_async_smem();
   }
-  if (warp == 1) tmem_alloc(tmem_slot, kTmemCols);
+  if (warp == 1) tmem_alloc(tmem_slot, C::kTmemCols);
   tmem_fence_before();
   __syncthreads();
   tmem_fence_after();
@@ -138,6 +146,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     tmem_fence_after();
     auto issue_qk = [&](int j) -> bool {
       const int s = j & 1;
+      const int sbuf = j % C::kSBufs;
       if (!mbar_wait(&k_full[s], (j >> 1) & 1u, abort_flag)) return false;
       tmem_fence_after();
       const uint32_t qa = smem_u32(sq), ka = smem_u32(sk + s * C::kTileBytes);
@@ -145,16 +154,19 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       for (int c = 0; c < C::kDBlocks; ++c)
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
-          umma_bf16(tmem_base + s * kTile, make_desc(qa + c * kBlockBytes + kk * 32, 16, 1024),
+          umma_bf16(tmem_base + sbuf * kTile, make_desc(qa + c * kBlockBytes + kk * 32, 16, 1024),
                     make_desc(ka + c * kBlockBytes + kk * 32, 16, 1024), idesc_qk, (c | kk) ? 1u : 0u);
       umma_commit(&k_empty[s]);
-      umma_commit(&s_full[s]);
+      umma_commit(&s_full[sbuf]);
       return true;
     };
     if (ok) ok = issue_qk(0);
     for (int j = 0; j < n_tiles && ok; ++j) {
-      if (j + 1 < n_tiles && !issue_qk(j + 1)) { ok = false; break; }
+      // with two score buffers the next Q K^T runs while the softmax warps work on this tile;
+      // with one it has to wait until they have consumed the scores (signalled with P)
+      if (C::kSBufs == 2 && j + 1 < n_tiles && !issue_qk(j + 1)) { ok = false; break; }
       if (!mbar_wait(p_full, j & 1u, abort_flag)) { ok = false; break; }
+      if (C::kSBufs == 1 && j + 1 < n_tiles && !issue_qk(j + 1)) { ok = false; break; }
       const int s = j & 1;
       if (!mbar_wait(&v_full[s], (j >> 1) & 1u, abort_flag)) { ok = false; break; }
       tmem_fence_after();
@@ -182,8 +194,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     for (int i = 0; i < D; ++i) o[i] = 0.f;
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
-      const int sb = j & 1;
-      ok = __all_sync(0xffffffffu, mbar_wait(&s_full[sb], (j >> 1) & 1u, abort_flag));
+      const int sb = j % C::kSBufs;
+      ok = __all_sync(0xffffffffu, mbar_wait(&s_full[sb], (j / C::kSBufs) & 1u, abort_flag));
       if (!ok) break;
       tmem_fence_after();
       const int valid = min(kTile, p.skv - j * kTile);
@@ -283,7 +295,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   __syncthreads();
   if (warp == 1) {
     tmem_fence_after();
-    tmem_dealloc(tmem_base, kTmemCols);
+    tmem_dealloc(tmem_base, C::kTmemCols);
   }
 }
 

@@ -90,10 +90,11 @@ adaln_fwd_warp_kernel(const bf16* __restrict__ x, const bf16* __restrict__ shift
   }
 }
 
-// Backward: a block of 8 warps covers `kAdaBlockRows` rows of ONE sample.  Per-column sums for
-// d(shift) and d(scale) go to shared memory with one shared atomic per element (lanes of a warp
-// hit distinct columns), then once per block to global memory.
-constexpr int kAdaBlockRows = 32;
+// Backward: a block of 8 warps covers `kAdaBlockRows` rows of ONE sample, 16 rows per warp.  Each
+// lane keeps the per-column sums for d(shift) and d(scale) of its own columns in registers over
+// those rows, adds them to a shared-memory copy once, and the block flushes that copy to global
+// memory with one atomic per column.
+constexpr int kAdaBlockRows = 128;
 
 template <int VPL>
 __global__ void __launch_bounds__(kRowWarps * 32)
@@ -108,6 +109,11 @@ adaln_bwd_warp_kernel(const bf16* __restrict__ gy, const bf16* __restrict__ x,
   for (int i = threadIdx.x; i < 2 * d; i += blockDim.x) col_acc[i] = 0.f;
   __syncthreads();
   const bf16x8* sc = reinterpret_cast<const bf16x8*>(scale + (int64_t)sample * scale_ld);
+  float acc_sh[VPL][8], acc_sc[VPL][8];
+#pragma unroll
+  for (int k = 0; k < VPL; ++k)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { acc_sh[k][j] = 0.f; acc_sc[k][j] = 0.f; }
   const int r_begin = blockIdx.x * kAdaBlockRows;
   for (int r = r_begin + warp; r < r_begin + kAdaBlockRows && r < rows_per_sample; r += kRowWarps) {
     const int64_t row = (int64_t)sample * rows_per_sample + r;
@@ -138,8 +144,8 @@ adaln_bwd_warp_kernel(const bf16* __restrict__ gy, const bf16* __restrict__ x,
           const float gp = gv[j] * (1.f + t[j]);
           s1 += gp;
           s2 += gp * xh;
-          atomicAdd(&col_acc[i * 8 + j], gv[j]);
-          atomicAdd(&col_acc[d + i * 8 + j], gv[j] * xh);
+          acc_sh[k][j] += gv[j];
+          acc_sc[k][j] += gv[j] * xh;
         }
       }
     }
@@ -160,6 +166,17 @@ adaln_bwd_warp_kernel(const bf16* __restrict__ gy, const bf16* __restrict__ x,
           o[j] = rs * (gv[j] * (1.f + t[j]) - m1 - xh * m2);
         }
         gxr[i] = pack8(o);
+      }
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < VPL; ++k) {
+    const int i = lane + k * 32;
+    if (i < nvec) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        atomicAdd(&col_acc[i * 8 + j], acc_sh[k][j]);
+        atomicAdd(&col_acc[d + i * 8 + j], acc_sc[k][j]);
       }
     }
   }
@@ -572,8 +589,9 @@ gate_residual_fwd_kernel(const bf16* __restrict__ y, const bf16* __restrict__ ga
   }
 }
 
-constexpr int kGateBlockRows = 32;
+constexpr int kGateBlockRows = 128;
 
+template <int VPL>
 __global__ void __launch_bounds__(kRowWarps * 32)
 gate_residual_bwd_kernel(const bf16* __restrict__ g, const bf16* __restrict__ y,
                          const bf16* __restrict__ gate, bf16* __restrict__ gy,
@@ -585,23 +603,48 @@ gate_residual_bwd_kernel(const bf16* __restrict__ g, const bf16* __restrict__ y,
   for (int i = threadIdx.x; i < d; i += blockDim.x) col_acc[i] = 0.f;
   __syncthreads();
   const bf16x8* gt = reinterpret_cast<const bf16x8*>(gate + (int64_t)sample * gate_ld);
+  float acc[VPL][8], gtv[VPL][8];
+#pragma unroll
+  for (int k = 0; k < VPL; ++k) {
+    const int i = lane + k * 32;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { acc[k][j] = 0.f; gtv[k][j] = 0.f; }
+    if (i < nvec) unpack8(gt[i], gtv[k]);
+  }
   const int r_begin = blockIdx.x * kGateBlockRows;
   for (int r = r_begin + warp; r < r_begin + kGateBlockRows && r < rows_per_sample; r += kRowWarps) {
     const int64_t row = (int64_t)sample * rows_per_sample + r;
     const bf16x8* gr = reinterpret_cast<const bf16x8*>(g + row * d);
     const bf16x8* yr = reinterpret_cast<const bf16x8*>(y + row * d);
     bf16x8* orow = reinterpret_cast<bf16x8*>(gy + row * d);
-    for (int i = lane; i < nvec; i += 32) {
-      float a[8], b[8], c[8], o[8];
-      unpack8(gr[i], a);
-      unpack8(yr[i], b);
-      unpack8(gt[i], c);
+    bf16x8 graw[VPL], yraw[VPL];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        o[j] = a[j] * c[j];
-        atomicAdd(&col_acc[i * 8 + j], a[j] * b[j]);
+    for (int k = 0; k < VPL; ++k) {
+      const int i = lane + k * 32;
+      if (i < nvec) { graw[k] = gr[i]; yraw[k] = yr[i]; }
+    }
+#pragma unroll
+    for (int k = 0; k < VPL; ++k) {
+      const int i = lane + k * 32;
+      if (i < nvec) {
+        float a[8], b[8], o[8];
+        unpack8(graw[k], a);
+        unpack8(yraw[k], b);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          o[j] = a[j] * gtv[k][j];
+          acc[k][j] += a[j] * b[j];
+        }
+        orow[i] = pack8(o);
       }
-      orow[i] = pack8(o);
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < VPL; ++k) {
+    const int i = lane + k * 32;
+    if (i < nvec) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) atomicAdd(&col_acc[i * 8 + j], acc[k][j]);
     }
   }
   __syncthreads();
@@ -633,16 +676,17 @@ std::vector<torch::Tensor> gate_residual_bwd(torch::Tensor g, torch::Tensor y, t
   const c10::cuda::CUDAGuard guard(y.device());
   const int b = (int)y.size(0), s = (int)y.size(1), d = (int)y.size(2);
   g = g.to(torch::kBFloat16).contiguous();
-  TORCH_CHECK(g.sizes() == y.sizes() && d % 8 == 0 && d <= 8192);
+  TORCH_CHECK(g.sizes() == y.sizes() && d % 8 == 0 && d <= 2048, "gate_residual_bwd: D <= 2048");
   gate = strided_rows(gate, b, d);
   auto gy = torch::empty_like(y);
   auto ggate = torch::zeros({b, d}, y.options().dtype(torch::kFloat32));
   if (b * s == 0) return {gy, ggate};
   dim3 grid((s + kGateBlockRows - 1) / kGateBlockRows, b);
-  gate_residual_bwd_kernel<<<grid, kRowWarps * 32, d * sizeof(float), at::cuda::getCurrentCUDAStream()>>>(
+  auto stream = at::cuda::getCurrentCUDAStream();
+  VRL_DISPATCH_VPL(d / 8, gate_residual_bwd_kernel<VPL><<<grid, kRowWarps * 32, d * sizeof(float), stream>>>(
       reinterpret_cast<const bf16*>(g.data_ptr()), reinterpret_cast<const bf16*>(y.data_ptr()),
       reinterpret_cast<const bf16*>(gate.data_ptr()), reinterpret_cast<bf16*>(gy.data_ptr()),
-      ggate.data_ptr<float>(), s, d, gate.stride(0));
+      ggate.data_ptr<float>(), s, d, gate.stride(0)));
   C10_CUDA_KERNEL_LAUNCH_CHECK();
   return {gy, ggate};
 }

@@ -128,7 +128,7 @@ def gate_residual(y, gate, residual):
 
     if (y.is_cuda and y.dim() == 3 and gate.dim() == 2 and y.dtype == torch.bfloat16
             and gate.dtype == torch.bfloat16 and residual.dtype == torch.bfloat16
-            and y.shape[-1] % 8 == 0 and y.shape[-1] <= 8192 and _ext.kernels_enabled()
+            and y.shape[-1] % 8 == 0 and y.shape[-1] <= 2048 and _ext.kernels_enabled()
             and _ext.has("gate_residual_fwd")):
         return _GateResidualFn.apply(y, gate, residual)
     return residual + (gate.unsqueeze(1) if y.dim() == 3 else gate) * y
