@@ -586,3 +586,94 @@ def test_gate_residual_fused_forward_backward():
         res.append((out, y.grad, mod.grad, r.grad))
     for got, ref in zip(*res):
         assert _rel(got, ref) < 2e-2
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("shape", [(2, 128, 64, 48), (1, 256, 33, 17), (2, 512, 16, 16)])
+@pytest.mark.parametrize("apply_silu", [True, False])
+def test_groupnorm_nhwc_matches_fp32(shape, apply_silu):
+    from visionrl_b200.ops.norm import group_norm_silu
+
+    torch.manual_seed(13)
+    n, c, h, w = shape
+    norm = torch.nn.GroupNorm(32, c, eps=1e-6).cuda().bfloat16()
+    with torch.no_grad():
+        norm.weight.copy_(1 + 0.2 * torch.randn(c))
+        norm.bias.copy_(0.1 * torch.randn(c))
+    x = (torch.randn(n, c, h, w, device="cuda") * 2 + 0.5).bfloat16().contiguous(memory_format=torch.channels_last)
+    with torch.no_grad():
+        got = group_norm_silu(x, norm, apply_silu)
+    ref = torch.nn.functional.group_norm(x.float(), 32, norm.weight.float(), norm.bias.float(), 1e-6)
+    if apply_silu:
+        ref = torch.nn.functional.silu(ref)
+    assert got.is_contiguous(memory_format=torch.channels_last)
+    assert torch.allclose(got.float(), ref, atol=3e-2, rtol=3e-2)
+
+
+@pytest.mark.gpu
+def test_gelu_mlp_fused_epilogues_match_fp32():
+    from visionrl_b200.ops.linear import gelu_mlp
+
+    torch.manual_seed(14)
+    m, d, hid = 333, 256, 1024
+    res = []
+    for fused in (True, False):
+        gen = torch.Generator("cuda").manual_seed(2)
+        dt = torch.bfloat16 if fused else torch.float32
+        x = torch.randn(3, m // 3, d, device="cuda", generator=gen).to(dt).requires_grad_()
+        w1 = (torch.randn(hid, d, device="cuda", generator=gen) * 0.05).to(dt).requires_grad_()
+        b1 = (torch.randn(hid, device="cuda", generator=gen) * 0.1).to(dt).requires_grad_()
+        w2 = (torch.randn(d, hid, device="cuda", generator=gen) * 0.05).to(dt).requires_grad_()
+        b2 = (torch.randn(d, device="cuda", generator=gen) * 0.1).to(dt).requires_grad_()
+        if fused:
+            y = gelu_mlp(x, w1, b1, w2, b2)
+        else:
+            hpre = torch.nn.functional.linear(x, w1, b1)
+            y = torch.nn.functional.linear(torch.nn.functional.gelu(hpre, approximate="tanh"), w2, b2)
+        g = torch.randn(y.shape, device="cuda", generator=gen).to(dt)
+        y.backward(g)
+        res.append((y, x.grad, w1.grad, b1.grad, w2.grad, b2.grad))
+    for got, ref in zip(*res):
+        assert _rel(got, ref) < 3e-2
+
+
+@pytest.mark.gpu
+def test_gemm_dual_output_returns_pre_and_post_activation():
+    from visionrl_b200.ops import _ext
+
+    torch.manual_seed(15)
+    a = torch.randn(300, 192, device="cuda").bfloat16()
+    w = (torch.randn(200, 192, device="cuda") * 0.1).bfloat16()
+    b = torch.randn(200, device="cuda").bfloat16()
+    post, pre = _ext.load().gemm_bf16_dual(a, w, b, 1)
+    ref = a.float() @ w.float().t() + b.float()
+    assert torch.allclose(pre.float(), ref, atol=5e-2, rtol=2e-2)
+    assert torch.allclose(post.float(), torch.nn.functional.gelu(ref, approximate="tanh"), atol=5e-2, rtol=2e-2)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("int4", [False, True])
+def test_janus_graph_decode_matches_eager_decode(int4):
+    from visionrl_b200.models.families.janus_pro.policy import JanusProConfig, JanusProPolicy
+
+    arch = {"num_layers": 2, "hidden_size": 256, "num_heads": 2, "ffn_dim": 512, "vocab_size": 512,
+            "image_vocab_size": 1024, "codebook_dim": 8, "vq_base": 32, "vq_mults": (1, 2), "vq_blocks": 1}
+    cfg = JanusProConfig(model_path="", dtype="bfloat16", use_lora=True, lora_rank=4, lora_alpha=8,
+                         image_token_num=16, image_size=64, patch_size=16, random_init=True,
+                         int4_decode=int4, arch=arch)
+    policy = JanusProPolicy(cfg, device="cuda")
+    b, l_text = 3, 8
+    ids = torch.randint(0, 512, (2 * b, l_text), device="cuda")
+    mask = torch.ones(2 * b, l_text, dtype=torch.long, device="cuda")
+    mask[0, -2:] = 0
+    emb = policy.embed_text(ids)
+    outs = []
+    for graph in (True, False):
+        policy.decode_graph = graph
+        gen = torch.Generator(device="cpu").manual_seed(5)
+        tokens, logp = policy.sample_image_tokens(emb[:b], emb[b:], mask[:b], mask[b:], cfg_weight=3.0,
+                                                  temperature=0.9, image_token_num=16, generator=gen)
+        outs.append((tokens.clone(), logp.clone()))
+    assert torch.equal(outs[0][0], outs[1][0])
+    assert torch.equal(outs[0][1], outs[1][1])
+    assert outs[0][0].min() >= 0 and outs[0][0].max() < 1024 and torch.isfinite(outs[0][1]).all()

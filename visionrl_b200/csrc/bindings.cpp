@@ -61,8 +61,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("moe_permute", &vrl::moe_permute);
   m.def("moe_gather_rows", &vrl::moe_gather_rows);
   m.def("moe_combine", &vrl::moe_combine);
+  m.def("groupnorm_nhwc", &vrl::groupnorm_nhwc);
   m.def("flash_attn_fwd", &vrl::flash_attn_fwd);
   m.def("flash_attn_last_status", &vrl::flash_attn_last_status);
   m.def("gemm_bf16", &vrl::gemm_bf16);
+  m.def("gemm_bf16_dual", &vrl::gemm_bf16_dual);
   m.def("gemm_last_status", &vrl::gemm_last_status);
 }

@@ -56,7 +56,8 @@ struct Params {
   const __nv_bfloat16* residual;   // [M, N] or null
   int* status;
   int m, n, k;
-  int act;                         // 0 none, 1 gelu-tanh, 2 silu
+  int act;                         // 0 none, 1 gelu-tanh, 2 silu, 3 multiply by gelu'(residual)
+  int dual;                        // also store the pre-activation (acc + bias) through map_c2
   int rows_per_gate;
   int64_t gate_ld;                 // elements between consecutive gate rows
   int a_mn, b_mn;
@@ -207,7 +208,7 @@ __host__ __device__ constexpr uint32_t make_idesc(int a_mn, int b_mn) {
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                  const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_r,
-                 const Params p) {
+                 const __grid_constant__ CUtensorMap map_c2, const Params p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -361,6 +362,34 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         }
         tmem_ld_wait();
         if (!ok) break;
+        if (p.dual) {
+          // first output: the pre-activation values, kept for the backward pass of the activation
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            const int col = colbase + g * 8;
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[g * 8 + j]);
+            if (p.bias && col < p.n) {
+              float b[8];
+              unpack8(*reinterpret_cast<const bf16x8*>(p.bias + col), b);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v[j] += b[j];
+            }
+            const bf16x8 o = pack8(v);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(
+                             stage_row + ((uint32_t)(g ^ swz) << 4)),
+                         "r"(o.u.x), "r"(o.u.y), "r"(o.u.z), "r"(o.u.w)
+                         : "memory");
+          }
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(stage, &map_c2, colbase, row0);
+            tma_store_wait_read();
+          }
+          __syncwarp();
+        }
 #pragma unroll
         for (int g = 0; g < 8; ++g) {
           const int col = colbase + g * 8;
@@ -396,7 +425,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 #pragma unroll
               for (int j = 0; j < 8; ++j) rs[j] = 0.f;
             }
-            if (p.gate) {
+            if (p.act == 3) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v[j] *= gelu_tanh_grad(rs[j]);
+            } else if (p.gate) {
               float gt[8];
               if (col_ok) {
                 unpack8(*reinterpret_cast<const bf16x8*>(p.gate + gate_row * p.gate_ld + col), gt);
@@ -506,11 +538,38 @@ int64_t gemm_last_status() {
   return host;
 }
 
+static std::vector<torch::Tensor> gemm_impl(torch::Tensor a, torch::Tensor b,
+                                            c10::optional<torch::Tensor> bias,
+                                            c10::optional<torch::Tensor> gate,
+                                            c10::optional<torch::Tensor> residual, int64_t act,
+                                            int64_t rows_per_gate, bool a_mn_major, bool b_mn_major,
+                                            bool out_fp32, bool dual);
+
 torch::Tensor gemm_bf16(torch::Tensor a, torch::Tensor b, c10::optional<torch::Tensor> bias,
                         c10::optional<torch::Tensor> gate, c10::optional<torch::Tensor> residual,
                         int64_t act, int64_t rows_per_gate, bool a_mn_major, bool b_mn_major,
                         bool out_fp32) {
+  return gemm_impl(a, b, bias, gate, residual, act, rows_per_gate, a_mn_major, b_mn_major, out_fp32,
+                   false)[0];
+}
+
+// (activation(a b^T + bias), a b^T + bias): the second tensor is what the activation's backward needs.
+std::vector<torch::Tensor> gemm_bf16_dual(torch::Tensor a, torch::Tensor b,
+                                          c10::optional<torch::Tensor> bias, int64_t act) {
+  return gemm_impl(a, b, bias, c10::nullopt, c10::nullopt, act, 0, false, false, false, true);
+}
+
+static std::vector<torch::Tensor> gemm_impl(torch::Tensor a, torch::Tensor b,
+                                            c10::optional<torch::Tensor> bias,
+                                            c10::optional<torch::Tensor> gate,
+                                            c10::optional<torch::Tensor> residual, int64_t act,
+                                            int64_t rows_per_gate, bool a_mn_major, bool b_mn_major,
+                                            bool out_fp32, bool dual) {
   using namespace gemm;
+  TORCH_CHECK(act >= 0 && act <= 3, "gemm_bf16: unknown epilogue activation");
+  TORCH_CHECK(act != 3 || (residual.has_value() && !gate.has_value() && !out_fp32),
+              "gemm_bf16: the gelu-gradient epilogue needs the pre-activation as `residual`");
+  TORCH_CHECK(!dual || (!residual.has_value() && !out_fp32), "gemm_bf16: dual output excludes residual/fp32");
   TORCH_CHECK(a.is_cuda() && b.is_cuda() && a.dim() == 2 && b.dim() == 2);
   TORCH_CHECK(a.scalar_type() == torch::kBFloat16 && b.scalar_type() == torch::kBFloat16);
   TORCH_CHECK(a.stride(1) == 1 && b.stride(1) == 1, "gemm_bf16: innermost dimension must be contiguous");
@@ -533,7 +592,8 @@ torch::Tensor gemm_bf16(torch::Tensor a, torch::Tensor b, c10::optional<torch::T
   TORCH_CHECK(reinterpret_cast<uintptr_t>(a.data_ptr()) % 16 == 0 &&
               reinterpret_cast<uintptr_t>(b.data_ptr()) % 16 == 0, "gemm_bf16: 16-byte alignment");
   auto out = torch::empty({m, n}, a.options().dtype(out_fp32 ? torch::kFloat32 : torch::kBFloat16));
-  if (m == 0 || n == 0) return out;
+  torch::Tensor pre = dual ? torch::empty({m, n}, a.options()) : torch::Tensor();
+  if (m == 0 || n == 0) return {out, pre};
   TORCH_CHECK(k > 0, "gemm_bf16: empty contraction");
 
   CUtensorMap map_a = a_mn_major ? make_map(a.data_ptr(), m, k, a.stride(0), 64, BK)
@@ -573,6 +633,7 @@ torch::Tensor gemm_bf16(torch::Tensor a, torch::Tensor b, c10::optional<torch::T
   p.a_mn = a_mn_major ? 1 : 0;
   p.b_mn = b_mn_major ? 1 : 0;
   p.out_fp32 = out_fp32 ? 1 : 0;
+  p.dual = dual ? 1 : 0;
 
   static const bool attr_set = [] {
     C10_CUDA_CHECK(cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -586,10 +647,11 @@ torch::Tensor gemm_bf16(torch::Tensor a, torch::Tensor b, c10::optional<torch::T
   // output / residual maps: 64-column x 32-row boxes matching one epilogue warp's staging tile
   CUtensorMap map_c = out_fp32 ? map_a : make_map(out.data_ptr(), n, m, n, 64, 32);
   CUtensorMap map_r = (p.residual && !out_fp32) ? make_map(p.residual, n, m, n, 64, 32) : map_c;
+  CUtensorMap map_c2 = dual ? make_map(pre.data_ptr(), n, m, n, 64, 32) : map_c;
   gemm_bf16_kernel<<<grid, kThreads, kSmemBytes, at::cuda::getCurrentCUDAStream()>>>(map_a, map_b, map_c,
-                                                                                    map_r, p);
+                                                                                    map_r, map_c2, p);
   C10_CUDA_KERNEL_LAUNCH_CHECK();
-  return out;
+  return {out, pre};
 }
 
 }  // namespace vrl

@@ -95,6 +95,10 @@ std::vector<torch::Tensor> moe_permute(torch::Tensor experts, int64_t num_expert
 torch::Tensor moe_gather_rows(torch::Tensor x, torch::Tensor perm, int64_t topk);
 torch::Tensor moe_combine(torch::Tensor yp, torch::Tensor inv, torch::Tensor weights);
 
+// groupnorm.cu
+torch::Tensor groupnorm_nhwc(torch::Tensor x, torch::Tensor weight, torch::Tensor bias, int64_t groups,
+                             double eps, bool apply_silu);
+
 // attention_sm100.cu
 std::vector<torch::Tensor> flash_attn_fwd(torch::Tensor q, torch::Tensor k, torch::Tensor v, double scale);
 int64_t flash_attn_last_status();
@@ -104,6 +108,8 @@ torch::Tensor gemm_bf16(torch::Tensor a, torch::Tensor b, c10::optional<torch::T
                         c10::optional<torch::Tensor> gate, c10::optional<torch::Tensor> residual,
                         int64_t act, int64_t rows_per_gate, bool a_mn_major, bool b_mn_major,
                         bool out_fp32);
+std::vector<torch::Tensor> gemm_bf16_dual(torch::Tensor a, torch::Tensor b,
+                                          c10::optional<torch::Tensor> bias, int64_t act);
 int64_t gemm_last_status();
 
 }  // namespace vrl

@@ -123,8 +123,27 @@ class DiffusionPolicy(nn.Module, ABC):
             raise ValueError(
                 f"load_trainable_state only accepts policy keys prefixed with {prefix!r}; got {bad}"
             )
-        return transformer.load_state_dict({k[len(prefix):]: v for k, v in state.items()},
-                                           strict=True)
+        sub = {k[len(prefix):]: v for k, v in state.items()}
+        own = transformer.state_dict()
+        unexpected = sorted(k for k in sub if k not in own)
+        if unexpected:
+            raise ValueError(f"load_trainable_state got keys the transformer does not have: {unexpected}")
+        if len(sub) == len(own):
+            return transformer.load_state_dict(sub, strict=True)
+        # a partial payload must at least cover everything that trains (adapters or full weights)
+        trainable = {n for n, p in transformer.named_parameters() if p.requires_grad}
+        missing = sorted(trainable - sub.keys())
+        if missing:
+            raise ValueError(f"load_trainable_state payload misses trainable keys: {missing[:8]}"
+                             f"{' ...' if len(missing) > 8 else ''}")
+        return transformer.load_state_dict(sub, strict=False)
+
+    def trainable_state_dict(self) -> dict[str, Any]:
+        """``transformer.``-prefixed tensors of exactly the parameters that train, in name order —
+        the payload of a trainer-to-rollout weight push."""
+        transformer = self._require_transformer()
+        return {f"transformer.{n}": p.detach() for n, p in sorted(transformer.named_parameters())
+                if p.requires_grad}
 
     # -- backend ownership ------------------------------------------------------------
     @classmethod

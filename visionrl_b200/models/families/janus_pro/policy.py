@@ -163,6 +163,7 @@ class JanusProPolicy(nn.Module):
             self._apply_lora()
         self.fused_logprob = True
         self._int4_layers = -1          # -1: int4 copies not built yet
+        self.decode_graph = True        # replay the decode step from a CUDA graph on GPU
 
     def _int4_context(self):
         """Context under which the trunk's decode-sized linears read int4 weights.
@@ -349,16 +350,67 @@ class JanusProPolicy(nn.Module):
             state.positions[rows] += 1
         return tokens, log_probs
 
+    # -- whole-batch decode with device-side positions (CUDA-graph replay) ------------------
+    def _step_all(self, state: JanusProARState, pos_img: torch.Tensor, pos_cache: torch.Tensor) -> None:
+        """Sample the token at image position ``pos_img`` for every row, feed it back at cache
+        position ``pos_cache`` and advance both counters — all indices live on the device."""
+        u = state.uniforms.index_select(1, pos_img)[:, 0]
+        logits = self.policy.image_logits_fp32(state.last_hidden)
+        n = logits.shape[0] // 2
+        tokens, log_probs = sampling_ops.sample_cfg_tokens(
+            logits[:n], logits[n:], u, state.cfg_weight, state.temperature)
+        state.token_ids.index_copy_(1, pos_img, tokens.unsqueeze(1))
+        state.log_probs.index_copy_(1, pos_img, log_probs.unsqueeze(1))
+        nxt = self.policy.align(tokens)
+        with self._int4_context():
+            hidden = self.policy.language_model.decode_step_at(
+                torch.cat([nxt, nxt], dim=0), state.cache, pos_cache)
+        state.last_hidden.copy_(hidden)
+        pos_img.add_(1)
+        pos_cache.add_(1)
+
+    def _decode_all_positions(self, state: JanusProARState) -> None:
+        """The 576-step (or so) decode loop is launch-bound: each step is a few hundred small
+        kernels.  Two steps run eagerly (they also finish every lazy set-up), the third is
+        captured in a CUDA graph and the graph is replayed for the remaining positions."""
+        n = state.image_token_num
+        dev = state.token_ids.device
+        pos_img = torch.zeros(1, dtype=torch.long, device=dev)
+        pos_cache = torch.full((1,), state.text_len, dtype=torch.long, device=dev)
+        eager = min(n, 2)
+        for _ in range(eager):
+            self._step_all(state, pos_img, pos_cache)
+        if n > eager:
+            if self.decode_graph:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    self._step_all(state, pos_img, pos_cache)
+                for _ in range(n - eager):
+                    graph.replay()
+                torch.cuda.current_stream().synchronize()
+                del graph
+            else:
+                for _ in range(n - eager):
+                    self._step_all(state, pos_img, pos_cache)
+        state.cache.length = state.text_len + n
+        state.positions += n
+
     @torch.no_grad()
     def sample_image_tokens(self, cond_inputs_embeds, uncond_inputs_embeds, cond_attention_mask,
                             uncond_attention_mask, *, cfg_weight=None, temperature=None,
                             image_token_num=None, generator: torch.Generator | None = None):
+        from visionrl_b200.ops import _ext
+
         state = self.init_ar_state(cond_inputs_embeds, uncond_inputs_embeds, cond_attention_mask,
                                    uncond_attention_mask, cfg_weight=cfg_weight,
                                    temperature=temperature, image_token_num=image_token_num,
                                    generator=generator)
-        for position in range(state.image_token_num):
-            self._sample_rows(state, None, position)
+        if self.device.type == "cuda" and _ext.kernels_enabled() and _ext.has("decode_attention") \
+                and self.dtype == torch.bfloat16:
+            self._decode_all_positions(state)
+        else:
+            for position in range(state.image_token_num):
+                self._sample_rows(state, None, position)
         return self.finalize_ar_state(state)
 
     @torch.no_grad()

@@ -227,6 +227,11 @@ class MLP(nn.Module):
         self.act = act
 
     def forward(self, x, gate=None, residual=None):
+        plain = type(self.fc1) is Linear and type(self.fc2) is Linear
+        if (plain and self.act == "gelu_tanh" and torch.is_grad_enabled()
+                and self.fc1.int4_shadow is None and self.fc2.int4_shadow is None):
+            y = linear_ops.gelu_mlp(x, self.fc1.weight, self.fc1.bias, self.fc2.weight, self.fc2.bias)
+            return linear_ops.linear_epilogue(y, None, gate, residual)
         return self.fc2(self.fc1(x, act=self.act), gate=gate, residual=residual)
 
 

@@ -109,6 +109,18 @@ class LlamaLayer(nn.Module):
         x = x + self.attn.out(merge_heads(o))
         return x + self.mlp(self.mlp_norm(x))
 
+    def decode_at(self, x, cos, sin, cache: KVCache, layer_idx: int, pos: torch.Tensor):
+        """:meth:`decode` for all rows with the position as a device tensor (graph-capturable)."""
+        q, k, v = self.attn._split(self.attn.qkv(self.attn_norm(x)))
+        q = apply_rope_reference(q, cos, sin)
+        k = apply_rope_reference(k, cos, sin)
+        cache.data[layer_idx, 0].index_copy_(2, pos, k)
+        cache.data[layer_idx, 1].index_copy_(2, pos, v.contiguous())
+        o = attn_ops.decode_attention(q, cache.data[layer_idx, 0], cache.data[layer_idx, 1],
+                                      cache.valid, cache.max_len)
+        x = x + self.attn.out(merge_heads(o))
+        return x + self.mlp(self.mlp_norm(x))
+
     def decode(self, x, cos, sin, cache: KVCache, layer_idx: int, rows=None, pos=None):
         """``x[R, 1, D]`` at position ``pos`` (already marked valid) of cache rows ``rows``."""
         q, k, v = self.attn._split(self.attn.qkv(self.attn_norm(x)))
@@ -171,6 +183,23 @@ class LlamaDecoder(AdapterMixin, nn.Module):
             else:
                 x = layer(x, cos, sin, bias, cache, i, 0)
         return self.norm(x)
+
+    def decode_step_at(self, embeds, cache: KVCache, pos: torch.Tensor):
+        """One decode step of every cache row at the position held in the device tensor ``pos``
+        (int64, one element).
+
+        Nothing here depends on a host-side value: the cache is written with ``index_copy_``,
+        the rotary angles are computed from ``pos`` and attention walks the whole static cache
+        with the validity mask selecting the filled positions.  The step can therefore be
+        captured once in a CUDA graph and replayed for every position; the caller keeps
+        ``cache.length`` up to date.
+        """
+        cache.valid.index_fill_(1, pos, True)
+        cos, sin = rope_tables(pos, self.head_dim, self.cfg.rope_theta)
+        x = embeds.unsqueeze(1)
+        for i, layer in enumerate(self.layers):
+            x = layer.decode_at(x, cos, sin, cache, i, pos)
+        return self.norm(x)[:, 0]
 
     def decode_step(self, embeds, cache: KVCache, rows=None, position: int | None = None):
         """``embeds[R, D]`` for the next position → hidden ``[R, D]``.

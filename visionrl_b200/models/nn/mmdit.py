@@ -79,6 +79,22 @@ class StreamAttention(nn.Module):
         return qkv_prepare(self.qkv(x), self.heads, self.q_norm, self.k_norm)
 
 
+class _SplitStreams(torch.autograd.Function):
+    """Joint ``[B, Sx + Sc, D]`` activations → contiguous image and text parts.
+
+    The gradient is one concatenation instead of two zero-filled full-size tensors and an add.
+    """
+
+    @staticmethod
+    def forward(ctx, o, sx):
+        ctx.sx = sx
+        return o[:, :sx].contiguous(), o[:, sx:].contiguous()
+
+    @staticmethod
+    def backward(ctx, gx, gc):
+        return torch.cat([gx, gc], dim=1), None
+
+
 class JointBlock(nn.Module):
     def __init__(self, cfg: MMDiTConfig, context_pre_only: bool = False):
         super().__init__()
@@ -102,12 +118,12 @@ class JointBlock(nn.Module):
             ax.qkv(norm_ops.adaln_layernorm(x, mx[0], mx[1])),
             ac.qkv(norm_ops.adaln_layernorm(c, mc[0], mc[1])),
             ax.heads, (ax.q_norm, ax.k_norm), (ac.q_norm, ac.k_norm))
-        o = merge_heads(sdpa(q, k, v))
-        x = self.attn_x.out(o[:, :sx], gate=mx[2], residual=x)
+        ox, oc = _SplitStreams.apply(merge_heads(sdpa(q, k, v)), sx)
+        x = self.attn_x.out(ox, gate=mx[2], residual=x)
         x = self.mlp_x(norm_ops.adaln_layernorm(x, mx[3], mx[4]), gate=mx[5], residual=x)
         if self.context_pre_only:
             return x, None
-        c = self.attn_c.out(o[:, sx:], gate=mc[2], residual=c)
+        c = self.attn_c.out(oc, gate=mc[2], residual=c)
         c = self.mlp_c(norm_ops.adaln_layernorm(c, mc[3], mc[4]), gate=mc[5], residual=c)
         return x, c
 

@@ -14,6 +14,7 @@ import torch
 import torch.nn.functional as F
 from torch import nn
 
+from visionrl_b200.ops import norm as norm_ops
 from visionrl_b200.models.nn.layers import LayerNorm, Linear, MLP, merge_heads, sdpa, split_heads
 
 
@@ -34,8 +35,8 @@ class ResBlock2D(nn.Module):
         self.skip = nn.Conv2d(cin, cout, 1) if cin != cout else None
 
     def forward(self, x):
-        h = self.c1(F.silu(self.n1(x)))
-        h = self.c2(F.silu(self.n2(h)))
+        h = self.c1(norm_ops.group_norm_silu(x, self.n1))
+        h = self.c2(norm_ops.group_norm_silu(h, self.n2))
         return (x if self.skip is None else self.skip(x)) + h
 
 
@@ -71,7 +72,7 @@ class LatentDecoder2D(nn.Module):
         if z.is_cuda:
             z = z.contiguous(memory_format=torch.channels_last)
         h = self.up(self.mid(self.conv_in(z)))
-        return self.conv_out(F.silu(self.norm_out(h)))
+        return self.conv_out(norm_ops.group_norm_silu(h, self.norm_out))
 
 
 class LatentDecoder3D(nn.Module):

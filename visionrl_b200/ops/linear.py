@@ -134,6 +134,65 @@ def gate_residual(y, gate, residual):
     return residual + (gate.unsqueeze(1) if y.dim() == 3 else gate) * y
 
 
+class _GeluMLPFn(torch.autograd.Function):
+    """``fc2(gelu_tanh(fc1(x)))`` with the activation folded into the GEMM epilogues.
+
+    Forward: the first GEMM stores both the pre-activation ``h`` and ``gelu(h)`` from one pass
+    over the accumulator.  Backward: the GEMM that forms ``d gelu(h)`` multiplies by
+    ``gelu'(h)`` in its epilogue, so no stand-alone activation kernel runs in either direction.
+    """
+
+    @staticmethod
+    def forward(ctx, x, w1, b1, w2, b2):
+        from visionrl_b200.ops import _ext
+
+        x2 = x.reshape(-1, x.shape[-1])
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        a, h = _ext.load().gemm_bf16_dual(x2, w1, b1, _ACTS["gelu_tanh"])
+        y = gemm_nt(a, w2, b2)
+        ctx.save_for_backward(x2, w1, w2, h, a)
+        ctx.has_b1, ctx.has_b2 = b1 is not None, b2 is not None
+        ctx.x_shape = x.shape
+        return y.view(*x.shape[:-1], w2.shape[0])
+
+    @staticmethod
+    def backward(ctx, gy):
+        from visionrl_b200.ops import _ext
+
+        ext = _ext.load()
+        x2, w1, w2, h, a = ctx.saved_tensors
+        gy2 = gy.reshape(-1, gy.shape[-1])
+        if not gy2.is_contiguous():
+            gy2 = gy2.contiguous()
+        # gh = (gy @ w2) * gelu'(h): w2 is [out, hidden] row-major, i.e. the MN-major B operand
+        gh = ext.gemm_bf16(gy2, w2, None, None, h, 3, 0, False, True, False)
+        gx = gw1 = gb1 = gw2 = gb2 = None
+        if ctx.needs_input_grad[3]:
+            gw2 = gemm_tn(gy2, a)
+        if ctx.has_b2 and ctx.needs_input_grad[4]:
+            gb2 = ext.colsum(gy2).to(gy2.dtype)
+        if ctx.needs_input_grad[1]:
+            gw1 = gemm_tn(gh, x2)
+        if ctx.has_b1 and ctx.needs_input_grad[2]:
+            gb1 = ext.colsum(gh).to(gh.dtype)
+        if ctx.needs_input_grad[0]:
+            gx = gemm_nn(gh, w1).view(ctx.x_shape)
+        return gx, gw1, gb1, gw2, gb2
+
+
+def gelu_mlp(x, w1, b1, w2, b2):
+    """Two-layer GELU-tanh MLP; fused epilogues when gradients are needed on bf16 CUDA tensors."""
+    from visionrl_b200.ops import _ext
+
+    needs_grad = torch.is_grad_enabled() and any(
+        t is not None and t.requires_grad for t in (x, w1, b1, w2, b2))
+    if (needs_grad and _use_kernel(x, w1) and w2.dtype == torch.bfloat16 and w1.shape[0] % 8 == 0
+            and w2.shape[0] % 8 == 0 and _ext.has("gemm_bf16_dual")):
+        return _GeluMLPFn.apply(x, w1, b1, w2, b2)
+    return linear(linear(x, w1, b1, act="gelu_tanh"), w2, b2)
+
+
 def linear(x, w, bias=None, act=None, gate=None, residual=None):
     """Differentiable linear with optional fused epilogue (fused only without grad)."""
     if not _use_kernel(x, w):

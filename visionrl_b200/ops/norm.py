@@ -87,3 +87,25 @@ def rmsnorm(x, weight, eps: float = 1e-6):
 
 def layernorm(x, weight, bias, eps: float = 1e-5):
     return F.layer_norm(x, (x.shape[-1],), weight, bias, eps)
+
+
+def group_norm_silu(x, norm, apply_silu: bool = True):
+    """``silu(group_norm(x))`` for a ``torch.nn.GroupNorm`` module ``norm``.
+
+    Channels-last bf16 CUDA activations outside autograd (the frozen decoders of the reward
+    path) take one statistics pass and one fused normalise(+SiLU) pass of the sm_100a kernel;
+    everything else evaluates the module and the activation separately.
+    """
+    import torch.nn.functional as F
+
+    from visionrl_b200.ops import _ext
+
+    c = x.shape[1] if x.dim() == 4 else 0
+    if (x.dim() == 4 and x.is_cuda and x.dtype == torch.bfloat16 and not torch.is_grad_enabled()
+            and norm.affine and c % 8 == 0 and 256 % (c // 8) == 0 and c // 8 <= 256
+            and x.is_contiguous(memory_format=torch.channels_last)
+            and _ext.kernels_enabled() and _ext.has("groupnorm_nhwc")):
+        return _ext.load().groupnorm_nhwc(x, norm.weight, norm.bias, int(norm.num_groups),
+                                          float(norm.eps), bool(apply_silu))
+    y = norm(x)
+    return F.silu(y) if apply_silu else y

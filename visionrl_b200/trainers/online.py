@@ -198,10 +198,16 @@ class OnlineTrainer(Trainer):
     async def _ensure_rollout_weights_initialized(self) -> None:
         if self._rollout_weights_initialized or self.weight_syncer is None:
             return
-        await self.weight_syncer.push(self.model.state_dict())
+        await self.weight_syncer.push(self._sync_payload())
         self._rollout_weights_initialized = True
 
     # -- optimisation helpers ------------------------------------------------------------
+    def _sync_payload(self) -> dict:
+        """What a weight push carries: the trainable set when the policy can name it (adapters
+        only under LoRA), otherwise the whole ``state_dict()``."""
+        export = getattr(self.model, "trainable_state_dict", None)
+        return export() if callable(export) else self.model.state_dict()
+
     def _backward(self, loss: Any) -> None:
         if self.accelerator is not None:
             self.accelerator.backward(loss)
@@ -526,7 +532,7 @@ class OnlineTrainer(Trainer):
         self.state.total_reward += out.reward_mean
         self.state.total_loss += out.loss
         if self.weight_syncer is not None:
-            await self.weight_syncer.push(self.model.state_dict())
+            await self.weight_syncer.push(self._sync_payload())
         return out
 
     def _check_kernel_status(self) -> None:
