@@ -119,15 +119,24 @@ class DiffusionPipelineExecutorBase:
         spec = self.parse_spec(request)
         plan = plan_prompt_group_microbatches(
             list(request.prompts), int(request.samples_per_prompt), spec.base.sample_batch_size)
+        # every prompt is encoded once, however many micro-batches its group is split into
+        encoded_by_prompt: dict[int, Any] = {}
         chunks = run_microbatches_with_oom_retry(
-            plan.micro_batches, lambda mb: self.forward_chunk(request, mb))
+            plan.micro_batches,
+            lambda mb: self.forward_chunk(request, mb, encoded_cache=encoded_by_prompt))
         return self.gather_chunks(request, sample_specs, chunks)
 
-    def forward_chunk(self, request: GenerationRequest, chunk: MicroBatchPlan) -> DiffusionChunkResult:
+    def forward_chunk(self, request: GenerationRequest, chunk: MicroBatchPlan,
+                      encoded_cache: dict[int, Any] | None = None) -> DiffusionChunkResult:
         spec = self.parse_spec(request)
         video_request = self.build_video_request(chunk.prompt, spec)
         hook = dict(generation_request=request, video_request=video_request, spec=spec, chunk=chunk)
-        encoded = self.encode_prompt_for_chunk(**hook)
+        if encoded_cache is not None and chunk.prompt_index in encoded_cache:
+            encoded = encoded_cache[chunk.prompt_index]
+        else:
+            encoded = self.encode_prompt_for_chunk(**hook)
+            if encoded_cache is not None:
+                encoded_cache[chunk.prompt_index] = encoded
         return run_diffusion_denoise_chunk(
             policy=self.model, request=video_request,
             encoded=self.build_chunk_encoded(encoded=encoded, **hook),
