@@ -20,11 +20,11 @@ class _Head(nn.Module):
     def __init__(self):
         super().__init__()
         torch.manual_seed(0)
-        self.net = nn.Linear(6 + 4 + 1, 6)
+        self.proj = nn.Linear(6 + 4 + 1, 6)
 
     def forward(self, x, t, cond):
         tt = t.reshape(-1, 1).expand(x.shape[0], 1).to(x.dtype)
-        return self.net(torch.cat([x, cond, tt], dim=-1))
+        return self.proj(torch.cat([x, cond, tt], dim=-1))
 
 
 def test_replay_with_saved_noise_reproduces_the_sampled_log_prob():
