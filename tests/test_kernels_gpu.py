@@ -677,3 +677,26 @@ def test_janus_graph_decode_matches_eager_decode(int4):
     assert torch.equal(outs[0][0], outs[1][0])
     assert torch.equal(outs[0][1], outs[1][1])
     assert outs[0][0].min() >= 0 and outs[0][0].max() < 1024 and torch.isfinite(outs[0][1]).all()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("m", [1, 20, 32, 64])
+@pytest.mark.parametrize("nk", [(2048 + 24, 2048), (512, 5632), (6144, 256)])
+def test_int4_tensor_core_gemm_matches_dequantised_matmul(m, nk):
+    from visionrl_b200.ops import _ext
+    from visionrl_b200.ops.quant import int4_linear_reference, quantize_int4
+
+    torch.manual_seed(16)
+    n, k = nk
+    w = torch.randn(n, k, device="cuda") * 0.05
+    packed, scales = quantize_int4(w)
+    x = torch.randn(m, k, device="cuda").bfloat16()
+    bias = torch.randn(n, device="cuda").bfloat16()
+    ext = _ext.load()
+    got = ext.int4_gemm(x, packed, scales, bias, 128)
+    torch.cuda.synchronize()
+    assert ext.int4_gemm_last_status() == 0
+    ref = int4_linear_reference(x.float(), packed, scales, bias)
+    assert torch.allclose(got.float(), ref, atol=4e-2, rtol=2e-2)
+    again = ext.int4_gemm(x, packed, scales, None, 128)
+    assert torch.allclose(again.float(), ref - bias.float(), atol=4e-2, rtol=2e-2)

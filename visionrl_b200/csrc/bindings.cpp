@@ -61,6 +61,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("moe_permute", &vrl::moe_permute);
   m.def("moe_gather_rows", &vrl::moe_gather_rows);
   m.def("moe_combine", &vrl::moe_combine);
+  m.def("int4_gemm", &vrl::int4_gemm);
+  m.def("int4_gemm_last_status", &vrl::int4_gemm_last_status);
   m.def("groupnorm_nhwc", &vrl::groupnorm_nhwc);
   m.def("flash_attn_fwd", &vrl::flash_attn_fwd);
   m.def("flash_attn_last_status", &vrl::flash_attn_last_status);

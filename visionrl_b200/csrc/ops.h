@@ -95,6 +95,11 @@ std::vector<torch::Tensor> moe_permute(torch::Tensor experts, int64_t num_expert
 torch::Tensor moe_gather_rows(torch::Tensor x, torch::Tensor perm, int64_t topk);
 torch::Tensor moe_combine(torch::Tensor yp, torch::Tensor inv, torch::Tensor weights);
 
+// int4_gemm_sm100.cu
+torch::Tensor int4_gemm(torch::Tensor x, torch::Tensor qweight, torch::Tensor scales,
+                        c10::optional<torch::Tensor> bias, int64_t group);
+int64_t int4_gemm_last_status();
+
 // groupnorm.cu
 torch::Tensor groupnorm_nhwc(torch::Tensor x, torch::Tensor weight, torch::Tensor bias, int64_t groups,
                              double eps, bool apply_silu);

@@ -51,13 +51,18 @@ def int4_linear_reference(x, packed, scales, bias=None, group: int = GROUP):
 
 
 def int4_linear(x, packed, scales, bias=None, group: int = GROUP):
-    """``x[..., K]`` times the dequantised ``[N, K]`` weight; kernel path for ≤ 32 rows on CUDA."""
+    """``x[..., K]`` times the dequantised ``[N, K]`` weight; kernel paths for decode-sized
+    batches on CUDA (≤ 64 rows on the tensor cores, else the CUDA-core GEMV or the oracle)."""
     from visionrl_b200.ops import _ext
 
     lead = x.shape[:-1]
     x2 = x.reshape(-1, x.shape[-1])
-    if (x2.is_cuda and x2.dtype == torch.bfloat16 and x2.shape[0] <= 32 and x2.shape[1] % 256 == 0
-            and _ext.kernels_enabled() and _ext.has("int4_gemv")):
+    on_gpu = x2.is_cuda and x2.dtype == torch.bfloat16 and _ext.kernels_enabled()
+    if (on_gpu and 1 <= x2.shape[0] <= 64 and x2.shape[1] % 64 == 0 and group % 64 == 0
+            and _ext.has("int4_gemm")):
+        # tensor-core path: codes are dequantised inside the SM and fed to tcgen05.mma
+        y = _ext.load().int4_gemm(x2.contiguous(), packed, scales, bias, int(group))
+    elif (on_gpu and x2.shape[0] <= 32 and x2.shape[1] % 256 == 0 and _ext.has("int4_gemv")):
         y = _ext.load().int4_gemv(x2.contiguous(), packed, scales, bias, int(group))
     else:
         y = int4_linear_reference(x2, packed, scales, bias, group)
