@@ -149,3 +149,50 @@ def weight_broadcast_and_timeout(rank, world, port, out):
         out.put({"ok": bool(flags[0]), "timed_out": bool(flags[1])})
     dist.barrier()
     dist.destroy_process_group()
+
+
+def allgather_gemm_matches_library(rank, world, port, out):
+    """The GEMM with the all-gather fused in equals all_gather + matmul, also on a second call."""
+    from visionrl_b200.ops import _ext
+    from visionrl_b200.parallel.mesh import ProcessMesh
+    from visionrl_b200.parallel.sharded_linear import ShardedLinearWeight
+    from visionrl_b200.parallel.symm import SymmetricPool
+
+    _init(rank, world, port, "nccl")
+    dev = torch.device("cuda", rank)
+    mesh = ProcessMesh.build()
+    pool = SymmetricPool(mesh)
+    results = []
+    for (m, n, k, act, use_bias) in [(1000, 1536, 512, None, False), (4096, 4608, 1536, "gelu_tanh", True)]:
+        gen = torch.Generator().manual_seed(7)
+        w = (torch.randn(n, k, generator=gen) * 0.05).to(dev)
+        b = (torch.randn(n, generator=gen) * 0.1).to(dev)
+        x = torch.randn(m, k, generator=torch.Generator().manual_seed(100 + rank)).to(dev, torch.bfloat16)
+        layer = ShardedLinearWeight(pool, n, k, dev, bias=use_bias)
+        layer.load_full(w)
+        if use_bias:
+            layer.bias.copy_(b)
+        torch.cuda.synchronize()
+        pool.barrier()
+        ref = torch.nn.functional.linear(x.float(), w.bfloat16().float(), b.bfloat16().float() if use_bias else None)
+        if act == "gelu_tanh":
+            ref = torch.nn.functional.gelu(ref, approximate="tanh")
+        for _ in range(2):
+            layer.full.fill_(float("nan"))            # stale contents must never be read
+            got = layer.forward(x, act)
+            torch.cuda.synchronize()
+            status = _ext.load().gemm_last_status()
+            ok = status == 0 and bool(torch.isfinite(got.float()).all()) and torch.allclose(
+                got.float(), ref, atol=6e-2, rtol=3e-2)
+            results.append(ok)
+            pool.barrier()
+        layer.collectives = "nccl"
+        base = layer.forward(x, act)
+        results.append(torch.allclose(base.float(), ref, atol=6e-2, rtol=3e-2))
+        results.append(layer.kernel_launches == 2)
+    flags = torch.tensor([float(all(results))], device=dev)
+    dist.all_reduce(flags, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        out.put({"ok": bool(flags[0]), "detail": results})
+    dist.barrier()
+    dist.destroy_process_group()

@@ -68,3 +68,11 @@ def test_weight_broadcast_versions_and_bounded_wait():
     world = min(torch.cuda.device_count(), 4)
     res = _run(_workers.weight_broadcast_and_timeout, world)
     assert res["ok"] and res["timed_out"]
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+def test_allgather_fused_gemm_matches_library():
+    world = min(torch.cuda.device_count(), 4)
+    res = _run(_workers.allgather_gemm_matches_library, world)
+    assert res["ok"], res["detail"]

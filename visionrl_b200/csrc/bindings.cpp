@@ -68,5 +68,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("flash_attn_last_status", &vrl::flash_attn_last_status);
   m.def("gemm_bf16", &vrl::gemm_bf16);
   m.def("gemm_bf16_dual", &vrl::gemm_bf16_dual);
+  m.def("gemm_allgather", &vrl::gemm_allgather);
   m.def("gemm_last_status", &vrl::gemm_last_status);
 }

@@ -62,12 +62,38 @@ struct Params {
   int64_t gate_ld;                 // elements between consecutive gate rows
   int a_mn, b_mn;
   int out_fp32;
+  // all-gather fused into the GEMM (B operand sharded by rows over `g_world` ranks)
+  const __nv_bfloat16* g_peer[16]; // every rank's shard [g_rows, K] (peer-mapped pointers)
+  __nv_bfloat16* g_full;           // local [N, K] buffer the shards are gathered into (= B operand)
+  int* g_ready;                    // [g_world] arrival counters, zero before the launch
+  int g_world, g_rank, g_rows;     // g_rows = N / g_world
+  int g_first_tile;                // n-tile holding this rank's own rows: processed first
 };
+
+constexpr int kGatherThreads = 128;
+enum : int { kTimeoutGather = 4 };
+
+// Tile index -> tile origin.  Plain GEMMs sweep n fastest; the gathering variant sweeps m fastest
+// and starts at the n-tiles of the local shard, so the peers' rows are needed as late as possible.
+template <bool kGather>
+__device__ __forceinline__ void tile_origin(int tile, int m_tiles, int n_tiles, const Params& p, int& m0,
+                                            int& n0) {
+  if (kGather) {
+    int nt = tile / m_tiles + p.g_first_tile;
+    if (nt >= n_tiles) nt -= n_tiles;
+    m0 = (tile % m_tiles) * BM;
+    n0 = nt * BN;
+  } else {
+    m0 = (tile / n_tiles) * BM;
+    n0 = (tile % n_tiles) * BN;
+  }
+}
 
 using namespace ptx;
 
 // ------------------------------------------------------------------------------------- kernel
-__global__ void __launch_bounds__(kThreads, 1)
+template <bool kGather>
+__global__ void __launch_bounds__(kGather ? kThreads + kGatherThreads : kThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                  const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_r,
                  const __grid_constant__ CUtensorMap map_c2, const Params p) {
@@ -107,8 +133,28 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     // ------------------------------------------------------------------ TMA producer
     uint32_t it = 0;
     bool ok = true;
+    uint32_t slabs_seen = 0;       // bit r: the rows of rank r are known to be in g_full
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-      const int m0 = (tile / n_tiles) * BM, n0 = (tile % n_tiles) * BN;
+      int m0, n0;
+      tile_origin<kGather>(tile, m_tiles, n_tiles, p, m0, n0);
+      if (kGather) {
+        // the B rows of this tile must have been copied by the gather warps of EVERY CTA
+        const int lo = n0 / p.g_rows, hi = min(p.n - 1, n0 + BN - 1) / p.g_rows;
+        for (int r = lo; r <= hi && ok; ++r) {
+          if (slabs_seen & (1u << r)) continue;
+          bool ready = false;
+          for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+            int v;
+            asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p.g_ready + r) : "memory");
+            if (v >= (int)gridDim.x) { ready = true; break; }
+            if ((spin & 1023u) == 1023u && *abort_flag) break;
+          }
+          if (!ready) { ok = false; break; }
+          slabs_seen |= 1u << r;
+          asm volatile("fence.proxy.async;" ::: "memory");   // generic-proxy writes -> TMA reads
+        }
+        if (!ok) break;
+      }
       for (int kb = 0; kb < k_blocks; ++kb, ++it) {
         const int s = it % kStages;
         const uint32_t parity = ((it / kStages) & 1u) ^ 1u;
@@ -175,7 +221,31 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     if (!ok) {
       if (atomicCAS(const_cast<int*>(abort_flag), 0, 1) == 0) atomicExch(p.status, kTimeoutMma);
     }
-  } else if (warp >= 2) {
+  } else if (kGather && warp >= 2 + kEpiWarps) {
+    // ------------------------------------------------------------------------ gather
+    // The 128 extra threads of every CTA copy this CTA's share of each rank's shard into the
+    // local full-weight buffer, own rows first, then peer (r + 1), (r + 2), ... over NVLink with
+    // plain 16-byte loads.  After a shard's share is written the group publishes it with a
+    // release (fence + atomic); a shard is complete when all gridDim.x CTAs have published.
+    const int gt = threadIdx.x - (2 + kEpiWarps) * 32;
+    const int64_t vec_per_shard = (int64_t)p.g_rows * p.k / 8;
+    const int64_t v_lo = vec_per_shard * blockIdx.x / gridDim.x;
+    const int64_t v_hi = vec_per_shard * (blockIdx.x + 1) / gridDim.x;
+    for (int step = 0; step < p.g_world; ++step) {
+      int r = p.g_rank + step;
+      if (r >= p.g_world) r -= p.g_world;
+      const uint4* src = reinterpret_cast<const uint4*>(p.g_peer[r]);
+      uint4* dst = reinterpret_cast<uint4*>(p.g_full + (int64_t)r * p.g_rows * p.k);
+      for (int64_t v = v_lo + gt; v < v_hi; v += kGatherThreads) dst[v] = src[v];
+      __threadfence();
+      asm volatile("bar.sync 1, %0;" ::"n"(kGatherThreads) : "memory");
+      if (gt == 0) {
+        __threadfence();                            // cumulative release of the group's stores
+        asm volatile("fence.proxy.async;" ::: "memory");
+        atomicAdd(p.g_ready + r, 1);
+      }
+    }
+  } else if (warp >= 2 && warp < 2 + kEpiWarps) {
     // ---------------------------------------------------------------------- epilogue
     // bf16 results leave through shared memory: each warp converts a 32-row x 64-column piece,
     // writes it 128-byte-swizzled into its own staging tile and lane 0 hands that tile to a TMA
@@ -192,7 +262,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_it) {
       const uint32_t buf = tile_it & 1u;
-      const int m0 = (tile / n_tiles) * BM, n0 = (tile % n_tiles) * BN;
+      int m0, n0;
+      tile_origin<kGather>(tile, m_tiles, n_tiles, p, m0, n0);
       if (!mbar_wait(&acc_full[buf], (tile_it >> 1) & 1u, abort_flag)) { ok = false; break; }
       tmem_fence_after();
       const int row0 = m0 + quarter * 32;
@@ -498,7 +569,7 @@ static std::vector<torch::Tensor> gemm_impl(torch::Tensor a, torch::Tensor b,
   p.dual = dual ? 1 : 0;
 
   static const bool attr_set = [] {
-    C10_CUDA_CHECK(cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    C10_CUDA_CHECK(cudaFuncSetAttribute(gemm_bf16_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         kSmemBytes));
     return true;
   }();
@@ -510,10 +581,77 @@ static std::vector<torch::Tensor> gemm_impl(torch::Tensor a, torch::Tensor b,
   CUtensorMap map_c = out_fp32 ? map_a : make_map(out.data_ptr(), n, m, n, 64, 32);
   CUtensorMap map_r = (p.residual && !out_fp32) ? make_map(p.residual, n, m, n, 64, 32) : map_c;
   CUtensorMap map_c2 = dual ? make_map(pre.data_ptr(), n, m, n, 64, 32) : map_c;
-  gemm_bf16_kernel<<<grid, kThreads, kSmemBytes, at::cuda::getCurrentCUDAStream()>>>(map_a, map_b, map_c,
-                                                                                    map_r, map_c2, p);
+  gemm_bf16_kernel<false><<<grid, kThreads, kSmemBytes, at::cuda::getCurrentCUDAStream()>>>(
+      map_a, map_b, map_c, map_r, map_c2, p);
   C10_CUDA_KERNEL_LAUNCH_CHECK();
   return {out, pre};
+}
+
+// y = act(x W^T + bias) where W [N, K] is sharded by rows over `world` ranks.  `peer_ptrs` holds the
+// address of every rank's shard [N / world, K] as mapped into THIS process (own shard included),
+// `full` is a local [N, K] buffer the kernel gathers the shards into while it computes, `ready`
+// a zeroed int32 [world] scratch.  All ranks' shards must be complete before the launch.
+torch::Tensor gemm_allgather(torch::Tensor x, torch::Tensor peer_ptrs, torch::Tensor full,
+                             torch::Tensor ready, c10::optional<torch::Tensor> bias, int64_t act,
+                             int64_t rank, int64_t world) {
+  using namespace gemm;
+  TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.scalar_type() == torch::kBFloat16 && x.stride(1) == 1);
+  TORCH_CHECK(full.is_cuda() && full.dim() == 2 && full.scalar_type() == torch::kBFloat16 && full.is_contiguous());
+  TORCH_CHECK(peer_ptrs.device().is_cpu() && peer_ptrs.scalar_type() == torch::kInt64 &&
+              peer_ptrs.numel() == world, "peer_ptrs: CPU int64 tensor with one address per rank");
+  TORCH_CHECK(world >= 1 && world <= 16 && rank >= 0 && rank < world);
+  TORCH_CHECK(ready.is_cuda() && ready.scalar_type() == torch::kInt32 && ready.numel() >= world);
+  TORCH_CHECK(act >= 0 && act <= 2);
+  const int64_t m = x.size(0), k = x.size(1), n = full.size(0);
+  TORCH_CHECK(full.size(1) == k && n % world == 0 && n % 8 == 0 && k % 8 == 0 && x.stride(0) % 8 == 0);
+  TORCH_CHECK(((n / world) * k) % 8 == 0, "gemm_allgather: shard size must be a multiple of 16 bytes");
+  const c10::cuda::CUDAGuard guard(x.device());
+  static thread_local bool context_bound = false;
+  if (!context_bound) {
+    C10_CUDA_CHECK(cudaFree(nullptr));
+    context_bound = true;
+  }
+  auto out = torch::empty({m, n}, x.options());
+  if (m == 0) return out;
+  auto stream = at::cuda::getCurrentCUDAStream();
+  C10_CUDA_CHECK(cudaMemsetAsync(ready.data_ptr(), 0, sizeof(int) * world, stream));
+  Params p{};
+  p.c = out.data_ptr();
+  torch::Tensor bias_c;
+  if (bias.has_value()) {
+    bias_c = bias->to(torch::kBFloat16).contiguous();
+    TORCH_CHECK(bias_c.numel() == n);
+    p.bias = reinterpret_cast<const __nv_bfloat16*>(bias_c.data_ptr());
+  }
+  p.status = status_word(x.get_device());
+  p.m = (int)m; p.n = (int)n; p.k = (int)k;
+  p.act = (int)act;
+  p.rows_per_gate = 1;
+  const int64_t* ptrs = peer_ptrs.data_ptr<int64_t>();
+  for (int r = 0; r < world; ++r) {
+    TORCH_CHECK(ptrs[r] != 0 && ptrs[r] % 16 == 0, "gemm_allgather: shard addresses must be 16-byte aligned");
+    p.g_peer[r] = reinterpret_cast<const __nv_bfloat16*>(ptrs[r]);
+  }
+  p.g_full = reinterpret_cast<__nv_bfloat16*>(full.data_ptr());
+  p.g_ready = ready.data_ptr<int>();
+  p.g_world = (int)world; p.g_rank = (int)rank; p.g_rows = (int)(n / world);
+  p.g_first_tile = (int)((rank * (n / world)) / BN);
+  const CUtensorMap map_a = make_map(x.data_ptr(), k, m, x.stride(0), BK, BM);
+  const CUtensorMap map_b = make_map(full.data_ptr(), k, n, k, BK, BN);
+  const CUtensorMap map_c = make_map(out.data_ptr(), n, m, n, 64, 32);
+  static const bool attr_set = [] {
+    C10_CUDA_CHECK(cudaFuncSetAttribute(gemm_bf16_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        kSmemBytes));
+    return true;
+  }();
+  (void)attr_set;
+  const int tiles = (int)(((m + BM - 1) / BM) * ((n + BN - 1) / BN));
+  const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+  const int grid = std::min(tiles, sms);     // one CTA per SM at most: every CTA is resident
+  gemm_bf16_kernel<true><<<grid, kThreads + kGatherThreads, kSmemBytes, stream>>>(map_a, map_b, map_c, map_c,
+                                                                                  map_c, p);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return out;
 }
 
 }  // namespace vrl

@@ -115,6 +115,9 @@ torch::Tensor gemm_bf16(torch::Tensor a, torch::Tensor b, c10::optional<torch::T
                         bool out_fp32);
 std::vector<torch::Tensor> gemm_bf16_dual(torch::Tensor a, torch::Tensor b,
                                           c10::optional<torch::Tensor> bias, int64_t act);
+torch::Tensor gemm_allgather(torch::Tensor x, torch::Tensor peer_ptrs, torch::Tensor full,
+                             torch::Tensor ready, c10::optional<torch::Tensor> bias, int64_t act,
+                             int64_t rank, int64_t world);
 int64_t gemm_last_status();
 
 }  // namespace vrl
