@@ -207,9 +207,14 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         uint32_t r[32];
         tmem_ld32(s_addr + c * 32, r);
         tmem_ld_wait();
+        if (valid == kTile) {                          // only the last key tile is ever partial
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (c * 32 + i < valid) mx = fmaxf(mx, __uint_as_float(r[i]));
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (c * 32 + i < valid) mx = fmaxf(mx, __uint_as_float(r[i]));
+        }
       }
       const float m_new = fmaxf(m, mx * p.scale_log2);
       const float corr = exp2f(m - m_new);              // 0 on the first tile (m = -inf)
@@ -229,12 +234,20 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
           float pv[8];
+          if (valid == kTile) {
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int col = c * 32 + g * 8 + i;
-            const float e = exp2f(__uint_as_float(r[g * 8 + i]) * p.scale_log2 - m_new);
-            pv[i] = col < valid ? e : 0.f;
-            rowsum += pv[i];
+            for (int i = 0; i < 8; ++i) {
+              pv[i] = exp2f(__uint_as_float(r[g * 8 + i]) * p.scale_log2 - m_new);
+              rowsum += pv[i];
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int col = c * 32 + g * 8 + i;
+              const float e = exp2f(__uint_as_float(r[g * 8 + i]) * p.scale_log2 - m_new);
+              pv[i] = col < valid ? e : 0.f;
+              rowsum += pv[i];
+            }
           }
           const bf16x8 packed = pack8(pv);
           const uint32_t chunk = (uint32_t)((c & 1) * 4 + g);
