@@ -4,7 +4,8 @@
 // the small activation batch is the UMMA N dimension (32 or 64).
 //
 // One CTA owns 128 output features and a slice of K (split-K fills the machine when N / 128 is
-// small; partial sums meet in an fp32 buffer through atomics).
+// small; every split writes its own fp32 slice and the slices are summed afterwards, so the result
+// does not depend on the order in which CTAs finish).
 //   warp 0       TMA producer: packed int4 weights [128 x 32 bytes] and the activation tile
 //                [32|64 rows x 64 k] per 64-wide k-block, 4-stage ring
 //   warp 1       MMA issuer and TMEM owner
@@ -44,7 +45,7 @@ enum Status : int { kOk = 0, kTimeoutProducer = 21, kTimeoutMma = 22, kTimeoutDe
 struct Params {
   const __nv_bfloat16* scales;     // [N, K / group]
   const __nv_bfloat16* bias;       // [N] or null
-  float* acc;                      // [M, N] fp32, zero-initialised (split-K target)
+  float* acc;                      // [ksplit, M, N] fp32 partial results, one slice per K split
   int* status;
   int m, n, k, group;
   int nmma;                        // 32 or 64: UMMA N (activation rows, zero padded)
@@ -172,7 +173,8 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
 #pragma unroll
               for (int i = 0; i < 32; ++i) {
                 const int mrow = c * 32 + i;
-                if (mrow < p.m) atomicAdd(p.acc + (int64_t)mrow * p.n + col, __uint_as_float(r[i]) + b);
+                if (mrow < p.m)
+                  p.acc[((int64_t)blockIdx.y * p.m + mrow) * p.n + col] = __uint_as_float(r[i]) + b;
               }
             }
           }
@@ -263,7 +265,6 @@ torch::Tensor int4_gemm(torch::Tensor x, torch::Tensor qweight, torch::Tensor sc
     C10_CUDA_CHECK(cudaFree(nullptr));
     context_bound = true;
   }
-  auto acc = torch::zeros({m, n}, x.options().dtype(torch::kFloat32));
   const __nv_bfloat16* bias_p = nullptr;
   torch::Tensor bias_c;
   if (bias.has_value()) {
@@ -274,7 +275,6 @@ torch::Tensor int4_gemm(torch::Tensor x, torch::Tensor qweight, torch::Tensor sc
   Params p{};
   p.scales = reinterpret_cast<const __nv_bfloat16*>(scales.data_ptr());
   p.bias = bias_p;
-  p.acc = acc.data_ptr<float>();
   p.status = status_word(x.get_device());
   p.m = (int)m; p.n = (int)n; p.k = (int)k; p.group = (int)group;
   p.nmma = m <= 32 ? 32 : 64;
@@ -286,7 +286,11 @@ torch::Tensor int4_gemm(torch::Tensor x, torch::Tensor qweight, torch::Tensor sc
   const int n_tiles = (int)((n + kRows - 1) / kRows);
   const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
   const int k_blocks = (int)(k / kBK);
-  p.ksplit = std::max(1, std::min((sms + n_tiles - 1) / n_tiles, std::max(1, k_blocks / 4)));
+  const int want = std::max(1, std::min((sms + n_tiles - 1) / n_tiles, std::max(1, k_blocks / 4)));
+  const int per_split = (k_blocks + want - 1) / want;
+  p.ksplit = (k_blocks + per_split - 1) / per_split;       // no empty split: every slice is written
+  auto acc = torch::empty({(int64_t)p.ksplit, m, n}, x.options().dtype(torch::kFloat32));
+  p.acc = acc.data_ptr<float>();
   const CUtensorMap map_w = make_map(qweight.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_INT32, 4, k / 8, n, 8, kRows,
                                      CU_TENSOR_MAP_SWIZZLE_NONE);
   const CUtensorMap map_x = make_map(x.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, k, p.nmma, kBK, p.nmma,
@@ -300,7 +304,7 @@ torch::Tensor int4_gemm(torch::Tensor x, torch::Tensor qweight, torch::Tensor sc
   int4_gemm_kernel<<<dim3(n_tiles, p.ksplit), kThreads, kSmemBytes, at::cuda::getCurrentCUDAStream()>>>(
       map_w, map_x, p);
   C10_CUDA_KERNEL_LAUNCH_CHECK();
-  return acc.to(torch::kBFloat16);
+  return (p.ksplit == 1 ? acc.select(0, 0) : acc.sum(0)).to(torch::kBFloat16);
 }
 
 }  // namespace vrl
