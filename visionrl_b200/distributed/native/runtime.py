@@ -119,7 +119,7 @@ class NativeRolloutLauncher:
                driver_policy: Any | None = None, mesh: ProcessMesh | None = None) -> NativeRolloutRuntime:
         cfg = RolloutBackendConfig.from_cfg(config)
         spec = GenerationRuntimeSpec.from_value(runtime_spec)
-        mesh = mesh or ProcessMesh.build()
+        mesh = mesh or ProcessMesh.current() or ProcessMesh.build()
         if driver_policy is not None and cfg.allow_driver_gpu_overlap:
             executor = import_from_path(str(spec.executor_cls))(
                 driver_policy, **dict(spec.executor_kwargs))

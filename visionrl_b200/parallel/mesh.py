@@ -48,6 +48,11 @@ def init_distributed(backend: str | None = None, timeout_s: float = 1800.0) -> t
     return rank, world, local
 
 
+# mesh of the running job: components that are constructed far from the recipe (the rollout
+# runtime) pick it up here instead of rebuilding a default (sp = 1) mesh
+_CURRENT: list = [None]
+
+
 @dataclass
 class ProcessMesh:
     rank: int = 0
@@ -84,8 +89,15 @@ class ProcessMesh:
                 g = dist.new_group(ranks)
                 if rank in ranks:
                     dp_group = g
-        return cls(rank=rank, world_size=world, dp=dp, sp=sp, fsdp=fsdp, sp_group=sp_group,
+        mesh = cls(rank=rank, world_size=world, dp=dp, sp=sp, fsdp=fsdp, sp_group=sp_group,
                    dp_group=dp_group)
+        _CURRENT[0] = mesh
+        return mesh
+
+    @classmethod
+    def current(cls) -> "ProcessMesh | None":
+        """The mesh the running job was set up with (``None`` before any :meth:`build`)."""
+        return _CURRENT[0]
 
     @property
     def dp_rank(self) -> int:

@@ -86,6 +86,10 @@ def setup_run(cfg: Any) -> RunContext:
                              dp=int(cfg_path(cfg, "distributed.mesh.dp", -1) or -1),
                              fsdp=bool(cfg_path(cfg, "distributed.mesh.fsdp", True))) \
         if native else ProcessMesh()
+    # Sampling noise comes from the default generators: the ranks of one sequence-parallel group
+    # must draw identical noise (they hold replicas of the same samples), data-parallel ranks
+    # must not, and a rerun with the same seed must reproduce the run.
+    torch.manual_seed(int(tc.seed) + 1_000_003 * int(mesh.dp_rank))
     dtype_name = cfg_path(cfg, "model.dtype", None)
     if dtype_name is not None:
         from visionrl_b200.models.families.flow_policy import resolve_dtype
