@@ -60,12 +60,17 @@ def seeded_init(module: nn.Module, seed: int) -> None:
     Construction already initialised the weights; this only makes the draw a
     function of ``seed`` so every rank (and every run) builds identical weights.
     """
-    gen = torch.Generator().manual_seed(seed)
+    gens: dict = {}
     with torch.no_grad():
         for _, p in sorted(module.named_parameters()):
             if p.dim() >= 2:
+                # draw on the parameter's own device: a 14B-parameter model is built directly in
+                # HBM, never as an fp32 host copy
+                gen = gens.get(p.device)
+                if gen is None:
+                    gen = gens[p.device] = torch.Generator(device=p.device).manual_seed(seed)
                 std = float(p.float().std().item()) or 1.0 / math.sqrt(p.shape[-1])
-                p.copy_(torch.randn(p.shape, generator=gen) * std)
+                p.copy_(torch.randn(p.shape, generator=gen, device=p.device) * std)
 
 
 class NativeFlowPolicy(DiffusionPolicy):
@@ -103,7 +108,8 @@ class NativeFlowPolicy(DiffusionPolicy):
         dtype = resolve_dtype(spec.dtype)
         device = torch.device(spec.device)
         seed = int(native.get("init_seed", 0))
-        with torch.device("cpu"):
+        # large networks are constructed where they will live (fp32 there, cast afterwards)
+        with torch.device(device if device.type == "cuda" else "cpu"):
             transformer, decoder, text = cls._build_modules(arch, native)
         if native.get("random_init", True):
             seeded_init(transformer, seed)

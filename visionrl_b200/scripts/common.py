@@ -249,8 +249,11 @@ async def run_online_recipe(ctx: RunContext, parts: RecipeParts, reward_fn: Any,
             on_epoch_end(epoch, metrics, trainer)
         if tc.save_freq > 0 and (epoch + 1 - parts.first_epoch) % tc.save_freq == 0:
             checkpoint(f"checkpoint-{epoch + 1}", epoch + 1)
-    checkpoint("checkpoint-final", end)
-    logger.info("Training complete. Final checkpoint: %s", out_dir / "checkpoint-final")
+    if bool(cfg_path(cfg, "trainer.save_final", True)):
+        checkpoint("checkpoint-final", end)
+        logger.info("Training complete. Final checkpoint: %s", out_dir / "checkpoint-final")
+    else:
+        logger.info("Training complete (trainer.save_final=false: no final checkpoint written)")
     shutdown = getattr(collector, "shutdown", None)
     if callable(shutdown):
         await shutdown()
