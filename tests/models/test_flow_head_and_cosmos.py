@@ -56,3 +56,25 @@ def test_cosmos_request_reference_image_overrides_the_constructor_image():
     override = GenerationRequest(**base, metadata={"reference_image": "request.png"})
     assert ex.build_prepare_kwargs(generation_request=override, **hook) == {"reference_image": "request.png"}
     assert ex.respect_cfg_flag is False and (ex.family, ex.task) == ("cosmos", "v2w")
+
+
+def test_mmdit_with_routed_ffn_runs_and_trains():
+    from visionrl_b200.models.nn.mmdit import MMDiT, MMDiTConfig
+    from visionrl_b200.ops import moe
+
+    torch.manual_seed(0)
+    cfg = MMDiTConfig(num_layers=1, hidden_size=64, num_heads=2, in_channels=4, context_dim=32,
+                      pooled_dim=16, max_grid=8, moe_experts=4, moe_top_k=2)
+    net = MMDiT(cfg)
+    assert isinstance(net.blocks[0].mlp_x.ffn, moe.MoEFFN)
+    lat, ctx, pooled = torch.randn(2, 4, 8, 8), torch.randn(2, 5, 32), torch.randn(2, 16)
+    out = net(lat, torch.tensor([500.0, 200.0]), ctx, pooled)
+    assert out.shape == lat.shape
+    out.pow(2).mean().backward()
+    ffn = net.blocks[0].mlp_x.ffn
+    assert ffn.w1.grad is not None and ffn.gate.weight.grad is not None
+    # routing invariants of the oracle
+    w, idx = moe.route_reference(torch.randn(7, 4), 2)
+    assert torch.allclose(w.sum(-1), torch.ones(7)) and idx.shape == (7, 2)
+    perm, inv, off = moe.permute_reference(idx, 4)
+    assert off[-1].item() == 14 and torch.equal(perm[inv.long()].long(), torch.arange(14))

@@ -38,6 +38,8 @@ class MMDiTConfig:
     mlp_ratio: float = 4.0
     max_grid: int = 192          # largest latent side (in patches) of the position table
     qk_norm: bool = True
+    moe_experts: int = 0         # > 0: the image-stream FFN is a routed mixture of this many experts
+    moe_top_k: int = 2
 
     @classmethod
     def from_dict(cls, d: dict) -> "MMDiTConfig":
@@ -79,6 +81,21 @@ class StreamAttention(nn.Module):
         return qkv_prepare(self.qkv(x), self.heads, self.q_norm, self.k_norm)
 
 
+class _MoEAdapter(nn.Module):
+    """Routed feed-forward block with the calling convention of :class:`MLP`."""
+
+    def __init__(self, dim: int, hidden: int, experts: int, top_k: int):
+        super().__init__()
+        from visionrl_b200.ops.moe import MoEFFN
+
+        self.ffn = MoEFFN(dim, hidden, experts, min(top_k, experts))
+
+    def forward(self, x, gate=None, residual=None):
+        from visionrl_b200.ops.linear import linear_epilogue
+
+        return linear_epilogue(self.ffn(x), None, gate, residual)
+
+
 class _SplitStreams(torch.autograd.Function):
     """Joint ``[B, Sx + Sc, D]`` activations → contiguous image and text parts.
 
@@ -106,7 +123,8 @@ class JointBlock(nn.Module):
         self.attn_c = StreamAttention(d, cfg.num_heads, cfg.qk_norm, has_out=not context_pre_only)
         self.attn_x.set_aliases(("to_q", "to_k", "to_v"), "to_out.0")
         self.attn_c.set_aliases(("add_q_proj", "add_k_proj", "add_v_proj"), "to_add_out")
-        self.mlp_x = MLP(d, hidden)
+        self.mlp_x = _MoEAdapter(d, hidden, cfg.moe_experts, cfg.moe_top_k) if cfg.moe_experts > 0 \
+            else MLP(d, hidden)
         self.mlp_c = None if context_pre_only else MLP(d, hidden)
 
     def forward(self, x, c, temb_act):
