@@ -5,14 +5,13 @@
 //   warp 0      TMA producer: Q once, then K and V tiles through two-stage rings
 //   warp 1      MMA issuer and TMEM owner: S[j+1] = Q K[j+1]^T is issued before P[j] V[j], so the
 //               tensor core works on the next score tile while the softmax warps handle this one
-//   warps 2..5  softmax: thread r owns query row r.  Two passes over the score tile in TMEM (row
-//               maximum, then exponentials), probabilities written as bf16 into a 128-byte-swizzled
-//               shared tile that is the A operand of P V; the running output lives in registers and
-//               absorbs each P V partial product from TMEM with the usual rescale.
-// TMEM columns: the score buffers (128 each), then O0, O1 (D each).  Head dimension 128 double-buffers
-// the scores (512 columns, one CTA per SM); head dimension 64 keeps one score buffer (256 columns)
-// so that two CTAs share an SM and overlap each other's softmax and MMA phases.  Every wait is
-// bounded; on expiry the
+//   warps 2..9  softmax: two threads per query row, each owning 64 of the tile's 128 scores and
+//               half of the output columns.  Scores are read from TMEM once, probabilities are
+//               written as bf16 into a 128-byte-swizzled shared tile that is the A operand of P V;
+//               the running output lives in registers and absorbs each P V partial product from
+//               TMEM with the usual rescale.
+// TMEM columns: S0, S1 (128 each), then O0, O1 (D each); one CTA per SM.  Every wait is bounded; on
+// expiry the
 // role records a status code, raises the CTA's abort flag and all roles fall through to the
 // common exit where the TMEM is released.
 #include <ATen/cuda/CUDAContext.h>
@@ -32,7 +31,7 @@ namespace attn {
 using namespace ptx;
 
 constexpr int kTile = 128;                 // query rows per CTA and keys per step
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;              // TMA warp, MMA warp, 8 softmax warps
 constexpr uint32_t kBlockBytes = kTile * 128;   // one 64-column swizzle block of a 128-row tile
 constexpr uint32_t kPBytes = 2 * kBlockBytes;
 
@@ -43,11 +42,12 @@ template <int D>
 struct Cfg {
   static constexpr int kDBlocks = D / 64;
   static constexpr uint32_t kTileBytes = kDBlocks * kBlockBytes;      // Q, K or V tile
-  static constexpr uint32_t kSmemBytes = 5 * kTileBytes + kPBytes + 256;
-  static constexpr int kSBufs = D == 64 ? 1 : 2;                      // score buffers in TMEM
+  static constexpr uint32_t kXchBytes = 12 * kTile * 4;               // max/tag [2][2][128], sum/tag [2][128]
+  static constexpr uint32_t kSmemBytes = 5 * kTileBytes + kPBytes + kXchBytes + 256;
+  static constexpr int kSBufs = 2;                                    // score buffers in TMEM
   static constexpr uint32_t kOCol = kSBufs * kTile;                   // first O column in TMEM
-  static constexpr uint32_t kTmemCols = kOCol + 2 * D;                // 256 or 512
-  static constexpr int kCtasPerSm = D == 64 ? 2 : 1;
+  static constexpr uint32_t kTmemCols = 512;                          // S0 S1 O0 O1 (power of two)
+  static constexpr int kCtasPerSm = 1;
 };
 
 struct Params {
@@ -58,6 +58,26 @@ struct Params {
   int sq, skv;
   float scale_log2;       // softmax scale times log2(e)
 };
+
+// Publish `mine` in slot `me` with tag `tag`, then read the partner's value once its slot carries the
+// same tag.  Bounded: returns false when the partner does not show up.
+__device__ __forceinline__ bool exchange(float* vals, int* tags, int me, int partner, float mine, int tag,
+                                         float& theirs, volatile int* abort_flag) {
+  volatile float* v = vals;
+  volatile int* t = tags;
+  v[me] = mine;
+  __threadfence_block();
+  t[me] = tag;
+  for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+    if (t[partner] == tag) {
+      __threadfence_block();
+      theirs = v[partner];
+      return true;
+    }
+    if ((spin & 1023u) == 1023u && *abort_flag) return false;
+  }
+  return false;
+}
 
 template <int D>
 __global__ void __launch_bounds__(kThreads, Cfg<D>::kCtasPerSm)
@@ -73,7 +93,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   uint8_t* sk = sq + C::kTileBytes;            // [2]
   uint8_t* sv = sk + 2 * C::kTileBytes;        // [2]
   uint8_t* sp = sv + 2 * C::kTileBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sp + kPBytes);
+  float* xmax = reinterpret_cast<float*>(sp + kPBytes);          // [2 parities][2 halves][128]
+  int* xtag = reinterpret_cast<int*>(xmax + 4 * kTile);          // tile number + 1 of each xmax slot
+  float* xsum = reinterpret_cast<float*>(xtag + 4 * kTile);      // [2 halves][128]
+  int* xsum_tag = reinterpret_cast<int*>(xsum + 2 * kTile);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sp + kPBytes + C::kXchBytes);
   uint64_t* q_full = bars;
   uint64_t* k_full = bars + 1;     // [2]
   uint64_t* k_empty = bars + 3;    // [2]
@@ -97,11 +121,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
       mbar_init(&s_full[s], 1); mbar_init(&o_full[s], 1);
     }
-    mbar_init(p_full, 4);
+    mbar_init(p_full, 8);
     *abort_flag = 0;
     mbar_fence_init();
     fence_async_smem();
   }
+  for (int i = threadIdx.x; i < 4 * kTile; i += kThreads) xtag[i] = 0;
+  for (int i = threadIdx.x; i < 2 * kTile; i += kThreads) xsum_tag[i] = 0;
   if (warp == 1) tmem_alloc(tmem_slot, C::kTmemCols);
   tmem_fence_before();
   __syncthreads();
@@ -182,39 +208,52 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     if (!ok && atomicCAS(const_cast<int*>(abort_flag), 0, 1) == 0) atomicExch(p.status, kTimeoutMma);
   } else if (warp >= 2) {
     // --------------------------------------------------------------------------- softmax
+    // Eight warps: warp w may read TMEM lanes 32 (w % 4) .. +31, so two warps share every block
+    // of 32 query rows.  Partner threads split a row's 128 scores (and the D output columns) in
+    // halves, exchange their half-row maxima through shared memory once per key tile, and keep
+    // separate partial row sums that are combined at the very end.  Each thread reads its 64
+    // scores from TMEM once (both 32-column loads in flight together).
     const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int row_local = quarter * 32 + lane;
     const int row = q0 + row_local;
     const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
-    const uint32_t p_row = smem_u32(sp) + row_local * 128;
+    const uint32_t p_row = smem_u32(sp) + half * kBlockBytes + row_local * 128;
     const int swz = row_local & 7;
+    constexpr int DH = D / 2;                      // output columns owned by this thread
     float m = -INFINITY, l = 0.f;
-    float o[D];
+    float o[DH];
 #pragma unroll
-    for (int i = 0; i < D; ++i) o[i] = 0.f;
+    for (int i = 0; i < DH; ++i) o[i] = 0.f;
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
-      const int sb = j % C::kSBufs;
-      ok = __all_sync(0xffffffffu, mbar_wait(&s_full[sb], (j / C::kSBufs) & 1u, abort_flag));
+      const int sb = j & 1;
+      ok = __all_sync(0xffffffffu, mbar_wait(&s_full[sb], (j >> 1) & 1u, abort_flag));
       if (!ok) break;
       tmem_fence_after();
-      const int valid = min(kTile, p.skv - j * kTile);
-      const uint32_t s_addr = lane_base + sb * kTile;
-      // pass 1: row maximum
+      const int valid = min(kTile, p.skv - j * kTile) - half * 64;     // valid columns of my half
+      uint32_t r[64];
+      tmem_ld32(lane_base + sb * kTile + half * 64, r);
+      tmem_ld32(lane_base + sb * kTile + half * 64 + 32, r + 32);
+      tmem_ld_wait();
       float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld32(s_addr + c * 32, r);
-        tmem_ld_wait();
-        if (valid == kTile) {                          // only the last key tile is ever partial
+      if (valid >= 64) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
-        } else {
+        for (int i = 0; i < 64; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+      } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (c * 32 + i < valid) mx = fmaxf(mx, __uint_as_float(r[i]));
-        }
+        for (int i = 0; i < 64; ++i)
+          if (i < valid) mx = fmaxf(mx, __uint_as_float(r[i]));
+      }
+      // exchange with the partner thread of the other half (slots alternate with the tile parity;
+      // a tagged slot is rewritten two tiles later, after the partner has published its next one)
+      {
+        float other;
+        ok = __all_sync(0xffffffffu,
+                        exchange(xmax, xtag, ((j & 1) * 2 + half) * kTile + row_local,
+                                 ((j & 1) * 2 + (half ^ 1)) * kTile + row_local, mx, j + 1, other, abort_flag));
+        if (!ok) break;
+        mx = fmaxf(mx, other);
       }
       const float m_new = fmaxf(m, mx * p.scale_log2);
       const float corr = exp2f(m - m_new);              // 0 on the first tile (m = -inf)
@@ -224,54 +263,43 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         if (!ok) break;
         tmem_fence_after();
       }
-      // pass 2: probabilities -> shared memory (bf16, swizzled K-major), row sum
       float rowsum = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld32(s_addr + c * 32, r);
-        tmem_ld_wait();
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          float pv[8];
-          if (valid == kTile) {
+      for (int g = 0; g < 8; ++g) {
+        float pv[8];
+        if (valid >= 64) {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              pv[i] = exp2f(__uint_as_float(r[g * 8 + i]) * p.scale_log2 - m_new);
-              rowsum += pv[i];
-            }
-          } else {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const int col = c * 32 + g * 8 + i;
-              const float e = exp2f(__uint_as_float(r[g * 8 + i]) * p.scale_log2 - m_new);
-              pv[i] = col < valid ? e : 0.f;
-              rowsum += pv[i];
-            }
+          for (int i = 0; i < 8; ++i) {
+            pv[i] = exp2f(__uint_as_float(r[g * 8 + i]) * p.scale_log2 - m_new);
+            rowsum += pv[i];
           }
-          const bf16x8 packed = pack8(pv);
-          const uint32_t chunk = (uint32_t)((c & 1) * 4 + g);
-          const uint32_t addr = p_row + (c >> 1) * kBlockBytes + ((chunk ^ (uint32_t)swz) << 4);
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(packed.u.x),
-                       "r"(packed.u.y), "r"(packed.u.z), "r"(packed.u.w)
-                       : "memory");
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float e = exp2f(__uint_as_float(r[g * 8 + i]) * p.scale_log2 - m_new);
+            pv[i] = (g * 8 + i) < valid ? e : 0.f;
+            rowsum += pv[i];
+          }
         }
+        const bf16x8 packed = pack8(pv);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(
+                         p_row + (((uint32_t)g ^ (uint32_t)swz) << 4)),
+                     "r"(packed.u.x), "r"(packed.u.y), "r"(packed.u.z), "r"(packed.u.w)
+                     : "memory");
       }
       fence_async_smem();
       tmem_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full);
-      // absorb the previous partial product: o = (o + P[j-1] V[j-1]) * corr
+      // absorb my half of the previous partial product: o = (o + P[j-1] V[j-1]) * corr
       if (j > 0) {
-        const uint32_t o_addr = lane_base + C::kOCol + ((j - 1) & 1) * D;
+        const uint32_t o_addr = lane_base + C::kOCol + ((j - 1) & 1) * D + half * DH;
+        uint32_t q[DH];
 #pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld32(o_addr + c * 32, r);
-          tmem_ld_wait();
+        for (int c = 0; c < DH / 32; ++c) tmem_ld32(o_addr + c * 32, q + c * 32);
+        tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o[c * 32 + i] = (o[c * 32 + i] + __uint_as_float(r[i])) * corr;
-        }
+        for (int i = 0; i < DH; ++i) o[i] = (o[i] + __uint_as_float(q[i])) * corr;
       }
       l = l * corr + rowsum;
       m = m_new;
@@ -283,23 +311,27 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     if (ok) {
       tmem_fence_after();
       const int last = n_tiles - 1;
-      const uint32_t o_addr = lane_base + C::kOCol + (last & 1) * D;
+      const uint32_t o_addr = lane_base + C::kOCol + (last & 1) * D + half * DH;
+      // combine the partners' partial row sums (both are relative to the same running maximum)
+      float other_l = 0.f;
+      ok = __all_sync(0xffffffffu, exchange(xsum, xsum_tag, half * kTile + row_local,
+                                            (half ^ 1) * kTile + row_local, l, 1, other_l, abort_flag));
+      l += other_l;
       const float inv = 1.f / l;
+      uint32_t q[DH];
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(o_addr + c * 32, r);
-        tmem_ld_wait();
+      for (int c = 0; c < DH / 32; ++c) tmem_ld32(o_addr + c * 32, q + c * 32);
+      tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) o[c * 32 + i] = (o[c * 32 + i] + __uint_as_float(r[i])) * inv;
+      for (int i = 0; i < DH; ++i) o[i] = (o[i] + __uint_as_float(q[i])) * inv;
+      if (ok && row < p.sq) {
+        __nv_bfloat16* dst = p.out + (((int64_t)bi * p.sq + row) * p.heads + hi) * D + half * DH;
+#pragma unroll
+        for (int g = 0; g < DH / 8; ++g) *reinterpret_cast<bf16x8*>(dst + g * 8) = pack8(&o[g * 8]);
+        if (half == 0) p.lse[(int64_t)bh * p.sq + row] = (m + log2f(l)) * 0.6931471805599453f;
       }
-      if (row < p.sq) {
-        __nv_bfloat16* dst = p.out + (((int64_t)bi * p.sq + row) * p.heads + hi) * D;
-#pragma unroll
-        for (int g = 0; g < D / 8; ++g) *reinterpret_cast<bf16x8*>(dst + g * 8) = pack8(&o[g * 8]);
-        p.lse[(int64_t)bh * p.sq + row] = (m + log2f(l)) * 0.6931471805599453f;
-      }
-    } else if (lane == 0) {
+    }
+    if (!ok && lane == 0) {
       if (atomicCAS(const_cast<int*>(abort_flag), 0, 1) == 0) atomicExch(p.status, kTimeoutSoftmax);
     }
   }
