@@ -700,3 +700,34 @@ def test_int4_tensor_core_gemm_matches_dequantised_matmul(m, nk):
     assert torch.allclose(got.float(), ref, atol=4e-2, rtol=2e-2)
     again = ext.int4_gemm(x, packed, scales, None, 128)
     assert torch.allclose(again.float(), ref - bias.float(), atol=4e-2, rtol=2e-2)
+
+
+@pytest.mark.gpu
+def test_weight_gradients_accumulate_in_place_across_backward_calls():
+    from visionrl_b200.ops.linear import accumulate_weight_grads_in_place, gelu_mlp, linear
+
+    torch.manual_seed(17)
+    d, hid = 256, 512
+    w = (torch.randn(d, d, device="cuda") * 0.05).bfloat16().requires_grad_()
+    w1 = (torch.randn(hid, d, device="cuda") * 0.05).bfloat16().requires_grad_()
+    w2 = (torch.randn(d, hid, device="cuda") * 0.05).bfloat16().requires_grad_()
+    params = [w, w1, w2]
+    for p in params:
+        p.grad = torch.zeros_like(p)
+    buffers = [p.grad.data_ptr() for p in params]
+    ref = [torch.zeros_like(p, dtype=torch.float32) for p in params]
+    for step in range(3):
+        x = torch.randn(4, 100, d, device="cuda").bfloat16()
+        with accumulate_weight_grads_in_place():
+            (gelu_mlp(linear(x, w), w1, None, w2, None).float().pow(2).mean() * 50).backward()
+        xf = x.float()
+        pf = [p.detach().float().requires_grad_() for p in params]
+        h = torch.nn.functional.linear(xf, pf[0])
+        y = torch.nn.functional.linear(torch.nn.functional.gelu(torch.nn.functional.linear(h, pf[1]),
+                                                                approximate="tanh"), pf[2])
+        (y.pow(2).mean() * 50).backward()
+        for r, q in zip(ref, pf):
+            r += q.grad
+    for p, ptr, r in zip(params, buffers, ref):
+        assert p.grad.data_ptr() == ptr                      # still the same buffer
+        assert _rel(p.grad, r) < 4e-2

@@ -69,5 +69,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_bf16", &vrl::gemm_bf16);
   m.def("gemm_bf16_dual", &vrl::gemm_bf16_dual);
   m.def("gemm_allgather", &vrl::gemm_allgather);
+  m.def("gemm_bf16_acc", &vrl::gemm_bf16_acc);
   m.def("gemm_last_status", &vrl::gemm_last_status);
 }

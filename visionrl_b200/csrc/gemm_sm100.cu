@@ -476,7 +476,8 @@ static std::vector<torch::Tensor> gemm_impl(torch::Tensor a, torch::Tensor b,
                                             c10::optional<torch::Tensor> gate,
                                             c10::optional<torch::Tensor> residual, int64_t act,
                                             int64_t rows_per_gate, bool a_mn_major, bool b_mn_major,
-                                            bool out_fp32, bool dual);
+                                            bool out_fp32, bool dual,
+                                            c10::optional<torch::Tensor> out_given = c10::nullopt);
 
 torch::Tensor gemm_bf16(torch::Tensor a, torch::Tensor b, c10::optional<torch::Tensor> bias,
                         c10::optional<torch::Tensor> gate, c10::optional<torch::Tensor> residual,
@@ -484,6 +485,14 @@ torch::Tensor gemm_bf16(torch::Tensor a, torch::Tensor b, c10::optional<torch::T
                         bool out_fp32) {
   return gemm_impl(a, b, bias, gate, residual, act, rows_per_gate, a_mn_major, b_mn_major, out_fp32,
                    false)[0];
+}
+
+// acc += op(a) op(b)^T in place (weight-gradient accumulation straight into the flat gradient buffer:
+// the existing values come in through the residual path and leave through the same tile's store).
+void gemm_bf16_acc(torch::Tensor a, torch::Tensor b, torch::Tensor acc, bool a_mn_major, bool b_mn_major) {
+  TORCH_CHECK(acc.is_cuda() && acc.dim() == 2 && acc.scalar_type() == torch::kBFloat16 && acc.is_contiguous() &&
+              reinterpret_cast<uintptr_t>(acc.data_ptr()) % 16 == 0, "gemm_bf16_acc: contiguous aligned bf16 target");
+  gemm_impl(a, b, c10::nullopt, c10::nullopt, acc, 0, 0, a_mn_major, b_mn_major, false, false, acc);
 }
 
 // (activation(a b^T + bias), a b^T + bias): the second tensor is what the activation's backward needs.
@@ -497,7 +506,8 @@ static std::vector<torch::Tensor> gemm_impl(torch::Tensor a, torch::Tensor b,
                                             c10::optional<torch::Tensor> gate,
                                             c10::optional<torch::Tensor> residual, int64_t act,
                                             int64_t rows_per_gate, bool a_mn_major, bool b_mn_major,
-                                            bool out_fp32, bool dual) {
+                                            bool out_fp32, bool dual,
+                                            c10::optional<torch::Tensor> out_given) {
   using namespace gemm;
   TORCH_CHECK(act >= 0 && act <= 3, "gemm_bf16: unknown epilogue activation");
   TORCH_CHECK(act != 3 || (residual.has_value() && !gate.has_value() && !out_fp32),
@@ -524,7 +534,13 @@ static std::vector<torch::Tensor> gemm_impl(torch::Tensor a, torch::Tensor b,
   TORCH_CHECK(a.stride(0) % 8 == 0 && b.stride(0) % 8 == 0, "gemm_bf16: row pitch must be a multiple of 8");
   TORCH_CHECK(reinterpret_cast<uintptr_t>(a.data_ptr()) % 16 == 0 &&
               reinterpret_cast<uintptr_t>(b.data_ptr()) % 16 == 0, "gemm_bf16: 16-byte alignment");
-  auto out = torch::empty({m, n}, a.options().dtype(out_fp32 ? torch::kFloat32 : torch::kBFloat16));
+  torch::Tensor out;
+  if (out_given.has_value()) {
+    out = *out_given;
+    TORCH_CHECK(!out_fp32 && out.size(0) == m && out.size(1) == n, "gemm_bf16: output shape mismatch");
+  } else {
+    out = torch::empty({m, n}, a.options().dtype(out_fp32 ? torch::kFloat32 : torch::kBFloat16));
+  }
   torch::Tensor pre = dual ? torch::empty({m, n}, a.options()) : torch::Tensor();
   if (m == 0 || n == 0) return {out, pre};
   TORCH_CHECK(k > 0, "gemm_bf16: empty contraction");
@@ -556,7 +572,10 @@ static std::vector<torch::Tensor> gemm_impl(torch::Tensor a, torch::Tensor b,
   if (residual.has_value()) {
     res_c = residual->to(torch::kBFloat16).contiguous();
     TORCH_CHECK(res_c.numel() == m * n);
-    if (reinterpret_cast<uintptr_t>(res_c.data_ptr()) % 16 != 0) res_c = res_c.clone();
+    if (reinterpret_cast<uintptr_t>(res_c.data_ptr()) % 16 != 0) {
+      TORCH_CHECK(!out_given.has_value(), "gemm_bf16: in-place accumulation needs a 16-byte aligned target");
+      res_c = res_c.clone();
+    }
     p.residual = reinterpret_cast<const __nv_bfloat16*>(res_c.data_ptr());
   }
   p.status = status_word(a.get_device());

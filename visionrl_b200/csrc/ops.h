@@ -118,6 +118,7 @@ std::vector<torch::Tensor> gemm_bf16_dual(torch::Tensor a, torch::Tensor b,
 torch::Tensor gemm_allgather(torch::Tensor x, torch::Tensor peer_ptrs, torch::Tensor full,
                              torch::Tensor ready, c10::optional<torch::Tensor> bias, int64_t act,
                              int64_t rank, int64_t world);
+void gemm_bf16_acc(torch::Tensor a, torch::Tensor b, torch::Tensor acc, bool a_mn_major, bool b_mn_major);
 int64_t gemm_last_status();
 
 }  // namespace vrl

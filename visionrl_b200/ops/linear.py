@@ -11,6 +11,8 @@ the accumulator in tensor memory → epilogue from ``tcgen05.ld``); anything els
 
 from __future__ import annotations
 
+import contextlib
+
 import torch
 import torch.nn.functional as F
 
@@ -71,6 +73,35 @@ def gemm_tn(a, b, out_fp32: bool = False):
     return _ext.load().gemm_bf16(a, b, None, None, None, 0, 0, True, True, out_fp32)
 
 
+# While the trainer's backward pass runs, weight gradients are added straight into the parameters'
+# existing ``.grad`` buffers by the GEMM epilogue (no temporary, no separate accumulation kernel).
+# Functional uses of autograd (``torch.autograd.grad``) never enable this.
+_ACCUMULATE_IN_PLACE = [False]
+
+
+@contextlib.contextmanager
+def accumulate_weight_grads_in_place(enabled: bool = True):
+    previous = _ACCUMULATE_IN_PLACE[0]
+    _ACCUMULATE_IN_PLACE[0] = bool(enabled)
+    try:
+        yield
+    finally:
+        _ACCUMULATE_IN_PLACE[0] = previous
+
+
+def _weight_grad(gy2, x2, param):
+    """``gy2.T @ x2`` — returned, or added into ``param.grad`` in place (then ``None``)."""
+    from visionrl_b200.ops import _ext
+
+    grad = getattr(param, "grad", None)
+    if (_ACCUMULATE_IN_PLACE[0] and grad is not None and grad.dtype == torch.bfloat16
+            and grad.is_contiguous() and grad.shape == (gy2.shape[1], x2.shape[1])
+            and grad.data_ptr() % 16 == 0 and _ext.has("gemm_bf16_acc")):
+        _ext.load().gemm_bf16_acc(gy2, x2, grad, True, True)
+        return None
+    return gemm_tn(gy2, x2)
+
+
 class _LinearFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, bias):
@@ -79,6 +110,7 @@ class _LinearFn(torch.autograd.Function):
             x2 = x2.contiguous()
         y = gemm_nt(x2, w, bias)
         ctx.save_for_backward(x2, w)
+        ctx.weight_param = w            # the parameter object itself (its .grad buffer is the target)
         ctx.has_bias = bias is not None
         ctx.x_shape = x.shape
         return y.view(*x.shape[:-1], w.shape[0])
@@ -93,7 +125,7 @@ class _LinearFn(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             gx = gemm_nn(gy2, w).view(ctx.x_shape)
         if ctx.needs_input_grad[1]:
-            gw = gemm_tn(gy2, x2)
+            gw = _weight_grad(gy2, x2, ctx.weight_param)
         if ctx.has_bias and ctx.needs_input_grad[2]:
             from visionrl_b200.ops import _ext
 
@@ -152,6 +184,7 @@ class _GeluMLPFn(torch.autograd.Function):
         a, h = _ext.load().gemm_bf16_dual(x2, w1, b1, _ACTS["gelu_tanh"])
         y = gemm_nt(a, w2, b2)
         ctx.save_for_backward(x2, w1, w2, h, a)
+        ctx.w1_param, ctx.w2_param = w1, w2
         ctx.has_b1, ctx.has_b2 = b1 is not None, b2 is not None
         ctx.x_shape = x.shape
         return y.view(*x.shape[:-1], w2.shape[0])
@@ -169,11 +202,11 @@ class _GeluMLPFn(torch.autograd.Function):
         gh = ext.gemm_bf16(gy2, w2, None, None, h, 3, 0, False, True, False)
         gx = gw1 = gb1 = gw2 = gb2 = None
         if ctx.needs_input_grad[3]:
-            gw2 = gemm_tn(gy2, a)
+            gw2 = _weight_grad(gy2, a, ctx.w2_param)
         if ctx.has_b2 and ctx.needs_input_grad[4]:
             gb2 = ext.colsum(gy2).to(gy2.dtype)
         if ctx.needs_input_grad[1]:
-            gw1 = gemm_tn(gh, x2)
+            gw1 = _weight_grad(gh, x2, ctx.w1_param)
         if ctx.has_b1 and ctx.needs_input_grad[2]:
             gb1 = ext.colsum(gh).to(gh.dtype)
         if ctx.needs_input_grad[0]:

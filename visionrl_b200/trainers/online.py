@@ -212,7 +212,11 @@ class OnlineTrainer(Trainer):
         if self.accelerator is not None:
             self.accelerator.backward(loss)
         else:
-            loss.backward()
+            from visionrl_b200.ops.linear import accumulate_weight_grads_in_place
+
+            # weight gradients are summed into the existing .grad buffers by the GEMM itself
+            with accumulate_weight_grads_in_place():
+                loss.backward()
 
     def _clip_and_step(self, optimizer: Any) -> Any:
         """Clip, step, zero.  Returns the pre-clip gradient norm (tensor or float)."""
