@@ -538,6 +538,58 @@ def test_flash_attention_token_major_views_and_dispatch():
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("shape", [(1, 1, 64, 64, 64), (2, 2, 130, 77, 64), (1, 2, 300, 512, 128),
+                                   (1, 4, 515, 515, 128), (2, 3, 1178, 1178, 64)])
+def test_flash_attention_backward_matches_fp32_autograd(shape):
+    from visionrl_b200.ops import _ext
+    from visionrl_b200.ops.attention import (attention_reference, flash_attention_backward,
+                                             flash_attention_forward)
+
+    b, h, sq, skv, d = shape
+    torch.manual_seed(18)
+    q = torch.randn(b, h, sq, d, device="cuda").bfloat16()
+    k = torch.randn(b, h, skv, d, device="cuda").bfloat16()
+    v = torch.randn(b, h, skv, d, device="cuda").bfloat16()
+    dout = torch.randn(b, h, sq, d, device="cuda").bfloat16()
+    out, lse = flash_attention_forward(q, k, v, d ** -0.5)
+    dq, dk, dv = flash_attention_backward(dout, q, k, v, out, lse, d ** -0.5)
+    torch.cuda.synchronize()
+    assert _ext.load().flash_attn_last_status() == 0
+    qf, kf, vf = (t.float().requires_grad_(True) for t in (q, k, v))
+    ref = torch.autograd.grad(attention_reference(qf, kf, vf), (qf, kf, vf), dout.float())
+    for got, want in zip((dq, dk, dv), ref):
+        assert got.shape == want.shape
+        err = (got.float() - want).abs().max().item()
+        assert err <= 2e-2 * max(1.0, want.abs().max().item()), err
+    # same inputs, same bits: no atomics anywhere in the backward
+    again = flash_attention_backward(dout, q, k, v, out, lse, d ** -0.5)
+    assert all(torch.equal(a, b_) for a, b_ in zip(again, (dq, dk, dv)))
+
+
+@pytest.mark.gpu
+def test_differentiable_attention_runs_own_kernels_on_token_major_views():
+    from visionrl_b200.ops import attention as A
+
+    torch.manual_seed(19)
+    b, s, h, d = 2, 333, 4, 64
+    bufs = [torch.randn(b, s, h, d, device="cuda").bfloat16().requires_grad_(True) for _ in range(3)]
+    w = torch.randn(b, h, s, d, device="cuda").bfloat16()
+    grads = {}
+    for impl in ("own", "library"):
+        A.set_backward_impl(impl)
+        try:
+            q, k, v = (t.transpose(1, 2) for t in bufs)
+            out = A.attention(q, k, v)
+            grads[impl] = torch.autograd.grad((out.float() * w.float()).sum(), bufs)
+            if impl == "own":
+                assert type(out.grad_fn).__name__ == "_FlashAttnFnBackward"
+        finally:
+            A.set_backward_impl("own")
+    for a, b_ in zip(grads["own"], grads["library"]):
+        assert torch.allclose(a.float(), b_.float(), atol=3e-2, rtol=3e-2)
+
+
+@pytest.mark.gpu
 def test_joint_qkv_prepare_matches_concatenated_reference():
     from visionrl_b200.ops.qkv import joint_qkv_prepare, qkv_prepare_reference
 

@@ -21,6 +21,7 @@
 #include <map>
 #include <mutex>
 
+#include "attn_host.cuh"
 #include "common.cuh"
 #include "ops.h"
 #include "sm100_ptx.cuh"
@@ -618,45 +619,7 @@ flash_fwd_small_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 }
 
 // --------------------------------------------------------------------------------- host side
-using EncodeFn = PFN_cuTensorMapEncodeTiled_v12000;
-
-static EncodeFn encode_fn() {
-  static EncodeFn fn = [] {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    C10_CUDA_CHECK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q));
-    TORCH_CHECK(ptr != nullptr && q == cudaDriverEntryPointSuccess,
-                "cuTensorMapEncodeTiled is not available from this driver");
-    return reinterpret_cast<EncodeFn>(ptr);
-  }();
-  return fn;
-}
-
-// A [B, H, S, D] bf16 view with unit stride in D: dims {D, S, H, B}; box = 64 columns x 128 rows of
-// one (batch, head).  Rows past S read as zeros.
-static CUtensorMap make_map4(const torch::Tensor& t) {
-  CUtensorMap map;
-  cuuint64_t dims[4] = {(cuuint64_t)t.size(3), (cuuint64_t)t.size(2), (cuuint64_t)t.size(1),
-                        (cuuint64_t)t.size(0)};
-  cuuint64_t strides[3] = {(cuuint64_t)t.stride(2) * 2, (cuuint64_t)t.stride(1) * 2,
-                           (cuuint64_t)t.stride(0) * 2};
-  cuuint32_t box[4] = {64, (cuuint32_t)kTile, 1, 1};
-  cuuint32_t elem[4] = {1, 1, 1, 1};
-  CUresult rc = encode_fn()(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, t.data_ptr(), dims, strides, box,
-                            elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  TORCH_CHECK(rc == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with code ", (int)rc);
-  return map;
-}
-
-// A tensor the 4-D map can describe as is: unit stride in D, other strides multiples of 16 bytes.
-static torch::Tensor mappable(torch::Tensor t) {
-  const bool ok = t.stride(3) == 1 && t.stride(0) % 8 == 0 && t.stride(1) % 8 == 0 && t.stride(2) % 8 == 0 &&
-                  reinterpret_cast<uintptr_t>(t.data_ptr()) % 16 == 0;
-  return ok ? t : t.contiguous();
-}
-
-static int* status_word(int device) {
+int* status_word(int device) {
   static std::map<int, int*> words;
   static std::mutex mu;
   std::lock_guard<std::mutex> lock(mu);
@@ -717,20 +680,16 @@ std::vector<torch::Tensor> flash_attn_fwd(torch::Tensor q, torch::Tensor k, torc
   k = mappable(k);
   v = mappable(v);
   const c10::cuda::CUDAGuard guard(q.device());
-  static thread_local bool context_bound = false;   // the encoder is a driver entry point
-  if (!context_bound) {
-    C10_CUDA_CHECK(cudaFree(nullptr));
-    context_bound = true;
-  }
+  bind_context();
   // token-major output, returned as a [B, H, S, D] view: merging heads afterwards is free
   auto out_tm = torch::empty({b, sq, h, d}, q.options());
   auto out = out_tm.transpose(1, 2);
   auto lse = torch::empty({b, h, sq}, q.options().dtype(torch::kFloat32));
   if (b * h == 0 || sq == 0) return {out, lse};
   TORCH_CHECK(skv > 0, "flash_attn_fwd: empty key sequence");
-  const CUtensorMap mq = make_map4(q);
-  const CUtensorMap mk = make_map4(k);
-  const CUtensorMap mv = make_map4(v);
+  const CUtensorMap mq = make_map4(q, kTile);
+  const CUtensorMap mk = make_map4(k, kTile);
+  const CUtensorMap mv = make_map4(v, kTile);
   Params p{};
   p.out = reinterpret_cast<__nv_bfloat16*>(out_tm.data_ptr());
   p.heads = (int)h;

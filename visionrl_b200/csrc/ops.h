@@ -108,6 +108,10 @@ torch::Tensor groupnorm_nhwc(torch::Tensor x, torch::Tensor weight, torch::Tenso
 std::vector<torch::Tensor> flash_attn_fwd(torch::Tensor q, torch::Tensor k, torch::Tensor v, double scale);
 int64_t flash_attn_last_status();
 
+// attention_bwd_sm100.cu
+std::vector<torch::Tensor> flash_attn_bwd(torch::Tensor dout, torch::Tensor q, torch::Tensor k, torch::Tensor v,
+                                          torch::Tensor out, torch::Tensor lse, double scale);
+
 // gemm_sm100.cu
 torch::Tensor gemm_bf16(torch::Tensor a, torch::Tensor b, c10::optional<torch::Tensor> bias,
                         c10::optional<torch::Tensor> gate, c10::optional<torch::Tensor> residual,

@@ -22,7 +22,7 @@ _LAUNCHES = {
     "sde_step_fwd": 2, "sde_step_bwd": 1, "token_loss_fwd": 1, "per_sample_mse": 2,
     "sum_squares": 2, "colsum": 1, "ulysses_scatter": 1, "p2p_broadcast_versioned": 2, "wait_flag": 1, "adamw_flat": 1, "adaln_fwd": 1, "adaln_bwd": 1, "rmsnorm_fwd": 1,
     "rmsnorm_bwd": 1, "qkv_prepare_fwd": 1, "qkv_prepare_bwd": 1, "gemm_bf16": 1,
-    "flash_attn_bwd": 2, "token_logprob_fwd": 1, "token_logprob_bwd": 1,
+    "flash_attn_bwd": 3, "token_logprob_fwd": 1, "token_logprob_bwd": 1,
     "decode_attention": 1, "rs_sum_slice": 1, "adamw_slice_broadcast": 1, "int4_gemv": 1,
     "sample_tokens": 1, "lse_chunk_update": 1, "softmax_grad_chunk": 1, "group_advantages": 1,
     "groupnorm_nhwc": 2, "gemm_bf16_acc": 1, "gemm_allgather": 1, "int4_gemm": 1, "gemm_bf16_dual": 1, "gate_residual_fwd": 1, "gate_residual_bwd": 1, "flash_attn_fwd": 1, "moe_gate_topk": 1, "moe_permute": 1, "moe_gather_rows": 1, "moe_combine": 1,

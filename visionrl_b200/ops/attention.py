@@ -7,6 +7,7 @@ The oracle is ``softmax(q k^T / sqrt(D)) v`` in fp32.
 from __future__ import annotations
 
 import math
+import os
 
 import torch
 import torch.nn.functional as F
@@ -31,6 +32,12 @@ def _native_ok(q, k, v) -> bool:
             and _ext.kernels_enabled() and _ext.has("flash_attn_fwd"))
 
 
+def _has_backward() -> bool:
+    from visionrl_b200.ops import _ext
+
+    return _ext.has("flash_attn_bwd")
+
+
 def flash_attention_forward(q, k, v, scale: float):
     """tcgen05 forward kernel: returns ``(out, lse)`` with ``lse[B, H, S]`` in natural log."""
     from visionrl_b200.ops import _ext
@@ -39,17 +46,62 @@ def flash_attention_forward(q, k, v, scale: float):
     return out, lse
 
 
+def flash_attention_backward(dout, q, k, v, out, lse, scale: float):
+    """tcgen05 backward kernels (delta pre-pass, dK/dV pass, dQ pass): returns ``(dq, dk, dv)``."""
+    from visionrl_b200.ops import _ext
+
+    return _ext.load().flash_attn_bwd(dout, q, k, v, out, lse, float(scale))
+
+
+class _FlashAttnFn(torch.autograd.Function):
+    """Differentiable attention on the sm_100a kernels: forward saves ``out`` and the row
+    log-sum-exp, backward recomputes the probabilities tile by tile."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, scale):
+        out, lse = flash_attention_forward(q, k, v, scale)
+        ctx.save_for_backward(q, k, v, out, lse)
+        ctx.scale = scale
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, out, lse = ctx.saved_tensors
+        dq, dk, dv = flash_attention_backward(dout, q, k, v, out, lse, ctx.scale)
+        return dq, dk, dv, None
+
+
+# Which implementation differentiable calls use: "own" = the tcgen05 forward/backward pair above,
+# "library" = torch's fused scaled_dot_product_attention.  Chosen per process.
+_BACKWARD_IMPL = os.environ.get("VRL_ATTENTION_BACKWARD", "own")
+
+
+def set_backward_impl(name: str) -> None:
+    global _BACKWARD_IMPL
+    if name not in ("own", "library"):
+        raise ValueError(f"attention backward implementation must be 'own' or 'library', got {name!r}")
+    _BACKWARD_IMPL = name
+
+
+def backward_impl() -> str:
+    return _BACKWARD_IMPL
+
+
 def attention(q, k, v, causal: bool = False, scale: float | None = None):
     """Bidirectional (or causal) attention over ``[B, H, S, D]``.
 
-    Calls that need no gradient (rollout sampling, frozen-reference passes, reward towers) run
-    the hand-written sm_100a forward kernel; differentiable calls use the library's fused
-    forward/backward pair until the tcgen05 backward lands.
+    Bidirectional bf16 calls with head dimension 64 or 128 run the hand-written sm_100a kernels:
+    the forward alone when no gradient is needed (rollout sampling, frozen-reference passes,
+    reward towers), the forward/backward pair otherwise.  Causal calls and other shapes use the
+    library's fused attention.
     """
     scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
     needs_grad = torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad)
-    if not causal and not needs_grad and _native_ok(q, k, v):
-        return flash_attention_forward(q, k, v, scale)[0]
+    if not causal and _native_ok(q, k, v):
+        if not needs_grad:
+            return flash_attention_forward(q, k, v, scale)[0]
+        if _BACKWARD_IMPL == "own" and _has_backward():
+            return _FlashAttnFn.apply(q, k, v, scale)
     if q.is_cuda:
         return F.scaled_dot_product_attention(q, k, v, is_causal=causal, scale=scale)
     return attention_reference(q, k, v, causal, scale)

@@ -93,8 +93,8 @@ def _weight_grad(gy2, x2, param):
     """``gy2.T @ x2`` — returned, or added into ``param.grad`` in place (then ``None``)."""
     from visionrl_b200.ops import _ext
 
-    grad = getattr(param, "grad", None)
-    if (_ACCUMULATE_IN_PLACE[0] and grad is not None and grad.dtype == torch.bfloat16
+    grad = param.grad if (_ACCUMULATE_IN_PLACE[0] and param is not None and param.is_leaf) else None
+    if (grad is not None and grad.dtype == torch.bfloat16
             and grad.is_contiguous() and grad.shape == (gy2.shape[1], x2.shape[1])
             and grad.data_ptr() % 16 == 0 and _ext.has("gemm_bf16_acc")):
         _ext.load().gemm_bf16_acc(gy2, x2, grad, True, True)

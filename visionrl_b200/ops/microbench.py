@@ -141,6 +141,24 @@ def bench_attention(args) -> dict:
                 "ms": round(t, 4), "tflops": round(flops / t / 1e9, 1)})
     if args.peak_tflops:
         out["frac_of_measured_peak"] = round(out["tflops"] / args.peak_tflops, 3)
+    if args.backward:
+        from visionrl_b200.ops.attention import flash_attention_backward, flash_attention_forward
+
+        scale = d ** -0.5
+        dout = torch.randn_like(q)
+        o, lse = flash_attention_forward(q, k, v, scale)
+        t_b = _time(lambda: flash_attention_backward(dout, q, k, v, o, lse, scale), args.iters, args.warmup, flush)
+        ql, kl, vl = (t.detach().clone().requires_grad_(True) for t in (q, k, v))
+        ol = torch.nn.functional.scaled_dot_product_attention(ql, kl, vl)
+        t_lb = _time(lambda: torch.autograd.grad(ol, (ql, kl, vl), dout, retain_graph=True),
+                     args.iters, args.warmup, flush)
+        qf, kf, vf = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+        ref = torch.autograd.grad(torch.nn.functional.scaled_dot_product_attention(qf, kf, vf), (qf, kf, vf),
+                                  dout.float())
+        got = flash_attention_backward(dout, q, k, v, o, lse, scale)
+        out.update({"bwd_ms": round(t_b, 4), "bwd_tflops": round(2.5 * flops / t_b / 1e9, 1),
+                    "sdpa_bwd_ms": round(t_lb, 4), "sdpa_bwd_tflops": round(2.5 * flops / t_lb / 1e9, 1),
+                    "bwd_max_abs_err": [round((g.float() - r).abs().max().item(), 5) for g, r in zip(got, ref)]})
     return out
 
 
@@ -175,6 +193,7 @@ def main(argv=None) -> int:
     t.add_argument("--heads", type=int, default=24)
     t.add_argument("--seq", type=int, default=1178)
     t.add_argument("--head-dim", type=int, default=64)
+    t.add_argument("--backward", action="store_true")
     t.set_defaults(fn=bench_attention)
     args = parser.parse_args(argv)
     if not torch.cuda.is_available():
