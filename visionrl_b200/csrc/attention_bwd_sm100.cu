@@ -9,19 +9,21 @@
 // pair and "str" the streamed pair, one step is
 //   S'  = own1 . str1^T            (K Q^T   |  Q K^T)        128 x 64, TMEM
 //   dP' = own2 . str2^T            (V dO^T  |  dO V^T)       128 x 64, TMEM
-//   P   = exp2(S' * scale * log2e - LSE * log2e),  dS = P * (dP' - delta)   in registers, bf16 to smem
-//   acc1 += P  . str2              (dV += P^T dO)            dK/dV pass only
-//   acc2 += dS . str1              (dK += dS^T Q  |  dQ += dS K)
+//   P   = exp2(S' * scale * log2e - LSE * log2e),  dS = P * (dP' - delta)   in registers, then as
+//                                  bf16 pairs back into TMEM over the columns S' and dP' came from
+//   acc1 += P  . str2              (dV += P^T dO)            dK/dV pass only, A operand from TMEM
+//   acc2 += dS . str1              (dK += dS^T Q  |  dQ += dS K)           A operand from TMEM
 // where delta = rowsum(dO * O) per query comes from a small pre-pass.  The streamed tiles are read
 // twice from the same shared-memory copy: K-major for the first two products, MN-major for the
-// accumulating ones.
+// accumulating ones.  Keeping P and dS out of shared memory matters: every tcgen05.mma with a
+// shared-memory A operand re-reads 4 KB of it, and that traffic, not the math, bounds small tiles.
 //
 //   warp 0      producer: own tiles once, then streamed tiles (and, in the dK/dV pass, the
 //               queries' LSE and delta) through a ring
 //   warp 1      MMA issuer and TMEM owner; S'/dP' are double-buffered so that the tensor core
 //               works on step j+1 while the other warps handle step j
-//   warps 2..9  elementwise: two threads per owned row, 32 of the 64 columns each; no reductions
-//               across threads are needed in the backward
+//   warps 2..9  elementwise: two threads per owned row, 32 of the step's 64 columns each; no
+//               reductions across threads are needed in the backward
 // TMEM columns: [S'0 dP'0 S'1 dP'1] (64 each), acc1 (D), acc2 (D).  Every wait is bounded; on
 // expiry the role records a status code, raises the CTA's abort flag and all roles fall through to
 // the common exit where the TMEM is released.
@@ -37,10 +39,10 @@ using namespace ptx;
 
 constexpr int kOwn = 128;                  // rows the CTA owns
 constexpr int kStr = 64;                   // streamed rows per step
-constexpr int kThreads = 320;
+constexpr int kEwWarps = 8;                // elementwise warps: two threads per owned row
+constexpr int kThreads = 64 + 32 * kEwWarps;
 constexpr uint32_t kOwnBlock = kOwn * 128;       // one 64-column swizzle block of an owned tile
 constexpr uint32_t kStrBlock = kStr * 128;       // the same for a streamed tile
-constexpr uint32_t kPBytes = kOwn * kStr * 2;    // one P or dS tile (bf16, one swizzle block wide)
 
 enum Status : int { kOk = 0, kTimeoutProducer = 21, kTimeoutMma = 22, kTimeoutElementwise = 23,
                     kMisalignedSmem = 24 };
@@ -48,12 +50,12 @@ enum Status : int { kOk = 0, kTimeoutProducer = 21, kTimeoutMma = 22, kTimeoutEl
 template <int D>
 struct Cfg {
   static constexpr int kDBlocks = D / 64;
-  static constexpr int kStages = D == 64 ? 4 : 3;
+  static constexpr int kStages = 4;
   static constexpr uint32_t kOwnBytes = kDBlocks * kOwnBlock;
   static constexpr uint32_t kStrBytes = kDBlocks * kStrBlock;
   static constexpr uint32_t kVecBytes = kStages * kStr * 4;          // LSE or delta of the staged queries
   static constexpr uint32_t kSmemBytes =
-      2 * kOwnBytes + 2 * kStages * kStrBytes + 4 * kPBytes + 2 * kVecBytes + 256;
+      2 * kOwnBytes + 2 * kStages * kStrBytes + 2 * kVecBytes + 256;
   static constexpr uint32_t kAcc1Col = 4 * kStr;
   static constexpr uint32_t kAcc2Col = 4 * kStr + D;
   static constexpr uint32_t kTmemCols = 512;
@@ -69,7 +71,17 @@ struct Params {
   float scale_log2;       // softmax scale times log2(e)
   float scale;
   int* status;
+  unsigned long long* timing;   // optional [16] phase cycle counters (see flash_attn_bwd_timing), or null
 };
+
+// Adds the cycles since `t0` to counter `slot` and restarts the interval.
+__device__ __forceinline__ void lap(const Params& p, int slot, long long& t0) {
+  if (p.timing != nullptr) {
+    const long long t1 = clock64();
+    atomicAdd(p.timing + slot, (unsigned long long)(t1 - t0));
+    t0 = clock64();
+  }
+}
 
 template <int D, bool kDQ>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -86,9 +98,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_own1, const __grid_cons
   uint8_t* so2 = so1 + C::kOwnBytes;
   uint8_t* ss1 = so2 + C::kOwnBytes;                       // [kStages]
   uint8_t* ss2 = ss1 + C::kStages * C::kStrBytes;          // [kStages]
-  uint8_t* sp = ss2 + C::kStages * C::kStrBytes;           // P [2]
-  uint8_t* sds = sp + 2 * kPBytes;                         // dS [2]
-  float* lse_s = reinterpret_cast<float*>(sds + 2 * kPBytes);      // [kStages][kStr], times log2(e)
+  float* lse_s = reinterpret_cast<float*>(ss2 + C::kStages * C::kStrBytes);   // [kStages][kStr], times log2(e)
   float* del_s = lse_s + C::kStages * kStr;                        // [kStages][kStr]
   uint64_t* bars = reinterpret_cast<uint64_t*>(del_s + C::kStages * kStr);
   uint64_t* own_full = bars;
@@ -96,8 +106,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_own1, const __grid_cons
   uint64_t* str_empty = str_full + C::kStages;     // [kStages]
   uint64_t* s_full = str_empty + C::kStages;       // [2]
   uint64_t* p_full = s_full + 2;                   // [2]
-  uint64_t* p_empty = p_full + 2;                  // [2]
-  uint64_t* acc_full = p_empty + 2;
+  uint64_t* acc_full = p_full + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* skip_flag = abort_flag + 1;
@@ -120,8 +129,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_own1, const __grid_cons
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&s_full[s], 1);
-      mbar_init(&p_full[s], 8);
-      mbar_init(&p_empty[s], 1);
+      mbar_init(&p_full[s], kEwWarps);
     }
     mbar_init(acc_full, 1);
     *abort_flag = 0;
@@ -137,6 +145,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_own1, const __grid_cons
   if (warp == 0) {
     // --------------------------------------------------------------------------- producer
     bool ok = true;
+    long long t0 = clock64();
     if (lane == 0) {
       mbar_expect_tx(own_full, 2 * C::kOwnBytes);
 #pragma unroll
@@ -150,6 +159,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_own1, const __grid_cons
       const uint32_t ph = ((j / C::kStages) & 1u) ^ 1u;
       ok = __all_sync(0xffffffffu, mbar_wait(&str_empty[s], ph, abort_flag));
       if (!ok) break;
+      if (lane == 0) lap(p, 12, t0);
       if (!kDQ) {
         // the streamed rows are queries: stage their LSE (in log2 units) and delta next to the tiles
 #pragma unroll
@@ -162,6 +172,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_own1, const __grid_cons
         }
         __syncwarp();
       }
+      if (lane == 0) lap(p, 13, t0);
       if (lane == 0) {
         mbar_expect_tx(&str_full[s], 2 * C::kStrBytes);
 #pragma unroll
@@ -187,27 +198,35 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_own1, const __grid_cons
     // ------------------------------------------------------------------------ MMA issuer
     constexpr uint32_t idesc_s = make_idesc(kOwn, kStr, 0, 0);
     constexpr uint32_t idesc_acc = make_idesc(kOwn, D, 0, 1);
+    long long t0 = clock64();
+    const long long t_begin = t0;
     bool ok = mbar_wait(own_full, 0, abort_flag);
+    lap(p, 2, t0);
     tmem_fence_after();
+    // operand descriptors: constant high halves, low halves = base + (byte offset >> 4)
+    constexpr uint32_t hi = desc_hi(1024);
+    const uint32_t a1_lo = desc_lo(smem_u32(so1), 16), a2_lo = desc_lo(smem_u32(so2), 16);
+    const uint32_t b1_lo = desc_lo(smem_u32(ss1), 16), b2_lo = desc_lo(smem_u32(ss2), 16);        // K-major
+    const uint32_t b1_mn = desc_lo(smem_u32(ss1), kStrBlock), b2_mn = desc_lo(smem_u32(ss2), kStrBlock);
     auto issue_s = [&](int j) -> bool {
       const int s = j % C::kStages;
+      lap(p, 15, t0);
       if (!mbar_wait(&str_full[s], (j / C::kStages) & 1u, abort_flag)) return false;
+      lap(p, 3, t0);
       tmem_fence_after();
-      const uint32_t a1 = smem_u32(so1), a2 = smem_u32(so2);
-      const uint32_t b1 = smem_u32(ss1 + s * C::kStrBytes), b2 = smem_u32(ss2 + s * C::kStrBytes);
+      const uint32_t stage = (uint32_t)s * (C::kStrBytes >> 4);
       const uint32_t col = tmem_base + (uint32_t)(j & 1) * 2 * kStr;
+      // the two products are independent accumulation chains: alternate them, so that one's
+      // tcgen05.mma does not wait for the other's previous k-step to drain
 #pragma unroll
       for (int c = 0; c < C::kDBlocks; ++c)
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          umma_bf16(col, make_desc(a1 + c * kOwnBlock + kk * 32, 16, 1024),
-                    make_desc(b1 + c * kStrBlock + kk * 32, 16, 1024), idesc_s, (c | kk) ? 1u : 0u);
-#pragma unroll
-      for (int c = 0; c < C::kDBlocks; ++c)
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          umma_bf16(col + kStr, make_desc(a2 + c * kOwnBlock + kk * 32, 16, 1024),
-                    make_desc(b2 + c * kStrBlock + kk * 32, 16, 1024), idesc_s, (c | kk) ? 1u : 0u);
+        for (int kk = 0; kk < 4; ++kk) {
+          umma_bf16_split(col, a1_lo + ((c * kOwnBlock + kk * 32) >> 4), hi,
+                          b1_lo + stage + ((c * kStrBlock + kk * 32) >> 4), hi, idesc_s, (c | kk) ? 1u : 0u);
+          umma_bf16_split(col + kStr, a2_lo + ((c * kOwnBlock + kk * 32) >> 4), hi,
+                          b2_lo + stage + ((c * kStrBlock + kk * 32) >> 4), hi, idesc_s, (c | kk) ? 1u : 0u);
+        }
       umma_commit(&s_full[j & 1]);
       return true;
     };
@@ -215,69 +234,77 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_own1, const __grid_cons
     if (ok && n_tiles > 1) ok = issue_s(1);
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int s = j % C::kStages, b = j & 1;
+      lap(p, 15, t0);
       if (!mbar_wait(&p_full[b], (j >> 1) & 1u, abort_flag)) { ok = false; break; }
+      lap(p, 4, t0);
       tmem_fence_after();
-      const uint32_t pa = smem_u32(sp + b * kPBytes), da = smem_u32(sds + b * kPBytes);
-      const uint32_t b1 = smem_u32(ss1 + s * C::kStrBytes), b2 = smem_u32(ss2 + s * C::kStrBytes);
-      if (!kDQ) {
+      const uint32_t stage = (uint32_t)s * (C::kStrBytes >> 4);
+      const uint32_t first = j ? 1u : 0u;
+      // P and dS (bf16 pairs) sit in TMEM over the first columns of each thread's share of S' and dP':
+      // the 16 values of k-step kk are the 8 columns at (kk / 2) * 32 + (kk % 2) * 8
+      const uint32_t pcol = tmem_base + (uint32_t)b * 2 * kStr;
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          umma_bf16(tmem_base + C::kAcc1Col, make_desc(pa + kk * 32, 16, 1024),
-                    make_desc(b2 + kk * 2048, kStrBlock, 1024), idesc_acc, (j | kk) ? 1u : 0u);
+      for (int kk = 0; kk < 4; ++kk) {
+        if (!kDQ)
+          umma_bf16_tmem_a(tmem_base + C::kAcc1Col, pcol + (kk >> 1) * 32 + (kk & 1) * 8,
+                           b2_mn + stage + ((kk * 2048) >> 4), hi, idesc_acc, kk ? 1u : first);
+        umma_bf16_tmem_a(tmem_base + C::kAcc2Col, pcol + kStr + (kk >> 1) * 32 + (kk & 1) * 8,
+                         b1_mn + stage + ((kk * 2048) >> 4), hi, idesc_acc, kk ? 1u : first);
       }
-#pragma unroll
-      for (int kk = 0; kk < 4; ++kk)
-        umma_bf16(tmem_base + C::kAcc2Col, make_desc(da + kk * 32, 16, 1024),
-                  make_desc(b1 + kk * 2048, kStrBlock, 1024), idesc_acc, (j | kk) ? 1u : 0u);
       umma_commit(&str_empty[s]);
-      umma_commit(&p_empty[b]);
       // the elementwise warps have drained S'/dP' buffer b (they said so with p_full)
       if (j + 2 < n_tiles && !issue_s(j + 2)) { ok = false; break; }
     }
     if (ok) umma_commit(acc_full);
+    if (p.timing != nullptr) {
+      atomicAdd(p.timing + 0, 1ull);
+      atomicAdd(p.timing + 1, (unsigned long long)(clock64() - t_begin));
+      atomicAdd(p.timing + 14, (unsigned long long)n_tiles);
+    }
     if (!ok && atomicCAS(const_cast<int*>(abort_flag), 0, 1) == 0) atomicExch(p.status, kTimeoutMma);
   } else if (warp >= 2) {
     // ----------------------------------------------------------------------- elementwise
     // Warp w may read TMEM lanes 32 (w % 4) .. +31, so two warps share every block of 32 owned
-    // rows; they split the step's 64 columns in halves.
+    // rows; they split the step's 64 columns (and the output columns) evenly.
+    constexpr int kParts = kEwWarps / 4;
+    static_assert(kStr / kParts == 32, "the TMEM store below moves 16 packed columns per thread");
+    constexpr int CPT = kStr / kParts;            // columns of a step per thread
     const int quarter = warp & 3;
-    const int half = (warp - 2) >> 2;
+    const int half = (warp - 2) >> 2;             // which part of the columns
     const int row_local = quarter * 32 + lane;
     const int row = r0 + row_local;
     const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
-    const uint32_t row_off = row_local * 128;
-    const uint32_t swz = row_local & 7;
     float lse_row = INFINITY, del_row = 0.f;
     if (kDQ && row < p.sq) {
       lse_row = p.lse[(int64_t)bh * p.sq + row] * 1.4426950408889634f;
       del_row = p.delta[(int64_t)bh * p.sq + row];
     }
     bool ok = true;
+    const bool timed = warp == 2 && lane == 0;
+    long long t0 = clock64();
     for (int j = 0; j < n_tiles; ++j) {
       const int b = j & 1, s = j % C::kStages;
       ok = __all_sync(0xffffffffu, mbar_wait(&s_full[b], (j >> 1) & 1u, abort_flag));
       if (!ok) break;
+      if (timed) lap(p, 5, t0);
       if (!kDQ) {
         // acquire the producer's LSE / delta writes of this stage directly (already complete here)
         ok = __all_sync(0xffffffffu, mbar_wait(&str_full[s], (j / C::kStages) & 1u, abort_flag));
         if (!ok) break;
       }
       tmem_fence_after();
-      uint32_t rs[32], rp[32];
-      tmem_ld32(lane_base + b * 2 * kStr + half * 32, rs);
-      tmem_ld32(lane_base + b * 2 * kStr + kStr + half * 32, rp);
+      uint32_t rs[CPT], rp[CPT];
+      tmem_ld_cols<CPT>(lane_base + b * 2 * kStr + half * CPT, rs);
+      tmem_ld_cols<CPT>(lane_base + b * 2 * kStr + kStr + half * CPT, rp);
       tmem_ld_wait();
-      // the accumulating products of step j-2 must have finished reading P/dS buffer b
-      ok = __all_sync(0xffffffffu, mbar_wait(&p_empty[b], ((j >> 1) & 1u) ^ 1u, abort_flag));
-      if (!ok) break;
-      const float4* lse_t = reinterpret_cast<const float4*>(lse_s + s * kStr + half * 32);
-      const float4* del_t = reinterpret_cast<const float4*>(del_s + s * kStr + half * 32);
+      if (timed) lap(p, 6, t0);
+      const float4* lse_t = reinterpret_cast<const float4*>(lse_s + s * kStr + half * CPT);
+      const float4* del_t = reinterpret_cast<const float4*>(del_s + s * kStr + half * CPT);
       // dQ pass: keys past the end read as zero rows, their probabilities must not count
-      const int valid = kDQ ? min(kStr, p.s_str - j * kStr) - half * 32 : 32;
-      const uint32_t p_row = smem_u32(sp + b * kPBytes) + row_off;
-      const uint32_t d_row = smem_u32(sds + b * kPBytes) + row_off;
+      const int valid = kDQ ? min(kStr, p.s_str - j * kStr) - half * CPT : CPT;
+      uint32_t pk[CPT / 2], dk[CPT / 2];             // bf16 pairs
 #pragma unroll
-      for (int g = 0; g < 4; ++g) {
+      for (int g = 0; g < CPT / 8; ++g) {
         float pv[8], dv[8], lv[8], dl[8];
         if (kDQ) {
 #pragma unroll
@@ -291,35 +318,39 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_own1, const __grid_cons
         for (int i = 0; i < 8; ++i) {
           const int c = g * 8 + i;
           pv[i] = exp2f(fmaf(__uint_as_float(rs[c]), p.scale_log2, -lv[i]));
-          if (kDQ && c >= valid) pv[i] = 0.f;
-          dv[i] = pv[i] * (__uint_as_float(rp[c]) - dl[i]);
         }
-        const uint32_t chunk = (((uint32_t)(half * 4 + g)) ^ swz) << 4;
-        if (!kDQ) {
-          const bf16x8 pk = pack8(pv);
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(p_row + chunk), "r"(pk.u.x),
-                       "r"(pk.u.y), "r"(pk.u.z), "r"(pk.u.w)
-                       : "memory");
+        if (kDQ && valid < CPT) {                  // only the last step of a ragged sequence
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            if (g * 8 + i >= valid) pv[i] = 0.f;
         }
-        const bf16x8 dk = pack8(dv);
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(d_row + chunk), "r"(dk.u.x),
-                     "r"(dk.u.y), "r"(dk.u.z), "r"(dk.u.w)
-                     : "memory");
+#pragma unroll
+        for (int i = 0; i < 8; ++i) dv[i] = pv[i] * (__uint_as_float(rp[g * 8 + i]) - dl[i]);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          pk[g * 4 + i] = float2_to_bf16pair(pv[2 * i], pv[2 * i + 1]);
+          dk[g * 4 + i] = float2_to_bf16pair(dv[2 * i], dv[2 * i + 1]);
+        }
       }
-      fence_async_smem();
+      // over this thread's own, already consumed, S' and dP' columns
+      if (!kDQ) tmem_st16(lane_base + b * 2 * kStr + half * CPT, pk);
+      tmem_st16(lane_base + b * 2 * kStr + kStr + half * CPT, dk);
+      tmem_st_wait();
+      if (timed) lap(p, 8, t0);
       tmem_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full[b]);
+      if (timed) lap(p, 9, t0);
     }
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(acc_full, 0, abort_flag));
+    if (timed) lap(p, 10, t0);
     if (ok) {
       tmem_fence_after();
-      constexpr int DH = D / 2;                    // output columns owned by this thread
+      constexpr int DH = D / kParts;               // output columns owned by this thread
       const int64_t dst_off = (((int64_t)bi * p.s_own + row) * p.heads + hi) * D + half * DH;
       if (!kDQ) {
         uint32_t q[DH];
-#pragma unroll
-        for (int c = 0; c < DH / 32; ++c) tmem_ld32(lane_base + C::kAcc1Col + half * DH + c * 32, q + c * 32);
+        tmem_ld_cols<DH>(lane_base + C::kAcc1Col + half * DH, q);
         tmem_ld_wait();
         if (row < p.s_own) {
 #pragma unroll
@@ -333,8 +364,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_own1, const __grid_cons
       }
       {
         uint32_t q[DH];
-#pragma unroll
-        for (int c = 0; c < DH / 32; ++c) tmem_ld32(lane_base + C::kAcc2Col + half * DH + c * 32, q + c * 32);
+        tmem_ld_cols<DH>(lane_base + C::kAcc2Col + half * DH, q);
         tmem_ld_wait();
         if (row < p.s_own) {
 #pragma unroll
@@ -347,6 +377,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_own1, const __grid_cons
         }
       }
     }
+    if (timed) lap(p, 11, t0);
     if (!ok && lane == 0) {
       if (atomicCAS(const_cast<int*>(abort_flag), 0, 1) == 0) atomicExch(p.status, kTimeoutElementwise);
     }
@@ -401,6 +432,9 @@ static void launch(const CUtensorMap& o1, const CUtensorMap& o2, const CUtensorM
   C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
 
+// Phase counters of the next backward calls on this device ([2 passes][16] cycles), or null when off.
+static unsigned long long* g_timing = nullptr;
+
 template <int D>
 static void run(const torch::Tensor& dout, const torch::Tensor& q, const torch::Tensor& k, const torch::Tensor& v,
                 const torch::Tensor& out, const torch::Tensor& lse, torch::Tensor& delta, torch::Tensor& dq,
@@ -424,6 +458,7 @@ static void run(const torch::Tensor& dout, const torch::Tensor& q, const torch::
   p.scale = (float)scale;
   p.scale_log2 = (float)(scale * 1.4426950408889634);
   p.status = attn::status_word(q.get_device());
+  p.timing = g_timing;
   {
     // dK/dV: own K, V; stream Q, dO
     p.out1 = reinterpret_cast<__nv_bfloat16*>(dv.data_ptr());
@@ -439,12 +474,36 @@ static void run(const torch::Tensor& dout, const torch::Tensor& q, const torch::
     p.out2 = reinterpret_cast<__nv_bfloat16*>(dq.data_ptr());
     p.s_own = (int)sq;
     p.s_str = (int)skv;
+    if (g_timing != nullptr) p.timing = g_timing + 16;
     launch<D, true>(make_map4(q, kOwn), make_map4(dout, kOwn), make_map4(k, kStr), make_map4(v, kStr), p,
                     (int)((sq + kOwn - 1) / kOwn), (int)(b * h), stream);
   }
 }
 
 }  // namespace attn_bwd
+
+// Developer aid: switch per-phase cycle counters of the backward kernels on (zeroing them) or off, and
+// read them back as a [2, 16] int64 tensor (row 0 the dK/dV pass, row 1 the dQ pass).  Slots: 0 CTAs,
+// 1 CTA cycles, 2 MMA wait own tiles, 3 MMA wait streamed tiles, 4 MMA wait P/dS, 5 elementwise wait
+// S'/dP', 6 TMEM load, 7 unused, 8 compute + TMEM stores, 9 fence + arrive, 10 wait
+// accumulators, 11 epilogue, 12 producer wait free stage, 13 producer LSE/delta staging, 14 steps,
+// 15 MMA issue.  Elementwise slots are measured on one thread per CTA.
+torch::Tensor flash_attn_bwd_timing(bool enable) {
+  using attn_bwd::g_timing;
+  auto out = torch::zeros({2, 16}, torch::dtype(torch::kInt64));
+  if (g_timing != nullptr) {
+    C10_CUDA_CHECK(cudaDeviceSynchronize());
+    C10_CUDA_CHECK(cudaMemcpy(out.data_ptr(), g_timing, 32 * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
+  }
+  if (enable) {
+    if (g_timing == nullptr) C10_CUDA_CHECK(cudaMalloc(&g_timing, 32 * sizeof(unsigned long long)));
+    C10_CUDA_CHECK(cudaMemset(g_timing, 0, 32 * sizeof(unsigned long long)));
+  } else if (g_timing != nullptr) {
+    C10_CUDA_CHECK(cudaFree(g_timing));
+    g_timing = nullptr;
+  }
+  return out;
+}
 
 // Gradients of softmax(scale * Q K^T) V for [B, H, S, D] bf16 views (any strides the 4-D tensor map
 // can describe, unit stride in D).  `out` and `lse` are what flash_attn_fwd returned.  The three

@@ -111,6 +111,7 @@ int64_t flash_attn_last_status();
 // attention_bwd_sm100.cu
 std::vector<torch::Tensor> flash_attn_bwd(torch::Tensor dout, torch::Tensor q, torch::Tensor k, torch::Tensor v,
                                           torch::Tensor out, torch::Tensor lse, double scale);
+torch::Tensor flash_attn_bwd_timing(bool enable);
 
 // gemm_sm100.cu
 torch::Tensor gemm_bf16(torch::Tensor a, torch::Tensor b, c10::optional<torch::Tensor> bias,
