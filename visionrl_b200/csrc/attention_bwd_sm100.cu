@@ -20,11 +20,13 @@
 //
 //   warp 0      producer: own tiles once, then streamed tiles (and, in the dK/dV pass, the
 //               queries' LSE and delta) through a ring
-//   warp 1      MMA issuer and TMEM owner; S'/dP' are double-buffered so that the tensor core
-//               works on step j+1 while the other warps handle step j
-//   warps 2..9  elementwise: two threads per owned row, 32 of the step's 64 columns each; no
+//   warp 1      MMA issuer A (S', dP') and TMEM owner; S'/dP' are double-buffered so that the
+//               tensor core works on step j+1 while the other warps handle step j
+//   warp 2      MMA issuer B (the accumulating products); warp 3 idles
+//   warps 4..11 elementwise: two threads per owned row, 32 of the step's 64 columns each; no
 //               reductions across threads are needed in the backward
-// TMEM columns: [S'0 dP'0 S'1 dP'1] (64 each), acc1 (D), acc2 (D).  Every wait is bounded; on
+// TMEM columns: [S'0 dP'0 S'1 dP'1] (64 each), acc1 (D), acc2 (D), and for D = 64 [P0 dS0 P1 dS1]
+// (32 each).  Every wait is bounded; on
 // expiry the role records a status code, raises the CTA's abort flag and all roles fall through to
 // the common exit where the TMEM is released.
 #include "attn_host.cuh"
@@ -40,7 +42,8 @@ using namespace ptx;
 constexpr int kOwn = 128;                  // rows the CTA owns
 constexpr int kStr = 64;                   // streamed rows per step
 constexpr int kEwWarps = 8;                // elementwise warps: two threads per owned row
-constexpr int kThreads = 64 + 32 * kEwWarps;
+constexpr int kFirstEw = 4;                // warps 0..3: producer, two MMA issuers, one idle
+constexpr int kThreads = 32 * (kFirstEw + kEwWarps);
 constexpr uint32_t kOwnBlock = kOwn * 128;       // one 64-column swizzle block of an owned tile
 constexpr uint32_t kStrBlock = kStr * 128;       // the same for a streamed tile
 
@@ -50,7 +53,7 @@ enum Status : int { kOk = 0, kTimeoutProducer = 21, kTimeoutMma = 22, kTimeoutEl
 template <int D>
 struct Cfg {
   static constexpr int kDBlocks = D / 64;
-  static constexpr int kStages = 4;
+  static constexpr int kStages = D == 64 ? 8 : 5;      // streamed-tile ring (fills the shared memory)
   static constexpr uint32_t kOwnBytes = kDBlocks * kOwnBlock;
   static constexpr uint32_t kStrBytes = kDBlocks * kStrBlock;
   static constexpr uint32_t kVecBytes = kStages * kStr * 4;          // LSE or delta of the staged queries
@@ -59,6 +62,12 @@ struct Cfg {
   static constexpr uint32_t kAcc1Col = 4 * kStr;
   static constexpr uint32_t kAcc2Col = 4 * kStr + D;
   static constexpr uint32_t kTmemCols = 512;
+  // Where P and dS (bf16 pairs, 32 columns each per buffer) live in TMEM.  D = 64 leaves 128 spare
+  // columns for two separate buffers; D = 128 does not, so there they overwrite the S'/dP' columns
+  // they were computed from (each thread its own 32), and S' of step j+2 has to wait for the
+  // accumulating products of step j.
+  static constexpr bool kAliasP = 2 * D + 6 * kStr > 512;
+  static constexpr uint32_t kPCol = 4 * kStr + 2 * D;
 };
 
 struct Params {
@@ -104,9 +113,11 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_own1, const __grid_cons
   uint64_t* own_full = bars;
   uint64_t* str_full = bars + 1;                   // [kStages]
   uint64_t* str_empty = str_full + C::kStages;     // [kStages]
-  uint64_t* s_full = str_empty + C::kStages;       // [2]
-  uint64_t* p_full = s_full + 2;                   // [2]
-  uint64_t* acc_full = p_full + 2;
+  uint64_t* s_full = str_empty + C::kStages;       // [2] S' of a step is in TMEM
+  uint64_t* d_full = s_full + 2;                   // [2] dP' of a step is in TMEM
+  uint64_t* p_full = d_full + 2;                   // [2]
+  uint64_t* p_empty = p_full + 2;                  // [2]
+  uint64_t* acc_full = p_empty + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* skip_flag = abort_flag + 1;
@@ -129,7 +140,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_own1, const __grid_cons
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&s_full[s], 1);
+      mbar_init(&d_full[s], 1);
       mbar_init(&p_full[s], kEwWarps);
+      mbar_init(&p_empty[s], 1);
     }
     mbar_init(acc_full, 1);
     *abort_flag = 0;
@@ -157,18 +170,26 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_own1, const __grid_cons
     for (int j = 0; j < n_tiles; ++j) {
       const int s = j % C::kStages;
       const uint32_t ph = ((j / C::kStages) & 1u) ^ 1u;
+      // the streamed rows are queries: fetch their LSE (to log2 units) and delta while waiting for
+      // the stage, then put them next to the tiles
+      float vl[kStr / 32], vd[kStr / 32];
+      if (!kDQ) {
+#pragma unroll
+        for (int i = 0; i < kStr / 32; ++i) {
+          const int qi = j * kStr + i * 32 + lane;
+          const bool in = qi < p.sq;
+          vl[i] = in ? p.lse[(int64_t)bh * p.sq + qi] * 1.4426950408889634f : INFINITY;
+          vd[i] = in ? p.delta[(int64_t)bh * p.sq + qi] : 0.f;
+        }
+      }
       ok = __all_sync(0xffffffffu, mbar_wait(&str_empty[s], ph, abort_flag));
       if (!ok) break;
       if (lane == 0) lap(p, 12, t0);
       if (!kDQ) {
-        // the streamed rows are queries: stage their LSE (in log2 units) and delta next to the tiles
 #pragma unroll
         for (int i = 0; i < kStr / 32; ++i) {
-          const int col = i * 32 + lane;
-          const int qi = j * kStr + col;
-          const bool in = qi < p.sq;
-          lse_s[s * kStr + col] = in ? p.lse[(int64_t)bh * p.sq + qi] * 1.4426950408889634f : INFINITY;
-          del_s[s * kStr + col] = in ? p.delta[(int64_t)bh * p.sq + qi] : 0.f;
+          lse_s[s * kStr + i * 32 + lane] = vl[i];
+          del_s[s * kStr + i * 32 + lane] = vd[i];
         }
         __syncwarp();
       }
@@ -195,74 +216,99 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_own1, const __grid_cons
       }
     }
   } else if (warp == 1 && lane == 0) {
-    // ------------------------------------------------------------------------ MMA issuer
+    // ------------------------------------------------- MMA issuer A: S' and dP' of every step
+    // One tcgen05.mma costs its issuing thread about 48 cycles, a commit about 100 and an mbarrier
+    // wait 100 or more even when it is already complete, so a single thread issuing all four
+    // products of a step is the bottleneck of the CTA.  Two threads share the work: this one the
+    // products that feed the elementwise warps, warp 2 the accumulating ones.
     constexpr uint32_t idesc_s = make_idesc(kOwn, kStr, 0, 0);
-    constexpr uint32_t idesc_acc = make_idesc(kOwn, D, 0, 1);
+    constexpr uint32_t hi = desc_hi(1024);
     long long t0 = clock64();
     const long long t_begin = t0;
     bool ok = mbar_wait(own_full, 0, abort_flag);
     lap(p, 2, t0);
-    tmem_fence_after();
-    // operand descriptors: constant high halves, low halves = base + (byte offset >> 4)
-    constexpr uint32_t hi = desc_hi(1024);
     const uint32_t a1_lo = desc_lo(smem_u32(so1), 16), a2_lo = desc_lo(smem_u32(so2), 16);
-    const uint32_t b1_lo = desc_lo(smem_u32(ss1), 16), b2_lo = desc_lo(smem_u32(ss2), 16);        // K-major
-    const uint32_t b1_mn = desc_lo(smem_u32(ss1), kStrBlock), b2_mn = desc_lo(smem_u32(ss2), kStrBlock);
+    const uint32_t b1_lo = desc_lo(smem_u32(ss1), 16), b2_lo = desc_lo(smem_u32(ss2), 16);
     auto issue_s = [&](int j) -> bool {
       const int s = j % C::kStages;
       lap(p, 15, t0);
       if (!mbar_wait(&str_full[s], (j / C::kStages) & 1u, abort_flag)) return false;
       lap(p, 3, t0);
-      tmem_fence_after();
       const uint32_t stage = (uint32_t)s * (C::kStrBytes >> 4);
       const uint32_t col = tmem_base + (uint32_t)(j & 1) * 2 * kStr;
-      // the two products are independent accumulation chains: alternate them, so that one's
-      // tcgen05.mma does not wait for the other's previous k-step to drain
+      // S' first and signalled on its own: the elementwise warps start on the exponentials while
+      // the tensor core still works on dP'
 #pragma unroll
       for (int c = 0; c < C::kDBlocks; ++c)
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk) {
+        for (int kk = 0; kk < 4; ++kk)
           umma_bf16_split(col, a1_lo + ((c * kOwnBlock + kk * 32) >> 4), hi,
                           b1_lo + stage + ((c * kStrBlock + kk * 32) >> 4), hi, idesc_s, (c | kk) ? 1u : 0u);
+      umma_commit(&s_full[j & 1]);
+#pragma unroll
+      for (int c = 0; c < C::kDBlocks; ++c)
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
           umma_bf16_split(col + kStr, a2_lo + ((c * kOwnBlock + kk * 32) >> 4), hi,
                           b2_lo + stage + ((c * kStrBlock + kk * 32) >> 4), hi, idesc_s, (c | kk) ? 1u : 0u);
-        }
-      umma_commit(&s_full[j & 1]);
+      umma_commit(&d_full[j & 1]);
       return true;
     };
     if (ok) ok = issue_s(0);
     if (ok && n_tiles > 1) ok = issue_s(1);
-    for (int j = 0; j < n_tiles && ok; ++j) {
-      const int s = j % C::kStages, b = j & 1;
+    for (int j = 0; j + 2 < n_tiles && ok; ++j) {
+      const int b = j & 1;
       lap(p, 15, t0);
+      // S'/dP' buffer b is free once the elementwise warps have read step j out of it ...
       if (!mbar_wait(&p_full[b], (j >> 1) & 1u, abort_flag)) { ok = false; break; }
+      // ... and, where P and dS were written back over it, once step j's accumulating products
+      // have consumed them
+      if (C::kAliasP && !mbar_wait(&p_empty[b], (j >> 1) & 1u, abort_flag)) { ok = false; break; }
       lap(p, 4, t0);
       tmem_fence_after();
-      const uint32_t stage = (uint32_t)s * (C::kStrBytes >> 4);
-      const uint32_t first = j ? 1u : 0u;
-      // P and dS (bf16 pairs) sit in TMEM over the first columns of each thread's share of S' and dP':
-      // the 16 values of k-step kk are the 8 columns at (kk / 2) * 32 + (kk % 2) * 8
-      const uint32_t pcol = tmem_base + (uint32_t)b * 2 * kStr;
-#pragma unroll
-      for (int kk = 0; kk < 4; ++kk) {
-        if (!kDQ)
-          umma_bf16_tmem_a(tmem_base + C::kAcc1Col, pcol + (kk >> 1) * 32 + (kk & 1) * 8,
-                           b2_mn + stage + ((kk * 2048) >> 4), hi, idesc_acc, kk ? 1u : first);
-        umma_bf16_tmem_a(tmem_base + C::kAcc2Col, pcol + kStr + (kk >> 1) * 32 + (kk & 1) * 8,
-                         b1_mn + stage + ((kk * 2048) >> 4), hi, idesc_acc, kk ? 1u : first);
-      }
-      umma_commit(&str_empty[s]);
-      // the elementwise warps have drained S'/dP' buffer b (they said so with p_full)
-      if (j + 2 < n_tiles && !issue_s(j + 2)) { ok = false; break; }
+      if (!issue_s(j + 2)) { ok = false; break; }
     }
-    if (ok) umma_commit(acc_full);
     if (p.timing != nullptr) {
       atomicAdd(p.timing + 0, 1ull);
       atomicAdd(p.timing + 1, (unsigned long long)(clock64() - t_begin));
       atomicAdd(p.timing + 14, (unsigned long long)n_tiles);
     }
     if (!ok && atomicCAS(const_cast<int*>(abort_flag), 0, 1) == 0) atomicExch(p.status, kTimeoutMma);
-  } else if (warp >= 2) {
+  } else if (warp == 2 && lane == 0) {
+    // ------------------------------------------ MMA issuer B: the accumulating products
+    constexpr uint32_t idesc_acc = make_idesc(kOwn, D, 0, 1);
+    constexpr uint32_t hi = desc_hi(1024);
+    const uint32_t b1_mn = desc_lo(smem_u32(ss1), kStrBlock), b2_mn = desc_lo(smem_u32(ss2), kStrBlock);
+    long long t0 = clock64();
+    bool ok = true;
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int s = j % C::kStages, b = j & 1;
+      if (!mbar_wait(&p_full[b], (j >> 1) & 1u, abort_flag)) { ok = false; break; }
+      // the streamed tiles of this step landed long ago; this acquires them for this thread
+      if (!mbar_wait(&str_full[s], (j / C::kStages) & 1u, abort_flag)) { ok = false; break; }
+      lap(p, 7, t0);
+      tmem_fence_after();
+      const uint32_t stage = (uint32_t)s * (C::kStrBytes >> 4);
+      const uint32_t first = j ? 1u : 0u;
+      // 16 values of k-step kk = 8 packed columns
+      const uint32_t pcol = C::kAliasP ? tmem_base + (uint32_t)b * 2 * kStr : tmem_base + C::kPCol + (uint32_t)b * kStr;
+      const uint32_t dcol = C::kAliasP ? pcol + kStr : pcol + kStr / 2;
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) {
+        const uint32_t koff = C::kAliasP ? (kk >> 1) * 32 + (kk & 1) * 8 : kk * 8;
+        if (!kDQ)
+          umma_bf16_tmem_a(tmem_base + C::kAcc1Col, pcol + koff, b2_mn + stage + ((kk * 2048) >> 4), hi, idesc_acc,
+                           kk ? 1u : first);
+        umma_bf16_tmem_a(tmem_base + C::kAcc2Col, dcol + koff, b1_mn + stage + ((kk * 2048) >> 4), hi, idesc_acc,
+                         kk ? 1u : first);
+      }
+      umma_commit(&str_empty[s]);
+      umma_commit(&p_empty[b]);
+      lap(p, 10, t0);
+    }
+    if (ok) umma_commit(acc_full);
+    if (!ok && atomicCAS(const_cast<int*>(abort_flag), 0, 1) == 0) atomicExch(p.status, kTimeoutMma);
+  } else if (warp >= kFirstEw) {
     // ----------------------------------------------------------------------- elementwise
     // Warp w may read TMEM lanes 32 (w % 4) .. +31, so two warps share every block of 32 owned
     // rows; they split the step's 64 columns (and the output columns) evenly.
@@ -270,7 +316,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_own1, const __grid_cons
     static_assert(kStr / kParts == 32, "the TMEM store below moves 16 packed columns per thread");
     constexpr int CPT = kStr / kParts;            // columns of a step per thread
     const int quarter = warp & 3;
-    const int half = (warp - 2) >> 2;             // which part of the columns
+    const int half = (warp - kFirstEw) >> 2;      // which part of the columns
     const int row_local = quarter * 32 + lane;
     const int row = r0 + row_local;
     const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
@@ -280,7 +326,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_own1, const __grid_cons
       del_row = p.delta[(int64_t)bh * p.sq + row];
     }
     bool ok = true;
-    const bool timed = warp == 2 && lane == 0;
+    const bool timed = warp == kFirstEw && lane == 0;
     long long t0 = clock64();
     for (int j = 0; j < n_tiles; ++j) {
       const int b = j & 1, s = j % C::kStages;
@@ -293,48 +339,62 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_own1, const __grid_cons
         if (!ok) break;
       }
       tmem_fence_after();
-      uint32_t rs[CPT], rp[CPT];
+      uint32_t rs[CPT];
       tmem_ld_cols<CPT>(lane_base + b * 2 * kStr + half * CPT, rs);
-      tmem_ld_cols<CPT>(lane_base + b * 2 * kStr + kStr + half * CPT, rp);
       tmem_ld_wait();
       if (timed) lap(p, 6, t0);
       const float4* lse_t = reinterpret_cast<const float4*>(lse_s + s * kStr + half * CPT);
       const float4* del_t = reinterpret_cast<const float4*>(del_s + s * kStr + half * CPT);
       // dQ pass: keys past the end read as zero rows, their probabilities must not count
       const int valid = kDQ ? min(kStr, p.s_str - j * kStr) - half * CPT : CPT;
+      float pv[CPT];
       uint32_t pk[CPT / 2], dk[CPT / 2];             // bf16 pairs
 #pragma unroll
-      for (int g = 0; g < CPT / 8; ++g) {
-        float pv[8], dv[8], lv[8], dl[8];
-        if (kDQ) {
-#pragma unroll
-          for (int i = 0; i < 8; ++i) { lv[i] = lse_row; dl[i] = del_row; }
-        } else {
-          const float4 l0 = lse_t[2 * g], l1 = lse_t[2 * g + 1], d0 = del_t[2 * g], d1 = del_t[2 * g + 1];
-          lv[0] = l0.x; lv[1] = l0.y; lv[2] = l0.z; lv[3] = l0.w; lv[4] = l1.x; lv[5] = l1.y; lv[6] = l1.z; lv[7] = l1.w;
-          dl[0] = d0.x; dl[1] = d0.y; dl[2] = d0.z; dl[3] = d0.w; dl[4] = d1.x; dl[5] = d1.y; dl[6] = d1.z; dl[7] = d1.w;
-        }
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int c = g * 8 + i;
-          pv[i] = exp2f(fmaf(__uint_as_float(rs[c]), p.scale_log2, -lv[i]));
-        }
-        if (kDQ && valid < CPT) {                  // only the last step of a ragged sequence
-#pragma unroll
-          for (int i = 0; i < 8; ++i)
-            if (g * 8 + i >= valid) pv[i] = 0.f;
-        }
-#pragma unroll
-        for (int i = 0; i < 8; ++i) dv[i] = pv[i] * (__uint_as_float(rp[g * 8 + i]) - dl[i]);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          pk[g * 4 + i] = float2_to_bf16pair(pv[2 * i], pv[2 * i + 1]);
-          dk[g * 4 + i] = float2_to_bf16pair(dv[2 * i], dv[2 * i + 1]);
-        }
+      for (int g = 0; g < CPT / 4; ++g) {
+        float4 l4 = make_float4(lse_row, lse_row, lse_row, lse_row);
+        if (!kDQ) l4 = lse_t[g];
+        pv[4 * g + 0] = exp2f(fmaf(__uint_as_float(rs[4 * g + 0]), p.scale_log2, -l4.x));
+        pv[4 * g + 1] = exp2f(fmaf(__uint_as_float(rs[4 * g + 1]), p.scale_log2, -l4.y));
+        pv[4 * g + 2] = exp2f(fmaf(__uint_as_float(rs[4 * g + 2]), p.scale_log2, -l4.z));
+        pv[4 * g + 3] = exp2f(fmaf(__uint_as_float(rs[4 * g + 3]), p.scale_log2, -l4.w));
       }
-      // over this thread's own, already consumed, S' and dP' columns
-      if (!kDQ) tmem_st16(lane_base + b * 2 * kStr + half * CPT, pk);
-      tmem_st16(lane_base + b * 2 * kStr + kStr + half * CPT, dk);
+      if (kDQ && valid < CPT) {                    // only the last step of a ragged sequence
+#pragma unroll
+        for (int c = 0; c < CPT; ++c)
+          if (c >= valid) pv[c] = 0.f;
+      }
+      if (!kDQ) {
+#pragma unroll
+        for (int c = 0; c < CPT / 2; ++c) pk[c] = float2_to_bf16pair(pv[2 * c], pv[2 * c + 1]);
+      }
+      // now dP' (the tensor core produced it while the exponentials ran)
+      ok = __all_sync(0xffffffffu, mbar_wait(&d_full[b], (j >> 1) & 1u, abort_flag));
+      if (!ok) break;
+      tmem_fence_after();
+      tmem_ld_cols<CPT>(lane_base + b * 2 * kStr + kStr + half * CPT, rs);
+      tmem_ld_wait();
+#pragma unroll
+      for (int g = 0; g < CPT / 4; ++g) {
+        float4 d4 = make_float4(del_row, del_row, del_row, del_row);
+        if (!kDQ) d4 = del_t[g];
+        const float d0 = pv[4 * g + 0] * (__uint_as_float(rs[4 * g + 0]) - d4.x);
+        const float d1 = pv[4 * g + 1] * (__uint_as_float(rs[4 * g + 1]) - d4.y);
+        const float d2 = pv[4 * g + 2] * (__uint_as_float(rs[4 * g + 2]) - d4.z);
+        const float d3 = pv[4 * g + 3] * (__uint_as_float(rs[4 * g + 3]) - d4.w);
+        dk[2 * g] = float2_to_bf16pair(d0, d1);
+        dk[2 * g + 1] = float2_to_bf16pair(d2, d3);
+      }
+      if (C::kAliasP) {
+        // over this thread's own, already consumed, S' and dP' columns
+        if (!kDQ) tmem_st16(lane_base + b * 2 * kStr + half * CPT, pk);
+        tmem_st16(lane_base + b * 2 * kStr + kStr + half * CPT, dk);
+      } else {
+        // separate P/dS buffer b: the accumulating products of step j-2 must be done with it
+        ok = __all_sync(0xffffffffu, mbar_wait(&p_empty[b], ((j >> 1) & 1u) ^ 1u, abort_flag));
+        if (!ok) break;
+        if (!kDQ) tmem_st16(lane_base + C::kPCol + b * kStr + half * (CPT / 2), pk);
+        tmem_st16(lane_base + C::kPCol + b * kStr + kStr / 2 + half * (CPT / 2), dk);
+      }
       tmem_st_wait();
       if (timed) lap(p, 8, t0);
       tmem_fence_before();
@@ -343,7 +403,6 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_own1, const __grid_cons
       if (timed) lap(p, 9, t0);
     }
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(acc_full, 0, abort_flag));
-    if (timed) lap(p, 10, t0);
     if (ok) {
       tmem_fence_after();
       constexpr int DH = D / kParts;               // output columns owned by this thread
@@ -485,8 +544,8 @@ static void run(const torch::Tensor& dout, const torch::Tensor& q, const torch::
 // Developer aid: switch per-phase cycle counters of the backward kernels on (zeroing them) or off, and
 // read them back as a [2, 16] int64 tensor (row 0 the dK/dV pass, row 1 the dQ pass).  Slots: 0 CTAs,
 // 1 CTA cycles, 2 MMA wait own tiles, 3 MMA wait streamed tiles, 4 MMA wait P/dS, 5 elementwise wait
-// S'/dP', 6 TMEM load, 7 unused, 8 compute + TMEM stores, 9 fence + arrive, 10 wait
-// accumulators, 11 epilogue, 12 producer wait free stage, 13 producer LSE/delta staging, 14 steps,
+// S'/dP', 6 TMEM load, 7 issuer B waits, 8 compute + TMEM stores, 9 fence + arrive, 10 issuer B issue (and elementwise wait for the
+// accumulators), 11 epilogue, 12 producer wait free stage, 13 producer LSE/delta staging, 14 steps,
 // 15 MMA issue.  Elementwise slots are measured on one thread per CTA.
 torch::Tensor flash_attn_bwd_timing(bool enable) {
   using attn_bwd::g_timing;
