@@ -193,6 +193,7 @@ def run(args) -> None:
                 "train_timesteps": 9, "reward": "ViT-L/14 scalar head on VAE-decoded 512x512",
                 "l2_policy": "working set (4 GB weights + activations) exceeds the 126 MB L2",
                 "collectives": "nccl" if baseline else args.collectives,
+                "attention": "library SDPA" if baseline else _attention_impl(),
             },
             "clocks": clocks,
             "e2e": {"value": round(e2e_value, 4), "unit": "samples/s",
@@ -206,6 +207,13 @@ def run(args) -> None:
     if dist.is_initialized():
         dist.barrier()
         dist.destroy_process_group()
+
+
+def _attention_impl() -> str:
+    from visionrl_b200.ops import attention as A
+
+    return ("own tcgen05 forward + backward" if A.backward_impl() == "own"
+            else "own tcgen05 forward (no-grad calls), library SDPA under autograd")
 
 
 def main() -> None:

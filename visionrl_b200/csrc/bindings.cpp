@@ -68,6 +68,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("flash_attn_last_status", &vrl::flash_attn_last_status);
   m.def("flash_attn_bwd", &vrl::flash_attn_bwd);
   m.def("flash_attn_bwd_timing", &vrl::flash_attn_bwd_timing);
+  m.def("mma_issue_probe", &vrl::mma_issue_probe);
   m.def("gemm_bf16", &vrl::gemm_bf16);
   m.def("gemm_bf16_dual", &vrl::gemm_bf16_dual);
   m.def("gemm_allgather", &vrl::gemm_allgather);

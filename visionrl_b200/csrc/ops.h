@@ -113,6 +113,10 @@ std::vector<torch::Tensor> flash_attn_bwd(torch::Tensor dout, torch::Tensor q, t
                                           torch::Tensor out, torch::Tensor lse, double scale);
 torch::Tensor flash_attn_bwd_timing(bool enable);
 
+// mma_probe.cu
+torch::Tensor mma_issue_probe(int64_t n, int64_t iters, int64_t group, bool commit_each, bool wait_each,
+                              bool tmem_a);
+
 // gemm_sm100.cu
 torch::Tensor gemm_bf16(torch::Tensor a, torch::Tensor b, c10::optional<torch::Tensor> bias,
                         c10::optional<torch::Tensor> gate, c10::optional<torch::Tensor> residual,

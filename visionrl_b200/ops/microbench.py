@@ -162,6 +162,53 @@ def bench_attention(args) -> dict:
     return out
 
 
+def bench_mma_issue(args) -> dict:
+    """Cycles one issuing thread spends per tcgen05.mma, per commit and per (complete) mbarrier wait."""
+    from visionrl_b200.ops import _ext
+
+    ext = _ext.load()
+    rows = []
+    for n in (64, 128, 256):
+        for group, commit, wait, tmem_a in ((8, False, False, False), (8, True, False, False),
+                                            (8, True, True, False), (4, True, True, False),
+                                            (8, False, False, True)):
+            if tmem_a and n == 256:
+                continue
+            ext.mma_issue_probe(n, 8, group, commit, wait, tmem_a)                    # warm-up
+            issue, complete, ok = ext.mma_issue_probe(n, args.groups, group, commit, wait, tmem_a).tolist()
+            rows.append({"n": n, "group": group, "commit_each_group": commit, "wait_each_group": wait,
+                         "a_in_tmem": tmem_a, "issue_cycles_per_group": round(issue / args.groups, 1),
+                         "complete_cycles_per_group": round(complete / args.groups, 1), "ok": bool(ok)})
+    return {"kernel": "mma_issue_probe", "groups": args.groups, "rows": rows}
+
+
+def bench_attention_phases(args) -> dict:
+    """Per-step cycle counters of the two backward passes (see ``flash_attn_bwd_timing``)."""
+    from visionrl_b200.ops import _ext
+    from visionrl_b200.ops.attention import flash_attention_backward, flash_attention_forward
+
+    ext = _ext.load()
+    names = ["ctas", "cta_cycles", "issuerA_wait_own", "issuerA_wait_tiles", "issuerA_wait_elementwise",
+             "elementwise_wait_S", "elementwise_tmem_load", "issuerB_waits", "elementwise_compute",
+             "elementwise_fence_arrive", "issuerB_issue", "elementwise_epilogue", "producer_wait_stage",
+             "producer_vectors", "steps", "issuerA_issue"]
+    b, h, s, d = args.batch, args.heads, args.seq, args.head_dim
+    q, k, v, do = (torch.randn(b, h, s, d, device="cuda", dtype=torch.bfloat16) for _ in range(4))
+    o, lse = flash_attention_forward(q, k, v, d ** -0.5)
+    for _ in range(2):
+        flash_attention_backward(do, q, k, v, o, lse, d ** -0.5)
+    torch.cuda.synchronize()
+    ext.flash_attn_bwd_timing(True)
+    flash_attention_backward(do, q, k, v, o, lse, d ** -0.5)
+    t = ext.flash_attn_bwd_timing(False).tolist()
+    out = {"kernel": "attention_bwd_phases", "batch": b, "heads": h, "seq": s, "head_dim": d}
+    for row, name in zip(t, ("dkv_pass", "dq_pass")):
+        steps = max(row[14], 1)
+        out[name] = {"cycles_per_step": round(row[1] / steps, 1),
+                     **{n: round(row[i] / steps, 1) for i, n in enumerate(names) if i not in (0, 1, 14)}}
+    return out
+
+
 def main(argv=None) -> int:
     parser = argparse.ArgumentParser(prog="visionrl_b200.ops.microbench")
     parser.add_argument("--iters", type=int, default=20)
@@ -195,6 +242,15 @@ def main(argv=None) -> int:
     t.add_argument("--head-dim", type=int, default=64)
     t.add_argument("--backward", action="store_true")
     t.set_defaults(fn=bench_attention)
+    tp = sub.add_parser("attention_phases")
+    tp.add_argument("--batch", type=int, default=16)
+    tp.add_argument("--heads", type=int, default=24)
+    tp.add_argument("--seq", type=int, default=1178)
+    tp.add_argument("--head-dim", type=int, default=64)
+    tp.set_defaults(fn=bench_attention_phases)
+    mp = sub.add_parser("mma_issue")
+    mp.add_argument("--groups", type=int, default=256)
+    mp.set_defaults(fn=bench_mma_issue)
     args = parser.parse_args(argv)
     if not torch.cuda.is_available():
         print(json.dumps({"error": "no CUDA device"}))
