@@ -194,6 +194,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   } else if (warp == 1 && lane == 0) {
     // -------------------------------------------------------------------- MMA issuer
     const uint32_t idesc = make_idesc(BM, BN, p.a_mn, p.b_mn);
+    // Descriptor halves: the issuing thread is the scarcest resource of the CTA (a tcgen05.mma costs
+    // it ~48 cycles, a commit ~100, a wait more), so per product only the low half changes, by one
+    // add.  K-major operands advance 32 bytes per k-step, MN-major ones 16 rows of 128 bytes.
+    const uint32_t a_lo0 = desc_lo(smem_u32(smem), p.a_mn ? BK * 128 : 16);
+    const uint32_t b_lo0 = desc_lo(smem_u32(smem) + kABytes, p.b_mn ? BK * 128 : 16);
+    const uint32_t a_step = p.a_mn ? (UMMA_K * 128) >> 4 : (UMMA_K * 2) >> 4;
+    const uint32_t b_step = p.b_mn ? (UMMA_K * 128) >> 4 : (UMMA_K * 2) >> 4;
     uint32_t it = 0, tile_it = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_it) {
@@ -205,15 +212,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         const int s = it % kStages;
         if (!mbar_wait(&full[s], (it / kStages) & 1u, abort_flag)) { ok = false; break; }
         tmem_fence_after();
-        const uint32_t sa = smem_u32(smem + s * kStageBytes), sb = sa + kABytes;
+        const uint32_t sa = a_lo0 + (uint32_t)s * (kStageBytes >> 4), sb = b_lo0 + (uint32_t)s * (kStageBytes >> 4);
 #pragma unroll
-        for (int kk = 0; kk < BK / UMMA_K; ++kk) {
-          const uint64_t da = p.a_mn ? make_desc(sa + kk * UMMA_K * 128, BK * 128, 1024)
-                                     : make_desc(sa + kk * UMMA_K * 2, 16, 1024);
-          const uint64_t db = p.b_mn ? make_desc(sb + kk * UMMA_K * 128, BK * 128, 1024)
-                                     : make_desc(sb + kk * UMMA_K * 2, 16, 1024);
-          umma_bf16(tmem_c, da, db, idesc, (kb | kk) ? 1u : 0u);
-        }
+        for (int kk = 0; kk < BK / UMMA_K; ++kk)
+          umma_bf16_split(tmem_c, sa + kk * a_step, desc_hi(1024), sb + kk * b_step, desc_hi(1024), idesc,
+                          (kb | kk) ? 1u : 0u);
         umma_commit(&empty[s]);           // frees the stage once these MMAs have read it
       }
       if (ok) umma_commit(&acc_full[buf]);

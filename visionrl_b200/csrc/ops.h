@@ -114,7 +114,7 @@ std::vector<torch::Tensor> flash_attn_bwd(torch::Tensor dout, torch::Tensor q, t
 torch::Tensor flash_attn_bwd_timing(bool enable);
 
 // mma_probe.cu
-torch::Tensor mma_issue_probe(int64_t n, int64_t iters, int64_t group, bool commit_each, bool wait_each,
+torch::Tensor mma_issue_probe(int64_t n, int64_t iters, int64_t group, bool commit_each, int64_t wait_each,
                               bool tmem_a);
 
 // gemm_sm100.cu

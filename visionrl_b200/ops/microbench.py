@@ -169,10 +169,10 @@ def bench_mma_issue(args) -> dict:
     ext = _ext.load()
     rows = []
     for n in (64, 128, 256):
-        for group, commit, wait, tmem_a in ((8, False, False, False), (8, True, False, False),
-                                            (8, True, True, False), (4, True, True, False),
-                                            (8, False, False, True)):
-            if tmem_a and n == 256:
+        # wait: 0 none, 1 bounded try_wait loop, 2 one non-blocking test_wait
+        for group, commit, wait, tmem_a in ((8, False, 0, False), (8, True, 0, False), (8, True, 1, False),
+                                            (8, True, 2, False), (4, True, 1, False), (8, False, 0, True)):
+            if n == 256 and (tmem_a or group != 8):
                 continue
             ext.mma_issue_probe(n, 8, group, commit, wait, tmem_a)                    # warm-up
             issue, complete, ok = ext.mma_issue_probe(n, args.groups, group, commit, wait, tmem_a).tolist()
