@@ -590,6 +590,29 @@ def test_differentiable_attention_runs_own_kernels_on_token_major_views():
 
 
 @pytest.mark.gpu
+def test_backward_phase_counters_and_mma_issue_probe():
+    from visionrl_b200.ops import _ext
+    from visionrl_b200.ops.attention import flash_attention_backward, flash_attention_forward
+
+    ext = _ext.load()
+    torch.manual_seed(20)
+    q, k, v, do = (torch.randn(1, 2, 300, 64, device="cuda").bfloat16() for _ in range(4))
+    out, lse = flash_attention_forward(q, k, v, 0.125)
+    plain = flash_attention_backward(do, q, k, v, out, lse, 0.125)
+    ext.flash_attn_bwd_timing(True)
+    timed = flash_attention_backward(do, q, k, v, out, lse, 0.125)
+    counters = ext.flash_attn_bwd_timing(False)
+    assert counters.shape == (2, 16)
+    # 2 heads x ceil(300 / 128) owned tiles per pass, ceil(300 / 64) steps each
+    assert counters[:, 0].tolist() == [6, 6] and counters[:, 14].tolist() == [30, 30]
+    assert (counters[:, 1] > 0).all()
+    assert all(torch.equal(a, b) for a, b in zip(plain, timed))          # counters do not change results
+    assert ext.flash_attn_last_status() == 0
+    issue, complete, ok = ext.mma_issue_probe(128, 32, 8, True, 1, False).tolist()
+    assert ok == 1 and 0 < issue <= complete < 32 * 8 * 2000
+
+
+@pytest.mark.gpu
 def test_joint_qkv_prepare_matches_concatenated_reference():
     from visionrl_b200.ops.qkv import joint_qkv_prepare, qkv_prepare_reference
 
