@@ -860,7 +860,7 @@ std::vector<torch::Tensor> qkv_prepare_fwd(torch::Tensor qkv, c10::optional<torc
 constexpr int kQkvBwdTokens = 16;
 
 template <int kQkvMaxVec>
-__global__ void __launch_bounds__(kNormThreads)
+__global__ void __launch_bounds__(kNormThreads, 3)
 qkv_prepare_bwd_kernel(const bf16* __restrict__ gq, const bf16* __restrict__ gk,
                        const bf16* __restrict__ gv, const bf16* __restrict__ qkv,
                        const bf16* __restrict__ qw, const bf16* __restrict__ kw,
