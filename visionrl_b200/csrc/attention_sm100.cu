@@ -103,7 +103,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   uint64_t* k_full = bars + 1;     // [2]
   uint64_t* k_empty = bars + 3;    // [2]
   uint64_t* v_full = bars + 5;     // [2]
-  uint64_t* v_empty = bars + 7;    // [2]
+  uint64_t* v_empty = bars + 7;    // [2] spare: the V stage is released through o_full
   uint64_t* s_full = bars + 9;     // [2]
   uint64_t* o_full = bars + 11;    // [2]
   uint64_t* p_full = bars + 13;
@@ -149,7 +149,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 #pragma unroll
       for (int c = 0; c < C::kDBlocks; ++c)
         tma_load_4d(sk + s * C::kTileBytes + c * kBlockBytes, &map_k, &k_full[s], c * 64, j * kTile, hi, bi);
-      if (!mbar_wait(&v_empty[s], ph, abort_flag)) { ok = false; break; }
+      if (!mbar_wait(&o_full[s], ph, abort_flag)) { ok = false; break; }     // P V of step j-2 done
       mbar_expect_tx(&v_full[s], C::kTileBytes);
 #pragma unroll
       for (int c = 0; c < C::kDBlocks; ++c)
@@ -169,6 +169,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     // ------------------------------------------------------------------------ MMA issuer
     constexpr uint32_t idesc_qk = make_idesc(kTile, kTile, 0, 0);
     constexpr uint32_t idesc_pv = make_idesc(kTile, D, 0, 1);
+    // operand descriptors: constant high half, low half = base + (byte offset >> 4)
+    constexpr uint32_t hi = desc_hi(1024);
+    const uint32_t q_lo = desc_lo(smem_u32(sq), 16), k_lo = desc_lo(smem_u32(sk), 16);
+    const uint32_t p_lo = desc_lo(smem_u32(sp), 16), v_lo = desc_lo(smem_u32(sv), kBlockBytes);
     bool ok = mbar_wait(q_full, 0, abort_flag);
     tmem_fence_after();
     auto issue_qk = [&](int j) -> bool {
@@ -176,13 +180,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       const int sbuf = j % C::kSBufs;
       if (!mbar_wait(&k_full[s], (j >> 1) & 1u, abort_flag)) return false;
       tmem_fence_after();
-      const uint32_t qa = smem_u32(sq), ka = smem_u32(sk + s * C::kTileBytes);
+      const uint32_t stage = (uint32_t)s * (C::kTileBytes >> 4);
 #pragma unroll
       for (int c = 0; c < C::kDBlocks; ++c)
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
-          umma_bf16(tmem_base + sbuf * kTile, make_desc(qa + c * kBlockBytes + kk * 32, 16, 1024),
-                    make_desc(ka + c * kBlockBytes + kk * 32, 16, 1024), idesc_qk, (c | kk) ? 1u : 0u);
+          umma_bf16_split(tmem_base + sbuf * kTile, q_lo + ((c * kBlockBytes + kk * 32) >> 4), hi,
+                          k_lo + stage + ((c * kBlockBytes + kk * 32) >> 4), hi, idesc_qk, (c | kk) ? 1u : 0u);
       umma_commit(&k_empty[s]);
       umma_commit(&s_full[sbuf]);
       return true;
@@ -197,13 +201,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       const int s = j & 1;
       if (!mbar_wait(&v_full[s], (j >> 1) & 1u, abort_flag)) { ok = false; break; }
       tmem_fence_after();
-      const uint32_t pa = smem_u32(sp), va = smem_u32(sv + s * C::kTileBytes);
+      const uint32_t vstage = (uint32_t)s * (C::kTileBytes >> 4);
 #pragma unroll
       for (int kk = 0; kk < 8; ++kk)
-        umma_bf16(tmem_base + C::kOCol + s * D,
-                  make_desc(pa + (kk >> 2) * kBlockBytes + (kk & 3) * 32, 16, 1024),
-                  make_desc(va + kk * 2048, kBlockBytes, 1024), idesc_pv, kk ? 1u : 0u);
-      umma_commit(&v_empty[s]);
+        umma_bf16_split(tmem_base + C::kOCol + s * D, p_lo + (((kk >> 2) * kBlockBytes + (kk & 3) * 32) >> 4), hi,
+                        v_lo + vstage + ((kk * 2048) >> 4), hi, idesc_pv, kk ? 1u : 0u);
+      // one commit serves both readers of "P V of this step is done": the softmax warps (partial
+      // output ready) and the producer (V stage free); a commit costs the issuing thread ~100 cycles
       umma_commit(&o_full[s]);
     }
     if (!ok && atomicCAS(const_cast<int*>(abort_flag), 0, 1) == 0) atomicExch(p.status, kTimeoutMma);
@@ -384,7 +388,7 @@ flash_fwd_small_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   uint64_t* k_full = bars + 1;     // [2]
   uint64_t* k_empty = bars + 3;    // [2]
   uint64_t* v_full = bars + 5;     // [2]
-  uint64_t* v_empty = bars + 7;    // [2]
+  uint64_t* v_empty = bars + 7;    // [2] spare: the V stage is released through o_full
   uint64_t* s_full = bars + 9;     // [2]
   uint64_t* o_full = bars + 11;    // [2]
   uint64_t* p_full = bars + 13;
@@ -428,7 +432,7 @@ flash_fwd_small_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
       for (int c = 0; c < C::kDBlocks; ++c)
         tma_load_4d(sk + s * C::kTileBytes + c * kBlockBytes, &map_k, &k_full[s], c * 64, j * kTile, hi, bi);
-      if (!mbar_wait(&v_empty[s], ph, abort_flag)) { ok = false; break; }
+      if (!mbar_wait(&o_full[s], ph, abort_flag)) { ok = false; break; }     // P V of step j-2 done
       mbar_expect_tx(&v_full[s], C::kTileBytes);
 #pragma unroll
       for (int c = 0; c < C::kDBlocks; ++c)
@@ -448,6 +452,10 @@ flash_fwd_small_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     // ------------------------------------------------------------------------ MMA issuer
     constexpr uint32_t idesc_qk = make_idesc(kTile, kTile, 0, 0);
     constexpr uint32_t idesc_pv = make_idesc(kTile, D, 0, 1);
+    // operand descriptors: constant high half, low half = base + (byte offset >> 4)
+    constexpr uint32_t hi = desc_hi(1024);
+    const uint32_t q_lo = desc_lo(smem_u32(sq), 16), k_lo = desc_lo(smem_u32(sk), 16);
+    const uint32_t p_lo = desc_lo(smem_u32(sp), 16), v_lo = desc_lo(smem_u32(sv), kBlockBytes);
     bool ok = mbar_wait(q_full, 0, abort_flag);
     tmem_fence_after();
     auto issue_qk = [&](int j) -> bool {
@@ -455,13 +463,13 @@ flash_fwd_small_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       const int sbuf = j % C::kSBufs;
       if (!mbar_wait(&k_full[s], (j >> 1) & 1u, abort_flag)) return false;
       tmem_fence_after();
-      const uint32_t qa = smem_u32(sq), ka = smem_u32(sk + s * C::kTileBytes);
+      const uint32_t stage = (uint32_t)s * (C::kTileBytes >> 4);
 #pragma unroll
       for (int c = 0; c < C::kDBlocks; ++c)
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
-          umma_bf16(tmem_base + sbuf * kTile, make_desc(qa + c * kBlockBytes + kk * 32, 16, 1024),
-                    make_desc(ka + c * kBlockBytes + kk * 32, 16, 1024), idesc_qk, (c | kk) ? 1u : 0u);
+          umma_bf16_split(tmem_base + sbuf * kTile, q_lo + ((c * kBlockBytes + kk * 32) >> 4), hi,
+                          k_lo + stage + ((c * kBlockBytes + kk * 32) >> 4), hi, idesc_qk, (c | kk) ? 1u : 0u);
       umma_commit(&k_empty[s]);
       umma_commit(&s_full[sbuf]);
       return true;
@@ -476,13 +484,13 @@ flash_fwd_small_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       const int s = j & 1;
       if (!mbar_wait(&v_full[s], (j >> 1) & 1u, abort_flag)) { ok = false; break; }
       tmem_fence_after();
-      const uint32_t pa = smem_u32(sp), va = smem_u32(sv + s * C::kTileBytes);
+      const uint32_t vstage = (uint32_t)s * (C::kTileBytes >> 4);
 #pragma unroll
       for (int kk = 0; kk < 8; ++kk)
-        umma_bf16(tmem_base + C::kOCol + s * D,
-                  make_desc(pa + (kk >> 2) * kBlockBytes + (kk & 3) * 32, 16, 1024),
-                  make_desc(va + kk * 2048, kBlockBytes, 1024), idesc_pv, kk ? 1u : 0u);
-      umma_commit(&v_empty[s]);
+        umma_bf16_split(tmem_base + C::kOCol + s * D, p_lo + (((kk >> 2) * kBlockBytes + (kk & 3) * 32) >> 4), hi,
+                        v_lo + vstage + ((kk * 2048) >> 4), hi, idesc_pv, kk ? 1u : 0u);
+      // one commit serves both readers of "P V of this step is done": the softmax warps (partial
+      // output ready) and the producer (V stage free); a commit costs the issuing thread ~100 cycles
       umma_commit(&o_full[s]);
     }
     if (!ok && atomicCAS(const_cast<int*>(abort_flag), 0, 1) == 0) atomicExch(p.status, kTimeoutMma);
