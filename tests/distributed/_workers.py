@@ -196,3 +196,94 @@ def allgather_gemm_matches_library(rank, world, port, out):
         out.put({"ok": bool(flags[0]), "detail": results})
     dist.barrier()
     dist.destroy_process_group()
+
+
+def _tiny_mmdit(dev, dtype, layers=3):
+    from visionrl_b200.models.nn.mmdit import MMDiT, MMDiTConfig
+
+    torch.manual_seed(3)
+    cfg = MMDiTConfig(num_layers=layers, hidden_size=128, num_heads=2, patch_size=2, in_channels=4,
+                      context_dim=64, pooled_dim=32, max_grid=8)
+    return MMDiT(cfg).to(dev, dtype)
+
+
+def _mmdit_inputs(seed, dev, dtype, batch=2):
+    g = torch.Generator().manual_seed(seed)
+    lat = torch.randn(batch, 4, 8, 8, generator=g).to(dev, dtype)
+    t = torch.rand(batch, generator=g).to(dev) * 1000
+    ctx = torch.randn(batch, 8, 64, generator=g).to(dev, dtype)
+    pooled = torch.randn(batch, 32, generator=g).to(dev, dtype)
+    target = torch.randn(batch, 4, 8, 8, generator=g).to(dev)
+    return lat, t, ctx, pooled, target
+
+
+def fsdp_training_matches_replicated(rank, world, port, backend, collectives, replicate, checkpointing, out):
+    """Block weights sharded over the ranks (gather in the consuming GEMM, bucketed reduce-scatter
+    during backward, sharded AdamW) train exactly like one replicated model on the mean gradient."""
+    import copy
+
+    from visionrl_b200.ops.linear import accumulate_weight_grads_in_place
+    from visionrl_b200.ops.optim import FusedAdamW
+    from visionrl_b200.parallel.fsdp import shard_model
+    from visionrl_b200.parallel.mesh import ProcessMesh
+    from visionrl_b200.parallel.sharded import ShardedGradSync
+
+    _init(rank, world, port, backend)
+    dev = torch.device("cuda", rank) if backend == "nccl" else torch.device("cpu")
+    dtype = torch.bfloat16 if backend == "nccl" else torch.float32
+    net = _tiny_mmdit(dev, dtype)
+    ref = copy.deepcopy(net).float()
+    net.enable_gradient_checkpointing(checkpointing)
+    mesh = ProcessMesh.build(replicate=replicate)
+    rt = shard_model(net, mesh, dev, collectives=collectives, ring=2)
+    assert rt is not None and len(rt.handles) > 0
+    sync = ShardedGradSync(mesh, collectives=collectives, param_runtime=rt)
+    opt = FusedAdamW([p for p in net.parameters() if p.requires_grad], lr=1e-2, weight_decay=0.01)
+    sync.prepare(opt)
+    ref_opt = torch.optim.AdamW(ref.parameters(), lr=1e-2, weight_decay=0.01)
+    micro = 2
+    fwd_err = 0.0
+    for step in range(2):
+        opt.flat_buffers()
+        for mb in range(micro):
+            lat, t, ctx, pooled, target = _mmdit_inputs(1000 * step + 10 * mb + rank, dev, dtype)
+            pred = net(lat, t, ctx, pooled)
+            loss = ((pred.float() - target) ** 2).mean() / micro
+            with accumulate_weight_grads_in_place():
+                loss.backward()
+        norm = sync.reduce_clip_step(opt, max_norm=1.0)
+        sync.check("test step")
+        # reference: the same micro-batches of every rank on one replicated fp32 model
+        for r in range(world):
+            for mb in range(micro):
+                lat, t, ctx, pooled, target = _mmdit_inputs(1000 * step + 10 * mb + r, torch.device("cpu"),
+                                                            torch.float32)
+                pred = ref(lat, t, ctx, pooled)
+                (((pred - target) ** 2).mean() / micro / world).backward()
+        ref_norm = torch.nn.utils.clip_grad_norm_(ref.parameters(), 1.0)
+        ref_opt.step()
+        ref_opt.zero_grad()
+        tol = 5e-2 if dtype == torch.bfloat16 else 1e-4
+        assert abs(float(ref_norm) - float(norm)) <= tol * max(1.0, float(ref_norm)), (float(ref_norm), float(norm))
+    # no-grad forward (the rollout path) through the gathered weights
+    with torch.no_grad():
+        lat, t, ctx, pooled, _ = _mmdit_inputs(77, dev, dtype)
+        got = net(lat, t, ctx, pooled).float().cpu()
+        want = ref(*(_mmdit_inputs(77, torch.device("cpu"), torch.float32)[:4]))
+        fwd_err = (got - want).abs().max().item()
+    full = net.state_dict()          # gathers every sharded weight to its full shape
+    ref_state = ref.state_dict()
+    err = max((full[k].float().cpu() - ref_state[k]).abs().max().item() for k in ref_state)
+    shapes_ok = all(tuple(full[k].shape) == tuple(ref_state[k].shape) for k in ref_state)
+    opt_state = opt.state_dict()
+    report = rt.memory_report()
+    flags = torch.tensor([err, fwd_err], device=dev)
+    dist.all_reduce(flags, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        out.put({"err": float(flags[0]), "fwd_err": float(flags[1]), "shapes_ok": shapes_ok,
+                 "handles": len(rt.handles), "buckets": rt.buckets_reduced, "gathers": rt.gathers,
+                 "fused_gathers": rt.fused_gathers, "report": report,
+                 "opt_entries": len(opt_state["state"]),
+                 "params": sum(1 for _ in net.parameters())})
+    dist.barrier()
+    dist.destroy_process_group()

@@ -43,6 +43,34 @@ def test_ulysses_attention_gloo_world2():
     assert res["fwd"] and res["bwd"]
 
 
+@pytest.mark.parametrize("checkpointing", [True, False])
+def test_fsdp_gloo_world2_matches_replicated(checkpointing):
+    res = _run(_workers.fsdp_training_matches_replicated, 2, "gloo", "nccl", 1, checkpointing)
+    assert res["shapes_ok"] and res["err"] < 2e-4 and res["fwd_err"] < 1e-3, res
+    assert res["handles"] > 0 and res["buckets"] > 0
+    assert res["opt_entries"] == res["params"]
+    rep = res["report"]
+    assert rep["param_shard_bytes"] * 2 == rep["full_param_bytes"]
+
+
+def test_hsdp_gloo_world4_matches_replicated():
+    res = _run(_workers.fsdp_training_matches_replicated, 4, "gloo", "nccl", 2, True)
+    assert res["shapes_ok"] and res["err"] < 2e-4 and res["fwd_err"] < 1e-3, res
+    rep = res["report"]
+    assert rep["param_shard_bytes"] * 2 == rep["full_param_bytes"]      # sharded over 2 of the 4 ranks
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+@pytest.mark.parametrize("collectives", ["nccl", "fused"])
+def test_fsdp_gpu_matches_replicated(collectives):
+    world = min(torch.cuda.device_count(), 4)
+    res = _run(_workers.fsdp_training_matches_replicated, world, "nccl", collectives, 1, True)
+    assert res["shapes_ok"] and res["err"] < 6e-2 and res["fwd_err"] < 0.25, res
+    assert res["handles"] > 0 and res["buckets"] > 0
+    assert (res["fused_gathers"] > 0) == (collectives == "fused")
+
+
 @pytest.mark.gpu
 @pytest.mark.multigpu
 @pytest.mark.parametrize("collectives", ["nccl", "fused"])

@@ -64,6 +64,48 @@ def test_noalloc_entry_matches_tensor_entry_twice():
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("deterministic,gaussian", [(False, True), (True, True), (False, False)])
+def test_noalloc_entry_tail_unaligned_and_modes(deterministic, gaussian):
+    """Sizes that are no multiple of four, pointers offset by 4 bytes (the scalar path), the
+    deterministic step and the cps score all agree with the tensor entry point, twice."""
+    from visionrl_b200.ops import _ext
+
+    ext = _ext.load()
+    fn = _load_symbol()
+    torch.manual_seed(1)
+    batch, n = 5, 4099 * 3 + 1            # n % 4 != 0, several blocks per sample
+    def offset(t):                        # same values, storage shifted by one float (4 bytes)
+        buf = torch.empty(t.numel() + 1, device="cuda")
+        buf[1:].copy_(t.reshape(-1))
+        return buf[1:].view(t.shape)
+    v = offset(torch.randn(batch, n, device="cuda"))
+    x = offset(torch.randn(batch, n, device="cuda"))
+    noise = offset(torch.randn(batch, n, device="cuda"))
+    assert v.data_ptr() % 16 != 0
+    a, b, scale, dt = (torch.rand(batch, device="cuda") + 0.2 for _ in range(4))
+    ref_next, ref_logp, ref_mean = ext.sde_step_fwd(v.contiguous(), x.contiguous(), a, b, scale, dt,
+                                                    None, noise.contiguous(), deterministic, gaussian)
+    for _ in range(2):
+        rc, msg, nxt, logp, mean = _call(fn, v, x, a, b, scale, dt, None, noise, deterministic, gaussian)
+        torch.cuda.synchronize()
+        assert rc == 0, msg
+        assert torch.allclose(nxt, ref_next, atol=1e-6, rtol=1e-6)
+        assert torch.allclose(mean, ref_mean, atol=1e-6, rtol=1e-6)
+        assert torch.allclose(logp, ref_logp, atol=1e-5, rtol=1e-5)
+
+
+@pytest.mark.gpu
+def test_noalloc_entry_rejects_absurd_length():
+    """A length whose block count does not fit 32 bits is refused as too large (rc 2), not wrapped."""
+    fn = _load_symbol()
+    dummy = torch.zeros(8, device="cuda")
+    err = ctypes.create_string_buffer(256)
+    p = ctypes.c_void_p(dummy.data_ptr())
+    rc = fn(p, p, p, p, p, p, None, p, p, p, p, 1, (1 << 44) + 5, 0, 1, None, err, len(err))
+    assert rc == 2, err.value
+
+
+@pytest.mark.gpu
 def test_noalloc_entry_rejects_oversized_problem():
     fn = _load_symbol()
     batch, n = 20, 4096 * 4000          # 20 * 4000 partial sums > 65536

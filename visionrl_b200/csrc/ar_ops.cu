@@ -318,6 +318,7 @@ group_advantages_kernel(const float* __restrict__ rewards, const int64_t* __rest
 std::vector<torch::Tensor> token_logprob_fwd(torch::Tensor logits, torch::Tensor ids, double temperature) {
   TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.is_contiguous());
   TORCH_CHECK(ids.is_cuda() && ids.scalar_type() == torch::kInt64 && ids.numel() == logits.size(0));
+  VRL_CHECK_OPERAND(ids, logits);
   const c10::cuda::CUDAGuard guard(logits.device());
   const int64_t rows = logits.size(0);
   const int vocab = (int)logits.size(1);
@@ -345,6 +346,9 @@ std::vector<torch::Tensor> token_logprob_fwd(torch::Tensor logits, torch::Tensor
 torch::Tensor token_logprob_bwd(torch::Tensor logits, torch::Tensor ids, torch::Tensor lse,
                                 torch::Tensor g, double temperature) {
   TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.is_contiguous());
+  VRL_CHECK_OPERAND(ids, logits, torch::kInt64, logits.size(0));
+  VRL_CHECK_OPERAND(lse, logits, torch::kFloat32, logits.size(0));
+  VRL_CHECK_OPERAND(g, logits, c10::nullopt, logits.size(0));
   const c10::cuda::CUDAGuard guard(logits.device());
   const int64_t rows = logits.size(0);
   const int vocab = (int)logits.size(1);
@@ -376,6 +380,12 @@ void lse_chunk_update(torch::Tensor chunk, torch::Tensor ids, torch::Tensor run_
               chunk.scalar_type() == torch::kFloat32);
   TORCH_CHECK(run_max.scalar_type() == torch::kFloat32 && run_sum.scalar_type() == torch::kFloat32 &&
               target.scalar_type() == torch::kFloat32 && ids.scalar_type() == torch::kInt64);
+  VRL_CHECK_OPERAND(ids, chunk, torch::kInt64, chunk.size(0));
+  VRL_CHECK_OPERAND(run_max, chunk, torch::kFloat32, chunk.size(0));
+  VRL_CHECK_OPERAND(run_sum, chunk, torch::kFloat32, chunk.size(0));
+  VRL_CHECK_OPERAND(target, chunk, torch::kFloat32, chunk.size(0));
+  TORCH_CHECK(ids.is_contiguous() && run_max.is_contiguous() && run_sum.is_contiguous() && target.is_contiguous(),
+              "lse_chunk_update: per-row operands must be contiguous");
   const c10::cuda::CUDAGuard guard(chunk.device());
   const int64_t rows = chunk.size(0);
   if (rows == 0) return;
@@ -390,6 +400,11 @@ torch::Tensor softmax_grad_chunk(torch::Tensor chunk, torch::Tensor ids, torch::
                                  torch::Tensor g, int64_t col0, double temperature) {
   TORCH_CHECK(chunk.is_cuda() && chunk.dim() == 2 && chunk.is_contiguous() &&
               chunk.scalar_type() == torch::kFloat32);
+  VRL_CHECK_OPERAND(ids, chunk, torch::kInt64, chunk.size(0));
+  VRL_CHECK_OPERAND(lse, chunk, torch::kFloat32, chunk.size(0));
+  VRL_CHECK_OPERAND(g, chunk, torch::kFloat32, chunk.size(0));
+  TORCH_CHECK(ids.is_contiguous() && lse.is_contiguous() && g.is_contiguous(),
+              "softmax_grad_chunk: per-row operands must be contiguous");
   const c10::cuda::CUDAGuard guard(chunk.device());
   auto out = torch::empty(chunk.sizes(), chunk.options().dtype(torch::kBFloat16));
   const int64_t rows = chunk.size(0);
@@ -407,6 +422,8 @@ std::vector<torch::Tensor> sample_tokens(torch::Tensor cond, torch::Tensor uncon
   TORCH_CHECK(cond.is_cuda() && cond.dim() == 2 && cond.is_contiguous() && uncond.is_contiguous());
   TORCH_CHECK(cond.sizes() == uncond.sizes() && cond.scalar_type() == uncond.scalar_type());
   TORCH_CHECK(u.scalar_type() == torch::kFloat32 && u.numel() == cond.size(0) && u.is_contiguous());
+  VRL_CHECK_OPERAND(uncond, cond);
+  VRL_CHECK_OPERAND(u, cond);
   const c10::cuda::CUDAGuard guard(cond.device());
   const int64_t rows = cond.size(0);
   auto tokens = torch::empty({rows}, cond.options().dtype(torch::kInt64));
@@ -441,6 +458,12 @@ torch::Tensor decode_attention(torch::Tensor q, torch::Tensor k_cache, torch::Te
               v_cache.stride(0) % 4 == 0 && v_cache.stride(1) % 4 == 0 && v_cache.stride(2) % 4 == 0 &&
               reinterpret_cast<uintptr_t>(k_cache.data_ptr()) % 8 == 0 &&
               reinterpret_cast<uintptr_t>(v_cache.data_ptr()) % 8 == 0, "decode_attention: cache alignment");
+  VRL_CHECK_OPERAND(k_cache, q);
+  VRL_CHECK_OPERAND(v_cache, q);
+  VRL_CHECK_OPERAND(valid, q);
+  TORCH_CHECK(k_cache.size(0) >= q.size(0) && v_cache.size(0) >= q.size(0) && valid.size(0) >= q.size(0) &&
+              k_cache.size(1) == q.size(1) && v_cache.size(1) == q.size(1) && length <= v_cache.size(2),
+              "decode_attention: cache / mask shapes do not cover the query rows");
   const c10::cuda::CUDAGuard guard(q.device());
   const int64_t rows = q.size(0), heads = q.size(1);
   auto out = torch::empty_like(q);
@@ -459,6 +482,7 @@ torch::Tensor decode_attention(torch::Tensor q, torch::Tensor k_cache, torch::Te
 torch::Tensor group_advantages(torch::Tensor rewards, torch::Tensor group_ids, double eps, double clip,
                                bool global_std) {
   TORCH_CHECK(rewards.is_cuda() && rewards.dim() == 1 && group_ids.numel() == rewards.numel());
+  VRL_CHECK_OPERAND(group_ids, rewards);
   const c10::cuda::CUDAGuard guard(rewards.device());
   auto r = rewards.to(torch::kFloat32).contiguous();
   auto g = group_ids.to(torch::kInt64).contiguous();

@@ -579,6 +579,11 @@ std::vector<torch::Tensor> flash_attn_bwd(torch::Tensor dout, torch::Tensor q, t
   TORCH_CHECK(dout.sizes() == q.sizes() && out.sizes() == q.sizes());
   TORCH_CHECK(lse.scalar_type() == torch::kFloat32 && lse.is_contiguous() && lse.numel() == b * h * sq);
   TORCH_CHECK(b * h <= 65535, "flash_attn_bwd: batch * heads exceeds the grid limit");
+  VRL_CHECK_OPERAND(dout, q);
+  VRL_CHECK_OPERAND(k, q);
+  VRL_CHECK_OPERAND(v, q);
+  VRL_CHECK_OPERAND(out, q);
+  VRL_CHECK_OPERAND(lse, q);
   q = mappable(q);
   k = mappable(k);
   v = mappable(v);

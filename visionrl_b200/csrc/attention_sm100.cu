@@ -627,18 +627,7 @@ flash_fwd_small_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 }
 
 // --------------------------------------------------------------------------------- host side
-int* status_word(int device) {
-  static std::map<int, int*> words;
-  static std::mutex mu;
-  std::lock_guard<std::mutex> lock(mu);
-  auto it = words.find(device);
-  if (it != words.end()) return it->second;
-  int* w = nullptr;
-  C10_CUDA_CHECK(cudaMalloc(&w, sizeof(int)));
-  C10_CUDA_CHECK(cudaMemset(w, 0, sizeof(int)));
-  words[device] = w;
-  return w;
-}
+int* status_word(int device) { return kernel_status_block(device) + kStatusAttention; }
 
 static void launch_small(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const Params& p,
                          int q_tiles, int bh, cudaStream_t stream) {
@@ -667,15 +656,6 @@ static void launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorM
 
 }  // namespace attn
 
-int64_t flash_attn_last_status() {
-  int device = 0;
-  C10_CUDA_CHECK(cudaGetDevice(&device));
-  int host = 0;
-  C10_CUDA_CHECK(cudaMemcpy(&host, attn::status_word(device), sizeof(int), cudaMemcpyDeviceToHost));
-  if (host != 0) C10_CUDA_CHECK(cudaMemset(attn::status_word(device), 0, sizeof(int)));
-  return host;
-}
-
 std::vector<torch::Tensor> flash_attn_fwd(torch::Tensor q, torch::Tensor k, torch::Tensor v, double scale) {
   using namespace attn;
   TORCH_CHECK(q.is_cuda() && q.dim() == 4 && k.dim() == 4 && v.dim() == 4, "flash_attn_fwd: [B, H, S, D]");
@@ -684,6 +664,8 @@ std::vector<torch::Tensor> flash_attn_fwd(torch::Tensor q, torch::Tensor k, torc
   const int64_t b = q.size(0), h = q.size(1), sq = q.size(2), d = q.size(3), skv = k.size(2);
   TORCH_CHECK(d == 64 || d == 128, "flash_attn_fwd: head dimension 64 or 128");
   TORCH_CHECK(k.size(0) == b && k.size(1) == h && k.size(3) == d && v.sizes() == k.sizes());
+  VRL_CHECK_OPERAND(k, q);
+  VRL_CHECK_OPERAND(v, q);
   q = mappable(q);
   k = mappable(k);
   v = mappable(v);

@@ -49,6 +49,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("p2p_broadcast_versioned", &vrl::p2p_broadcast_versioned);
   m.def("wait_flag", &vrl::wait_flag);
   m.def("ulysses_scatter", &vrl::ulysses_scatter);
+  m.def("flag_signal", &vrl::flag_signal);
+  m.def("flag_wait", &vrl::flag_wait);
+  m.def("flag_barrier", &vrl::flag_barrier);
+  m.def("bucket_reduce_acc", &vrl::bucket_reduce_acc);
+  m.def("p2p_gather_rows", &vrl::p2p_gather_rows);
   m.def("token_logprob_fwd", &vrl::token_logprob_fwd);
   m.def("token_logprob_bwd", &vrl::token_logprob_bwd);
   m.def("lse_chunk_update", &vrl::lse_chunk_update);
@@ -73,5 +78,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_bf16_dual", &vrl::gemm_bf16_dual);
   m.def("gemm_allgather", &vrl::gemm_allgather);
   m.def("gemm_bf16_acc", &vrl::gemm_bf16_acc);
+  m.def("gemm_bf16_out", &vrl::gemm_bf16_out);
   m.def("gemm_last_status", &vrl::gemm_last_status);
+  m.def("kernel_status_all", &vrl::kernel_status_all);
 }

@@ -167,8 +167,14 @@ void adamw_slice_broadcast(torch::Tensor peers, torch::Tensor g, torch::Tensor m
                            torch::Tensor m, torch::Tensor v, int64_t lo, int64_t n, int64_t world,
                            int64_t rank, double lr, double b1, double b2, double eps, double wd,
                            int64_t step, c10::optional<torch::Tensor> clip, bool is_bf16) {
-  TORCH_CHECK(g.is_cuda() && g.scalar_type() == torch::kFloat32 && g.numel() >= n);
-  TORCH_CHECK(master.scalar_type() == torch::kFloat32 && master.numel() >= n);
+  TORCH_CHECK(g.is_cuda() && g.scalar_type() == torch::kFloat32 && g.numel() >= n && g.is_contiguous());
+  VRL_CHECK_OPERAND(master, g, torch::kFloat32);
+  VRL_CHECK_OPERAND(m, g, torch::kFloat32);
+  VRL_CHECK_OPERAND(v, g, torch::kFloat32);
+  VRL_CHECK_OPERAND(clip, g);
+  TORCH_CHECK(master.numel() >= n && m.numel() >= n && v.numel() >= n && master.is_contiguous() &&
+              m.is_contiguous() && v.is_contiguous(),
+              "adamw_slice_broadcast: master / moments must be contiguous and cover the slice");
   TORCH_CHECK(lo % 8 == 0 && n % 8 == 0, "slice bounds must be multiples of 8 elements");
   const c10::cuda::CUDAGuard guard(g.device());
   const PeerPtrs pp = load_peers(peers, (int)world);
@@ -263,6 +269,214 @@ torch::Tensor wait_flag(torch::Tensor flags, int64_t slot, int64_t expected, dou
       flags.data_ptr<int>() + slot, (int)expected, status.data_ptr<int>(), spins);
   C10_CUDA_KERNEL_LAUNCH_CHECK();
   return status;
+}
+
+// ------------------------------------------------------------------------------------------
+// Flag signalling between ranks.  A flag array is a small symmetric int32 allocation; slot
+// (base + r) of every rank's array is written only by rank r, so no slot has two writers.
+// Every wait is bounded by wall-clock time (%globaltimer): on expiry the kernel records
+// {1, peer slot, last value seen, value expected} in `status` (first failure wins) and RETURNS,
+// so a departed peer costs the others a timeout and a Python exception, never a hung GPU.
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+// true when `flag` reached `expected` (wrap-safe signed distance) before the deadline
+__device__ __forceinline__ bool bounded_flag_wait(const int* flag, int expected, unsigned long long timeout_ns,
+                                                  int* seen_out) {
+  const unsigned long long t0 = global_ns();
+  int seen = 0;
+  for (;;) {
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
+    if (seen - expected >= 0) { *seen_out = seen; return true; }
+    if (global_ns() - t0 > timeout_ns) { *seen_out = seen; return false; }
+    __nanosleep(100);
+  }
+}
+
+__device__ __forceinline__ void report_timeout(int* status, int slot, int seen, int expected) {
+  if (atomicCAS(status, 0, 1) == 0) {
+    status[1] = slot;
+    status[2] = seen;
+    status[3] = expected;
+  }
+}
+
+// Lane r stores `value` into slot `slot` of rank r's flag array.  Everything this rank wrote
+// before (earlier kernels of the stream included) is visible to a peer that acquires the flag.
+__global__ void flag_signal_kernel(PeerPtrs flags, int slot, int world, int value) {
+  __threadfence_system();
+  if (threadIdx.x < world) {
+    int* f = reinterpret_cast<int*>(flags.p[threadIdx.x]) + slot;
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(f), "r"(value) : "memory");
+  }
+}
+
+// Lane i waits until local slot (slot0 + i) has reached `expected`.
+__global__ void flag_wait_kernel(const int* __restrict__ flags, int slot0, int count, int expected,
+                                 unsigned long long timeout_ns, int* __restrict__ status) {
+  if (threadIdx.x < count) {
+    int seen = 0;
+    if (!bounded_flag_wait(flags + slot0 + threadIdx.x, expected, timeout_ns, &seen))
+      report_timeout(status, slot0 + threadIdx.x, seen, expected);
+  }
+  __threadfence_system();
+}
+
+// Barrier = signal every peer, then wait for every peer, in one launch.
+__global__ void flag_barrier_kernel(PeerPtrs flags, const int* __restrict__ local, int base, int world,
+                                    int rank, int epoch, unsigned long long timeout_ns,
+                                    int* __restrict__ status) {
+  __threadfence_system();
+  if (threadIdx.x < world) {
+    int* f = reinterpret_cast<int*>(flags.p[threadIdx.x]) + base + rank;
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(f), "r"(epoch) : "memory");
+    int seen = 0;
+    if (!bounded_flag_wait(local + base + threadIdx.x, epoch, timeout_ns, &seen))
+      report_timeout(status, base + threadIdx.x, seen, epoch);
+  }
+  __threadfence_system();
+}
+
+static unsigned long long to_ns(double timeout_s) {
+  return (unsigned long long)(std::max(1e-4, std::min(timeout_s, 600.0)) * 1e9);
+}
+
+static void check_flags(const torch::Tensor& flags, const torch::Tensor& status, int64_t last_slot) {
+  TORCH_CHECK(flags.is_cuda() && flags.scalar_type() == torch::kInt32 && flags.is_contiguous() &&
+              last_slot < flags.numel(), "flag array: contiguous int32 CUDA tensor covering the slots");
+  VRL_CHECK_OPERAND(status, flags, torch::kInt32);
+  TORCH_CHECK(status.numel() >= 4 && status.is_contiguous(), "status: int32[>=4]");
+}
+
+void flag_signal(torch::Tensor flag_peers, torch::Tensor flags, int64_t slot, int64_t world, int64_t value) {
+  TORCH_CHECK(flags.is_cuda() && flags.scalar_type() == torch::kInt32 && slot >= 0 && slot < flags.numel());
+  const c10::cuda::CUDAGuard guard(flags.device());
+  const PeerPtrs fp = load_peers(flag_peers, (int)world);
+  flag_signal_kernel<<<1, 32, 0, at::cuda::getCurrentCUDAStream()>>>(fp, (int)slot, (int)world, (int)value);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
+void flag_wait(torch::Tensor flags, int64_t slot0, int64_t count, int64_t expected, double timeout_s,
+               torch::Tensor status) {
+  TORCH_CHECK(count >= 1 && count <= 32 && slot0 >= 0, "flag_wait: 1..32 consecutive slots");
+  check_flags(flags, status, slot0 + count - 1);
+  const c10::cuda::CUDAGuard guard(flags.device());
+  flag_wait_kernel<<<1, 32, 0, at::cuda::getCurrentCUDAStream()>>>(
+      flags.data_ptr<int>(), (int)slot0, (int)count, (int)expected, to_ns(timeout_s), status.data_ptr<int>());
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
+void flag_barrier(torch::Tensor flag_peers, torch::Tensor flags, int64_t base, int64_t world, int64_t rank,
+                  int64_t epoch, double timeout_s, torch::Tensor status) {
+  TORCH_CHECK(world >= 1 && world <= kMaxPeers && rank >= 0 && rank < world && base >= 0);
+  check_flags(flags, status, base + world - 1);
+  const c10::cuda::CUDAGuard guard(flags.device());
+  const PeerPtrs fp = load_peers(flag_peers, (int)world);
+  flag_barrier_kernel<<<1, 32, 0, at::cuda::getCurrentCUDAStream()>>>(
+      fp, flags.data_ptr<int>(), (int)base, (int)world, (int)rank, (int)epoch, to_ns(timeout_s),
+      status.data_ptr<int>());
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------------------------------
+// Sharded-parameter training (F1 / F2 support kernels).
+//
+//   bucket_reduce_acc   gradient reduce-scatter of one bucket fused with the bf16 -> fp32 cast,
+//                       the scale and the accumulation into this rank's persistent fp32 gradient
+//                       shard: for every segment (one per weight of the bucket)
+//                           gshard[dst + i] += scale * sum_r stage_r[src + i]
+//                       where stage_r is rank r's staging buffer read over NVLink.
+//   p2p_gather_rows     stand-alone all-gather of a row-sharded weight into a local full buffer
+//                       (the fused form lives in the GEMM; this one serves checkpoints and the
+//                       rare backward that finds its gathered copy evicted).
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+bucket_reduce_acc_kernel(PeerPtrs stage, const int64_t* __restrict__ table, float* __restrict__ gshard,
+                         float scale, int world, int rank) {
+  const int64_t src = table[blockIdx.y * 3 + 0], dst = table[blockIdx.y * 3 + 1];
+  const int64_t nvec = table[blockIdx.y * 3 + 2] / 8;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    bf16x8 part[kMaxPeers];
+    // issue every peer's load before the first use: NVLink latency overlaps across peers
+#pragma unroll
+    for (int r = 0; r < kMaxPeers; ++r) {
+      if (r < world) {
+        const int from = (rank + r) % world;
+        part[r] = *(reinterpret_cast<const bf16x8*>(reinterpret_cast<const __nv_bfloat16*>(stage.p[from]) + src) + i);
+      }
+    }
+    float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int r = 0; r < kMaxPeers; ++r) {
+      if (r < world) {
+        float f[8];
+        unpack8(part[r], f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) s[j] += f[j];
+      }
+    }
+    float4* out = reinterpret_cast<float4*>(gshard + dst + i * 8);
+    float4 lo = out[0], hi = out[1];
+    lo.x += scale * s[0]; lo.y += scale * s[1]; lo.z += scale * s[2]; lo.w += scale * s[3];
+    hi.x += scale * s[4]; hi.y += scale * s[5]; hi.z += scale * s[6]; hi.w += scale * s[7];
+    out[0] = lo;
+    out[1] = hi;
+  }
+}
+
+void bucket_reduce_acc(torch::Tensor stage_peers, torch::Tensor table, torch::Tensor gshard, double scale,
+                       int64_t world, int64_t rank, int64_t max_segment) {
+  TORCH_CHECK(gshard.is_cuda() && gshard.scalar_type() == torch::kFloat32 && gshard.is_contiguous() &&
+              reinterpret_cast<uintptr_t>(gshard.data_ptr()) % 16 == 0, "bucket_reduce_acc: fp32 gradient shard");
+  VRL_CHECK_OPERAND(table, gshard, torch::kInt64);
+  TORCH_CHECK(table.dim() == 2 && table.size(1) == 3 && table.is_contiguous() && table.size(0) >= 1 &&
+              table.size(0) <= 65535, "bucket_reduce_acc: segment table [segments, 3] (src, dst, count)");
+  TORCH_CHECK(world >= 1 && world <= kMaxPeers && rank >= 0 && rank < world && max_segment > 0);
+  const c10::cuda::CUDAGuard guard(gshard.device());
+  const PeerPtrs sp = load_peers(stage_peers, (int)world);
+  const int bx = (int)std::max<int64_t>(1, std::min<int64_t>((max_segment / 8 + 255) / 256, 64));
+  bucket_reduce_acc_kernel<<<dim3(bx, (unsigned)table.size(0)), 256, 0, at::cuda::getCurrentCUDAStream()>>>(
+      sp, table.data_ptr<int64_t>(), gshard.data_ptr<float>(), (float)scale, (int)world, (int)rank);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
+__global__ void __launch_bounds__(256)
+p2p_gather_rows_kernel(PeerPtrs shards, uint4* __restrict__ full, int64_t vec_per_shard, int world, int rank) {
+  for (int step = 0; step < world; ++step) {
+    const int r = (rank + step) % world;
+    const uint4* src = reinterpret_cast<const uint4*>(shards.p[r]);
+    uint4* dst = full + (int64_t)r * vec_per_shard;
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (; i + 3 * stride < vec_per_shard; i += 4 * stride) {
+      const uint4 v0 = src[i], v1 = src[i + stride], v2 = src[i + 2 * stride], v3 = src[i + 3 * stride];
+      dst[i] = v0; dst[i + stride] = v1; dst[i + 2 * stride] = v2; dst[i + 3 * stride] = v3;
+    }
+    for (; i < vec_per_shard; i += stride) dst[i] = src[i];
+  }
+}
+
+void p2p_gather_rows(torch::Tensor shard_peers, torch::Tensor full, int64_t shard_elems, int64_t world,
+                     int64_t rank) {
+  TORCH_CHECK(full.is_cuda() && full.is_contiguous() && full.element_size() == 2 &&
+              full.numel() == shard_elems * world && shard_elems % 8 == 0 &&
+              reinterpret_cast<uintptr_t>(full.data_ptr()) % 16 == 0,
+              "p2p_gather_rows: `full` must hold world * shard_elems 16-bit elements, 16-byte aligned");
+  TORCH_CHECK(world >= 1 && world <= kMaxPeers && rank >= 0 && rank < world);
+  const c10::cuda::CUDAGuard guard(full.device());
+  const PeerPtrs sp = load_peers(shard_peers, (int)world);
+  for (int r = 0; r < world; ++r)
+    TORCH_CHECK(reinterpret_cast<uintptr_t>(sp.p[r]) % 16 == 0, "p2p_gather_rows: shard addresses must be 16-byte aligned");
+  const int64_t vec = shard_elems / 8;
+  const int blocks = (int)std::max<int64_t>(1, std::min<int64_t>((vec + 1023) / 1024, 148 * 4));
+  p2p_gather_rows_kernel<<<blocks, 256, 0, at::cuda::getCurrentCUDAStream()>>>(
+      sp, reinterpret_cast<uint4*>(full.data_ptr()), vec, (int)world, (int)rank);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
 
 // ------------------------------------------------------------------------------------------

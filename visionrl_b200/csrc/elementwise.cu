@@ -123,6 +123,14 @@ std::vector<torch::Tensor> sde_step_fwd(torch::Tensor v, torch::Tensor x, torch:
   TORCH_CHECK(v.is_cuda() && v.scalar_type() == torch::kFloat32 && v.is_contiguous());
   TORCH_CHECK(x.scalar_type() == torch::kFloat32 && x.is_contiguous() && x.sizes() == v.sizes());
   TORCH_CHECK(prev_sample.has_value() || noise.has_value(), "need prev_sample or noise");
+  TORCH_CHECK(v.dim() >= 1 && v.size(0) > 0, "sde_step_fwd: empty batch");
+  VRL_CHECK_OPERAND(x, v);
+  VRL_CHECK_OPERAND(a, v, c10::nullopt, v.size(0));
+  VRL_CHECK_OPERAND(b, v, c10::nullopt, v.size(0));
+  VRL_CHECK_OPERAND(scale, v, c10::nullopt, v.size(0));
+  VRL_CHECK_OPERAND(dt, v, c10::nullopt, v.size(0));
+  VRL_CHECK_OPERAND(prev_sample, v);
+  VRL_CHECK_OPERAND(noise, v);
   const c10::cuda::CUDAGuard guard(v.device());
   const int batch = (int)v.size(0);
   const int64_t n = v.numel() / batch;
@@ -178,6 +186,15 @@ __global__ void sde_step_bwd_kernel(const float* __restrict__ prev, const float*
 std::vector<torch::Tensor> sde_step_bwd(torch::Tensor prev, torch::Tensor mean, torch::Tensor a,
                                         torch::Tensor b, torch::Tensor scale, torch::Tensor g_logp,
                                         c10::optional<torch::Tensor> g_mean, bool gaussian) {
+  TORCH_CHECK(prev.is_cuda() && prev.scalar_type() == torch::kFloat32 && prev.is_contiguous() &&
+              prev.dim() >= 1 && prev.size(0) > 0, "sde_step_bwd: prev must be contiguous fp32 CUDA");
+  VRL_CHECK_OPERAND(mean, prev, torch::kFloat32, prev.numel());
+  TORCH_CHECK(mean.is_contiguous(), "sde_step_bwd: mean must be contiguous");
+  VRL_CHECK_OPERAND(a, prev, c10::nullopt, prev.size(0));
+  VRL_CHECK_OPERAND(b, prev, c10::nullopt, prev.size(0));
+  VRL_CHECK_OPERAND(scale, prev, c10::nullopt, prev.size(0));
+  VRL_CHECK_OPERAND(g_logp, prev, c10::nullopt, prev.size(0));
+  VRL_CHECK_OPERAND(g_mean, prev, c10::nullopt, prev.numel());
   const c10::cuda::CUDAGuard guard(prev.device());
   const int batch = (int)prev.size(0);
   const int64_t n = prev.numel() / batch;
@@ -265,7 +282,11 @@ std::vector<torch::Tensor> token_loss_fwd(torch::Tensor lp, torch::Tensor old, t
                                           c10::optional<torch::Tensor> mask,
                                           c10::optional<torch::Tensor> ref, double eps_clip,
                                           bool k3) {
-  TORCH_CHECK(lp.is_cuda() && lp.dim() == 2 && lp.scalar_type() == torch::kFloat32);
+  TORCH_CHECK(lp.is_cuda() && lp.dim() == 2 && lp.scalar_type() == torch::kFloat32 && lp.is_contiguous());
+  VRL_CHECK_OPERAND(old, lp, c10::nullopt, lp.numel());
+  VRL_CHECK_OPERAND(adv, lp, c10::nullopt, lp.size(0));
+  VRL_CHECK_OPERAND(mask, lp, c10::nullopt, lp.numel());
+  VRL_CHECK_OPERAND(ref, lp, c10::nullopt, lp.numel());
   const c10::cuda::CUDAGuard guard(lp.device());
   const int batch = (int)lp.size(0), len = (int)lp.size(1);
   old = old.to(torch::kFloat32).contiguous();
@@ -316,6 +337,7 @@ __global__ void mean_finalize_kernel(const float* __restrict__ partial, float* _
 
 torch::Tensor per_sample_mse(torch::Tensor pred, torch::Tensor target) {
   TORCH_CHECK(pred.is_cuda() && pred.sizes() == target.sizes() && pred.dtype() == target.dtype());
+  VRL_CHECK_OPERAND(target, pred);
   const c10::cuda::CUDAGuard guard(pred.device());
   pred = pred.contiguous();
   target = target.contiguous();
@@ -429,7 +451,13 @@ void adamw_flat(torch::Tensor p, torch::Tensor g, torch::Tensor master, torch::T
                 torch::Tensor v, double lr, double b1, double b2, double eps, double wd,
                 int64_t step, c10::optional<torch::Tensor> clip) {
   TORCH_CHECK(p.is_cuda() && p.is_contiguous() && g.is_contiguous());
-  TORCH_CHECK(master.scalar_type() == torch::kFloat32 && m.scalar_type() == torch::kFloat32);
+  VRL_CHECK_OPERAND(g, p, c10::nullopt, p.numel());
+  VRL_CHECK_OPERAND(master, p, torch::kFloat32, p.numel());
+  VRL_CHECK_OPERAND(m, p, torch::kFloat32, p.numel());
+  VRL_CHECK_OPERAND(v, p, torch::kFloat32, p.numel());
+  VRL_CHECK_OPERAND(clip, p);
+  TORCH_CHECK(master.is_contiguous() && m.is_contiguous() && v.is_contiguous(),
+              "adamw_flat: optimizer state must be contiguous");
   const c10::cuda::CUDAGuard guard(p.device());
   const int64_t n = p.numel();
   TORCH_CHECK(g.numel() == n && master.numel() == n && m.numel() == n && v.numel() == n);

@@ -239,7 +239,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       if (r >= p.g_world) r -= p.g_world;
       const uint4* src = reinterpret_cast<const uint4*>(p.g_peer[r]);
       uint4* dst = reinterpret_cast<uint4*>(p.g_full + (int64_t)r * p.g_rows * p.k);
-      for (int64_t v = v_lo + gt; v < v_hi; v += kGatherThreads) dst[v] = src[v];
+      // four independent 16-byte loads in flight per thread: a peer load takes microseconds, so
+      // bandwidth over NVLink needs many outstanding requests
+      int64_t v = v_lo + gt;
+      for (; v + 3 * kGatherThreads < v_hi; v += 4 * kGatherThreads) {
+        const uint4 t0 = src[v], t1 = src[v + kGatherThreads], t2 = src[v + 2 * kGatherThreads],
+                    t3 = src[v + 3 * kGatherThreads];
+        dst[v] = t0;
+        dst[v + kGatherThreads] = t1;
+        dst[v + 2 * kGatherThreads] = t2;
+        dst[v + 3 * kGatherThreads] = t3;
+      }
+      for (; v < v_hi; v += kGatherThreads) dst[v] = src[v];
       __threadfence();
       asm volatile("bar.sync 1, %0;" ::"n"(kGatherThreads) : "memory");
       if (gt == 0) {
@@ -450,29 +461,17 @@ static CUtensorMap make_map(const void* base, uint64_t inner, uint64_t outer, ui
   return map;
 }
 
-static int* status_word(int device) {
-  static std::map<int, int*> words;
-  static std::mutex mu;
-  std::lock_guard<std::mutex> lock(mu);
-  auto it = words.find(device);
-  if (it != words.end()) return it->second;
-  int* w = nullptr;
-  C10_CUDA_CHECK(cudaMalloc(&w, sizeof(int)));
-  C10_CUDA_CHECK(cudaMemset(w, 0, sizeof(int)));
-  words[device] = w;
-  return w;
-}
+static int* status_word(int device) { return kernel_status_block(device) + kStatusGemm; }
 
 }  // namespace gemm
 
-int64_t gemm_last_status() {
-  int device = 0;
-  C10_CUDA_CHECK(cudaGetDevice(&device));
-  int host = 0;
-  C10_CUDA_CHECK(cudaMemcpy(&host, gemm::status_word(device), sizeof(int), cudaMemcpyDeviceToHost));
-  if (host != 0) C10_CUDA_CHECK(cudaMemset(gemm::status_word(device), 0, sizeof(int)));
-  return host;
-}
+// All-gather fused into the GEMM: the B operand [N, K] is sharded by rows over `world` ranks.
+// `peer_ptrs` (CPU int64) holds every rank's shard address as mapped into this process, `ready`
+// is an int32 [world] scratch; the gathered rows land in the tensor passed as `b`.
+struct GatherSpec {
+  torch::Tensor peer_ptrs, ready;
+  int64_t rank, world;
+};
 
 static std::vector<torch::Tensor> gemm_impl(torch::Tensor a, torch::Tensor b,
                                             c10::optional<torch::Tensor> bias,
@@ -480,7 +479,8 @@ static std::vector<torch::Tensor> gemm_impl(torch::Tensor a, torch::Tensor b,
                                             c10::optional<torch::Tensor> residual, int64_t act,
                                             int64_t rows_per_gate, bool a_mn_major, bool b_mn_major,
                                             bool out_fp32, bool dual,
-                                            c10::optional<torch::Tensor> out_given = c10::nullopt);
+                                            c10::optional<torch::Tensor> out_given = c10::nullopt,
+                                            const struct GatherSpec* gather = nullptr);
 
 torch::Tensor gemm_bf16(torch::Tensor a, torch::Tensor b, c10::optional<torch::Tensor> bias,
                         c10::optional<torch::Tensor> gate, c10::optional<torch::Tensor> residual,
@@ -510,7 +510,8 @@ static std::vector<torch::Tensor> gemm_impl(torch::Tensor a, torch::Tensor b,
                                             c10::optional<torch::Tensor> residual, int64_t act,
                                             int64_t rows_per_gate, bool a_mn_major, bool b_mn_major,
                                             bool out_fp32, bool dual,
-                                            c10::optional<torch::Tensor> out_given) {
+                                            c10::optional<torch::Tensor> out_given,
+                                            const GatherSpec* gather) {
   using namespace gemm;
   TORCH_CHECK(act >= 0 && act <= 3, "gemm_bf16: unknown epilogue activation");
   TORCH_CHECK(act != 3 || (residual.has_value() && !gate.has_value() && !out_fp32),
@@ -519,6 +520,11 @@ static std::vector<torch::Tensor> gemm_impl(torch::Tensor a, torch::Tensor b,
   TORCH_CHECK(a.is_cuda() && b.is_cuda() && a.dim() == 2 && b.dim() == 2);
   TORCH_CHECK(a.scalar_type() == torch::kBFloat16 && b.scalar_type() == torch::kBFloat16);
   TORCH_CHECK(a.stride(1) == 1 && b.stride(1) == 1, "gemm_bf16: innermost dimension must be contiguous");
+  VRL_CHECK_OPERAND(b, a);
+  VRL_CHECK_OPERAND(bias, a);
+  VRL_CHECK_OPERAND(gate, a);
+  VRL_CHECK_OPERAND(residual, a);
+  VRL_CHECK_OPERAND(out_given, a);
   const c10::cuda::CUDAGuard guard(a.device());
   // The tensor-map encoder is a driver entry point.  A thread that has made no runtime call yet
   // (a fresh autograd worker) has no context bound, so bind the primary context once per thread.
@@ -593,75 +599,6 @@ static std::vector<torch::Tensor> gemm_impl(torch::Tensor a, torch::Tensor b,
   static const bool attr_set = [] {
     C10_CUDA_CHECK(cudaFuncSetAttribute(gemm_bf16_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         kSmemBytes));
-    return true;
-  }();
-  (void)attr_set;
-  const int tiles = (int)(((m + BM - 1) / BM) * ((n + BN - 1) / BN));
-  const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
-  const int grid = std::min(tiles, sms);
-  // output / residual maps: 64-column x 32-row boxes matching one epilogue warp's staging tile
-  CUtensorMap map_c = out_fp32 ? map_a : make_map(out.data_ptr(), n, m, n, 64, 32);
-  CUtensorMap map_r = (p.residual && !out_fp32) ? make_map(p.residual, n, m, n, 64, 32) : map_c;
-  CUtensorMap map_c2 = dual ? make_map(pre.data_ptr(), n, m, n, 64, 32) : map_c;
-  gemm_bf16_kernel<false><<<grid, kThreads, kSmemBytes, at::cuda::getCurrentCUDAStream()>>>(
-      map_a, map_b, map_c, map_r, map_c2, p);
-  C10_CUDA_KERNEL_LAUNCH_CHECK();
-  return {out, pre};
-}
-
-// y = act(x W^T + bias) where W [N, K] is sharded by rows over `world` ranks.  `peer_ptrs` holds the
-// address of every rank's shard [N / world, K] as mapped into THIS process (own shard included),
-// `full` is a local [N, K] buffer the kernel gathers the shards into while it computes, `ready`
-// a zeroed int32 [world] scratch.  All ranks' shards must be complete before the launch.
-torch::Tensor gemm_allgather(torch::Tensor x, torch::Tensor peer_ptrs, torch::Tensor full,
-                             torch::Tensor ready, c10::optional<torch::Tensor> bias, int64_t act,
-                             int64_t rank, int64_t world) {
-  using namespace gemm;
-  TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.scalar_type() == torch::kBFloat16 && x.stride(1) == 1);
-  TORCH_CHECK(full.is_cuda() && full.dim() == 2 && full.scalar_type() == torch::kBFloat16 && full.is_contiguous());
-  TORCH_CHECK(peer_ptrs.device().is_cpu() && peer_ptrs.scalar_type() == torch::kInt64 &&
-              peer_ptrs.numel() == world, "peer_ptrs: CPU int64 tensor with one address per rank");
-  TORCH_CHECK(world >= 1 && world <= 16 && rank >= 0 && rank < world);
-  TORCH_CHECK(ready.is_cuda() && ready.scalar_type() == torch::kInt32 && ready.numel() >= world);
-  TORCH_CHECK(act >= 0 && act <= 2);
-  const int64_t m = x.size(0), k = x.size(1), n = full.size(0);
-  TORCH_CHECK(full.size(1) == k && n % world == 0 && n % 8 == 0 && k % 8 == 0 && x.stride(0) % 8 == 0);
-  TORCH_CHECK(((n / world) * k) % 8 == 0, "gemm_allgather: shard size must be a multiple of 16 bytes");
-  const c10::cuda::CUDAGuard guard(x.device());
-  static thread_local bool context_bound = false;
-  if (!context_bound) {
-    C10_CUDA_CHECK(cudaFree(nullptr));
-    context_bound = true;
-  }
-  auto out = torch::empty({m, n}, x.options());
-  if (m == 0) return out;
-  auto stream = at::cuda::getCurrentCUDAStream();
-  C10_CUDA_CHECK(cudaMemsetAsync(ready.data_ptr(), 0, sizeof(int) * world, stream));
-  Params p{};
-  p.c = out.data_ptr();
-  torch::Tensor bias_c;
-  if (bias.has_value()) {
-    bias_c = bias->to(torch::kBFloat16).contiguous();
-    TORCH_CHECK(bias_c.numel() == n);
-    p.bias = reinterpret_cast<const __nv_bfloat16*>(bias_c.data_ptr());
-  }
-  p.status = status_word(x.get_device());
-  p.m = (int)m; p.n = (int)n; p.k = (int)k;
-  p.act = (int)act;
-  p.rows_per_gate = 1;
-  const int64_t* ptrs = peer_ptrs.data_ptr<int64_t>();
-  for (int r = 0; r < world; ++r) {
-    TORCH_CHECK(ptrs[r] != 0 && ptrs[r] % 16 == 0, "gemm_allgather: shard addresses must be 16-byte aligned");
-    p.g_peer[r] = reinterpret_cast<const __nv_bfloat16*>(ptrs[r]);
-  }
-  p.g_full = reinterpret_cast<__nv_bfloat16*>(full.data_ptr());
-  p.g_ready = ready.data_ptr<int>();
-  p.g_world = (int)world; p.g_rank = (int)rank; p.g_rows = (int)(n / world);
-  p.g_first_tile = (int)((rank * (n / world)) / BN);
-  const CUtensorMap map_a = make_map(x.data_ptr(), k, m, x.stride(0), BK, BM);
-  const CUtensorMap map_b = make_map(full.data_ptr(), k, n, k, BK, BN);
-  const CUtensorMap map_c = make_map(out.data_ptr(), n, m, n, 64, 32);
-  static const bool attr_set = [] {
     C10_CUDA_CHECK(cudaFuncSetAttribute(gemm_bf16_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         kSmemBytes));
     return true;
@@ -669,11 +606,70 @@ torch::Tensor gemm_allgather(torch::Tensor x, torch::Tensor peer_ptrs, torch::Te
   (void)attr_set;
   const int tiles = (int)(((m + BM - 1) / BM) * ((n + BN - 1) / BN));
   const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
-  const int grid = std::min(tiles, sms);     // one CTA per SM at most: every CTA is resident
-  gemm_bf16_kernel<true><<<grid, kThreads + kGatherThreads, kSmemBytes, stream>>>(map_a, map_b, map_c, map_c,
-                                                                                  map_c, p);
+  // output / residual maps: 64-column x 32-row boxes matching one epilogue warp's staging tile
+  CUtensorMap map_c = out_fp32 ? map_a : make_map(out.data_ptr(), n, m, n, 64, 32);
+  CUtensorMap map_r = (p.residual && !out_fp32) ? make_map(p.residual, n, m, n, 64, 32) : map_c;
+  CUtensorMap map_c2 = dual ? make_map(pre.data_ptr(), n, m, n, 64, 32) : map_c;
+  auto stream = at::cuda::getCurrentCUDAStream();
+  if (gather != nullptr) {
+    const int64_t world = gather->world, rank = gather->rank;
+    TORCH_CHECK(!a_mn_major && !b_mn_major && b.is_contiguous(),
+                "gemm_allgather: K-major operands, contiguous gathered weight");
+    TORCH_CHECK(world >= 1 && world <= 16 && rank >= 0 && rank < world && n % world == 0 && k % 8 == 0 &&
+                ((n / world) * k) % 8 == 0, "gemm_allgather: rows must divide evenly into 16-byte aligned shards");
+    TORCH_CHECK(gather->peer_ptrs.device().is_cpu() && gather->peer_ptrs.scalar_type() == torch::kInt64 &&
+                gather->peer_ptrs.numel() == world, "peer_ptrs: CPU int64 tensor with one address per rank");
+    VRL_CHECK_OPERAND(gather->ready, a, torch::kInt32);
+    TORCH_CHECK(gather->ready.numel() >= world && gather->ready.is_contiguous());
+    const int64_t* ptrs = gather->peer_ptrs.data_ptr<int64_t>();
+    for (int r = 0; r < world; ++r) {
+      TORCH_CHECK(ptrs[r] != 0 && ptrs[r] % 16 == 0, "gemm_allgather: shard addresses must be 16-byte aligned");
+      p.g_peer[r] = reinterpret_cast<const __nv_bfloat16*>(ptrs[r]);
+    }
+    p.g_full = reinterpret_cast<__nv_bfloat16*>(b.data_ptr());
+    p.g_ready = gather->ready.data_ptr<int>();
+    p.g_world = (int)world; p.g_rank = (int)rank; p.g_rows = (int)(n / world);
+    p.g_first_tile = (int)((rank * (n / world)) / BN);
+    C10_CUDA_CHECK(cudaMemsetAsync(p.g_ready, 0, sizeof(int) * world, stream));
+    // One CTA per SM, all resident (the producers wait for every CTA's share of the gather), and
+    // ALL of them even when the product has fewer tiles: the copy wants every SM's load slots.
+    gemm_bf16_kernel<true><<<sms, kThreads + kGatherThreads, kSmemBytes, stream>>>(map_a, map_b, map_c, map_r,
+                                                                                  map_c2, p);
+  } else {
+    const int grid = std::min(tiles, sms);
+    gemm_bf16_kernel<false><<<grid, kThreads, kSmemBytes, stream>>>(map_a, map_b, map_c, map_r, map_c2, p);
+  }
   C10_CUDA_KERNEL_LAUNCH_CHECK();
-  return out;
+  return {out, pre};
+}
+
+// op(a) op(b)^T written into a caller-provided bf16 [M, N] tensor (the weight-gradient staging
+// buffers of sharded training are filled this way).
+void gemm_bf16_out(torch::Tensor a, torch::Tensor b, torch::Tensor out, bool a_mn_major, bool b_mn_major) {
+  TORCH_CHECK(out.is_cuda() && out.dim() == 2 && out.scalar_type() == torch::kBFloat16 && out.is_contiguous() &&
+              reinterpret_cast<uintptr_t>(out.data_ptr()) % 16 == 0, "gemm_bf16_out: contiguous aligned bf16 target");
+  gemm_impl(a, b, c10::nullopt, c10::nullopt, c10::nullopt, 0, 0, a_mn_major, b_mn_major, false, false, out);
+}
+
+// epilogue(x W^T + bias) where W [N, K] is sharded by rows over `world` ranks.  `peer_ptrs` holds the
+// address of every rank's shard [N / world, K] as mapped into THIS process (own shard included),
+// `full` is a local [N, K] buffer the kernel gathers the shards into while it computes (and that the
+// caller may reuse afterwards, e.g. for dX = dY W), `ready` an int32 [world] scratch.  All ranks'
+// shards must be final before the launch.  Returns {y} or, with `dual`, {act(y), y}.
+std::vector<torch::Tensor> gemm_allgather(torch::Tensor x, torch::Tensor peer_ptrs, torch::Tensor full,
+                                          torch::Tensor ready, c10::optional<torch::Tensor> bias, int64_t act,
+                                          int64_t rank, int64_t world, c10::optional<torch::Tensor> gate,
+                                          c10::optional<torch::Tensor> residual, int64_t rows_per_gate,
+                                          bool dual) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.scalar_type() == torch::kBFloat16 && x.stride(1) == 1);
+  TORCH_CHECK(full.is_cuda() && full.dim() == 2 && full.scalar_type() == torch::kBFloat16 && full.is_contiguous());
+  TORCH_CHECK(act >= 0 && act <= 2, "gemm_allgather: activation none / gelu-tanh / silu");
+  TORCH_CHECK(x.size(0) > 0, "gemm_allgather: empty activation (the gather would not run)");
+  const GatherSpec spec{peer_ptrs, ready, rank, world};
+  auto outs = gemm_impl(x, full, bias, gate, residual, act, rows_per_gate, false, false, false, dual,
+                        c10::nullopt, &spec);
+  if (!dual) outs.resize(1);
+  return outs;
 }
 
 }  // namespace vrl

@@ -99,6 +99,8 @@ torch::Tensor groupnorm_nhwc(torch::Tensor x, torch::Tensor weight, torch::Tenso
   TORCH_CHECK(c % 8 == 0 && c % groups == 0 && kGnThreads % (c / 8) == 0 && c / 8 <= kGnThreads,
               "groupnorm_nhwc: unsupported channel count ", c);
   TORCH_CHECK(n <= 65535 && weight.numel() == c && bias.numel() == c);
+  VRL_CHECK_OPERAND(weight, x);
+  VRL_CHECK_OPERAND(bias, x);
   const c10::cuda::CUDAGuard guard(x.device());
   auto w = weight.to(torch::kBFloat16).contiguous();
   auto b = bias.to(torch::kBFloat16).contiguous();

@@ -222,29 +222,9 @@ static CUtensorMap make_map(const void* base, CUtensorMapDataType type, uint64_t
   return map;
 }
 
-static int* status_word(int device) {
-  static std::map<int, int*> words;
-  static std::mutex mu;
-  std::lock_guard<std::mutex> lock(mu);
-  auto it = words.find(device);
-  if (it != words.end()) return it->second;
-  int* w = nullptr;
-  C10_CUDA_CHECK(cudaMalloc(&w, sizeof(int)));
-  C10_CUDA_CHECK(cudaMemset(w, 0, sizeof(int)));
-  words[device] = w;
-  return w;
-}
+static int* status_word(int device) { return kernel_status_block(device) + kStatusInt4Gemm; }
 
 }  // namespace i4
-
-int64_t int4_gemm_last_status() {
-  int device = 0;
-  C10_CUDA_CHECK(cudaGetDevice(&device));
-  int host = 0;
-  C10_CUDA_CHECK(cudaMemcpy(&host, i4::status_word(device), sizeof(int), cudaMemcpyDeviceToHost));
-  if (host != 0) C10_CUDA_CHECK(cudaMemset(i4::status_word(device), 0, sizeof(int)));
-  return host;
-}
 
 torch::Tensor int4_gemm(torch::Tensor x, torch::Tensor qweight, torch::Tensor scales,
                         c10::optional<torch::Tensor> bias, int64_t group) {
@@ -254,6 +234,9 @@ torch::Tensor int4_gemm(torch::Tensor x, torch::Tensor qweight, torch::Tensor sc
   TORCH_CHECK(scales.scalar_type() == torch::kBFloat16 && scales.is_contiguous());
   const int64_t m = x.size(0), k = x.size(1), n = qweight.size(0);
   TORCH_CHECK(m >= 1 && m <= 64, "int4_gemm: 1..64 activation rows");
+  VRL_CHECK_OPERAND(qweight, x);
+  VRL_CHECK_OPERAND(scales, x);
+  VRL_CHECK_OPERAND(bias, x);
   TORCH_CHECK(k % kBK == 0 && qweight.size(1) * 8 == k, "int4_gemm: K must be a multiple of 64");
   TORCH_CHECK(group % kBK == 0 && k % group == 0 && scales.numel() == n * (k / group),
               "int4_gemm: scales must be [N, K / group] with group a multiple of 64");

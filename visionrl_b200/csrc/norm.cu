@@ -291,6 +291,8 @@ adaln_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ shift,
 std::vector<torch::Tensor> adaln_fwd(torch::Tensor x, torch::Tensor shift, torch::Tensor scale,
                                      double eps) {
   TORCH_CHECK(x.is_cuda() && x.dim() == 3 && x.scalar_type() == torch::kBFloat16 && x.is_contiguous());
+  VRL_CHECK_OPERAND(shift, x);
+  VRL_CHECK_OPERAND(scale, x);
   const c10::cuda::CUDAGuard guard(x.device());
   const int b = (int)x.size(0), s = (int)x.size(1), d = (int)x.size(2);
   TORCH_CHECK(d % 8 == 0 && d <= 8 * kMaxVec * kNormThreads, "adaln: D must be a multiple of 8, <= 8192");
@@ -397,6 +399,12 @@ adaln_bwd_kernel(const bf16* __restrict__ gy, const bf16* __restrict__ x,
 
 std::vector<torch::Tensor> adaln_bwd(torch::Tensor gy, torch::Tensor x, torch::Tensor scale,
                                      torch::Tensor mean, torch::Tensor rstd) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 3 && x.scalar_type() == torch::kBFloat16 && x.is_contiguous());
+  VRL_CHECK_OPERAND(gy, x, c10::nullopt, x.numel());
+  VRL_CHECK_OPERAND(scale, x);
+  VRL_CHECK_OPERAND(mean, x, torch::kFloat32, x.size(0) * x.size(1));
+  VRL_CHECK_OPERAND(rstd, x, torch::kFloat32, x.size(0) * x.size(1));
+  TORCH_CHECK(mean.is_contiguous() && rstd.is_contiguous(), "adaln_bwd: row statistics must be contiguous");
   const c10::cuda::CUDAGuard guard(x.device());
   const int b = (int)x.size(0), s = (int)x.size(1), d = (int)x.size(2);
   gy = gy.to(torch::kBFloat16).contiguous();
@@ -461,7 +469,8 @@ rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16*
 }
 
 std::vector<torch::Tensor> rmsnorm_fwd(torch::Tensor x, torch::Tensor w, double eps) {
-  TORCH_CHECK(x.is_cuda() && x.scalar_type() == torch::kBFloat16 && x.is_contiguous());
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == torch::kBFloat16 && x.is_contiguous() && x.dim() >= 1);
+  VRL_CHECK_OPERAND(w, x, c10::nullopt, x.size(-1));
   const c10::cuda::CUDAGuard guard(x.device());
   const int d = (int)x.size(-1);
   const int64_t rows = x.numel() / d;
@@ -547,6 +556,11 @@ rmsnorm_bwd_kernel(const bf16* __restrict__ gy, const bf16* __restrict__ x,
 
 std::vector<torch::Tensor> rmsnorm_bwd(torch::Tensor gy, torch::Tensor x, torch::Tensor w,
                                        torch::Tensor rstd) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == torch::kBFloat16 && x.is_contiguous() && x.dim() >= 1);
+  VRL_CHECK_OPERAND(gy, x, c10::nullopt, x.numel());
+  VRL_CHECK_OPERAND(w, x, c10::nullopt, x.size(-1));
+  VRL_CHECK_OPERAND(rstd, x, torch::kFloat32, x.numel() / x.size(-1));
+  TORCH_CHECK(rstd.is_contiguous(), "rmsnorm_bwd: rstd must be contiguous");
   const c10::cuda::CUDAGuard guard(x.device());
   const int d = (int)x.size(-1);
   const int64_t rows = x.numel() / d;
@@ -655,6 +669,8 @@ torch::Tensor gate_residual_fwd(torch::Tensor y, torch::Tensor gate, torch::Tens
   TORCH_CHECK(y.is_cuda() && y.dim() == 3 && y.scalar_type() == torch::kBFloat16 && y.is_contiguous());
   TORCH_CHECK(residual.scalar_type() == torch::kBFloat16 && residual.is_contiguous() &&
               residual.sizes() == y.sizes());
+  VRL_CHECK_OPERAND(gate, y);
+  VRL_CHECK_OPERAND(residual, y);
   const c10::cuda::CUDAGuard guard(y.device());
   const int b = (int)y.size(0), s = (int)y.size(1), d = (int)y.size(2);
   TORCH_CHECK(d % 8 == 0);
@@ -673,6 +689,8 @@ torch::Tensor gate_residual_fwd(torch::Tensor y, torch::Tensor gate, torch::Tens
 
 std::vector<torch::Tensor> gate_residual_bwd(torch::Tensor g, torch::Tensor y, torch::Tensor gate) {
   TORCH_CHECK(y.is_cuda() && y.dim() == 3 && y.scalar_type() == torch::kBFloat16 && y.is_contiguous());
+  VRL_CHECK_OPERAND(g, y);
+  VRL_CHECK_OPERAND(gate, y);
   const c10::cuda::CUDAGuard guard(y.device());
   const int b = (int)y.size(0), s = (int)y.size(1), d = (int)y.size(2);
   g = g.to(torch::kBFloat16).contiguous();
@@ -805,6 +823,16 @@ std::vector<torch::Tensor> qkv_prepare_fwd(torch::Tensor qkv, c10::optional<torc
                                            c10::optional<torch::Tensor> dst_v, int64_t seq_offset) {
   TORCH_CHECK(qkv.is_cuda() && qkv.dim() == 3 && qkv.scalar_type() == torch::kBFloat16 &&
               qkv.is_contiguous());
+  TORCH_CHECK(qw.has_value() == kw.has_value() && cos.has_value() == sin.has_value() &&
+              dst_q.has_value() == dst_k.has_value() && dst_q.has_value() == dst_v.has_value(),
+              "qkv_prepare: q/k norm weights, cos/sin tables and destinations come in complete sets");
+  VRL_CHECK_OPERAND(qw, qkv);
+  VRL_CHECK_OPERAND(kw, qkv);
+  VRL_CHECK_OPERAND(cos, qkv);
+  VRL_CHECK_OPERAND(sin, qkv);
+  VRL_CHECK_OPERAND(dst_q, qkv);
+  VRL_CHECK_OPERAND(dst_k, qkv);
+  VRL_CHECK_OPERAND(dst_v, qkv);
   const c10::cuda::CUDAGuard guard(qkv.device());
   const int b = (int)qkv.size(0), s = (int)qkv.size(1);
   const int dmodel = (int)(qkv.size(2) / 3), dh = dmodel / (int)heads;
@@ -989,6 +1017,18 @@ std::vector<torch::Tensor> qkv_prepare_bwd(torch::Tensor gq, torch::Tensor gk, t
                                            c10::optional<torch::Tensor> cos,
                                            c10::optional<torch::Tensor> sin, torch::Tensor rstd,
                                            int64_t heads, int64_t seq_offset) {
+  TORCH_CHECK(qkv.is_cuda() && qkv.dim() == 3 && qkv.scalar_type() == torch::kBFloat16 &&
+              qkv.is_contiguous());
+  TORCH_CHECK(qw.has_value() == kw.has_value() && cos.has_value() == sin.has_value(),
+              "qkv_prepare_bwd: q/k norm weights and cos/sin tables come in pairs");
+  VRL_CHECK_OPERAND(gq, qkv);
+  VRL_CHECK_OPERAND(gk, qkv);
+  VRL_CHECK_OPERAND(gv, qkv);
+  VRL_CHECK_OPERAND(qw, qkv);
+  VRL_CHECK_OPERAND(kw, qkv);
+  VRL_CHECK_OPERAND(cos, qkv);
+  VRL_CHECK_OPERAND(sin, qkv);
+  VRL_CHECK_OPERAND(rstd, qkv, torch::kFloat32);
   const c10::cuda::CUDAGuard guard(qkv.device());
   const int b = (int)qkv.size(0), s = (int)qkv.size(1);
   const int dmodel = (int)(qkv.size(2) / 3), dh = dmodel / (int)heads;

@@ -8,6 +8,31 @@
 
 namespace vrl {
 
+// Operand checks shared by every host wrapper.  A wrapper hands raw pointers to its kernel, so EVERY
+// tensor operand (not only the first) must live on the launch device; a CPU tensor or one on another
+// GPU has to fail here as a Python error, never as an illegal address inside the kernel.
+inline void check_operand(const torch::Tensor& t, const torch::Tensor& ref, const char* name,
+                          c10::optional<c10::ScalarType> dtype = c10::nullopt, int64_t numel = -1) {
+  TORCH_CHECK(t.defined(), name, ": undefined tensor");
+  TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor (got ", t.device(), ")");
+  TORCH_CHECK(t.device() == ref.device(), name, " is on ", t.device(), " but the launch device is ",
+              ref.device());
+  if (dtype.has_value())
+    TORCH_CHECK(t.scalar_type() == *dtype, name, " must have dtype ", *dtype, " (got ", t.scalar_type(), ")");
+  if (numel >= 0) TORCH_CHECK(t.numel() == numel, name, " must have ", numel, " elements (got ", t.numel(), ")");
+}
+inline void check_operand(const c10::optional<torch::Tensor>& t, const torch::Tensor& ref, const char* name,
+                          c10::optional<c10::ScalarType> dtype = c10::nullopt, int64_t numel = -1) {
+  if (t.has_value()) check_operand(*t, ref, name, dtype, numel);
+}
+#define VRL_CHECK_OPERAND(t, ref, ...) ::vrl::check_operand((t), (ref), #t, ##__VA_ARGS__)
+
+// status.cpp: the per-device block of kernel status words (one 16-byte read polls them all)
+constexpr int kStatusWords = 4;
+enum StatusIndex : int { kStatusGemm = 0, kStatusAttention = 1, kStatusInt4Gemm = 2 };
+int* kernel_status_block(int device);
+std::vector<int64_t> kernel_status_all();      // {gemm, attention, int4 gemm}; clears what it read
+
 // elementwise.cu
 int sde_blocks_per_sample(int64_t n);
 void sde_step_launch(const float* v, const float* x, const float* a, const float* b,
@@ -69,6 +94,15 @@ void p2p_broadcast_versioned(torch::Tensor src, torch::Tensor dst_peers, int64_t
                              torch::Tensor flag_peers, int64_t flag_slot, int64_t world,
                              int64_t rank, int64_t version, bool include_self);
 torch::Tensor wait_flag(torch::Tensor flags, int64_t slot, int64_t expected, double timeout_s);
+void flag_signal(torch::Tensor flag_peers, torch::Tensor flags, int64_t slot, int64_t world, int64_t value);
+void flag_wait(torch::Tensor flags, int64_t slot0, int64_t count, int64_t expected, double timeout_s,
+               torch::Tensor status);
+void flag_barrier(torch::Tensor flag_peers, torch::Tensor flags, int64_t base, int64_t world, int64_t rank,
+                  int64_t epoch, double timeout_s, torch::Tensor status);
+void bucket_reduce_acc(torch::Tensor stage_peers, torch::Tensor table, torch::Tensor gshard, double scale,
+                       int64_t world, int64_t rank, int64_t max_segment);
+void p2p_gather_rows(torch::Tensor shard_peers, torch::Tensor full, int64_t shard_elems, int64_t world,
+                     int64_t rank);
 void ulysses_scatter(torch::Tensor src, torch::Tensor dst_peers, int64_t batch, int64_t heads,
                      int64_t s_loc, int64_t head_dim, int64_t world, int64_t rank, bool to_heads);
 
@@ -124,9 +158,12 @@ torch::Tensor gemm_bf16(torch::Tensor a, torch::Tensor b, c10::optional<torch::T
                         bool out_fp32);
 std::vector<torch::Tensor> gemm_bf16_dual(torch::Tensor a, torch::Tensor b,
                                           c10::optional<torch::Tensor> bias, int64_t act);
-torch::Tensor gemm_allgather(torch::Tensor x, torch::Tensor peer_ptrs, torch::Tensor full,
-                             torch::Tensor ready, c10::optional<torch::Tensor> bias, int64_t act,
-                             int64_t rank, int64_t world);
+std::vector<torch::Tensor> gemm_allgather(torch::Tensor x, torch::Tensor peer_ptrs, torch::Tensor full,
+                                          torch::Tensor ready, c10::optional<torch::Tensor> bias, int64_t act,
+                                          int64_t rank, int64_t world, c10::optional<torch::Tensor> gate,
+                                          c10::optional<torch::Tensor> residual, int64_t rows_per_gate,
+                                          bool dual);
+void gemm_bf16_out(torch::Tensor a, torch::Tensor b, torch::Tensor out, bool a_mn_major, bool b_mn_major);
 void gemm_bf16_acc(torch::Tensor a, torch::Tensor b, torch::Tensor acc, bool a_mn_major, bool b_mn_major);
 int64_t gemm_last_status();
 

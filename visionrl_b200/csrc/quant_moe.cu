@@ -211,6 +211,9 @@ torch::Tensor int4_gemv(torch::Tensor x, torch::Tensor qweight, torch::Tensor sc
   TORCH_CHECK(group > 0 && group % 8 == 0 && k % group == 0 && scales.numel() == n * (k / group),
               "int4_gemv: scales must be [N, K / group]");
   TORCH_CHECK(reinterpret_cast<uintptr_t>(x.data_ptr()) % 16 == 0);
+  VRL_CHECK_OPERAND(qweight, x);
+  VRL_CHECK_OPERAND(scales, x);
+  VRL_CHECK_OPERAND(bias, x);
   const c10::cuda::CUDAGuard guard(x.device());
   auto y = torch::empty({m, n}, x.options());
   if (m == 0 || n == 0) return y;
@@ -275,6 +278,7 @@ std::vector<torch::Tensor> moe_permute(torch::Tensor experts, int64_t num_expert
 torch::Tensor moe_gather_rows(torch::Tensor x, torch::Tensor perm, int64_t topk) {
   TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.scalar_type() == torch::kBFloat16 && x.is_contiguous());
   TORCH_CHECK(x.size(1) % 8 == 0 && perm.scalar_type() == torch::kInt32 && perm.is_contiguous());
+  VRL_CHECK_OPERAND(perm, x);
   const c10::cuda::CUDAGuard guard(x.device());
   auto xp = torch::empty({perm.numel(), x.size(1)}, x.options());
   if (perm.numel() == 0) return xp;
@@ -289,6 +293,9 @@ torch::Tensor moe_combine(torch::Tensor yp, torch::Tensor inv, torch::Tensor wei
   TORCH_CHECK(yp.is_cuda() && yp.dim() == 2 && yp.scalar_type() == torch::kBFloat16 && yp.is_contiguous());
   TORCH_CHECK(weights.dim() == 2 && weights.scalar_type() == torch::kFloat32 && weights.is_contiguous());
   TORCH_CHECK(inv.scalar_type() == torch::kInt32 && inv.numel() == weights.numel() && yp.size(1) % 8 == 0);
+  VRL_CHECK_OPERAND(inv, yp);
+  VRL_CHECK_OPERAND(weights, yp);
+  TORCH_CHECK(inv.is_contiguous(), "moe_combine: inverse permutation must be contiguous");
   const c10::cuda::CUDAGuard guard(yp.device());
   const int64_t tokens = weights.size(0), topk = weights.size(1);
   auto y = torch::empty({tokens, yp.size(1)}, yp.options());

@@ -47,8 +47,15 @@ extern "C" __attribute__((visibility("default"))) int vrl_sde_step_noalloc(
   if (batch <= 0 || n <= 0) return fail(1, err, err_len, "batch and n must be positive", nullptr);
   if (batch > 65535) return fail(1, err, err_len, "batch exceeds the grid limit of 65535", nullptr);
 
-  const int64_t need = (int64_t)batch * vrl::sde_blocks_per_sample(n);
-  if (need > VRL_SDE_NOALLOC_MAX_SCRATCH_FLOATS) {
+  // blocks per sample in 64-bit arithmetic BEFORE any narrowing: an absurd n must be rejected
+  // here (rc 2) instead of wrapping through `int` and reaching the launch
+  constexpr int64_t kElemsPerBlock = 4096;
+  const int64_t blocks_per_sample = n / kElemsPerBlock + (n % kElemsPerBlock != 0 ? 1 : 0);
+  const int64_t need = blocks_per_sample <= VRL_SDE_NOALLOC_MAX_SCRATCH_FLOATS
+                           ? (int64_t)batch * blocks_per_sample
+                           : (int64_t)VRL_SDE_NOALLOC_MAX_SCRATCH_FLOATS + 1;
+  if (need > VRL_SDE_NOALLOC_MAX_SCRATCH_FLOATS ||
+      blocks_per_sample != (int64_t)vrl::sde_blocks_per_sample(n)) {
     char detail[160];
     snprintf(detail, sizeof(detail), "batch * ceil(n / 4096) = %lld floats of scratch needed, %d available",
              (long long)need, VRL_SDE_NOALLOC_MAX_SCRATCH_FLOATS);
@@ -68,6 +75,12 @@ extern "C" __attribute__((visibility("default"))) int vrl_sde_step_noalloc(
     g_scratch_addr[device].store(scratch, std::memory_order_release);
   }
 
+  // An error left behind by unrelated earlier work would otherwise be reported (and cleared) as
+  // this call's launch failure: look without clearing, and name it for what it is.
+  rc = cudaPeekAtLastError();
+  if (rc != cudaSuccess)
+    return fail(5, err, err_len, "a CUDA error from earlier work is pending; nothing was launched",
+                cudaGetErrorString(rc));
   vrl::sde_step_launch(v, x, a, b, scale, dt, prev_in, noise, next_out, mean_out, logp, scratch, batch,
                        n, deterministic != 0, gaussian != 0, static_cast<cudaStream_t>(stream));
   rc = cudaGetLastError();

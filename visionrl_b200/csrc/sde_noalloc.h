@@ -29,8 +29,9 @@ extern "C" {
 // `prev_in` and `noise` may be null.  `stream` is a cudaStream_t (null = default stream).
 //
 // Returns 0 on success.  Non-zero: 1 bad argument, 2 the problem needs more scratch than
-// VRL_SDE_NOALLOC_MAX_SCRATCH_FLOATS, 3 a CUDA call failed during set-up, 4 a launch failed.  When
-// `err` is non-null a NUL-terminated description is written to it (at most `err_len` bytes).
+// VRL_SDE_NOALLOC_MAX_SCRATCH_FLOATS, 3 a CUDA call failed during set-up, 4 a launch failed, 5 an
+// error from earlier, unrelated CUDA work was already pending (nothing is launched and the pending
+// error is left in place for its owner to read).  When `err` is non-null a NUL-terminated description is written to it (at most `err_len` bytes).
 //
 // The function performs no device or host allocation.  The first call on each device looks up
 // the address of the module's scratch array (one cudaGetSymbolAddress call with that device

@@ -33,8 +33,13 @@ class Linear(nn.Module):
 
     # Int4 copy of ``weight`` used for decode-sized inputs while :func:`int4_decode` is active.
     int4_shadow = None
+    # Set by :mod:`visionrl_b200.parallel.fsdp` when ``weight`` holds only this rank's rows: the
+    # handle gathers the full matrix inside the consuming GEMM and stages the weight gradient.
+    sharded = None
 
     def _base(self, x, act=None, gate=None, residual=None):
+        if self.sharded is not None:
+            return self.sharded.linear(x, self.bias, act=act, gate=gate, residual=residual)
         shadow = self.int4_shadow
         if (shadow is not None and _INT4_DECODE_ACTIVE and not torch.is_grad_enabled()
                 and x.numel() // x.shape[-1] <= 32):
@@ -46,7 +51,25 @@ class Linear(nn.Module):
         return self._base(x, act=act, gate=gate, residual=residual)
 
     def extra_repr(self) -> str:
-        return f"in={self.in_features}, out={self.out_features}, bias={self.bias is not None}"
+        return (f"in={self.in_features}, out={self.out_features}, bias={self.bias is not None}"
+                + (", row-sharded" if self.sharded is not None else ""))
+
+    # A sharded layer still saves and loads the FULL ``[out, in]`` matrix, so checkpoints do not
+    # depend on how many ranks wrote them.
+    def _save_to_state_dict(self, destination, prefix, keep_vars):
+        super()._save_to_state_dict(destination, prefix, keep_vars)
+        if self.sharded is not None:
+            destination[prefix + "weight"] = self.sharded.gather_copy()
+
+    def _load_from_state_dict(self, state_dict, prefix, *args, **kwargs):
+        handle = self.sharded
+        if handle is not None:
+            key = prefix + "weight"
+            value = state_dict.get(key)
+            if value is not None and tuple(value.shape) == (handle.n, handle.k):
+                state_dict[key] = handle.local_rows(value)
+            handle.rt.mark_dirty()
+        super()._load_from_state_dict(state_dict, prefix, *args, **kwargs)
 
 
 class LoRALinear(Linear):
@@ -228,7 +251,14 @@ class MLP(nn.Module):
 
     def forward(self, x, gate=None, residual=None):
         plain = type(self.fc1) is Linear and type(self.fc2) is Linear
+        if plain and self.act == "gelu_tanh" and self.fc1.sharded is not None \
+                and self.fc2.sharded is not None and torch.is_grad_enabled():
+            from visionrl_b200.parallel.fsdp import sharded_gelu_mlp
+
+            y = sharded_gelu_mlp(x, self.fc1, self.fc2)
+            return linear_ops.linear_epilogue(y, None, gate, residual)
         if (plain and self.act == "gelu_tanh" and torch.is_grad_enabled()
+                and self.fc1.sharded is None and self.fc2.sharded is None
                 and self.fc1.int4_shadow is None and self.fc2.int4_shadow is None):
             y = linear_ops.gelu_mlp(x, self.fc1.weight, self.fc1.bias, self.fc2.weight, self.fc2.bias)
             return linear_ops.linear_epilogue(y, None, gate, residual)

@@ -12,7 +12,16 @@ flat array instead of one per tensor.  The update is decoupled-weight-decay Adam
 computed on the fp32 master weights and re-cast to the parameter dtype in the same
 pass.  ``state_dict()`` uses the ``torch.optim.AdamW`` layout (state keyed by
 parameter index with ``step`` / ``exp_avg`` / ``exp_avg_sq``) so checkpoints stay
-interchangeable (reference optimiser: ``vrl/trainers/online.py:33-56,322-341``).
+interchangeable (reference optimiser: ``vrl/trainers/online.py:33-56,322-341``); for
+low-precision parameters each entry additionally carries the fp32 ``master`` copy
+(a key ``torch.optim.AdamW`` ignores), so a resumed run continues from exactly the
+weights the interrupted run held rather than from their bf16 rounding.
+
+Parameters that a :class:`visionrl_b200.parallel.fsdp.ShardedParamRuntime` has sharded
+(marked ``_vrl_sharded``) are not flattened here — the runtime owns their shards,
+moments and update — but they keep their place in ``state_dict()``: their state is
+gathered to the full ``[N, K]`` shape on save and sliced on load, so a checkpoint
+does not depend on the number of ranks that wrote it.
 """
 
 from __future__ import annotations
@@ -67,7 +76,8 @@ class FusedAdamW(torch.optim.Optimizer):
     def _build(self) -> None:
         self._flat = []
         for group in self.param_groups:
-            params = [p for p in group["params"] if p.requires_grad]
+            params = [p for p in group["params"]
+                      if p.requires_grad and getattr(p, "_vrl_sharded", None) is None]
             by_key: dict[tuple, list] = {}
             for p in params:
                 by_key.setdefault((p.device, p.dtype), []).append(p)
@@ -196,11 +206,27 @@ class FusedAdamW(torch.optim.Optimizer):
         state: dict[int, dict[str, Any]] = {}
         for e in self._flat:
             full_m, full_v = self._full_moments(e)
+            full_w = self._full_master(e)
             for p, off, n in zip(e["params"], e["offsets"], e["sizes"]):
-                state[index[id(p)]] = {
+                entry = {
                     "step": torch.tensor(float(e["step"])),
                     "exp_avg": full_m[off:off + n].view(p.shape).clone(),
                     "exp_avg_sq": full_v[off:off + n].view(p.shape).clone(),
+                }
+                if full_w is not None:
+                    entry["master"] = full_w[off:off + n].view(p.shape).clone()
+                state[index[id(p)]] = entry
+        for group in self.param_groups:
+            for p in group["params"]:
+                handle = getattr(p, "_vrl_sharded", None)
+                if handle is None or not p.requires_grad:
+                    continue
+                rt = handle.rt
+                state[index[id(p)]] = {
+                    "step": torch.tensor(float(rt.step_count)),
+                    "exp_avg": rt.gather_state(handle, "exp_avg"),
+                    "exp_avg_sq": rt.gather_state(handle, "exp_avg_sq"),
+                    "master": rt.gather_state(handle, "master"),
                 }
         groups = []
         start = 0
@@ -241,7 +267,27 @@ class FusedAdamW(torch.optim.Optimizer):
                 self._load_slice(e, "exp_avg_sq", off, n, s["exp_avg_sq"].reshape(-1))
                 e["step"] = int(float(s["step"]))
             if e["param"].dtype != torch.float32:
+                # bf16 rounding of the parameters is the fallback; a saved fp32 master wins
                 e["master"].copy_(e["param"][e["lo"]:e["lo"] + e["shard"]])
+                for p, off, n in zip(e["params"], e["offsets"], e["sizes"]):
+                    s = saved.get(index[id(p)])
+                    if s is not None and "master" in s:
+                        self._load_slice(e, "master", off, n, s["master"].reshape(-1).float())
+        for group in self.param_groups:
+            for p in group["params"]:
+                handle = getattr(p, "_vrl_sharded", None)
+                s = saved.get(index.get(id(p), -1))
+                if handle is None or s is None:
+                    continue
+                rt = handle.rt
+                if tuple(s["exp_avg"].shape) != (handle.n, handle.k):
+                    raise ValueError("optimizer state shape does not match the sharded weight's "
+                                     f"full shape {(handle.n, handle.k)}")
+                rt.load_state(handle, "exp_avg", s["exp_avg"])
+                rt.load_state(handle, "exp_avg_sq", s["exp_avg_sq"])
+                if "master" in s:
+                    rt.load_state(handle, "master", s["master"])
+                rt.step_count = int(float(s["step"]))
 
     @staticmethod
     def _load_slice(e, key: str, off: int, n: int, src: torch.Tensor) -> None:
@@ -250,6 +296,18 @@ class FusedAdamW(torch.optim.Optimizer):
         a, b = max(off, lo), min(off + n, hi)
         if a < b:
             e[key][a - lo:b - lo].copy_(src[a - off:b - off])
+
+    def _full_master(self, e):
+        """Full-length fp32 master weights, or ``None`` when the parameters are fp32 themselves."""
+        if e["param"].dtype == torch.float32:
+            return None
+        if self._shard_world == 1:
+            return e["master"]
+        import torch.distributed as dist
+
+        parts = [torch.empty_like(e["master"]) for _ in range(self._shard_world)]
+        dist.all_gather(parts, e["master"].contiguous())
+        return torch.cat(parts)
 
     def _full_moments(self, e):
         """Full-length moments (all shards, gathered when the state is sharded)."""

@@ -1,8 +1,13 @@
-"""Process mesh ``(dp, sp)`` over ``torch.distributed``.
+"""Process mesh ``(dp, sp)`` × ``(replicate, shard)`` over ``torch.distributed``.
 
 Ranks are laid out ``rank = dp_rank * sp + sp_rank`` so a sequence-parallel group is
-a run of adjacent ranks (adjacent GPUs).  Parameters are sharded over the whole
-world when ``fsdp`` is on.  One process owns one GPU; with no initialised process
+a run of adjacent ranks (adjacent GPUs).  Independently of that, parameter sharding
+(``fsdp``) uses a second factorisation of the same ranks, ``rank = replica * shard +
+shard_rank``: parameters, gradients and optimiser state are sharded over a *shard group* of
+``world / replicate`` adjacent ranks and replicated across the ``replicate`` groups
+(hybrid sharding; ``replicate = 1`` shards over the whole world).  The reference describes
+the same ``(replicate, shard)`` device mesh for its FSDP wrapper
+(``vrl/trainers/fsdp.py:59-67``).  One process owns one GPU; with no initialised process
 group everything degenerates to a single rank.
 """
 
@@ -62,15 +67,23 @@ class ProcessMesh:
     fsdp: bool = True
     sp_group: Any = None
     dp_group: Any = None
+    replicate: int = 1
+    shard_group: Any = None          # None = the whole world
+    replicate_group: Any = None
 
     @classmethod
-    def build(cls, sp: int = 1, dp: int = -1, fsdp: bool = True) -> "ProcessMesh":
+    def build(cls, sp: int = 1, dp: int = -1, fsdp: bool = True, replicate: int = 1) -> "ProcessMesh":
         if not dist_ready():
             if sp not in (1, None):
                 raise ValueError(f"sp={sp} needs an initialised process group")
+            if replicate not in (1, None):
+                raise ValueError(f"replicate={replicate} needs an initialised process group")
             return cls(fsdp=fsdp)
         rank, world = dist.get_rank(), dist.get_world_size()
         sp = int(sp or 1)
+        replicate = int(replicate or 1)
+        if replicate < 1 or world % replicate != 0:
+            raise ValueError(f"world_size={world} is not divisible by replicate={replicate}")
         if world % sp != 0:
             raise ValueError(f"world_size={world} is not divisible by sp={sp}")
         if dp in (-1, None):
@@ -89,8 +102,22 @@ class ProcessMesh:
                 g = dist.new_group(ranks)
                 if rank in ranks:
                     dp_group = g
+        shard_group = replicate_group = None
+        if replicate > 1:
+            shard = world // replicate
+            for rep in range(replicate):
+                ranks = list(range(rep * shard, (rep + 1) * shard))
+                g = dist.new_group(ranks)
+                if rank in ranks:
+                    shard_group = g
+            for s in range(shard):
+                ranks = list(range(s, world, shard))
+                g = dist.new_group(ranks)
+                if rank in ranks:
+                    replicate_group = g
         mesh = cls(rank=rank, world_size=world, dp=dp, sp=sp, fsdp=fsdp, sp_group=sp_group,
-                   dp_group=dp_group)
+                   dp_group=dp_group, replicate=replicate, shard_group=shard_group,
+                   replicate_group=replicate_group)
         _CURRENT[0] = mesh
         return mesh
 
@@ -106,6 +133,18 @@ class ProcessMesh:
     @property
     def sp_rank(self) -> int:
         return self.rank % self.sp
+
+    @property
+    def shard_size(self) -> int:
+        return self.world_size // max(self.replicate, 1)
+
+    @property
+    def shard_rank(self) -> int:
+        return self.rank % self.shard_size
+
+    @property
+    def replica_rank(self) -> int:
+        return self.rank // self.shard_size
 
     @property
     def is_main(self) -> bool:

@@ -1,4 +1,8 @@
-"""Row-sharded linear weights whose all-gather is fused into the consuming GEMM (kernel F1).
+"""One row-sharded linear weight whose all-gather is fused into the consuming GEMM (kernel F1).
+
+This is the single-layer form, kept for micro-benchmarks and kernel tests; whole models are
+sharded by :mod:`visionrl_b200.parallel.fsdp`, which drives the same kernel from a shared ring of
+gather buffers.
 
 Every rank keeps ``N / world`` rows of a ``[N, K]`` weight in symmetric memory.  A forward call
 launches ONE kernel: 128 extra threads per CTA copy the peers' rows into the local full-weight
@@ -57,7 +61,7 @@ class ShardedLinearWeight:
         if fused:
             y = _ext.load().gemm_allgather(x2.contiguous(), self.pool.peer_pointers(self.shard.view(-1)),
                                            self.full, self.ready, self.bias, _ACTS[act], self.rank,
-                                           self.world)
+                                           self.world, None, None, 0, False)[0]
             self.kernel_launches += 1
         else:
             dist.all_gather_into_tensor(self.full.view(-1), self.shard.reshape(-1).contiguous(),

@@ -17,7 +17,7 @@ import torch.distributed as dist
 
 from visionrl_b200.parallel.symm import SymmetricPool
 
-VERSION_SLOT = 1
+VERSION_SLOT = 16      # slots [16, 32): one published policy version per owner rank
 
 
 class DeviceWeightBroadcaster:

@@ -84,7 +84,8 @@ def setup_run(cfg: Any) -> RunContext:
         device = torch.device("cpu")
     mesh = ProcessMesh.build(sp=int(cfg_path(cfg, "distributed.mesh.sp", 1) or 1),
                              dp=int(cfg_path(cfg, "distributed.mesh.dp", -1) or -1),
-                             fsdp=bool(cfg_path(cfg, "distributed.mesh.fsdp", True))) \
+                             fsdp=bool(cfg_path(cfg, "distributed.mesh.fsdp", True)),
+                             replicate=int(cfg_path(cfg, "distributed.mesh.replicate", 1) or 1)) \
         if native else ProcessMesh()
     # Sampling noise comes from the default generators: the ranks of one sequence-parallel group
     # must draw identical noise (they hold replicas of the same samples), data-parallel ranks
@@ -157,9 +158,21 @@ def build_online_trainer(ctx: RunContext, parts: RecipeParts, reward_fn: Any):
     if mesh.world_size > 1:
         from visionrl_b200.parallel.sharded import ShardedGradSync
 
-        grad_sync = ShardedGradSync(mesh, shard_optimizer=mesh.fsdp,
-                                    collectives=str(cfg_path(cfg, "distributed.collectives",
-                                                             "fused")))
+        collectives = str(cfg_path(cfg, "distributed.collectives", "fused"))
+        param_runtime = None
+        sharding = str(cfg_path(cfg, "distributed.param_sharding", "full"))
+        if mesh.fsdp and sharding == "full":
+            from visionrl_b200.parallel.fsdp import shard_model
+
+            # block weights, their gradients and optimiser state live 1/shard-group per rank
+            param_runtime = shard_model(policy, mesh, ctx.device, collectives=collectives,
+                                        ring=int(cfg_path(cfg, "distributed.gather_ring", 2) or 2))
+            if param_runtime is not None:
+                policy.param_runtime = param_runtime
+                logger.info("sharded %d block weights over %d ranks: %s", len(param_runtime.handles),
+                            param_runtime.world, param_runtime.memory_report())
+        grad_sync = ShardedGradSync(mesh, shard_optimizer=mesh.fsdp, collectives=collectives,
+                                    param_runtime=param_runtime)
     trainer = OnlineTrainer(
         algorithm=parts.algorithm, collector=collector, evaluator=parts.evaluator, model=policy,
         ref_model=parts.ref_model,

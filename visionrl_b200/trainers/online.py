@@ -547,11 +547,19 @@ class OnlineTrainer(Trainer):
 
         if not (_ext.kernels_enabled() and _ext.available()):
             return
-        status = int(_ext.load().gemm_last_status())
-        self.last_d2h_bytes += 4
-        if status != 0:
-            raise RuntimeError(f"a GEMM kernel gave up waiting on a barrier (status {status}: "
-                               "1 = TMA producer, 2 = MMA issuer, 3 = epilogue)")
+        # one 16-byte read covers the GEMM, the attention kernels and the int4 GEMM
+        words = [int(v) for v in _ext.load().kernel_status_all()]
+        self.last_d2h_bytes += 16
+        names = ("bf16 GEMM (1 = TMA producer, 2 = MMA issuer, 3 = epilogue)",
+                 "flash attention", "int4 GEMM")
+        bad = [f"{name}: status {word}" for name, word in zip(names, words) if word != 0]
+        if bad:
+            raise RuntimeError("a kernel gave up waiting on one of its barriers; this step's "
+                               "results are invalid (" + "; ".join(bad) + ")")
+        check = getattr(self.grad_sync, "check", None)
+        if callable(check):
+            check(f"training step {self.state.step}")
+            self.last_d2h_bytes += 16
 
     # -- state -------------------------------------------------------------------------------------
     def state_dict(self) -> dict:
