@@ -117,6 +117,8 @@ def run(args) -> None:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}; launch with torchrun")
     overrides = [
         f"distributed.collectives={'nccl' if baseline else args.collectives}",
+        f"distributed.param_sharding={args.sharding}",
+        f"distributed.rollout_replica={'true' if args.rollout_replica else 'false'}",
         "trainer.output_dir=/tmp/vrl_bench", f"rollout.rollout_batch_size={args.prompts}",
         f"rollout.n={args.group}", f"rollout.sample_batch_size={args.group}",
     ] + list(args.override)
@@ -139,9 +141,11 @@ def run(args) -> None:
     loop = asyncio.new_event_loop()
     for _ in range(args.warmup):
         loop.run_until_complete(one_step())
-    ext_status = _ext.load().gemm_last_status() if not baseline else 0
-    if ext_status:
-        raise RuntimeError(f"GEMM kernel status {ext_status} during warm-up")
+    ext_status = [int(v) for v in _ext.load().kernel_status_all()] if not baseline else []
+    if any(ext_status):
+        raise RuntimeError(f"kernel status words {ext_status} (gemm, attention, int4) during warm-up")
+    runtime = getattr(policy, "param_runtime", None)
+    sharded = runtime is not None and runtime.active
 
     def timed(clear_device_cache: bool):
         barrier()
@@ -188,7 +192,8 @@ def run(args) -> None:
             "impl": args.impl,
             "config": {
                 "model": MODEL, "global_batch": samples_per_step, "seq_len": 1024 + 154,
-                "parallelism": f"dp{args.gpus}+sharded-optimizer" if args.gpus > 1 else "single",
+                "parallelism": ("single" if args.gpus == 1 else f"fsdp{runtime.world}" if sharded
+                                else f"dp{args.gpus}+sharded-optimizer"),
                 "prompts": args.prompts, "group_size": args.group, "sde_steps": 10, "cfg": 4.5,
                 "train_timesteps": 9, "reward": "ViT-L/14 scalar head on VAE-decoded 512x512",
                 "l2_policy": "working set (4 GB weights + activations) exceeds the 126 MB L2",
@@ -200,6 +205,10 @@ def run(args) -> None:
                     "h2d_bytes_per_step": int(h2d // max(args.steps, 1)),
                     "d2h_bytes_per_step": int(d2h // max(args.steps, 1))},
             "gpu_launches": launches,
+            "sharding": ({**runtime.memory_report(), "fused_gathers": runtime.fused_gathers,
+                          "gathers": runtime.gathers, "buckets_reduced": runtime.buckets_reduced,
+                          "weight_broadcasts": runtime.broadcasts}
+                         if sharded else None),
             "last_metrics": {"loss": metrics.loss, "reward_mean": metrics.reward_mean,
                              "grad_norm": metrics.grad_norm},
         }
@@ -223,6 +232,12 @@ def main() -> None:
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", default="native", choices=["native", "torch_baseline", "reference"])
     parser.add_argument("--collectives", default="fused", choices=["fused", "nccl"])
+    parser.add_argument("--sharding", default="full", choices=["full", "optimizer_only"],
+                        help="full: block weights, gradients and optimiser state sharded over the "
+                             "ranks (FSDP); optimizer_only: replicated bf16 weights")
+    parser.add_argument("--no-rollout-replica", dest="rollout_replica", action="store_false",
+                        help="rollouts gather the sharded weights like training does instead of "
+                             "reading a full per-rank replica kept current by the P2P broadcast")
     parser.add_argument("--prompts", type=int, default=8)
     parser.add_argument("--group", type=int, default=8)
     parser.add_argument("--override", action="append", default=[],

@@ -217,7 +217,8 @@ def _mmdit_inputs(seed, dev, dtype, batch=2):
     return lat, t, ctx, pooled, target
 
 
-def fsdp_training_matches_replicated(rank, world, port, backend, collectives, replicate, checkpointing, out):
+def fsdp_training_matches_replicated(rank, world, port, backend, collectives, replicate, checkpointing, out,
+                                     replica=True):
     """Block weights sharded over the ranks (gather in the consuming GEMM, bucketed reduce-scatter
     during backward, sharded AdamW) train exactly like one replicated model on the mean gradient."""
     import copy
@@ -232,10 +233,10 @@ def fsdp_training_matches_replicated(rank, world, port, backend, collectives, re
     dev = torch.device("cuda", rank) if backend == "nccl" else torch.device("cpu")
     dtype = torch.bfloat16 if backend == "nccl" else torch.float32
     net = _tiny_mmdit(dev, dtype)
-    ref = copy.deepcopy(net).float()
+    ref = copy.deepcopy(net).float().cpu()
     net.enable_gradient_checkpointing(checkpointing)
     mesh = ProcessMesh.build(replicate=replicate)
-    rt = shard_model(net, mesh, dev, collectives=collectives, ring=2)
+    rt = shard_model(net, mesh, dev, collectives=collectives, ring=2, rollout_replica=replica)
     assert rt is not None and len(rt.handles) > 0
     sync = ShardedGradSync(mesh, collectives=collectives, param_runtime=rt)
     opt = FusedAdamW([p for p in net.parameters() if p.requires_grad], lr=1e-2, weight_decay=0.01)
@@ -271,6 +272,9 @@ def fsdp_training_matches_replicated(rank, world, port, backend, collectives, re
         got = net(lat, t, ctx, pooled).float().cpu()
         want = ref(*(_mmdit_inputs(77, torch.device("cpu"), torch.float32)[:4]))
         fwd_err = (got - want).abs().max().item()
+        gathers_before = rt.gathers
+        net(lat, t, ctx, pooled)
+        replica_used = rt.gathers == gathers_before       # a no-grad forward needs no gather
     full = net.state_dict()          # gathers every sharded weight to its full shape
     ref_state = ref.state_dict()
     err = max((full[k].float().cpu() - ref_state[k]).abs().max().item() for k in ref_state)
@@ -282,8 +286,154 @@ def fsdp_training_matches_replicated(rank, world, port, backend, collectives, re
     if rank == 0:
         out.put({"err": float(flags[0]), "fwd_err": float(flags[1]), "shapes_ok": shapes_ok,
                  "handles": len(rt.handles), "buckets": rt.buckets_reduced, "gathers": rt.gathers,
-                 "fused_gathers": rt.fused_gathers, "report": report,
+                 "fused_gathers": rt.fused_gathers, "report": report, "replica_used": replica_used,
+                 "broadcasts": rt.broadcasts,
                  "opt_entries": len(opt_state["state"]),
                  "params": sum(1 for _ in net.parameters())})
     dist.barrier()
+    dist.destroy_process_group()
+
+
+# ---------------------------------------------------------------------------------------------
+# Failure detection: every fault below is made on the host (an exception, a silent thread, a
+# process that leaves between steps); no device is involved.
+# ---------------------------------------------------------------------------------------------
+def _fake_trainer(rank, world, fail_on_step=None, liveness=None):
+    from tests.trainers.test_online import _FakeAlgorithm, _FakeCollector, _FakeEvaluator
+    from visionrl_b200.trainers.online import OnlineTrainer
+    from visionrl_b200.trainers.types import TrainerConfig
+
+    class _FailingCollector(_FakeCollector):
+        step = 0
+
+        async def collect(self, prompts, group_size, **kwargs):
+            if fail_on_step is not None and self.step == fail_on_step:
+                raise RuntimeError("injected collector failure")
+            self.step += 1
+            return await super().collect(prompts, group_size, **kwargs)
+
+    torch.manual_seed(0)
+    cfg = TrainerConfig(n=2, rollout_batch_size=2, bf16=False)
+    return OnlineTrainer(_FakeAlgorithm(), _FailingCollector([]), _FakeEvaluator(), torch.nn.Linear(1, 1),
+                         config=cfg, prompts=["a", "b"], device="cpu", liveness=liveness)
+
+
+def rank_raises_between_steps(rank, world, port, out):
+    """Rank 1's second step raises; rank 0 learns of it from the store before its next step."""
+    import asyncio
+    import time
+
+    from visionrl_b200.parallel.liveness import RankFailure, RankLiveness, default_store
+
+    _init(rank, world, port, "gloo")
+    live = RankLiveness(default_store(), rank, world, interval_s=0.1, deadline_s=5.0).start()
+    trainer = _fake_trainer(rank, world, fail_on_step=1 if rank == 1 else None, liveness=live)
+    loop = asyncio.new_event_loop()
+    loop.run_until_complete(trainer.step())
+    dist.barrier()                      # both ranks finished step 0; nothing is in flight
+    result = {}
+    if rank == 1:
+        try:
+            loop.run_until_complete(trainer.step())
+            result["raised"] = False
+        except RuntimeError as exc:
+            result["raised"] = "injected" in str(exc)
+    else:
+        t0 = time.time()
+        caught = None
+        while time.time() - t0 < 4.0:
+            try:
+                loop.run_until_complete(trainer.step())
+            except RankFailure as exc:
+                caught = exc
+                break
+            time.sleep(0.05)
+        result = {"detected": caught is not None, "failed_rank": getattr(caught, "rank", None),
+                  "reason": getattr(caught, "reason", ""), "seconds": time.time() - t0}
+        out.put(result)
+    live.stop()
+    # no barrier: the failed rank leaves; the survivor must not wait for it
+
+
+def heartbeat_withheld(rank, world, port, out):
+    """Rank 1 stays alive but its heartbeat thread stops; rank 0 notices after the deadline."""
+    import time
+
+    from visionrl_b200.parallel.liveness import RankFailure, RankLiveness, default_store
+
+    _init(rank, world, port, "gloo")
+    live = RankLiveness(default_store(), rank, world, interval_s=0.1, deadline_s=0.8).start()
+    dist.barrier()
+    if rank == 1:
+        live.stop()                    # the process lives on, silent
+        time.sleep(2.5)
+    else:
+        live.check()                   # fresh heartbeats: no complaint
+        t0 = time.time()
+        caught = None
+        while time.time() - t0 < 2.3:
+            try:
+                live.check()
+            except RankFailure as exc:
+                caught = exc
+                break
+            time.sleep(0.05)
+        out.put({"detected": caught is not None, "failed_rank": getattr(caught, "rank", None),
+                 "reason": getattr(caught, "reason", ""), "seconds": time.time() - t0})
+        live.stop()
+
+
+def rank_leaves_between_steps(rank, world, port, out):
+    """A rank exits between steps; the survivor's next collective fails within the (short)
+    process-group timeout instead of blocking."""
+    import datetime
+    import time
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank),
+                      WORLD_SIZE=str(world), LOCAL_RANK=str(rank))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=3))
+    t = torch.ones(4)
+    dist.all_reduce(t)                  # step 0 completes on both ranks
+    dist.barrier()
+    if rank == 1:
+        return                          # leaves with nothing in flight
+    time.sleep(0.5)
+    t0 = time.time()
+    failed = False
+    try:
+        dist.all_reduce(torch.ones(4))
+    except Exception:  # noqa: BLE001 - gloo reports a closed connection or a timeout
+        failed = True
+    out.put({"failed": failed, "seconds": time.time() - t0})
+
+
+def barrier_times_out_when_a_rank_skips(rank, world, port, out):
+    """GPU, host-side injection: rank 1 never enters the second barrier; rank 0's bounded wait
+    gives up, the stream keeps running, and the host raises CollectiveTimeout."""
+    import time
+
+    from visionrl_b200.parallel.mesh import ProcessMesh
+    from visionrl_b200.parallel.symm import CollectiveTimeout, SymmetricPool
+
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    _init(rank, world, port, "nccl")
+    mesh = ProcessMesh.build()
+    pool = SymmetricPool(mesh, timeout_s=5.0)
+    pool.barrier()
+    pool.check("first barrier")          # everybody arrives: fine
+    result = {}
+    if rank == 0:
+        t0 = time.time()
+        pool.barrier(timeout_s=0.5)      # rank 1 does not call this one
+        probe = torch.ones(8, device="cuda") * 3      # the stream is still usable afterwards
+        try:
+            pool.check("skipped barrier")
+            result["timed_out"] = False
+        except CollectiveTimeout as exc:
+            result["timed_out"] = True
+            result["message"] = str(exc)
+        result["seconds"] = time.time() - t0
+        result["stream_ok"] = float(probe.sum().item()) == 24.0
+        out.put(result)
+    dist.barrier()                       # both ranks leave together, nothing in flight
     dist.destroy_process_group()

@@ -51,6 +51,9 @@ def test_fsdp_gloo_world2_matches_replicated(checkpointing):
     assert res["opt_entries"] == res["params"]
     rep = res["report"]
     assert rep["param_shard_bytes"] * 2 == rep["full_param_bytes"]
+    # the rollout replica is republished after every optimiser step and serves no-grad forwards
+    assert res["replica_used"] and res["broadcasts"] == 3
+    assert rep["rollout_replica_bytes"] == rep["full_param_bytes"]
 
 
 def test_hsdp_gloo_world4_matches_replicated():

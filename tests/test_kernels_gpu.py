@@ -806,3 +806,60 @@ def test_weight_gradients_accumulate_in_place_across_backward_calls():
     for p, ptr, r in zip(params, buffers, ref):
         assert p.grad.data_ptr() == ptr                      # still the same buffer
         assert _rel(p.grad, r) < 4e-2
+
+
+@pytest.mark.gpu
+def test_flag_signal_wait_and_bounded_expiry_single_device():
+    """Flag kernels on one device: a signalled slot satisfies the wait; a slot nobody sets makes
+    the wait give up after its limit and report, leaving the stream usable."""
+    import time
+
+    from visionrl_b200.ops import _ext
+
+    ext = _ext.load()
+    flags = torch.zeros(64, dtype=torch.int32, device="cuda")
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    peers = torch.tensor([flags.data_ptr()], dtype=torch.int64)       # a group of one: this device
+    ext.flag_signal(peers, flags, 9, 1, 5)
+    ext.flag_wait(flags, 9, 1, 5, 1.0, status)
+    torch.cuda.synchronize()
+    assert int(flags[9]) == 5 and status.tolist() == [0, 0, 0, 0]
+    t0 = time.time()
+    ext.flag_wait(flags, 20, 2, 3, 0.3, status)                        # slots 20, 21 stay at zero
+    after = torch.ones(4, device="cuda").sum()
+    torch.cuda.synchronize()
+    assert 0.25 < time.time() - t0 < 3.0
+    code, slot, seen, expected = status.tolist()
+    assert code == 1 and slot in (20, 21) and seen == 0 and expected == 3
+    assert float(after) == 4.0
+    # barrier of a one-rank group returns at once
+    status.zero_()
+    ext.flag_barrier(peers, flags, 0, 1, 0, 1, 1.0, status)
+    torch.cuda.synchronize()
+    assert status.tolist() == [0, 0, 0, 0] and int(flags[0]) == 1
+
+
+@pytest.mark.gpu
+def test_wrappers_refuse_cpu_operands():
+    """Every tensor operand is checked, not only the first: a CPU tensor is a Python error."""
+    from visionrl_b200.ops import _ext
+
+    ext = _ext.load()
+    n = 1024
+    p = torch.zeros(n, device="cuda", dtype=torch.bfloat16)
+    g = torch.zeros(n, device="cuda", dtype=torch.bfloat16)
+    master = torch.zeros(n, device="cuda")
+    m_cpu = torch.zeros(n)
+    v = torch.zeros(n, device="cuda")
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        ext.adamw_flat(p, g, master, m_cpu, v, 1e-3, 0.9, 0.999, 1e-8, 0.0, 1, None)
+    r = torch.zeros(8, device="cuda")
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        ext.group_advantages(r, torch.zeros(8, dtype=torch.int64), 1e-6, 5.0, False)
+    x = torch.zeros(2, 64, device="cuda")
+    ab = torch.ones(2, device="cuda")
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        ext.sde_step_fwd(x, x.clone(), ab, ab, torch.ones(2), ab, None, x.clone(), False, True)
+    lp = torch.zeros(2, 8, device="cuda")
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        ext.token_loss_fwd(lp, torch.zeros(2, 8), torch.zeros(2, device="cuda"), None, None, 0.2, True)

@@ -54,6 +54,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("flag_barrier", &vrl::flag_barrier);
   m.def("bucket_reduce_acc", &vrl::bucket_reduce_acc);
   m.def("p2p_gather_rows", &vrl::p2p_gather_rows);
+  m.def("p2p_broadcast_table", &vrl::p2p_broadcast_table);
   m.def("token_logprob_fwd", &vrl::token_logprob_fwd);
   m.def("token_logprob_bwd", &vrl::token_logprob_bwd);
   m.def("lse_chunk_update", &vrl::lse_chunk_update);

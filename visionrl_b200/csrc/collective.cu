@@ -246,6 +246,42 @@ void p2p_broadcast_versioned(torch::Tensor src, torch::Tensor dst_peers, int64_t
   C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
 
+// Table-driven form of the broadcast: segment j copies `count` 16-bit elements from
+// src_flat + src_off to offset dst_off of EVERY rank's destination buffer.  One launch publishes
+// all of a rank's parameter shards into the rollout replicas of the whole group.
+__global__ void __launch_bounds__(256)
+p2p_broadcast_table_kernel(const uint4* __restrict__ src, PeerPtrs dst, const int64_t* __restrict__ table,
+                           int world, int rank) {
+  const int64_t src_vec = table[blockIdx.y * 3 + 0] / 8, dst_vec = table[blockIdx.y * 3 + 1] / 8;
+  const int64_t nvec = table[blockIdx.y * 3 + 2] / 8;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const uint4 val = src[src_vec + i];
+    for (int r = 0; r < world; ++r) {
+      const int d = (rank + r) % world;          // own copy first, then round the ring
+      reinterpret_cast<uint4*>(dst.p[d])[dst_vec + i] = val;
+    }
+  }
+}
+
+void p2p_broadcast_table(torch::Tensor src_flat, torch::Tensor dst_peers, torch::Tensor table,
+                         int64_t world, int64_t rank, int64_t max_segment) {
+  TORCH_CHECK(src_flat.is_cuda() && src_flat.is_contiguous() && src_flat.element_size() == 2 &&
+              reinterpret_cast<uintptr_t>(src_flat.data_ptr()) % 16 == 0,
+              "p2p_broadcast_table: contiguous 16-bit source, 16-byte aligned");
+  VRL_CHECK_OPERAND(table, src_flat, torch::kInt64);
+  TORCH_CHECK(table.dim() == 2 && table.size(1) == 3 && table.is_contiguous() && table.size(0) >= 1 &&
+              table.size(0) <= 65535, "p2p_broadcast_table: segment table [segments, 3] (src, dst, count), "
+              "all multiples of 8 elements");
+  TORCH_CHECK(world >= 1 && world <= kMaxPeers && rank >= 0 && rank < world && max_segment > 0);
+  const c10::cuda::CUDAGuard guard(src_flat.device());
+  const PeerPtrs dp = load_peers(dst_peers, (int)world);
+  const int bx = (int)std::max<int64_t>(1, std::min<int64_t>((max_segment / 8 + 255) / 256, 32));
+  p2p_broadcast_table_kernel<<<dim3(bx, (unsigned)table.size(0)), 256, 0, at::cuda::getCurrentCUDAStream()>>>(
+      reinterpret_cast<const uint4*>(src_flat.data_ptr()), dp, table.data_ptr<int64_t>(), (int)world, (int)rank);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
 // Bounded wait: status[0] = 0 when flag >= expected was observed, 1 when the limit ran out.
 __global__ void wait_flag_kernel(const int* __restrict__ flag, int expected, int* __restrict__ status,
                                  long long max_spins) {

@@ -101,6 +101,8 @@ void flag_barrier(torch::Tensor flag_peers, torch::Tensor flags, int64_t base, i
                   int64_t epoch, double timeout_s, torch::Tensor status);
 void bucket_reduce_acc(torch::Tensor stage_peers, torch::Tensor table, torch::Tensor gshard, double scale,
                        int64_t world, int64_t rank, int64_t max_segment);
+void p2p_broadcast_table(torch::Tensor src_flat, torch::Tensor dst_peers, torch::Tensor table,
+                         int64_t world, int64_t rank, int64_t max_segment);
 void p2p_gather_rows(torch::Tensor shard_peers, torch::Tensor full, int64_t shard_elems, int64_t world,
                      int64_t rank);
 void ulysses_scatter(torch::Tensor src, torch::Tensor dst_peers, int64_t batch, int64_t heads,

@@ -18,14 +18,14 @@ import dataclasses
 from typing import Any
 
 from visionrl_b200.distributed.ray.module_loading import import_from_path
+from visionrl_b200.distributed.ray.rollout.planner import request_chunks
 from visionrl_b200.distributed.ray.rollout.worker import build_executor_from_spec
+from visionrl_b200.engine.core.runtime import stamp_policy_version
 from visionrl_b200.engine.core.runtime_spec import GenerationRuntimeSpec
 from visionrl_b200.engine.core.types import GenerationRequest, OutputBatch
 from visionrl_b200.engine.core.worker import GenerationIdFactory
 from visionrl_b200.engine.gather import gather_pipeline_chunks, require_chunk_gatherer, require_chunked_executor
-from visionrl_b200.engine.microbatching import (
-    plan_prompt_group_microbatches, run_microbatches_with_oom_retry,
-)
+from visionrl_b200.engine.microbatching import BisectingRunner
 from visionrl_b200.parallel.mesh import ProcessMesh
 from visionrl_b200.rollouts.runtime.config import RolloutBackendConfig
 
@@ -43,55 +43,34 @@ class NativeRolloutRuntime:
         self.weight_sync = object() if sync_enabled else None
         self.requires_driver_model_offload = False
         self.last_local_chunks = 0
+        self.last_bisections = 0
         # False: the caller already handed this rank only its own prompts
         self.split_chunks = True
 
     def local_chunks(self, request: GenerationRequest):
-        cap = int(request.sampling.get("sample_batch_size", request.samples_per_prompt))
-        plan = plan_prompt_group_microbatches(request.prompts, request.samples_per_prompt,
-                                              max(1, cap))
+        """This rank's share of the request's chunk list (every rank derives the same list)."""
+        plan = request_chunks(request)
         if not self.split_chunks or self.mesh.dp <= 1:
             return list(plan.micro_batches)
-        return [c for i, c in enumerate(plan.micro_batches)
-                if i % self.mesh.dp == self.mesh.dp_rank]
+        return list(plan.for_rank(self.mesh.dp_rank, self.mesh.dp))
 
     async def generate(self, request: GenerationRequest) -> OutputBatch:
-        want = request.policy_version
-        if want is None and self.current_policy_version is not None:
-            request = dataclasses.replace(request, policy_version=self.current_policy_version)
-        elif want is not None and self.current_policy_version is not None \
-                and want != self.current_policy_version:
-            raise RuntimeError(f"policy_version mismatch: expected={want}, "
-                               f"actual={self.current_policy_version}")
+        request = stamp_policy_version(request, self.current_policy_version)
         chunks = self.local_chunks(request)
         self.last_local_chunks = len(chunks)
         if not chunks:
             raise RuntimeError(
                 f"rank {self.mesh.rank} received no rollout chunks: the request has fewer "
                 f"micro-batches than data-parallel ranks ({self.mesh.dp})")
-        results = run_microbatches_with_oom_retry(
-            chunks, lambda c: self.executor.forward_chunk(request, c))
-        # after OOM bisection a planned chunk may have become several; recover their ranges
-        ranges = self._result_ranges(chunks, results)
-        all_specs = self.id_factory.build_sample_specs(request)
-        by_key = {(s.prompt_index, s.sample_index): s for s in all_specs}
-        specs = [by_key[(p, j)] for p, start, count in ranges for j in range(start, start + count)]
+        runner = BisectingRunner(lambda c: self.executor.forward_chunk(request, c))
+        results = runner.run(chunks)
+        self.last_bisections = runner.bisections
+        # the runner knows which samples every result holds, also after a chunk was bisected
+        spec_of = {(s.prompt_index, s.sample_index): s
+                   for s in self.id_factory.build_sample_specs(request)}
+        specs = [spec_of[(c.prompt_index, j)] for c in runner.executed
+                 for j in range(c.sample_start, c.sample_end)]
         return gather_pipeline_chunks(self.gatherer, request, specs, results)
-
-    @staticmethod
-    def _result_ranges(chunks, results):
-        if len(results) == len(chunks):
-            return [(c.prompt_index, c.sample_start, c.sample_count) for c in chunks]
-        out = []
-        it = iter(results)
-        for c in chunks:
-            covered = 0
-            while covered < c.sample_count:
-                r = next(it)
-                n = int(getattr(r, "sample_count", 0) or r.log_probs.shape[0])
-                out.append((c.prompt_index, c.sample_start + covered, n))
-                covered += n
-        return out
 
     async def update_weights(self, state_ref: Any, policy_version: int) -> None:
         """Bring the rollout copy to ``policy_version``.

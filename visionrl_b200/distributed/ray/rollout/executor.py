@@ -1,23 +1,41 @@
-"""Runs one request across rollout workers and gathers the chunks
-(reference: ``vrl/distributed/ray/rollout/executor.py:18-141``).
+"""One request over a pool of rollout workers.
 
-Worker methods are called directly unless they expose ``.remote`` (a Ray actor
-method); remote jobs respect a per-worker in-flight cap.  Results are restored to
-plan order, then checked for errors, stale policy versions and missing outputs.
+Each assignment of the planner becomes one job.  A worker whose ``execute_chunk`` is a plain
+method (workers living in this process: tests, the in-process facade) is called directly; one that
+exposes ``.remote`` (a Ray actor method) is awaited on a helper thread, with a per-worker
+semaphore keeping at most ``max_inflight_chunks_per_worker`` of its chunks in flight.  Jobs are
+independent coroutines collected with ``asyncio.gather``, so results come back in plan order by
+construction.  Before gathering, every result is vetted: a chunk that reported an error, ran with
+another policy version than the request names, or carries no output ends the request with a
+``RuntimeError`` that says which worker and which chunk.  Behavioural reference:
+``vrl/distributed/ray/rollout/executor.py:18-141``.
 """
 
 from __future__ import annotations
 
 import asyncio
-from collections import deque
 from typing import Any
 
 from visionrl_b200.distributed.ray.dependencies import require_ray
-from visionrl_b200.distributed.ray.rollout.planner import DistributedExecutionPlanner
+from visionrl_b200.distributed.ray.rollout.planner import DeviceAssignment, DistributedExecutionPlanner
 from visionrl_b200.distributed.ray.rollout.types import RayChunkResult, RayWorkerHandle
 from visionrl_b200.engine.core.types import GenerationRequest, OutputBatch
 from visionrl_b200.engine.core.worker import GenerationIdFactory
 from visionrl_b200.engine.gather import ChunkGatherer, gather_pipeline_chunks
+
+
+def vet_chunk_result(result: RayChunkResult, request: GenerationRequest) -> Any:
+    """The chunk's output, or a ``RuntimeError`` describing why it cannot be used."""
+    where = f"worker_id={result.worker_id}"
+    if result.error:
+        raise RuntimeError(f"distributed rollout chunk failed ({where}, chunk={result.chunk}): "
+                           f"{result.error}")
+    if request.policy_version is not None and result.policy_version != request.policy_version:
+        raise RuntimeError(f"distributed rollout policy_version mismatch ({where}, "
+                           f"expected={request.policy_version}, actual={result.policy_version})")
+    if result.output is None:
+        raise RuntimeError(f"distributed rollout chunk returned no output: {result}")
+    return result.output
 
 
 class DistributedRolloutExecutor:
@@ -32,66 +50,31 @@ class DistributedRolloutExecutor:
         self.id_factory = id_factory or GenerationIdFactory()
         self.max_inflight_chunks_per_worker = int(max_inflight_chunks_per_worker)
 
-    async def execute(self, request: GenerationRequest) -> OutputBatch:
-        assignments = self.planner.plan(request, self.workers)
-        by_id = {w.worker_id: w for w in self.workers}
-        done: dict[int, RayChunkResult] = {}
-        remote_jobs = []
-        for idx, a in enumerate(assignments):
-            worker = by_id[a.worker_id]
-            if worker.actor is None:
-                raise RuntimeError(f"worker {worker.worker_id!r} has no actor")
-            fn = worker.actor.execute_chunk
-            remote = getattr(fn, "remote", None)
-            if callable(remote):
-                remote_jobs.append((idx, remote, worker, a.chunk))
-            else:
-                done[idx] = fn(request, a.chunk)
-        if remote_jobs:
-            done.update(await self._run_remote(request, remote_jobs))
-        if len(done) != len(assignments):
-            raise RuntimeError("distributed rollout returned wrong number of chunks: "
-                               f"{len(done)} != {len(assignments)}")
-        outputs = []
-        for idx in range(len(assignments)):
-            r = done[idx]
-            if r.error:
-                raise RuntimeError(f"distributed rollout chunk failed (worker_id={r.worker_id}, "
-                                   f"chunk={r.chunk}): {r.error}")
-            if request.policy_version is not None and r.policy_version != request.policy_version:
-                raise RuntimeError(
-                    f"distributed rollout policy_version mismatch (worker_id={r.worker_id}, "
-                    f"expected={request.policy_version}, actual={r.policy_version})")
-            if r.output is None:
-                raise RuntimeError(f"distributed rollout chunk returned no output: {r}")
-            outputs.append(r.output)
-        specs = self.id_factory.build_sample_specs(request)
-        return gather_pipeline_chunks(self.gatherer, request, specs, outputs)
-
-    async def _run_remote(self, request, jobs) -> dict[int, RayChunkResult]:
+    async def _run_job(self, request: GenerationRequest, job: DeviceAssignment,
+                       worker: RayWorkerHandle, gate: asyncio.Semaphore) -> RayChunkResult:
+        if worker.actor is None:
+            raise RuntimeError(f"worker {worker.worker_id!r} has no actor")
+        call = worker.actor.execute_chunk
+        remote = getattr(call, "remote", None)
+        if not callable(remote):
+            return call(request, job.chunk)
         ray = require_ray()
-        pending = deque(jobs)
-        inflight = {w.worker_id: 0 for _, _, w, _ in jobs}
-        refs: dict[Any, tuple[int, str]] = {}
-        out: dict[int, RayChunkResult] = {}
+        async with gate:
+            return await asyncio.to_thread(ray.get, remote(request, job.chunk))
 
-        def submit() -> None:
-            for _ in range(len(pending)):
-                idx, remote, worker, chunk = pending.popleft()
-                if inflight[worker.worker_id] >= self.max_inflight_chunks_per_worker:
-                    pending.append((idx, remote, worker, chunk))
-                    continue
-                refs[remote(request, chunk)] = (idx, worker.worker_id)
-                inflight[worker.worker_id] += 1
-
-        submit()
-        while refs:
-            ready, _ = await asyncio.to_thread(ray.wait, list(refs), num_returns=1)
-            idx, wid = refs.pop(ready[0])
-            inflight[wid] -= 1
-            out[idx] = await asyncio.to_thread(ray.get, ready[0])
-            submit()
-        return out
+    async def execute(self, request: GenerationRequest) -> OutputBatch:
+        jobs = self.planner.plan(request, self.workers)
+        workers = {w.worker_id: w for w in self.workers}
+        gates = {wid: asyncio.Semaphore(self.max_inflight_chunks_per_worker) for wid in workers}
+        results = await asyncio.gather(*(
+            self._run_job(request, job, workers[job.worker_id], gates[job.worker_id])
+            for job in jobs))
+        if len(results) != len(jobs):
+            raise RuntimeError("distributed rollout returned wrong number of chunks: "
+                               f"{len(results)} != {len(jobs)}")
+        outputs = [vet_chunk_result(r, request) for r in results]
+        return gather_pipeline_chunks(self.gatherer, request,
+                                      self.id_factory.build_sample_specs(request), outputs)
 
 
-__all__ = ["DistributedRolloutExecutor"]
+__all__ = ["DistributedRolloutExecutor", "vet_chunk_result"]

@@ -24,6 +24,15 @@ How the collectives are fused with compute (``collectives="fused"``, bf16 on CUD
   all-reduce and the sharded AdamW remain after the backward pass.  All waits on peers are
   bounded and report through :meth:`SymmetricPool.check`.
 
+* **trainer → rollout weight broadcast** (``rollout_replica=True``) — rollouts read a full bf16
+  copy of the block weights that every rank keeps in symmetric memory, so the thousands of
+  no-grad forwards of a rollout cost no NVLink traffic at all.  After each optimiser step ONE
+  kernel per rank stores that rank's freshly updated shards into every rank's replica over
+  NVLink and then publishes the new policy version with a release flag; the next rollout waits
+  (bounded) until every owner's version has arrived.  This replaces the reference's
+  ``state_dict()`` → CPU → object store → ``load_state_dict`` round trip
+  (``vrl/trainers/weight_sync.py:55-60``, ``vrl/distributed/ray/rollout/weight_sync.py:29-48``).
+
 ``collectives="nccl"`` performs the same steps with ``all_gather_into_tensor`` /
 ``reduce_scatter_tensor`` and is the measured baseline; on CPU (gloo) an all-reduce based variant
 keeps the semantics for tests.  A ``replicate`` dimension (HSDP) shards inside groups of adjacent
@@ -92,6 +101,10 @@ class ShardedWeight:
     def _stage_view(self) -> torch.Tensor:
         buf = self.rt.stage_ring[self.unit % 2]
         return buf[self.unit_off:self.unit_off + self.n * self.k].view(self.n, self.k)
+
+    def replica_view(self) -> torch.Tensor:
+        off = self.rt.replica_off[self.name]
+        return self.rt.replica_flat[off:off + self.n * self.k].view(self.n, self.k)
 
     def peer_pointers(self) -> torch.Tensor:
         if self._peers is None:
@@ -211,6 +224,9 @@ class ShardedWeight:
             x.requires_grad or self.param.requires_grad or (bias is not None and bias.requires_grad)
             or (gate is not None and gate.requires_grad)
             or (residual is not None and residual.requires_grad))
+        if not needs_grad and rt.replica_ready():
+            # rollout path: the rank's full replica, no gather
+            return linear_ops.linear(x, self.replica_view(), bias, act=act, gate=gate, residual=residual)
         usable = linear_ops._use_kernel(x, self.shard)
         if not usable:
             # generic path (CPU, fp32, kernels off): gather, then the ordinary differentiable op
@@ -340,7 +356,7 @@ class ShardedParamRuntime:
 
     def __init__(self, mesh: Any, device: torch.device, collectives: str = "fused",
                  dtype: torch.dtype = torch.bfloat16, ring: int = 2, grad_scale: float | None = None,
-                 pool: Any | None = None) -> None:
+                 pool: Any | None = None, rollout_replica: bool = False) -> None:
         self.mesh = mesh
         self.device = torch.device(device)
         self.dtype = dtype
@@ -383,6 +399,13 @@ class ShardedParamRuntime:
         self._built = False
         self._dirty = False
         self.step_count = 0
+        # full-weight rollout replica (None = rollouts gather like training does)
+        self.want_replica = bool(rollout_replica)
+        self.replica_flat: torch.Tensor | None = None
+        self.replica_off: dict[str, int] = {}
+        self.replica_version = -1
+        self.replica_waited = -1
+        self.broadcasts = 0
 
     # -- construction ----------------------------------------------------------------------------------
     def shard_units(self, units: Iterable[nn.Module]) -> int:
@@ -455,12 +478,71 @@ class ShardedParamRuntime:
             if rows:
                 self._tables[u] = (torch.tensor(rows, dtype=torch.int64, device=dev),
                                    max(r[2] for r in rows))
+        if self.want_replica:
+            self._build_replica()
         if self.fused:
             self._side = torch.cuda.Stream(device=dev)
             torch.cuda.synchronize(dev)
             self.pool.barrier()          # every rank's shards are in place before the first gather
+        if self.want_replica:
+            self.publish_replica()
         self._built = True
         return len(self.handles)
+
+    # -- rollout replica (trainer -> rollout weight broadcast) -----------------------------------------
+    def _build_replica(self) -> None:
+        dev, dt = self.device, self.dtype
+        off = 0
+        for h in self.handles:
+            self.replica_off[h.name] = off
+            off += h.n * h.k
+        if self.fused:
+            self.replica_flat = self.pool.allocate(off, dt, dev, "rollout_replica")
+            self.version_slot = self.pool.reserve_slots(16)
+            rows = [(h.shard_off, self.replica_off[h.name] + self.rank * h.numel_shard, h.numel_shard)
+                    for h in self.handles]
+            self._replica_table = (torch.tensor(rows, dtype=torch.int64, device=dev),
+                                   max(r[2] for r in rows))
+        else:
+            self.replica_flat = torch.empty(off, device=dev, dtype=dt)
+
+    def publish_replica(self) -> None:
+        """Bring every rank's rollout replica to the current parameter version."""
+        if self.replica_flat is None:
+            return
+        version = self.version + 1          # flag values start at 1
+        if self.fused:
+            from visionrl_b200.ops import _ext
+
+            table, longest = self._replica_table
+            _ext.load().p2p_broadcast_table(self.shard_flat, self.pool.peer_pointers(self.replica_flat),
+                                            table, self.world, self.rank, longest)
+            self.pool.signal(self.version_slot + self.rank, version)
+            self.kernel_launches += 2
+        else:
+            for h in self.handles:
+                dst = h.replica_view()
+                if self.world == 1:
+                    dst.copy_(h.shard)
+                elif dst.is_cuda:
+                    dist.all_gather_into_tensor(dst.view(-1), h.shard.reshape(-1), group=self.group)
+                else:
+                    parts = [torch.empty_like(h.shard) for _ in range(self.world)]
+                    dist.all_gather(parts, h.shard.contiguous(), group=self.group)
+                    dst.copy_(torch.cat(parts))
+        self.replica_version = self.version
+        self.broadcasts += 1
+
+    def replica_ready(self) -> bool:
+        """True when rollouts may read the replica; the first use after a publish enqueues the
+        bounded wait for every owner's version flag."""
+        if self.replica_flat is None or self._dirty or self.replica_version != self.version:
+            return False
+        if self.fused and self.replica_waited != self.version:
+            self.pool.wait(self.version_slot, self.world, self.version + 1)
+            self.kernel_launches += 1
+            self.replica_waited = self.version
+        return True
 
     @property
     def active(self) -> bool:
@@ -576,10 +658,13 @@ class ShardedParamRuntime:
         self.grad_shard.zero_()
         self.version += 1
 
-    def publish(self) -> None:
-        """Order the peers' next gathers after this rank's shard update."""
-        if self.fused:
+    def publish(self, barrier: bool = True) -> None:
+        """Order the peers' next gathers after this rank's shard update (``barrier=False`` when
+        the caller has just run one on the same pool), and push the new shards into the rollout
+        replicas."""
+        if self.fused and barrier:
             self.pool.barrier()
+        self.publish_replica()
 
     def invalidate(self) -> None:
         """Shards were changed behind the runtime's back (state-dict load, EMA swap): refresh the
@@ -629,6 +714,7 @@ class ShardedParamRuntime:
             "optimizer_shard_bytes": 3 * self.master.numel() * 4,
             "gather_ring_bytes": sum(b.numel() for b in self.gather_ring) * e,
             "grad_staging_bytes": sum(b.numel() for b in self.stage_ring) * e,
+            "rollout_replica_bytes": 0 if self.replica_flat is None else self.replica_flat.numel() * e,
         }
 
 
@@ -645,7 +731,7 @@ def find_units(model: nn.Module) -> list[nn.Module]:
 
 
 def shard_model(model: nn.Module, mesh: Any, device: torch.device, collectives: str = "fused",
-                ring: int = 2) -> ShardedParamRuntime | None:
+                ring: int = 2, rollout_replica: bool = False) -> ShardedParamRuntime | None:
     """Shard the block weights of ``model`` in place; ``None`` when nothing qualifies."""
     units = find_units(model)
     if not units:
@@ -653,7 +739,8 @@ def shard_model(model: nn.Module, mesh: Any, device: torch.device, collectives: 
     first = next((p for p in units[0].parameters() if p.dim() == 2), None)
     if first is None:
         return None
-    rt = ShardedParamRuntime(mesh, device, collectives=collectives, dtype=first.dtype, ring=ring)
+    rt = ShardedParamRuntime(mesh, device, collectives=collectives, dtype=first.dtype, ring=ring,
+                             rollout_replica=rollout_replica)
     if rt.world <= 1:
         return None
     if rt.shard_units(units) == 0:

@@ -149,6 +149,8 @@ class ShardedGradSync:
                     dist.all_gather(parts, own)
                     p.copy_(torch.cat(parts))
                 e["grad_shard"] = None
+        if self.param_runtime is not None:
+            self.param_runtime.publish()
         optimizer.zero_grad()
         return norm
 
@@ -189,7 +191,7 @@ class ShardedGradSync:
         # before a peer gathers them
         symm.barrier()
         rt = self.param_runtime
-        if rt is not None and rt.pool is not symm:
-            rt.publish()
+        if rt is not None:
+            rt.publish(barrier=rt.pool is not symm)
         optimizer.zero_grad()
         return norm

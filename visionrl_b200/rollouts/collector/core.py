@@ -1,9 +1,23 @@
-"""Generic collector: build request → runtime.generate → score rewards → pack
-(reference: ``vrl/rollouts/collector/core.py:20-163``).  With
-``VRL_PROFILE_COLLECT=1`` the two sub-phases are timed into ``phase_sink``."""
+"""The collector of every family: request → rollout backend → rewards → ``RolloutBatch``.
+
+What differs between families is injected — the request builder (which sampling fields a family
+declares), the packer (how an ``OutputBatch`` becomes observations / actions / extras) and the
+reward scorer — so this class holds only the sequence and the plumbing around it:
+
+1. build one ``GenerationRequest`` for the prompts (``group_size`` samples each);
+2. hand it to the rollout backend.  In a multi-rank job every rank makes the same call and gets
+   back the samples IT generated; nothing is gathered across ranks here;
+3. score the decoded outputs and pack.  Outputs, rewards and the packed batch stay on the
+   device of the policy.
+
+With ``VRL_PROFILE_COLLECT=1`` the time of step 2 and of step 3 (each fenced by a device
+synchronise) is written into ``phase_sink`` for the trainer's phase report.  Behavioural
+reference: ``vrl/rollouts/collector/core.py:20-163``.
+"""
 
 from __future__ import annotations
 
+import contextlib
 import os
 import time
 from collections.abc import Mapping
@@ -16,12 +30,31 @@ from visionrl_b200.rollouts.collector.rewards import RewardScorer
 from visionrl_b200.rollouts.packers.base import RolloutPackContext, RolloutPacker
 
 
-def _now_synced() -> float:
-    import torch
+class _PhaseClock:
+    """Device-fenced wall-clock timing of named phases; inert unless enabled."""
 
-    if torch.cuda.is_available():
-        torch.cuda.synchronize()
-    return time.perf_counter()
+    def __init__(self, enabled: bool) -> None:
+        self.enabled = enabled
+        self.seconds: dict[str, float] = {}
+
+    @staticmethod
+    def _fence() -> float:
+        import torch
+
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+        return time.perf_counter()
+
+    @contextlib.contextmanager
+    def phase(self, name: str):
+        if not self.enabled:
+            yield
+            return
+        start = self._fence()
+        try:
+            yield
+        finally:
+            self.seconds[name] = self.seconds.get(name, 0.0) + self._fence() - start
 
 
 class RolloutCollector:
@@ -39,6 +72,7 @@ class RolloutCollector:
         self.executor_kwargs = dict(executor_kwargs or {})
         self.phase_sink = phase_sink
 
+    # -- the backend this collector talks to -------------------------------------------------
     def set_runtime(self, runtime: RolloutBackend) -> None:
         if not callable(getattr(runtime, "generate", None)):
             raise TypeError("rollout runtime must implement async generate(request) -> OutputBatch")
@@ -51,50 +85,49 @@ class RolloutCollector:
                                "call set_runtime(...) before collect(...)")
         return self._runtime
 
-    async def shutdown(self) -> None:
-        stop = getattr(self._runtime, "shutdown", None)
-        if stop is not None:
-            await stop()
-        self._runtime = None
+    async def _call_runtime(self, method: str) -> None:
+        fn = getattr(self._runtime, method, None)
+        if fn is not None:
+            await fn()
 
     async def release_runtime_memory(self) -> None:
-        release = getattr(self._runtime, "release_memory", None)
-        if release is not None:
-            await release()
+        await self._call_runtime("release_memory")
+
+    async def shutdown(self) -> None:
+        await self._call_runtime("shutdown")
+        self._runtime = None
+
+    # -- collecting -------------------------------------------------------------------------------
+    def _pack_context(self, plan: RolloutRequestPlan) -> RolloutPackContext:
+        cfg = self.config
+        return RolloutPackContext(metadata=dict(plan.pack_metadata),
+                                  device=getattr(self.model, "device", None),
+                                  kl_reward=float(getattr(cfg, "kl_reward", 0.0)),
+                                  rescale_to_unit=bool(getattr(cfg, "rescale_to_unit", False)))
+
+    async def _score_and_pack(self, output: OutputBatch, plan: RolloutRequestPlan) -> RolloutBatch:
+        ctx = self._pack_context(plan)
+        scored = self.packer.reward_outputs(output, ctx)
+        device = ctx.device if ctx.device is not None else getattr(scored, "device", "cpu")
+        rewards = await self.reward_scorer.score(scored, self.packer.reward_prompts(output, ctx),
+                                                 plan.reward_metadata, device)
+        return await self.packer.pack(output, rewards, ctx)
 
     async def collect(self, prompts: list[str], **kwargs: Any) -> RolloutBatch:
         group_size = int(kwargs.get("group_size", self.default_group_size))
         plan = self.request_builder.build(prompts, group_size, dict(kwargs))
-        profile = os.environ.get("VRL_PROFILE_COLLECT") == "1"
-        phases: dict[str, float] = {}
-        t0 = _now_synced() if profile else 0.0
-        output = await self.runtime.generate(plan.request)
-        if output.error:
-            raise RuntimeError(f"{self.family}/{self.task} generation failed "
-                               f"(request_id={plan.request.request_id}): {output.error}")
-        if profile:
-            t1 = _now_synced()
-            phases["collect.engine_generate"] = t1 - t0
-            t0 = t1
-        batch = await self._to_rollout_batch(output, plan)
-        if profile:
-            phases["collect.reward_score"] = _now_synced() - t0
-            if self.phase_sink is not None:
-                self.phase_sink.clear()
-                self.phase_sink.update(phases)
+        clock = _PhaseClock(os.environ.get("VRL_PROFILE_COLLECT") == "1")
+        with clock.phase("collect.engine_generate"):
+            output = await self.runtime.generate(plan.request)
+            if output.error:
+                raise RuntimeError(f"{self.family}/{self.task} generation failed "
+                                   f"(request_id={plan.request.request_id}): {output.error}")
+        with clock.phase("collect.reward_score"):
+            batch = await self._score_and_pack(output, plan)
+        if clock.enabled and self.phase_sink is not None:
+            self.phase_sink.clear()
+            self.phase_sink.update(clock.seconds)
         return batch
-
-    async def _to_rollout_batch(self, output: OutputBatch, plan: RolloutRequestPlan) -> RolloutBatch:
-        ctx = RolloutPackContext(
-            metadata=dict(plan.pack_metadata), device=getattr(self.model, "device", None),
-            kl_reward=float(getattr(self.config, "kl_reward", 0.0)),
-            rescale_to_unit=bool(getattr(self.config, "rescale_to_unit", False)),
-        )
-        outputs = self.packer.reward_outputs(output, ctx)
-        device = ctx.device if ctx.device is not None else getattr(outputs, "device", "cpu")
-        rewards = await self.reward_scorer.score(outputs, self.packer.reward_prompts(output, ctx),
-                                                 plan.reward_metadata, device)
-        return await self.packer.pack(output, rewards, ctx)
 
 
 __all__ = ["RolloutCollector"]

@@ -165,8 +165,11 @@ def build_online_trainer(ctx: RunContext, parts: RecipeParts, reward_fn: Any):
             from visionrl_b200.parallel.fsdp import shard_model
 
             # block weights, their gradients and optimiser state live 1/shard-group per rank
-            param_runtime = shard_model(policy, mesh, ctx.device, collectives=collectives,
-                                        ring=int(cfg_path(cfg, "distributed.gather_ring", 2) or 2))
+            param_runtime = shard_model(
+                policy, mesh, ctx.device, collectives=collectives,
+                ring=int(cfg_path(cfg, "distributed.gather_ring", 2) or 2),
+                rollout_replica=str(cfg_path(cfg, "distributed.weight_sync", "p2p")) != "disabled"
+                and bool(cfg_path(cfg, "distributed.rollout_replica", True)))
             if param_runtime is not None:
                 policy.param_runtime = param_runtime
                 logger.info("sharded %d block weights over %d ranks: %s", len(param_runtime.handles),
@@ -180,13 +183,39 @@ def build_online_trainer(ctx: RunContext, parts: RecipeParts, reward_fn: Any):
             collector.runtime,
             initial_policy_version=ctx.resume.next_step if ctx.resume is not None else None),
         config=tc, device=ctx.device, stat_tracker=parts.stat_tracker, mesh=mesh,
-        grad_sync=grad_sync)
+        grad_sync=grad_sync, liveness=_build_liveness(cfg, mesh))
     if ctx.resume is not None:
         restore_training_checkpoint(ctx.resume, trainer=trainer, bundle=bundle,
                                     strict=tc.resume_strict)
         logger.info("Resuming from %s, start_epoch=%d", ctx.resume.checkpoint_dir,
                     ctx.resume.next_epoch)
     return trainer, collector
+
+
+def _build_liveness(cfg: Any, mesh: Any):
+    """Heartbeats between the ranks of a native multi-rank job (``distributed.heartbeat.*``)."""
+    if mesh.world_size <= 1 or not bool(cfg_path(cfg, "distributed.heartbeat.enable", True)):
+        return None
+    from visionrl_b200.parallel.liveness import build_liveness
+
+    return build_liveness(mesh,
+                          interval_s=float(cfg_path(cfg, "distributed.heartbeat.interval_s", 1.0)),
+                          deadline_s=float(cfg_path(cfg, "distributed.heartbeat.deadline_s", 60.0)))
+
+
+def shutdown_distributed(trainer: Any | None = None) -> None:
+    """Stop the heartbeat thread and tear the process group down (every recipe's last act)."""
+    import torch.distributed as dist
+
+    live = getattr(trainer, "liveness", None)
+    if live is not None:
+        live.stop()
+    if dist.is_available() and dist.is_initialized():
+        try:
+            dist.barrier()
+        except Exception:  # noqa: BLE001 - a peer is already gone; still release our side
+            pass
+        dist.destroy_process_group()
 
 
 async def run_online_recipe(ctx: RunContext, parts: RecipeParts, reward_fn: Any,
@@ -270,6 +299,8 @@ async def run_online_recipe(ctx: RunContext, parts: RecipeParts, reward_fn: Any,
     shutdown = getattr(collector, "shutdown", None)
     if callable(shutdown):
         await shutdown()
+    if bool(cfg_path(cfg, "distributed.destroy_on_exit", True)):
+        shutdown_distributed(trainer)
     return {"trainer": trainer, "bundle": bundle, "metrics": metrics}
 
 

@@ -155,7 +155,7 @@ class OnlineTrainer(Trainer):
                  config: TrainerConfig | None = None, prompts: list[str] | None = None,
                  device: torch.device | str = "cuda", accelerator: Any | None = None,
                  stat_tracker: Any | None = None, mesh: Any | None = None,
-                 grad_sync: Any | None = None) -> None:
+                 grad_sync: Any | None = None, liveness: Any | None = None) -> None:
         self.algorithm, self.collector, self.evaluator = algorithm, collector, evaluator
         self.model, self.ref_model, self.weight_syncer = model, ref_model, weight_syncer
         self.config = config or TrainerConfig()
@@ -166,6 +166,8 @@ class OnlineTrainer(Trainer):
         self.stat_tracker = stat_tracker
         self.mesh = mesh
         self.grad_sync = grad_sync
+        # host-side heartbeats of a multi-rank job (visionrl_b200.parallel.liveness.RankLiveness)
+        self.liveness = liveness
         self._optimizer: torch.optim.Optimizer | None = None
         self._ema: EMAModuleWrapper | None = None
         self._rollout_weights_initialized = False
@@ -405,6 +407,21 @@ class OnlineTrainer(Trainer):
 
     # -- the step ------------------------------------------------------------------------------
     async def step(self, prompts: list[str] | None = None) -> TrainStepMetrics:
+        """One policy step.  In a multi-rank job the peers' liveness is checked first (a rank that
+        failed or fell silent ends this rank with ``RankFailure`` before anything is launched),
+        and an exception raised here is announced to the peers before it propagates."""
+        live = self.liveness
+        if live is not None:
+            live.check()
+            live.beat(self.state.step)
+        try:
+            return await self._step(prompts)
+        except BaseException as exc:
+            if live is not None:
+                live.announce_failure(f"{type(exc).__name__}: {exc}")
+            raise
+
+    async def _step(self, prompts: list[str] | None = None) -> TrainStepMetrics:
         from visionrl_b200.rollouts.evaluators.types import SignalRequest
 
         if prompts is not None:
