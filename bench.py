@@ -206,7 +206,8 @@ def run(args) -> None:
                     "d2h_bytes_per_step": int(d2h // max(args.steps, 1))},
             "gpu_launches": launches,
             "sharding": ({**runtime.memory_report(), "fused_gathers": runtime.fused_gathers,
-                          "gathers": runtime.gathers, "buckets_reduced": runtime.buckets_reduced,
+                          "gathers": runtime.gathers, "standalone_gathers": runtime.standalone_gathers,
+                          "gather_ahead_launches": runtime.prefetches, "buckets_reduced": runtime.buckets_reduced,
                           "weight_broadcasts": runtime.broadcasts}
                          if sharded else None),
             "last_metrics": {"loss": metrics.loss, "reward_mean": metrics.reward_mean,

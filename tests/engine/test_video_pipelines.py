@@ -82,3 +82,37 @@ def test_wan_replay_reproduces_rollout_log_probs(wan):
     for j in range(STEPS):
         sig = ev.evaluate(bundle.policy, batch, j)
         assert torch.allclose(sig.log_prob, batch.extras["log_probs"][:, j], atol=1e-5)
+
+
+def test_wan_official_policy_samples_with_both_flow_solvers(wan):
+    """The two-expert variant generates with UniPC and DPM-Solver++; both are deterministic for a
+    seed, agree with each other far better than with a first-order run of the same length, and
+    switch to the low-noise expert below the boundary timestep."""
+    from visionrl_b200.models.diffusion import VideoGenerationRequest
+    from visionrl_b200.models.families.wan_2_1.official_policy import WanT2VOfficialPolicy
+
+    base = wan[0].policy
+    policy = WanT2VOfficialPolicy.__new__(WanT2VOfficialPolicy)
+    policy.__dict__.update(base.__dict__)
+    policy.boundary = 0.5
+    object.__setattr__(policy, "_low_noise", None)
+    policy._prompt_cache = {}
+    policy.attach_low_noise_expert()
+    used = []
+    original = policy._expert
+    policy._expert = lambda t: used.append(float(t.flatten()[0])) or original(t)
+
+    def run(solver, steps):
+        req = VideoGenerationRequest(prompt="a red fox", num_steps=steps, guidance_scale=3.0, height=32,
+                                     width=32, frame_count=5, seed=11, sample_solver=solver, shift=3.0,
+                                     extra={"max_sequence_length": 8})
+        return policy.sample(req, decode=False)
+
+    uni, dpm = run("unipc", 8), run("dpmpp", 8)
+    assert uni.shape == dpm.shape and uni.ndim == 5 and bool(torch.isfinite(uni).all())
+    assert torch.equal(uni, run("unipc", 8))
+    fine = run("dpmpp", 64)
+    assert (uni - fine).abs().mean() < 0.2 * fine.abs().mean()
+    assert (dpm - fine).abs().mean() < 0.2 * fine.abs().mean()
+    assert max(used) >= 500.0 > min(used)                      # both experts were consulted
+    assert len(policy._prompt_cache) == 1                      # one prompt, encoded once

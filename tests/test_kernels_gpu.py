@@ -522,6 +522,82 @@ def test_flash_attention_forward_matches_fp32(shape):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("variant", [1, 2])
+@pytest.mark.parametrize("shape", [(2, 3, 1178, 1178, 64), (1, 2, 300, 512, 128), (2, 2, 128, 77, 64),
+                                   (1, 2, 515, 515, 128)])
+def test_flash_attention_forward_variants_agree_with_fp32(shape, variant):
+    """Both forward kernels (register-accumulating, lazy-rescale) against the fp32 oracle; the
+    lazy one is also checked on scores with a large dynamic range, where its running maximum
+    grows past the rescale threshold several times."""
+    from visionrl_b200.ops import _ext
+    from visionrl_b200.ops.attention import attention_reference, flash_attention_forward
+
+    b, h, sq, skv, d = shape
+    torch.manual_seed(8)
+    for spread in (1.0, 6.0):
+        q = (torch.randn(b, h, sq, d, device="cuda") * spread).bfloat16()
+        k = torch.randn(b, h, skv, d, device="cuda").bfloat16()
+        # keys grow along the sequence so later tiles raise the maximum
+        k = (k.float() * torch.linspace(0.2, 1.5, skv, device="cuda")[None, None, :, None]).bfloat16()
+        v = torch.randn(b, h, skv, d, device="cuda").bfloat16()
+        out, lse = flash_attention_forward(q, k, v, d ** -0.5, False, variant)
+        torch.cuda.synchronize()
+        assert _ext.load().flash_attn_last_status() == 0
+        ref = attention_reference(q.float(), k.float(), v.float())
+        assert torch.allclose(out.float(), ref, atol=3e-2, rtol=3e-2)
+        scores = torch.matmul(q.float(), k.float().transpose(-1, -2)) * d ** -0.5
+        assert torch.allclose(lse, torch.logsumexp(scores, dim=-1), atol=5e-3, rtol=2e-3)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("shape", [(2, 3, 640, 640, 128), (1, 2, 300, 300, 64), (2, 2, 130, 515, 128),
+                                   (1, 4, 77, 77, 64), (1, 2, 1, 200, 128)])
+def test_flash_attention_causal_forward_backward_match_fp32(shape):
+    """Causal attention (Sq <= Skv, last query aligned with the last key), tails included."""
+    from visionrl_b200.ops import _ext
+    from visionrl_b200.ops.attention import (attention_reference, flash_attention_backward,
+                                             flash_attention_forward)
+
+    b, h, sq, skv, d = shape
+    torch.manual_seed(28)
+    q = torch.randn(b, h, sq, d, device="cuda").bfloat16()
+    k = torch.randn(b, h, skv, d, device="cuda").bfloat16()
+    v = torch.randn(b, h, skv, d, device="cuda").bfloat16()
+    dout = torch.randn(b, h, sq, d, device="cuda").bfloat16()
+    out, lse = flash_attention_forward(q, k, v, d ** -0.5, True)
+    dq, dk, dv = flash_attention_backward(dout, q, k, v, out, lse, d ** -0.5, True)
+    torch.cuda.synchronize()
+    assert _ext.load().flash_attn_last_status() == 0
+    qf, kf, vf = (t.float().requires_grad_(True) for t in (q, k, v))
+    ref_out = attention_reference(qf, kf, vf, causal=True)
+    assert torch.allclose(out.float(), ref_out, atol=2e-2, rtol=2e-2)
+    ref = torch.autograd.grad(ref_out, (qf, kf, vf), dout.float())
+    for got, want in zip((dq, dk, dv), ref):
+        err = (got.float() - want).abs().max().item()
+        assert err <= 2e-2 * max(1.0, want.abs().max().item()), err
+
+
+@pytest.mark.gpu
+def test_causal_attention_dispatch_trains_through_own_kernels():
+    from visionrl_b200.ops import _ext
+    from visionrl_b200.ops import attention as A
+
+    torch.manual_seed(29)
+    b, h, s, d = 2, 4, 200, 128
+    q, k, v = (torch.randn(b, h, s, d, device="cuda").bfloat16().requires_grad_(True) for _ in range(3))
+    before = _ext.launch_count
+    out = A.attention(q, k, v, causal=True)
+    out.float().pow(2).sum().backward()
+    assert _ext.launch_count - before >= 4          # forward + three backward launches
+    qf, kf, vf = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    ref = A.attention_reference(qf, kf, vf, causal=True)
+    ref.pow(2).sum().backward()
+    assert torch.allclose(out.float(), ref, atol=2e-2, rtol=2e-2)
+    for got, want in ((q, qf), (k, kf), (v, vf)):
+        assert (got.grad.float() - want.grad).abs().max().item() <= 3e-2 * max(1.0, want.grad.abs().max().item())
+
+
+@pytest.mark.gpu
 def test_flash_attention_token_major_views_and_dispatch():
     from visionrl_b200.ops.attention import attention, attention_reference
 

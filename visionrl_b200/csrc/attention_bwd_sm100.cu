@@ -81,6 +81,8 @@ struct Params {
   float scale;
   int* status;
   unsigned long long* timing;   // optional [16] phase cycle counters (see flash_attn_bwd_timing), or null
+  int causal;             // query row r attends keys 0 .. r + causal_off
+  int causal_off;         // Skv - Sq
 };
 
 // Adds the cycles since `t0` to counter `slot` and restarts the interval.
@@ -130,7 +132,22 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_own1, const __grid_cons
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int bh = blockIdx.y, r0 = blockIdx.x * kOwn;
   const int bi = bh / p.heads, hi = bh % p.heads;
-  const int n_tiles = (p.s_str + kStr - 1) / kStr;
+  // Streamed steps this CTA has to visit.  Causal attention skips the steps that lie entirely above
+  // the diagonal: the dQ pass (owned queries, streamed keys) stops after the last key its rows can
+  // see; the dK/dV pass (owned keys, streamed queries) starts at the first query that sees its keys.
+  // `j_lo` is the first streamed step; loop counters keep running from 0 so stage / parity
+  // arithmetic is unchanged.
+  int n_tiles = (p.s_str + kStr - 1) / kStr;
+  int j_lo = 0;
+  if (p.causal) {
+    if (kDQ) {
+      const int last_key = min(r0 + kOwn, p.s_own) - 1 + p.causal_off;
+      n_tiles = max(1, min(n_tiles, last_key / kStr + 1));
+    } else {
+      j_lo = min(max(0, (r0 - p.causal_off) / kStr), n_tiles - 1);
+      n_tiles -= j_lo;
+    }
+  }
 
   if (threadIdx.x == 0) {
     mbar_init(own_full, 1);
@@ -176,7 +193,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_own1, const __grid_cons
       if (!kDQ) {
 #pragma unroll
         for (int i = 0; i < kStr / 32; ++i) {
-          const int qi = j * kStr + i * 32 + lane;
+          const int qi = (j + j_lo) * kStr + i * 32 + lane;
           const bool in = qi < p.sq;
           vl[i] = in ? p.lse[(int64_t)bh * p.sq + qi] * 1.4426950408889634f : INFINITY;
           vd[i] = in ? p.delta[(int64_t)bh * p.sq + qi] : 0.f;
@@ -198,8 +215,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_own1, const __grid_cons
         mbar_expect_tx(&str_full[s], 2 * C::kStrBytes);
 #pragma unroll
         for (int c = 0; c < C::kDBlocks; ++c) {
-          tma_load_4d(ss1 + s * C::kStrBytes + c * kStrBlock, &map_str1, &str_full[s], c * 64, j * kStr, hi, bi);
-          tma_load_4d(ss2 + s * C::kStrBytes + c * kStrBlock, &map_str2, &str_full[s], c * 64, j * kStr, hi, bi);
+          tma_load_4d(ss1 + s * C::kStrBytes + c * kStrBlock, &map_str1, &str_full[s], c * 64, (j + j_lo) * kStr, hi, bi);
+          tma_load_4d(ss2 + s * C::kStrBytes + c * kStrBlock, &map_str2, &str_full[s], c * 64, (j + j_lo) * kStr, hi, bi);
         }
       }
     }
@@ -363,6 +380,26 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_own1, const __grid_cons
         for (int c = 0; c < CPT; ++c)
           if (c >= valid) pv[c] = 0.f;
       }
+      if (p.causal) {
+        // column c of this thread is streamed index s0 + c; the pair (query, key) is masked when
+        // key > query + causal_off
+        const int s0 = (j + j_lo) * kStr + half * CPT;
+        if (kDQ) {
+          const int seen = row + p.causal_off - s0 + 1;          // keys s0 .. s0 + seen - 1 are visible
+          if (seen < CPT) {
+#pragma unroll
+            for (int c = 0; c < CPT; ++c)
+              if (c >= seen) pv[c] = 0.f;
+          }
+        } else {
+          const int hidden = row - p.causal_off - s0;            // queries s0 .. s0 + hidden - 1 cannot see key `row`
+          if (hidden > 0) {
+#pragma unroll
+            for (int c = 0; c < CPT; ++c)
+              if (c < hidden) pv[c] = 0.f;
+          }
+        }
+      }
       if (!kDQ) {
 #pragma unroll
         for (int c = 0; c < CPT / 2; ++c) pk[c] = float2_to_bf16pair(pv[2 * c], pv[2 * c + 1]);
@@ -497,7 +534,7 @@ static unsigned long long* g_timing = nullptr;
 template <int D>
 static void run(const torch::Tensor& dout, const torch::Tensor& q, const torch::Tensor& k, const torch::Tensor& v,
                 const torch::Tensor& out, const torch::Tensor& lse, torch::Tensor& delta, torch::Tensor& dq,
-                torch::Tensor& dk, torch::Tensor& dv, double scale, cudaStream_t stream) {
+                torch::Tensor& dk, torch::Tensor& dv, double scale, bool causal, cudaStream_t stream) {
   const int64_t b = q.size(0), h = q.size(1), sq = q.size(2), skv = k.size(2);
   {
     const int64_t rows = b * h * sq;
@@ -518,6 +555,8 @@ static void run(const torch::Tensor& dout, const torch::Tensor& q, const torch::
   p.scale_log2 = (float)(scale * 1.4426950408889634);
   p.status = attn::status_word(q.get_device());
   p.timing = g_timing;
+  p.causal = causal ? 1 : 0;
+  p.causal_off = (int)(skv - sq);
   {
     // dK/dV: own K, V; stream Q, dO
     p.out1 = reinterpret_cast<__nv_bfloat16*>(dv.data_ptr());
@@ -568,7 +607,7 @@ torch::Tensor flash_attn_bwd_timing(bool enable) {
 // can describe, unit stride in D).  `out` and `lse` are what flash_attn_fwd returned.  The three
 // gradients are token-major [B, S, H, D] buffers returned as [B, H, S, D] views.
 std::vector<torch::Tensor> flash_attn_bwd(torch::Tensor dout, torch::Tensor q, torch::Tensor k, torch::Tensor v,
-                                          torch::Tensor out, torch::Tensor lse, double scale) {
+                                          torch::Tensor out, torch::Tensor lse, double scale, bool causal) {
   using namespace attn;
   TORCH_CHECK(q.is_cuda() && q.dim() == 4 && k.dim() == 4 && v.dim() == 4 && dout.dim() == 4 && out.dim() == 4,
               "flash_attn_bwd: [B, H, S, D]");
@@ -601,8 +640,9 @@ std::vector<torch::Tensor> flash_attn_bwd(torch::Tensor dout, torch::Tensor q, t
   }
   auto delta = torch::empty({b, h, sq}, lse.options());
   auto stream = at::cuda::getCurrentCUDAStream();
-  if (d == 64) attn_bwd::run<64>(dout, q, k, v, out, lse, delta, dq_tm, dk_tm, dv_tm, scale, stream);
-  else attn_bwd::run<128>(dout, q, k, v, out, lse, delta, dq_tm, dk_tm, dv_tm, scale, stream);
+  TORCH_CHECK(!causal || sq <= skv, "flash_attn_bwd: causal attention needs Sq <= Skv");
+  if (d == 64) attn_bwd::run<64>(dout, q, k, v, out, lse, delta, dq_tm, dk_tm, dv_tm, scale, causal, stream);
+  else attn_bwd::run<128>(dout, q, k, v, out, lse, delta, dq_tm, dk_tm, dv_tm, scale, causal, stream);
   return grads;
 }
 

@@ -54,6 +54,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("flag_barrier", &vrl::flag_barrier);
   m.def("bucket_reduce_acc", &vrl::bucket_reduce_acc);
   m.def("p2p_gather_rows", &vrl::p2p_gather_rows);
+  m.def("p2p_gather_table", &vrl::p2p_gather_table);
   m.def("p2p_broadcast_table", &vrl::p2p_broadcast_table);
   m.def("token_logprob_fwd", &vrl::token_logprob_fwd);
   m.def("token_logprob_bwd", &vrl::token_logprob_bwd);
@@ -70,9 +71,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("int4_gemm", &vrl::int4_gemm);
   m.def("int4_gemm_last_status", &vrl::int4_gemm_last_status);
   m.def("groupnorm_nhwc", &vrl::groupnorm_nhwc);
-  m.def("flash_attn_fwd", &vrl::flash_attn_fwd);
+  m.def("flash_attn_fwd", &vrl::flash_attn_fwd, pybind11::arg("q"), pybind11::arg("k"), pybind11::arg("v"),
+        pybind11::arg("scale"), pybind11::arg("causal") = false, pybind11::arg("variant") = 0);
   m.def("flash_attn_last_status", &vrl::flash_attn_last_status);
-  m.def("flash_attn_bwd", &vrl::flash_attn_bwd);
+  m.def("flash_attn_bwd", &vrl::flash_attn_bwd, pybind11::arg("dout"), pybind11::arg("q"), pybind11::arg("k"),
+        pybind11::arg("v"), pybind11::arg("out"), pybind11::arg("lse"), pybind11::arg("scale"),
+        pybind11::arg("causal") = false);
   m.def("flash_attn_bwd_timing", &vrl::flash_attn_bwd_timing);
   m.def("mma_issue_probe", &vrl::mma_issue_probe);
   m.def("gemm_bf16", &vrl::gemm_bf16);

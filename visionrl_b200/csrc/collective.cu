@@ -497,6 +497,47 @@ p2p_gather_rows_kernel(PeerPtrs shards, uint4* __restrict__ full, int64_t vec_pe
   }
 }
 
+// Table-driven all-gather of many row-sharded weights in one launch: segment j pulls `count`
+// elements from offset src_off of EVERY rank's shard buffer into dst + dst_off + peer * count, so
+// the destination holds the full [world * count] weight.  Used to fetch a whole block's weights
+// ahead of the block's backward pass, on a side stream.
+__global__ void __launch_bounds__(256)
+p2p_gather_table_kernel(PeerPtrs shards, uint4* __restrict__ dst, const int64_t* __restrict__ table, int world,
+                        int rank) {
+  const int64_t src_vec = table[blockIdx.y * 3 + 0] / 8, dst_vec = table[blockIdx.y * 3 + 1] / 8;
+  const int64_t nvec = table[blockIdx.y * 3 + 2] / 8;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int step = 0; step < world; ++step) {
+    const int r = (rank + step) % world;
+    const uint4* src = reinterpret_cast<const uint4*>(shards.p[r]) + src_vec;
+    uint4* out = dst + dst_vec + (int64_t)r * nvec;
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    for (; i + 3 * stride < nvec; i += 4 * stride) {
+      const uint4 v0 = src[i], v1 = src[i + stride], v2 = src[i + 2 * stride], v3 = src[i + 3 * stride];
+      out[i] = v0; out[i + stride] = v1; out[i + 2 * stride] = v2; out[i + 3 * stride] = v3;
+    }
+    for (; i < nvec; i += stride) out[i] = src[i];
+  }
+}
+
+void p2p_gather_table(torch::Tensor shard_peers, torch::Tensor dst, torch::Tensor table, int64_t world,
+                      int64_t rank, int64_t max_segment) {
+  TORCH_CHECK(dst.is_cuda() && dst.is_contiguous() && dst.element_size() == 2 &&
+              reinterpret_cast<uintptr_t>(dst.data_ptr()) % 16 == 0,
+              "p2p_gather_table: contiguous 16-bit destination, 16-byte aligned");
+  VRL_CHECK_OPERAND(table, dst, torch::kInt64);
+  TORCH_CHECK(table.dim() == 2 && table.size(1) == 3 && table.is_contiguous() && table.size(0) >= 1 &&
+              table.size(0) <= 65535, "p2p_gather_table: segment table [segments, 3] (src, dst, count), "
+              "all multiples of 8 elements");
+  TORCH_CHECK(world >= 1 && world <= kMaxPeers && rank >= 0 && rank < world && max_segment > 0);
+  const c10::cuda::CUDAGuard guard(dst.device());
+  const PeerPtrs sp = load_peers(shard_peers, (int)world);
+  const int bx = (int)std::max<int64_t>(1, std::min<int64_t>((max_segment / 8 + 1023) / 1024, 16));
+  p2p_gather_table_kernel<<<dim3(bx, (unsigned)table.size(0)), 256, 0, at::cuda::getCurrentCUDAStream()>>>(
+      sp, reinterpret_cast<uint4*>(dst.data_ptr()), table.data_ptr<int64_t>(), (int)world, (int)rank);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
 void p2p_gather_rows(torch::Tensor shard_peers, torch::Tensor full, int64_t shard_elems, int64_t world,
                      int64_t rank) {
   TORCH_CHECK(full.is_cuda() && full.is_contiguous() && full.element_size() == 2 &&

@@ -103,6 +103,8 @@ void bucket_reduce_acc(torch::Tensor stage_peers, torch::Tensor table, torch::Te
                        int64_t world, int64_t rank, int64_t max_segment);
 void p2p_broadcast_table(torch::Tensor src_flat, torch::Tensor dst_peers, torch::Tensor table,
                          int64_t world, int64_t rank, int64_t max_segment);
+void p2p_gather_table(torch::Tensor shard_peers, torch::Tensor dst, torch::Tensor table, int64_t world,
+                      int64_t rank, int64_t max_segment);
 void p2p_gather_rows(torch::Tensor shard_peers, torch::Tensor full, int64_t shard_elems, int64_t world,
                      int64_t rank);
 void ulysses_scatter(torch::Tensor src, torch::Tensor dst_peers, int64_t batch, int64_t heads,
@@ -141,12 +143,13 @@ torch::Tensor groupnorm_nhwc(torch::Tensor x, torch::Tensor weight, torch::Tenso
                              double eps, bool apply_silu);
 
 // attention_sm100.cu
-std::vector<torch::Tensor> flash_attn_fwd(torch::Tensor q, torch::Tensor k, torch::Tensor v, double scale);
+std::vector<torch::Tensor> flash_attn_fwd(torch::Tensor q, torch::Tensor k, torch::Tensor v, double scale,
+                                          bool causal, int64_t variant);
 int64_t flash_attn_last_status();
 
 // attention_bwd_sm100.cu
 std::vector<torch::Tensor> flash_attn_bwd(torch::Tensor dout, torch::Tensor q, torch::Tensor k, torch::Tensor v,
-                                          torch::Tensor out, torch::Tensor lse, double scale);
+                                          torch::Tensor out, torch::Tensor lse, double scale, bool causal);
 torch::Tensor flash_attn_bwd_timing(bool enable);
 
 // mma_probe.cu

@@ -1,10 +1,13 @@
-"""Wan variant with two timestep experts and sequential CFG.
+"""Wan variant with two timestep experts, sequential CFG and the multistep flow solvers.
 
 A high-noise and a low-noise transformer are switched at a boundary timestep
 (``boundary * num_train_timesteps``); conditional and unconditional branches run as two
-forwards; encoded prompts are cached by a SHA-256 key.  As in the reference
-(``vrl/models/families/wan_2_1/official_policy.py:65-602``) this variant is rollout-only:
-it has no adapter path and ``restore_eval_state`` raises.
+forwards; encoded prompts are cached by a SHA-256 key.  ``request.sample_solver`` picks the
+deterministic sampler of :meth:`sample`: ``"unipc"`` (UniPC) or anything else, by default
+``"dpmpp"`` (DPM-Solver++ 2M), both from :mod:`visionrl_b200.models.nn.flow_solvers` on the
+shifted uniform grid of ``request.shift``.  As in the reference
+(``vrl/models/families/wan_2_1/official_policy.py:65-602``, solver choice at ``:453-478``) this
+variant is rollout-only: it has no adapter path and ``restore_eval_state`` raises.
 """
 
 from __future__ import annotations
@@ -57,6 +60,36 @@ class WanT2VOfficialPolicy(WanT2VDiffusersPolicy):
         else:
             uncond, noise_pred = torch.zeros_like(cond), cond
         return {"noise_pred": noise_pred, "noise_pred_cond": cond, "noise_pred_uncond": uncond}
+
+    def build_solver(self, request: Any):
+        """The ODE solver ``request.sample_solver`` names, configured for ``request.num_steps``."""
+        from visionrl_b200.models.nn import flow_solvers as fs
+
+        train_steps = int(self._scheduler.num_train_timesteps)
+        shift = float(getattr(request, "shift", 1.0) or 1.0)
+        if str(getattr(request, "sample_solver", "dpmpp")) == "unipc":
+            solver = fs.FlowUniPCMultistepScheduler(num_train_timesteps=train_steps, shift=1.0)
+            solver.set_timesteps(int(request.num_steps), device=self._device, shift=shift)
+        else:
+            solver = fs.FlowDPMSolverMultistepScheduler(num_train_timesteps=train_steps, shift=1.0)
+            fs.retrieve_timesteps(solver, device=self._device,
+                                  sigmas=fs.get_sampling_sigmas(int(request.num_steps), shift))
+        return solver
+
+    @torch.no_grad()
+    def sample(self, request: Any, encoded: dict[str, Any] | None = None, decode: bool = True):
+        """Deterministic generation with the requested multistep solver (no log-probabilities:
+        this is the preview / evaluation sampler, not the SDE rollout)."""
+        if encoded is None:
+            encoded = self.encode_prompt(request.prompt, request.negative_prompt or None,
+                                         guidance_scale=request.guidance_scale, request=request)
+        state = self.prepare_sampling(request, encoded)
+        solver = self.build_solver(request)
+        state.scheduler, state.timesteps = solver, solver.timesteps
+        for i, t in enumerate(solver.timesteps):
+            pred = self.forward_step(state, i)["noise_pred"]
+            state.latents = solver.step(pred, t, state.latents)
+        return self.decode_latents(state.latents) if decode else state.latents
 
     def apply_lora(self, spec: Any) -> None:
         raise NotImplementedError("the two-expert Wan variant has no adapter path")

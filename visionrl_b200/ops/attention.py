@@ -38,19 +38,22 @@ def _has_backward() -> bool:
     return _ext.has("flash_attn_bwd")
 
 
-def flash_attention_forward(q, k, v, scale: float):
-    """tcgen05 forward kernel: returns ``(out, lse)`` with ``lse[B, H, S]`` in natural log."""
+def flash_attention_forward(q, k, v, scale: float, causal: bool = False, variant: int = 0):
+    """tcgen05 forward kernel: returns ``(out, lse)`` with ``lse[B, H, S]`` in natural log.
+
+    ``causal``: query row ``r`` attends keys ``0 … r + (Skv - Sq)``.  ``variant`` selects the kernel
+    (0 = default for the shape, 1 = register-accumulating, 2 = lazy-rescale) for benchmarks."""
     from visionrl_b200.ops import _ext
 
-    out, lse = _ext.load().flash_attn_fwd(q, k, v, float(scale))
+    out, lse = _ext.load().flash_attn_fwd(q, k, v, float(scale), bool(causal), int(variant))
     return out, lse
 
 
-def flash_attention_backward(dout, q, k, v, out, lse, scale: float):
+def flash_attention_backward(dout, q, k, v, out, lse, scale: float, causal: bool = False):
     """tcgen05 backward kernels (delta pre-pass, dK/dV pass, dQ pass): returns ``(dq, dk, dv)``."""
     from visionrl_b200.ops import _ext
 
-    return _ext.load().flash_attn_bwd(dout, q, k, v, out, lse, float(scale))
+    return _ext.load().flash_attn_bwd(dout, q, k, v, out, lse, float(scale), bool(causal))
 
 
 class _FlashAttnFn(torch.autograd.Function):
@@ -58,17 +61,17 @@ class _FlashAttnFn(torch.autograd.Function):
     log-sum-exp, backward recomputes the probabilities tile by tile."""
 
     @staticmethod
-    def forward(ctx, q, k, v, scale):
-        out, lse = flash_attention_forward(q, k, v, scale)
+    def forward(ctx, q, k, v, scale, causal=False):
+        out, lse = flash_attention_forward(q, k, v, scale, causal)
         ctx.save_for_backward(q, k, v, out, lse)
-        ctx.scale = scale
+        ctx.scale, ctx.causal = scale, bool(causal)
         return out
 
     @staticmethod
     def backward(ctx, dout):
         q, k, v, out, lse = ctx.saved_tensors
-        dq, dk, dv = flash_attention_backward(dout, q, k, v, out, lse, ctx.scale)
-        return dq, dk, dv, None
+        dq, dk, dv = flash_attention_backward(dout, q, k, v, out, lse, ctx.scale, ctx.causal)
+        return dq, dk, dv, None, None
 
 
 # Which implementation differentiable calls use: "own" = the tcgen05 forward/backward pair above,
@@ -90,18 +93,18 @@ def backward_impl() -> str:
 def attention(q, k, v, causal: bool = False, scale: float | None = None):
     """Bidirectional (or causal) attention over ``[B, H, S, D]``.
 
-    Bidirectional bf16 calls with head dimension 64 or 128 run the hand-written sm_100a kernels:
-    the forward alone when no gradient is needed (rollout sampling, frozen-reference passes,
-    reward towers), the forward/backward pair otherwise.  Causal calls and other shapes use the
-    library's fused attention.
+    bf16 calls with head dimension 64 or 128 — bidirectional or causal (``Sq <= Skv``, the last
+    query aligned with the last key) — run the hand-written sm_100a kernels: the forward alone when
+    no gradient is needed (rollout sampling, prefill, frozen-reference passes, reward towers), the
+    forward/backward pair otherwise.  Other shapes use the library's fused attention.
     """
     scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
     needs_grad = torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad)
-    if not causal and _native_ok(q, k, v):
+    if _native_ok(q, k, v) and (not causal or q.shape[2] <= k.shape[2]):
         if not needs_grad:
-            return flash_attention_forward(q, k, v, scale)[0]
+            return flash_attention_forward(q, k, v, scale, causal)[0]
         if _BACKWARD_IMPL == "own" and _has_backward():
-            return _FlashAttnFn.apply(q, k, v, scale)
+            return _FlashAttnFn.apply(q, k, v, scale, causal)
     if q.is_cuda:
         return F.scaled_dot_product_attention(q, k, v, is_causal=causal, scale=scale)
     return attention_reference(q, k, v, causal, scale)

@@ -19,22 +19,6 @@ CSRC = os.path.join(PKG_DIR, "csrc")
 BUILD_DIR = os.path.join(PKG_DIR, "csrc", "build")
 
 
-def _cutlass_include() -> list[str]:
-    """CuTe / CUTLASS header roots vendored in site-packages (used for descriptor helpers)."""
-    import site
-
-    out = []
-    for root in site.getsitepackages():
-        for rel in ("flashinfer/data/cutlass/include", "tilelang/3rdparty/cutlass/include"):
-            path = os.path.join(root, rel)
-            if os.path.isdir(path):
-                out.append(path)
-                break
-        if out:
-            break
-    return out
-
-
 def sources() -> list[str]:
     found = sorted(glob.glob(os.path.join(CSRC, "*.cu")) + glob.glob(os.path.join(CSRC, "*.cpp")))
     return found
@@ -55,7 +39,7 @@ def build_extension(verbose: bool = False, ptxas_verbose: bool = False) -> str:
         cuda_flags += ["-Xptxas", "-v"]
     module = load(
         name="_C", sources=sources(), extra_cflags=["-O3", "-std=c++17"],
-        extra_cuda_cflags=cuda_flags, extra_include_paths=[CSRC, *_cutlass_include()],
+        extra_cuda_cflags=cuda_flags, extra_include_paths=[CSRC],
         extra_ldflags=["-lcuda"], build_directory=BUILD_DIR, verbose=verbose,
         is_python_module=True,
     )

@@ -124,19 +124,22 @@ def bench_adaln(args) -> dict:
 
 
 def bench_attention(args) -> dict:
-    from visionrl_b200.ops.attention import attention
+    from visionrl_b200.ops.attention import flash_attention_forward
 
     b, h, s, d = args.batch, args.heads, args.seq, args.head_dim
+    causal, variant = bool(args.causal), int(args.variant)
     q, k, v = (torch.randn(b, h, s, d, device="cuda", dtype=torch.bfloat16) for _ in range(3))
     flush = _flush_buffer(not args.no_flush)
-    flops = 4.0 * b * h * s * s * d
-    out = {"kernel": "attention_fwd", "batch": b, "heads": h, "seq": s, "head_dim": d}
+    flops = 4.0 * b * h * s * s * d * (0.5 if causal else 1.0)
+    out = {"kernel": "attention_fwd", "batch": b, "heads": h, "seq": s, "head_dim": d,
+           "causal": causal, "variant": variant}
+    sdpa = torch.nn.functional.scaled_dot_product_attention
+    own = lambda: flash_attention_forward(q, k, v, d ** -0.5, causal, variant)[0]  # noqa: E731
     with torch.no_grad():
-        t_lib = _time(lambda: torch.nn.functional.scaled_dot_product_attention(q, k, v),
-                      args.iters, args.warmup, flush)
-        t = _time(lambda: attention(q, k, v), args.iters, args.warmup, flush)
-        ref = torch.nn.functional.scaled_dot_product_attention(q.float(), k.float(), v.float())
-        out["max_abs_err"] = round((attention(q, k, v).float() - ref).abs().max().item(), 5)
+        t_lib = _time(lambda: sdpa(q, k, v, is_causal=causal), args.iters, args.warmup, flush)
+        t = _time(own, args.iters, args.warmup, flush)
+        ref = sdpa(q.float(), k.float(), v.float(), is_causal=causal)
+        out["max_abs_err"] = round((own().float() - ref).abs().max().item(), 5)
     out.update({"sdpa_ms": round(t_lib, 4), "sdpa_tflops": round(flops / t_lib / 1e9, 1),
                 "ms": round(t, 4), "tflops": round(flops / t / 1e9, 1)})
     if args.peak_tflops:
@@ -146,16 +149,17 @@ def bench_attention(args) -> dict:
 
         scale = d ** -0.5
         dout = torch.randn_like(q)
-        o, lse = flash_attention_forward(q, k, v, scale)
-        t_b = _time(lambda: flash_attention_backward(dout, q, k, v, o, lse, scale), args.iters, args.warmup, flush)
+        o, lse = flash_attention_forward(q, k, v, scale, causal, variant)
+        t_b = _time(lambda: flash_attention_backward(dout, q, k, v, o, lse, scale, causal), args.iters,
+                    args.warmup, flush)
         ql, kl, vl = (t.detach().clone().requires_grad_(True) for t in (q, k, v))
-        ol = torch.nn.functional.scaled_dot_product_attention(ql, kl, vl)
+        ol = torch.nn.functional.scaled_dot_product_attention(ql, kl, vl, is_causal=causal)
         t_lb = _time(lambda: torch.autograd.grad(ol, (ql, kl, vl), dout, retain_graph=True),
                      args.iters, args.warmup, flush)
         qf, kf, vf = (t.detach().float().requires_grad_(True) for t in (q, k, v))
-        ref = torch.autograd.grad(torch.nn.functional.scaled_dot_product_attention(qf, kf, vf), (qf, kf, vf),
-                                  dout.float())
-        got = flash_attention_backward(dout, q, k, v, o, lse, scale)
+        ref = torch.autograd.grad(torch.nn.functional.scaled_dot_product_attention(qf, kf, vf, is_causal=causal),
+                                  (qf, kf, vf), dout.float())
+        got = flash_attention_backward(dout, q, k, v, o, lse, scale, causal)
         out.update({"bwd_ms": round(t_b, 4), "bwd_tflops": round(2.5 * flops / t_b / 1e9, 1),
                     "sdpa_bwd_ms": round(t_lb, 4), "sdpa_bwd_tflops": round(2.5 * flops / t_lb / 1e9, 1),
                     "bwd_max_abs_err": [round((g.float() - r).abs().max().item(), 5) for g, r in zip(got, ref)]})
@@ -241,6 +245,9 @@ def main(argv=None) -> int:
     t.add_argument("--seq", type=int, default=1178)
     t.add_argument("--head-dim", type=int, default=64)
     t.add_argument("--backward", action="store_true")
+    t.add_argument("--causal", action="store_true")
+    t.add_argument("--variant", type=int, default=0,
+                   help="forward kernel: 0 default for the shape, 1 register-accumulating, 2 lazy-rescale")
     t.set_defaults(fn=bench_attention)
     tp = sub.add_parser("attention_phases")
     tp.add_argument("--batch", type=int, default=16)

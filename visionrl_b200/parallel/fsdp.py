@@ -15,7 +15,11 @@ How the collectives are fused with compute (``collectives="fused"``, bf16 on CUD
   threads per CTA pull the peers' rows over NVLink into the gather buffer (own rows first) while the
   tcgen05 warps already multiply the tiles whose rows have arrived.  The gathered copy then serves
   the ``dX = dY·W`` product of the same block's backward (activation checkpointing re-runs the
-  forward right before it); a copy found evicted is re-gathered by a plain peer-copy kernel.
+  forward right before it).  Where no GEMM can hide a gather — the weights a backward pass
+  without recomputation needs again, and projections applied to a handful of rows (the adaLN
+  modulation) whose product is over before the rows arrive — the NEXT block's weights are
+  fetched ahead of time by one table-driven peer-copy kernel on a side stream while the current
+  block computes; a copy found neither gathered nor prefetched is fetched on the spot.
 * **reduce-scatter ⊕ cast ⊕ scale ⊕ accumulate, overlapped with backward** — the ``dW`` GEMMs of a
   block write into that block's staging buffer.  When the backward pass moves on to the next
   block the finished bucket is published to the peers with a release flag and, on a side stream,
@@ -85,6 +89,7 @@ class ShardedWeight:
         self._gather_epoch = -1
         self._gather_version = -1
         self._peers: torch.Tensor | None = None
+        self.last_rows = -1                 # rows of the last activation multiplied with this weight
 
     # -- views -------------------------------------------------------------------------------
     @property
@@ -112,13 +117,12 @@ class ShardedWeight:
         return self._peers
 
     # -- gathering ---------------------------------------------------------------------------------
-    def _claim(self) -> torch.Tensor:
+    def _claim(self, backward: bool = False) -> torch.Tensor:
         """The gather-ring view of this weight; taking a slot over from another unit evicts it."""
-        self.rt._settle()
-        state = self.rt.gather_slots[self._slot()]
-        if state.owner != self.unit:
-            state.owner = self.unit
-            state.epoch += 1
+        rt = self.rt
+        rt._settle()
+        if rt._cursor != (self.unit, backward):
+            rt.visit_unit(self.unit, backward)
         return self._full_view()
 
     def _mark_gathered(self) -> None:
@@ -130,12 +134,13 @@ class ShardedWeight:
         return (state.owner == self.unit and self._gather_epoch == state.epoch
                 and self._gather_version == self.rt.version)
 
-    def gather(self) -> torch.Tensor:
+    def gather(self, backward: bool = False) -> torch.Tensor:
         """The full ``[N, K]`` weight in its gather buffer (stand-alone all-gather when stale)."""
         rt = self.rt
-        full = self._claim()
+        full = self._claim(backward)
         if self.is_gathered():
             return full
+        rt.standalone_gathers += 1
         if rt.fused and full.is_cuda:
             from visionrl_b200.ops import _ext
 
@@ -165,6 +170,7 @@ class ShardedWeight:
 
         rt = self.rt
         ext = _ext.load()
+        self.last_rows = int(x2.shape[0])
         full = self._claim()
         act_id = linear_ops._ACTS[act]
         if self.is_gathered() or rt.world == 1 or not rt.fused:
@@ -290,7 +296,7 @@ class _ShardedLinearFn(torch.autograd.Function):
             gy2 = gy2.contiguous()
         gx = gb = None
         if ctx.needs_input_grad[0]:
-            gx = linear_ops.gemm_nn(gy2, handle.gather()).view(ctx.x_shape)
+            gx = linear_ops.gemm_nn(gy2, handle.gather(backward=True)).view(ctx.x_shape)
         if handle.param.requires_grad:
             handle.stage_grad(gy2, x2)
         if ctx.has_bias and ctx.needs_input_grad[1]:
@@ -325,7 +331,7 @@ class _ShardedGeluMLPFn(torch.autograd.Function):
         if not gy2.is_contiguous():
             gy2 = gy2.contiguous()
         # gh = (gy @ W2) * gelu'(h): W2 is [out, hidden] row-major, the MN-major B operand
-        gh = ext.gemm_bf16(gy2, h2.gather(), None, None, h, 3, 0, False, True, False)
+        gh = ext.gemm_bf16(gy2, h2.gather(backward=True), None, None, h, 3, 0, False, True, False)
         gx = gb1 = gb2 = None
         if h2.param.requires_grad:
             h2.stage_grad(gy2, a)
@@ -336,7 +342,7 @@ class _ShardedGeluMLPFn(torch.autograd.Function):
         if ctx.has_b1 and ctx.needs_input_grad[1]:
             gb1 = ext.colsum(gh).to(gh.dtype)
         if ctx.needs_input_grad[0]:
-            gx = linear_ops.gemm_nn(gh, h1.gather()).view(ctx.x_shape)
+            gx = linear_ops.gemm_nn(gh, h1.gather(backward=True)).view(ctx.x_shape)
         return gx, gb1, gb2, None, None, None
 
 
@@ -390,6 +396,16 @@ class ShardedParamRuntime:
         self.kernel_launches = 0
         self.gathers = 0
         self.fused_gathers = 0
+        self.standalone_gathers = 0
+        self.prefetches = 0
+        # gather-ahead of the next unit's weights on a side stream
+        self.prefetch = True
+        self.small_rows = 1024              # a product of fewer rows cannot hide its own gather
+        self._cursor: tuple[int, bool] = (-1, False)
+        self._last_unit = -1
+        self._pending: dict[int, tuple[Any, list, int]] = {}
+        self._fetch_tables: dict[tuple, tuple[torch.Tensor, int]] = {}
+        self._prefetch_stream: Any = None
         self.buckets_reduced = 0
         # bucket pipeline
         self.current_bucket = -1
@@ -482,6 +498,7 @@ class ShardedParamRuntime:
             self._build_replica()
         if self.fused:
             self._side = torch.cuda.Stream(device=dev)
+            self._prefetch_stream = torch.cuda.Stream(device=dev)
             torch.cuda.synchronize(dev)
             self.pool.barrier()          # every rank's shards are in place before the first gather
         if self.want_replica:
@@ -547,6 +564,65 @@ class ShardedParamRuntime:
     @property
     def active(self) -> bool:
         return bool(self.handles)
+
+    # -- unit traversal and gather-ahead ---------------------------------------------------------------
+    def visit_unit(self, unit: int, backward: bool) -> None:
+        """Called when the computation moves to another unit (or turns from forward to backward
+        inside one): take the unit's ring slot over, adopt what was fetched ahead for it, and
+        start fetching the unit that comes next in the direction of travel."""
+        step = unit - self._last_unit if self._last_unit >= 0 and unit != self._last_unit else 0
+        direction = (1 if step > 0 else -1) if step else (-1 if backward else 1)
+        self._cursor = (unit, backward)
+        self._last_unit = unit
+        slot = self.gather_slots[unit % self.ring]
+        pending = self._pending.pop(unit, None)
+        if slot.owner != unit:
+            slot.owner = unit
+            slot.epoch += 1
+        if pending is not None:
+            event, handles, version = pending
+            if version == self.version:
+                torch.cuda.current_stream(self.device).wait_event(event)
+                for h in handles:
+                    h._mark_gathered()
+        if self.fused and self.prefetch and self.ring >= 2:
+            self._fetch_ahead(unit + direction, whole_unit=backward)
+
+    def _fetch_ahead(self, unit: int, whole_unit: bool) -> None:
+        if unit < 0 or unit not in self.unit_sizes or unit in self._pending:
+            return
+        wanted = [h for h in self.handles if h.unit == unit and not h.is_gathered()
+                  and (whole_unit or 0 <= h.last_rows < self.small_rows)]
+        if not wanted:
+            return
+        from visionrl_b200.ops import _ext
+
+        slot_index = unit % self.ring
+        slot = self.gather_slots[slot_index]
+        # the slot changes hands now: whatever its previous owner had gathered there is void
+        if slot.owner != unit:
+            slot.owner = -1
+            slot.epoch += 1
+        key = (unit, tuple(h.index for h in wanted))
+        cached = self._fetch_tables.get(key)
+        if cached is None:
+            rows = [(h.shard_off, h.unit_off, h.numel_shard) for h in wanted]
+            cached = (torch.tensor(rows, dtype=torch.int64, device=self.device), max(r[2] for r in rows))
+            self._fetch_tables[key] = cached
+        table, longest = cached
+        main = torch.cuda.current_stream(self.device)
+        ready = torch.cuda.Event()
+        ready.record(main)                       # the slot's previous readers are all enqueued before this
+        with torch.cuda.stream(self._prefetch_stream):
+            self._prefetch_stream.wait_event(ready)
+            _ext.load().p2p_gather_table(self.pool.peer_pointers(self.shard_flat), self.gather_ring[slot_index],
+                                         table, self.world, self.rank, longest)
+            done = torch.cuda.Event()
+            done.record(self._prefetch_stream)
+        self._pending[unit] = (done, wanted, self.version)
+        self.prefetches += 1
+        self.gathers += len(wanted)
+        self.kernel_launches += 1
 
     # -- bucket pipeline ---------------------------------------------------------------------------------
     def open_bucket(self, unit: int) -> None:
@@ -641,6 +717,7 @@ class ShardedParamRuntime:
         if not self.active:
             return
         self._settle()
+        self._drain_fetches()
         self.step_count += 1
         b1, b2 = group["betas"]
         kw = dict(lr=float(group["lr"]), beta1=float(b1), beta2=float(b2), eps=float(group["eps"]),
@@ -666,10 +743,18 @@ class ShardedParamRuntime:
             self.pool.barrier()
         self.publish_replica()
 
+    def _drain_fetches(self) -> None:
+        """No gather-ahead of the old parameter version may still be writing a ring slot."""
+        if self._prefetch_stream is not None and self._pending:
+            torch.cuda.current_stream(self.device).wait_stream(self._prefetch_stream)
+        self._pending.clear()
+        self._cursor = (-1, False)
+
     def invalidate(self) -> None:
         """Shards were changed behind the runtime's back (state-dict load, EMA swap): refresh the
         fp32 master copy and drop every gathered copy."""
         self._dirty = False
+        self._drain_fetches()
         if self.active:
             self.master.copy_(self.shard_flat)
         self.version += 1

@@ -24,6 +24,9 @@ class DeviceWeightBroadcaster:
     def __init__(self, pool: SymmetricPool, numel: int, dtype: torch.dtype, device: Any) -> None:
         self.pool = pool
         self.replica = pool.allocate(numel, dtype, device, "rollout_params").zero_()
+        # a peer's first publish must not race with this rank's zero-fill
+        torch.cuda.synchronize(device)
+        pool.barrier()
         self.version = 0
         self.launches = 0
 
