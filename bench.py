@@ -34,7 +34,39 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 METRIC = "GRPO samples/sec (rollout+train, device-timed, max over ranks)"
-MODEL = "SD3.5-medium-shape MMDiT (24 blocks, hidden 1536, 24 heads, 1024+154 tokens)"
+
+# The workloads BASELINE.json names.  `--config` picks one; the default is the headline one.
+CONFIGS = {
+    "sd3_5": {
+        "experiment": "experiment/sd3_5_shape_grpo",
+        "model": "SD3.5-medium-shape MMDiT (24 blocks, hidden 1536, 24 heads, 1024+154 tokens)",
+        "seq_len": 1024 + 154, "prompts": 8, "group": 8,
+        "extra": {"sde_steps": 10, "cfg": 4.5, "train_timesteps": 9,
+                  "reward": "ViT-L/14 scalar head on VAE-decoded 512x512"},
+    },
+    "wan_1_3b": {
+        "experiment": "experiment/wan_2_1_1_3b_shape_grpo",
+        "model": "Wan-2.1-1.3B-shape video DiT (30 blocks, dim 1536, 12 heads, FFN 8960, 14040 tokens)",
+        "seq_len": 14040, "prompts": 2, "group": 8,
+        "extra": {"sde_steps": 16, "cfg": 5.0, "reward": "ViT-L/14 scalar head on 4 frames",
+                  "mesh": "dp = N / sp, Ulysses sp = min(4, N)"},
+    },
+    "wan_14b": {
+        "experiment": "experiment/wan_2_1_14b_shape_grpo",
+        "model": "Wan-2.1-14B-shape video DiT (40 blocks, dim 5120, 40 heads, FFN 13824, 32760 tokens)",
+        "seq_len": 32760, "prompts": 1, "group": 4,
+        "extra": {"sde_steps": 16, "cfg": 5.0, "reward": "ViT-L/14 scalar head on 4 frames",
+                  "mesh": "Ulysses sp = N"},
+    },
+    "janus": {
+        "experiment": "experiment/janus_pro_1b_shape_grpo",
+        "model": "Janus-Pro-1B-shape LLaMA decoder (24 layers, hidden 2048, 16 heads, 576 image tokens)",
+        "seq_len": 64 + 576, "prompts": 1, "group": 16,
+        "extra": {"cfg": 5.0, "decode": "int4 weight-only KV-cache decode",
+                  "reward": "ViT-B/16 scalar head on the VQ-decoded image"},
+    },
+}
+MODEL = CONFIGS["sd3_5"]["model"]
 
 
 class ClockSampler:
@@ -102,14 +134,22 @@ def reference_arm() -> None:
 
 
 def run(args) -> None:
+    import inspect
+
     import torch
     import torch.distributed as dist
 
     from visionrl_b200.config.loader import load_config
     from visionrl_b200.ops import _ext
-    from visionrl_b200.scripts.flagship import build_flagship_trainer
+    from visionrl_b200.scripts.common import capture_trainer
+    from visionrl_b200.scripts.train import run_config
 
-    baseline = args.impl == "torch_baseline"
+    spec = CONFIGS[args.config]
+    if args.prompts is None:
+        args.prompts = spec["prompts"]
+    if args.group is None:
+        args.group = spec["group"]
+    baseline = args.impl in ("torch_baseline", "torch_compile_baseline")
     if baseline:
         _ext.set_kernels_enabled(False)
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -119,15 +159,40 @@ def run(args) -> None:
         f"distributed.collectives={'nccl' if baseline else args.collectives}",
         f"distributed.param_sharding={args.sharding}",
         f"distributed.rollout_replica={'true' if args.rollout_replica else 'false'}",
+        "distributed.destroy_on_exit=false",
         "trainer.output_dir=/tmp/vrl_bench", f"rollout.rollout_batch_size={args.prompts}",
-        f"rollout.n={args.group}", f"rollout.sample_batch_size={args.group}",
-    ] + list(args.override)
-    cfg = load_config("experiment/sd3_5_shape_grpo", overrides=overrides)
-    trainer, prompts = build_flagship_trainer(cfg)
+    ]
+    if args.config == "janus":
+        overrides += [f"rollout.n_samples_per_prompt={args.group}"]
+    else:
+        overrides += [f"rollout.n={args.group}"]
+    if args.config == "sd3_5":
+        overrides += [f"rollout.sample_batch_size={args.group}"]
+    if args.config == "wan_1_3b":
+        overrides += [f"distributed.mesh.sp={min(4, args.gpus)}"]
+    if args.config == "wan_14b":
+        overrides += [f"distributed.mesh.sp={args.gpus}"]
+    overrides += list(args.override)
+    cfg = load_config(spec["experiment"], overrides=overrides)
+    loop = asyncio.new_event_loop()
+    # the recipe named by the config builds everything (model, collector, runtime, trainer) exactly
+    # as a training run would, then hands the trainer over instead of entering its epoch loop
+    with capture_trainer() as box:
+        outcome = run_config(cfg)
+        if inspect.isawaitable(outcome):
+            loop.run_until_complete(outcome)
+    trainer, examples = box["trainer"], box["examples"]
+    gen = torch.Generator().manual_seed(box["ctx"].trainer_config.seed)
+    prompts = [examples[i] for i in torch.randperm(len(examples), generator=gen)[:args.prompts].tolist()]
     rank = dist.get_rank() if dist.is_initialized() else 0
     device = trainer.device
     policy = trainer.model
-    text = policy.backend_handle.text
+    if args.impl == "torch_compile_baseline":
+        # what the reference's stock diffusion path does to its transformer (comparison arm only)
+        policy.transformer = torch.compile(policy.transformer, mode="default", dynamic=False)
+    text = getattr(getattr(policy, "backend_handle", None), "text", None)
+    if text is None or not hasattr(text, "drop_device_cache"):
+        text = _NoHostConditioning()
     samples_per_step = args.prompts * args.group
 
     def barrier():
@@ -138,7 +203,6 @@ def run(args) -> None:
     async def one_step():
         return await trainer.step(prompts)
 
-    loop = asyncio.new_event_loop()
     for _ in range(args.warmup):
         loop.run_until_complete(one_step())
     ext_status = [int(v) for v in _ext.load().kernel_status_all()] if not baseline else []
@@ -191,19 +255,20 @@ def run(args) -> None:
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "impl": args.impl,
             "config": {
-                "model": MODEL, "global_batch": samples_per_step, "seq_len": 1024 + 154,
+                "name": args.config, "model": spec["model"], "global_batch": samples_per_step,
+                "seq_len": spec["seq_len"],
                 "parallelism": ("single" if args.gpus == 1 else f"fsdp{runtime.world}" if sharded
                                 else f"dp{args.gpus}+sharded-optimizer"),
-                "prompts": args.prompts, "group_size": args.group, "sde_steps": 10, "cfg": 4.5,
-                "train_timesteps": 9, "reward": "ViT-L/14 scalar head on VAE-decoded 512x512",
-                "l2_policy": "working set (4 GB weights + activations) exceeds the 126 MB L2",
+                "prompts": args.prompts, "group_size": args.group, **spec["extra"],
+                "l2_policy": "working set (GBs of weights + activations) exceeds the 126 MB L2",
                 "collectives": "nccl" if baseline else args.collectives,
                 "attention": "library SDPA" if baseline else _attention_impl(),
             },
             "clocks": clocks,
-            "e2e": {"value": round(e2e_value, 4), "unit": "samples/s",
-                    "h2d_bytes_per_step": int(h2d // max(args.steps, 1)),
-                    "d2h_bytes_per_step": int(d2h // max(args.steps, 1))},
+            "e2e": ({"value": round(e2e_value, 4), "unit": "samples/s",
+                     "h2d_bytes_per_step": int(h2d // max(args.steps, 1)),
+                     "d2h_bytes_per_step": int(d2h // max(args.steps, 1))}
+                    if not isinstance(text, _NoHostConditioning) else None),
             "gpu_launches": launches,
             "sharding": ({**runtime.memory_report(), "fused_gathers": runtime.fused_gathers,
                           "gathers": runtime.gathers, "standalone_gathers": runtime.standalone_gathers,
@@ -219,6 +284,19 @@ def run(args) -> None:
         dist.destroy_process_group()
 
 
+class _NoHostConditioning:
+    """Stand-in for families whose prompt conditioning is not staged through pinned host memory
+    (no end-to-end figure is reported for them)."""
+
+    h2d_bytes = 0
+
+    def reset_transfer_stats(self) -> None:
+        return None
+
+    def drop_device_cache(self) -> None:
+        return None
+
+
 def _attention_impl() -> str:
     from visionrl_b200.ops import attention as A
 
@@ -231,7 +309,14 @@ def main() -> None:
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=2)
     parser.add_argument("--warmup", type=int, default=3)
-    parser.add_argument("--impl", default="native", choices=["native", "torch_baseline", "reference"])
+    parser.add_argument("--impl", default="native",
+                        choices=["native", "torch_baseline", "torch_compile_baseline", "reference"],
+                        help="native: this repository's kernels; torch_baseline: the same models in "
+                             "eager PyTorch (cuBLAS + SDPA + NCCL); torch_compile_baseline: that, with "
+                             "the transformer under torch.compile as the reference's stock path has "
+                             "it; reference: the unmodified reference package")
+    parser.add_argument("--config", default="sd3_5", choices=sorted(CONFIGS),
+                        help="which BASELINE.json workload to run (default: the headline one)")
     parser.add_argument("--collectives", default="fused", choices=["fused", "nccl"])
     parser.add_argument("--sharding", default="full", choices=["full", "optimizer_only"],
                         help="full: block weights, gradients and optimiser state sharded over the "
@@ -239,8 +324,8 @@ def main() -> None:
     parser.add_argument("--no-rollout-replica", dest="rollout_replica", action="store_false",
                         help="rollouts gather the sharded weights like training does instead of "
                              "reading a full per-rank replica kept current by the P2P broadcast")
-    parser.add_argument("--prompts", type=int, default=8)
-    parser.add_argument("--group", type=int, default=8)
+    parser.add_argument("--prompts", type=int, default=None, help="default: the config's own")
+    parser.add_argument("--group", type=int, default=None, help="default: the config's own")
     parser.add_argument("--override", action="append", default=[],
                         help="extra config override, e.g. model.arch.num_layers=4")
     args = parser.parse_args()

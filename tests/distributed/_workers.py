@@ -81,7 +81,12 @@ def sharded_adamw_matches_single(rank, world, port, backend, collectives, out):
 
 
 def ulysses_attention_matches_dense(rank, world, port, backend, use_kernels, out):
+    """Sequence-parallel attention equals dense attention on the full sequence.  Library path:
+    q / k / v in, all-to-all exchanges.  Fused path: the QKV projection output in, exchanges done by
+    the producing kernels' stores; checked with and without gradients, several layers in a row so
+    that the double-buffered exchange slots and their flags wrap around."""
     from visionrl_b200.ops.attention import attention_reference
+    from visionrl_b200.ops.qkv import qkv_prepare_reference
     from visionrl_b200.parallel.mesh import ProcessMesh
     from visionrl_b200.parallel.ulysses import SequenceParallel
 
@@ -97,23 +102,58 @@ def ulysses_attention_matches_dense(rank, world, port, backend, use_kernels, out
     sp = SequenceParallel(mesh, pool)
     torch.manual_seed(1)
     b, h, s, d = 2, 4 * world, 16 * world, 64
-    q, k, v = (torch.randn(b, h, s, d).to(dev, dtype) for _ in range(3))
     sl = slice(rank * s // world, (rank + 1) * s // world)
-    ql, kl, vl = (t[:, :, sl].clone().requires_grad_() for t in (q, k, v))
-    o = sp.attention(ql, kl, vl)
-    w = torch.randn(b, h, s, d, generator=torch.Generator().manual_seed(5)).to(dev, dtype)
-    (o.float() * w[:, :, sl].float()).sum().backward()
-    qf, kf, vf = (t.float().requires_grad_() for t in (q, k, v))
-    of = attention_reference(qf, kf, vf)
-    (of * w.float()).sum().backward()
     tol = 3e-2 if dtype == torch.bfloat16 else 1e-4
-    ok_fwd = torch.allclose(o.float(), of[:, :, sl], atol=tol, rtol=tol)
-    ok_bwd = all(torch.allclose(a.grad.float(), b_.grad[:, :, sl], atol=tol * 4, rtol=tol * 4)
-                 for a, b_ in ((ql, qf), (kl, kf), (vl, vf)))
+    ok_fwd = ok_bwd = True
+    if not use_kernels:
+        q, k, v = (torch.randn(b, h, s, d).to(dev, dtype) for _ in range(3))
+        ql, kl, vl = (t[:, :, sl].clone().requires_grad_() for t in (q, k, v))
+        o = sp.attention(ql, kl, vl)
+        w = torch.randn(b, h, s, d, generator=torch.Generator().manual_seed(5)).to(dev, dtype)
+        (o.float() * w[:, :, sl].float()).sum().backward()
+        qf, kf, vf = (t.float().requires_grad_() for t in (q, k, v))
+        of = attention_reference(qf, kf, vf)
+        (of * w.float()).sum().backward()
+        ok_fwd = torch.allclose(o.float(), of[:, :, sl], atol=tol, rtol=tol)
+        ok_bwd = all(torch.allclose(a.grad.float(), b_.grad[:, :, sl], atol=tol * 4, rtol=tol * 4)
+                     for a, b_ in ((ql, qf), (kl, kf), (vl, vf)))
+    else:
+        gen = torch.Generator().manual_seed(3)
+        qw = (1 + 0.1 * torch.randn(h * d, generator=gen)).to(dev, dtype)
+        kw = (1 + 0.1 * torch.randn(h * d, generator=gen)).to(dev, dtype)
+        ang = torch.rand(s, d // 2, generator=gen) * 6.28
+        cos, sin = torch.cos(ang).to(dev), torch.sin(ang).to(dev)
+        for layer in range(5):                  # > 2 exchanges per kind: slots and flags wrap
+            qkv = torch.randn(b, s, 3 * h * d, generator=gen).to(dev, dtype)
+            wgt = torch.randn(b, s, h * d, generator=gen).to(dev)
+            # dense oracle on the full sequence, fp32
+            qkv_f = qkv.float().requires_grad_()
+            qw_f, kw_f = qw.float().requires_grad_(), kw.float().requires_grad_()
+            qf, kf, vf = qkv_prepare_reference(qkv_f, h, qw_f, kw_f, 1e-6, (cos, sin))
+            of = attention_reference(qf, kf, vf).transpose(1, 2).reshape(b, s, h * d)
+            (of * wgt).sum().backward()
+            with_grad = layer % 2 == 0
+            local = qkv[:, sl].clone().requires_grad_(with_grad)
+            qw_l, kw_l = qw.clone().requires_grad_(with_grad), kw.clone().requires_grad_(with_grad)
+            assert sp.can_fuse(local, h)
+            with torch.set_grad_enabled(with_grad):
+                o = sp.fused_attention(local, h, qw_l, kw_l, (cos[sl], sin[sl]))
+            ok_fwd = ok_fwd and torch.allclose(o.float(), of[:, sl].detach(), atol=tol, rtol=tol)
+            if with_grad:
+                (o.float() * wgt[:, sl]).sum().backward()
+                scale = max(1.0, qkv_f.grad.abs().max().item())
+                ok_bwd = ok_bwd and (local.grad.float() - qkv_f.grad[:, sl]).abs().max().item() <= 4 * tol * scale
+                # norm-weight gradients are partial sums over this rank's tokens
+                gq = qw_l.grad.float().clone()
+                dist.all_reduce(gq)
+                ok_bwd = ok_bwd and torch.allclose(gq, qw_f.grad, atol=0.15, rtol=0.1)
+        torch.cuda.synchronize()
+        pool.check("fused ulysses test")
     flags = torch.tensor([float(ok_fwd), float(ok_bwd)], device=dev)
     dist.all_reduce(flags, op=dist.ReduceOp.MIN)
     if rank == 0:
-        out.put({"fwd": bool(flags[0]), "bwd": bool(flags[1]), "launches": sp.kernel_launches})
+        out.put({"fwd": bool(flags[0]), "bwd": bool(flags[1]), "launches": sp.kernel_launches,
+                 "fused_layers": sp.fused_layers})
     dist.barrier()
     dist.destroy_process_group()
 

@@ -91,6 +91,7 @@ def test_ulysses_attention_gpu(use_kernels):
     res = _run(_workers.ulysses_attention_matches_dense, world, "nccl", use_kernels)
     assert res["fwd"] and res["bwd"]
     assert (res["launches"] > 0) == use_kernels
+    assert res["fused_layers"] == (5 if use_kernels else 0)
 
 
 @pytest.mark.gpu

@@ -114,3 +114,29 @@ def test_remote_reward_payload_and_score(monkeypatch):
     monkeypatch.setattr(reward, "_post", fake_post)
     assert _run(reward.score(rollout)) == pytest.approx(0.4)
     assert _run(reward.score_batch([rollout, rollout])) == pytest.approx([0.4, 0.6])
+
+
+def test_aesthetic_head_weights_are_resolved_from_path_env_or_assets(tmp_path, monkeypatch):
+    import torch
+
+    from visionrl_b200.rewards.aesthetic import AestheticMLP, AestheticReward, resolve_mlp_weights
+
+    monkeypatch.delenv("VRL_AESTHETIC_MLP", raising=False)
+    assert resolve_mlp_weights(None) is None                      # nothing shipped: stand-in is used
+    with pytest.raises(FileNotFoundError):
+        resolve_mlp_weights(str(tmp_path / "missing.pth"))
+    head = AestheticMLP(768)
+    with torch.no_grad():
+        for p in head.parameters():
+            p.fill_(0.01)
+    path = tmp_path / "head.pth"
+    torch.save(head.state_dict(), path)
+    assert resolve_mlp_weights(str(path)) == path
+    monkeypatch.setenv("VRL_AESTHETIC_MLP", str(path))
+    assert resolve_mlp_weights(None) == path
+    reward = AestheticReward(device="cpu", model_name="vit_tiny", random_init=False)
+    try:
+        reward._ensure_loaded()
+    except Exception:      # noqa: BLE001 - the image tower needs weights that are not available offline
+        return
+    assert torch.allclose(reward._mlp.layers[0].weight, torch.full_like(reward._mlp.layers[0].weight, 0.01))

@@ -59,7 +59,23 @@ struct Params {
   int sq, skv;
   float scale_log2;       // softmax scale times log2(e)
   int causal;             // query row r attends keys 0 .. r + (skv - sq) (lazy-rescale kernel only)
+  // Sequence-parallel output (sp_world > 1): this rank computed `heads` local heads over the FULL
+  // sequence; query row r belongs to rank r / sp_sloc, whose [B, sp_sloc, sp_heads_total, D] buffer
+  // (peer-mapped address out_peer[r / sp_sloc]) receives it at head offset sp_head0 — the
+  // heads -> sequence exchange of Ulysses happens in the epilogue's stores.
+  __nv_bfloat16* out_peer[16];
+  int sp_world, sp_sloc, sp_heads_total, sp_head0;
 };
+
+// Address of the D output values of (batch bi, query row, local head hi).
+template <int D>
+__device__ __forceinline__ __nv_bfloat16* out_row(const Params& p, int bi, int row, int hi) {
+  if (p.sp_world > 1) {
+    const int owner = row / p.sp_sloc, local = row - owner * p.sp_sloc;
+    return p.out_peer[owner] + (((int64_t)bi * p.sp_sloc + local) * p.sp_heads_total + p.sp_head0 + hi) * D;
+  }
+  return p.out + (((int64_t)bi * p.sq + row) * p.heads + hi) * D;
+}
 
 // Publish `mine` in slot `me` with tag `tag`, then read the partner's value once its slot carries the
 // same tag.  Bounded: returns false when the partner does not show up.
@@ -331,7 +347,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 #pragma unroll
       for (int i = 0; i < DH; ++i) o[i] = (o[i] + __uint_as_float(q[i])) * inv;
       if (ok && row < p.sq) {
-        __nv_bfloat16* dst = p.out + (((int64_t)bi * p.sq + row) * p.heads + hi) * D + half * DH;
+        __nv_bfloat16* dst = out_row<D>(p, bi, row, hi) + half * DH;
 #pragma unroll
         for (int g = 0; g < DH / 8; ++g) *reinterpret_cast<bf16x8*>(dst + g * 8) = pack8(&o[g * 8]);
         if (half == 0) p.lse[(int64_t)bh * p.sq + row] = (m + log2f(l)) * 0.6931471805599453f;
@@ -609,7 +625,7 @@ flash_fwd_small_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         for (int i = 0; i < 32; ++i) o[c * 32 + i] = (o[c * 32 + i] + __uint_as_float(r[i])) * inv;
       }
       if (row < p.sq) {
-        __nv_bfloat16* dst = p.out + (((int64_t)bi * p.sq + row) * p.heads + hi) * D;
+        __nv_bfloat16* dst = out_row<D>(p, bi, row, hi);
 #pragma unroll
         for (int g = 0; g < D / 8; ++g) *reinterpret_cast<bf16x8*>(dst + g * 8) = pack8(&o[g * 8]);
         p.lse[(int64_t)bh * p.sq + row] = (m + log2f(l)) * 0.6931471805599453f;
@@ -917,7 +933,7 @@ flash_fwd_lazy_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         for (int i = 0; i < 32; ++i) o[c * 32 + i] = __uint_as_float(q[i]) * inv;
       }
       if (row < p.sq) {
-        __nv_bfloat16* dst = p.out + (((int64_t)bi * p.sq + row) * p.heads + hi) * D;
+        __nv_bfloat16* dst = out_row<D>(p, bi, row, hi);
 #pragma unroll
         for (int g = 0; g < D / 8; ++g) *reinterpret_cast<bf16x8*>(dst + g * 8) = pack8(&o[g * 8]);
         p.lse[(int64_t)bh * p.sq + row] = (m + log2f(l)) * 0.6931471805599453f;
@@ -980,8 +996,33 @@ static void launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorM
 
 // `causal`: query row r attends keys 0 .. r + (Skv - Sq) (needs Sq <= Skv).  `variant`: 0 picks the
 // default kernel for the shape, 1 forces the register-accumulating kernels, 2 the lazy-rescale one.
+static std::vector<torch::Tensor> flash_attn_fwd_impl(torch::Tensor q, torch::Tensor k, torch::Tensor v, double scale,
+                                                      bool causal, int64_t variant, const torch::Tensor* out_peers,
+                                                      int64_t sp_world, int64_t sp_rank, int64_t heads_total);
+
 std::vector<torch::Tensor> flash_attn_fwd(torch::Tensor q, torch::Tensor k, torch::Tensor v, double scale,
                                           bool causal, int64_t variant) {
+  return flash_attn_fwd_impl(q, k, v, scale, causal, variant, nullptr, 1, 0, 0);
+}
+
+// Sequence-parallel form: q, k, v hold this rank's `H / world` heads over the full sequence; the
+// output rows are stored into the sequence owners' [B, S / world, heads_total, D] buffers
+// (`out_peers`: CPU int64 table of their peer-mapped addresses).  Returns {lse}.
+std::vector<torch::Tensor> flash_attn_fwd_peers(torch::Tensor q, torch::Tensor k, torch::Tensor v, double scale,
+                                                torch::Tensor out_peers, int64_t world, int64_t rank,
+                                                int64_t heads_total) {
+  TORCH_CHECK(world >= 2 && world <= 16 && rank >= 0 && rank < world, "flash_attn_fwd_peers: 2..16 ranks");
+  TORCH_CHECK(out_peers.device().is_cpu() && out_peers.scalar_type() == torch::kInt64 && out_peers.numel() >= world,
+              "out_peers: CPU int64 tensor with one address per rank");
+  TORCH_CHECK(q.dim() == 4 && q.size(2) % world == 0 && q.size(1) * world == heads_total,
+              "flash_attn_fwd_peers: sequence must divide by the ranks and heads_total = local heads * world");
+  auto outs = flash_attn_fwd_impl(q, k, v, scale, false, 0, &out_peers, world, rank, heads_total);
+  return {outs[1]};
+}
+
+static std::vector<torch::Tensor> flash_attn_fwd_impl(torch::Tensor q, torch::Tensor k, torch::Tensor v, double scale,
+                                                      bool causal, int64_t variant, const torch::Tensor* out_peers,
+                                                      int64_t sp_world, int64_t sp_rank, int64_t heads_total) {
   using namespace attn;
   TORCH_CHECK(q.is_cuda() && q.dim() == 4 && k.dim() == 4 && v.dim() == 4, "flash_attn_fwd: [B, H, S, D]");
   TORCH_CHECK(q.scalar_type() == torch::kBFloat16 && k.scalar_type() == torch::kBFloat16 &&
@@ -997,7 +1038,9 @@ std::vector<torch::Tensor> flash_attn_fwd(torch::Tensor q, torch::Tensor k, torc
   const c10::cuda::CUDAGuard guard(q.device());
   bind_context();
   // token-major output, returned as a [B, H, S, D] view: merging heads afterwards is free
-  auto out_tm = torch::empty({b, sq, h, d}, q.options());
+  // (the sequence-parallel form writes into the peers' buffers instead and allocates nothing here)
+  auto out_tm = out_peers != nullptr ? torch::empty({0, 0, h, d}, q.options())
+                                     : torch::empty({b, sq, h, d}, q.options());
   auto out = out_tm.transpose(1, 2);
   auto lse = torch::empty({b, h, sq}, q.options().dtype(torch::kFloat32));
   if (b * h == 0 || sq == 0) return {out, lse};
@@ -1017,6 +1060,17 @@ std::vector<torch::Tensor> flash_attn_fwd(torch::Tensor q, torch::Tensor k, torc
   p.skv = (int)skv;
   p.scale_log2 = (float)(scale * 1.4426950408889634);
   p.causal = causal ? 1 : 0;
+  if (out_peers != nullptr) {
+    p.sp_world = (int)sp_world;
+    p.sp_sloc = (int)(sq / sp_world);
+    p.sp_heads_total = (int)heads_total;
+    p.sp_head0 = (int)(sp_rank * h);
+    for (int r = 0; r < sp_world; ++r) {
+      const int64_t addr = out_peers->data_ptr<int64_t>()[r];
+      TORCH_CHECK(addr != 0 && addr % 16 == 0, "flash_attn_fwd_peers: output addresses must be 16-byte aligned");
+      p.out_peer[r] = reinterpret_cast<__nv_bfloat16*>(addr);
+    }
+  }
   const int q_tiles = (int)((sq + kTile - 1) / kTile);
   TORCH_CHECK(b * h <= 65535, "flash_attn_fwd: batch * heads exceeds the grid limit");
   auto stream = at::cuda::getCurrentCUDAStream();

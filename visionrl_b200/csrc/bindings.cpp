@@ -44,11 +44,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("rmsnorm_bwd", &vrl::rmsnorm_bwd);
   m.def("qkv_prepare_fwd", &vrl::qkv_prepare_fwd);
   m.def("qkv_prepare_bwd", &vrl::qkv_prepare_bwd);
+  m.def("qkv_prepare_fwd_peers", &vrl::qkv_prepare_fwd_peers);
   m.def("rs_sum_slice", &vrl::rs_sum_slice);
   m.def("adamw_slice_broadcast", &vrl::adamw_slice_broadcast);
   m.def("p2p_broadcast_versioned", &vrl::p2p_broadcast_versioned);
   m.def("wait_flag", &vrl::wait_flag);
   m.def("ulysses_scatter", &vrl::ulysses_scatter);
+  m.def("ulysses_exchange_tm", &vrl::ulysses_exchange_tm);
   m.def("flag_signal", &vrl::flag_signal);
   m.def("flag_wait", &vrl::flag_wait);
   m.def("flag_barrier", &vrl::flag_barrier);
@@ -73,6 +75,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("groupnorm_nhwc", &vrl::groupnorm_nhwc);
   m.def("flash_attn_fwd", &vrl::flash_attn_fwd, pybind11::arg("q"), pybind11::arg("k"), pybind11::arg("v"),
         pybind11::arg("scale"), pybind11::arg("causal") = false, pybind11::arg("variant") = 0);
+  m.def("flash_attn_fwd_peers", &vrl::flash_attn_fwd_peers);
   m.def("flash_attn_last_status", &vrl::flash_attn_last_status);
   m.def("flash_attn_bwd", &vrl::flash_attn_bwd, pybind11::arg("dout"), pybind11::arg("q"), pybind11::arg("k"),
         pybind11::arg("v"), pybind11::arg("out"), pybind11::arg("lse"), pybind11::arg("scale"),

@@ -602,6 +602,53 @@ ulysses_to_seq_kernel(const uint4* __restrict__ src, PeerPtrs dst, int batch, in
   }
 }
 
+// Token-major forms of the same exchange (what the backward pass of fused sequence-parallel attention
+// needs: gradients arrive and leave token-major).  A "chunk" is one rank's heads of one token,
+// C = (H / P) * D contiguous elements.
+//   to_heads : src [B, S_loc, P, C]  -> peer g's dst [B, S, C]          at row rank * S_loc + s
+//   to_seq   : src [B, S, C]         -> peer (s / S_loc)'s dst [B, S_loc, P, C] at chunk `rank`
+__global__ void __launch_bounds__(256)
+ulysses_tm_kernel(const uint4* __restrict__ src, PeerPtrs dst, int batch, int s_loc, int world, int rank,
+                  int cvec, int to_heads) {
+  const int64_t s_full = (int64_t)s_loc * world;
+  const int64_t total = (int64_t)batch * s_full * cvec;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int v = (int)(i % cvec);
+    int64_t t = i / cvec;
+    if (to_heads) {
+      const int g = (int)(t % world); t /= world;
+      const int s = (int)(t % s_loc);
+      const int64_t b = t / s_loc;
+      const int64_t o = ((b * s_full + (int64_t)rank * s_loc + s) * cvec) + v;
+      reinterpret_cast<uint4*>(dst.p[g])[o] = src[i];
+    } else {
+      const int64_t s = t % s_full;
+      const int64_t b = t / s_full;
+      const int peer = (int)(s / s_loc);
+      const int64_t sl = s - (int64_t)peer * s_loc;
+      const int64_t o = (((b * s_loc + sl) * world + rank) * cvec) + v;
+      reinterpret_cast<uint4*>(dst.p[peer])[o] = src[i];
+    }
+  }
+}
+
+void ulysses_exchange_tm(torch::Tensor src, torch::Tensor dst_peers, int64_t batch, int64_t s_loc,
+                         int64_t chunk_elems, int64_t world, int64_t rank, bool to_heads) {
+  TORCH_CHECK(src.is_cuda() && src.is_contiguous() && src.element_size() == 2 &&
+              reinterpret_cast<uintptr_t>(src.data_ptr()) % 16 == 0, "ulysses_exchange_tm: contiguous 16-bit source");
+  TORCH_CHECK(chunk_elems % 8 == 0 && world >= 1 && world <= kMaxPeers && rank >= 0 && rank < world);
+  TORCH_CHECK(src.numel() == batch * s_loc * world * chunk_elems, "ulysses_exchange_tm: source size mismatch");
+  const c10::cuda::CUDAGuard guard(src.device());
+  const PeerPtrs dp = load_peers(dst_peers, (int)world);
+  const int64_t total = src.numel() / 8;
+  const int blocks = (int)std::max<int64_t>(1, std::min<int64_t>((total + 255) / 256, 148 * 8));
+  ulysses_tm_kernel<<<blocks, 256, 0, at::cuda::getCurrentCUDAStream()>>>(
+      reinterpret_cast<const uint4*>(src.data_ptr()), dp, (int)batch, (int)s_loc, (int)world, (int)rank,
+      (int)(chunk_elems / 8), to_heads ? 1 : 0);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
 void ulysses_scatter(torch::Tensor src, torch::Tensor dst_peers, int64_t batch, int64_t heads,
                      int64_t s_loc, int64_t head_dim, int64_t world, int64_t rank, bool to_heads) {
   TORCH_CHECK(src.is_cuda() && src.is_contiguous() && src.element_size() == 2);

@@ -735,13 +735,24 @@ __device__ __forceinline__ float group_sum(float v, int lanes) {
   return v;
 }
 
+// Destinations of the sequence-parallel form: head group g = h / (heads / world) of every token goes
+// to rank g's [B, seq_total, heads / world, Dh] buffer (peer-mapped addresses), at this rank's
+// sequence offset.  world <= 1 means "local destinations" and the table is not read.
+struct QkvPeers {
+  bf16* q[16];
+  bf16* k[16];
+  bf16* v[16];
+  int world;
+};
+
 template <int kQkvMaxVec>
 __global__ void __launch_bounds__(kNormThreads)
 qkv_prepare_fwd_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ qw,
                        const bf16* __restrict__ kw, const float* __restrict__ cosT,
                        const float* __restrict__ sinT, bf16* __restrict__ q, bf16* __restrict__ k,
                        bf16* __restrict__ v, float* __restrict__ rstd_o, int seq, int heads,
-                       int dh, int mode, float eps, int seq_total, int seq_offset) {
+                       int dh, int mode, float eps, int seq_total, int seq_offset,
+                       const QkvPeers peers) {
   __shared__ float red[32];
   const int64_t tok = blockIdx.x;
   const int b = (int)(tok / seq), s = (int)(tok % seq);
@@ -807,10 +818,19 @@ qkv_prepare_fwd_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ qw
         o[2 * p + 1] = x0 * sn[p] + x1 * c[p];
       }
     }
-    bf16* dst = which == 0 ? q : (which == 1 ? k : v);
-    // token-major destination [B, seq_total, H, Dh]: one token's heads are contiguous
-    *reinterpret_cast<bf16x8*>(dst + (((int64_t)b * seq_total + seq_offset + s) * heads + h) * dh + j8 * 8) =
-        pack8(o);
+    if (peers.world > 1) {
+      // the head <-> sequence exchange of sequence parallelism happens in this store: the head's
+      // owner receives the token at this rank's place in the full sequence, over NVLink
+      const int hp = heads / peers.world, g = h / hp, hl = h - g * hp;
+      bf16* dst = which == 0 ? peers.q[g] : (which == 1 ? peers.k[g] : peers.v[g]);
+      *reinterpret_cast<bf16x8*>(dst + (((int64_t)b * seq_total + seq_offset + s) * hp + hl) * dh + j8 * 8) =
+          pack8(o);
+    } else {
+      bf16* dst = which == 0 ? q : (which == 1 ? k : v);
+      // token-major destination [B, seq_total, H, Dh]: one token's heads are contiguous
+      *reinterpret_cast<bf16x8*>(dst + (((int64_t)b * seq_total + seq_offset + s) * heads + h) * dh + j8 * 8) =
+          pack8(o);
+    }
   }
 }
 
@@ -880,9 +900,71 @@ std::vector<torch::Tensor> qkv_prepare_fwd(torch::Tensor qkv, c10::optional<torc
       cos.has_value() ? cosc.data_ptr<float>() : nullptr,
       cos.has_value() ? sinc.data_ptr<float>() : nullptr, reinterpret_cast<bf16*>(q.data_ptr()),
       reinterpret_cast<bf16*>(k.data_ptr()), reinterpret_cast<bf16*>(v.data_ptr()),
-      rstd.data_ptr<float>(), s, (int)heads, dh, mode, (float)eps, (int)seq_total, (int)seq_offset));
+      rstd.data_ptr<float>(), s, (int)heads, dh, mode, (float)eps, (int)seq_total, (int)seq_offset,
+      QkvPeers{}));
   C10_CUDA_KERNEL_LAUNCH_CHECK();
   return {q, k, v, rstd};
+}
+
+// Sequence-parallel form: q / k / v of this rank's tokens are stored straight into the head owners'
+// [B, seq_total, heads / world, Dh] buffers.  `peers_*` are CPU int64 tables of the peer-mapped base
+// addresses of those buffers (one per rank).  Returns the norm statistics the backward pass needs.
+torch::Tensor qkv_prepare_fwd_peers(torch::Tensor qkv, c10::optional<torch::Tensor> qw,
+                                    c10::optional<torch::Tensor> kw, c10::optional<torch::Tensor> cos,
+                                    c10::optional<torch::Tensor> sin, int64_t heads, double eps,
+                                    torch::Tensor peers_q, torch::Tensor peers_k, torch::Tensor peers_v,
+                                    int64_t world, int64_t seq_total, int64_t seq_offset) {
+  TORCH_CHECK(qkv.is_cuda() && qkv.dim() == 3 && qkv.scalar_type() == torch::kBFloat16 && qkv.is_contiguous());
+  TORCH_CHECK(qw.has_value() == kw.has_value() && cos.has_value() == sin.has_value());
+  VRL_CHECK_OPERAND(qw, qkv);
+  VRL_CHECK_OPERAND(kw, qkv);
+  VRL_CHECK_OPERAND(cos, qkv);
+  VRL_CHECK_OPERAND(sin, qkv);
+  TORCH_CHECK(world >= 2 && world <= 16 && heads % world == 0, "qkv_prepare_fwd_peers: heads must divide by 2..16 ranks");
+  const c10::cuda::CUDAGuard guard(qkv.device());
+  const int b = (int)qkv.size(0), s = (int)qkv.size(1);
+  const int dmodel = (int)(qkv.size(2) / 3), dh = dmodel / (int)heads;
+  TORCH_CHECK(dh % 8 == 0 && kNormThreads % (dh / 8) == 0 && (dh / 8) <= 32, "unsupported head dim");
+  TORCH_CHECK(3 * dmodel / 8 <= kQkvVecLimit * kNormThreads, "model width too large for qkv_prepare");
+  TORCH_CHECK(seq_offset >= 0 && seq_offset + s <= seq_total, "qkv_prepare_fwd_peers: sequence window out of range");
+  int mode = 0;
+  torch::Tensor qwc, kwc;
+  if (qw.has_value()) {
+    qwc = qw->to(torch::kBFloat16).contiguous();
+    kwc = kw->to(torch::kBFloat16).contiguous();
+    mode = (qwc.numel() == dh && heads > 1) || (heads == 1) ? 1 : 2;
+    TORCH_CHECK(qwc.numel() == (mode == 1 ? dh : dmodel));
+  }
+  torch::Tensor cosc, sinc;
+  if (cos.has_value()) {
+    cosc = cos->to(torch::kFloat32).contiguous();
+    sinc = sin->to(torch::kFloat32).contiguous();
+    TORCH_CHECK(cosc.size(0) == s && cosc.size(1) == dh / 2);
+  }
+  QkvPeers peers{};
+  peers.world = (int)world;
+  const torch::Tensor* tables[3] = {&peers_q, &peers_k, &peers_v};
+  bf16** slots[3] = {peers.q, peers.k, peers.v};
+  for (int t = 0; t < 3; ++t) {
+    TORCH_CHECK(tables[t]->device().is_cpu() && tables[t]->scalar_type() == torch::kInt64 &&
+                tables[t]->numel() >= world, "peer tables: CPU int64 tensors with one address per rank");
+    for (int r = 0; r < world; ++r) {
+      const int64_t addr = tables[t]->data_ptr<int64_t>()[r];
+      TORCH_CHECK(addr != 0 && addr % 16 == 0, "peer destinations must be 16-byte aligned");
+      slots[t][r] = reinterpret_cast<bf16*>(addr);
+    }
+  }
+  auto rstd = torch::empty({(int64_t)b * s * 2 * (mode == 1 ? heads : 1)}, qkv.options().dtype(torch::kFloat32));
+  auto stream = at::cuda::getCurrentCUDAStream();
+  VRL_DISPATCH_QKV(3 * dmodel / 8, qkv_prepare_fwd_kernel<T><<<b * s, kNormThreads, 0, stream>>>(
+      reinterpret_cast<const bf16*>(qkv.data_ptr()),
+      mode ? reinterpret_cast<const bf16*>(qwc.data_ptr()) : nullptr,
+      mode ? reinterpret_cast<const bf16*>(kwc.data_ptr()) : nullptr,
+      cos.has_value() ? cosc.data_ptr<float>() : nullptr,
+      cos.has_value() ? sinc.data_ptr<float>() : nullptr, nullptr, nullptr, nullptr,
+      rstd.data_ptr<float>(), s, (int)heads, dh, mode, (float)eps, (int)seq_total, (int)seq_offset, peers));
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return rstd;
 }
 
 constexpr int kQkvBwdTokens = 16;

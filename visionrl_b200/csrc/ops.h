@@ -76,6 +76,11 @@ std::vector<torch::Tensor> qkv_prepare_fwd(torch::Tensor qkv, c10::optional<torc
                                            double eps, c10::optional<torch::Tensor> dst_q,
                                            c10::optional<torch::Tensor> dst_k,
                                            c10::optional<torch::Tensor> dst_v, int64_t seq_offset);
+torch::Tensor qkv_prepare_fwd_peers(torch::Tensor qkv, c10::optional<torch::Tensor> qw,
+                                    c10::optional<torch::Tensor> kw, c10::optional<torch::Tensor> cos,
+                                    c10::optional<torch::Tensor> sin, int64_t heads, double eps,
+                                    torch::Tensor peers_q, torch::Tensor peers_k, torch::Tensor peers_v,
+                                    int64_t world, int64_t seq_total, int64_t seq_offset);
 std::vector<torch::Tensor> qkv_prepare_bwd(torch::Tensor gq, torch::Tensor gk, torch::Tensor gv,
                                            torch::Tensor qkv, c10::optional<torch::Tensor> qw,
                                            c10::optional<torch::Tensor> kw,
@@ -107,6 +112,8 @@ void p2p_gather_table(torch::Tensor shard_peers, torch::Tensor dst, torch::Tenso
                       int64_t rank, int64_t max_segment);
 void p2p_gather_rows(torch::Tensor shard_peers, torch::Tensor full, int64_t shard_elems, int64_t world,
                      int64_t rank);
+void ulysses_exchange_tm(torch::Tensor src, torch::Tensor dst_peers, int64_t batch, int64_t s_loc,
+                         int64_t chunk_elems, int64_t world, int64_t rank, bool to_heads);
 void ulysses_scatter(torch::Tensor src, torch::Tensor dst_peers, int64_t batch, int64_t heads,
                      int64_t s_loc, int64_t head_dim, int64_t world, int64_t rank, bool to_heads);
 
@@ -145,6 +152,9 @@ torch::Tensor groupnorm_nhwc(torch::Tensor x, torch::Tensor weight, torch::Tenso
 // attention_sm100.cu
 std::vector<torch::Tensor> flash_attn_fwd(torch::Tensor q, torch::Tensor k, torch::Tensor v, double scale,
                                           bool causal, int64_t variant);
+std::vector<torch::Tensor> flash_attn_fwd_peers(torch::Tensor q, torch::Tensor k, torch::Tensor v, double scale,
+                                                torch::Tensor out_peers, int64_t world, int64_t rank,
+                                                int64_t heads_total);
 int64_t flash_attn_last_status();
 
 // attention_bwd_sm100.cu

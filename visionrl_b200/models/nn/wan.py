@@ -79,7 +79,13 @@ class WanSelfAttention(nn.Module):
         self.out.lora_aliases = ("to_out.0",)
 
     def forward(self, x, rope, gate, residual, sp=None):
-        q, k, v = qkv_prepare(self.qkv(x), self.heads, self.q_norm, self.k_norm, rope=rope)
+        qkv = self.qkv(x)
+        if sp is not None and sp.can_fuse(qkv, self.heads):
+            # head split + QK norm + RoPE store straight into the head owners' buffers, attention
+            # stores straight into the token owners' buffer: the output projection reads a view
+            o = sp.fused_attention(qkv, self.heads, self.q_norm, self.k_norm, rope)
+            return self.out(o, gate=gate, residual=residual)
+        q, k, v = qkv_prepare(qkv, self.heads, self.q_norm, self.k_norm, rope=rope)
         if sp is not None:
             o = sp.attention(q, k, v)
         else:

@@ -1,8 +1,20 @@
 """Aesthetic predictor: L2-normalised ViT-L/14 image features → MLP
 ``768→1024→128→64→16→1``; videos average the frames at 25/50/75 %
-(reference: ``vrl/rewards/aesthetic.py:15-121``)."""
+(reference: ``vrl/rewards/aesthetic.py:15-121``).
+
+The MLP head is the public LAION "improved aesthetic predictor" (``sac+logos+ava1-l14-linearMSE.pth``,
+3.7 MB, keys ``layers.{0,2,4,6,7}.{weight,bias}``).  The file is a third-party trained artefact and
+is not redistributed with this package; it is looked up, in this order, at ``mlp_path``
+(``reward.kwargs.aesthetic.mlp_path``), at ``$VRL_AESTHETIC_MLP`` and at
+``visionrl_b200/rewards/assets/sac+logos+ava1-l14-linearMSE.pth`` (drop the file there to use it).
+Without it — and always under ``random_init`` — a fixed-seed stand-in of the same shape is used,
+which keeps the reward a deterministic function of the image for tests and benchmarks.
+"""
 
 from __future__ import annotations
+
+import os
+from pathlib import Path
 
 import torch
 from torch import nn
@@ -23,6 +35,21 @@ class AestheticMLP(nn.Module):
         return self.layers(x)
 
 
+ASSET_NAME = "sac+logos+ava1-l14-linearMSE.pth"
+
+
+def resolve_mlp_weights(explicit: str | None = None) -> Path | None:
+    """Path of the aesthetic head's weights, or ``None`` when no copy is available."""
+    candidates = [explicit, os.environ.get("VRL_AESTHETIC_MLP"),
+                  str(Path(__file__).with_name("assets") / ASSET_NAME)]
+    for c in candidates:
+        if c and Path(c).is_file():
+            return Path(c)
+    if explicit:
+        raise FileNotFoundError(f"aesthetic MLP weights not found at {explicit}")
+    return None
+
+
 class AestheticReward(RewardFunction):
     frame_fractions = (0.25, 0.5, 0.75)
 
@@ -39,8 +66,9 @@ class AestheticReward(RewardFunction):
         self._tower = build_image_tower(self.model_name, self._device, random_init=self.random_init)
         width = self._tower.proj.out_features
         mlp = AestheticMLP(width)
-        if self.mlp_path:
-            mlp.load_state_dict(torch.load(self.mlp_path, map_location="cpu"))
+        weights = None if self.random_init else resolve_mlp_weights(self.mlp_path)
+        if weights is not None:
+            mlp.load_state_dict(torch.load(weights, map_location="cpu"))
         else:
             gen = torch.Generator().manual_seed(1234)
             with torch.no_grad():

@@ -14,6 +14,7 @@ sharded runtime, and only rank 0 writes logs, CSV rows and checkpoints.
 
 from __future__ import annotations
 
+import contextlib
 import logging
 import os
 from dataclasses import dataclass, field
@@ -218,6 +219,23 @@ def shutdown_distributed(trainer: Any | None = None) -> None:
         dist.destroy_process_group()
 
 
+_CAPTURE: list = [None]
+
+
+@contextlib.contextmanager
+def capture_trainer():
+    """While active, a recipe stops after it has built its trainer and hands the pieces back
+    (``box["trainer"]``, ``box["examples"]``, ``box["parts"]``, ``box["ctx"]``) instead of running
+    its epoch loop.  Benchmarks and smoke tests use this to drive ``trainer.step`` of ANY family's
+    recipe themselves, through exactly the objects a training run would use."""
+    box: dict[str, Any] = {}
+    _CAPTURE[0] = box
+    try:
+        yield box
+    finally:
+        _CAPTURE[0] = None
+
+
 async def run_online_recipe(ctx: RunContext, parts: RecipeParts, reward_fn: Any,
                             reward_names: list[str], *,
                             on_epoch_end: Callable[[int, Any, Any], Any] | None = None) -> Any:
@@ -230,6 +248,10 @@ async def run_online_recipe(ctx: RunContext, parts: RecipeParts, reward_fn: Any,
     if not manifest.startswith("synthetic:") and not Path(manifest).exists():
         raise FileNotFoundError(f"Manifest not found: {manifest}")
     examples = load_prompt_manifest(manifest)
+    if _CAPTURE[0] is not None:
+        _CAPTURE[0].update(trainer=trainer, collector=collector, examples=examples, parts=parts,
+                           ctx=ctx, reward_fn=reward_fn)
+        return _CAPTURE[0]
     start = ctx.resume.next_epoch if ctx.resume is not None else parts.first_epoch
     end = tc.total_epochs + parts.first_epoch
     if start > end:
