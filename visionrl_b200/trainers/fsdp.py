@@ -1,10 +1,12 @@
 """Sharded-training utilities under the reference's ``vrl.trainers.fsdp`` names
 (``vrl/trainers/fsdp.py:35-183``).
 
-``fsdp_wrapper`` attaches the native sharded runtime of
-:mod:`visionrl_b200.parallel.sharded` (flat bf16 parameters, fp32 master weights and
-Adam moments sharded over the ranks, gradient reduce-scatter fused with the optimiser
-step) instead of wrapping modules in ``torch.distributed.fsdp``.
+``fsdp_wrapper`` attaches the native sharded runtime instead of wrapping modules in
+``torch.distributed.fsdp``: with ``FULL_SHARD`` / ``HYBRID_SHARD`` the transformer-block weights,
+their gradients and optimiser state are sharded over the shard group
+(:mod:`visionrl_b200.parallel.fsdp`: all-gather inside the consuming GEMM, bucketed
+reduce-scatter during backward), with ``SHARD_GRAD_OP`` only the optimiser state of flat bf16
+parameters is (:mod:`visionrl_b200.parallel.sharded`), ``NO_SHARD`` replicates everything.
 ``save_fsdp_checkpoint`` writes rank 0's full state dict to
 ``checkpoint-<step>/model.safetensors`` and then barriers.
 """
@@ -46,7 +48,9 @@ def fsdp_wrapper(model: nn.Module, config: FSDPConfig | None = None, *,
     from visionrl_b200.parallel.sharded import ShardedGradSync
 
     config = config or FSDPConfig()
-    mesh = mesh or ProcessMesh.build()
+    if mesh is None:
+        hybrid = config.sharding_strategy == "HYBRID_SHARD" and config.num_replicate > 1
+        mesh = ProcessMesh.build(replicate=config.num_replicate if hybrid else 1)
     if config.use_activation_checkpointing:
         enable = getattr(model, "enable_gradient_checkpointing", None)
         inner = getattr(model, "transformer", None)
@@ -55,7 +59,16 @@ def fsdp_wrapper(model: nn.Module, config: FSDPConfig | None = None, *,
         elif inner is not None and callable(getattr(inner, "enable_gradient_checkpointing", None)):
             inner.enable_gradient_checkpointing(True)
     shard = config.sharding_strategy != "NO_SHARD"
-    model.sharded_runtime = ShardedGradSync(mesh, shard_optimizer=shard, collectives=collectives)
+    param_runtime = None
+    if config.sharding_strategy in ("FULL_SHARD", "HYBRID_SHARD") and mesh.world_size > 1:
+        from visionrl_b200.parallel.fsdp import shard_model
+
+        first = next(model.parameters(), None)
+        device = first.device if first is not None else torch.device("cpu")
+        param_runtime = shard_model(model, mesh, device, collectives=collectives)
+        model.param_runtime = param_runtime
+    model.sharded_runtime = ShardedGradSync(mesh, shard_optimizer=shard, collectives=collectives,
+                                            param_runtime=param_runtime)
     return model
 
 
