@@ -242,6 +242,19 @@ def run(args) -> None:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    phases = None
+    if args.phases:
+        # one more step, outside both timed regions, with a device synchronisation around every
+        # phase: where the step's time goes (the synchronisations make it slower than a timed step)
+        was = trainer.config.profile
+        trainer.config.profile = True
+        try:
+            barrier()
+            pm = loop.run_until_complete(one_step())
+        finally:
+            trainer.config.profile = was
+        phases = {k: round(max_over_ranks(float(v)) * 1e3, 1) for k, v in sorted(pm.phase_times.items())}
+
     dev_ms = max_over_ranks(dev_ms)
     e2e_s = max_over_ranks(max(e2e_ms / 1e3, e2e_wall))
     launches = int(max_over_ranks(float(launches)))
@@ -275,6 +288,7 @@ def run(args) -> None:
                           "gather_ahead_launches": runtime.prefetches, "buckets_reduced": runtime.buckets_reduced,
                           "weight_broadcasts": runtime.broadcasts}
                          if sharded else None),
+            "phases_ms": phases,
             "last_metrics": {"loss": metrics.loss, "reward_mean": metrics.reward_mean,
                              "grad_norm": metrics.grad_norm},
         }
@@ -324,6 +338,9 @@ def main() -> None:
     parser.add_argument("--no-rollout-replica", dest="rollout_replica", action="store_false",
                         help="rollouts gather the sharded weights like training does instead of "
                              "reading a full per-rank replica kept current by the P2P broadcast")
+    parser.add_argument("--phases", action="store_true",
+                        help="after the timed regions, run one synchronised step and report the time "
+                             "of each phase (collect, evaluate, backward, optimiser, ...)")
     parser.add_argument("--prompts", type=int, default=None, help="default: the config's own")
     parser.add_argument("--group", type=int, default=None, help="default: the config's own")
     parser.add_argument("--override", action="append", default=[],

@@ -354,18 +354,26 @@ def test_token_logprob_fwd_bwd(dtype):
 
 
 @pytest.mark.gpu
-def test_fused_head_log_probs_matches_reference():
+@pytest.mark.parametrize("form,rows,vocab,temp", [
+    ("epilogue", 300, 4096 + 1024, 1.0),
+    ("epilogue", 37, 2048 + 8 * 13, 0.7),        # row tail, vocabulary not a multiple of 64
+    ("chunked", 300, 4096 + 1024, 1.0),
+])
+def test_fused_head_log_probs_matches_reference(monkeypatch, form, rows, vocab, temp):
+    from visionrl_b200.ops import logprob as LP
     from visionrl_b200.ops.logprob import fused_head_log_probs, fused_head_log_probs_reference
 
+    monkeypatch.setattr(LP, "_CHUNKED_FOLD", form == "chunked")
     torch.manual_seed(1)
-    rows, hid, vocab = 300, 256, 4096 + 1024
+    hid = 256
     h = (torch.randn(rows, hid, device="cuda") * 0.5).bfloat16().requires_grad_()
     w = (torch.randn(vocab, hid, device="cuda") * 0.05).bfloat16().requires_grad_()
     b = (torch.randn(vocab, device="cuda") * 0.1).bfloat16().requires_grad_()
     ids = torch.randint(0, vocab, (rows,), device="cuda")
-    lp = fused_head_log_probs(h, w, b, ids, 1.0, chunk=2048)
+    ids[0], ids[-1] = 0, vocab - 1                  # first and last column as targets
+    lp = fused_head_log_probs(h, w, b, ids, temp, chunk=2048)
     hf, wf, bf = (t.detach().float().requires_grad_() for t in (h, w, b))
-    ref = fused_head_log_probs_reference(hf, wf, bf, ids, 1.0)
+    ref = fused_head_log_probs_reference(hf, wf, bf, ids, temp)
     assert torch.allclose(lp, ref, atol=5e-3, rtol=1e-3)
     g = torch.randn_like(lp)
     lp.backward(g)
@@ -939,3 +947,87 @@ def test_wrappers_refuse_cpu_operands():
     lp = torch.zeros(2, 8, device="cuda")
     with pytest.raises(RuntimeError, match="CUDA tensor"):
         ext.token_loss_fwd(lp, torch.zeros(2, 8), torch.zeros(2, device="cuda"), None, None, 0.2, True)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("has_cfg,dtype", [(True, torch.bfloat16), (False, torch.float32)])
+@pytest.mark.parametrize("sde_type", ["sde", "cps"])
+def test_fused_rollout_step_matches_the_separate_ops(has_cfg, dtype, sde_type):
+    """Guidance combine + SDE step + log-density + trajectory write in one kernel against the
+    separate tensor ops, with the noise given; the replay of what it wrote reproduces the
+    recorded log-probability bit for bit; with Philox noise the step is a pure function of the seed."""
+    from visionrl_b200.algorithms.flow_matching import step_coefficients
+    from visionrl_b200.ops import _ext
+    from visionrl_b200.ops.sde import sde_step
+
+    ext = _ext.load()
+    torch.manual_seed(31)
+    b, steps, shape, g = 3, 4, (16, 12, 20), 4.5
+    n = 16 * 12 * 20
+    path = torch.zeros(b, steps + 1, *shape, device="cuda")
+    path[:, 1] = torch.randn(b, *shape, device="cuda")
+    pred = torch.randn((2 if has_cfg else 1) * b, *shape, device="cuda").to(dtype)
+    sigmas = torch.linspace(1.0, 0.0, steps + 1, device="cuda")
+    index = torch.full((b,), 1, dtype=torch.long, device="cuda")
+    a, bb, _std, scale, _sq, dt = step_coefficients(sigmas, index, 0.7, sde_type)
+    noise = torch.randn(b, n, device="cuda")
+    logp = torch.zeros(b, steps, device="cuda")
+    ext.sde_rollout_step(pred, has_cfg, g, 0, path, 1, a.contiguous(), bb.contiguous(), scale.contiguous(),
+                         dt.contiguous(), noise, 0, 0, logp, False, sde_type == "sde")
+    if has_cfg:
+        u, c = pred.float().chunk(2, dim=0)
+        v = u + g * (c - u)
+    else:
+        v = pred.float()
+    want_next, want_lp, _ = sde_step(v, path[:, 1].contiguous(), a, bb, scale, dt, None, noise.view(b, *shape),
+                                     False, sde_type == "sde")
+    assert torch.allclose(path[:, 2], want_next, atol=1e-6, rtol=1e-6)
+    assert torch.allclose(logp[:, 1], want_lp, atol=1e-5, rtol=1e-5)
+    # replay: the recorded next latent given back reproduces the recorded log-probability exactly
+    _, replay_lp, _ = sde_step(v, path[:, 1].contiguous(), a, bb, scale, dt, path[:, 2].contiguous(), None,
+                               False, sde_type == "sde")
+    assert torch.equal(replay_lp, logp[:, 1])
+    # Philox noise: same seed and offset -> same bits, another seed -> other bits, sane moments
+    outs = []
+    for seed in (7, 7, 8):
+        p2, lp2 = path.clone(), torch.zeros_like(logp)
+        ext.sde_rollout_step(pred, has_cfg, g, 0, p2, 1, a.contiguous(), bb.contiguous(), scale.contiguous(),
+                             dt.contiguous(), None, seed, 4, lp2, False, sde_type == "sde")
+        outs.append(p2[:, 2].clone())
+    assert torch.equal(outs[0], outs[1]) and not torch.equal(outs[0], outs[2])
+    mean = a.view(-1, 1, 1, 1) * path[:, 1] + bb.view(-1, 1, 1, 1) * v
+    eps = (outs[0] - mean) / scale.view(-1, 1, 1, 1)
+    assert abs(float(eps.mean())) < 0.05 and abs(float(eps.std()) - 1.0) < 0.05
+    # deterministic steps ignore the noise
+    p3, lp3 = path.clone(), torch.zeros_like(logp)
+    ext.sde_rollout_step(pred, has_cfg, g, 0, p3, 1, a.contiguous(), bb.contiguous(), scale.contiguous(),
+                         dt.contiguous(), None, 1, 0, lp3, True, sde_type == "sde")
+    assert torch.allclose(p3[:, 2], path[:, 1] + dt.view(-1, 1, 1, 1) * v, atol=1e-6)
+
+
+@pytest.mark.gpu
+def test_fused_decode_step_matches_the_tensor_op_layer_path(monkeypatch):
+    """The decode step with fused glue kernels (add + RMSNorm, RoPE + cache append, SwiGLU) against
+    the same step written with tensor ops: hidden state and cache contents, three positions."""
+    from visionrl_b200.models.nn.llama import LlamaConfig, LlamaDecoder
+
+    torch.manual_seed(41)
+    cfg = LlamaConfig(num_layers=3, hidden_size=512, num_heads=4, ffn_dim=1024, vocab_size=128)
+    net = LlamaDecoder(cfg).to("cuda", torch.bfloat16).eval()
+    rows, max_len = 6, 16
+    outs, caches = [], []
+    for fused in (True, False):
+        if not fused:
+            monkeypatch.setattr(LlamaDecoder, "_fused_decode_ok", lambda self, e: False)
+        cache = net.new_cache(rows, max_len, torch.device("cuda"), torch.bfloat16)
+        gen = torch.Generator(device="cuda").manual_seed(5)
+        hidden = []
+        with torch.no_grad():
+            for p in range(3):
+                emb = torch.randn(rows, cfg.hidden_size, device="cuda", generator=gen).bfloat16()
+                hidden.append(net.decode_step_at(emb, cache, torch.tensor([p], device="cuda")))
+        outs.append(torch.stack(hidden))
+        caches.append(cache.data.clone())
+    assert torch.allclose(outs[0].float(), outs[1].float(), atol=6e-2, rtol=6e-2)
+    assert torch.allclose(caches[0].float(), caches[1].float(), atol=3e-2, rtol=3e-2)
+    assert float(caches[0][:, :, :, :, 3:].abs().max()) == 0.0           # nothing written past position 2

@@ -479,6 +479,156 @@ torch::Tensor decode_attention(torch::Tensor q, torch::Tensor k_cache, torch::Te
   return out;
 }
 
+// ------------------------------------------------------------------------------------------
+// Decode-step glue of the LLaMA trunk (one query position per row, launch-latency bound): each of
+// the three kernels below replaces a chain of tiny tensor ops that would otherwise cost a launch
+// apiece inside the replayed CUDA graph.
+//   decode_qkv_rope_append   fused QKV output [R, 3 H Dh] -> rotated q [R, H, 1, Dh]; rotated k and
+//                            v are written straight into the caches at the position held in `pos`
+//   swiglu_rows              [R, 2 F] (gate | up) -> silu(gate) * up  [R, F]
+//   add_rmsnorm_rows         x += delta ; y = rmsnorm(x) * w   (residual add fused with the next norm)
+// ------------------------------------------------------------------------------------------
+namespace {
+
+__global__ void __launch_bounds__(128)
+decode_qkv_rope_append_kernel(const __nv_bfloat16* __restrict__ qkv, const float* __restrict__ cosT,
+                              const float* __restrict__ sinT, const int64_t* __restrict__ pos,
+                              __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ kc,
+                              __nv_bfloat16* __restrict__ vc, int heads, int dh, int max_len,
+                              int64_t c_sr, int64_t c_sh, int64_t c_sl) {
+  // one block per (row, head); thread t owns the element pair (2t, 2t + 1) of q, k and v
+  const int r = blockIdx.x / heads, h = blockIdx.x % heads;
+  const int t = threadIdx.x;
+  if (2 * t >= dh) return;
+  const int64_t p = pos[0];
+  if (p < 0 || p >= max_len) return;                       // a bad position must not write anywhere
+  const int dmodel = heads * dh;
+  const __nv_bfloat16* row = qkv + (int64_t)r * 3 * dmodel + h * dh + 2 * t;
+  const float2 q2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(row));
+  const float2 k2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(row + dmodel));
+  const __nv_bfloat162 v2 = *reinterpret_cast<const __nv_bfloat162*>(row + 2 * dmodel);
+  const float c = cosT[t], s = sinT[t];
+  // bf16 rounding of the rotated values happens once, as in the tensor formulation
+  const __nv_bfloat162 qr = __floats2bfloat162_rn(q2.x * c - q2.y * s, q2.x * s + q2.y * c);
+  const __nv_bfloat162 kr = __floats2bfloat162_rn(k2.x * c - k2.y * s, k2.x * s + k2.y * c);
+  *reinterpret_cast<__nv_bfloat162*>(q_out + ((int64_t)r * heads + h) * dh + 2 * t) = qr;
+  const int64_t off = r * c_sr + h * c_sh + p * c_sl + 2 * t;
+  *reinterpret_cast<__nv_bfloat162*>(kc + off) = kr;
+  *reinterpret_cast<__nv_bfloat162*>(vc + off) = v2;
+}
+
+__global__ void __launch_bounds__(256)
+swiglu_rows_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int64_t rows, int f) {
+  const int64_t vec_per_row = f / 8;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < rows * vec_per_row;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / vec_per_row, v = i - r * vec_per_row;
+    float g[8], u[8];
+    unpack8(*reinterpret_cast<const bf16x8*>(gu + r * 2 * f + v * 8), g);
+    unpack8(*reinterpret_cast<const bf16x8*>(gu + r * 2 * f + f + v * 8), u);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      // silu in fp32, rounded to bf16 before the product, like F.silu(g) * u on bf16 tensors
+      const float sg = __bfloat162float(__float2bfloat16_rn(g[j] / (1.f + __expf(-g[j]))));
+      g[j] = sg * u[j];
+    }
+    *reinterpret_cast<bf16x8*>(out + r * f + v * 8) = pack8(g);
+  }
+}
+
+__global__ void __launch_bounds__(256)
+add_rmsnorm_rows_kernel(__nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ delta,
+                        const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y, int d, float eps) {
+  __shared__ float red[32];
+  const int64_t r = blockIdx.x;
+  float acc = 0.f;
+  for (int v = threadIdx.x; v < d / 8; v += blockDim.x) {
+    float a[8], b[8];
+    unpack8(*reinterpret_cast<const bf16x8*>(x + r * d + v * 8), a);
+    if (delta != nullptr) {
+      unpack8(*reinterpret_cast<const bf16x8*>(delta + r * d + v * 8), b);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) a[j] = __bfloat162float(__float2bfloat16_rn(a[j] + b[j]));
+      *reinterpret_cast<bf16x8*>(x + r * d + v * 8) = pack8(a);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc += a[j] * a[j];
+  }
+  const float rs = rsqrtf(block_sum(acc, red) / (float)d + eps);
+  for (int v = threadIdx.x; v < d / 8; v += blockDim.x) {
+    float a[8], ww[8];
+    unpack8(*reinterpret_cast<const bf16x8*>(x + r * d + v * 8), a);
+    unpack8(*reinterpret_cast<const bf16x8*>(w + v * 8), ww);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) a[j] = a[j] * rs * ww[j];
+    *reinterpret_cast<bf16x8*>(y + r * d + v * 8) = pack8(a);
+  }
+}
+
+}  // namespace
+
+torch::Tensor decode_qkv_rope_append(torch::Tensor qkv, torch::Tensor cos, torch::Tensor sin, torch::Tensor pos,
+                                     torch::Tensor k_cache, torch::Tensor v_cache, int64_t heads) {
+  TORCH_CHECK(qkv.is_cuda() && qkv.dim() == 2 && qkv.scalar_type() == torch::kBFloat16 && qkv.is_contiguous(),
+              "decode_qkv_rope_append: qkv must be contiguous bf16 [R, 3 * H * Dh]");
+  const int64_t rows = qkv.size(0), dmodel = qkv.size(1) / 3, dh = dmodel / heads;
+  TORCH_CHECK(qkv.size(1) == 3 * heads * dh && dh % 2 == 0 && dh <= 256, "decode_qkv_rope_append: head size");
+  VRL_CHECK_OPERAND(cos, qkv, torch::kFloat32, dh / 2);
+  VRL_CHECK_OPERAND(sin, qkv, torch::kFloat32, dh / 2);
+  VRL_CHECK_OPERAND(pos, qkv, torch::kInt64, 1);
+  VRL_CHECK_OPERAND(k_cache, qkv, torch::kBFloat16);
+  VRL_CHECK_OPERAND(v_cache, qkv, torch::kBFloat16);
+  TORCH_CHECK(cos.is_contiguous() && sin.is_contiguous());
+  TORCH_CHECK(k_cache.dim() == 4 && k_cache.sizes() == v_cache.sizes() && k_cache.strides() == v_cache.strides() &&
+              k_cache.size(0) >= rows && k_cache.size(1) == heads && k_cache.size(3) == dh &&
+              k_cache.stride(3) == 1 && k_cache.stride(0) % 2 == 0 && k_cache.stride(1) % 2 == 0 &&
+              k_cache.stride(2) % 2 == 0, "decode_qkv_rope_append: caches must be [R, H, L, Dh] with unit inner stride");
+  const c10::cuda::CUDAGuard guard(qkv.device());
+  auto q = torch::empty({rows, heads, 1, dh}, qkv.options());
+  if (rows == 0) return q;
+  decode_qkv_rope_append_kernel<<<(unsigned)(rows * heads), 128, 0, at::cuda::getCurrentCUDAStream()>>>(
+      reinterpret_cast<const __nv_bfloat16*>(qkv.data_ptr()), cos.data_ptr<float>(), sin.data_ptr<float>(),
+      pos.data_ptr<int64_t>(), reinterpret_cast<__nv_bfloat16*>(q.data_ptr()),
+      reinterpret_cast<__nv_bfloat16*>(k_cache.data_ptr()), reinterpret_cast<__nv_bfloat16*>(v_cache.data_ptr()),
+      (int)heads, (int)dh, (int)k_cache.size(2), k_cache.stride(0), k_cache.stride(1), k_cache.stride(2));
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return q;
+}
+
+torch::Tensor swiglu_rows(torch::Tensor gate_up) {
+  TORCH_CHECK(gate_up.is_cuda() && gate_up.dim() == 2 && gate_up.scalar_type() == torch::kBFloat16 &&
+              gate_up.is_contiguous() && gate_up.size(1) % 16 == 0, "swiglu_rows: contiguous bf16 [R, 2 F], F % 8 == 0");
+  const c10::cuda::CUDAGuard guard(gate_up.device());
+  const int64_t rows = gate_up.size(0), f = gate_up.size(1) / 2;
+  auto out = torch::empty({rows, f}, gate_up.options());
+  if (rows == 0) return out;
+  const int blocks = (int)std::max<int64_t>(1, std::min<int64_t>((rows * f / 8 + 255) / 256, 148 * 4));
+  swiglu_rows_kernel<<<blocks, 256, 0, at::cuda::getCurrentCUDAStream()>>>(
+      reinterpret_cast<const __nv_bfloat16*>(gate_up.data_ptr()), reinterpret_cast<__nv_bfloat16*>(out.data_ptr()),
+      rows, (int)f);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return out;
+}
+
+// x (updated in place when `delta` is given) and the normalised rows.
+torch::Tensor add_rmsnorm_rows(torch::Tensor x, c10::optional<torch::Tensor> delta, torch::Tensor w, double eps) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.scalar_type() == torch::kBFloat16 && x.is_contiguous() &&
+              x.size(1) % 8 == 0, "add_rmsnorm_rows: contiguous bf16 [R, D], D % 8 == 0");
+  VRL_CHECK_OPERAND(delta, x, torch::kBFloat16, x.numel());
+  VRL_CHECK_OPERAND(w, x, torch::kBFloat16, x.size(1));
+  TORCH_CHECK(w.is_contiguous() && (!delta.has_value() || delta->is_contiguous()));
+  const c10::cuda::CUDAGuard guard(x.device());
+  auto y = torch::empty_like(x);
+  if (x.size(0) == 0) return y;
+  add_rmsnorm_rows_kernel<<<(unsigned)x.size(0), 256, 0, at::cuda::getCurrentCUDAStream()>>>(
+      reinterpret_cast<__nv_bfloat16*>(x.data_ptr()),
+      delta.has_value() ? reinterpret_cast<const __nv_bfloat16*>(delta->data_ptr()) : nullptr,
+      reinterpret_cast<const __nv_bfloat16*>(w.data_ptr()), reinterpret_cast<__nv_bfloat16*>(y.data_ptr()),
+      (int)x.size(1), (float)eps);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return y;
+}
+
 torch::Tensor group_advantages(torch::Tensor rewards, torch::Tensor group_ids, double eps, double clip,
                                bool global_std) {
   TORCH_CHECK(rewards.is_cuda() && rewards.dim() == 1 && group_ids.numel() == rewards.numel());

@@ -7,6 +7,7 @@
 
 #include <cstdlib>
 
+#include "head_lse.h"
 #include "ops.h"
 
 namespace {
@@ -31,6 +32,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   }
   m.def("sde_step_fwd", &vrl::sde_step_fwd);
   m.def("sde_step_bwd", &vrl::sde_step_bwd);
+  m.def("sde_rollout_step", &vrl::sde_rollout_step);
   m.def("token_loss_fwd", &vrl::token_loss_fwd);
   m.def("per_sample_mse", &vrl::per_sample_mse);
   m.def("sum_squares", &vrl::sum_squares);
@@ -65,6 +67,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("sample_tokens", &vrl::sample_tokens);
   m.def("decode_attention", &vrl::decode_attention);
   m.def("group_advantages", &vrl::group_advantages);
+  m.def("decode_qkv_rope_append", &vrl::decode_qkv_rope_append);
+  m.def("swiglu_rows", &vrl::swiglu_rows);
+  m.def("add_rmsnorm_rows", &vrl::add_rmsnorm_rows);
   m.def("int4_gemv", &vrl::int4_gemv);
   m.def("moe_gate_topk", &vrl::moe_gate_topk);
   m.def("moe_permute", &vrl::moe_permute);
@@ -85,6 +90,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_bf16", &vrl::gemm_bf16);
   m.def("gemm_bf16_dual", &vrl::gemm_bf16_dual);
   m.def("gemm_allgather", &vrl::gemm_allgather);
+  m.def("head_logprob_fwd", &vrl::head_logprob_fwd);
+  m.def("head_softmax_grad", &vrl::head_softmax_grad);
   m.def("gemm_bf16_acc", &vrl::gemm_bf16_acc);
   m.def("gemm_bf16_out", &vrl::gemm_bf16_out);
   m.def("gemm_last_status", &vrl::gemm_last_status);

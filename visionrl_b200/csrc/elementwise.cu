@@ -6,6 +6,8 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
 
+#include <curand_kernel.h>
+
 #include "common.cuh"
 #include "ops.h"
 
@@ -16,6 +18,20 @@ namespace vrl {
 // ------------------------------------------------------------------------------------------
 constexpr int kSdeThreads = 256;
 constexpr int kSdeElemsPerBlock = kSdeThreads * 4 * 4;   // 4 float4 per thread
+
+// The step's arithmetic, spelled with explicitly rounded operations: the rollout kernel and the
+// replay kernel must produce the same bits for the same inputs, which an expression left to the
+// compiler's choice of multiply-add contraction does not guarantee across two kernels.
+__device__ __forceinline__ float sde_mean(float ca, float x, float cb, float v) {
+  return __fmaf_rn(ca, x, __fmul_rn(cb, v));
+}
+__device__ __forceinline__ float sde_sample(float mu, float cs, float e) { return __fmaf_rn(cs, e, mu); }
+__device__ __forceinline__ float sde_ode(float x, float cdt, float v) { return __fmaf_rn(cdt, v, x); }
+__device__ __forceinline__ float sde_sq4(float acc, const float4& pr, const float4& mu) {
+  const float d0 = __fsub_rn(pr.x, mu.x), d1 = __fsub_rn(pr.y, mu.y), d2 = __fsub_rn(pr.z, mu.z),
+              d3 = __fsub_rn(pr.w, mu.w);
+  return __fmaf_rn(d3, d3, __fmaf_rn(d2, d2, __fmaf_rn(d1, d1, __fmaf_rn(d0, d0, acc))));
+}
 
 __global__ void __launch_bounds__(kSdeThreads)
 sde_step_fwd_kernel(const float* __restrict__ v, const float* __restrict__ x,
@@ -38,32 +54,38 @@ sde_step_fwd_kernel(const float* __restrict__ v, const float* __restrict__ x,
       const float4 vv = *reinterpret_cast<const float4*>(v + base + i);
       const float4 xx = *reinterpret_cast<const float4*>(x + base + i);
       float4 mu, pr;
-      mu.x = ca * xx.x + cb * vv.x; mu.y = ca * xx.y + cb * vv.y;
-      mu.z = ca * xx.z + cb * vv.z; mu.w = ca * xx.w + cb * vv.w;
+      mu.x = sde_mean(ca, xx.x, cb, vv.x); mu.y = sde_mean(ca, xx.y, cb, vv.y);
+      mu.z = sde_mean(ca, xx.z, cb, vv.z); mu.w = sde_mean(ca, xx.w, cb, vv.w);
       if (prev_in != nullptr) {
         pr = *reinterpret_cast<const float4*>(prev_in + base + i);
       } else {
         const float4 e = *reinterpret_cast<const float4*>(noise + base + i);
-        pr.x = mu.x + cs * e.x; pr.y = mu.y + cs * e.y; pr.z = mu.z + cs * e.z; pr.w = mu.w + cs * e.w;
+        pr.x = sde_sample(mu.x, cs, e.x); pr.y = sde_sample(mu.y, cs, e.y);
+        pr.z = sde_sample(mu.z, cs, e.z); pr.w = sde_sample(mu.w, cs, e.w);
       }
       if (deterministic) {
-        pr.x = xx.x + cdt * vv.x; pr.y = xx.y + cdt * vv.y;
-        pr.z = xx.z + cdt * vv.z; pr.w = xx.w + cdt * vv.w;
+        pr.x = sde_ode(xx.x, cdt, vv.x); pr.y = sde_ode(xx.y, cdt, vv.y);
+        pr.z = sde_ode(xx.z, cdt, vv.z); pr.w = sde_ode(xx.w, cdt, vv.w);
       }
       *reinterpret_cast<float4*>(mean_out + base + i) = mu;
       *reinterpret_cast<float4*>(prev_out + base + i) = pr;
-      const float d0 = pr.x - mu.x, d1 = pr.y - mu.y, d2 = pr.z - mu.z, d3 = pr.w - mu.w;
-      acc += d0 * d0 + d1 * d1 + d2 * d2 + d3 * d3;
+      acc = sde_sq4(acc, pr, mu);
     } else {
+      // ragged end (or unaligned operands): the same operations in the same order, element by element
+      float4 mu = make_float4(0.f, 0.f, 0.f, 0.f), pr = mu;
+      float* mu_e = &mu.x;
+      float* pr_e = &pr.x;
       for (int64_t j = i; j < n && j < i + 4; ++j) {
         const float vv = v[base + j], xx = x[base + j];
-        const float mu = ca * xx + cb * vv;
-        float pr = (prev_in != nullptr) ? prev_in[base + j] : mu + cs * noise[base + j];
-        if (deterministic) pr = xx + cdt * vv;
-        mean_out[base + j] = mu;
-        prev_out[base + j] = pr;
-        acc += (pr - mu) * (pr - mu);
+        const float m = sde_mean(ca, xx, cb, vv);
+        float q = (prev_in != nullptr) ? prev_in[base + j] : sde_sample(m, cs, noise[base + j]);
+        if (deterministic) q = sde_ode(xx, cdt, vv);
+        mean_out[base + j] = m;
+        prev_out[base + j] = q;
+        mu_e[j - i] = m;
+        pr_e[j - i] = q;
       }
+      acc = sde_sq4(acc, pr, mu);
     }
   }
   const float total = block_sum(acc, red);
@@ -85,6 +107,160 @@ __global__ void sde_logprob_finalize_kernel(const float* __restrict__ partial,
   } else {
     logp[sample] = -mean_sq;
   }
+}
+
+// ------------------------------------------------------------------------------------------
+// K5, rollout form: classifier-free-guidance combine + SDE / CPS step + Gaussian log-density + the
+// write into the trajectory buffer, in ONE pass over the model output.
+//   v   = cond                                   (no guidance)
+//       = uncond + g (cond - uncond)             (cfg_form 0)   or   cond + g (cond - uncond)  (cfg_form 1)
+//   mu  = a x + b v ;  x' = mu + scale * eps  (or x + dt v when deterministic)
+// `pred` is the transformer output in its own dtype, [uncond ; cond] stacked along the batch when
+// guidance is on.  x is row i of the trajectory buffer, x' goes to row i + 1 (both addressed with the
+// buffer's batch stride), the per-sample log-density goes to column i of the [B, T] log-prob table.
+// eps comes from `noise` when given, otherwise from Philox-4x32-10 keyed by (seed, element, step),
+// so a rollout is a pure function of its seed and no noise tensor is materialised.
+// ------------------------------------------------------------------------------------------
+template <typename TV>
+__device__ __forceinline__ float4 load4(const TV* p);
+template <>
+__device__ __forceinline__ float4 load4<float>(const float* p) { return *reinterpret_cast<const float4*>(p); }
+template <>
+__device__ __forceinline__ float4 load4<__nv_bfloat16>(const __nv_bfloat16* p) {
+  const uint2 u = *reinterpret_cast<const uint2*>(p);
+  const float2 lo = bf16pair_to_float2(u.x), hi = bf16pair_to_float2(u.y);
+  return make_float4(lo.x, lo.y, hi.x, hi.y);
+}
+
+template <typename TV>
+__global__ void __launch_bounds__(kSdeThreads)
+sde_rollout_step_kernel(const TV* __restrict__ pred, int has_cfg, float guidance, int cfg_form,
+                        const float* __restrict__ x, float* __restrict__ next, int64_t path_bstride,
+                        const float* __restrict__ a, const float* __restrict__ b,
+                        const float* __restrict__ scale, const float* __restrict__ dt,
+                        const float* __restrict__ noise, unsigned long long seed,
+                        unsigned long long offset, float* __restrict__ partial, int64_t n,
+                        int blocks_per_sample, int batch, int deterministic) {
+  __shared__ float red[32];
+  const int sample = blockIdx.y;
+  const float ca = a[sample], cb = b[sample], cs = scale[sample], cdt = dt[sample];
+  const TV* cond = pred + ((int64_t)(has_cfg ? batch : 0) + sample) * n;
+  const TV* uncond = pred + (int64_t)sample * n;
+  const float* xs = x + (int64_t)sample * path_bstride;
+  float* out = next + (int64_t)sample * path_bstride;
+  const int64_t start = (int64_t)blockIdx.x * kSdeElemsPerBlock;
+  curandStatePhilox4_32_10_t rng;
+  if (noise == nullptr && !deterministic)
+    curand_init(seed, ((unsigned long long)sample * blocks_per_sample + blockIdx.x) * kSdeThreads + threadIdx.x,
+                offset, &rng);
+  float acc = 0.f;
+#pragma unroll
+  for (int it = 0; it < 4; ++it) {
+    const int64_t i = start + ((int64_t)it * kSdeThreads + threadIdx.x) * 4;
+    float4 e = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (!deterministic) {
+      // every thread draws in every iteration so the Philox counters do not depend on n
+      if (noise == nullptr) e = curand_normal4(&rng);
+      else if (i + 3 < n) e = *reinterpret_cast<const float4*>(noise + (int64_t)sample * n + i);
+    }
+    if (i + 3 < n) {
+      float4 vv = load4<TV>(cond + i);
+      if (has_cfg) {
+        const float4 uu = load4<TV>(uncond + i);
+        const float4 base = cfg_form == 0 ? uu : vv;
+        // three separately rounded operations, exactly what the training replay's tensor expression
+        // `base + g * (cond - uncond)` does: rollout and replay must see the same v bit for bit
+        vv = make_float4(__fadd_rn(base.x, __fmul_rn(guidance, __fsub_rn(vv.x, uu.x))),
+                         __fadd_rn(base.y, __fmul_rn(guidance, __fsub_rn(vv.y, uu.y))),
+                         __fadd_rn(base.z, __fmul_rn(guidance, __fsub_rn(vv.z, uu.z))),
+                         __fadd_rn(base.w, __fmul_rn(guidance, __fsub_rn(vv.w, uu.w))));
+      }
+      const float4 xx = *reinterpret_cast<const float4*>(xs + i);
+      float4 mu, pr;
+      mu.x = sde_mean(ca, xx.x, cb, vv.x); mu.y = sde_mean(ca, xx.y, cb, vv.y);
+      mu.z = sde_mean(ca, xx.z, cb, vv.z); mu.w = sde_mean(ca, xx.w, cb, vv.w);
+      if (deterministic) {
+        pr.x = sde_ode(xx.x, cdt, vv.x); pr.y = sde_ode(xx.y, cdt, vv.y);
+        pr.z = sde_ode(xx.z, cdt, vv.z); pr.w = sde_ode(xx.w, cdt, vv.w);
+      } else {
+        pr.x = sde_sample(mu.x, cs, e.x); pr.y = sde_sample(mu.y, cs, e.y);
+        pr.z = sde_sample(mu.z, cs, e.z); pr.w = sde_sample(mu.w, cs, e.w);
+      }
+      *reinterpret_cast<float4*>(out + i) = pr;
+      acc = sde_sq4(acc, pr, mu);
+    }
+  }
+  const float total = block_sum(acc, red);
+  if (threadIdx.x == 0) partial[(int64_t)sample * blocks_per_sample + blockIdx.x] = total;
+}
+
+__global__ void sde_logprob_finalize_strided_kernel(const float* __restrict__ partial,
+                                                    const float* __restrict__ scale,
+                                                    float* __restrict__ logp, int64_t logp_stride,
+                                                    int blocks_per_sample, int64_t n, int gaussian,
+                                                    int batch) {
+  const int sample = blockIdx.x * blockDim.x + threadIdx.x;
+  if (sample >= batch) return;
+  float s = 0.f;
+  for (int i = 0; i < blocks_per_sample; ++i) s += partial[(int64_t)sample * blocks_per_sample + i];
+  const float mean_sq = s / (float)n;
+  float value = -mean_sq;
+  if (gaussian) {
+    const float nu = scale[sample];
+    value = -mean_sq / (2.f * nu * nu) - logf(nu) - 0.9189385332046727f;
+  }
+  logp[(int64_t)sample * logp_stride] = value;
+}
+
+void sde_rollout_step(torch::Tensor pred, bool has_cfg, double guidance, int64_t cfg_form,
+                      torch::Tensor path, int64_t step, torch::Tensor a, torch::Tensor b,
+                      torch::Tensor scale, torch::Tensor dt, c10::optional<torch::Tensor> noise,
+                      int64_t seed, int64_t offset, torch::Tensor log_probs, bool deterministic,
+                      bool gaussian) {
+  TORCH_CHECK(path.is_cuda() && path.scalar_type() == torch::kFloat32 && path.is_contiguous() &&
+              path.dim() >= 3, "sde_rollout_step: path must be a contiguous fp32 [B, T + 1, ...] buffer");
+  const int64_t batch = path.size(0), rows = path.size(1);
+  TORCH_CHECK(batch >= 1 && batch <= 65535 && step >= 0 && step + 1 < rows, "sde_rollout_step: step out of range");
+  const int64_t n = path.numel() / (batch * rows);
+  TORCH_CHECK(n % 4 == 0 && reinterpret_cast<uintptr_t>(path.data_ptr()) % 16 == 0,
+              "sde_rollout_step: the per-sample latent size must be a multiple of 4 floats");
+  VRL_CHECK_OPERAND(pred, path);
+  TORCH_CHECK(pred.is_contiguous() && pred.numel() == (has_cfg ? 2 : 1) * batch * n &&
+              reinterpret_cast<uintptr_t>(pred.data_ptr()) % 16 == 0 &&
+              (pred.scalar_type() == torch::kFloat32 || pred.scalar_type() == torch::kBFloat16),
+              "sde_rollout_step: pred must be contiguous fp32 / bf16 [(2) B, ...] matching the latents");
+  VRL_CHECK_OPERAND(a, path, torch::kFloat32, batch);
+  VRL_CHECK_OPERAND(b, path, torch::kFloat32, batch);
+  VRL_CHECK_OPERAND(scale, path, torch::kFloat32, batch);
+  VRL_CHECK_OPERAND(dt, path, torch::kFloat32, batch);
+  VRL_CHECK_OPERAND(noise, path, torch::kFloat32, batch * n);
+  VRL_CHECK_OPERAND(log_probs, path, torch::kFloat32);
+  TORCH_CHECK(a.is_contiguous() && b.is_contiguous() && scale.is_contiguous() && dt.is_contiguous() &&
+              (!noise.has_value() || noise->is_contiguous()), "sde_rollout_step: contiguous per-sample operands");
+  TORCH_CHECK(log_probs.dim() == 2 && log_probs.size(0) == batch && step < log_probs.size(1),
+              "sde_rollout_step: log_probs must be [B, T]");
+  TORCH_CHECK(cfg_form == 0 || cfg_form == 1, "sde_rollout_step: cfg_form 0 (uncond + g d) or 1 (cond + g d)");
+  const c10::cuda::CUDAGuard guard(path.device());
+  const int bps = sde_blocks_per_sample(n);
+  auto partial = torch::empty({batch, bps}, path.options());
+  auto stream = at::cuda::getCurrentCUDAStream();
+  const float* x = path.data_ptr<float>() + step * n;
+  float* next = path.data_ptr<float>() + (step + 1) * n;
+  const float* noise_ptr = noise.has_value() ? noise->data_ptr<float>() : nullptr;
+  dim3 grid(bps, (unsigned)batch);
+#define VRL_LAUNCH_ROLLOUT(TV)                                                                        \
+  sde_rollout_step_kernel<TV><<<grid, kSdeThreads, 0, stream>>>(                                      \
+      reinterpret_cast<const TV*>(pred.data_ptr()), has_cfg ? 1 : 0, (float)guidance, (int)cfg_form, x,  \
+      next, rows * n, a.data_ptr<float>(), b.data_ptr<float>(), scale.data_ptr<float>(),              \
+      dt.data_ptr<float>(), noise_ptr, (unsigned long long)seed, (unsigned long long)offset,          \
+      partial.data_ptr<float>(), n, bps, (int)batch, deterministic ? 1 : 0)
+  if (pred.scalar_type() == torch::kBFloat16) VRL_LAUNCH_ROLLOUT(__nv_bfloat16);
+  else VRL_LAUNCH_ROLLOUT(float);
+#undef VRL_LAUNCH_ROLLOUT
+  sde_logprob_finalize_strided_kernel<<<(unsigned)((batch + 127) / 128), 128, 0, stream>>>(
+      partial.data_ptr<float>(), scale.data_ptr<float>(), log_probs.data_ptr<float>() + step,
+      log_probs.stride(0), bps, n, gaussian ? 1 : 0, (int)batch);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
 
 // float4 accesses need every sample's base (sample * n floats) on a 16-byte boundary

@@ -68,20 +68,41 @@ struct Params {
   int* g_ready;                    // [g_world] arrival counters, zero before the launch
   int g_world, g_rank, g_rows;     // g_rows = N / g_world
   int g_first_tile;                // n-tile holding this rank's own rows: processed first
+  int g_band;                      // m-tiles per band of the gathering variant's tile order
+  // log-sum-exp epilogues of the vocabulary head (0 = off).  1: nothing is stored but, per row and
+  // 64-column chunk, the maximum and the exponential sum of (acc + bias) / T, plus the target's
+  // value; 2: the stored bf16 value is g/T * (onehot(id) - exp((acc + bias) / T - lse)).
+  int lse_mode;
+  const int64_t* lse_ids;          // [M] target column (global index; lse_col0 is this product's first)
+  int64_t lse_col0;
+  float lse_inv_t;
+  float* lse_part_max;             // [ceil(N / 64), M]
+  float* lse_part_sum;             // [ceil(N / 64), M]
+  float* lse_target;               // [M]
+  const float* lse_lse;            // [M]  (mode 2)
+  const float* lse_g;              // [M]  (mode 2)
 };
 
 constexpr int kGatherThreads = 128;
 enum : int { kTimeoutGather = 4 };
 
-// Tile index -> tile origin.  Plain GEMMs sweep n fastest; the gathering variant sweeps m fastest
-// and starts at the n-tiles of the local shard, so the peers' rows are needed as late as possible.
+// Tile index -> tile origin.  Plain GEMMs sweep n fastest.  The gathering variant works through
+// bands of `g_band` m-tiles; inside a band it sweeps m fastest and starts at the n-tiles of the
+// local shard, so the peers' rows are needed as late as the first band allows.  The band keeps the
+// A rows that one pass over the n-tiles re-reads small enough to stay in L2: an m-fastest sweep
+// over all of a large A would fetch it from DRAM once per n-tile.
 template <bool kGather>
 __device__ __forceinline__ void tile_origin(int tile, int m_tiles, int n_tiles, const Params& p, int& m0,
                                             int& n0) {
   if (kGather) {
-    int nt = tile / m_tiles + p.g_first_tile;
+    const int band_tiles = p.g_band * n_tiles;
+    const int band = tile / band_tiles;
+    const int mt0 = band * p.g_band;
+    const int mb = min(p.g_band, m_tiles - mt0);
+    const int t = tile - band * band_tiles;
+    int nt = t / mb + p.g_first_tile;
     if (nt >= n_tiles) nt -= n_tiles;
-    m0 = (tile % m_tiles) * BM;
+    m0 = (mt0 + t % mb) * BM;
     n0 = nt * BN;
   } else {
     m0 = (tile / n_tiles) * BM;
@@ -309,6 +330,43 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         }
         tmem_ld_wait();
         if (!ok) break;
+        if (p.lse_mode == 1) {
+          // one thread holds 64 consecutive logits of one row: fold them here, store 8 bytes
+          const int t = row_ok ? (int)(p.lse_ids[row] - p.lse_col0 - colbase) : -1;
+          float mx = -INFINITY;
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            const int col = colbase + g * 8;
+            float b[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) b[j] = 0.f;
+            if (p.bias && col < p.n) unpack8(*reinterpret_cast<const bf16x8*>(p.bias + col), b);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              float sv = (__uint_as_float(r[g * 8 + j]) + b[j]) * p.lse_inv_t;
+              if (col >= p.n) sv = -INFINITY;
+              r[g * 8 + j] = __float_as_uint(sv);
+              mx = fmaxf(mx, sv);
+            }
+          }
+          float sum = 0.f, tgt = 0.f;
+#pragma unroll
+          for (int i = 0; i < 64; ++i) {
+            const float sv = __uint_as_float(r[i]);
+            sum += __expf(sv - mx);
+            if (i == t) tgt = sv;
+          }
+          if (row_ok) {
+            const int64_t slot = (int64_t)(colbase >> 6) * p.m + row;
+            p.lse_part_max[slot] = mx;
+            p.lse_part_sum[slot] = sum;
+            if (t >= 0 && t < 64) p.lse_target[row] = tgt;
+          }
+          continue;
+        }
+        const float lse_r = (p.lse_mode == 2 && row_ok) ? p.lse_lse[row] : 0.f;
+        const float lse_gs = (p.lse_mode == 2 && row_ok) ? p.lse_g[row] * p.lse_inv_t : 0.f;
+        const int lse_id = (p.lse_mode == 2 && row_ok) ? (int)(p.lse_ids[row] - p.lse_col0) : -1;
         if (p.dual) {
           // first output: the pre-activation values, kept for the backward pass of the activation
 #pragma unroll
@@ -349,6 +407,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             unpack8(*reinterpret_cast<const bf16x8*>(p.bias + col), b);
 #pragma unroll
             for (int j = 0; j < 8; ++j) v[j] += b[j];
+          }
+          if (p.lse_mode == 2) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              v[j] = lse_gs * ((col + j == lse_id ? 1.f : 0.f) - __expf(v[j] * p.lse_inv_t - lse_r));
           }
           if (p.act == 1) {
 #pragma unroll
@@ -473,6 +536,16 @@ struct GatherSpec {
   int64_t rank, world;
 };
 
+// Log-sum-exp epilogues of the vocabulary head (Params::lse_mode).
+struct LseSpec {
+  int mode;                              // 1 = partial (max, sum, target) per 64-column chunk; 2 = softmax gradient
+  torch::Tensor ids;                     // int64 [M]
+  int64_t col0;                          // global index of this product's first column
+  double inv_t;
+  torch::Tensor part_max, part_sum, target;   // mode 1
+  torch::Tensor lse, g;                        // mode 2
+};
+
 static std::vector<torch::Tensor> gemm_impl(torch::Tensor a, torch::Tensor b,
                                             c10::optional<torch::Tensor> bias,
                                             c10::optional<torch::Tensor> gate,
@@ -480,7 +553,8 @@ static std::vector<torch::Tensor> gemm_impl(torch::Tensor a, torch::Tensor b,
                                             int64_t rows_per_gate, bool a_mn_major, bool b_mn_major,
                                             bool out_fp32, bool dual,
                                             c10::optional<torch::Tensor> out_given = c10::nullopt,
-                                            const struct GatherSpec* gather = nullptr);
+                                            const struct GatherSpec* gather = nullptr,
+                                            const struct LseSpec* lse = nullptr);
 
 torch::Tensor gemm_bf16(torch::Tensor a, torch::Tensor b, c10::optional<torch::Tensor> bias,
                         c10::optional<torch::Tensor> gate, c10::optional<torch::Tensor> residual,
@@ -511,8 +585,12 @@ static std::vector<torch::Tensor> gemm_impl(torch::Tensor a, torch::Tensor b,
                                             int64_t rows_per_gate, bool a_mn_major, bool b_mn_major,
                                             bool out_fp32, bool dual,
                                             c10::optional<torch::Tensor> out_given,
-                                            const GatherSpec* gather) {
+                                            const GatherSpec* gather, const LseSpec* lse) {
   using namespace gemm;
+  const bool lse_partial = lse != nullptr && lse->mode == 1;
+  TORCH_CHECK(lse == nullptr || (!gate.has_value() && !residual.has_value() && !dual && act == 0 &&
+                                 gather == nullptr && !out_given.has_value() && !out_fp32),
+              "gemm_bf16: the log-sum-exp epilogues take bias only");
   TORCH_CHECK(act >= 0 && act <= 3, "gemm_bf16: unknown epilogue activation");
   TORCH_CHECK(act != 3 || (residual.has_value() && !gate.has_value() && !out_fp32),
               "gemm_bf16: the gelu-gradient epilogue needs the pre-activation as `residual`");
@@ -547,6 +625,8 @@ static std::vector<torch::Tensor> gemm_impl(torch::Tensor a, torch::Tensor b,
   if (out_given.has_value()) {
     out = *out_given;
     TORCH_CHECK(!out_fp32 && out.size(0) == m && out.size(1) == n, "gemm_bf16: output shape mismatch");
+  } else if (lse_partial) {
+    out = torch::empty({0}, a.options());      // this epilogue stores no product
   } else {
     out = torch::empty({m, n}, a.options().dtype(out_fp32 ? torch::kFloat32 : torch::kBFloat16));
   }
@@ -595,6 +675,28 @@ static std::vector<torch::Tensor> gemm_impl(torch::Tensor a, torch::Tensor b,
   p.b_mn = b_mn_major ? 1 : 0;
   p.out_fp32 = out_fp32 ? 1 : 0;
   p.dual = dual ? 1 : 0;
+  if (lse != nullptr) {
+    const int64_t chunks = (n + 63) / 64;
+    VRL_CHECK_OPERAND(lse->ids, a, torch::kInt64, m);
+    p.lse_mode = lse->mode;
+    p.lse_ids = lse->ids.data_ptr<int64_t>();
+    p.lse_col0 = lse->col0;
+    p.lse_inv_t = (float)lse->inv_t;
+    if (lse_partial) {
+      VRL_CHECK_OPERAND(lse->part_max, a, torch::kFloat32, chunks * m);
+      VRL_CHECK_OPERAND(lse->part_sum, a, torch::kFloat32, chunks * m);
+      VRL_CHECK_OPERAND(lse->target, a, torch::kFloat32, m);
+      p.lse_part_max = lse->part_max.data_ptr<float>();
+      p.lse_part_sum = lse->part_sum.data_ptr<float>();
+      p.lse_target = lse->target.data_ptr<float>();
+      p.out_fp32 = 1;                           // no staging tile, no TMA store
+    } else {
+      VRL_CHECK_OPERAND(lse->lse, a, torch::kFloat32, m);
+      VRL_CHECK_OPERAND(lse->g, a, torch::kFloat32, m);
+      p.lse_lse = lse->lse.data_ptr<float>();
+      p.lse_g = lse->g.data_ptr<float>();
+    }
+  }
 
   static const bool attr_set = [] {
     C10_CUDA_CHECK(cudaFuncSetAttribute(gemm_bf16_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -607,7 +709,7 @@ static std::vector<torch::Tensor> gemm_impl(torch::Tensor a, torch::Tensor b,
   const int tiles = (int)(((m + BM - 1) / BM) * ((n + BN - 1) / BN));
   const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
   // output / residual maps: 64-column x 32-row boxes matching one epilogue warp's staging tile
-  CUtensorMap map_c = out_fp32 ? map_a : make_map(out.data_ptr(), n, m, n, 64, 32);
+  CUtensorMap map_c = (out_fp32 || lse_partial) ? map_a : make_map(out.data_ptr(), n, m, n, 64, 32);
   CUtensorMap map_r = (p.residual && !out_fp32) ? make_map(p.residual, n, m, n, 64, 32) : map_c;
   CUtensorMap map_c2 = dual ? make_map(pre.data_ptr(), n, m, n, 64, 32) : map_c;
   auto stream = at::cuda::getCurrentCUDAStream();
@@ -630,6 +732,10 @@ static std::vector<torch::Tensor> gemm_impl(torch::Tensor a, torch::Tensor b,
     p.g_ready = gather->ready.data_ptr<int>();
     p.g_world = (int)world; p.g_rank = (int)rank; p.g_rows = (int)(n / world);
     p.g_first_tile = (int)((rank * (n / world)) / BN);
+    // a band's A rows (g_band * BM * K bf16) stay within a quarter of the L2
+    const int64_t m_tiles_h = (m + BM - 1) / BM;
+    const int64_t band = (32ll << 20) / ((int64_t)BM * k * 2);
+    p.g_band = (int)std::max<int64_t>(1, std::min<int64_t>(m_tiles_h, band));
     C10_CUDA_CHECK(cudaMemsetAsync(p.g_ready, 0, sizeof(int) * world, stream));
     // One CTA per SM, all resident (the producers wait for every CTA's share of the gather), and
     // ALL of them even when the product has fewer tiles: the copy wants every SM's load slots.
@@ -670,6 +776,71 @@ std::vector<torch::Tensor> gemm_allgather(torch::Tensor x, torch::Tensor peer_pt
                         c10::nullopt, &spec);
   if (!dual) outs.resize(1);
   return outs;
+}
+
+// ------------------------------------------------------------- vocabulary head with log-sum-exp
+namespace gemm {
+
+// One thread per row: fold the per-chunk (max, sum) pairs into the row's log-sum-exp and finish
+// the target's log-probability.
+__global__ void lse_merge_kernel(const float* __restrict__ part_max, const float* __restrict__ part_sum,
+                                 const float* __restrict__ target, int chunks, int m, float* __restrict__ logp,
+                                 float* __restrict__ lse) {
+  const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= m) return;
+  float mx = -INFINITY;
+  for (int c = 0; c < chunks; ++c) mx = fmaxf(mx, part_max[(int64_t)c * m + row]);
+  float sum = 0.f;
+  for (int c = 0; c < chunks; ++c)
+    sum += part_sum[(int64_t)c * m + row] * __expf(part_max[(int64_t)c * m + row] - mx);
+  const float l = mx + logf(sum);
+  lse[row] = l;
+  logp[row] = target[row] - l;
+}
+
+}  // namespace gemm
+
+static void check_head_operands(const torch::Tensor& h, const torch::Tensor& w, const torch::Tensor& ids) {
+  TORCH_CHECK(h.is_cuda() && h.dim() == 2 && h.scalar_type() == torch::kBFloat16 && h.is_contiguous(),
+              "head log-probs: hidden must be a contiguous bf16 [rows, dim] CUDA tensor");
+  TORCH_CHECK(w.dim() == 2 && w.scalar_type() == torch::kBFloat16 && w.is_contiguous() && w.size(1) == h.size(1),
+              "head log-probs: weight must be contiguous bf16 [vocab, dim]");
+  TORCH_CHECK(ids.dim() == 1 && ids.is_contiguous() && ids.size(0) == h.size(0), "head log-probs: ids must be [rows]");
+}
+
+// log_softmax((h W^T + bias) / T)[ids] and the row log-sum-exp, with the fold over the vocabulary
+// done in the product's epilogue: what reaches memory per row is 8 bytes per 64 vocabulary
+// columns instead of 256 bytes of fp32 logits.  Ids outside [0, vocab) are the caller's error.
+std::vector<torch::Tensor> head_logprob_fwd(torch::Tensor h, torch::Tensor w, c10::optional<torch::Tensor> bias,
+                                            torch::Tensor ids, double temperature) {
+  check_head_operands(h, w, ids);
+  TORCH_CHECK(temperature > 0, "head log-probs: temperature must be positive");
+  const int64_t m = h.size(0), n = w.size(0), chunks = (n + 63) / 64;
+  auto f32 = h.options().dtype(torch::kFloat32);
+  torch::Tensor logp = torch::empty({m}, f32), lse = torch::empty({m}, f32);
+  if (m == 0) return {logp, lse};
+  LseSpec spec{1, ids, 0, 1.0 / temperature, torch::empty({chunks, m}, f32), torch::empty({chunks, m}, f32),
+               torch::zeros({m}, f32), torch::Tensor(), torch::Tensor()};
+  gemm_impl(h, w, bias, c10::nullopt, c10::nullopt, 0, 0, false, false, false, false, c10::nullopt, nullptr, &spec);
+  const c10::cuda::CUDAGuard guard(h.device());
+  gemm::lse_merge_kernel<<<(unsigned)((m + 127) / 128), 128, 0, at::cuda::getCurrentCUDAStream()>>>(
+      spec.part_max.data_ptr<float>(), spec.part_sum.data_ptr<float>(), spec.target.data_ptr<float>(), (int)chunks,
+      (int)m, logp.data_ptr<float>(), lse.data_ptr<float>());
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return {logp, lse};
+}
+
+// d logits = g / T * (onehot(ids) - softmax) for the vocabulary slice [col0, col0 + w.size(0)), as bf16,
+// produced in the epilogue of the recomputed product (no fp32 logits in memory).
+torch::Tensor head_softmax_grad(torch::Tensor h, torch::Tensor w, c10::optional<torch::Tensor> bias,
+                                torch::Tensor ids, torch::Tensor lse, torch::Tensor g, int64_t col0,
+                                double temperature) {
+  check_head_operands(h, w, ids);
+  TORCH_CHECK(lse.is_contiguous() && g.is_contiguous(), "head_softmax_grad: contiguous lse and g");
+  TORCH_CHECK(temperature > 0, "head_softmax_grad: temperature must be positive");
+  LseSpec spec{2, ids, col0, 1.0 / temperature, torch::Tensor(), torch::Tensor(), torch::Tensor(), lse, g};
+  return gemm_impl(h, w, bias, c10::nullopt, c10::nullopt, 0, 0, false, false, false, false, c10::nullopt, nullptr,
+                   &spec)[0];
 }
 
 }  // namespace vrl

@@ -237,6 +237,264 @@ rmsnorm_fwd_warp_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, 
     else { constexpr int VPL = 8; __VA_ARGS__; }                        \
   } while (0)
 
+// ----------------------------------------------------------------- column-owner variants
+// One thread owns ONE 8-column vector of the row (block = D / 8 threads rounded up to a warp) and
+// walks over a run of rows, RB rows per pass: RB independent 16-byte loads per operand are in
+// flight per thread, row statistics are block sums of RB values at a time (one barrier per RB rows),
+// and a per-column gradient sum is 8 registers per thread instead of a whole row's worth per
+// lane.  The register count stays low enough for several blocks per SM, which is what a
+// bandwidth-bound pass needs.
+constexpr int kColsRowsPerPass = 4;
+
+__device__ __forceinline__ void red_add_v4(float* addr, const float* v) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(v[0]), "f"(v[1]), "f"(v[2]),
+               "f"(v[3])
+               : "memory");
+}
+
+// Block-wide sums of NV values per thread, result in every thread.  `red` holds 32 * NV floats and
+// must not be reused before the next barrier of the block (callers alternate two buffers).
+template <int NV>
+__device__ __forceinline__ void block_sum_vals(float (&v)[NV], float* red, int nwarps) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#pragma unroll
+  for (int q = 0; q < NV; ++q) v[q] = warp_sum(v[q]);
+  if (lane == 0) {
+#pragma unroll
+    for (int q = 0; q < NV; ++q) red[warp * NV + q] = v[q];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int q = 0; q < NV; ++q) {
+    float t = 0.f;
+    for (int w = 0; w < nwarps; ++w) t += red[w * NV + q];
+    v[q] = t;
+  }
+}
+
+// rows per block so that the grid has a few blocks per SM slot, in multiples of the pass size
+static int cols_rows_per_block(int64_t total_rows, int rows_per_sample) {
+  int64_t rpb = total_rows / (148 * 4);
+  rpb = std::max<int64_t>(8, std::min<int64_t>(64, rpb));
+  rpb = (rpb + kColsRowsPerPass - 1) / kColsRowsPerPass * kColsRowsPerPass;
+  return (int)std::min<int64_t>(rpb, std::max(rows_per_sample, kColsRowsPerPass));
+}
+
+#define VRL_DISPATCH_COLS(threads, ...)                                  \
+  do {                                                                   \
+    if ((threads) <= 256) { constexpr int kMaxT = 256; __VA_ARGS__; }    \
+    else if ((threads) <= 512) { constexpr int kMaxT = 512; __VA_ARGS__; } \
+    else { constexpr int kMaxT = 1024; __VA_ARGS__; }                    \
+  } while (0)
+
+template <int kMaxT>
+__global__ void __launch_bounds__(kMaxT)
+adaln_fwd_cols_kernel(const bf16* __restrict__ x, const bf16* __restrict__ shift,
+                      const bf16* __restrict__ scale, bf16* __restrict__ y, float* __restrict__ mean_o,
+                      float* __restrict__ rstd_o, int rows_per_sample, int d, float eps, int64_t shift_ld,
+                      int64_t scale_ld, int rows_per_block) {
+  constexpr int RB = kColsRowsPerPass;
+  __shared__ float red[2 * 32 * RB];
+  const int i = threadIdx.x, nvec = d / 8, nwarps = blockDim.x >> 5;
+  const bool act = i < nvec;
+  const int sample = blockIdx.y;
+  float sh[8], sc1[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) { sh[j] = 0.f; sc1[j] = 1.f; }
+  if (act) {
+    float t[8];
+    unpack8(reinterpret_cast<const bf16x8*>(shift + (int64_t)sample * shift_ld)[i], sh);
+    unpack8(reinterpret_cast<const bf16x8*>(scale + (int64_t)sample * scale_ld)[i], t);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) sc1[j] = 1.f + t[j];
+  }
+  const int r_begin = blockIdx.x * rows_per_block;
+  const int r_end = min(r_begin + rows_per_block, rows_per_sample);
+  for (int rb = r_begin; rb < r_end; rb += RB) {
+    bf16x8 raw[RB];
+#pragma unroll
+    for (int q = 0; q < RB; ++q) {
+      raw[q].u = make_uint4(0u, 0u, 0u, 0u);
+      if (act && rb + q < r_end)
+        raw[q] = reinterpret_cast<const bf16x8*>(x + ((int64_t)sample * rows_per_sample + rb + q) * d)[i];
+    }
+    float mu[RB], var[RB];
+#pragma unroll
+    for (int q = 0; q < RB; ++q) {
+      float f[8];
+      unpack8(raw[q], f);
+      float t = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) t += f[j];
+      mu[q] = t;
+    }
+    block_sum_vals<RB>(mu, red, nwarps);
+#pragma unroll
+    for (int q = 0; q < RB; ++q) {
+      mu[q] /= (float)d;
+      float f[8];
+      unpack8(raw[q], f);
+      float t = 0.f;
+      if (act) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { const float c = f[j] - mu[q]; t += c * c; }
+      }
+      var[q] = t;
+    }
+    block_sum_vals<RB>(var, red + 32 * RB, nwarps);
+#pragma unroll
+    for (int q = 0; q < RB; ++q) {
+      if (rb + q >= r_end) continue;
+      const int64_t row = (int64_t)sample * rows_per_sample + rb + q;
+      const float rstd = rsqrtf(var[q] / (float)d + eps);
+      if (i == 0) { mean_o[row] = mu[q]; rstd_o[row] = rstd; }
+      if (act) {
+        float f[8], o[8];
+        unpack8(raw[q], f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = (f[j] - mu[q]) * rstd * sc1[j] + sh[j];
+        reinterpret_cast<bf16x8*>(y + row * d)[i] = pack8(o);
+      }
+    }
+    __syncthreads();            // both halves of `red` are free again
+  }
+}
+
+template <int kMaxT>
+__global__ void __launch_bounds__(kMaxT)
+adaln_bwd_cols_kernel(const bf16* __restrict__ gy, const bf16* __restrict__ x,
+                      const bf16* __restrict__ scale, const float* __restrict__ mean,
+                      const float* __restrict__ rstd, bf16* __restrict__ gx, float* __restrict__ gshift,
+                      float* __restrict__ gscale, int rows_per_sample, int d, int64_t scale_ld,
+                      int rows_per_block) {
+  constexpr int RB = kColsRowsPerPass;
+  __shared__ float red[2 * 32 * 2 * RB];
+  const int i = threadIdx.x, nvec = d / 8, nwarps = blockDim.x >> 5;
+  const bool act = i < nvec;
+  const int sample = blockIdx.y;
+  float one_plus[8], acc_sh[8], acc_sc[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) { one_plus[j] = 1.f; acc_sh[j] = 0.f; acc_sc[j] = 0.f; }
+  if (act) {
+    float t[8];
+    unpack8(reinterpret_cast<const bf16x8*>(scale + (int64_t)sample * scale_ld)[i], t);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) one_plus[j] = 1.f + t[j];
+  }
+  const int r_begin = blockIdx.x * rows_per_block;
+  const int r_end = min(r_begin + rows_per_block, rows_per_sample);
+  int parity = 0;
+  for (int rb = r_begin; rb < r_end; rb += RB, parity ^= 1) {
+    bf16x8 xr[RB], gr[RB];
+    float mu[RB], rs[RB];
+#pragma unroll
+    for (int q = 0; q < RB; ++q) {
+      const bool ok = rb + q < r_end;
+      const int64_t row = (int64_t)sample * rows_per_sample + (ok ? rb + q : r_end - 1);
+      mu[q] = mean[row];
+      rs[q] = rstd[row];
+      xr[q].u = make_uint4(0u, 0u, 0u, 0u);
+      gr[q].u = make_uint4(0u, 0u, 0u, 0u);
+      if (act && ok) {
+        xr[q] = reinterpret_cast<const bf16x8*>(x + row * d)[i];
+        gr[q] = reinterpret_cast<const bf16x8*>(gy + row * d)[i];
+      }
+    }
+    float part[2 * RB];
+#pragma unroll
+    for (int q = 0; q < RB; ++q) {
+      float xv[8], gv[8];
+      unpack8(xr[q], xv);
+      unpack8(gr[q], gv);
+      float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float xh = (xv[j] - mu[q]) * rs[q];
+        const float gp = gv[j] * one_plus[j];
+        s1 += gp;
+        s2 += gp * xh;
+        acc_sh[j] += gv[j];
+        acc_sc[j] += gv[j] * xh;
+      }
+      part[2 * q] = s1;
+      part[2 * q + 1] = s2;
+    }
+    block_sum_vals<2 * RB>(part, red + parity * 32 * 2 * RB, nwarps);
+#pragma unroll
+    for (int q = 0; q < RB; ++q) {
+      if (!act || rb + q >= r_end) continue;
+      const int64_t row = (int64_t)sample * rows_per_sample + rb + q;
+      const float m1 = part[2 * q] / (float)d, m2 = part[2 * q + 1] / (float)d;
+      float xv[8], gv[8], o[8];
+      unpack8(xr[q], xv);
+      unpack8(gr[q], gv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float xh = (xv[j] - mu[q]) * rs[q];
+        o[j] = rs[q] * (gv[j] * one_plus[j] - m1 - xh * m2);
+      }
+      reinterpret_cast<bf16x8*>(gx + row * d)[i] = pack8(o);
+    }
+  }
+  if (act) {
+    float* ds = gshift + (int64_t)sample * d + i * 8;
+    float* dc = gscale + (int64_t)sample * d + i * 8;
+    red_add_v4(ds, acc_sh);
+    red_add_v4(ds + 4, acc_sh + 4);
+    red_add_v4(dc, acc_sc);
+    red_add_v4(dc + 4, acc_sc + 4);
+  }
+}
+
+// d(out)/d(y) = g * gate and d(gate)[sample] = sum over the sample's rows of g * y, column owners.
+template <int kMaxT>
+__global__ void __launch_bounds__(kMaxT)
+gate_residual_bwd_cols_kernel(const bf16* __restrict__ g, const bf16* __restrict__ y,
+                              const bf16* __restrict__ gate, bf16* __restrict__ gy,
+                              float* __restrict__ ggate, int rows_per_sample, int d, int64_t gate_ld,
+                              int rows_per_block) {
+  constexpr int RB = kColsRowsPerPass;
+  const int i = threadIdx.x, nvec = d / 8;
+  if (i >= nvec) return;                        // no barrier in this kernel
+  const int sample = blockIdx.y;
+  float gt[8], acc[8];
+  unpack8(reinterpret_cast<const bf16x8*>(gate + (int64_t)sample * gate_ld)[i], gt);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+  const int r_begin = blockIdx.x * rows_per_block;
+  const int r_end = min(r_begin + rows_per_block, rows_per_sample);
+  for (int rb = r_begin; rb < r_end; rb += RB) {
+    bf16x8 graw[RB], yraw[RB];
+#pragma unroll
+    for (int q = 0; q < RB; ++q) {
+      graw[q].u = make_uint4(0u, 0u, 0u, 0u);
+      yraw[q].u = make_uint4(0u, 0u, 0u, 0u);
+      if (rb + q < r_end) {
+        const int64_t row = (int64_t)sample * rows_per_sample + rb + q;
+        graw[q] = reinterpret_cast<const bf16x8*>(g + row * d)[i];
+        yraw[q] = reinterpret_cast<const bf16x8*>(y + row * d)[i];
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < RB; ++q) {
+      if (rb + q >= r_end) continue;
+      const int64_t row = (int64_t)sample * rows_per_sample + rb + q;
+      float a[8], b[8], o[8];
+      unpack8(graw[q], a);
+      unpack8(yraw[q], b);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        o[j] = a[j] * gt[j];
+        acc[j] += a[j] * b[j];
+      }
+      reinterpret_cast<bf16x8*>(gy + row * d)[i] = pack8(o);
+    }
+  }
+  float* dg = ggate + (int64_t)sample * d + i * 8;
+  red_add_v4(dg, acc);
+  red_add_v4(dg + 4, acc + 4);
+}
+
 // ------------------------------------------------------------------------------ adaLN forward
 __global__ void __launch_bounds__(kNormThreads)
 adaln_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ shift,
@@ -302,6 +560,18 @@ std::vector<torch::Tensor> adaln_fwd(torch::Tensor x, torch::Tensor shift, torch
   auto mean = torch::empty({(int64_t)b * s}, x.options().dtype(torch::kFloat32));
   auto rstd = torch::empty_like(mean);
   auto stream = at::cuda::getCurrentCUDAStream();
+  if (b * s > 0 && b <= 65535) {
+    const int threads = (d / 8 + 31) / 32 * 32;
+    const int rpb = cols_rows_per_block((int64_t)b * s, s);
+    dim3 grid((s + rpb - 1) / rpb, b);
+    VRL_DISPATCH_COLS(threads, adaln_fwd_cols_kernel<kMaxT><<<grid, threads, 0, stream>>>(
+        reinterpret_cast<const bf16*>(x.data_ptr()), reinterpret_cast<const bf16*>(shift.data_ptr()),
+        reinterpret_cast<const bf16*>(scale.data_ptr()), reinterpret_cast<bf16*>(y.data_ptr()),
+        mean.data_ptr<float>(), rstd.data_ptr<float>(), s, d, (float)eps, shift.stride(0), scale.stride(0),
+        rpb));
+    C10_CUDA_KERNEL_LAUNCH_CHECK();
+    return {y, mean, rstd};
+  }
   if (d <= 2048) {
     const int64_t rows = (int64_t)b * s;
     const unsigned blocks = (unsigned)((rows + kRowWarps - 1) / kRowWarps);
@@ -412,6 +682,19 @@ std::vector<torch::Tensor> adaln_bwd(torch::Tensor gy, torch::Tensor x, torch::T
   auto gx = torch::empty_like(x);
   auto gshift = torch::zeros({b, d}, x.options().dtype(torch::kFloat32));
   auto gscale = torch::zeros({b, d}, x.options().dtype(torch::kFloat32));
+  if (b * s > 0 && b <= 65535) {
+    const int threads = (d / 8 + 31) / 32 * 32;
+    const int rpb = cols_rows_per_block((int64_t)b * s, s);
+    dim3 grid((s + rpb - 1) / rpb, b);
+    auto stream = at::cuda::getCurrentCUDAStream();
+    VRL_DISPATCH_COLS(threads, adaln_bwd_cols_kernel<kMaxT><<<grid, threads, 0, stream>>>(
+        reinterpret_cast<const bf16*>(gy.data_ptr()), reinterpret_cast<const bf16*>(x.data_ptr()),
+        reinterpret_cast<const bf16*>(scale.data_ptr()), mean.data_ptr<float>(), rstd.data_ptr<float>(),
+        reinterpret_cast<bf16*>(gx.data_ptr()), gshift.data_ptr<float>(), gscale.data_ptr<float>(), s, d,
+        scale.stride(0), rpb));
+    C10_CUDA_KERNEL_LAUNCH_CHECK();
+    return {gx, gshift, gscale};
+  }
   if (d <= 2048) {
     dim3 wgrid((s + kAdaBlockRows - 1) / kAdaBlockRows, b);
     auto stream = at::cuda::getCurrentCUDAStream();
@@ -694,11 +977,24 @@ std::vector<torch::Tensor> gate_residual_bwd(torch::Tensor g, torch::Tensor y, t
   const c10::cuda::CUDAGuard guard(y.device());
   const int b = (int)y.size(0), s = (int)y.size(1), d = (int)y.size(2);
   g = g.to(torch::kBFloat16).contiguous();
-  TORCH_CHECK(g.sizes() == y.sizes() && d % 8 == 0 && d <= 2048, "gate_residual_bwd: D <= 2048");
+  TORCH_CHECK(g.sizes() == y.sizes() && d % 8 == 0 && d <= 8192, "gate_residual_bwd: D <= 8192");
   gate = strided_rows(gate, b, d);
   auto gy = torch::empty_like(y);
   auto ggate = torch::zeros({b, d}, y.options().dtype(torch::kFloat32));
   if (b * s == 0) return {gy, ggate};
+  if (b <= 65535) {
+    const int threads = (d / 8 + 31) / 32 * 32;
+    const int rpb = cols_rows_per_block((int64_t)b * s, s);
+    dim3 cgrid((s + rpb - 1) / rpb, b);
+    VRL_DISPATCH_COLS(threads, gate_residual_bwd_cols_kernel<kMaxT><<<cgrid, threads, 0,
+                                                                   at::cuda::getCurrentCUDAStream()>>>(
+        reinterpret_cast<const bf16*>(g.data_ptr()), reinterpret_cast<const bf16*>(y.data_ptr()),
+        reinterpret_cast<const bf16*>(gate.data_ptr()), reinterpret_cast<bf16*>(gy.data_ptr()),
+        ggate.data_ptr<float>(), s, d, gate.stride(0), rpb));
+    C10_CUDA_KERNEL_LAUNCH_CHECK();
+    return {gy, ggate};
+  }
+  TORCH_CHECK(d <= 2048, "gate_residual_bwd: D <= 2048 for more than 65535 samples");
   dim3 grid((s + kGateBlockRows - 1) / kGateBlockRows, b);
   auto stream = at::cuda::getCurrentCUDAStream();
   VRL_DISPATCH_VPL(d / 8, gate_residual_bwd_kernel<VPL><<<grid, kRowWarps * 32, d * sizeof(float), stream>>>(
@@ -715,20 +1011,7 @@ std::vector<torch::Tensor> gate_residual_bwd(torch::Tensor g, torch::Tensor y, t
 // block write into one buffer at different offsets, so no concatenation copy is needed).  Norm modes: 0 none, 1 per head (weights of
 // Dh elements), 2 full width (weights of H*Dh elements).  rstd layout: [b, s, 2, H] (mode 1)
 // or [b, s, 2] (mode 2).  Rotary tables are [S, Dh/2]; pairs are (2i, 2i+1).
-constexpr int kQkvVecLimit = 8;     // vectors per thread: 3*H*Dh/8 <= 8*256  => H*Dh <= 5461
-
-// Instantiates the kernel for the number of 8-element vectors each thread really owns, so the
-// per-thread arrays (and the register count) match the model width.
-#define VRL_DISPATCH_QKV(nvec, ...)                                              \
-  do {                                                                           \
-    const int per_thread = ((nvec) + kNormThreads - 1) / kNormThreads;           \
-    if (per_thread <= 1) { constexpr int T = 1; __VA_ARGS__; }                   \
-    else if (per_thread <= 2) { constexpr int T = 2; __VA_ARGS__; }              \
-    else if (per_thread <= 3) { constexpr int T = 3; __VA_ARGS__; }              \
-    else if (per_thread <= 4) { constexpr int T = 4; __VA_ARGS__; }              \
-    else if (per_thread <= 6) { constexpr int T = 6; __VA_ARGS__; }              \
-    else { constexpr int T = 8; __VA_ARGS__; }                                   \
-  } while (0)
+constexpr int kQkvTokensPerPass = 4;
 
 __device__ __forceinline__ float group_sum(float v, int lanes) {
   for (int o = lanes >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -745,93 +1028,136 @@ struct QkvPeers {
   int world;
 };
 
-template <int kQkvMaxVec>
-__global__ void __launch_bounds__(kNormThreads)
+// tokens per block so that the three grids together give every SM a few blocks
+static int qkv_tokens_per_block(int64_t tokens) {
+  int64_t tpb = tokens * 3 / (148 * 6);
+  tpb = std::max<int64_t>(kQkvTokensPerPass, std::min<int64_t>(32, tpb));
+  return (int)((tpb + kQkvTokensPerPass - 1) / kQkvTokensPerPass * kQkvTokensPerPass);
+}
+
+// Column owners: blockIdx.y picks q, k or v; thread i owns vector i of that part's H * Dh / 8 (head
+// i / (Dh / 8)) and walks over a run of tokens, four per pass, so four independent 16-byte loads are
+// in flight per thread.  The per-head statistics are sums over the Dh / 8 neighbouring lanes; the
+// full-width ones are block sums of four values at a time.
+template <int kMaxT>
+__global__ void __launch_bounds__(kMaxT)
 qkv_prepare_fwd_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ qw,
                        const bf16* __restrict__ kw, const float* __restrict__ cosT,
                        const float* __restrict__ sinT, bf16* __restrict__ q, bf16* __restrict__ k,
-                       bf16* __restrict__ v, float* __restrict__ rstd_o, int seq, int heads,
-                       int dh, int mode, float eps, int seq_total, int seq_offset,
+                       bf16* __restrict__ v, float* __restrict__ rstd_o, int64_t tokens, int seq, int heads,
+                       int dh, int mode, float eps, int seq_total, int seq_offset, int tokens_per_block,
                        const QkvPeers peers) {
-  __shared__ float red[32];
-  const int64_t tok = blockIdx.x;
-  const int b = (int)(tok / seq), s = (int)(tok % seq);
+  constexpr int TB = kQkvTokensPerPass;
+  __shared__ float red[2 * 32 * TB];
+  const int i = threadIdx.x, nwarps = blockDim.x >> 5;
+  const int which = blockIdx.y;
   const int dmodel = heads * dh;
-  const int vec_per_head = dh / 8, vec_per_which = dmodel / 8, nvec = 3 * vec_per_which;
-  const bf16x8* src = reinterpret_cast<const bf16x8*>(qkv + tok * 3 * dmodel);
-  float f[kQkvMaxVec][8];
-  float ssq[kQkvMaxVec];
-  float tot_q = 0.f, tot_k = 0.f;
+  const int vec_per_head = dh / 8, vec_per_which = dmodel / 8;
+  const bool act = i < vec_per_which;
+  const int h = i / vec_per_head, j8 = i - h * vec_per_head;
+  const bool normed = which < 2 && mode != 0;
+  float ww[8];
 #pragma unroll
-  for (int t = 0; t < kQkvMaxVec; ++t) {
-    const int i = threadIdx.x + t * kNormThreads;
-    ssq[t] = 0.f;
-    if (i < nvec) {
-      unpack8(src[i], f[t]);
+  for (int j = 0; j < 8; ++j) ww[j] = 1.f;
+  if (act && normed)
+    unpack8(*reinterpret_cast<const bf16x8*>((which == 0 ? qw : kw) + (mode == 1 ? j8 * 8 : i * 8)), ww);
+  bf16* dst_local = which == 0 ? q : (which == 1 ? k : v);
+  const int hp = peers.world > 1 ? heads / peers.world : heads;
+  const int pg = h / hp, hl = h - pg * hp;
+  bf16* dst_peer = nullptr;
+  if (peers.world > 1 && act) dst_peer = which == 0 ? peers.q[pg] : (which == 1 ? peers.k[pg] : peers.v[pg]);
+  const int64_t tok_begin = (int64_t)blockIdx.x * tokens_per_block;
+  const int64_t tok_end = min(tok_begin + (int64_t)tokens_per_block, tokens);
+  int parity = 0;
+  for (int64_t tb = tok_begin; tb < tok_end; tb += TB) {
+    bf16x8 raw[TB];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) ssq[t] += f[t][j] * f[t][j];
-      const int which = i / vec_per_which;
-      if (which == 0) tot_q += ssq[t];
-      if (which == 1) tot_k += ssq[t];
+    for (int t = 0; t < TB; ++t) {
+      raw[t].u = make_uint4(0u, 0u, 0u, 0u);
+      if (act && tb + t < tok_end)
+        raw[t] = *reinterpret_cast<const bf16x8*>(qkv + ((tb + t) * 3 + which) * dmodel + i * 8);
     }
-  }
-  float full_q = 0.f, full_k = 0.f;
-  if (mode == 2) {
-    full_q = rsqrtf(block_sum(tot_q, red) / (float)dmodel + eps);
-    full_k = rsqrtf(block_sum(tot_k, red) / (float)dmodel + eps);
-    if (threadIdx.x == 0) { rstd_o[tok * 2] = full_q; rstd_o[tok * 2 + 1] = full_k; }
-  }
+    float ssq[TB];
 #pragma unroll
-  for (int t = 0; t < kQkvMaxVec; ++t) {
-    const int i = threadIdx.x + t * kNormThreads;
-    // the whole head group takes part in the shuffle, so no early exit before it
-    float head_ssq = (mode == 1) ? group_sum(ssq[t], vec_per_head) : 0.f;
-    if (i >= nvec) continue;
-    const int which = i / vec_per_which;
-    const int rem = i - which * vec_per_which;
-    const int h = rem / vec_per_head, j8 = rem - h * vec_per_head;
-    float o[8];
-    if (which < 2 && mode != 0) {
-      float rs;
+    for (int t = 0; t < TB; ++t) {
+      float f[8];
+      unpack8(raw[t], f);
+      float a = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) a += f[j] * f[j];
+      ssq[t] = a;
+    }
+    if (normed) {                                   // uniform over the block
       if (mode == 1) {
-        rs = rsqrtf(head_ssq / (float)dh + eps);
-        if (j8 == 0) rstd_o[(tok * 2 + which) * heads + h] = rs;
+#pragma unroll
+        for (int t = 0; t < TB; ++t) ssq[t] = group_sum(ssq[t], vec_per_head);
       } else {
-        rs = which == 0 ? full_q : full_k;
-      }
-      const bf16* wsrc = (which == 0 ? qw : kw) + (mode == 1 ? j8 * 8 : rem * 8);
-      float ww[8];
-      unpack8(*reinterpret_cast<const bf16x8*>(wsrc), ww);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) o[j] = f[t][j] * rs * ww[j];
-    } else {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) o[j] = f[t][j];
-    }
-    if (which < 2 && cosT != nullptr) {
-      const float* c = cosT + (int64_t)s * (dh / 2) + j8 * 4;
-      const float* sn = sinT + (int64_t)s * (dh / 2) + j8 * 4;
-#pragma unroll
-      for (int p = 0; p < 4; ++p) {
-        const float x0 = o[2 * p], x1 = o[2 * p + 1];
-        o[2 * p] = x0 * c[p] - x1 * sn[p];
-        o[2 * p + 1] = x0 * sn[p] + x1 * c[p];
+        block_sum_vals<TB>(ssq, red + parity * 32 * TB, nwarps);
+        parity ^= 1;
       }
     }
-    if (peers.world > 1) {
-      // the head <-> sequence exchange of sequence parallelism happens in this store: the head's
-      // owner receives the token at this rank's place in the full sequence, over NVLink
-      const int hp = heads / peers.world, g = h / hp, hl = h - g * hp;
-      bf16* dst = which == 0 ? peers.q[g] : (which == 1 ? peers.k[g] : peers.v[g]);
-      *reinterpret_cast<bf16x8*>(dst + (((int64_t)b * seq_total + seq_offset + s) * hp + hl) * dh + j8 * 8) =
-          pack8(o);
-    } else {
-      bf16* dst = which == 0 ? q : (which == 1 ? k : v);
-      // token-major destination [B, seq_total, H, Dh]: one token's heads are contiguous
-      *reinterpret_cast<bf16x8*>(dst + (((int64_t)b * seq_total + seq_offset + s) * heads + h) * dh + j8 * 8) =
-          pack8(o);
+#pragma unroll
+    for (int t = 0; t < TB; ++t) {
+      const int64_t tok = tb + t;
+      if (!act || tok >= tok_end) continue;
+      const int b = (int)(tok / seq), sidx = (int)(tok - (int64_t)b * seq);
+      float o[8];
+      unpack8(raw[t], o);
+      if (normed) {
+        const float rs = rsqrtf(ssq[t] / (float)(mode == 1 ? dh : dmodel) + eps);
+        if (mode == 1) {
+          if (j8 == 0) rstd_o[(tok * 2 + which) * heads + h] = rs;
+        } else if (i == 0) {
+          rstd_o[tok * 2 + which] = rs;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = o[j] * rs * ww[j];
+      }
+      if (which < 2 && cosT != nullptr) {
+        const float4 c = *reinterpret_cast<const float4*>(cosT + (int64_t)sidx * (dh / 2) + j8 * 4);
+        const float4 sn = *reinterpret_cast<const float4*>(sinT + (int64_t)sidx * (dh / 2) + j8 * 4);
+        const float cc[4] = {c.x, c.y, c.z, c.w}, sv[4] = {sn.x, sn.y, sn.z, sn.w};
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+          const float x0 = o[2 * p], x1 = o[2 * p + 1];
+          o[2 * p] = x0 * cc[p] - x1 * sv[p];
+          o[2 * p + 1] = x0 * sv[p] + x1 * cc[p];
+        }
+      }
+      const int64_t drow = (int64_t)b * seq_total + seq_offset + sidx;
+      if (peers.world > 1) {
+        // the head <-> sequence exchange of sequence parallelism happens in this store: the head's
+        // owner receives the token at this rank's place in the full sequence, over NVLink
+        *reinterpret_cast<bf16x8*>(dst_peer + (drow * hp + hl) * dh + j8 * 8) = pack8(o);
+      } else {
+        // token-major destination [B, seq_total, H, Dh]: one token's heads are contiguous
+        *reinterpret_cast<bf16x8*>(dst_local + (drow * heads + h) * dh + j8 * 8) = pack8(o);
+      }
     }
   }
+}
+
+// shared launch of the forward kernel (local or peer destinations)
+static void launch_qkv_fwd(const torch::Tensor& qkv, const bf16* qw, const bf16* kw, const float* cosT,
+                           const float* sinT, bf16* q, bf16* k, bf16* v, float* rstd, int b, int s, int heads,
+                           int dh, int mode, float eps, int seq_total, int seq_offset, const QkvPeers& peers) {
+  const int64_t tokens = (int64_t)b * s;
+  if (tokens == 0) return;
+  const int threads = (heads * dh / 8 + 31) / 32 * 32;
+  const int tpb = qkv_tokens_per_block(tokens);
+  dim3 grid((unsigned)((tokens + tpb - 1) / tpb), 3);
+  auto stream = at::cuda::getCurrentCUDAStream();
+  VRL_DISPATCH_COLS(threads, qkv_prepare_fwd_kernel<kMaxT><<<grid, threads, 0, stream>>>(
+      reinterpret_cast<const bf16*>(qkv.data_ptr()), qw, kw, cosT, sinT, q, k, v, rstd, tokens, s, heads, dh,
+      mode, eps, seq_total, seq_offset, tpb, peers));
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
+// head dims whose Dh / 8 lanes form a power-of-two group inside a warp, widths of at most 1024 owners
+static void check_qkv_geometry(int dmodel, int dh) {
+  const int vph = dh / 8;
+  TORCH_CHECK(dh % 8 == 0 && vph >= 1 && vph <= 32 && (vph & (vph - 1)) == 0, "unsupported head dim");
+  TORCH_CHECK(dmodel / 8 <= 1024, "model width too large for qkv_prepare");
 }
 
 std::vector<torch::Tensor> qkv_prepare_fwd(torch::Tensor qkv, c10::optional<torch::Tensor> qw,
@@ -856,8 +1182,7 @@ std::vector<torch::Tensor> qkv_prepare_fwd(torch::Tensor qkv, c10::optional<torc
   const c10::cuda::CUDAGuard guard(qkv.device());
   const int b = (int)qkv.size(0), s = (int)qkv.size(1);
   const int dmodel = (int)(qkv.size(2) / 3), dh = dmodel / (int)heads;
-  TORCH_CHECK(dh % 8 == 0 && kNormThreads % (dh / 8) == 0 && (dh / 8) <= 32, "unsupported head dim");
-  TORCH_CHECK(3 * dmodel / 8 <= kQkvVecLimit * kNormThreads, "model width too large for qkv_prepare");
+  check_qkv_geometry(dmodel, dh);
   int mode = 0;
   torch::Tensor qwc, kwc;
   if (qw.has_value()) {
@@ -892,17 +1217,13 @@ std::vector<torch::Tensor> qkv_prepare_fwd(torch::Tensor qkv, c10::optional<torc
   }
   auto rstd = torch::empty({(int64_t)b * s * 2 * (mode == 1 ? heads : 1)},
                            opt.dtype(torch::kFloat32));
-  auto stream = at::cuda::getCurrentCUDAStream();
-  VRL_DISPATCH_QKV(3 * dmodel / 8, qkv_prepare_fwd_kernel<T><<<b * s, kNormThreads, 0, stream>>>(
-      reinterpret_cast<const bf16*>(qkv.data_ptr()),
-      mode ? reinterpret_cast<const bf16*>(qwc.data_ptr()) : nullptr,
-      mode ? reinterpret_cast<const bf16*>(kwc.data_ptr()) : nullptr,
-      cos.has_value() ? cosc.data_ptr<float>() : nullptr,
-      cos.has_value() ? sinc.data_ptr<float>() : nullptr, reinterpret_cast<bf16*>(q.data_ptr()),
-      reinterpret_cast<bf16*>(k.data_ptr()), reinterpret_cast<bf16*>(v.data_ptr()),
-      rstd.data_ptr<float>(), s, (int)heads, dh, mode, (float)eps, (int)seq_total, (int)seq_offset,
-      QkvPeers{}));
-  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  launch_qkv_fwd(qkv, mode ? reinterpret_cast<const bf16*>(qwc.data_ptr()) : nullptr,
+                 mode ? reinterpret_cast<const bf16*>(kwc.data_ptr()) : nullptr,
+                 cos.has_value() ? cosc.data_ptr<float>() : nullptr,
+                 cos.has_value() ? sinc.data_ptr<float>() : nullptr, reinterpret_cast<bf16*>(q.data_ptr()),
+                 reinterpret_cast<bf16*>(k.data_ptr()), reinterpret_cast<bf16*>(v.data_ptr()),
+                 rstd.data_ptr<float>(), b, s, (int)heads, dh, mode, (float)eps, (int)seq_total,
+                 (int)seq_offset, QkvPeers{});
   return {q, k, v, rstd};
 }
 
@@ -924,8 +1245,7 @@ torch::Tensor qkv_prepare_fwd_peers(torch::Tensor qkv, c10::optional<torch::Tens
   const c10::cuda::CUDAGuard guard(qkv.device());
   const int b = (int)qkv.size(0), s = (int)qkv.size(1);
   const int dmodel = (int)(qkv.size(2) / 3), dh = dmodel / (int)heads;
-  TORCH_CHECK(dh % 8 == 0 && kNormThreads % (dh / 8) == 0 && (dh / 8) <= 32, "unsupported head dim");
-  TORCH_CHECK(3 * dmodel / 8 <= kQkvVecLimit * kNormThreads, "model width too large for qkv_prepare");
+  check_qkv_geometry(dmodel, dh);
   TORCH_CHECK(seq_offset >= 0 && seq_offset + s <= seq_total, "qkv_prepare_fwd_peers: sequence window out of range");
   int mode = 0;
   torch::Tensor qwc, kwc;
@@ -955,141 +1275,143 @@ torch::Tensor qkv_prepare_fwd_peers(torch::Tensor qkv, c10::optional<torch::Tens
     }
   }
   auto rstd = torch::empty({(int64_t)b * s * 2 * (mode == 1 ? heads : 1)}, qkv.options().dtype(torch::kFloat32));
-  auto stream = at::cuda::getCurrentCUDAStream();
-  VRL_DISPATCH_QKV(3 * dmodel / 8, qkv_prepare_fwd_kernel<T><<<b * s, kNormThreads, 0, stream>>>(
-      reinterpret_cast<const bf16*>(qkv.data_ptr()),
-      mode ? reinterpret_cast<const bf16*>(qwc.data_ptr()) : nullptr,
-      mode ? reinterpret_cast<const bf16*>(kwc.data_ptr()) : nullptr,
-      cos.has_value() ? cosc.data_ptr<float>() : nullptr,
-      cos.has_value() ? sinc.data_ptr<float>() : nullptr, nullptr, nullptr, nullptr,
-      rstd.data_ptr<float>(), s, (int)heads, dh, mode, (float)eps, (int)seq_total, (int)seq_offset, peers));
-  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  launch_qkv_fwd(qkv, mode ? reinterpret_cast<const bf16*>(qwc.data_ptr()) : nullptr,
+                 mode ? reinterpret_cast<const bf16*>(kwc.data_ptr()) : nullptr,
+                 cos.has_value() ? cosc.data_ptr<float>() : nullptr,
+                 cos.has_value() ? sinc.data_ptr<float>() : nullptr, nullptr, nullptr, nullptr,
+                 rstd.data_ptr<float>(), b, s, (int)heads, dh, mode, (float)eps, (int)seq_total,
+                 (int)seq_offset, peers);
   return rstd;
 }
 
-constexpr int kQkvBwdTokens = 16;
-
-template <int kQkvMaxVec>
-__global__ void __launch_bounds__(kNormThreads, 3)
+// Backward of the above, the same column-owner layout: thread i owns vector i of q, k or v
+// (blockIdx.y) over a run of tokens, four per pass.  The weight gradient of the norm is eight
+// registers per thread, combined over the heads in shared memory (per-head weights) or sent
+// straight to memory (full-width weights) once per block.
+template <int kMaxT>
+__global__ void __launch_bounds__(kMaxT)
 qkv_prepare_bwd_kernel(const bf16* __restrict__ gq, const bf16* __restrict__ gk,
                        const bf16* __restrict__ gv, const bf16* __restrict__ qkv,
                        const bf16* __restrict__ qw, const bf16* __restrict__ kw,
                        const float* __restrict__ cosT, const float* __restrict__ sinT,
                        const float* __restrict__ rstd, bf16* __restrict__ gqkv,
                        float* __restrict__ gqw, float* __restrict__ gkw, int64_t tokens, int seq,
-                       int heads, int dh, int mode, int seq_offset, int64_t gq_sb, int64_t gq_sh,
-                       int64_t gq_ss, int64_t gk_sb, int64_t gk_sh, int64_t gk_ss, int64_t gv_sb,
-                       int64_t gv_sh, int64_t gv_ss) {
-  extern __shared__ float wacc[];          // [2][wlen] parameter-gradient accumulators
-  __shared__ float red[32];
+                       int heads, int dh, int mode, int seq_offset, int tokens_per_block, int64_t gq_sb,
+                       int64_t gq_sh, int64_t gq_ss, int64_t gk_sb, int64_t gk_sh, int64_t gk_ss,
+                       int64_t gv_sb, int64_t gv_sh, int64_t gv_ss) {
+  constexpr int TB = kQkvTokensPerPass;
+  __shared__ float red[2 * 32 * TB];
+  __shared__ float wacc[256];                  // per-head weights: Dh <= 256 column sums over the heads
+  const int i = threadIdx.x, nwarps = blockDim.x >> 5;
+  const int which = blockIdx.y;
   const int dmodel = heads * dh;
-  const int wlen = mode == 1 ? dh : dmodel;
-  const int vec_per_head = dh / 8, vec_per_which = dmodel / 8, nvec = 3 * vec_per_which;
-  if (mode != 0) {
-    for (int i = threadIdx.x; i < 2 * wlen; i += blockDim.x) wacc[i] = 0.f;
+  const int vec_per_head = dh / 8, vec_per_which = dmodel / 8;
+  const bool act = i < vec_per_which;
+  const int h = i / vec_per_head, j8 = i - h * vec_per_head;
+  const bool normed = which < 2 && mode != 0;
+  const bf16* gsrc = which == 0 ? gq : (which == 1 ? gk : gv);
+  const int64_t sb = which == 0 ? gq_sb : (which == 1 ? gk_sb : gv_sb);
+  const int64_t sh = which == 0 ? gq_sh : (which == 1 ? gk_sh : gv_sh);
+  const int64_t ss = which == 0 ? gq_ss : (which == 1 ? gk_ss : gv_ss);
+  float ww[8], wg[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) { ww[j] = 1.f; wg[j] = 0.f; }
+  if (act && normed)
+    unpack8(*reinterpret_cast<const bf16x8*>((which == 0 ? qw : kw) + (mode == 1 ? j8 * 8 : i * 8)), ww);
+  if (normed && mode == 1) {
+    for (int t = i; t < dh; t += blockDim.x) wacc[t] = 0.f;
+    __syncthreads();
   }
-  __syncthreads();
-  float wg[kQkvMaxVec][8];
+  const int64_t tok_begin = (int64_t)blockIdx.x * tokens_per_block;
+  const int64_t tok_end = min(tok_begin + (int64_t)tokens_per_block, tokens);
+  int parity = 0;
+  for (int64_t tb = tok_begin; tb < tok_end; tb += TB) {
+    bf16x8 graw[TB], xraw[TB];
+    float rs[TB];
 #pragma unroll
-  for (int t = 0; t < kQkvMaxVec; ++t)
-#pragma unroll
-    for (int j = 0; j < 8; ++j) wg[t][j] = 0.f;
-  const int64_t tok0 = (int64_t)blockIdx.x * kQkvBwdTokens;
-  for (int64_t tok = tok0; tok < tok0 + kQkvBwdTokens && tok < tokens; ++tok) {
-    const int b = (int)(tok / seq), s = (int)(tok % seq);
-    const bf16x8* src = reinterpret_cast<const bf16x8*>(qkv + tok * 3 * dmodel);
-    bf16x8* dst = reinterpret_cast<bf16x8*>(gqkv + tok * 3 * dmodel);
-    float gn[kQkvMaxVec][8], xh[kQkvMaxVec][8];
-    float dot[kQkvMaxVec];
-    float tot_q = 0.f, tot_k = 0.f;
-#pragma unroll
-    for (int t = 0; t < kQkvMaxVec; ++t) {
-      const int i = threadIdx.x + t * kNormThreads;
-      dot[t] = 0.f;
-      if (i >= nvec) continue;
-      const int which = i / vec_per_which;
-      const int rem = i - which * vec_per_which;
-      const int h = rem / vec_per_head, j8 = rem - h * vec_per_head;
-      const bf16* gsrc = which == 0 ? gq : (which == 1 ? gk : gv);
-      const int64_t sb = which == 0 ? gq_sb : (which == 1 ? gk_sb : gv_sb);
-      const int64_t sh = which == 0 ? gq_sh : (which == 1 ? gk_sh : gv_sh);
-      const int64_t ss = which == 0 ? gq_ss : (which == 1 ? gk_ss : gv_ss);
-      float g[8];
-      unpack8(*reinterpret_cast<const bf16x8*>(gsrc + b * sb + h * sh + (int64_t)(seq_offset + s) * ss + j8 * 8), g);
-      if (which == 2) {
-        dst[i] = pack8(g);
-        continue;
-      }
-      if (cosT != nullptr) {     // transpose of the rotation
-        const float* c = cosT + (int64_t)s * (dh / 2) + j8 * 4;
-        const float* sn = sinT + (int64_t)s * (dh / 2) + j8 * 4;
-#pragma unroll
-        for (int p = 0; p < 4; ++p) {
-          const float g0 = g[2 * p], g1 = g[2 * p + 1];
-          g[2 * p] = g0 * c[p] + g1 * sn[p];
-          g[2 * p + 1] = -g0 * sn[p] + g1 * c[p];
+    for (int t = 0; t < TB; ++t) {
+      const int64_t tok = tb + t;
+      graw[t].u = make_uint4(0u, 0u, 0u, 0u);
+      xraw[t].u = make_uint4(0u, 0u, 0u, 0u);
+      rs[t] = 0.f;
+      if (act && tok < tok_end) {
+        const int b = (int)(tok / seq), sidx = (int)(tok - (int64_t)b * seq);
+        graw[t] = *reinterpret_cast<const bf16x8*>(gsrc + b * sb + h * sh + (int64_t)(seq_offset + sidx) * ss + j8 * 8);
+        if (normed) {
+          xraw[t] = *reinterpret_cast<const bf16x8*>(qkv + (tok * 3 + which) * dmodel + i * 8);
+          rs[t] = mode == 1 ? rstd[(tok * 2 + which) * heads + h] : rstd[tok * 2 + which];
         }
       }
-      if (mode == 0) {
-        dst[i] = pack8(g);
-        continue;
-      }
-      float xv[8], ww[8];
-      unpack8(src[i], xv);
-      const float rs = mode == 1 ? rstd[(tok * 2 + which) * heads + h] : rstd[tok * 2 + which];
-      const int woff = mode == 1 ? j8 * 8 : rem * 8;
-      unpack8(*reinterpret_cast<const bf16x8*>((which == 0 ? qw : kw) + woff), ww);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        xh[t][j] = xv[j] * rs;
-        gn[t][j] = g[j] * ww[j];
-        dot[t] += gn[t][j] * xh[t][j];
-        wg[t][j] += g[j] * xh[t][j];
-      }
-      if (which == 0) tot_q += dot[t]; else tot_k += dot[t];
     }
-    float mean_q = 0.f, mean_k = 0.f;
-    if (mode == 2) {
-      mean_q = block_sum(tot_q, red) / (float)dmodel;
-      mean_k = block_sum(tot_k, red) / (float)dmodel;
+    float g[TB][8], dot[TB];
+#pragma unroll
+    for (int t = 0; t < TB; ++t) {
+      unpack8(graw[t], g[t]);
+      dot[t] = 0.f;
+      const int64_t tok = tb + t;
+      if (which < 2 && cosT != nullptr && act && tok < tok_end) {     // transpose of the rotation
+        const int sidx = (int)(tok % seq);
+        const float4 c = *reinterpret_cast<const float4*>(cosT + (int64_t)sidx * (dh / 2) + j8 * 4);
+        const float4 sn = *reinterpret_cast<const float4*>(sinT + (int64_t)sidx * (dh / 2) + j8 * 4);
+        const float cc[4] = {c.x, c.y, c.z, c.w}, sv[4] = {sn.x, sn.y, sn.z, sn.w};
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+          const float g0 = g[t][2 * p], g1 = g[t][2 * p + 1];
+          g[t][2 * p] = g0 * cc[p] + g1 * sv[p];
+          g[t][2 * p + 1] = -g0 * sv[p] + g1 * cc[p];
+        }
+      }
+      if (normed) {
+        float xv[8];
+        unpack8(xraw[t], xv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float xh = xv[j] * rs[t];
+          dot[t] += g[t][j] * ww[j] * xh;
+          wg[j] += g[t][j] * xh;
+        }
+      }
+    }
+    if (normed) {                                   // uniform over the block
+      if (mode == 1) {
+#pragma unroll
+        for (int t = 0; t < TB; ++t) dot[t] = group_sum(dot[t], vec_per_head) / (float)dh;
+      } else {
+        block_sum_vals<TB>(dot, red + parity * 32 * TB, nwarps);
+        parity ^= 1;
+#pragma unroll
+        for (int t = 0; t < TB; ++t) dot[t] /= (float)dmodel;
+      }
     }
 #pragma unroll
-    for (int t = 0; t < kQkvMaxVec; ++t) {
-      const int i = threadIdx.x + t * kNormThreads;
-      const float head_dot = (mode == 1) ? group_sum(dot[t], vec_per_head) : 0.f;
-      if (i >= nvec || mode == 0) continue;
-      const int which = i / vec_per_which;
-      if (which == 2) continue;
-      const int rem = i - which * vec_per_which;
-      const int h = rem / vec_per_head;
-      const float rs = mode == 1 ? rstd[(tok * 2 + which) * heads + h] : rstd[tok * 2 + which];
-      const float m = mode == 1 ? head_dot / (float)dh : (which == 0 ? mean_q : mean_k);
+    for (int t = 0; t < TB; ++t) {
+      const int64_t tok = tb + t;
+      if (!act || tok >= tok_end) continue;
       float o[8];
+      if (normed) {
+        float xv[8];
+        unpack8(xraw[t], xv);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) o[j] = rs * (gn[t][j] - xh[t][j] * m);
-      dst[i] = pack8(o);
+        for (int j = 0; j < 8; ++j) o[j] = rs[t] * (g[t][j] * ww[j] - xv[j] * rs[t] * dot[t]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = g[t][j];
+      }
+      *reinterpret_cast<bf16x8*>(gqkv + (tok * 3 + which) * dmodel + i * 8) = pack8(o);
     }
   }
-  if (mode != 0) {
+  if (!normed) return;
+  float* gw = which == 0 ? gqw : gkw;
+  if (mode == 1) {
+    if (act) {
 #pragma unroll
-    for (int t = 0; t < kQkvMaxVec; ++t) {
-      const int i = threadIdx.x + t * kNormThreads;
-      if (i >= nvec) continue;
-      const int which = i / vec_per_which;
-      if (which == 2) continue;
-      const int rem = i - which * vec_per_which;
-      const int j8 = rem % vec_per_head;
-      const int woff = mode == 1 ? j8 * 8 : rem * 8;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) atomicAdd(&wacc[which * wlen + woff + j], wg[t][j]);
+      for (int j = 0; j < 8; ++j) atomicAdd(&wacc[j8 * 8 + j], wg[j]);
     }
-  }
-  __syncthreads();
-  if (mode != 0) {
-    for (int i = threadIdx.x; i < wlen; i += blockDim.x) {
-      atomicAdd(gqw + i, wacc[i]);
-      atomicAdd(gkw + i, wacc[wlen + i]);
-    }
+    __syncthreads();
+    for (int t = i; t < dh; t += blockDim.x) atomicAdd(gw + t, wacc[t]);
+  } else if (act) {
+    red_add_v4(gw + i * 8, wg);
+    red_add_v4(gw + i * 8 + 4, wg + 4);
   }
 }
 
@@ -1143,10 +1465,13 @@ std::vector<torch::Tensor> qkv_prepare_bwd(torch::Tensor gq, torch::Tensor gk, t
   auto gqw = torch::zeros({mode ? wlen : 1}, qkv.options().dtype(torch::kFloat32));
   auto gkw = torch::zeros_like(gqw);
   const int64_t tokens = (int64_t)b * s;
-  const size_t smem = mode ? sizeof(float) * 2 * wlen : 0;
+  check_qkv_geometry(dmodel, dh);
+  if (tokens == 0) return {gqkv, gqw, gkw};
   auto stream = at::cuda::getCurrentCUDAStream();
-  const unsigned blocks = (unsigned)((tokens + kQkvBwdTokens - 1) / kQkvBwdTokens);
-  VRL_DISPATCH_QKV(3 * dmodel / 8, qkv_prepare_bwd_kernel<T><<<blocks, kNormThreads, smem, stream>>>(
+  const int threads = (dmodel / 8 + 31) / 32 * 32;
+  const int tpb = qkv_tokens_per_block(tokens);
+  dim3 grid((unsigned)((tokens + tpb - 1) / tpb), 3);
+  VRL_DISPATCH_COLS(threads, qkv_prepare_bwd_kernel<kMaxT><<<grid, threads, 0, stream>>>(
       reinterpret_cast<const bf16*>(gq.data_ptr()), reinterpret_cast<const bf16*>(gk.data_ptr()),
       reinterpret_cast<const bf16*>(gv.data_ptr()), reinterpret_cast<const bf16*>(qkv.data_ptr()),
       mode ? reinterpret_cast<const bf16*>(qwc.data_ptr()) : nullptr,
@@ -1154,7 +1479,7 @@ std::vector<torch::Tensor> qkv_prepare_bwd(torch::Tensor gq, torch::Tensor gk, t
       cos.has_value() ? cosc.data_ptr<float>() : nullptr,
       cos.has_value() ? sinc.data_ptr<float>() : nullptr, rstd.data_ptr<float>(),
       reinterpret_cast<bf16*>(gqkv.data_ptr()), gqw.data_ptr<float>(), gkw.data_ptr<float>(),
-      tokens, s, (int)heads, dh, mode, (int)seq_offset, gq.stride(0), gq.stride(1), gq.stride(2),
+      tokens, s, (int)heads, dh, mode, (int)seq_offset, tpb, gq.stride(0), gq.stride(1), gq.stride(2),
       gk.stride(0), gk.stride(1), gk.stride(2), gv.stride(0), gv.stride(1), gv.stride(2)));
   C10_CUDA_KERNEL_LAUNCH_CHECK();
   return {gqkv, gqw, gkw};

@@ -45,6 +45,11 @@ std::vector<torch::Tensor> sde_step_fwd(torch::Tensor v, torch::Tensor x, torch:
                                         c10::optional<torch::Tensor> prev_sample,
                                         c10::optional<torch::Tensor> noise, bool deterministic,
                                         bool gaussian);
+void sde_rollout_step(torch::Tensor pred, bool has_cfg, double guidance, int64_t cfg_form,
+                      torch::Tensor path, int64_t step, torch::Tensor a, torch::Tensor b,
+                      torch::Tensor scale, torch::Tensor dt, c10::optional<torch::Tensor> noise,
+                      int64_t seed, int64_t offset, torch::Tensor log_probs, bool deterministic,
+                      bool gaussian);
 std::vector<torch::Tensor> sde_step_bwd(torch::Tensor prev, torch::Tensor mean, torch::Tensor a,
                                         torch::Tensor b, torch::Tensor scale, torch::Tensor g_logp,
                                         c10::optional<torch::Tensor> g_mean, bool gaussian);
@@ -129,6 +134,10 @@ std::vector<torch::Tensor> sample_tokens(torch::Tensor cond, torch::Tensor uncon
                                          double cfg_weight, double temperature);
 torch::Tensor decode_attention(torch::Tensor q, torch::Tensor k_cache, torch::Tensor v_cache,
                                torch::Tensor valid, int64_t length, double scale);
+torch::Tensor decode_qkv_rope_append(torch::Tensor qkv, torch::Tensor cos, torch::Tensor sin, torch::Tensor pos,
+                                     torch::Tensor k_cache, torch::Tensor v_cache, int64_t heads);
+torch::Tensor swiglu_rows(torch::Tensor gate_up);
+torch::Tensor add_rmsnorm_rows(torch::Tensor x, c10::optional<torch::Tensor> delta, torch::Tensor w, double eps);
 torch::Tensor group_advantages(torch::Tensor rewards, torch::Tensor group_ids, double eps, double clip,
                                bool global_std);
 

@@ -19,7 +19,7 @@ from typing import Any
 
 import torch
 
-from visionrl_b200.algorithms.flow_matching import sde_step_with_logprob
+from visionrl_b200.algorithms.flow_matching import sde_step_with_logprob, step_coefficients
 from visionrl_b200.engine.core.protocols import PipelineChunkResult
 from visionrl_b200.engine.core.types import (
     GenerationMetrics, GenerationRequest, GenerationSampleSpec, OutputBatch,
@@ -77,6 +77,38 @@ def _chunk_generator(device, sample_start: int, seed: int | None, same_latent: b
     return gen
 
 
+# The fused rollout step (guidance combine + SDE step + log-density + trajectory write in one
+# kernel, noise from Philox keyed by the chunk's seed) is used whenever the policy can hand over its
+# raw transformer output; set to False to force the generic path (separate combine, torch.randn).
+FUSED_ROLLOUT_STEP = True
+
+
+def _fused_step_available(policy: Any, path: torch.Tensor) -> bool:
+    from visionrl_b200.ops import _ext
+
+    n = path[0, 0].numel()
+    return (FUSED_ROLLOUT_STEP and path.is_cuda and n % 4 == 0 and path.shape[0] <= 65535
+            and callable(getattr(policy, "forward_step_raw", None))
+            and type(policy).forward_step is _base_forward_step(policy)
+            and _ext.kernels_enabled() and _ext.has("sde_rollout_step"))
+
+
+def _base_forward_step(policy: Any):
+    """``forward_step`` of the class that defines ``forward_step_raw``: a subclass that overrides
+    ``forward_step`` (other guidance algebra, preconditioning) must take the generic path."""
+    for klass in type(policy).__mro__:
+        if "forward_step_raw" in klass.__dict__:
+            return klass.__dict__.get("forward_step")
+    return None
+
+
+def _philox_seed(config: "DiffusionDenoiseConfig") -> int:
+    if config.seed is not None:
+        return (int(config.seed) + int(config.sample_start)) & 0x7FFFFFFFFFFFFFFF
+    # unseeded requests follow the process-wide generator, like torch.randn would
+    return int(torch.randint(0, 2**62, (1,), dtype=torch.int64).item())
+
+
 def run_diffusion_denoise_chunk(*, policy: Any, request: Any, encoded: dict[str, Any],
                                 config: DiffusionDenoiseConfig,
                                 prepare_kwargs: dict[str, Any] | None = None) -> DiffusionChunkResult:
@@ -89,12 +121,30 @@ def run_diffusion_denoise_chunk(*, policy: Any, request: Any, encoded: dict[str,
     path = torch.empty((b, steps + 1, *latents0.shape[1:]), dtype=torch.float32, device=device)
     path[:, 0] = latents0
     log_probs = torch.empty((b, steps), dtype=torch.float32, device=device)
+    fused = _fused_step_available(policy, path)
+    if fused:
+        from visionrl_b200.ops import _ext
+
+        ext = _ext.load()
+        seed = _philox_seed(config)
+        sigmas = state.scheduler.sigmas.to(device)
+        state.scheduler.sigmas = sigmas
 
     with torch.no_grad():
         for i in range(steps):
             state.latents = path[:, i]
-            noise_pred = policy.forward_step(state, i)["noise_pred"]
             stochastic = config.sde_window is None or config.sde_window[0] <= i < config.sde_window[1]
+            if fused:
+                pred, has_cfg = policy.forward_step_raw(state, i)
+                index = torch.full((b,), i, dtype=torch.long, device=device)
+                ca, cb, _std, scale, _sq, dt = step_coefficients(sigmas, index, config.noise_level,
+                                                                 config.sde_type)
+                ext.sde_rollout_step(pred.contiguous(), bool(has_cfg), float(state.guidance_scale),
+                                     int(getattr(policy, "cfg_form", 0)), path, i, ca.contiguous(),
+                                     cb.contiguous(), scale.contiguous(), dt.contiguous(), None, seed,
+                                     4 * i, log_probs, not stochastic, config.sde_type == "sde")
+                continue
+            noise_pred = policy.forward_step(state, i)["noise_pred"]
             res = sde_step_with_logprob(
                 state.scheduler, noise_pred, state.timesteps[i].reshape(1).expand(b), path[:, i],
                 generator=generator if stochastic else None, deterministic=not stochastic,

@@ -248,23 +248,34 @@ class NativeFlowPolicy(DiffusionPolicy):
             do_cfg=request.guidance_scale > 1.0, seed=int(seed), extra=dict(kwargs),
         )
 
-    def forward_step(self, state: FlowSamplingState, step_idx: int) -> dict[str, Any]:
+    # how the guidance combine reads: 0 = uncond + g (cond - uncond), 1 = cond + g (cond - uncond)
+    cfg_form = 0
+
+    def forward_step_raw(self, state: FlowSamplingState, step_idx: int):
+        """The transformer output of one step BEFORE the guidance combine: ``(pred, do_cfg)`` with
+        ``pred`` = ``[uncond ; cond]`` stacked along the batch when guidance is on, in the
+        transformer's own dtype.  The rollout loop hands this to the fused SDE-step kernel, which
+        does the combine, the step, the log-density and the trajectory write in one pass."""
         t = state.timesteps[step_idx]
         b = state.latents.shape[0]
         t_batch = t.expand(b) if t.ndim == 0 else t
-        if state.do_cfg:
-            lat = torch.cat([state.latents, state.latents], dim=0)
-            emb = torch.cat([state.negative_prompt_embeds, state.prompt_embeds], dim=0)
-            pooled = None
-            if state.pooled_prompt_embeds is not None:
-                pooled = torch.cat([state.negative_pooled_prompt_embeds,
-                                    state.pooled_prompt_embeds], dim=0)
-            out = self._call_transformer(lat, torch.cat([t_batch, t_batch]), emb, pooled, state)
+        if not state.do_cfg:
+            return self._call_transformer(state.latents, t_batch, state.prompt_embeds,
+                                          state.pooled_prompt_embeds, state), False
+        lat = torch.cat([state.latents, state.latents], dim=0)
+        emb = torch.cat([state.negative_prompt_embeds, state.prompt_embeds], dim=0)
+        pooled = None
+        if state.pooled_prompt_embeds is not None:
+            pooled = torch.cat([state.negative_pooled_prompt_embeds, state.pooled_prompt_embeds], dim=0)
+        return self._call_transformer(lat, torch.cat([t_batch, t_batch]), emb, pooled, state), True
+
+    def forward_step(self, state: FlowSamplingState, step_idx: int) -> dict[str, Any]:
+        out, do_cfg = self.forward_step_raw(state, step_idx)
+        if do_cfg:
             uncond, cond = out.float().chunk(2, dim=0)
             noise_pred = self._combine_cfg(cond, uncond, state.guidance_scale)
         else:
-            cond = self._call_transformer(state.latents, t_batch, state.prompt_embeds,
-                                          state.pooled_prompt_embeds, state).float()
+            cond = out.float()
             uncond = torch.zeros_like(cond)
             noise_pred = cond
         return {"noise_pred": noise_pred, "noise_pred_cond": cond, "noise_pred_uncond": uncond}

@@ -196,10 +196,50 @@ class LlamaDecoder(AdapterMixin, nn.Module):
         """
         cache.valid.index_fill_(1, pos, True)
         cos, sin = rope_tables(pos, self.head_dim, self.cfg.rope_theta)
+        if self._fused_decode_ok(embeds):
+            return self._decode_step_fused(embeds, cache, pos, cos, sin)
         x = embeds.unsqueeze(1)
         for i, layer in enumerate(self.layers):
             x = layer.decode_at(x, cos, sin, cache, i, pos)
         return self.norm(x)[:, 0]
+
+    def _fused_decode_ok(self, embeds) -> bool:
+        from visionrl_b200.ops import _ext
+
+        return (embeds.is_cuda and embeds.dtype == torch.bfloat16 and embeds.dim() == 2
+                and not torch.is_grad_enabled() and self.head_dim == 128
+                and self.cfg.hidden_size % 8 == 0 and self.cfg.ffn_dim % 8 == 0
+                and _ext.kernels_enabled() and _ext.has("decode_qkv_rope_append"))
+
+    def _decode_step_fused(self, embeds, cache: KVCache, pos, cos, sin):
+        """The decode step with its glue folded into three kernels per layer: residual add + RMSNorm,
+        RoPE + cache append on the QKV output, SwiGLU.  A layer is then 13 launches (four
+        projections of two launches each, attention, and the glue) instead of some forty, which
+        is what a step of 32 rows — launch latency, not bandwidth — is made of."""
+        from visionrl_b200.ops import _ext
+
+        ext = _ext.load()
+        rows, d = embeds.shape
+        eps = float(self.norm.eps)
+        cos1, sin1 = cos.reshape(-1).contiguous(), sin.reshape(-1).contiguous()
+        x = embeds.clone()                       # updated in place by the fused residual adds
+        delta = None
+        heads = self.layers[0].attn.heads
+
+        def weight(norm):
+            w = norm.weight
+            return w if w.dtype == torch.bfloat16 else w.to(torch.bfloat16)
+
+        for i, layer in enumerate(self.layers):
+            h = ext.add_rmsnorm_rows(x, delta, weight(layer.attn_norm), float(layer.attn_norm.eps))
+            qkv = layer.attn.qkv(h)
+            q = ext.decode_qkv_rope_append(qkv.contiguous(), cos1, sin1, pos, cache.data[i, 0],
+                                           cache.data[i, 1], heads)
+            o = attn_ops.decode_attention(q, cache.data[i, 0], cache.data[i, 1], cache.valid, cache.max_len)
+            a = layer.attn.out(o.view(rows, d))
+            h2 = ext.add_rmsnorm_rows(x, a.contiguous(), weight(layer.mlp_norm), float(layer.mlp_norm.eps))
+            delta = layer.down(ext.swiglu_rows(layer.gate_up(h2).contiguous())).contiguous()
+        return ext.add_rmsnorm_rows(x, delta, weight(self.norm), eps)
 
     def decode_step(self, embeds, cache: KVCache, rows=None, position: int | None = None):
         """``embeds[R, D]`` for the next position → hidden ``[R, D]``.

@@ -2,14 +2,17 @@
 
 ``token_log_probs(logits, ids, T)`` = ``log_softmax(logits / T)[ids]`` in fp32.
 ``fused_head_log_probs(hidden, weight, bias, ids, T)`` computes the same quantity
-from the pre-head hidden states, tiling the head GEMM over the vocabulary with an
-online log-sum-exp so the ``[rows, vocab]`` fp32 logits never exist in HBM.
+from the pre-head hidden states with the log-sum-exp folded into the head GEMM's epilogue,
+so no fp32 logits exist in HBM.
 """
 
 from __future__ import annotations
 
 import torch
 import torch.nn.functional as F
+
+
+_CHUNKED_FOLD = False      # tests flip this to compare the two kernel forms
 
 
 def token_log_probs_reference(logits, ids, temperature: float = 1.0):
@@ -58,13 +61,64 @@ def fused_head_log_probs_reference(hidden, weight, bias, ids, temperature: float
     return token_log_probs_reference(logits, flat_ids, 1.0).view(ids.shape)
 
 
+class _HeadLogProbFn(torch.autograd.Function):
+    """Head GEMM with the log-sum-exp folded into its epilogue.
+
+    Forward: ONE tcgen05 GEMM over the whole vocabulary; each epilogue thread holds 64 consecutive
+    logits of one row and reduces them to (max, exponential sum, target value), so 8 bytes per row
+    and 64 columns reach memory instead of 256 bytes of fp32 logits; a one-thread-per-row kernel
+    merges the partials.  Backward: per vocabulary chunk the product is recomputed with an epilogue
+    that writes ``g/T (onehot - softmax)`` as bf16 straight away, which feeds the two gradient
+    GEMMs.  No fp32 logits exist in memory in either pass.
+    """
+
+    @staticmethod
+    def forward(ctx, hidden, weight, bias, ids, temperature, chunk):
+        from visionrl_b200.ops import _ext
+
+        h = hidden.reshape(-1, hidden.shape[-1]).contiguous()
+        flat_ids = ids.reshape(-1).contiguous()
+        logp, lse = _ext.load().head_logprob_fwd(h, weight.contiguous(), bias, flat_ids, float(temperature))
+        ctx.save_for_backward(h, weight, bias if bias is not None else h.new_zeros(0), flat_ids, lse)
+        ctx.has_bias = bias is not None
+        ctx.temperature, ctx.chunk = float(temperature), int(chunk)
+        ctx.hidden_shape = hidden.shape
+        return logp.view(ids.shape)
+
+    @staticmethod
+    def backward(ctx, g):
+        from visionrl_b200.ops import _ext
+        from visionrl_b200.ops.linear import gemm_nn, gemm_tn
+
+        ext = _ext.load()
+        h, weight, bias, flat_ids, lse = ctx.saved_tensors
+        bias = bias if ctx.has_bias else None
+        gflat = g.reshape(-1).contiguous().float()
+        vocab = weight.shape[0]
+        need_w = ctx.needs_input_grad[1]
+        gh = torch.zeros(h.shape, device=h.device, dtype=torch.float32)
+        gw = torch.empty_like(weight) if need_w else None
+        gb = torch.empty_like(bias) if (bias is not None and ctx.needs_input_grad[2]) else None
+        for c0 in range(0, vocab, ctx.chunk):
+            c1 = min(vocab, c0 + ctx.chunk)
+            dl = ext.head_softmax_grad(h, weight[c0:c1], None if bias is None else bias[c0:c1], flat_ids,
+                                       lse, gflat, c0, ctx.temperature)
+            gh += gemm_nn(dl, weight[c0:c1]).float()
+            if need_w:
+                gw[c0:c1] = gemm_tn(dl, h)
+            if gb is not None:
+                gb[c0:c1] = ext.colsum(dl).to(gb.dtype)
+        return gh.to(h.dtype).view(ctx.hidden_shape), gw, gb, None, None, None
+
+
 class _FusedHeadLogProbFn(torch.autograd.Function):
-    """Head GEMM tiled over the vocabulary with an online log-sum-exp.
+    """The same quantity with the fold done by a second kernel per vocabulary chunk (kept for
+    extension builds without the epilogue form, and as a cross-check of it).
 
     Forward: for every vocabulary chunk the tcgen05 GEMM writes fp32 logits ``[rows, chunk]``,
     one kernel folds them into the running (max, sum) and picks up the target logit.  Backward
     recomputes each chunk, turns it into ``g/T (onehot - softmax)`` in bf16 and feeds the two
-    gradient GEMMs, so neither pass ever holds ``[rows, vocab]`` logits.
+    gradient GEMMs.
     """
 
     @staticmethod
@@ -124,5 +178,7 @@ def fused_head_log_probs(hidden, weight, bias, ids, temperature: float = 1.0, ch
     if (hidden.is_cuda and hidden.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
             and hidden.shape[-1] % 8 == 0 and weight.shape[0] % 8 == 0 and chunk % 8 == 0
             and _ext.kernels_enabled() and _ext.has("lse_chunk_update")):
+        if _ext.has("head_logprob_fwd") and hidden.shape[-1] % 8 == 0 and not _CHUNKED_FOLD:
+            return _HeadLogProbFn.apply(hidden, weight, bias, ids, temperature, chunk)
         return _FusedHeadLogProbFn.apply(hidden, weight, bias, ids, temperature, chunk)
     return fused_head_log_probs_reference(hidden, weight, bias, ids, temperature)

@@ -47,11 +47,35 @@ def bench_gemm(args) -> dict:
 
     ext = _ext.load()
     m, n, k = args.m, args.n, args.k
+    flush = _flush_buffer(not args.no_flush)
+    act = {"none": 0, "gelu": 1, "silu": 2}[args.act]
+    if args.layout != "nt":
+        # the two backward forms of a linear layer: nn = dX = dY[M,K] @ W[K,N] (B row-major),
+        # tn = dW = dY[K,M].T @ X[K,N] (both operands row-major over the contraction)
+        a = torch.randn((m, k) if args.layout == "nn" else (k, m), device="cuda", dtype=torch.bfloat16)
+        b = torch.randn(k, n, device="cuda", dtype=torch.bfloat16) * 0.02
+        a_mn = args.layout == "tn"
+
+        def own_b():
+            return ext.gemm_bf16(a, b, None, None, None, 0, 0, a_mn, True, False)
+
+        def lib_b():
+            return (a.t() if a_mn else a) @ b
+
+        flops = 2.0 * m * n * k
+        t_lib = _time(lib_b, args.iters, args.warmup, flush)
+        t_own = _time(own_b, args.iters, args.warmup, flush)
+        err = (own_b().float() - lib_b().float()).abs().max().item() / max(lib_b().float().abs().max().item(), 1e-6)
+        out = {"kernel": "gemm_bf16", "layout": args.layout, "m": m, "n": n, "k": k,
+               "cublas_ms": round(t_lib, 4), "cublas_tflops": round(flops / t_lib / 1e9, 1),
+               "ms": round(t_own, 4), "tflops": round(flops / t_own / 1e9, 1),
+               "max_rel_diff_vs_cublas": round(err, 5), "status": int(ext.gemm_last_status())}
+        if args.peak_tflops:
+            out["frac_of_measured_peak"] = round(out["tflops"] / args.peak_tflops, 3)
+        return out
     a = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
     w = torch.randn(n, k, device="cuda", dtype=torch.bfloat16) * 0.02
     bias = torch.randn(n, device="cuda", dtype=torch.bfloat16) if args.bias else None
-    flush = _flush_buffer(not args.no_flush)
-    act = {"none": 0, "gelu": 1, "silu": 2}[args.act]
 
     def own():
         return ext.gemm_bf16(a, w, bias, None, None, act, 1, False, False, False)
@@ -120,6 +144,46 @@ def bench_adaln(args) -> dict:
            "gbs": round(moved / t / 1e6, 1)}
     if args.peak_gbs:
         out["frac_of_measured_peak"] = round(out["gbs"] / args.peak_gbs, 3)
+    return out
+
+
+def bench_rowwise(args) -> dict:
+    """The bandwidth-bound row kernels of a transformer block at one shape: adaLN forward/backward,
+    QKV post-processing forward/backward (per-head RMS norm), gated-residual backward.  GB/s counts
+    the tensors each kernel must read and write once."""
+    from visionrl_b200.ops import _ext
+
+    ext = _ext.load()
+    b, s, d, heads = args.batch, args.seq, args.dim, args.heads
+    dh = d // heads
+    dev, bf = "cuda", torch.bfloat16
+    x = torch.randn(b, s, d, device=dev, dtype=bf)
+    gy = torch.randn(b, s, d, device=dev, dtype=bf)
+    mod = torch.randn(b, 3 * d, device=dev, dtype=bf) * 0.1
+    shift, scale, gate = mod[:, :d], mod[:, d:2 * d], mod[:, 2 * d:]
+    qkv = torch.randn(b, s, 3 * d, device=dev, dtype=bf)
+    qw = torch.ones(dh, device=dev, dtype=bf)
+    kw = torch.ones(dh, device=dev, dtype=bf)
+    flush = _flush_buffer(not args.no_flush)
+    _, mean, rstd = ext.adaln_fwd(x, shift, scale, 1e-6)
+    q, k, v, qr = ext.qkv_prepare_fwd(qkv, qw, kw, None, None, heads, 1e-6, None, None, None, 0)
+    gq, gk, gv = (torch.randn_like(q).permute(0, 2, 1, 3) for _ in range(3))      # [B, H, S, Dh] views
+    row = x.numel() * 2
+    cases = {
+        "adaln_fwd": (lambda: ext.adaln_fwd(x, shift, scale, 1e-6), 2 * row),
+        "adaln_bwd": (lambda: ext.adaln_bwd(gy, x, scale, mean, rstd), 3 * row),
+        "qkv_prepare_fwd": (lambda: ext.qkv_prepare_fwd(qkv, qw, kw, None, None, heads, 1e-6, None, None, None, 0),
+                            6 * row),
+        "qkv_prepare_bwd": (lambda: ext.qkv_prepare_bwd(gq, gk, gv, qkv, qw, kw, None, None, qr, heads, 0),
+                            8 * row),          # g (3), q and k inputs (2), d(qkv) (3)
+        "gate_residual_bwd": (lambda: ext.gate_residual_bwd(gy, x, gate), 3 * row),
+    }
+    out = {"kernel": "rowwise", "batch": b, "seq": s, "dim": d, "heads": heads}
+    for name, (fn, moved) in cases.items():
+        t = _time(fn, args.iters, args.warmup, flush)
+        out[name] = {"ms": round(t, 4), "gbs": round(moved / t / 1e6, 1)}
+        if args.peak_gbs:
+            out[name]["frac_of_measured_peak"] = round(moved / t / 1e6 / args.peak_gbs, 3)
     return out
 
 
@@ -227,6 +291,8 @@ def main(argv=None) -> int:
     g.add_argument("--k", type=int, default=1536)
     g.add_argument("--act", default="none", choices=["none", "gelu", "silu"])
     g.add_argument("--bias", action="store_true")
+    g.add_argument("--layout", default="nt", choices=["nt", "nn", "tn"],
+                   help="nt: x @ W.T (forward); nn: dY @ W (input gradient); tn: dY.T @ X (weight gradient)")
     g.add_argument("--skip-lib", action="store_true")
     g.add_argument("--skip-check", action="store_true")
     g.set_defaults(fn=bench_gemm)
@@ -239,6 +305,12 @@ def main(argv=None) -> int:
     n.add_argument("--seq", type=int, default=1024)
     n.add_argument("--dim", type=int, default=1536)
     n.set_defaults(fn=bench_adaln)
+    rw = sub.add_parser("rowwise")
+    rw.add_argument("--batch", type=int, default=8)
+    rw.add_argument("--seq", type=int, default=1024)
+    rw.add_argument("--dim", type=int, default=1536)
+    rw.add_argument("--heads", type=int, default=24)
+    rw.set_defaults(fn=bench_rowwise)
     t = sub.add_parser("attention")
     t.add_argument("--batch", type=int, default=16)
     t.add_argument("--heads", type=int, default=24)

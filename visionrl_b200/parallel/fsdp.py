@@ -49,6 +49,7 @@ BACKWARD_PRE prefetch).
 
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass, field
 from typing import Any, Iterable
 
@@ -401,6 +402,14 @@ class ShardedParamRuntime:
         # gather-ahead of the next unit's weights on a side stream
         self.prefetch = True
         self.small_rows = 1024              # a product of fewer rows cannot hide its own gather
+        # which weights the forward pass fetches ahead (the backward pass always fetches the whole
+        # unit): "small" = only products too short to hide their own gather; "deep" = those plus
+        # weights with more columns than rows (few n-tiles, long k loop: the in-product gather has
+        # nothing to overlap with); "all" = the whole unit, the in-product gather then only serves
+        # the first unit of a pass
+        self.forward_ahead = os.environ.get("VRL_GATHER_AHEAD", "deep")
+        if self.forward_ahead not in ("small", "deep", "all"):
+            raise ValueError("VRL_GATHER_AHEAD must be small, deep or all")
         self._cursor: tuple[int, bool] = (-1, False)
         self._last_unit = -1
         self._pending: dict[int, tuple[Any, list, int]] = {}
@@ -591,8 +600,10 @@ class ShardedParamRuntime:
     def _fetch_ahead(self, unit: int, whole_unit: bool) -> None:
         if unit < 0 or unit not in self.unit_sizes or unit in self._pending:
             return
+        everything = whole_unit or self.forward_ahead == "all"
+        deep = self.forward_ahead == "deep"
         wanted = [h for h in self.handles if h.unit == unit and not h.is_gathered()
-                  and (whole_unit or 0 <= h.last_rows < self.small_rows)]
+                  and (everything or 0 <= h.last_rows < self.small_rows or (deep and h.k > h.n))]
         if not wanted:
             return
         from visionrl_b200.ops import _ext

@@ -206,7 +206,7 @@ def main(argv=None) -> int:
 
         mesh_sp = ProcessMesh(rank=rank, world_size=world, dp=1, sp=world, sp_group=dist.group.WORLD)
         sp = SequenceParallel(mesh_sp, pool)
-        heads, dh = 12 if 12 % world == 0 else 8 * world, 128
+        heads, dh = next(h for h in (12, 40, 16, 32) if h % world == 0), 128    # Wan-1.3B / Wan-14B head counts first
         s_full = 14040 // (8 * world) * (8 * world)
         s_loc, b = s_full // world, 2
         qkv = torch.randn(b, s_loc, 3 * heads * dh, device=dev, dtype=torch.bfloat16)

@@ -298,7 +298,11 @@ async def run_online_recipe(ctx: RunContext, parts: RecipeParts, reward_fn: Any,
         reset = getattr(reward_fn, "reset_components", None)
         if callable(reset):
             reset()
+        step_clock = _StepClock(ctx.device)
         metrics = await trainer.step([examples[i] for i in picked])
+        step_ms = step_clock.stop(mesh)
+        if mesh.is_main:
+            _append_perf(out_dir / "perf.jsonl", epoch, step_ms, trainer, mesh)
         if mesh.is_main and epoch % tc.log_freq == 0:
             comp = _component_means(reward_fn, reward_names)
             logger.info("Epoch %d | loss=%.4f kl=%.4f reward=%.4f+/-%.4f grad_norm=%.4f "
@@ -324,6 +328,58 @@ async def run_online_recipe(ctx: RunContext, parts: RecipeParts, reward_fn: Any,
     if bool(cfg_path(cfg, "distributed.destroy_on_exit", True)):
         shutdown_distributed(trainer)
     return {"trainer": trainer, "bundle": bundle, "metrics": metrics}
+
+
+class _StepClock:
+    """Device time of one training step: CUDA events on the current stream (wall clock on CPU),
+    the maximum over ranks."""
+
+    def __init__(self, device: torch.device) -> None:
+        import time
+
+        self.device = device
+        self._t0 = time.perf_counter()
+        self._events = None
+        if device.type == "cuda":
+            self._events = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+            self._events[0].record()
+
+    def stop(self, mesh: Any) -> float:
+        import time
+
+        import torch.distributed as dist
+
+        if self._events is not None:
+            self._events[1].record()
+            self._events[1].synchronize()
+            ms = float(self._events[0].elapsed_time(self._events[1]))
+        else:
+            ms = (time.perf_counter() - self._t0) * 1e3
+        if mesh.world_size > 1 and dist.is_available() and dist.is_initialized():
+            t = torch.tensor([ms], dtype=torch.float64, device=self.device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+
+def _append_perf(path: Path, epoch: int, step_ms: float, trainer: Any, mesh: Any) -> None:
+    """One line per step in ``perf.jsonl``: device-timed step, samples per second over the whole
+    job, and the kernel-launch count of this rank (kept apart from ``metrics.csv``, whose columns are
+    a fixed contract)."""
+    import json
+
+    from visionrl_b200.ops import _ext
+
+    dp = max(int(getattr(mesh, "dp", 1)), 1)
+    samples = int(getattr(trainer, "last_step_samples", 0)) * dp
+    row = {"epoch": epoch, "step_ms": round(step_ms, 3), "samples": samples,
+           "samples_per_sec": round(samples / (step_ms / 1e3), 4) if step_ms > 0 else None,
+           "n_ranks": int(getattr(mesh, "world_size", 1)), "kernel_launches_total": int(_ext.launch_count)}
+    try:
+        with open(path, "a") as fh:
+            fh.write(json.dumps(row) + "\n")
+    except OSError:
+        logger.warning("could not append to %s", path, exc_info=True)
 
 
 class _StateOnly:

@@ -43,30 +43,45 @@ from visionrl_b200.trainers.weight_sync import WeightSyncer
 logger = logging.getLogger(__name__)
 
 
+def _nvtx_wanted() -> bool:
+    return os.environ.get("VRL_NVTX", "0") == "1" and torch.cuda.is_available()
+
+
 class PhaseTimer:
-    """Named accumulating timer; synchronises the device around each phase when CUDA is up."""
+    """Named accumulating timer; synchronises the device around each phase when CUDA is up.
+
+    With ``VRL_NVTX=1`` every phase is also an NVTX range (``vrl/<phase>``), whether or not the
+    timer itself is enabled, so a timeline profiler shows the step's structure without the
+    synchronisation that exact phase times need."""
 
     def __init__(self, enabled: bool = False) -> None:
         self.enabled = enabled
         self.times: dict[str, float] = {}
         self.events: list[tuple[str, float, float]] = []
+        self._nvtx = _nvtx_wanted()
 
     @contextlib.contextmanager
     def time(self, name: str):
-        if not self.enabled:
-            yield
-            return
-        if torch.cuda.is_available():
-            torch.cuda.synchronize()
-        t0, w0 = time.perf_counter(), time.time()
+        if self._nvtx:
+            torch.cuda.nvtx.range_push(f"vrl/{name}")
         try:
-            yield
-        finally:
+            if not self.enabled:
+                yield
+                return
             if torch.cuda.is_available():
                 torch.cuda.synchronize()
-            dt = time.perf_counter() - t0
-            self.times[name] = self.times.get(name, 0.0) + dt
-            self.events.append((name, w0, w0 + dt))
+            t0, w0 = time.perf_counter(), time.time()
+            try:
+                yield
+            finally:
+                if torch.cuda.is_available():
+                    torch.cuda.synchronize()
+                dt = time.perf_counter() - t0
+                self.times[name] = self.times.get(name, 0.0) + dt
+                self.events.append((name, w0, w0 + dt))
+        finally:
+            if self._nvtx:
+                torch.cuda.nvtx.range_pop()
 
 
 def create_optimizer(params: list, config: TrainerConfig):

@@ -1,17 +1,19 @@
-"""Kernel-time breakdown of one training step of the flagship recipe.
+"""Kernel-time breakdown of one training step of any online recipe.
 
 ``python -m visionrl_b200.utils.profile_step [--config experiment/sd3_5_shape_grpo] [--prompts 1]
-[--torch-baseline] [--rows 40]`` builds the trainer the benchmark uses, runs one warm-up step, then
-records one step (rollout, reward, replay, backward, optimizer) with the PyTorch profiler and prints the
-CUDA kernels sorted by device time.  The reference reaches the same information through
-``torch.profiler`` hooks in its trainer loop (``vrl/trainers/online.py``); here it is a stand-alone tool
-so that a profile never perturbs a timed run.
+[--torch-baseline] [--rows 40] [key=value ...]`` lets the recipe named by the config build its trainer
+exactly as a training run would, runs one warm-up step, then records one step (rollout, reward,
+replay, backward, optimizer) with the PyTorch profiler and prints the CUDA kernels sorted by device
+time; kernels replayed from a CUDA graph (the autoregressive decode step) are listed like any other.
+The reference reaches the same information through ``torch.profiler`` hooks in its trainer loop
+(``vrl/trainers/online.py``); here it is a stand-alone tool so that a profile never perturbs a timed run.
 """
 
 from __future__ import annotations
 
 import argparse
 import asyncio
+import inspect
 
 import torch
 
@@ -32,14 +34,21 @@ def main(argv=None) -> int:
 
     from visionrl_b200.config.loader import load_config
     from visionrl_b200.ops import _ext
-    from visionrl_b200.scripts.flagship import build_flagship_trainer
+    from visionrl_b200.scripts.common import capture_trainer
+    from visionrl_b200.scripts.train import run_config
 
     if args.torch_baseline:
         _ext.set_kernels_enabled(False)
     cfg = load_config(args.config, overrides=[f"rollout.rollout_batch_size={args.prompts}",
-                                              "trainer.output_dir=/tmp/vrl_profile_step", *args.overrides])
-    trainer, prompts = build_flagship_trainer(cfg)
+                                              "trainer.output_dir=/tmp/vrl_profile_step",
+                                              "distributed.destroy_on_exit=false", *args.overrides])
     loop = asyncio.new_event_loop()
+    with capture_trainer() as box:
+        outcome = run_config(cfg)
+        if inspect.isawaitable(outcome):
+            loop.run_until_complete(outcome)
+    trainer = box["trainer"]
+    prompts = list(box["examples"])[:args.prompts]
     loop.run_until_complete(trainer.step(prompts))                      # warm-up: allocator, autotuned paths
     torch.cuda.synchronize()
     with profile(activities=[ProfilerActivity.CUDA, ProfilerActivity.CPU]) as prof:
