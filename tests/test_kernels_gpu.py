@@ -480,6 +480,66 @@ def test_moe_routing_kernels_and_block():
 
 
 @pytest.mark.gpu
+def test_moe_grouped_path_matches_fp32_oracle_forward_and_backward():
+    """Padded permutation + grouped tcgen05 products (device-scheduled, one launch per layer) against
+    the dense fp32 per-expert loop, gradients of inputs, expert weights, biases and the gate included;
+    one expert receives no token at all, and the token count is not a multiple of the tile height."""
+    import copy
+
+    from visionrl_b200.ops import moe
+
+    torch.manual_seed(16)
+    tokens, experts, k, dim, hidden = 777, 6, 2, 128, 320
+    logits = torch.randn(tokens, experts, device="cuda")
+    logits[:, 4] = -50.0                                  # expert 4 is never chosen
+    _, idx = moe.route(logits, k)
+    got = moe.permute_padded(idx, experts)
+    want = moe.permute_padded_reference(idx, experts)
+    for a, b in zip(got, want):
+        assert torch.equal(a, b)
+    assert int(got[2][5] - got[2][4]) == 0                # the empty expert owns no tile
+
+    block = moe.MoEFFN(dim, hidden, experts, k).cuda().bfloat16()
+    with torch.no_grad():
+        block.gate.weight[4].fill_(0.0)
+        block.gate.weight.mul_(4.0)
+        block.b1.normal_(std=0.1)
+        block.b2.normal_(std=0.1)
+    x = (torch.randn(3, 259, dim, device="cuda") * 0.7).bfloat16()
+    x[..., 0] = 1.0
+    with torch.no_grad():
+        block.gate.weight[4, 0] = -50.0                   # ... so expert 4 is never routed to here either
+    assert block._grouped_ok(x.reshape(-1, dim))
+    ref_block = copy.deepcopy(block).float()
+    xa = x.clone().requires_grad_()
+    xb = x.float().clone().requires_grad_()
+    ya = block(xa)
+    tokens_f = xb.reshape(-1, dim)
+    with torch.no_grad():                                 # the oracle follows the block's own routing choice
+        _, ex = moe.route(block.gate(x.reshape(-1, dim)), k)
+    assert not bool((ex == 4).any())
+    probs = torch.softmax(ref_block.gate(tokens_f), dim=-1).gather(-1, ex.long())
+    w = probs / probs.sum(-1, keepdim=True)
+    yb = torch.zeros_like(tokens_f)
+    for e in range(experts):
+        h = torch.nn.functional.gelu(tokens_f @ ref_block.w1[e].t() + ref_block.b1[e], approximate="tanh")
+        ye = h @ ref_block.w2[e].t() + ref_block.b2[e]
+        yb = yb + ye * ((ex == e).float() * w).sum(-1, keepdim=True)
+    yb = yb.view(x.shape)
+    assert _rel(ya, yb) < 2e-2
+    g = torch.randn_like(yb)
+    ya.backward(g.bfloat16())
+    yb.backward(g)
+    assert _rel(xa.grad, xb.grad) < 3e-2
+    for name in ("w1", "b1", "w2", "b2"):
+        ga, gb = getattr(block, name).grad, getattr(ref_block, name).grad
+        assert torch.isfinite(ga.float()).all()
+        assert _rel(ga, gb) < 3e-2, name
+        assert float(ga[4].float().abs().max()) == 0.0    # the empty expert's gradients are exact zeros
+    assert _rel(block.gate.weight.grad, ref_block.gate.weight.grad) < 5e-2
+
+
+@pytest.mark.gpu
 def test_gemm_tma_store_epilogue_tails_with_gate_residual():
     from visionrl_b200.ops import _ext
 
@@ -1031,3 +1091,55 @@ def test_fused_decode_step_matches_the_tensor_op_layer_path(monkeypatch):
     assert torch.allclose(outs[0].float(), outs[1].float(), atol=6e-2, rtol=6e-2)
     assert torch.allclose(caches[0].float(), caches[1].float(), atol=3e-2, rtol=3e-2)
     assert float(caches[0][:, :, :, :, 3:].abs().max()) == 0.0           # nothing written past position 2
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("rows,k,n,rank", [(32, 2048, 6144, 32), (5, 256, 264, 8), (64, 1024, 2048, 64)])
+def test_lora_apply_rows_matches_fp32_reference(rows, k, n, rank):
+    """The decode-sized low-rank update y += s (x A^T) B^T against fp32 tensor math, row and column tails
+    included, and the layer-level path it serves (LoRALinear without autograd, a few rows)."""
+    from visionrl_b200.models.nn.layers import LoRALinear
+    from visionrl_b200.ops import _ext
+
+    torch.manual_seed(41)
+    x = torch.randn(rows, k, device="cuda").bfloat16()
+    a = (torch.randn(rank, k, device="cuda") / rank).bfloat16()
+    b = (torch.randn(n, rank, device="cuda") * 0.1).bfloat16()
+    y0 = torch.randn(rows, n, device="cuda").bfloat16()
+    y = y0.clone()
+    _ext.load().lora_apply_rows(y, x, a, b, 0.5)
+    want = y0.float() + 0.5 * (x.float() @ a.float().t()) @ b.float().t()
+    assert torch.allclose(y.float(), want, atol=2e-2, rtol=2e-2)
+    layer = LoRALinear(k, n, bias=True).cuda().bfloat16()
+    layer.add_adapter(rank, 2.0 * rank)
+    with torch.no_grad():
+        layer.lora_B.normal_(std=0.05)
+        small = layer(x)                                    # kernel path (rows <= 64, no autograd)
+    big = layer(torch.cat([x] * (65 // rows + 1))[:65 + rows])[:rows]     # > 64 rows: the tensor-op path
+    assert _rel(small, big) < 2e-2
+
+
+@pytest.mark.gpu
+def test_decode_attention_skips_unwritten_slots_and_matches_reference():
+    """Runs of eight keys per pass: masked keys (including NaN-filled, never written cache slots) have no
+    influence, lengths that are not a multiple of the run are handled, fully masked rows give zeros."""
+    from visionrl_b200.ops import _ext
+
+    torch.manual_seed(43)
+    rows, heads, length, d = 6, 4, 77, 128
+    q = torch.randn(rows, heads, d, device="cuda").bfloat16()
+    kc = torch.randn(rows, heads, length, d, device="cuda").bfloat16()
+    vc = torch.randn(rows, heads, length, d, device="cuda").bfloat16()
+    valid = torch.rand(rows, length, device="cuda") < 0.6
+    valid[1] = False
+    valid[2, :] = True
+    kc[~valid.unsqueeze(1).expand(-1, heads, -1)] = float("nan")
+    vc[~valid.unsqueeze(1).expand(-1, heads, -1)] = float("nan")
+    out = _ext.load().decode_attention(q.view(rows, heads, 1, d), kc, vc, valid, length, d ** -0.5).view(rows, heads, d)
+    scores = torch.einsum("rhd,rhld->rhl", q.float(), torch.nan_to_num(kc.float())) * d ** -0.5
+    scores = scores.masked_fill(~valid.unsqueeze(1), float("-inf"))
+    probs = torch.nan_to_num(torch.softmax(scores, dim=-1))
+    want = torch.einsum("rhl,rhld->rhd", probs, torch.nan_to_num(vc.float()))
+    assert torch.isfinite(out.float()).all()
+    assert torch.allclose(out.float(), want, atol=2e-2, rtol=2e-2)
+    assert float(out[1].float().abs().max()) == 0.0

@@ -221,9 +221,10 @@ sample_tokens_kernel(const T* __restrict__ cond, const T* __restrict__ uncond,
 // ------------------------------------------------------------------------------------------
 // Decode attention: one query position per (row, head) against a static cache.
 // q [R, H, D], caches [R, H, L, D] (strided), valid [R, L]; D = 128.  One block of 4 warps per
-// (row, head); every warp walks keys w, w+4, ... with an online softmax, lanes own 4 dims.
+// (row, head); every warp walks runs of 8 keys with an online softmax, lanes own 4 dims.
 // ------------------------------------------------------------------------------------------
 constexpr int kDecodeWarps = 4;
+constexpr int kDecodeKeys = 8;
 
 __global__ void __launch_bounds__(kDecodeWarps * 32)
 decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kc,
@@ -242,20 +243,56 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
   const __nv_bfloat16* vbase = vc + r * v_sr + h * v_sh + lane * 4;
   const bool* vrow = valid + r * valid_sr;
   float m = -INFINITY, s = 0.f, o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
-  for (int j = warp; j < length; j += kDecodeWarps) {
-    if (!vrow[j]) continue;                                   // warp-uniform
-    const uint2 kraw = *reinterpret_cast<const uint2*>(kbase + j * k_sl);
-    const float2 k01 = bf16pair_to_float2(kraw.x), k23 = bf16pair_to_float2(kraw.y);
-    float dot = q01.x * k01.x + q01.y * k01.y + q23.x * k23.x + q23.y * k23.y;
-    dot = warp_sum(dot) * scale;
-    const float mn = fmaxf(m, dot);
+  // kDecodeKeys keys per pass: their loads, dot products and reductions are independent of one
+  // another, so one pass costs about one memory round trip instead of kDecodeKeys of them; the
+  // running maximum is raised once per pass.
+  for (int j0 = warp * kDecodeKeys; j0 < length; j0 += kDecodeWarps * kDecodeKeys) {
+    bool ok[kDecodeKeys];
+    bool any = false;
+#pragma unroll
+    for (int i = 0; i < kDecodeKeys; ++i) {
+      ok[i] = (j0 + i < length) && vrow[j0 + i];
+      any = any || ok[i];
+    }
+    if (!any) continue;                                       // warp-uniform
+    uint2 kraw[kDecodeKeys], vraw[kDecodeKeys];
+#pragma unroll
+    for (int i = 0; i < kDecodeKeys; ++i) {
+      kraw[i] = make_uint2(0u, 0u);
+      vraw[i] = make_uint2(0u, 0u);
+      if (ok[i]) {                                            // never touch a slot that was not written
+        kraw[i] = *reinterpret_cast<const uint2*>(kbase + (int64_t)(j0 + i) * k_sl);
+        vraw[i] = *reinterpret_cast<const uint2*>(vbase + (int64_t)(j0 + i) * v_sl);
+      }
+    }
+    float dot[kDecodeKeys];
+#pragma unroll
+    for (int i = 0; i < kDecodeKeys; ++i) {
+      const float2 k01 = bf16pair_to_float2(kraw[i].x), k23 = bf16pair_to_float2(kraw[i].y);
+      dot[i] = q01.x * k01.x + q01.y * k01.y + q23.x * k23.x + q23.y * k23.y;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+      for (int i = 0; i < kDecodeKeys; ++i) dot[i] += __shfl_xor_sync(0xffffffffu, dot[i], o);
+    }
+    float mn = m;
+#pragma unroll
+    for (int i = 0; i < kDecodeKeys; ++i) {
+      dot[i] = ok[i] ? dot[i] * scale : -INFINITY;
+      mn = fmaxf(mn, dot[i]);
+    }
     const float corr = (m == -INFINITY) ? 0.f : __expf(m - mn);
-    const float p = __expf(dot - mn);
-    const uint2 vraw = *reinterpret_cast<const uint2*>(vbase + j * v_sl);
-    const float2 v01 = bf16pair_to_float2(vraw.x), v23 = bf16pair_to_float2(vraw.y);
-    o0 = o0 * corr + p * v01.x; o1 = o1 * corr + p * v01.y;
-    o2 = o2 * corr + p * v23.x; o3 = o3 * corr + p * v23.y;
-    s = s * corr + p;
+    o0 *= corr; o1 *= corr; o2 *= corr; o3 *= corr;
+    s *= corr;
+#pragma unroll
+    for (int i = 0; i < kDecodeKeys; ++i) {
+      const float p = ok[i] ? __expf(dot[i] - mn) : 0.f;
+      const float2 v01 = bf16pair_to_float2(vraw[i].x), v23 = bf16pair_to_float2(vraw[i].y);
+      o0 = fmaf(p, v01.x, o0); o1 = fmaf(p, v01.y, o1);
+      o2 = fmaf(p, v23.x, o2); o3 = fmaf(p, v23.y, o3);
+      s += p;
+    }
     m = mn;
   }
   if (lane == 0) { sm_m[warp] = m; sm_s[warp] = s; }
@@ -627,6 +664,99 @@ torch::Tensor add_rmsnorm_rows(torch::Tensor x, c10::optional<torch::Tensor> del
       (int)x.size(1), (float)eps);
   C10_CUDA_KERNEL_LAUNCH_CHECK();
   return y;
+}
+
+// ------------------------------------------------------------------------------------------
+// Low-rank adapter for decode-sized inputs: y += scale * (x A^T) B^T with R <= 64 rows.  Two tiny
+// CUDA-core kernels (the contraction over K is split over blocks; the rank-r update is a few
+// multiply-adds per output) instead of two tensor-core launches whose single tile would stream
+// K serially, plus the scaling and the add.
+//   lora_down_rows   low[R, r] (fp32) = x[R, K] A[r, K]^T        one warp per (row, adapter row)
+//   lora_up_add_rows y[R, N] += scale * low[R, r] B[N, r]^T      one thread per (8 rows, column)
+// ------------------------------------------------------------------------------------------
+namespace {
+
+constexpr int kLoraRowsPerBlock = 8;
+
+__global__ void __launch_bounds__(kLoraRowsPerBlock * 32)
+lora_down_rows_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ a,
+                      float* __restrict__ low, int rows, int k, int rank) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = blockIdx.y * kLoraRowsPerBlock + warp, j = blockIdx.x;
+  if (row >= rows) return;
+  const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + (int64_t)row * k);
+  const bf16x8* ar = reinterpret_cast<const bf16x8*>(a + (int64_t)j * k);
+  float acc = 0.f;
+  for (int i = lane; i < k / 8; i += 32) {
+    float xv[8], av[8];
+    unpack8(xr[i], xv);
+    unpack8(ar[i], av);
+#pragma unroll
+    for (int t = 0; t < 8; ++t) acc = fmaf(xv[t], av[t], acc);
+  }
+  acc = warp_sum(acc);
+  if (lane == 0) low[(int64_t)row * rank + j] = acc;
+}
+
+__global__ void __launch_bounds__(256)
+lora_up_add_rows_kernel(__nv_bfloat16* __restrict__ y, const float* __restrict__ low,
+                        const __nv_bfloat16* __restrict__ b, int rows, int n, int rank, float scale) {
+  extern __shared__ float low_s[];                 // [kLoraRowsPerBlock][rank]
+  const int row0 = blockIdx.y * kLoraRowsPerBlock;
+  const int nrows = min(kLoraRowsPerBlock, rows - row0);
+  for (int i = threadIdx.x; i < nrows * rank; i += blockDim.x) low_s[i] = low[(int64_t)row0 * rank + i] * scale;
+  __syncthreads();
+  const int col = blockIdx.x * blockDim.x + threadIdx.x;
+  if (col >= n) return;
+  float acc[kLoraRowsPerBlock];
+#pragma unroll
+  for (int r = 0; r < kLoraRowsPerBlock; ++r) acc[r] = 0.f;
+  const bf16x8* br = reinterpret_cast<const bf16x8*>(b + (int64_t)col * rank);
+  for (int i = 0; i < rank / 8; ++i) {
+    float bv[8];
+    unpack8(br[i], bv);
+#pragma unroll
+    for (int r = 0; r < kLoraRowsPerBlock; ++r) {
+      if (r < nrows) {
+#pragma unroll
+        for (int t = 0; t < 8; ++t) acc[r] = fmaf(low_s[r * rank + i * 8 + t], bv[t], acc[r]);
+      }
+    }
+  }
+  for (int r = 0; r < nrows; ++r) {
+    __nv_bfloat16* dst = y + (int64_t)(row0 + r) * n + col;
+    *dst = __float2bfloat16_rn(__bfloat162float(*dst) + acc[r]);
+  }
+}
+
+}  // namespace
+
+// y (bf16 [R, N], updated in place) += scale * (x A^T) B^T for R <= 64 rows.
+void lora_apply_rows(torch::Tensor y, torch::Tensor x, torch::Tensor a, torch::Tensor b, double scale) {
+  TORCH_CHECK(y.is_cuda() && y.dim() == 2 && y.scalar_type() == torch::kBFloat16 && y.is_contiguous(),
+              "lora_apply_rows: y must be a contiguous bf16 [R, N] CUDA tensor");
+  VRL_CHECK_OPERAND(x, y, torch::kBFloat16);
+  VRL_CHECK_OPERAND(a, y, torch::kBFloat16);
+  VRL_CHECK_OPERAND(b, y, torch::kBFloat16);
+  const int64_t rows = y.size(0), n = y.size(1);
+  TORCH_CHECK(x.dim() == 2 && x.is_contiguous() && x.size(0) == rows && a.dim() == 2 && a.is_contiguous() &&
+              b.dim() == 2 && b.is_contiguous() && a.size(1) == x.size(1) && b.size(0) == n && b.size(1) == a.size(0),
+              "lora_apply_rows: x [R, K], A [r, K], B [N, r]");
+  const int64_t k = x.size(1), rank = a.size(0);
+  TORCH_CHECK(rows <= 64 && k % 8 == 0 && rank % 8 == 0 && rank <= 256, "lora_apply_rows: R <= 64, K % 8 == 0, r % 8 == 0");
+  if (rows == 0 || n == 0) return;
+  const c10::cuda::CUDAGuard guard(y.device());
+  auto low = torch::empty({rows, rank}, y.options().dtype(torch::kFloat32));
+  auto stream = at::cuda::getCurrentCUDAStream();
+  const unsigned row_blocks = (unsigned)((rows + kLoraRowsPerBlock - 1) / kLoraRowsPerBlock);
+  lora_down_rows_kernel<<<dim3((unsigned)rank, row_blocks), kLoraRowsPerBlock * 32, 0, stream>>>(
+      reinterpret_cast<const __nv_bfloat16*>(x.data_ptr()), reinterpret_cast<const __nv_bfloat16*>(a.data_ptr()),
+      low.data_ptr<float>(), (int)rows, (int)k, (int)rank);
+  lora_up_add_rows_kernel<<<dim3((unsigned)((n + 255) / 256), row_blocks), 256,
+                            kLoraRowsPerBlock * rank * sizeof(float), stream>>>(
+      reinterpret_cast<__nv_bfloat16*>(y.data_ptr()), low.data_ptr<float>(),
+      reinterpret_cast<const __nv_bfloat16*>(b.data_ptr()), (int)rows, (int)n, (int)rank, (float)scale);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
 
 torch::Tensor group_advantages(torch::Tensor rewards, torch::Tensor group_ids, double eps, double clip,

@@ -75,6 +75,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("moe_permute", &vrl::moe_permute);
   m.def("moe_gather_rows", &vrl::moe_gather_rows);
   m.def("moe_combine", &vrl::moe_combine);
+  m.def("moe_combine_bwd", &vrl::moe_combine_bwd);
+  m.def("moe_segment_colsum", &vrl::moe_segment_colsum);
+  m.def("lora_apply_rows", &vrl::lora_apply_rows);
   m.def("int4_gemm", &vrl::int4_gemm);
   m.def("int4_gemm_last_status", &vrl::int4_gemm_last_status);
   m.def("groupnorm_nhwc", &vrl::groupnorm_nhwc);
@@ -92,6 +95,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_allgather", &vrl::gemm_allgather);
   m.def("head_logprob_fwd", &vrl::head_logprob_fwd);
   m.def("head_softmax_grad", &vrl::head_softmax_grad);
+  m.def("gemm_grouped", &vrl::gemm_grouped);
+  m.def("gemm_grouped_wgrad", &vrl::gemm_grouped_wgrad);
   m.def("gemm_bf16_acc", &vrl::gemm_bf16_acc);
   m.def("gemm_bf16_out", &vrl::gemm_bf16_out);
   m.def("gemm_last_status", &vrl::gemm_last_status);

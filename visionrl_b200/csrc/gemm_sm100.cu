@@ -69,6 +69,18 @@ struct Params {
   int g_world, g_rank, g_rows;     // g_rows = N / g_world
   int g_first_tile;                // n-tile holding this rank's own rows: processed first
   int g_band;                      // m-tiles per band of the gathering variant's tile order
+  // Grouped products (mixture of experts; 0 = off).  The rows of the activation are sorted by
+  // expert and every expert's run is padded to a multiple of BM rows.
+  //   1: C[r, :] = epilogue(A[r, :] B_e^T), e = grp_tile_expert[r / BM] (negative: unused tile).
+  //      B holds all experts' matrices stacked along its outer dimension, grp_stride rows apart.
+  //   2: C_e = A[rows of e]^T B[rows of e] for every expert e (weight gradients): the contraction
+  //      runs over the expert's padded row range grp_offsets[e] .. grp_offsets[e + 1]; the tile
+  //      index also enumerates the experts and C_e starts at row e * m of the output.
+  int grp_mode;
+  int grp_experts;
+  int grp_stride;
+  const int* grp_tile_expert;
+  const int* grp_offsets;
   // log-sum-exp epilogues of the vocabulary head (0 = off).  1: nothing is stored but, per row and
   // 64-column chunk, the maximum and the exponential sum of (acc + bias) / T, plus the target's
   // value; 2: the stored bf16 value is g/T * (onehot(id) - exp((acc + bias) / T - lse)).
@@ -110,6 +122,42 @@ __device__ __forceinline__ void tile_origin(int tile, int m_tiles, int n_tiles, 
   }
 }
 
+// Everything a role needs to know about one tile; the three roles derive it independently and
+// must agree, so it is a pure function of the tile index and the launch parameters.
+struct TileInfo {
+  int m0, n0;        // tile origin in the (per-expert, for grouped mode 2) output
+  int kb0, kbn;      // first k-block and number of k-blocks of the contraction
+  int b_off;         // offset added to B's outer coordinate (expert's matrix)
+  int c_row_off;     // offset added to the output row coordinate
+  int bias_off;
+  bool skip;
+};
+
+template <bool kGather>
+__device__ __forceinline__ TileInfo tile_info(int tile, int m_tiles, int n_tiles, int k_blocks, const Params& p) {
+  TileInfo t;
+  t.kb0 = 0; t.kbn = k_blocks; t.b_off = 0; t.c_row_off = 0; t.bias_off = 0; t.skip = false;
+  if (!kGather && p.grp_mode == 2) {
+    const int per = m_tiles * n_tiles;
+    const int e = tile / per, r = tile - e * per;
+    t.m0 = (r / n_tiles) * BM;
+    t.n0 = (r % n_tiles) * BN;
+    const int lo = p.grp_offsets[e], hi = p.grp_offsets[e + 1];
+    t.kb0 = lo / BK;
+    t.kbn = (hi - lo) / BK;
+    t.c_row_off = e * p.m;
+    return t;
+  }
+  tile_origin<kGather>(tile, m_tiles, n_tiles, p, t.m0, t.n0);
+  if (!kGather && p.grp_mode == 1) {
+    const int e = p.grp_tile_expert[t.m0 / BM];
+    if (e < 0) { t.skip = true; t.kbn = 0; return t; }
+    t.b_off = e * p.grp_stride;
+    t.bias_off = e * p.n;
+  }
+  return t;
+}
+
 using namespace ptx;
 
 // ------------------------------------------------------------------------------------- kernel
@@ -133,7 +181,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m_tiles = (p.m + BM - 1) / BM, n_tiles = (p.n + BN - 1) / BN;
-  const int num_tiles = m_tiles * n_tiles;
+  const int num_tiles = m_tiles * n_tiles * (p.grp_mode == 2 ? p.grp_experts : 1);
   const int k_blocks = (p.k + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
@@ -156,8 +204,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     bool ok = true;
     uint32_t slabs_seen = 0;       // bit r: the rows of rank r are known to be in g_full
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-      int m0, n0;
-      tile_origin<kGather>(tile, m_tiles, n_tiles, p, m0, n0);
+      const TileInfo ti = tile_info<kGather>(tile, m_tiles, n_tiles, k_blocks, p);
+      if (ti.skip) continue;
+      const int m0 = ti.m0, n0 = ti.n0;
       if (kGather) {
         // the B rows of this tile must have been copied by the gather warps of EVERY CTA
         const int lo = n0 / p.g_rows, hi = min(p.n - 1, n0 + BN - 1) / p.g_rows;
@@ -176,14 +225,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         }
         if (!ok) break;
       }
-      for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+      for (int kb = 0; kb < ti.kbn; ++kb, ++it) {
         const int s = it % kStages;
         const uint32_t parity = ((it / kStages) & 1u) ^ 1u;
         if (!mbar_wait(&empty[s], parity, abort_flag)) { ok = false; break; }
         uint8_t* sa = smem + s * kStageBytes;
         uint8_t* sb = sa + kABytes;
         mbar_expect_tx(&full[s], kStageBytes);
-        const int k0 = kb * BK;
+        const int k0 = (ti.kb0 + kb) * BK;
         if (!p.a_mn) {
           tma_load_2d(sa, &map_a, &full[s], k0, m0);
         } else {
@@ -192,11 +241,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             tma_load_2d(sa + c * (BK * 128), &map_a, &full[s], m0 + c * 64, k0);
         }
         if (!p.b_mn) {
-          tma_load_2d(sb, &map_b, &full[s], k0, n0);
+          tma_load_2d(sb, &map_b, &full[s], k0, n0 + ti.b_off);
         } else {
+          // grouped mode 1 with a row-major B: the expert's matrix starts b_off rows down the
+          // contraction coordinate; mode 2 contracts over the rows themselves (b_off = 0)
 #pragma unroll
           for (int c = 0; c < BN / 64; ++c)
-            tma_load_2d(sb + c * (BK * 128), &map_b, &full[s], n0 + c * 64, k0);
+            tma_load_2d(sb + c * (BK * 128), &map_b, &full[s], n0 + c * 64, k0 + ti.b_off);
         }
       }
     }
@@ -224,12 +275,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const uint32_t b_step = p.b_mn ? (UMMA_K * 128) >> 4 : (UMMA_K * 2) >> 4;
     uint32_t it = 0, tile_it = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_it) {
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      const TileInfo ti = tile_info<kGather>(tile, m_tiles, n_tiles, k_blocks, p);
+      if (ti.skip) continue;
       const uint32_t buf = tile_it & 1u;
       if (!mbar_wait(&acc_empty[buf], ((tile_it >> 1) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
       tmem_fence_after();
       const uint32_t tmem_c = tmem_base + buf * BN;
-      for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+      for (int kb = 0; kb < ti.kbn; ++kb, ++it) {
         const int s = it % kStages;
         if (!mbar_wait(&full[s], (it / kStages) & 1u, abort_flag)) { ok = false; break; }
         tmem_fence_after();
@@ -240,7 +293,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                           (kb | kk) ? 1u : 0u);
         umma_commit(&empty[s]);           // frees the stage once these MMAs have read it
       }
-      if (ok) umma_commit(&acc_full[buf]);
+      if (ok) umma_commit(&acc_full[buf]);     // with no products issued it completes at once
+      ++tile_it;
     }
     if (!ok) {
       if (atomicCAS(const_cast<int*>(abort_flag), 0, 1) == 0) atomicExch(p.status, kTimeoutMma);
@@ -295,15 +349,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const int swz = lane & 7;
     uint32_t tile_it = 0, res_it = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_it) {
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      const TileInfo ti = tile_info<kGather>(tile, m_tiles, n_tiles, k_blocks, p);
+      if (ti.skip) continue;
       const uint32_t buf = tile_it & 1u;
-      int m0, n0;
-      tile_origin<kGather>(tile, m_tiles, n_tiles, p, m0, n0);
+      const int m0 = ti.m0, n0 = ti.n0;
+      const __nv_bfloat16* bias_t = p.bias ? p.bias + ti.bias_off : nullptr;
       if (!mbar_wait(&acc_full[buf], (tile_it >> 1) & 1u, abort_flag)) { ok = false; break; }
       tmem_fence_after();
       const int row0 = m0 + quarter * 32;
       const int row = row0 + lane;
       const bool row_ok = row < p.m;
+      // grouped weight gradients: a 32-row piece past the expert's matrix would land in the next one
+      const bool piece_ok = p.grp_mode != 2 || row0 < p.m;
       const int64_t gate_row = p.gate ? ((row_ok ? row : 0) / p.rows_per_gate) : 0;
 #pragma unroll 1
       for (int cc = 0; cc < 2 && ok; ++cc) {
@@ -311,6 +369,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         if (colbase >= p.n) break;                // warp-uniform
         const uint32_t taddr =
             tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN + half * 128 + cc * 64;
+        if (!piece_ok) break;                     // warp-uniform
         uint32_t r[64];
         tmem_ld32(taddr, r);
         tmem_ld32(taddr + 32, r + 32);
@@ -330,6 +389,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         }
         tmem_ld_wait();
         if (!ok) break;
+        if (ti.kbn == 0) {
+          // an expert without rows: no product was issued, the accumulator columns hold old data
+#pragma unroll
+          for (int i = 0; i < 64; ++i) r[i] = 0u;
+        }
         if (p.lse_mode == 1) {
           // one thread holds 64 consecutive logits of one row: fold them here, store 8 bytes
           const int t = row_ok ? (int)(p.lse_ids[row] - p.lse_col0 - colbase) : -1;
@@ -340,7 +404,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             float b[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) b[j] = 0.f;
-            if (p.bias && col < p.n) unpack8(*reinterpret_cast<const bf16x8*>(p.bias + col), b);
+            if (bias_t && col < p.n) unpack8(*reinterpret_cast<const bf16x8*>(bias_t + col), b);
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
               float sv = (__uint_as_float(r[g * 8 + j]) + b[j]) * p.lse_inv_t;
@@ -375,9 +439,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             float v[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[g * 8 + j]);
-            if (p.bias && col < p.n) {
+            if (bias_t && col < p.n) {
               float b[8];
-              unpack8(*reinterpret_cast<const bf16x8*>(p.bias + col), b);
+              unpack8(*reinterpret_cast<const bf16x8*>(bias_t + col), b);
 #pragma unroll
               for (int j = 0; j < 8; ++j) v[j] += b[j];
             }
@@ -390,7 +454,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           fence_async_smem();
           __syncwarp();
           if (lane == 0) {
-            tma_store_2d(stage, &map_c2, colbase, row0);
+            tma_store_2d(stage, &map_c2, colbase, row0 + ti.c_row_off);
             tma_store_wait_read();
           }
           __syncwarp();
@@ -402,9 +466,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           float v[8];
 #pragma unroll
           for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[g * 8 + j]);
-          if (p.bias && col_ok) {
+          if (bias_t && col_ok) {
             float b[8];
-            unpack8(*reinterpret_cast<const bf16x8*>(p.bias + col), b);
+            unpack8(*reinterpret_cast<const bf16x8*>(bias_t + col), b);
 #pragma unroll
             for (int j = 0; j < 8; ++j) v[j] += b[j];
           }
@@ -469,12 +533,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         if (!p.out_fp32) {
           fence_async_smem();                     // generic-proxy writes -> visible to the TMA unit
           __syncwarp();
-          if (lane == 0) tma_store_2d(stage, &map_c, colbase, row0);
+          if (lane == 0) tma_store_2d(stage, &map_c, colbase, row0 + ti.c_row_off);
         }
       }
       tmem_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[buf]);
+      ++tile_it;
     }
     if (lane == 0) tma_store_wait_all();          // staging must outlive the stores reading it
     if (!ok && lane == 0) {
@@ -546,6 +611,15 @@ struct LseSpec {
   torch::Tensor lse, g;                        // mode 2
 };
 
+// Grouped products (Params::grp_mode).  Mode 1: `b` is the 2-D view of the experts' stacked matrices
+// and `tile_expert` maps every BM-row tile of `a` to its expert (negative = unused).  Mode 2: `a` and
+// `b` are both [rows, *] and `offsets` [experts + 1] gives every expert's padded row range.
+struct GroupSpec {
+  int mode;
+  int64_t experts;
+  torch::Tensor table;                   // tile_expert (mode 1) or offsets (mode 2), int32
+};
+
 static std::vector<torch::Tensor> gemm_impl(torch::Tensor a, torch::Tensor b,
                                             c10::optional<torch::Tensor> bias,
                                             c10::optional<torch::Tensor> gate,
@@ -554,7 +628,8 @@ static std::vector<torch::Tensor> gemm_impl(torch::Tensor a, torch::Tensor b,
                                             bool out_fp32, bool dual,
                                             c10::optional<torch::Tensor> out_given = c10::nullopt,
                                             const struct GatherSpec* gather = nullptr,
-                                            const struct LseSpec* lse = nullptr);
+                                            const struct LseSpec* lse = nullptr,
+                                            const struct GroupSpec* grp = nullptr);
 
 torch::Tensor gemm_bf16(torch::Tensor a, torch::Tensor b, c10::optional<torch::Tensor> bias,
                         c10::optional<torch::Tensor> gate, c10::optional<torch::Tensor> residual,
@@ -585,8 +660,11 @@ static std::vector<torch::Tensor> gemm_impl(torch::Tensor a, torch::Tensor b,
                                             int64_t rows_per_gate, bool a_mn_major, bool b_mn_major,
                                             bool out_fp32, bool dual,
                                             c10::optional<torch::Tensor> out_given,
-                                            const GatherSpec* gather, const LseSpec* lse) {
+                                            const GatherSpec* gather, const LseSpec* lse, const GroupSpec* grp) {
   using namespace gemm;
+  TORCH_CHECK(grp == nullptr || (gather == nullptr && lse == nullptr && !out_fp32 && !gate.has_value() &&
+                                 !out_given.has_value()),
+              "gemm_bf16: grouped products take bias, activation, dual output and the gelu-gradient residual only");
   const bool lse_partial = lse != nullptr && lse->mode == 1;
   TORCH_CHECK(lse == nullptr || (!gate.has_value() && !residual.has_value() && !dual && act == 0 &&
                                  gather == nullptr && !out_given.has_value() && !out_fp32),
@@ -614,8 +692,14 @@ static std::vector<torch::Tensor> gemm_impl(torch::Tensor a, torch::Tensor b,
   // logical sizes: A is [M, K] (or stored [K, M] when MN-major), B is [N, K] (or stored [K, N])
   const int64_t m = a_mn_major ? a.size(1) : a.size(0);
   const int64_t k = a_mn_major ? a.size(0) : a.size(1);
-  const int64_t n = b_mn_major ? b.size(1) : b.size(0);
-  const int64_t kb = b_mn_major ? b.size(0) : b.size(1);
+  int64_t n = b_mn_major ? b.size(1) : b.size(0);
+  int64_t kb = b_mn_major ? b.size(0) : b.size(1);
+  const int64_t experts = grp != nullptr ? grp->experts : 1;
+  if (grp != nullptr && grp->mode == 1) {
+    // b is the stack of the experts' matrices: [E * N, K] (K-major) or [E * K, N] (row-major)
+    if (b_mn_major) { TORCH_CHECK(kb % experts == 0); kb /= experts; }
+    else { TORCH_CHECK(n % experts == 0); n /= experts; }
+  }
   TORCH_CHECK(k == kb, "gemm_bf16: contraction sizes differ: ", k, " vs ", kb);
   TORCH_CHECK(n % 8 == 0, "gemm_bf16: N must be a multiple of 8");
   TORCH_CHECK(a.stride(0) % 8 == 0 && b.stride(0) % 8 == 0, "gemm_bf16: row pitch must be a multiple of 8");
@@ -627,23 +711,28 @@ static std::vector<torch::Tensor> gemm_impl(torch::Tensor a, torch::Tensor b,
     TORCH_CHECK(!out_fp32 && out.size(0) == m && out.size(1) == n, "gemm_bf16: output shape mismatch");
   } else if (lse_partial) {
     out = torch::empty({0}, a.options());      // this epilogue stores no product
+  } else if (grp != nullptr && grp->mode == 2) {
+    out = torch::empty({experts * m, n}, a.options());
   } else {
     out = torch::empty({m, n}, a.options().dtype(out_fp32 ? torch::kFloat32 : torch::kBFloat16));
   }
   torch::Tensor pre = dual ? torch::empty({m, n}, a.options()) : torch::Tensor();
   if (m == 0 || n == 0) return {out, pre};
+  if (grp != nullptr && grp->mode == 2 && k == 0) { out.zero_(); return {out, pre}; }
   TORCH_CHECK(k > 0, "gemm_bf16: empty contraction");
 
+  // grouped mode 1: B's outer extent covers every expert's matrix
+  const int64_t b_outer = (grp != nullptr && grp->mode == 1) ? experts : 1;
   CUtensorMap map_a = a_mn_major ? make_map(a.data_ptr(), m, k, a.stride(0), 64, BK)
                                  : make_map(a.data_ptr(), k, m, a.stride(0), BK, BM);
-  CUtensorMap map_b = b_mn_major ? make_map(b.data_ptr(), n, k, b.stride(0), 64, BK)
-                                 : make_map(b.data_ptr(), k, n, b.stride(0), BK, BN);
+  CUtensorMap map_b = b_mn_major ? make_map(b.data_ptr(), n, k * b_outer, b.stride(0), 64, BK)
+                                 : make_map(b.data_ptr(), k, n * b_outer, b.stride(0), BK, BN);
   Params p{};
   p.c = out.data_ptr();
   torch::Tensor bias_c, gate_c, res_c;
   if (bias.has_value()) {
     bias_c = bias->to(torch::kBFloat16).contiguous();
-    TORCH_CHECK(bias_c.numel() == n);
+    TORCH_CHECK(bias_c.numel() == n * ((grp != nullptr && grp->mode == 1) ? experts : 1));
     p.bias = reinterpret_cast<const __nv_bfloat16*>(bias_c.data_ptr());
   }
   if (gate.has_value()) {
@@ -675,6 +764,23 @@ static std::vector<torch::Tensor> gemm_impl(torch::Tensor a, torch::Tensor b,
   p.b_mn = b_mn_major ? 1 : 0;
   p.out_fp32 = out_fp32 ? 1 : 0;
   p.dual = dual ? 1 : 0;
+  if (grp != nullptr) {
+    TORCH_CHECK(experts >= 1 && grp->table.is_contiguous(), "gemm_bf16: grouped table");
+    p.grp_mode = grp->mode;
+    p.grp_experts = (int)experts;
+    if (grp->mode == 1) {
+      TORCH_CHECK(!a_mn_major && m % BM == 0, "grouped product: rows padded to the tile height, K-major activations");
+      VRL_CHECK_OPERAND(grp->table, a, torch::kInt32, m / BM);
+      p.grp_tile_expert = grp->table.data_ptr<int>();
+      p.grp_stride = (int)(b_mn_major ? k : n);
+    } else {
+      TORCH_CHECK(a_mn_major && b_mn_major && k % BM == 0 && m % 32 == 0 && !bias.has_value() &&
+                  !residual.has_value() && !dual && act == 0,
+                  "grouped weight gradient: row-major operands over padded rows, output rows a multiple of 32");
+      VRL_CHECK_OPERAND(grp->table, a, torch::kInt32, experts + 1);
+      p.grp_offsets = grp->table.data_ptr<int>();
+    }
+  }
   if (lse != nullptr) {
     const int64_t chunks = (n + 63) / 64;
     VRL_CHECK_OPERAND(lse->ids, a, torch::kInt64, m);
@@ -706,10 +812,11 @@ static std::vector<torch::Tensor> gemm_impl(torch::Tensor a, torch::Tensor b,
     return true;
   }();
   (void)attr_set;
-  const int tiles = (int)(((m + BM - 1) / BM) * ((n + BN - 1) / BN));
+  const int tiles = (int)(((m + BM - 1) / BM) * ((n + BN - 1) / BN) * ((grp != nullptr && grp->mode == 2) ? experts : 1));
   const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
   // output / residual maps: 64-column x 32-row boxes matching one epilogue warp's staging tile
-  CUtensorMap map_c = (out_fp32 || lse_partial) ? map_a : make_map(out.data_ptr(), n, m, n, 64, 32);
+  const int64_t c_rows = (grp != nullptr && grp->mode == 2) ? experts * m : m;
+  CUtensorMap map_c = (out_fp32 || lse_partial) ? map_a : make_map(out.data_ptr(), n, c_rows, n, 64, 32);
   CUtensorMap map_r = (p.residual && !out_fp32) ? make_map(p.residual, n, m, n, 64, 32) : map_c;
   CUtensorMap map_c2 = dual ? make_map(pre.data_ptr(), n, m, n, 64, 32) : map_c;
   auto stream = at::cuda::getCurrentCUDAStream();
@@ -776,6 +883,35 @@ std::vector<torch::Tensor> gemm_allgather(torch::Tensor x, torch::Tensor peer_pt
                         c10::nullopt, &spec);
   if (!dual) outs.resize(1);
   return outs;
+}
+
+// ---------------------------------------------------------------------------- grouped products
+// epilogue(a[r, :] W_e^T + bias_e) for rows sorted by expert, every expert's run padded to 128 rows.
+// `w` is [E, N, K] (or, `w_row_major`, [E, K, N]: the input-gradient form), `tile_expert` int32
+// [rows / 128].  Returns {y} or, with `dual`, {act(y), y}; `residual` with act 3 is the
+// gelu-gradient epilogue.  No value is read on the host: the launch is the same for any routing.
+std::vector<torch::Tensor> gemm_grouped(torch::Tensor a, torch::Tensor w, torch::Tensor tile_expert,
+                                        c10::optional<torch::Tensor> bias, c10::optional<torch::Tensor> residual,
+                                        int64_t act, bool w_row_major, bool dual) {
+  TORCH_CHECK(a.is_cuda() && a.dim() == 2 && w.dim() == 3 && w.is_contiguous() && a.is_contiguous(),
+              "gemm_grouped: a [rows, K] and w [E, N, K] contiguous");
+  const int64_t experts = w.size(0);
+  const GroupSpec spec{1, experts, tile_expert};
+  auto outs = gemm_impl(a, w.view({experts * w.size(1), w.size(2)}), bias, c10::nullopt, residual, act, 0, false,
+                        w_row_major, false, dual, c10::nullopt, nullptr, nullptr, &spec);
+  if (!dual) outs.resize(1);
+  return outs;
+}
+
+// dW_e = gy[rows of e]^T x[rows of e] for every expert: [E, N, K] from gy [rows, N], x [rows, K] and the
+// experts' padded row offsets (int32 [E + 1], multiples of 128).  Rows of padding must be zero in `gy`.
+torch::Tensor gemm_grouped_wgrad(torch::Tensor gy, torch::Tensor x, torch::Tensor offsets, int64_t experts) {
+  TORCH_CHECK(gy.is_cuda() && gy.dim() == 2 && x.dim() == 2 && gy.size(0) == x.size(0) && gy.is_contiguous() &&
+              x.is_contiguous(), "gemm_grouped_wgrad: gy [rows, N], x [rows, K] contiguous");
+  const GroupSpec spec{2, experts, offsets};
+  auto out = gemm_impl(gy, x, c10::nullopt, c10::nullopt, c10::nullopt, 0, 0, true, true, false, false, c10::nullopt,
+                       nullptr, nullptr, &spec)[0];
+  return out.view({experts, gy.size(1), x.size(1)});
 }
 
 // ------------------------------------------------------------- vocabulary head with log-sum-exp

@@ -1,4 +1,5 @@
-// Vocabulary head with the log-sum-exp folded into the product's epilogue (gemm_sm100.cu).
+// Entry points of gemm_sm100.cu beyond the plain product: the vocabulary head with the log-sum-exp
+// folded into the epilogue, and grouped products.
 #pragma once
 
 #include <torch/extension.h>
@@ -14,5 +15,11 @@ std::vector<torch::Tensor> head_logprob_fwd(torch::Tensor h, torch::Tensor w, c1
 torch::Tensor head_softmax_grad(torch::Tensor h, torch::Tensor w, c10::optional<torch::Tensor> bias,
                                 torch::Tensor ids, torch::Tensor lse, torch::Tensor g, int64_t col0,
                                 double temperature);
+
+// grouped products over expert-sorted rows (mixture of experts), see gemm_sm100.cu
+std::vector<torch::Tensor> gemm_grouped(torch::Tensor a, torch::Tensor w, torch::Tensor tile_expert,
+                                        c10::optional<torch::Tensor> bias, c10::optional<torch::Tensor> residual,
+                                        int64_t act, bool w_row_major, bool dual);
+torch::Tensor gemm_grouped_wgrad(torch::Tensor gy, torch::Tensor x, torch::Tensor offsets, int64_t experts);
 
 }  // namespace vrl

@@ -224,6 +224,31 @@ static CUtensorMap make_map(const void* base, CUtensorMapDataType type, uint64_t
 
 static int* status_word(int device) { return kernel_status_block(device) + kStatusInt4Gemm; }
 
+// Sum of the split-K partial products, rounded to bf16 once: out[i] = sum_s acc[s, i].
+__global__ void splitk_sum_bf16_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ out,
+                                       int splits, int64_t elems) {
+  const int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (i >= elems) return;
+  if (i + 3 < elems) {
+    float4 t = *reinterpret_cast<const float4*>(acc + i);
+    for (int sp = 1; sp < splits; ++sp) {
+      const float4 u = *reinterpret_cast<const float4*>(acc + (int64_t)sp * elems + i);
+      t.x += u.x; t.y += u.y; t.z += u.z; t.w += u.w;
+    }
+    __nv_bfloat162 lo = __floats2bfloat162_rn(t.x, t.y), hi = __floats2bfloat162_rn(t.z, t.w);
+    uint2 packed;
+    packed.x = *reinterpret_cast<uint32_t*>(&lo);
+    packed.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(out + i) = packed;
+  } else {
+    for (int64_t j = i; j < elems; ++j) {
+      float t = 0.f;
+      for (int sp = 0; sp < splits; ++sp) t += acc[(int64_t)sp * elems + j];
+      out[j] = __float2bfloat16_rn(t);
+    }
+  }
+}
+
 }  // namespace i4
 
 torch::Tensor int4_gemm(torch::Tensor x, torch::Tensor qweight, torch::Tensor scales,
@@ -287,7 +312,13 @@ torch::Tensor int4_gemm(torch::Tensor x, torch::Tensor qweight, torch::Tensor sc
   int4_gemm_kernel<<<dim3(n_tiles, p.ksplit), kThreads, kSmemBytes, at::cuda::getCurrentCUDAStream()>>>(
       map_w, map_x, p);
   C10_CUDA_KERNEL_LAUNCH_CHECK();
-  return (p.ksplit == 1 ? acc.select(0, 0) : acc.sum(0)).to(torch::kBFloat16);
+  auto y = torch::empty({m, n}, x.options());
+  const int64_t elems = m * n;                 // m * n * 4 bytes per slice: slices stay 16-byte aligned when elems % 4 == 0
+  if (elems % 4 != 0) return (p.ksplit == 1 ? acc.select(0, 0) : acc.sum(0)).to(torch::kBFloat16);
+  splitk_sum_bf16_kernel<<<(unsigned)((elems / 4 + 255) / 256), 256, 0, at::cuda::getCurrentCUDAStream()>>>(
+      acc.data_ptr<float>(), reinterpret_cast<__nv_bfloat16*>(y.data_ptr()), p.ksplit, elems);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return y;
 }
 
 }  // namespace vrl

@@ -145,7 +145,11 @@ torch::Tensor group_advantages(torch::Tensor rewards, torch::Tensor group_ids, d
 torch::Tensor int4_gemv(torch::Tensor x, torch::Tensor qweight, torch::Tensor scales,
                         c10::optional<torch::Tensor> bias, int64_t group);
 std::vector<torch::Tensor> moe_gate_topk(torch::Tensor logits, int64_t topk);
-std::vector<torch::Tensor> moe_permute(torch::Tensor experts, int64_t num_experts);
+std::vector<torch::Tensor> moe_permute(torch::Tensor experts, int64_t num_experts, int64_t pad);
+std::vector<torch::Tensor> moe_combine_bwd(torch::Tensor gy, torch::Tensor yp, torch::Tensor perm,
+                                           torch::Tensor inv, torch::Tensor weights);
+torch::Tensor moe_segment_colsum(torch::Tensor g, torch::Tensor offsets, int64_t num_experts);
+void lora_apply_rows(torch::Tensor y, torch::Tensor x, torch::Tensor a, torch::Tensor b, double scale);
 torch::Tensor moe_gather_rows(torch::Tensor x, torch::Tensor perm, int64_t topk);
 torch::Tensor moe_combine(torch::Tensor yp, torch::Tensor inv, torch::Tensor weights);
 

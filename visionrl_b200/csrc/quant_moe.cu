@@ -125,10 +125,14 @@ __global__ void moe_gate_topk_kernel(const T* __restrict__ logits, float* __rest
 //   perm[pos]  = flat index of the entry placed at sorted position pos
 //   inv[flat]  = sorted position of the flat entry
 //   offsets[e] = first sorted position of expert e, offsets[E] = total
+// With pad > 1 every expert's run starts on a multiple of `pad` (the tile height of the grouped
+// product): the sorted positions then live in a padded row space whose unused slots keep the
+// perm value they were initialised with (-1), and tile_expert[t] names the expert of padded tile t.
 // ------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(1024)
 moe_permute_kernel(const int32_t* __restrict__ experts, int32_t* __restrict__ perm,
-                   int32_t* __restrict__ inv, int32_t* __restrict__ offsets, int n, int e) {
+                   int32_t* __restrict__ inv, int32_t* __restrict__ offsets,
+                   int32_t* __restrict__ tile_expert, int n, int e, int pad) {
   __shared__ int warp_tot[32];
   __shared__ int base_s;
   const int per = (n + 1023) / 1024;
@@ -155,9 +159,12 @@ moe_permute_kernel(const int32_t* __restrict__ experts, int32_t* __restrict__ pe
         if (lane >= o) wi += v;
       }
       warp_tot[lane] = wi - w;            // exclusive prefix of the warp totals
-      if (lane == 31) offsets[ex + 1] = base_s + wi;
+      if (lane == 31) offsets[ex + 1] = (base_s + wi + pad - 1) / pad * pad;
     }
     __syncthreads();
+    if (tile_expert != nullptr) {
+      for (int t = base_s / pad + threadIdx.x; t < offsets[ex + 1] / pad; t += blockDim.x) tile_expert[t] = ex;
+    }
     int pos = base_s + warp_tot[warp] + incl - c;
     for (int i = lo; i < hi; ++i)
       if (experts[i] == ex) { perm[pos] = i; inv[i] = pos; ++pos; }
@@ -172,10 +179,77 @@ __global__ void moe_gather_rows_kernel(const __nv_bfloat16* __restrict__ x,
                                        const int32_t* __restrict__ perm,
                                        __nv_bfloat16* __restrict__ xp, int dim, int topk) {
   const int64_t pos = blockIdx.x;
-  const int64_t tok = perm[pos] / topk;
-  const bf16x8* src = reinterpret_cast<const bf16x8*>(x + tok * dim);
+  const int flat = perm[pos];
   bf16x8* dst = reinterpret_cast<bf16x8*>(xp + pos * dim);
+  if (flat < 0) {                      // a padding row of the padded layout
+    bf16x8 z;
+    z.u = make_uint4(0u, 0u, 0u, 0u);
+    for (int i = threadIdx.x; i < dim / 8; i += blockDim.x) dst[i] = z;
+    return;
+  }
+  const int64_t tok = flat / topk;
+  const bf16x8* src = reinterpret_cast<const bf16x8*>(x + tok * dim);
   for (int i = threadIdx.x; i < dim / 8; i += blockDim.x) dst[i] = src[i];
+}
+
+// Backward of the combine with respect to the permuted rows: every row has exactly one consumer,
+// g_yp[pos, :] = w[perm[pos]] * gy[perm[pos] / topk, :] (zero for padding rows).
+__global__ void moe_combine_bwd_rows_kernel(const __nv_bfloat16* __restrict__ gy,
+                                            const int32_t* __restrict__ perm, const float* __restrict__ w,
+                                            __nv_bfloat16* __restrict__ g_yp, int dim, int topk) {
+  const int64_t pos = blockIdx.x;
+  const int flat = perm[pos];
+  bf16x8* dst = reinterpret_cast<bf16x8*>(g_yp + pos * dim);
+  if (flat < 0) {
+    bf16x8 z;
+    z.u = make_uint4(0u, 0u, 0u, 0u);
+    for (int i = threadIdx.x; i < dim / 8; i += blockDim.x) dst[i] = z;
+    return;
+  }
+  const float ws = w[flat];
+  const bf16x8* src = reinterpret_cast<const bf16x8*>(gy + (int64_t)(flat / topk) * dim);
+  for (int i = threadIdx.x; i < dim / 8; i += blockDim.x) {
+    float f[8];
+    unpack8(src[i], f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] *= ws;
+    dst[i] = pack8(f);
+  }
+}
+
+// Backward of the combine with respect to the gate weights: g_w[t, s] = <yp[inv[t, s], :], gy[t, :]>.
+__global__ void __launch_bounds__(128)
+moe_combine_bwd_weights_kernel(const __nv_bfloat16* __restrict__ yp, const __nv_bfloat16* __restrict__ gy,
+                               const int32_t* __restrict__ inv, float* __restrict__ g_w, int dim, int topk) {
+  __shared__ float red[32];
+  const int64_t t = blockIdx.x;
+  for (int sl = 0; sl < topk; ++sl) {
+    const int64_t pos = inv[t * topk + sl];
+    float acc = 0.f;
+    for (int i = threadIdx.x; i < dim / 8; i += blockDim.x) {
+      float a[8], b[8];
+      unpack8(reinterpret_cast<const bf16x8*>(yp + pos * dim)[i], a);
+      unpack8(reinterpret_cast<const bf16x8*>(gy + t * dim)[i], b);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc = fmaf(a[j], b[j], acc);
+    }
+    const float total = block_sum(acc, red);
+    if (threadIdx.x == 0) g_w[t * topk + sl] = total;
+  }
+}
+
+// Per-expert column sums of a padded, expert-sorted matrix (bias gradients): out[e, c] += sum of
+// g[r, c] over a chunk of the expert's rows; one thread per column, chunks of rows in blockIdx.z.
+constexpr int kSegRows = 256;
+__global__ void moe_segment_colsum_kernel(const __nv_bfloat16* __restrict__ g, const int32_t* __restrict__ offsets,
+                                          float* __restrict__ out, int n) {
+  const int e = blockIdx.y;
+  const int lo = offsets[e] + blockIdx.z * kSegRows, hi = min(offsets[e + 1], lo + kSegRows);
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= n || lo >= hi) return;
+  float acc = 0.f;
+  for (int r = lo; r < hi; ++r) acc += __bfloat162float(g[(int64_t)r * n + c]);
+  atomicAdd(out + (int64_t)e * n + c, acc);
 }
 
 // y[t, :] = sum_s w[t, s] * yp[inv[t * topk + s], :]
@@ -259,20 +333,76 @@ std::vector<torch::Tensor> moe_gate_topk(torch::Tensor logits, int64_t topk) {
   return {w, idx};
 }
 
-std::vector<torch::Tensor> moe_permute(torch::Tensor experts, int64_t num_experts) {
+// {perm, inv, offsets, tile_expert}.  pad <= 1: dense layout (perm has one entry per (token, slot),
+// tile_expert is empty).  pad > 1: every expert's run is padded to a multiple of `pad` rows; perm
+// then has (ceil(n / pad) + E) * pad entries, -1 in the padding, and tile_expert has one entry per
+// `pad` rows (-1 past the last expert).  The sizes depend on n and E only, never on the routing.
+std::vector<torch::Tensor> moe_permute(torch::Tensor experts, int64_t num_experts, int64_t pad) {
   TORCH_CHECK(experts.is_cuda() && experts.scalar_type() == torch::kInt32 && experts.is_contiguous());
   const c10::cuda::CUDAGuard guard(experts.device());
   const int64_t n = experts.numel();
-  TORCH_CHECK(n < (1 << 30));
-  auto perm = torch::empty({n}, experts.options());
+  TORCH_CHECK(n < (1 << 30) && num_experts >= 1);
+  if (pad < 1) pad = 1;
+  const int64_t slots = pad > 1 ? ((n + pad - 1) / pad + num_experts) * pad : n;
+  auto perm = pad > 1 ? torch::full({slots}, -1, experts.options()) : torch::empty({n}, experts.options());
   auto inv = torch::empty({n}, experts.options());
   auto offsets = torch::zeros({num_experts + 1}, experts.options());
-  if (n == 0) return {perm, inv, offsets};
+  auto tile_expert = pad > 1 ? torch::full({slots / pad}, -1, experts.options()) : torch::empty({0}, experts.options());
+  if (n == 0) return {perm, inv, offsets, tile_expert};
   moe_permute_kernel<<<1, 1024, 0, at::cuda::getCurrentCUDAStream()>>>(
       experts.data_ptr<int32_t>(), perm.data_ptr<int32_t>(), inv.data_ptr<int32_t>(),
-      offsets.data_ptr<int32_t>(), (int)n, (int)num_experts);
+      offsets.data_ptr<int32_t>(), pad > 1 ? tile_expert.data_ptr<int32_t>() : nullptr, (int)n,
+      (int)num_experts, (int)pad);
   C10_CUDA_KERNEL_LAUNCH_CHECK();
-  return {perm, inv, offsets};
+  return {perm, inv, offsets, tile_expert};
+}
+
+// {d(yp) [rows, D] bf16, d(weights) [T, k] fp32} of y[t] = sum_s w[t, s] yp[inv[t, s]]
+std::vector<torch::Tensor> moe_combine_bwd(torch::Tensor gy, torch::Tensor yp, torch::Tensor perm,
+                                           torch::Tensor inv, torch::Tensor weights) {
+  TORCH_CHECK(yp.is_cuda() && yp.dim() == 2 && yp.scalar_type() == torch::kBFloat16 && yp.is_contiguous());
+  TORCH_CHECK(gy.dim() == 2 && gy.scalar_type() == torch::kBFloat16 && gy.is_contiguous() && gy.size(1) == yp.size(1));
+  TORCH_CHECK(weights.dim() == 2 && weights.scalar_type() == torch::kFloat32 && weights.is_contiguous() &&
+              weights.size(0) == gy.size(0));
+  TORCH_CHECK(perm.scalar_type() == torch::kInt32 && perm.is_contiguous() && perm.numel() == yp.size(0) &&
+              inv.scalar_type() == torch::kInt32 && inv.is_contiguous() && inv.numel() == weights.numel() &&
+              yp.size(1) % 8 == 0, "moe_combine_bwd: permutation tables");
+  VRL_CHECK_OPERAND(gy, yp);
+  VRL_CHECK_OPERAND(perm, yp);
+  VRL_CHECK_OPERAND(inv, yp);
+  VRL_CHECK_OPERAND(weights, yp);
+  const c10::cuda::CUDAGuard guard(yp.device());
+  auto g_yp = torch::empty_like(yp);
+  auto g_w = torch::empty_like(weights);
+  auto stream = at::cuda::getCurrentCUDAStream();
+  const int dim = (int)yp.size(1), topk = (int)weights.size(1);
+  if (yp.size(0) > 0)
+    moe_combine_bwd_rows_kernel<<<(int)yp.size(0), 128, 0, stream>>>(
+        reinterpret_cast<const __nv_bfloat16*>(gy.data_ptr()), perm.data_ptr<int32_t>(), weights.data_ptr<float>(),
+        reinterpret_cast<__nv_bfloat16*>(g_yp.data_ptr()), dim, topk);
+  if (gy.size(0) > 0)
+    moe_combine_bwd_weights_kernel<<<(int)gy.size(0), 128, 0, stream>>>(
+        reinterpret_cast<const __nv_bfloat16*>(yp.data_ptr()), reinterpret_cast<const __nv_bfloat16*>(gy.data_ptr()),
+        inv.data_ptr<int32_t>(), g_w.data_ptr<float>(), dim, topk);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return {g_yp, g_w};
+}
+
+// fp32 [E, N]: column sums of g [rows, N] over every expert's row range offsets[e] .. offsets[e + 1]
+torch::Tensor moe_segment_colsum(torch::Tensor g, torch::Tensor offsets, int64_t num_experts) {
+  TORCH_CHECK(g.is_cuda() && g.dim() == 2 && g.scalar_type() == torch::kBFloat16 && g.is_contiguous());
+  VRL_CHECK_OPERAND(offsets, g, torch::kInt32, num_experts + 1);
+  TORCH_CHECK(offsets.is_contiguous());
+  const c10::cuda::CUDAGuard guard(g.device());
+  auto out = torch::zeros({num_experts, g.size(1)}, g.options().dtype(torch::kFloat32));
+  if (g.numel() == 0) return out;
+  const int n = (int)g.size(1);
+  dim3 grid((n + 255) / 256, (unsigned)num_experts, (unsigned)((g.size(0) + kSegRows - 1) / kSegRows));
+  TORCH_CHECK(grid.z <= 65535, "moe_segment_colsum: too many rows");
+  moe_segment_colsum_kernel<<<grid, 256, 0, at::cuda::getCurrentCUDAStream()>>>(
+      reinterpret_cast<const __nv_bfloat16*>(g.data_ptr()), offsets.data_ptr<int32_t>(), out.data_ptr<float>(), n);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return out;
 }
 
 torch::Tensor moe_gather_rows(torch::Tensor x, torch::Tensor perm, int64_t topk) {

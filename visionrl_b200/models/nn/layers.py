@@ -109,9 +109,28 @@ class LoRALinear(Linear):
         if not (self.has_adapter and self.adapter_enabled):
             return super().forward(x, act=act, gate=gate, residual=residual)
         y = self._base(x)
+        if self._decode_sized(x, y):
+            # a handful of rows without autograd (the decode step): two tiny kernels update y in place
+            from visionrl_b200.ops import _ext
+
+            x2 = x.reshape(-1, x.shape[-1])
+            y2 = y.reshape(-1, y.shape[-1])
+            _ext.load().lora_apply_rows(y2, x2 if x2.is_contiguous() else x2.contiguous(), self.lora_A,
+                                        self.lora_B, float(self.lora_scale))
+            return linear_ops.linear_epilogue(y, act, gate, residual)
         low = linear_ops.linear(x, self.lora_A)
         y = y + self.lora_scale * linear_ops.linear(low, self.lora_B)
         return linear_ops.linear_epilogue(y, act, gate, residual)
+
+    def _decode_sized(self, x, y) -> bool:
+        from visionrl_b200.ops import _ext
+
+        a, b = self.lora_A, self.lora_B
+        return (not torch.is_grad_enabled() and x.is_cuda and x.dtype == torch.bfloat16
+                and y.dtype == torch.bfloat16 and y.is_contiguous()
+                and x.numel() // x.shape[-1] <= 64 and a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+                and a.is_contiguous() and b.is_contiguous() and a.shape[0] % 8 == 0 and a.shape[0] <= 256
+                and x.shape[-1] % 8 == 0 and _ext.kernels_enabled() and _ext.has("lora_apply_rows"))
 
 
 _INT4_DECODE_ACTIVE = False

@@ -26,7 +26,7 @@ _LAUNCHES = {
     "decode_attention": 1, "decode_qkv_rope_append": 1, "swiglu_rows": 1, "add_rmsnorm_rows": 1, "rs_sum_slice": 1, "adamw_slice_broadcast": 1, "int4_gemv": 1,
     "sample_tokens": 1, "lse_chunk_update": 1, "softmax_grad_chunk": 1, "group_advantages": 1,
     "flag_signal": 1, "flag_wait": 1, "flag_barrier": 1, "bucket_reduce_acc": 1, "p2p_gather_rows": 1, "p2p_gather_table": 1, "p2p_broadcast_table": 1,
-    "head_logprob_fwd": 2, "head_softmax_grad": 1, "gemm_bf16_out": 1, "groupnorm_nhwc": 2, "gemm_bf16_acc": 1, "gemm_allgather": 1, "int4_gemm": 1, "gemm_bf16_dual": 1, "gate_residual_fwd": 1, "gate_residual_bwd": 1, "flash_attn_fwd": 1, "flash_attn_fwd_peers": 1, "moe_gate_topk": 1, "moe_permute": 1, "moe_gather_rows": 1, "moe_combine": 1,
+    "head_logprob_fwd": 2, "head_softmax_grad": 1, "gemm_bf16_out": 1, "groupnorm_nhwc": 2, "gemm_bf16_acc": 1, "gemm_allgather": 1, "int4_gemm": 2, "gemm_bf16_dual": 1, "gate_residual_fwd": 1, "gate_residual_bwd": 1, "flash_attn_fwd": 1, "flash_attn_fwd_peers": 1, "moe_gate_topk": 1, "moe_permute": 1, "moe_gather_rows": 1, "moe_combine": 1, "moe_combine_bwd": 2, "moe_segment_colsum": 1, "lora_apply_rows": 2, "gemm_grouped": 1, "gemm_grouped_wgrad": 1,
 }
 launch_count = 0
 _kernels_enabled = os.environ.get("VRL_FORCE_TORCH_OPS", "0") != "1"

@@ -29,6 +29,10 @@ def _time(fn, iters: int, warmup: int, flush: torch.Tensor | None) -> float:
             flush.add_(1)
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
+        # keep the device busy for ~0.1 ms while the host enqueues the work: the events then bracket
+        # device execution only, not the launch latency of the first kernel (which would dominate a
+        # kernel of a few microseconds)
+        torch.cuda._sleep(200_000)
         start.record()
         fn()
         stop.record()
