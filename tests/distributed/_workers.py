@@ -315,6 +315,19 @@ def fsdp_training_matches_replicated(rank, world, port, backend, collectives, re
         gathers_before = rt.gathers
         net(lat, t, ctx, pooled)
         replica_used = rt.gathers == gathers_before       # a no-grad forward needs no gather
+    if replica:
+        rt.verify_replicas()                              # every rank holds the same replica bits
+        if rank == world - 1:
+            # a torn replica on one rank must be noticed by all of them (host-side injection)
+            rt.replica_flat[7] += 1.0
+        try:
+            rt.verify_replicas()
+            caught = False
+        except RuntimeError as exc:
+            caught = "replicas differ" in str(exc)
+        assert caught, "a replica that differs on one rank went unnoticed"
+        if rank == world - 1:
+            rt.replica_flat[7] -= 1.0
     full = net.state_dict()          # gathers every sharded weight to its full shape
     ref_state = ref.state_dict()
     err = max((full[k].float().cpu() - ref_state[k]).abs().max().item() for k in ref_state)

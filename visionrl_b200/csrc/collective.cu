@@ -249,6 +249,15 @@ void p2p_broadcast_versioned(torch::Tensor src, torch::Tensor dst_peers, int64_t
 // Table-driven form of the broadcast: segment j copies `count` 16-bit elements from
 // src_flat + src_off to offset dst_off of EVERY rank's destination buffer.  One launch publishes
 // all of a rank's parameter shards into the rollout replicas of the whole group.
+// Blocks per segment of the table-driven kernels: enough blocks in total to give every SM several
+// (a peer access takes microseconds, so bandwidth over NVLink needs many requests in flight),
+// however few segments the table has, and never more than the longest segment can feed.
+static int table_grid_x(int64_t segments, int64_t max_segment) {
+  const int64_t wanted = (148 * 8 + segments - 1) / segments;
+  const int64_t useful = (max_segment / 8 + 255) / 256;
+  return (int)std::max<int64_t>(1, std::min<int64_t>(std::min(wanted, useful), 65535));
+}
+
 __global__ void __launch_bounds__(256)
 p2p_broadcast_table_kernel(const uint4* __restrict__ src, PeerPtrs dst, const int64_t* __restrict__ table,
                            int world, int rank) {
@@ -276,7 +285,7 @@ void p2p_broadcast_table(torch::Tensor src_flat, torch::Tensor dst_peers, torch:
   TORCH_CHECK(world >= 1 && world <= kMaxPeers && rank >= 0 && rank < world && max_segment > 0);
   const c10::cuda::CUDAGuard guard(src_flat.device());
   const PeerPtrs dp = load_peers(dst_peers, (int)world);
-  const int bx = (int)std::max<int64_t>(1, std::min<int64_t>((max_segment / 8 + 255) / 256, 32));
+  const int bx = table_grid_x(table.size(0), max_segment);
   p2p_broadcast_table_kernel<<<dim3(bx, (unsigned)table.size(0)), 256, 0, at::cuda::getCurrentCUDAStream()>>>(
       reinterpret_cast<const uint4*>(src_flat.data_ptr()), dp, table.data_ptr<int64_t>(), (int)world, (int)rank);
   C10_CUDA_KERNEL_LAUNCH_CHECK();
@@ -475,7 +484,7 @@ void bucket_reduce_acc(torch::Tensor stage_peers, torch::Tensor table, torch::Te
   TORCH_CHECK(world >= 1 && world <= kMaxPeers && rank >= 0 && rank < world && max_segment > 0);
   const c10::cuda::CUDAGuard guard(gshard.device());
   const PeerPtrs sp = load_peers(stage_peers, (int)world);
-  const int bx = (int)std::max<int64_t>(1, std::min<int64_t>((max_segment / 8 + 255) / 256, 64));
+  const int bx = table_grid_x(table.size(0), max_segment);
   bucket_reduce_acc_kernel<<<dim3(bx, (unsigned)table.size(0)), 256, 0, at::cuda::getCurrentCUDAStream()>>>(
       sp, table.data_ptr<int64_t>(), gshard.data_ptr<float>(), (float)scale, (int)world, (int)rank);
   C10_CUDA_KERNEL_LAUNCH_CHECK();
@@ -532,7 +541,7 @@ void p2p_gather_table(torch::Tensor shard_peers, torch::Tensor dst, torch::Tenso
   TORCH_CHECK(world >= 1 && world <= kMaxPeers && rank >= 0 && rank < world && max_segment > 0);
   const c10::cuda::CUDAGuard guard(dst.device());
   const PeerPtrs sp = load_peers(shard_peers, (int)world);
-  const int bx = (int)std::max<int64_t>(1, std::min<int64_t>((max_segment / 8 + 1023) / 1024, 16));
+  const int bx = table_grid_x(table.size(0), max_segment);
   p2p_gather_table_kernel<<<dim3(bx, (unsigned)table.size(0)), 256, 0, at::cuda::getCurrentCUDAStream()>>>(
       sp, reinterpret_cast<uint4*>(dst.data_ptr()), table.data_ptr<int64_t>(), (int)world, (int)rank);
   C10_CUDA_KERNEL_LAUNCH_CHECK();

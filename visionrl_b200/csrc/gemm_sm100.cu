@@ -198,10 +198,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   tmem_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 0 && lane == 0) {
+  if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
+    // Lane 0 does the waiting; the copies of a stage are issued by as many lanes as there are
+    // copies (one per operand, or one per 64-wide chunk of an MN-major operand: up to six), each
+    // lane one, so a stage costs the warp one issue slot instead of up to six in a row from a
+    // single thread (which took longer than the stage's products and starved the tensor pipe).
+    const int na = p.a_mn ? BM / 64 : 1, nb = p.b_mn ? BN / 64 : 1;
+    const int my_op = lane < na ? 0 : (lane < na + nb ? 1 : 2);      // 0: A copy, 1: B copy, 2: none
+    const int my_c = my_op == 0 ? lane : lane - na;
     uint32_t it = 0;
-    bool ok = true;
+    int ok = 1;
     uint32_t slabs_seen = 0;       // bit r: the rows of rank r are known to be in g_full
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       const TileInfo ti = tile_info<kGather>(tile, m_tiles, n_tiles, k_blocks, p);
@@ -209,58 +216,61 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       const int m0 = ti.m0, n0 = ti.n0;
       if (kGather) {
         // the B rows of this tile must have been copied by the gather warps of EVERY CTA
-        const int lo = n0 / p.g_rows, hi = min(p.n - 1, n0 + BN - 1) / p.g_rows;
-        for (int r = lo; r <= hi && ok; ++r) {
-          if (slabs_seen & (1u << r)) continue;
-          bool ready = false;
-          for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
-            int v;
-            asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p.g_ready + r) : "memory");
-            if (v >= (int)gridDim.x) { ready = true; break; }
-            if ((spin & 1023u) == 1023u && *abort_flag) break;
+        if (lane == 0) {
+          const int lo = n0 / p.g_rows, hi = min(p.n - 1, n0 + BN - 1) / p.g_rows;
+          for (int r = lo; r <= hi && ok; ++r) {
+            if (slabs_seen & (1u << r)) continue;
+            bool ready = false;
+            for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+              int v;
+              asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p.g_ready + r) : "memory");
+              if (v >= (int)gridDim.x) { ready = true; break; }
+              if ((spin & 1023u) == 1023u && *abort_flag) break;
+            }
+            if (!ready) { ok = 0; break; }
+            slabs_seen |= 1u << r;
           }
-          if (!ready) { ok = false; break; }
-          slabs_seen |= 1u << r;
-          asm volatile("fence.proxy.async;" ::: "memory");   // generic-proxy writes -> TMA reads
         }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
         if (!ok) break;
+        asm volatile("fence.proxy.async;" ::: "memory");   // generic-proxy writes -> TMA reads
       }
       for (int kb = 0; kb < ti.kbn; ++kb, ++it) {
         const int s = it % kStages;
         const uint32_t parity = ((it / kStages) & 1u) ^ 1u;
-        if (!mbar_wait(&empty[s], parity, abort_flag)) { ok = false; break; }
+        if (lane == 0) {
+          ok = mbar_wait(&empty[s], parity, abort_flag) ? 1 : 0;
+          if (ok) mbar_expect_tx(&full[s], kStageBytes);
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) break;
+        __syncwarp();
         uint8_t* sa = smem + s * kStageBytes;
         uint8_t* sb = sa + kABytes;
-        mbar_expect_tx(&full[s], kStageBytes);
         const int k0 = (ti.kb0 + kb) * BK;
-        if (!p.a_mn) {
-          tma_load_2d(sa, &map_a, &full[s], k0, m0);
-        } else {
-#pragma unroll
-          for (int c = 0; c < BM / 64; ++c)
-            tma_load_2d(sa + c * (BK * 128), &map_a, &full[s], m0 + c * 64, k0);
-        }
-        if (!p.b_mn) {
-          tma_load_2d(sb, &map_b, &full[s], k0, n0 + ti.b_off);
-        } else {
+        if (my_op == 0) {
+          if (!p.a_mn) tma_load_2d(sa, &map_a, &full[s], k0, m0);
+          else tma_load_2d(sa + my_c * (BK * 128), &map_a, &full[s], m0 + my_c * 64, k0);
+        } else if (my_op == 1) {
           // grouped mode 1 with a row-major B: the expert's matrix starts b_off rows down the
           // contraction coordinate; mode 2 contracts over the rows themselves (b_off = 0)
-#pragma unroll
-          for (int c = 0; c < BN / 64; ++c)
-            tma_load_2d(sb + c * (BK * 128), &map_b, &full[s], n0 + c * 64, k0 + ti.b_off);
+          if (!p.b_mn) tma_load_2d(sb, &map_b, &full[s], k0, n0 + ti.b_off);
+          else tma_load_2d(sb + my_c * (BK * 128), &map_b, &full[s], n0 + my_c * 64, k0 + ti.b_off);
         }
       }
     }
-    if (!ok) {
-      if (atomicCAS(const_cast<int*>(abort_flag), 0, 1) == 0) atomicExch(p.status, kTimeoutProducer);
-    }
-    // copies still in flight target this CTA's shared memory: give them time to land
-    if (*abort_flag) {
-      const uint32_t issued = it;
-      for (uint32_t j = issued > (uint32_t)kStages ? issued - kStages : 0; j < issued; ++j) {
-        const int s = j % kStages;
-        for (uint32_t spin = 0; spin < (1u << 20); ++spin)
-          if (mbar_try(&full[s], (j / kStages) & 1u)) break;
+    if (lane == 0) {
+      if (!ok) {
+        if (atomicCAS(const_cast<int*>(abort_flag), 0, 1) == 0) atomicExch(p.status, kTimeoutProducer);
+      }
+      // copies still in flight target this CTA's shared memory: give them time to land
+      if (*abort_flag) {
+        const uint32_t issued = it;
+        for (uint32_t j = issued > (uint32_t)kStages ? issued - kStages : 0; j < issued; ++j) {
+          const int s = j % kStages;
+          for (uint32_t spin = 0; spin < (1u << 20); ++spin)
+            if (mbar_try(&full[s], (j / kStages) & 1u)) break;
+        }
       }
     }
   } else if (warp == 1 && lane == 0) {

@@ -43,6 +43,10 @@ class NextStep1ARChunkResult(PipelineChunkResult):
 def _pack(request, sample_specs, fields, context, steps, micro_batches, peak) -> OutputBatch:
     extra = {k: fields[k] for k in _ROW_FIELDS if k != "output"}
     extra["context"] = dict(context)
+    # what reward models see: [0, 1] pixels when asked for, otherwise the decoder's own range
+    images = fields["output"]
+    extra["images_for_reward"] = ((images + 1.0) * 0.5).clamp(0.0, 1.0) if context.get("rescale_to_unit", True) \
+        else images
     return OutputBatch(
         request_id=request.request_id, family=request.family, task=request.task,
         prompts=list(request.prompts), sample_specs=list(sample_specs), output=fields["output"],

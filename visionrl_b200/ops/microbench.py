@@ -191,6 +191,43 @@ def bench_rowwise(args) -> dict:
     return out
 
 
+def bench_decode(args) -> dict:
+    """The three kernels a decode step of the LLaMA trunk spends its time in, at decode size: the int4
+    weight-only GEMM (per projection), decode attention over a half-filled cache, and the low-rank
+    update.  GB/s counts the bytes each must read once."""
+    from visionrl_b200.ops import _ext
+    from visionrl_b200.ops.quant import quantize_int4
+
+    ext = _ext.load()
+    rows, d, heads, ffn, length, rank = args.rows, args.dim, args.heads, args.ffn, args.length, args.rank
+    dev, bf = "cuda", torch.bfloat16
+    flush = _flush_buffer(not args.no_flush)
+    out = {"kernel": "decode", "rows": rows, "dim": d, "heads": heads, "ffn": ffn, "cache_len": length}
+    x = torch.randn(rows, d, device=dev, dtype=bf)
+    for name, (n, k) in {"int4_qkv": (3 * d, d), "int4_out": (d, d), "int4_gate_up": (2 * ffn, d),
+                         "int4_down": (d, ffn)}.items():
+        w = torch.randn(n, k, device=dev) * 0.02
+        packed, scales = quantize_int4(w, 128)
+        xin = x if k == d else torch.randn(rows, k, device=dev, dtype=bf)
+        t = _time(lambda: ext.int4_gemm(xin, packed, scales, None, 128), args.iters, args.warmup, flush)
+        out[name] = {"ms": round(t, 4), "gbs": round(n * k / 2 / t / 1e6, 1)}
+    dh = d // heads
+    q = torch.randn(rows, heads, 1, dh, device=dev, dtype=bf)
+    kc = torch.randn(rows, heads, length, dh, device=dev, dtype=bf)
+    vc = torch.randn(rows, heads, length, dh, device=dev, dtype=bf)
+    valid = torch.zeros(rows, length, device=dev, dtype=torch.bool)
+    valid[:, :length // 2] = True
+    t = _time(lambda: ext.decode_attention(q, kc, vc, valid, length, dh ** -0.5), args.iters, args.warmup, flush)
+    out["decode_attention"] = {"ms": round(t, 4),
+                               "gbs": round(2 * rows * heads * (length // 2) * dh * 2 / t / 1e6, 1)}
+    a = torch.randn(rank, d, device=dev, dtype=bf)
+    b = torch.randn(3 * d, rank, device=dev, dtype=bf)
+    y = torch.zeros(rows, 3 * d, device=dev, dtype=bf)
+    t = _time(lambda: ext.lora_apply_rows(y, x, a, b, 1.0), args.iters, args.warmup, flush)
+    out["lora_apply_rows"] = {"ms": round(t, 4)}
+    return out
+
+
 def bench_attention(args) -> dict:
     from visionrl_b200.ops.attention import flash_attention_forward
 
@@ -315,6 +352,14 @@ def main(argv=None) -> int:
     rw.add_argument("--dim", type=int, default=1536)
     rw.add_argument("--heads", type=int, default=24)
     rw.set_defaults(fn=bench_rowwise)
+    dc = sub.add_parser("decode")
+    dc.add_argument("--rows", type=int, default=32)
+    dc.add_argument("--dim", type=int, default=2048)
+    dc.add_argument("--heads", type=int, default=16)
+    dc.add_argument("--ffn", type=int, default=5632)
+    dc.add_argument("--length", type=int, default=640)
+    dc.add_argument("--rank", type=int, default=32)
+    dc.set_defaults(fn=bench_decode)
     t = sub.add_parser("attention")
     t.add_argument("--batch", type=int, default=16)
     t.add_argument("--heads", type=int, default=24)

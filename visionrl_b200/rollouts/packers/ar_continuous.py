@@ -16,7 +16,8 @@ from visionrl_b200.rollouts.packers.base import RolloutPackContext, prompt_group
 
 class ARContinuousRolloutPacker:
     def reward_outputs(self, output: OutputBatch, context: RolloutPackContext) -> Any:
-        return _unit_images(output.output, context.rescale_to_unit)
+        ready = output.extra.get("images_for_reward") if isinstance(output.extra, dict) else None
+        return ready if ready is not None else _unit_images(output.output, context.rescale_to_unit)
 
     def reward_prompts(self, output: OutputBatch, context: RolloutPackContext) -> list[str]:
         return [s.prompt for s in output.sample_specs]

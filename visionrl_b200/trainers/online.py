@@ -487,6 +487,9 @@ class OnlineTrainer(Trainer):
         num_accum = len(kept)
         if cfg.debug.first_step and self.state.step == 0:
             self._debug_first_step(kept[0], ctx)
+            runtime_check = getattr(getattr(self.model, "param_runtime", None), "verify_replicas", None)
+            if runtime_check is not None:
+                runtime_check()             # every rank rolled out with the same weights
 
         need_ref = self.algorithm.config.init_kl_coef > 0
         request = SignalRequest(need_ref=need_ref, need_kl_intermediates=need_ref)
