@@ -221,10 +221,10 @@ sample_tokens_kernel(const T* __restrict__ cond, const T* __restrict__ uncond,
 // ------------------------------------------------------------------------------------------
 // Decode attention: one query position per (row, head) against a static cache.
 // q [R, H, D], caches [R, H, L, D] (strided), valid [R, L]; D = 128.  One block of 4 warps per
-// (row, head); every warp walks runs of 8 keys with an online softmax, lanes own 4 dims.
+// (row, head); every warp walks runs of 16 keys with an online softmax, lanes own 4 dims.
 // ------------------------------------------------------------------------------------------
 constexpr int kDecodeWarps = 4;
-constexpr int kDecodeKeys = 8;
+constexpr int kDecodeKeys = 16;
 
 __global__ void __launch_bounds__(kDecodeWarps * 32)
 decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kc,
@@ -698,34 +698,39 @@ lora_down_rows_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* 
   if (lane == 0) low[(int64_t)row * rank + j] = acc;
 }
 
+template <int kRank>
 __global__ void __launch_bounds__(256)
 lora_up_add_rows_kernel(__nv_bfloat16* __restrict__ y, const float* __restrict__ low,
-                        const __nv_bfloat16* __restrict__ b, int rows, int n, int rank, float scale) {
-  extern __shared__ float low_s[];                 // [kLoraRowsPerBlock][rank]
+                        const __nv_bfloat16* __restrict__ b, int rows, int n, float scale) {
+  __shared__ __align__(16) float low_s[kLoraRowsPerBlock * kRank];
   const int row0 = blockIdx.y * kLoraRowsPerBlock;
   const int nrows = min(kLoraRowsPerBlock, rows - row0);
-  for (int i = threadIdx.x; i < nrows * rank; i += blockDim.x) low_s[i] = low[(int64_t)row0 * rank + i] * scale;
+  for (int i = threadIdx.x; i < kLoraRowsPerBlock * kRank; i += blockDim.x)
+    low_s[i] = i < nrows * kRank ? low[(int64_t)row0 * kRank + i] * scale : 0.f;
   __syncthreads();
   const int col = blockIdx.x * blockDim.x + threadIdx.x;
   if (col >= n) return;
-  float acc[kLoraRowsPerBlock];
+  // this column's adapter row stays in registers; the rows' low-rank activations are broadcast
+  // reads of shared memory, four values at a time
+  float bv[kRank];
+  const bf16x8* br = reinterpret_cast<const bf16x8*>(b + (int64_t)col * kRank);
 #pragma unroll
-  for (int r = 0; r < kLoraRowsPerBlock; ++r) acc[r] = 0.f;
-  const bf16x8* br = reinterpret_cast<const bf16x8*>(b + (int64_t)col * rank);
-  for (int i = 0; i < rank / 8; ++i) {
-    float bv[8];
-    unpack8(br[i], bv);
+  for (int i = 0; i < kRank / 8; ++i) unpack8(br[i], bv + i * 8);
 #pragma unroll
-    for (int r = 0; r < kLoraRowsPerBlock; ++r) {
-      if (r < nrows) {
+  for (int r = 0; r < kLoraRowsPerBlock; ++r) {
+    if (r >= nrows) break;
+    const float4* lr = reinterpret_cast<const float4*>(low_s + r * kRank);
+    float acc = 0.f;
 #pragma unroll
-        for (int t = 0; t < 8; ++t) acc[r] = fmaf(low_s[r * rank + i * 8 + t], bv[t], acc[r]);
-      }
+    for (int i = 0; i < kRank / 4; ++i) {
+      const float4 l4 = lr[i];
+      acc = fmaf(l4.x, bv[4 * i], acc);
+      acc = fmaf(l4.y, bv[4 * i + 1], acc);
+      acc = fmaf(l4.z, bv[4 * i + 2], acc);
+      acc = fmaf(l4.w, bv[4 * i + 3], acc);
     }
-  }
-  for (int r = 0; r < nrows; ++r) {
     __nv_bfloat16* dst = y + (int64_t)(row0 + r) * n + col;
-    *dst = __float2bfloat16_rn(__bfloat162float(*dst) + acc[r]);
+    *dst = __float2bfloat16_rn(__bfloat162float(*dst) + acc);
   }
 }
 
@@ -743,7 +748,8 @@ void lora_apply_rows(torch::Tensor y, torch::Tensor x, torch::Tensor a, torch::T
               b.dim() == 2 && b.is_contiguous() && a.size(1) == x.size(1) && b.size(0) == n && b.size(1) == a.size(0),
               "lora_apply_rows: x [R, K], A [r, K], B [N, r]");
   const int64_t k = x.size(1), rank = a.size(0);
-  TORCH_CHECK(rows <= 64 && k % 8 == 0 && rank % 8 == 0 && rank <= 256, "lora_apply_rows: R <= 64, K % 8 == 0, r % 8 == 0");
+  TORCH_CHECK(rows <= 64 && k % 8 == 0 && (rank == 8 || rank == 16 || rank == 32 || rank == 64),
+              "lora_apply_rows: R <= 64, K % 8 == 0, adapter rank 8, 16, 32 or 64");
   if (rows == 0 || n == 0) return;
   const c10::cuda::CUDAGuard guard(y.device());
   auto low = torch::empty({rows, rank}, y.options().dtype(torch::kFloat32));
@@ -752,10 +758,15 @@ void lora_apply_rows(torch::Tensor y, torch::Tensor x, torch::Tensor a, torch::T
   lora_down_rows_kernel<<<dim3((unsigned)rank, row_blocks), kLoraRowsPerBlock * 32, 0, stream>>>(
       reinterpret_cast<const __nv_bfloat16*>(x.data_ptr()), reinterpret_cast<const __nv_bfloat16*>(a.data_ptr()),
       low.data_ptr<float>(), (int)rows, (int)k, (int)rank);
-  lora_up_add_rows_kernel<<<dim3((unsigned)((n + 255) / 256), row_blocks), 256,
-                            kLoraRowsPerBlock * rank * sizeof(float), stream>>>(
-      reinterpret_cast<__nv_bfloat16*>(y.data_ptr()), low.data_ptr<float>(),
-      reinterpret_cast<const __nv_bfloat16*>(b.data_ptr()), (int)rows, (int)n, (int)rank, (float)scale);
+  const dim3 up_grid((unsigned)((n + 255) / 256), row_blocks);
+  __nv_bfloat16* yp = reinterpret_cast<__nv_bfloat16*>(y.data_ptr());
+  const __nv_bfloat16* bp = reinterpret_cast<const __nv_bfloat16*>(b.data_ptr());
+  switch (rank) {
+    case 8: lora_up_add_rows_kernel<8><<<up_grid, 256, 0, stream>>>(yp, low.data_ptr<float>(), bp, (int)rows, (int)n, (float)scale); break;
+    case 16: lora_up_add_rows_kernel<16><<<up_grid, 256, 0, stream>>>(yp, low.data_ptr<float>(), bp, (int)rows, (int)n, (float)scale); break;
+    case 32: lora_up_add_rows_kernel<32><<<up_grid, 256, 0, stream>>>(yp, low.data_ptr<float>(), bp, (int)rows, (int)n, (float)scale); break;
+    default: lora_up_add_rows_kernel<64><<<up_grid, 256, 0, stream>>>(yp, low.data_ptr<float>(), bp, (int)rows, (int)n, (float)scale); break;
+  }
   C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
 

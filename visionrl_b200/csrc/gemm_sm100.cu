@@ -22,6 +22,9 @@
 #include <cudaTypedefs.h>
 #include <torch/extension.h>
 
+#include <cstdlib>
+#include <string>
+
 #include <map>
 #include <mutex>
 #include <tuple>
@@ -61,6 +64,7 @@ struct Params {
   int rows_per_gate;
   int64_t gate_ld;                 // elements between consecutive gate rows
   int a_mn, b_mn;
+  int a_mn3, b_mn3;                // the MN-major operand's map is 3-D: one copy per stage instead of one per 64-wide chunk
   int out_fp32;
   // all-gather fused into the GEMM (B operand sharded by rows over `g_world` ranks)
   const __nv_bfloat16* g_peer[16]; // every rank's shard [g_rows, K] (peer-mapped pointers)
@@ -198,17 +202,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   tmem_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 0) {
+  if (warp == 0 && lane == 0) {
     // ------------------------------------------------------------------ TMA producer
-    // Lane 0 does the waiting; the copies of a stage are issued by as many lanes as there are
-    // copies (one per operand, or one per 64-wide chunk of an MN-major operand: up to six), each
-    // lane one, so a stage costs the warp one issue slot instead of up to six in a row from a
-    // single thread (which took longer than the stage's products and starved the tensor pipe).
-    const int na = p.a_mn ? BM / 64 : 1, nb = p.b_mn ? BN / 64 : 1;
-    const int my_op = lane < na ? 0 : (lane < na + nb ? 1 : 2);      // 0: A copy, 1: B copy, 2: none
-    const int my_c = my_op == 0 ? lane : lane - na;
     uint32_t it = 0;
-    int ok = 1;
+    bool ok = true;
     uint32_t slabs_seen = 0;       // bit r: the rows of rank r are known to be in g_full
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       const TileInfo ti = tile_info<kGather>(tile, m_tiles, n_tiles, k_blocks, p);
@@ -216,61 +213,62 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       const int m0 = ti.m0, n0 = ti.n0;
       if (kGather) {
         // the B rows of this tile must have been copied by the gather warps of EVERY CTA
-        if (lane == 0) {
-          const int lo = n0 / p.g_rows, hi = min(p.n - 1, n0 + BN - 1) / p.g_rows;
-          for (int r = lo; r <= hi && ok; ++r) {
-            if (slabs_seen & (1u << r)) continue;
-            bool ready = false;
-            for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
-              int v;
-              asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p.g_ready + r) : "memory");
-              if (v >= (int)gridDim.x) { ready = true; break; }
-              if ((spin & 1023u) == 1023u && *abort_flag) break;
-            }
-            if (!ready) { ok = 0; break; }
-            slabs_seen |= 1u << r;
+        const int lo = n0 / p.g_rows, hi = min(p.n - 1, n0 + BN - 1) / p.g_rows;
+        for (int r = lo; r <= hi && ok; ++r) {
+          if (slabs_seen & (1u << r)) continue;
+          bool ready = false;
+          for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+            int v;
+            asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p.g_ready + r) : "memory");
+            if (v >= (int)gridDim.x) { ready = true; break; }
+            if ((spin & 1023u) == 1023u && *abort_flag) break;
           }
+          if (!ready) { ok = false; break; }
+          slabs_seen |= 1u << r;
+          asm volatile("fence.proxy.async;" ::: "memory");   // generic-proxy writes -> TMA reads
         }
-        ok = __shfl_sync(0xffffffffu, ok, 0);
         if (!ok) break;
-        asm volatile("fence.proxy.async;" ::: "memory");   // generic-proxy writes -> TMA reads
       }
       for (int kb = 0; kb < ti.kbn; ++kb, ++it) {
         const int s = it % kStages;
         const uint32_t parity = ((it / kStages) & 1u) ^ 1u;
-        if (lane == 0) {
-          ok = mbar_wait(&empty[s], parity, abort_flag) ? 1 : 0;
-          if (ok) mbar_expect_tx(&full[s], kStageBytes);
-        }
-        ok = __shfl_sync(0xffffffffu, ok, 0);
-        if (!ok) break;
-        __syncwarp();
+        if (!mbar_wait(&empty[s], parity, abort_flag)) { ok = false; break; }
         uint8_t* sa = smem + s * kStageBytes;
         uint8_t* sb = sa + kABytes;
+        mbar_expect_tx(&full[s], kStageBytes);
         const int k0 = (ti.kb0 + kb) * BK;
-        if (my_op == 0) {
-          if (!p.a_mn) tma_load_2d(sa, &map_a, &full[s], k0, m0);
-          else tma_load_2d(sa + my_c * (BK * 128), &map_a, &full[s], m0 + my_c * 64, k0);
-        } else if (my_op == 1) {
+        if (!p.a_mn) {
+          tma_load_2d(sa, &map_a, &full[s], k0, m0);
+        } else if (p.a_mn3) {
+          tma_load_3d(sa, &map_a, &full[s], 0, k0, m0 / 64);
+        } else {
+#pragma unroll
+          for (int c = 0; c < BM / 64; ++c)
+            tma_load_2d(sa + c * (BK * 128), &map_a, &full[s], m0 + c * 64, k0);
+        }
+        if (!p.b_mn) {
+          tma_load_2d(sb, &map_b, &full[s], k0, n0 + ti.b_off);
+        } else if (p.b_mn3) {
+          tma_load_3d(sb, &map_b, &full[s], 0, k0 + ti.b_off, n0 / 64);
+        } else {
           // grouped mode 1 with a row-major B: the expert's matrix starts b_off rows down the
           // contraction coordinate; mode 2 contracts over the rows themselves (b_off = 0)
-          if (!p.b_mn) tma_load_2d(sb, &map_b, &full[s], k0, n0 + ti.b_off);
-          else tma_load_2d(sb + my_c * (BK * 128), &map_b, &full[s], n0 + my_c * 64, k0 + ti.b_off);
+#pragma unroll
+          for (int c = 0; c < BN / 64; ++c)
+            tma_load_2d(sb + c * (BK * 128), &map_b, &full[s], n0 + c * 64, k0 + ti.b_off);
         }
       }
     }
-    if (lane == 0) {
-      if (!ok) {
-        if (atomicCAS(const_cast<int*>(abort_flag), 0, 1) == 0) atomicExch(p.status, kTimeoutProducer);
-      }
-      // copies still in flight target this CTA's shared memory: give them time to land
-      if (*abort_flag) {
-        const uint32_t issued = it;
-        for (uint32_t j = issued > (uint32_t)kStages ? issued - kStages : 0; j < issued; ++j) {
-          const int s = j % kStages;
-          for (uint32_t spin = 0; spin < (1u << 20); ++spin)
-            if (mbar_try(&full[s], (j / kStages) & 1u)) break;
-        }
+    if (!ok) {
+      if (atomicCAS(const_cast<int*>(abort_flag), 0, 1) == 0) atomicExch(p.status, kTimeoutProducer);
+    }
+    // copies still in flight target this CTA's shared memory: give them time to land
+    if (*abort_flag) {
+      const uint32_t issued = it;
+      for (uint32_t j = issued > (uint32_t)kStages ? issued - kStages : 0; j < issued; ++j) {
+        const int s = j % kStages;
+        for (uint32_t spin = 0; spin < (1u << 20); ++spin)
+          if (mbar_try(&full[s], (j / kStages) & 1u)) break;
       }
     }
   } else if (warp == 1 && lane == 0) {
@@ -599,9 +597,39 @@ static CUtensorMap make_map(const void* base, uint64_t inner, uint64_t outer, ui
   return map;
 }
 
+// 3-D map of an MN-major operand stored [rows = k, mn] with pitch `pitch_elems`: (64 mn, k, mn / 64).
+// One box of (64, BK, chunks) lands in shared memory as `chunks` consecutive [BK x 128-byte] blocks,
+// the layout the MN-major descriptors expect, with ONE copy instruction: the producer thread's
+// issue slots are the scarce resource of the pipeline, and a copy per 64-wide chunk (up to six per
+// stage) ate into the latency the four stages can hide.  The chunk dimension has a smaller stride
+// than the row dimension; where the driver's encoder refuses that, the caller keeps the 2-D maps.
+static bool make_map_mn3(CUtensorMap* map, const void* base, uint64_t mn, uint64_t k, uint64_t pitch_elems,
+                         uint32_t chunks) {
+  static int supported = -1;                     // -1 unknown, 0 refused once, 1 accepted
+  if (supported == 0 || mn % 64 != 0) return false;
+  cuuint64_t dims[3] = {64, k, mn / 64};
+  cuuint64_t strides[2] = {pitch_elems * 2, 128};
+  cuuint32_t box[3] = {64, (cuuint32_t)BK, chunks};
+  cuuint32_t elem[3] = {1, 1, 1};
+  const CUresult rc = encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides,
+                                  box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (supported < 0) supported = rc == CUDA_SUCCESS ? 1 : 0;
+  return rc == CUDA_SUCCESS;
+}
+
 static int* status_word(int device) { return kernel_status_block(device) + kStatusGemm; }
 
 }  // namespace gemm
+
+// VRL_GEMM_MN3D=0 keeps the one-copy-per-chunk form of MN-major operands (a comparison switch).
+static bool gemm_mn3_enabled() {
+  static const bool on = [] {
+    const char* v = std::getenv("VRL_GEMM_MN3D");
+    return v == nullptr || std::string(v) != "0";
+  }();
+  return on;
+}
 
 // All-gather fused into the GEMM: the B operand [N, K] is sharded by rows over `world` ranks.
 // `peer_ptrs` (CPU int64) holds every rank's shard address as mapped into this process, `ready`
@@ -733,11 +761,19 @@ static std::vector<torch::Tensor> gemm_impl(torch::Tensor a, torch::Tensor b,
 
   // grouped mode 1: B's outer extent covers every expert's matrix
   const int64_t b_outer = (grp != nullptr && grp->mode == 1) ? experts : 1;
-  CUtensorMap map_a = a_mn_major ? make_map(a.data_ptr(), m, k, a.stride(0), 64, BK)
-                                 : make_map(a.data_ptr(), k, m, a.stride(0), BK, BM);
-  CUtensorMap map_b = b_mn_major ? make_map(b.data_ptr(), n, k * b_outer, b.stride(0), 64, BK)
-                                 : make_map(b.data_ptr(), k, n * b_outer, b.stride(0), BK, BN);
+  CUtensorMap map_a, map_b;
+  const bool use_mn3 = gemm_mn3_enabled();
+  const bool a_mn3 = a_mn_major && use_mn3 && make_map_mn3(&map_a, a.data_ptr(), m, k, a.stride(0), BM / 64);
+  const bool b_mn3 = b_mn_major && use_mn3 && make_map_mn3(&map_b, b.data_ptr(), n, k * b_outer, b.stride(0), BN / 64);
+  if (!a_mn3)
+    map_a = a_mn_major ? make_map(a.data_ptr(), m, k, a.stride(0), 64, BK)
+                       : make_map(a.data_ptr(), k, m, a.stride(0), BK, BM);
+  if (!b_mn3)
+    map_b = b_mn_major ? make_map(b.data_ptr(), n, k * b_outer, b.stride(0), 64, BK)
+                       : make_map(b.data_ptr(), k, n * b_outer, b.stride(0), BK, BN);
   Params p{};
+  p.a_mn3 = a_mn3 ? 1 : 0;
+  p.b_mn3 = b_mn3 ? 1 : 0;
   p.c = out.data_ptr();
   torch::Tensor bias_c, gate_c, res_c;
   if (bias.has_value()) {

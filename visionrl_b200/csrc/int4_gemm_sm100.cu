@@ -31,7 +31,7 @@ using namespace ptx;
 
 constexpr int kRows = 128;                 // output features per CTA
 constexpr int kBK = 64;                    // k per stage
-constexpr int kStages = 4;
+constexpr int kStages = 3;                 // 3 x 28 KiB: two CTAs fit on one SM
 constexpr int kThreads = 320;
 constexpr uint32_t kRawBytes = kRows * 32;         // packed codes of one k-block
 constexpr uint32_t kABytes = kRows * 128;          // dequantised bf16 A tile
@@ -52,7 +52,7 @@ struct Params {
   int ksplit;
 };
 
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, 2)
 int4_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                  const Params p) {
   extern __shared__ uint8_t smem_raw[];
@@ -294,7 +294,9 @@ torch::Tensor int4_gemm(torch::Tensor x, torch::Tensor qweight, torch::Tensor sc
   const int n_tiles = (int)((n + kRows - 1) / kRows);
   const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
   const int k_blocks = (int)(k / kBK);
-  const int want = std::max(1, std::min((sms + n_tiles - 1) / n_tiles, std::max(1, k_blocks / 4)));
+  // Split K so that the whole grid is resident at once (two CTAs per SM): a second, partly filled
+  // wave would double the time of a kernel whose CTAs all take the same few microseconds.
+  const int want = std::max(1, std::min((2 * sms) / n_tiles, std::max(1, k_blocks / 4)));
   const int per_split = (k_blocks + want - 1) / want;
   p.ksplit = (k_blocks + per_split - 1) / per_split;       // no empty split: every slice is written
   auto acc = torch::empty({(int64_t)p.ksplit, m, n}, x.options().dtype(torch::kFloat32));

@@ -310,23 +310,14 @@ adaln_fwd_cols_kernel(const bf16* __restrict__ x, const bf16* __restrict__ shift
   }
   const int r_begin = blockIdx.x * rows_per_block;
   const int r_end = min(r_begin + rows_per_block, rows_per_sample);
-  // the rows of the next pass are requested before the current pass starts its reductions, so a
-  // pass costs its arithmetic and barriers, not a memory round trip
-  auto fetch = [&](int rb, bf16x8 (&dst)[RB]) {
-#pragma unroll
-    for (int q = 0; q < RB; ++q) {
-      dst[q].u = make_uint4(0u, 0u, 0u, 0u);
-      if (act && rb + q < r_end)
-        dst[q] = reinterpret_cast<const bf16x8*>(x + ((int64_t)sample * rows_per_sample + rb + q) * d)[i];
-    }
-  };
-  bf16x8 ahead[RB];
-  fetch(r_begin, ahead);
   for (int rb = r_begin; rb < r_end; rb += RB) {
     bf16x8 raw[RB];
 #pragma unroll
-    for (int q = 0; q < RB; ++q) raw[q] = ahead[q];
-    fetch(rb + RB, ahead);
+    for (int q = 0; q < RB; ++q) {
+      raw[q].u = make_uint4(0u, 0u, 0u, 0u);
+      if (act && rb + q < r_end)
+        raw[q] = reinterpret_cast<const bf16x8*>(x + ((int64_t)sample * rows_per_sample + rb + q) * d)[i];
+    }
     float mu[RB], var[RB];
 #pragma unroll
     for (int q = 0; q < RB; ++q) {
@@ -393,31 +384,22 @@ adaln_bwd_cols_kernel(const bf16* __restrict__ gy, const bf16* __restrict__ x,
   const int r_begin = blockIdx.x * rows_per_block;
   const int r_end = min(r_begin + rows_per_block, rows_per_sample);
   int parity = 0;
-  // operands of the next pass are requested before the current pass is reduced (see the forward)
-  auto fetch = [&](int rb, bf16x8 (&dx)[RB], bf16x8 (&dg)[RB], float (&dmu)[RB], float (&drs)[RB]) {
-#pragma unroll
-    for (int q = 0; q < RB; ++q) {
-      const bool ok = rb + q < r_end;
-      const int64_t row = (int64_t)sample * rows_per_sample + min(rb + q, r_end - 1);
-      dmu[q] = mean[row];
-      drs[q] = rstd[row];
-      dx[q].u = make_uint4(0u, 0u, 0u, 0u);
-      dg[q].u = make_uint4(0u, 0u, 0u, 0u);
-      if (act && ok) {
-        dx[q] = reinterpret_cast<const bf16x8*>(x + row * d)[i];
-        dg[q] = reinterpret_cast<const bf16x8*>(gy + row * d)[i];
-      }
-    }
-  };
-  bf16x8 ax[RB], ag[RB];
-  float amu[RB], ars[RB];
-  fetch(r_begin, ax, ag, amu, ars);
   for (int rb = r_begin; rb < r_end; rb += RB, parity ^= 1) {
     bf16x8 xr[RB], gr[RB];
     float mu[RB], rs[RB];
 #pragma unroll
-    for (int q = 0; q < RB; ++q) { xr[q] = ax[q]; gr[q] = ag[q]; mu[q] = amu[q]; rs[q] = ars[q]; }
-    fetch(rb + RB, ax, ag, amu, ars);
+    for (int q = 0; q < RB; ++q) {
+      const bool ok = rb + q < r_end;
+      const int64_t row = (int64_t)sample * rows_per_sample + (ok ? rb + q : r_end - 1);
+      mu[q] = mean[row];
+      rs[q] = rstd[row];
+      xr[q].u = make_uint4(0u, 0u, 0u, 0u);
+      gr[q].u = make_uint4(0u, 0u, 0u, 0u);
+      if (act && ok) {
+        xr[q] = reinterpret_cast<const bf16x8*>(x + row * d)[i];
+        gr[q] = reinterpret_cast<const bf16x8*>(gy + row * d)[i];
+      }
+    }
     float part[2 * RB];
 #pragma unroll
     for (int q = 0; q < RB; ++q) {
@@ -1087,22 +1069,14 @@ qkv_prepare_fwd_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ qw
   const int64_t tok_begin = (int64_t)blockIdx.x * tokens_per_block;
   const int64_t tok_end = min(tok_begin + (int64_t)tokens_per_block, tokens);
   int parity = 0;
-  // the tokens of the next pass are requested before the current pass is reduced and stored
-  auto fetch = [&](int64_t tb, bf16x8 (&dst)[TB]) {
-#pragma unroll
-    for (int t = 0; t < TB; ++t) {
-      dst[t].u = make_uint4(0u, 0u, 0u, 0u);
-      if (act && tb + t < tok_end)
-        dst[t] = *reinterpret_cast<const bf16x8*>(qkv + ((tb + t) * 3 + which) * dmodel + i * 8);
-    }
-  };
-  bf16x8 ahead[TB];
-  fetch(tok_begin, ahead);
   for (int64_t tb = tok_begin; tb < tok_end; tb += TB) {
     bf16x8 raw[TB];
 #pragma unroll
-    for (int t = 0; t < TB; ++t) raw[t] = ahead[t];
-    fetch(tb + TB, ahead);
+    for (int t = 0; t < TB; ++t) {
+      raw[t].u = make_uint4(0u, 0u, 0u, 0u);
+      if (act && tb + t < tok_end)
+        raw[t] = *reinterpret_cast<const bf16x8*>(qkv + ((tb + t) * 3 + which) * dmodel + i * 8);
+    }
     float ssq[TB];
 #pragma unroll
     for (int t = 0; t < TB; ++t) {
@@ -1354,34 +1328,25 @@ qkv_prepare_bwd_kernel(const bf16* __restrict__ gq, const bf16* __restrict__ gk,
   const int64_t tok_begin = (int64_t)blockIdx.x * tokens_per_block;
   const int64_t tok_end = min(tok_begin + (int64_t)tokens_per_block, tokens);
   int parity = 0;
-  // operands of the next pass are requested before the current pass is reduced and stored
-  auto fetch = [&](int64_t tb, bf16x8 (&dg)[TB], bf16x8 (&dx)[TB], float (&drs)[TB]) {
-#pragma unroll
-    for (int t = 0; t < TB; ++t) {
-      const int64_t tok = tb + t;
-      dg[t].u = make_uint4(0u, 0u, 0u, 0u);
-      dx[t].u = make_uint4(0u, 0u, 0u, 0u);
-      drs[t] = 0.f;
-      if (act && tok < tok_end) {
-        int b = (int)((unsigned)tb / (unsigned)seq), sidx = (int)tb - b * seq + t;     // 32-bit on purpose
-        while (sidx >= seq) { sidx -= seq; ++b; }
-        dg[t] = *reinterpret_cast<const bf16x8*>(gsrc + b * sb + h * sh + (int64_t)(seq_offset + sidx) * ss + j8 * 8);
-        if (normed) {
-          dx[t] = *reinterpret_cast<const bf16x8*>(qkv + (tok * 3 + which) * dmodel + i * 8);
-          drs[t] = mode == 1 ? rstd[(tok * 2 + which) * heads + h] : rstd[tok * 2 + which];
-        }
-      }
-    }
-  };
-  bf16x8 ag[TB], ax[TB];
-  float ars[TB];
-  fetch(tok_begin, ag, ax, ars);
   for (int64_t tb = tok_begin; tb < tok_end; tb += TB) {
     bf16x8 graw[TB], xraw[TB];
     float rs[TB];
 #pragma unroll
-    for (int t = 0; t < TB; ++t) { graw[t] = ag[t]; xraw[t] = ax[t]; rs[t] = ars[t]; }
-    fetch(tb + TB, ag, ax, ars);
+    for (int t = 0; t < TB; ++t) {
+      const int64_t tok = tb + t;
+      graw[t].u = make_uint4(0u, 0u, 0u, 0u);
+      xraw[t].u = make_uint4(0u, 0u, 0u, 0u);
+      rs[t] = 0.f;
+      if (act && tok < tok_end) {
+        int b = (int)((unsigned)tb / (unsigned)seq), sidx = (int)tb - b * seq + t;     // 32-bit on purpose
+        while (sidx >= seq) { sidx -= seq; ++b; }
+        graw[t] = *reinterpret_cast<const bf16x8*>(gsrc + b * sb + h * sh + (int64_t)(seq_offset + sidx) * ss + j8 * 8);
+        if (normed) {
+          xraw[t] = *reinterpret_cast<const bf16x8*>(qkv + (tok * 3 + which) * dmodel + i * 8);
+          rs[t] = mode == 1 ? rstd[(tok * 2 + which) * heads + h] : rstd[tok * 2 + which];
+        }
+      }
+    }
     float g[TB][8], dot[TB];
 #pragma unroll
     for (int t = 0; t < TB; ++t) {

@@ -564,14 +564,16 @@ class ShardedParamRuntime:
         of its replica and the sums are compared over the process group.  Ranks whose fused
         broadcast lost or tore a write would roll out with different weights than their peers
         and silently bias the gradient; here that is an error naming the ranks that disagree."""
-        if self.replica_flat is None or self.world == 1 or not self.replica_ready():
+        if self.replica_flat is None or not (dist.is_available() and dist.is_initialized()) \
+                or dist.get_world_size() == 1 or not self.replica_ready():
             return
         if self.device.type == "cuda":
             torch.cuda.current_stream(self.device).synchronize()
         words = self.replica_flat.view(torch.int16).to(torch.int64)
         mine = torch.stack([words.sum(), (words * (torch.arange(words.numel(), device=words.device) % 8191 + 1)).sum()])
-        seen = [torch.empty_like(mine) for _ in range(self.world)]
-        dist.all_gather(seen, mine, group=self.group)
+        # every rank of the job holds the same full replica, whatever shard or replica group it is in
+        seen = [torch.empty_like(mine) for _ in range(dist.get_world_size())]
+        dist.all_gather(seen, mine)
         bad = [r for r, other in enumerate(seen) if not torch.equal(other.cpu(), seen[0].cpu())]
         if bad:
             raise RuntimeError(f"rollout replicas differ across ranks: ranks {bad} disagree with rank 0 "
