@@ -1094,7 +1094,7 @@ def test_fused_decode_step_matches_the_tensor_op_layer_path(monkeypatch):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("rows,k,n,rank", [(32, 2048, 6144, 32), (5, 256, 264, 8), (64, 1024, 2048, 64)])
+@pytest.mark.parametrize("rows,k,n,rank", [(32, 2048, 6144, 32), (5, 256, 264, 8), (64, 1024, 2048, 64), (32, 2048, 2048, 128), (9, 512, 520, 40)])
 def test_lora_apply_rows_matches_fp32_reference(rows, k, n, rank):
     """The decode-sized low-rank update y += s (x A^T) B^T against fp32 tensor math, row and column tails
     included, and the layer-level path it serves (LoRALinear without autograd, a few rows)."""

@@ -8,8 +8,12 @@
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 
+#include <cstdlib>
+#include <string>
+
 #include "common.cuh"
 #include "ops.h"
+#include "sm100_ptx.cuh"
 
 namespace vrl {
 
@@ -316,6 +320,162 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
 }
 
 // ------------------------------------------------------------------------------------------
+// Decode attention, streaming form (caches with contiguous keys: stride(2) == 128).  The keys and
+// values of a (row, head) are one contiguous run each, so they are brought into shared memory by
+// bulk asynchronous copies, 32 keys (8 KB + 8 KB) per stage through a three-stage ring: two stages
+// per block are always in flight without costing a register, four blocks fit on an SM, and the
+// arithmetic reads shared memory.  (The register form above keeps too little in flight: it reached
+// 1.3 TB/s of cache traffic with every warp stalled on its loads.)  Chunks without a valid key are
+// never copied; keys that are masked out are copied with their chunk but never read into the sums.
+// A wait that runs out sets the attention status word and the block writes zeros.
+// ------------------------------------------------------------------------------------------
+constexpr int kDaChunk = 32;
+constexpr int kDaStages = 3;
+constexpr int kDaThreads = 128;
+constexpr uint32_t kDaStageBytes = 2 * kDaChunk * 256;          // K then V
+enum : int { kDecodeAttnTimeout = 31 };
+
+__global__ void __launch_bounds__(kDaThreads)
+decode_attention_bulk_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kc,
+                             const __nv_bfloat16* __restrict__ vc, const bool* __restrict__ valid,
+                             __nv_bfloat16* __restrict__ out, int heads, int length, int64_t k_sr, int64_t k_sh,
+                             int64_t v_sr, int64_t v_sh, int64_t valid_sr, float scale, int* status) {
+  using namespace ptx;
+  extern __shared__ uint8_t da_raw[];
+  uint8_t* stages = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(da_raw) + 127) & ~static_cast<uintptr_t>(127));
+  __shared__ uint64_t full[kDaStages];
+  __shared__ unsigned chunk_mask;
+  __shared__ int abort_flag;
+  __shared__ float sm_m[4], sm_s[4];
+  __shared__ float sm_o[4][128];
+  const int r = blockIdx.x / heads, h = blockIdx.x % heads;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool* vrow = valid + r * valid_sr;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kDaStages; ++s) mbar_init(&full[s], 1);
+    chunk_mask = 0u;
+    abort_flag = 0;
+    mbar_fence_init();
+    fence_async_smem();
+  }
+  __syncthreads();
+  // which 32-key chunks hold at least one valid key (length <= 1024: thread t looks at 8 positions)
+  {
+    bool any = false;
+    const int p0 = threadIdx.x * 8;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) any = any || (p0 + i < length && vrow[p0 + i]);
+    if (any) atomicOr(&chunk_mask, 1u << (p0 / kDaChunk));
+  }
+  __syncthreads();
+  const unsigned mask = chunk_mask;
+  const int count = __popc(mask);
+  const __nv_bfloat16* kbase = kc + r * k_sr + h * k_sh;
+  const __nv_bfloat16* vbase = vc + r * v_sr + h * v_sh;
+  auto issue = [&](int chunk, int s) {
+    const int nkeys = min(kDaChunk, length - chunk * kDaChunk);
+    uint8_t* dst = stages + s * kDaStageBytes;
+    mbar_expect_tx(&full[s], 2u * (uint32_t)nkeys * 256u);
+    bulk_load(dst, kbase + (int64_t)chunk * kDaChunk * 128, (uint32_t)nkeys * 256u, &full[s]);
+    bulk_load(dst + kDaChunk * 256, vbase + (int64_t)chunk * kDaChunk * 128, (uint32_t)nkeys * 256u, &full[s]);
+  };
+  unsigned prod_rem = mask;                    // thread 0: chunks not yet requested
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kDaStages && prod_rem; ++s) {
+      issue(__ffs(prod_rem) - 1, s);
+      prod_rem &= prod_rem - 1;
+    }
+  }
+  const uint2 qraw = *reinterpret_cast<const uint2*>(q + ((int64_t)r * heads + h) * 128 + lane * 4);
+  const float2 q01 = bf16pair_to_float2(qraw.x), q23 = bf16pair_to_float2(qraw.y);
+  float m = -INFINITY, sum = 0.f, o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+  unsigned cons_rem = mask;
+  bool ok_all = true;
+  for (int it = 0; it < count; ++it) {
+    const int s = it % kDaStages;
+    const int chunk = __ffs(cons_rem) - 1;
+    cons_rem &= cons_rem - 1;
+    // this warp's eight keys of the chunk: their mask bytes are requested before the wait
+    const int j0 = chunk * kDaChunk + warp * 8;
+    bool ok[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ok[i] = (j0 + i < length) && vrow[j0 + i];
+    if (!mbar_wait(&full[s], (it / kDaStages) & 1u, &abort_flag)) { ok_all = false; }
+    ok_all = __syncthreads_and(ok_all ? 1 : 0) != 0;
+    if (!ok_all) break;
+    const uint8_t* ks = stages + s * kDaStageBytes + warp * 8 * 256 + lane * 8;
+    const uint8_t* vs = ks + kDaChunk * 256;
+    float dot[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint2 kraw = *reinterpret_cast<const uint2*>(ks + i * 256);
+      const float2 k01 = bf16pair_to_float2(kraw.x), k23 = bf16pair_to_float2(kraw.y);
+      dot[i] = q01.x * k01.x + q01.y * k01.y + q23.x * k23.x + q23.y * k23.y;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) dot[i] += __shfl_xor_sync(0xffffffffu, dot[i], o);
+    }
+    float mn = m;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      dot[i] = ok[i] ? dot[i] * scale : -INFINITY;
+      mn = fmaxf(mn, dot[i]);
+    }
+    if (mn != -INFINITY) {                                      // warp-uniform
+      const float corr = (m == -INFINITY) ? 0.f : __expf(m - mn);
+      o0 *= corr; o1 *= corr; o2 *= corr; o3 *= corr;
+      sum *= corr;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        if (!ok[i]) continue;                                   // a masked slot may hold anything
+        const float p = __expf(dot[i] - mn);
+        const uint2 vraw = *reinterpret_cast<const uint2*>(vs + i * 256);
+        const float2 v01 = bf16pair_to_float2(vraw.x), v23 = bf16pair_to_float2(vraw.y);
+        o0 = fmaf(p, v01.x, o0); o1 = fmaf(p, v01.y, o1);
+        o2 = fmaf(p, v23.x, o2); o3 = fmaf(p, v23.y, o3);
+        sum += p;
+      }
+      m = mn;
+    }
+    __syncthreads();                                            // every warp is done with stage s
+    if (threadIdx.x == 0 && prod_rem) {
+      issue(__ffs(prod_rem) - 1, s);
+      prod_rem &= prod_rem - 1;
+    }
+  }
+  if (!ok_all) {
+    // copies already requested still target this block's shared memory: wait (bounded) for them
+    if (threadIdx.x == 0) {
+      atomicExch(status, kDecodeAttnTimeout);
+      for (int spin = 0; spin < 2000; ++spin) __nanosleep(1000);       // ~2 ms, far longer than any copy
+    }
+    __syncthreads();
+    if (threadIdx.x < 128) out[((int64_t)r * heads + h) * 128 + threadIdx.x] = __float2bfloat16_rn(0.f);
+    return;
+  }
+  if (lane == 0) { sm_m[warp] = m; sm_s[warp] = sum; }
+  __syncthreads();
+  float gm = -INFINITY;
+#pragma unroll
+  for (int w2 = 0; w2 < 4; ++w2) gm = fmaxf(gm, sm_m[w2]);
+  const float mine = (m == -INFINITY) ? 0.f : __expf(m - gm);
+  sm_o[warp][lane * 4 + 0] = o0 * mine; sm_o[warp][lane * 4 + 1] = o1 * mine;
+  sm_o[warp][lane * 4 + 2] = o2 * mine; sm_o[warp][lane * 4 + 3] = o3 * mine;
+  __syncthreads();
+  {
+    float tot = 0.f, acc = 0.f;
+#pragma unroll
+    for (int w2 = 0; w2 < 4; ++w2) {
+      tot += (sm_m[w2] == -INFINITY) ? 0.f : sm_s[w2] * __expf(sm_m[w2] - gm);
+      acc += sm_o[w2][threadIdx.x];
+    }
+    out[((int64_t)r * heads + h) * 128 + threadIdx.x] = __float2bfloat16_rn(tot > 0.f ? acc / tot : 0.f);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
 // Group-normalised advantages: a = clamp((r - mean_g) / max(std_g, eps), +-clip), unbiased std,
 // singleton groups -> 0.  One block; every thread owns samples i, i + blockDim, ...
 // ------------------------------------------------------------------------------------------
@@ -483,6 +643,15 @@ std::vector<torch::Tensor> sample_tokens(torch::Tensor cond, torch::Tensor uncon
   return {tokens, logp};
 }
 
+// VRL_DECODE_ATTENTION=registers keeps the register form for caches the streaming form could serve
+static bool decode_attention_bulk_enabled() {
+  static const bool on = [] {
+    const char* v = std::getenv("VRL_DECODE_ATTENTION");
+    return v == nullptr || std::string(v) != "registers";
+  }();
+  return on;
+}
+
 torch::Tensor decode_attention(torch::Tensor q, torch::Tensor k_cache, torch::Tensor v_cache,
                                torch::Tensor valid, int64_t length, double scale) {
   TORCH_CHECK(q.is_cuda() && q.scalar_type() == torch::kBFloat16 && q.dim() == 4 && q.size(2) == 1 &&
@@ -505,6 +674,29 @@ torch::Tensor decode_attention(torch::Tensor q, torch::Tensor k_cache, torch::Te
   const int64_t rows = q.size(0), heads = q.size(1);
   auto out = torch::empty_like(q);
   if (rows == 0) return out;
+  // contiguous keys, 16-byte aligned runs, at most 1024 positions: the streaming form
+  const bool bulk = k_cache.stride(2) == 128 && v_cache.stride(2) == 128 && length <= 1024 &&
+                    k_cache.stride(0) % 8 == 0 && k_cache.stride(1) % 8 == 0 && v_cache.stride(0) % 8 == 0 &&
+                    v_cache.stride(1) % 8 == 0 && reinterpret_cast<uintptr_t>(k_cache.data_ptr()) % 16 == 0 &&
+                    reinterpret_cast<uintptr_t>(v_cache.data_ptr()) % 16 == 0 && decode_attention_bulk_enabled();
+  if (bulk) {
+    constexpr size_t smem = kDaStages * kDaStageBytes + 128;
+    static const bool attr_set = [] {
+      C10_CUDA_CHECK(cudaFuncSetAttribute(decode_attention_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          (int)smem));
+      return true;
+    }();
+    (void)attr_set;
+    decode_attention_bulk_kernel<<<rows * heads, kDaThreads, smem, at::cuda::getCurrentCUDAStream()>>>(
+        reinterpret_cast<const __nv_bfloat16*>(q.data_ptr()),
+        reinterpret_cast<const __nv_bfloat16*>(k_cache.data_ptr()),
+        reinterpret_cast<const __nv_bfloat16*>(v_cache.data_ptr()), valid.data_ptr<bool>(),
+        reinterpret_cast<__nv_bfloat16*>(out.data_ptr()), (int)heads, (int)length, k_cache.stride(0),
+        k_cache.stride(1), v_cache.stride(0), v_cache.stride(1), valid.stride(0), (float)scale,
+        kernel_status_block(q.get_device()) + kStatusAttention);
+    C10_CUDA_KERNEL_LAUNCH_CHECK();
+    return out;
+  }
   decode_attention_kernel<<<rows * heads, kDecodeWarps * 32, 0, at::cuda::getCurrentCUDAStream()>>>(
       reinterpret_cast<const __nv_bfloat16*>(q.data_ptr()),
       reinterpret_cast<const __nv_bfloat16*>(k_cache.data_ptr()),
@@ -698,39 +890,57 @@ lora_down_rows_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* 
   if (lane == 0) low[(int64_t)row * rank + j] = acc;
 }
 
-template <int kRank>
+constexpr int kLoraRankChunk = 32;
+
 __global__ void __launch_bounds__(256)
 lora_up_add_rows_kernel(__nv_bfloat16* __restrict__ y, const float* __restrict__ low,
-                        const __nv_bfloat16* __restrict__ b, int rows, int n, float scale) {
-  __shared__ __align__(16) float low_s[kLoraRowsPerBlock * kRank];
+                        const __nv_bfloat16* __restrict__ b, int rows, int n, int rank, float scale) {
+  extern __shared__ __align__(16) float low_s[];                 // [kLoraRowsPerBlock][rank]
   const int row0 = blockIdx.y * kLoraRowsPerBlock;
   const int nrows = min(kLoraRowsPerBlock, rows - row0);
-  for (int i = threadIdx.x; i < kLoraRowsPerBlock * kRank; i += blockDim.x)
-    low_s[i] = i < nrows * kRank ? low[(int64_t)row0 * kRank + i] * scale : 0.f;
+  for (int i = threadIdx.x; i < kLoraRowsPerBlock * rank; i += blockDim.x)
+    low_s[i] = i < nrows * rank ? low[(int64_t)row0 * rank + i] * scale : 0.f;
   __syncthreads();
   const int col = blockIdx.x * blockDim.x + threadIdx.x;
   if (col >= n) return;
-  // this column's adapter row stays in registers; the rows' low-rank activations are broadcast
-  // reads of shared memory, four values at a time
-  float bv[kRank];
-  const bf16x8* br = reinterpret_cast<const bf16x8*>(b + (int64_t)col * kRank);
+  float acc[kLoraRowsPerBlock];
 #pragma unroll
-  for (int i = 0; i < kRank / 8; ++i) unpack8(br[i], bv + i * 8);
+  for (int r = 0; r < kLoraRowsPerBlock; ++r) acc[r] = 0.f;
+  const bf16x8* br = reinterpret_cast<const bf16x8*>(b + (int64_t)col * rank);
+  // the adapter row goes through registers 32 values at a time; the rows' low-rank activations are
+  // broadcast reads of shared memory, four values per load
+  for (int c0 = 0; c0 < rank; c0 += kLoraRankChunk) {
+    const int width = min(kLoraRankChunk, rank - c0);            // a multiple of 8
+    float bv[kLoraRankChunk];
 #pragma unroll
-  for (int r = 0; r < kLoraRowsPerBlock; ++r) {
-    if (r >= nrows) break;
-    const float4* lr = reinterpret_cast<const float4*>(low_s + r * kRank);
-    float acc = 0.f;
+    for (int i = 0; i < kLoraRankChunk / 8; ++i) {
+      if (i * 8 < width) {
+        unpack8(br[c0 / 8 + i], bv + i * 8);
+      } else {
 #pragma unroll
-    for (int i = 0; i < kRank / 4; ++i) {
-      const float4 l4 = lr[i];
-      acc = fmaf(l4.x, bv[4 * i], acc);
-      acc = fmaf(l4.y, bv[4 * i + 1], acc);
-      acc = fmaf(l4.z, bv[4 * i + 2], acc);
-      acc = fmaf(l4.w, bv[4 * i + 3], acc);
+        for (int t = 0; t < 8; ++t) bv[i * 8 + t] = 0.f;
+      }
     }
+#pragma unroll
+    for (int r = 0; r < kLoraRowsPerBlock; ++r) {
+      const float4* lr = reinterpret_cast<const float4*>(low_s + r * rank + c0);
+      float a = acc[r];
+#pragma unroll
+      for (int i = 0; i < kLoraRankChunk / 4; ++i) {
+        if (i * 4 < width) {
+          const float4 l4 = lr[i];
+          a = fmaf(l4.x, bv[4 * i], a);
+          a = fmaf(l4.y, bv[4 * i + 1], a);
+          a = fmaf(l4.z, bv[4 * i + 2], a);
+          a = fmaf(l4.w, bv[4 * i + 3], a);
+        }
+      }
+      acc[r] = a;
+    }
+  }
+  for (int r = 0; r < nrows; ++r) {
     __nv_bfloat16* dst = y + (int64_t)(row0 + r) * n + col;
-    *dst = __float2bfloat16_rn(__bfloat162float(*dst) + acc);
+    *dst = __float2bfloat16_rn(__bfloat162float(*dst) + acc[r]);
   }
 }
 
@@ -748,8 +958,8 @@ void lora_apply_rows(torch::Tensor y, torch::Tensor x, torch::Tensor a, torch::T
               b.dim() == 2 && b.is_contiguous() && a.size(1) == x.size(1) && b.size(0) == n && b.size(1) == a.size(0),
               "lora_apply_rows: x [R, K], A [r, K], B [N, r]");
   const int64_t k = x.size(1), rank = a.size(0);
-  TORCH_CHECK(rows <= 64 && k % 8 == 0 && (rank == 8 || rank == 16 || rank == 32 || rank == 64),
-              "lora_apply_rows: R <= 64, K % 8 == 0, adapter rank 8, 16, 32 or 64");
+  TORCH_CHECK(rows <= 64 && k % 8 == 0 && rank % 8 == 0 && rank >= 8 && rank <= 256,
+              "lora_apply_rows: R <= 64, K % 8 == 0, adapter rank a multiple of 8 up to 256");
   if (rows == 0 || n == 0) return;
   const c10::cuda::CUDAGuard guard(y.device());
   auto low = torch::empty({rows, rank}, y.options().dtype(torch::kFloat32));
@@ -758,15 +968,10 @@ void lora_apply_rows(torch::Tensor y, torch::Tensor x, torch::Tensor a, torch::T
   lora_down_rows_kernel<<<dim3((unsigned)rank, row_blocks), kLoraRowsPerBlock * 32, 0, stream>>>(
       reinterpret_cast<const __nv_bfloat16*>(x.data_ptr()), reinterpret_cast<const __nv_bfloat16*>(a.data_ptr()),
       low.data_ptr<float>(), (int)rows, (int)k, (int)rank);
-  const dim3 up_grid((unsigned)((n + 255) / 256), row_blocks);
-  __nv_bfloat16* yp = reinterpret_cast<__nv_bfloat16*>(y.data_ptr());
-  const __nv_bfloat16* bp = reinterpret_cast<const __nv_bfloat16*>(b.data_ptr());
-  switch (rank) {
-    case 8: lora_up_add_rows_kernel<8><<<up_grid, 256, 0, stream>>>(yp, low.data_ptr<float>(), bp, (int)rows, (int)n, (float)scale); break;
-    case 16: lora_up_add_rows_kernel<16><<<up_grid, 256, 0, stream>>>(yp, low.data_ptr<float>(), bp, (int)rows, (int)n, (float)scale); break;
-    case 32: lora_up_add_rows_kernel<32><<<up_grid, 256, 0, stream>>>(yp, low.data_ptr<float>(), bp, (int)rows, (int)n, (float)scale); break;
-    default: lora_up_add_rows_kernel<64><<<up_grid, 256, 0, stream>>>(yp, low.data_ptr<float>(), bp, (int)rows, (int)n, (float)scale); break;
-  }
+  lora_up_add_rows_kernel<<<dim3((unsigned)((n + 255) / 256), row_blocks), 256,
+                            kLoraRowsPerBlock * rank * sizeof(float), stream>>>(
+      reinterpret_cast<__nv_bfloat16*>(y.data_ptr()), low.data_ptr<float>(),
+      reinterpret_cast<const __nv_bfloat16*>(b.data_ptr()), (int)rows, (int)n, (int)rank, (float)scale);
   C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
 

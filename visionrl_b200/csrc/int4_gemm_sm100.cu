@@ -130,14 +130,17 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
       const int n = n0 + row;
       const int groups_per_row = p.k / p.group;
       bool ok = true;
+      // the group scale of the NEXT k-block is requested before this one's barrier wait: a global
+      // load in front of every dequantisation would otherwise sit on the critical path of the stage
+      const __nv_bfloat16* srow = p.scales + (int64_t)min(n, p.n - 1) * groups_per_row;
+      float sc_next = n < p.n ? __bfloat162float(srow[(kb_begin * kBK) / p.group]) : 0.f;
       for (int it = 0; it < my_blocks; ++it) {
         const int s = it % kStages;
+        const float sc = sc_next;
+        if (it + 1 < my_blocks && n < p.n) sc_next = __bfloat162float(srow[((kb_begin + it + 1) * kBK) / p.group]);
         ok = __all_sync(0xffffffffu, mbar_wait(&raw_full[s], (it / kStages) & 1u, abort_flag));
         if (!ok) break;
         uint8_t* stage = smem + s * kStageBytes;
-        const int kb = kb_begin + it;
-        const float sc = n < p.n ? __bfloat162float(p.scales[(int64_t)n * groups_per_row + (kb * kBK) / p.group])
-                                 : 0.f;
         const uint4 words = *reinterpret_cast<const uint4*>(stage + kABytes + kXBytesMax + row * 32 + half * 16);
         const uint32_t w[4] = {words.x, words.y, words.z, words.w};
         const uint32_t a_row = smem_u32(stage) + row * 128;

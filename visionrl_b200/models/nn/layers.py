@@ -129,7 +129,7 @@ class LoRALinear(Linear):
         return (not torch.is_grad_enabled() and x.is_cuda and x.dtype == torch.bfloat16
                 and y.dtype == torch.bfloat16 and y.is_contiguous()
                 and x.numel() // x.shape[-1] <= 64 and a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
-                and a.is_contiguous() and b.is_contiguous() and a.shape[0] in (8, 16, 32, 64)
+                and a.is_contiguous() and b.is_contiguous() and a.shape[0] % 8 == 0 and 8 <= a.shape[0] <= 256
                 and x.shape[-1] % 8 == 0 and _ext.kernels_enabled() and _ext.has("lora_apply_rows"))
 
 
