@@ -41,6 +41,11 @@ def test_tiny_dit_grpo_trains_checkpoints_and_resumes(tmp_path, caplog):
     assert [r[0] for r in rows[1:]] == ["0", "1"]
     assert all(torch.isfinite(torch.tensor(float(v))) for r in rows[1:] for v in r[1:10])
     assert (out / "resolved_config.yaml").exists()
+    # one performance line per epoch, apart from the fixed-column CSV
+    perf = [json.loads(line) for line in (out / "perf.jsonl").read_text().splitlines()]
+    assert [p["epoch"] for p in perf] == [0, 1]
+    assert all(p["step_ms"] > 0 and p["samples"] == 4 and p["samples_per_sec"] > 0 and p["n_ranks"] == 1
+               for p in perf)
     for name in ("checkpoint-1", "checkpoint-final"):
         assert (out / name / "checkpoint.pt").exists() and (out / name / "checkpoint_meta.json").exists()
     meta = json.loads((out / "checkpoint-final" / "checkpoint_meta.json").read_text())
