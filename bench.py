@@ -35,7 +35,7 @@ if ROOT not in sys.path:
 
 METRIC = "GRPO samples/sec (rollout+train, device-timed, max over ranks)"
 
-# The workloads BASELINE.json names.  `--config` picks one; the default is the headline one.
+# The named benchmark workloads.  `--config` picks one; the default is the headline one.
 CONFIGS = {
     "sd3_5": {
         "experiment": "experiment/sd3_5_shape_grpo",
@@ -330,7 +330,7 @@ def main() -> None:
                              "the transformer under torch.compile as the reference's stock path has "
                              "it; reference: the unmodified reference package")
     parser.add_argument("--config", default="sd3_5", choices=sorted(CONFIGS),
-                        help="which BASELINE.json workload to run (default: the headline one)")
+                        help="which named workload to run (default: the headline one)")
     parser.add_argument("--collectives", default="fused", choices=["fused", "nccl"])
     parser.add_argument("--sharding", default="full", choices=["full", "optimizer_only"],
                         help="full: block weights, gradients and optimiser state sharded over the "
