@@ -11,7 +11,6 @@ Two entry points share the weights:
 
 from __future__ import annotations
 
-import math
 from dataclasses import dataclass
 
 import torch

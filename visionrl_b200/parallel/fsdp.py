@@ -50,7 +50,7 @@ BACKWARD_PRE prefetch).
 from __future__ import annotations
 
 import os
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Any, Iterable
 
 import torch
