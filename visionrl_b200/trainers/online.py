@@ -586,7 +586,7 @@ class OnlineTrainer(Trainer):
         words = [int(v) for v in _ext.load().kernel_status_all()]
         self.last_d2h_bytes += 16
         names = ("bf16 GEMM (1 = TMA producer, 2 = MMA issuer, 3 = epilogue)",
-                 "flash attention", "int4 GEMM")
+                 "attention (flash forward / backward; 31 = decode attention's copy ring)", "int4 GEMM")
         bad = [f"{name}: status {word}" for name, word in zip(names, words) if word != 0]
         if bad:
             raise RuntimeError("a kernel gave up waiting on one of its barriers; this step's "
