@@ -490,3 +490,48 @@ def barrier_times_out_when_a_rank_skips(rank, world, port, out):
         out.put(result)
     dist.barrier()                       # both ranks leave together, nothing in flight
     dist.destroy_process_group()
+
+
+def wan_recipe_runs_sharded_and_sequence_parallel(rank, world, port, sp, out_dir, resume_port, out):
+    """The Wan GRPO recipe end to end on CPU ranks, through the public entry point: sequence-parallel
+    attention over ``sp`` ranks, block weights sharded over all ranks, one epoch, metrics on rank 0."""
+    import asyncio
+    import csv
+    import inspect
+    import json
+    import pathlib
+
+    from visionrl_b200.config.loader import load_config
+    from visionrl_b200.scripts.train import run_config
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank))
+    overrides = [
+        "model.arch.num_layers=2", "model.arch.hidden_size=64", "model.arch.num_heads=2", "model.arch.ffn_dim=128",
+        "model.arch.text_dim=32", "model.arch.freq_dim=32", "model.dtype=float32",
+        "sampling.num_frames=5", "sampling.height=32", "sampling.width=32", "sampling.num_steps=3",
+        "sampling.max_sequence_length=8", "rollout.n=2", f"rollout.rollout_batch_size={max(1, world // sp)}",
+        "rollout.sample_batch_size=2", "trainer.total_epochs=1", f"trainer.output_dir={out_dir}",
+        "trainer.save_freq=0", "trainer.debug.first_step=true", "reward.kwargs.vit_scalar.preset=vit_tiny",
+        f"distributed.mesh.sp={sp}", "distributed.collectives=nccl", "distributed.param_sharding=full",
+        "distributed.heartbeat.enable=false", "actor.gradient_checkpointing=true",
+    ]
+    def train(extra):
+        cfg = load_config("experiment/wan_2_1_1_3b_shape_grpo", overrides=overrides + extra)
+        result = run_config(cfg)
+        if inspect.isawaitable(result):
+            asyncio.new_event_loop().run_until_complete(result)
+
+    train([])
+    # the resumed run is a new job: it gets its own rendezvous port (a second process group on the
+    # first one's port, inside the same process, can meet the first store's leftovers)
+    os.environ["MASTER_PORT"] = str(resume_port)
+    # resume from the final checkpoint (written by rank 0 from gathered, full-shape weights and
+    # optimiser state; every rank reads it back and keeps its own rows) for one more epoch
+    train(["trainer.total_epochs=2", f"trainer.resume_from={out_dir}/checkpoint-final"])
+    if rank == 0:
+        rows = list(csv.reader((pathlib.Path(out_dir) / "metrics.csv").open()))
+        perf = [json.loads(line) for line in (pathlib.Path(out_dir) / "perf.jsonl").read_text().splitlines()]
+        out.put({"rows": rows, "perf": perf})
+    if dist.is_initialized():
+        dist.destroy_process_group()

@@ -26,7 +26,7 @@ import torch
 from visionrl_b200.config.loader import build_configs, require
 from visionrl_b200.rollouts.runtime.config import cfg_path
 from visionrl_b200.trainers.checkpointing import (
-    LORA_WEIGHTS_NAME, capture_rng_state, load_training_checkpoint_from_config,
+    LORA_WEIGHTS_NAME, capture_rng_state, join_trainable_state_gathers, load_training_checkpoint_from_config,
     prepare_metrics_csv, prepare_model_config_for_training_resume, restore_rng_state,
     restore_training_checkpoint, sample_prompt_indices, save_resolved_config,
     save_training_checkpoint,
@@ -288,7 +288,9 @@ async def run_online_recipe(ctx: RunContext, parts: RecipeParts, reward_fn: Any,
                 rng_state=capture_rng_state(prompt_generator=rng), export_modules=export)
             logger.info("Saved checkpoint to %s", target)
         else:
+            # the same gathers, in the writer's order: trainer / optimiser state, then the model
             state_holder.state_dict()
+            join_trainable_state_gathers(bundle)
         mesh.barrier()
 
     metrics = None

@@ -17,7 +17,7 @@ import torch
 from visionrl_b200.config.loader import build_configs, optional_none, require
 from visionrl_b200.rollouts.runtime.config import cfg_path
 from visionrl_b200.trainers.checkpointing import (
-    capture_rng_state, load_training_checkpoint_from_config, prepare_metrics_csv,
+    capture_rng_state, join_trainable_state_gathers, load_training_checkpoint_from_config, prepare_metrics_csv,
     prepare_model_config_for_training_resume, restore_rng_state, restore_training_checkpoint,
     save_resolved_config, save_training_checkpoint,
 )
@@ -164,7 +164,9 @@ def train_wan_2_1_dpo(cfg: Any) -> Any:
                 progress={"completed_step": step, "next_step": step, "global_step": trainer.global_step},
                 rng_state=capture_rng_state(loader_generator=loader_gen))
         else:
+            # the same gathers as the writer, in its order (sharded optimiser state, then sharded weights)
             trainer.state_dict()
+            join_trainable_state_gathers(bundle)
         mesh.barrier()
 
     metrics = None

@@ -117,6 +117,17 @@ def export_trainable_state(bundle: Any) -> dict[str, dict[str, Any]]:
     return out
 
 
+def join_trainable_state_gathers(bundle: Any) -> None:
+    """What a rank that does NOT write the checkpoint has to do while the writer exports the model:
+    row-sharded weights are saved at their full shape, and gathering them is a collective (or needs
+    the peers' shards to stay put), so every rank walks the same state dicts in the same order and
+    throws the result away.  Modules without sharded layers are skipped."""
+    for module in _modules(bundle).values():
+        layers = getattr(module, "modules", None)
+        if callable(layers) and any(getattr(m, "sharded", None) is not None for m in layers()):
+            module.state_dict()
+
+
 def load_trainable_state(bundle: Any, state: dict[str, Any], *, strict: bool = True) -> None:
     modules = _modules(bundle)
     missing, extra = sorted(set(modules) - set(state)), sorted(set(state) - set(modules))
@@ -322,7 +333,7 @@ def sample_prompt_indices(rng: torch.Generator, *, num_examples: int,
 __all__ = [
     "CHECKPOINT_META_NAME", "CHECKPOINT_SCHEMA_VERSION", "LORA_WEIGHTS_NAME",
     "TRAINING_CHECKPOINT_NAME", "TrainingCheckpoint", "capture_rng_state",
-    "export_trainable_state", "infer_next_epoch", "load_trainable_state",
+    "export_trainable_state", "join_trainable_state_gathers", "infer_next_epoch", "load_trainable_state",
     "load_training_checkpoint", "load_training_checkpoint_from_config", "prepare_metrics_csv",
     "prepare_model_config_for_training_resume", "read_checkpoint_meta", "restore_rng_state",
     "restore_training_checkpoint", "sample_prompt_indices", "save_resolved_config",
