@@ -535,3 +535,37 @@ def wan_recipe_runs_sharded_and_sequence_parallel(rank, world, port, sp, out_dir
         out.put({"rows": rows, "perf": perf})
     if dist.is_initialized():
         dist.destroy_process_group()
+
+
+def recipe_runs_on_cpu_ranks(rank, world, port, experiment, overrides, out_dir, resume_port, out):
+    """Any online recipe through the public entry point on ``world`` gloo ranks: one epoch, the final
+    checkpoint, a resumed second epoch; rank 0 reports the CSV rows and the performance lines."""
+    import asyncio
+    import csv
+    import inspect
+    import json
+    import pathlib
+
+    from visionrl_b200.config.loader import load_config
+    from visionrl_b200.scripts.train import run_config
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank))
+    base = list(overrides) + [f"trainer.output_dir={out_dir}", "trainer.total_epochs=1", "trainer.save_freq=0",
+                              "distributed.backend=native", "distributed.collectives=nccl",
+                              "distributed.heartbeat.enable=false"]
+
+    def train(extra):
+        result = run_config(load_config(experiment, overrides=base + extra))
+        if inspect.isawaitable(result):
+            asyncio.new_event_loop().run_until_complete(result)
+
+    train([])
+    os.environ["MASTER_PORT"] = str(resume_port)          # the resumed run is a new job with its own rendezvous
+    train(["trainer.total_epochs=2", f"trainer.resume_from={out_dir}/checkpoint-final"])
+    if rank == 0:
+        rows = list(csv.reader((pathlib.Path(out_dir) / "metrics.csv").open()))
+        perf = [json.loads(line) for line in (pathlib.Path(out_dir) / "perf.jsonl").read_text().splitlines()]
+        out.put({"rows": rows, "perf": perf})
+    if dist.is_initialized():
+        dist.destroy_process_group()

@@ -79,6 +79,33 @@ def test_wan_recipe_on_two_cpu_ranks_sharded_with_and_without_sequence_paralleli
     assert perf[0]["samples"] == 2 * max(1, 2 // sp)                 # group of 2 per prompt, one prompt per DP rank
 
 
+TINY_JANUS = [
+    "model.arch.num_layers=2", "model.arch.hidden_size=64", "model.arch.num_heads=2", "model.arch.ffn_dim=128",
+    "model.arch.vocab_size=128", "model.arch.image_vocab_size=96", "model.arch.codebook_dim=8",
+    "+model.arch.vq_base=16", "+model.arch.vq_mults=[1,2]", "+model.arch.vq_blocks=1", "model.dtype=float32",
+    "model.lora.rank=4", "model.lora.alpha=8", "model.int4_decode=false", "sampling.image_token_num=9",
+    "sampling.image_size=32", "rollout.n_samples_per_prompt=4", "rollout.rollout_batch_size=2",
+    "rollout.max_text_length=8", "reward.kwargs.vit_scalar.preset=vit_tiny", "actor.bf16=false",
+]
+
+
+@pytest.mark.timeout(600)
+@pytest.mark.parametrize("experiment,overrides,samples", [
+    ("experiment/tiny_dit_grpo", ["sampling.num_steps=3", "rollout.n=2", "rollout.rollout_batch_size=2",
+                                  "rollout.sample_batch_size=2", "distributed.param_sharding=full"], 4),
+    ("experiment/janus_pro_1b_shape_grpo", TINY_JANUS, 8),
+])
+def test_recipes_train_checkpoint_and_resume_on_two_data_parallel_cpu_ranks(tmp_path, experiment, overrides, samples):
+    import math
+
+    res = _run(_workers.recipe_runs_on_cpu_ranks, 2, experiment, overrides, str(tmp_path / "run"), _free_port(),
+               timeout=500)
+    rows, perf = res["rows"], res["perf"]
+    assert [r[0] for r in rows[1:]] == ["0", "1"]
+    assert all(math.isfinite(float(v)) for r in rows[1:] for v in r[1:6])
+    assert [p["n_ranks"] for p in perf] == [2, 2] and perf[0]["samples"] == samples
+
+
 @pytest.mark.gpu
 @pytest.mark.multigpu
 @pytest.mark.parametrize("collectives", ["nccl", "fused"])
