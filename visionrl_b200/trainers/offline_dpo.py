@@ -24,6 +24,7 @@ import torch
 from torch import nn
 
 from visionrl_b200.algorithms.dpo import diffusion_dpo_loss, diffusion_sft_loss
+from visionrl_b200.trainers.base import raise_on_kernel_timeout
 
 logger = logging.getLogger(__name__)
 
@@ -221,6 +222,7 @@ class OfflineDPOTrainer:
                 self._optimizer.step()
             self._optimizer.zero_grad()
         self.global_step += 1
+        raise_on_kernel_timeout(self.device, self.grad_sync, f"DPO step {self.global_step}")
         vals = torch.stack([stats[k].detach().float() for k in
                             ("loss", "raw_model_loss", "raw_ref_loss", "model_diff", "ref_diff",
                              "implicit_acc")] + [sft.detach().float(),

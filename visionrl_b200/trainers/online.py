@@ -35,7 +35,7 @@ from torch import nn
 from visionrl_b200.algorithms.base import Algorithm
 from visionrl_b200.algorithms.types import TrainStepMetrics
 from visionrl_b200.rollouts.batch import RolloutBatch
-from visionrl_b200.trainers.base import Trainer
+from visionrl_b200.trainers.base import Trainer, raise_on_kernel_timeout
 from visionrl_b200.trainers.ema import EMAModuleWrapper
 from visionrl_b200.trainers.types import TrainerConfig, TrainState
 from visionrl_b200.trainers.weight_sync import WeightSyncer
@@ -576,25 +576,8 @@ class OnlineTrainer(Trainer):
 
     def _check_kernel_status(self) -> None:
         """Bounded device-side waits report here instead of hanging; raise if one gave up."""
-        if self.device.type != "cuda":
-            return
-        from visionrl_b200.ops import _ext
-
-        if not (_ext.kernels_enabled() and _ext.available()):
-            return
-        # one 16-byte read covers the GEMM, the attention kernels and the int4 GEMM
-        words = [int(v) for v in _ext.load().kernel_status_all()]
-        self.last_d2h_bytes += 16
-        names = ("bf16 GEMM (1 = TMA producer, 2 = MMA issuer, 3 = epilogue)",
-                 "attention (flash forward / backward; 31 = decode attention's copy ring)", "int4 GEMM")
-        bad = [f"{name}: status {word}" for name, word in zip(names, words) if word != 0]
-        if bad:
-            raise RuntimeError("a kernel gave up waiting on one of its barriers; this step's "
-                               "results are invalid (" + "; ".join(bad) + ")")
-        check = getattr(self.grad_sync, "check", None)
-        if callable(check):
-            check(f"training step {self.state.step}")
-            self.last_d2h_bytes += 16
+        self.last_d2h_bytes += raise_on_kernel_timeout(self.device, self.grad_sync,
+                                                       f"training step {self.state.step}")
 
     # -- state -------------------------------------------------------------------------------------
     def state_dict(self) -> dict:
