@@ -569,3 +569,32 @@ def recipe_runs_on_cpu_ranks(rank, world, port, experiment, overrides, out_dir, 
         out.put({"rows": rows, "perf": perf})
     if dist.is_initialized():
         dist.destroy_process_group()
+
+
+def recipe_restarts_in_place_after_a_rank_raises(rank, world, port, out_dir, second_port, out):
+    """Three epochs of the tiny recipe on gloo ranks under the in-place restart loop.  On the first
+    attempt rank 1's third step raises on the host before it launches anything (two epochs are
+    checkpointed by then); every rank leaves the group, meets again at the second port and resumes
+    from the latest checkpoint.  Rank 0 reports rows, restarts and the attempts it made."""
+    import csv
+    import pathlib
+
+    from visionrl_b200.scripts import elastic
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank), VRL_FAULT_INJECT="rank=1,step=2")
+    attempts = []
+    overrides = ["sampling.num_steps=3", "rollout.n=2", "rollout.rollout_batch_size=2", "rollout.sample_batch_size=2",
+                 f"trainer.output_dir={out_dir}", "trainer.total_epochs=3", "trainer.save_freq=1",
+                 "distributed.backend=native", "distributed.collectives=nccl",
+                 "distributed.heartbeat.interval_s=0.2", "distributed.heartbeat.deadline_s=20",
+                 "distributed.timeout_s=20"]
+    _, restarts = elastic.run_with_restarts("experiment/tiny_dit_grpo", overrides, max_restarts=1,
+                                            ports=[port, second_port], before_attempt=attempts.append)
+    if dist.is_initialized():
+        dist.destroy_process_group()
+    if rank == 0:
+        root = pathlib.Path(out_dir)
+        out.put({"rows": list(csv.reader((root / "metrics.csv").open())), "restarts": restarts,
+                 "attempts": attempts, "checkpoints": sorted(p.name for p in root.glob("checkpoint-*")),
+                 "resume_configs": len(list(root.glob("resume_config_*.yaml")))})

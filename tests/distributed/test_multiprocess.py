@@ -151,3 +151,14 @@ def test_allgather_fused_gemm_matches_library():
     world = min(torch.cuda.device_count(), 4)
     res = _run(_workers.allgather_gemm_matches_library, world)
     assert res["ok"], res["detail"]
+
+
+@pytest.mark.timeout(600)
+def test_recipe_restarts_in_place_from_the_latest_checkpoint_after_a_rank_raises(tmp_path):
+    res = _run(_workers.recipe_restarts_in_place_after_a_rank_raises, 2, str(tmp_path / "run"), _free_port(),
+               timeout=500)
+    assert res["restarts"] == 1 and res["attempts"] == [0, 1]
+    # epochs 0 and 1 ran before the failure, epoch 2 after the restart; nothing ran twice
+    assert [r[0] for r in res["rows"][1:]] == ["0", "1", "2"]
+    assert res["checkpoints"] == ["checkpoint-1", "checkpoint-2", "checkpoint-3", "checkpoint-final"]
+    assert res["resume_configs"] == 1

@@ -33,6 +33,33 @@ class RankFailure(RuntimeError):
         self.reason = reason
 
 
+class InjectedFault(RuntimeError):
+    """Raised on the host by :func:`maybe_inject_fault`; never reaches a device."""
+
+
+def maybe_inject_fault(rank: int, step: int) -> None:
+    """Host-side fault injection for recovery drills and tests: with
+    ``VRL_FAULT_INJECT="rank=<r>,step=<s>[,attempt=<a>]"`` in the environment, rank ``r`` raises
+    :class:`InjectedFault` at the start of its step ``s`` (0-based count of completed steps),
+    before anything is launched.  ``attempt`` (default 0) is compared with ``VRL_RESTART_ATTEMPT``
+    (set by the in-place restart loop) or else the launcher's ``TORCHELASTIC_RESTART_COUNT``, so
+    that the restarted run is left alone."""
+    import os
+
+    plan = os.environ.get("VRL_FAULT_INJECT", "").strip()
+    if not plan:
+        return
+    fields = dict(part.split("=", 1) for part in plan.replace(" ", "").split(",") if "=" in part)
+    try:
+        want_rank, want_step = int(fields["rank"]), int(fields["step"])
+        want_attempt = int(fields.get("attempt", 0))
+    except (KeyError, ValueError) as exc:
+        raise ValueError(f"VRL_FAULT_INJECT={plan!r}: expected rank=<int>,step=<int>[,attempt=<int>]") from exc
+    attempt = int(os.environ.get("VRL_RESTART_ATTEMPT") or os.environ.get("TORCHELASTIC_RESTART_COUNT") or 0)
+    if (rank, step, attempt) == (want_rank, want_step, want_attempt):
+        raise InjectedFault(f"injected failure on rank {rank} at step {step} (attempt {attempt})")
+
+
 def default_store() -> Any:
     """The key-value store of the default process group (``None`` when not initialised)."""
     import torch.distributed as dist
@@ -153,7 +180,17 @@ def build_liveness(mesh: Any, *, interval_s: float = 1.0, deadline_s: float = 15
     if store is None or getattr(mesh, "world_size", 1) <= 1:
         return None
     return RankLiveness(store, mesh.rank, mesh.world_size, interval_s=interval_s,
-                        deadline_s=deadline_s).start()
+                        deadline_s=deadline_s, prefix=f"vrl/liveness/{incarnation()}").start()
 
 
-__all__ = ["RankFailure", "RankLiveness", "build_liveness", "default_store"]
+def incarnation() -> str:
+    """Names this start of the job.  A launcher that restarts its workers keeps one store for all
+    of them, so the failure notice that ended one incarnation must not be read by the next."""
+    import os
+
+    return (f"{os.environ.get('TORCHELASTIC_RESTART_COUNT') or 0}."
+            f"{os.environ.get('VRL_RESTART_ATTEMPT') or 0}")
+
+
+__all__ = ["InjectedFault", "RankFailure", "RankLiveness", "build_liveness", "default_store", "incarnation",
+           "maybe_inject_fault"]

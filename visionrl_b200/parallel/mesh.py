@@ -48,9 +48,58 @@ def init_distributed(backend: str | None = None, timeout_s: float = 1800.0) -> t
         torch.cuda.set_device(local)
         if backend == "nccl":
             kwargs["device_id"] = torch.device("cuda", local)
-    dist.init_process_group(backend=backend, init_method="env://", rank=rank, world_size=world,
-                            timeout=datetime.timedelta(seconds=timeout_s), **kwargs)
+    factory = _STORE_FACTORY[0]
+    relaunches = int(os.environ.get("TORCHELASTIC_RESTART_COUNT") or 0)
+    if factory is None and relaunches > 0 and agent_store_in_use():
+        # workers started again by the launcher share the launcher's store with the workers they
+        # replace, whose connection addresses are still in it
+        def factory(rank: int, world: int) -> Any:
+            return fresh_prefix_store(rank, world, f"vrl/relaunch/{relaunches}")
+    if factory is None:
+        dist.init_process_group(backend=backend, init_method="env://", rank=rank, world_size=world,
+                                timeout=datetime.timedelta(seconds=timeout_s), **kwargs)
+    else:
+        # a job that re-forms its group (an in-place restart) brings its own key-value store, so
+        # that the keys of the group it left cannot be mistaken for the new group's
+        dist.init_process_group(backend=backend, store=factory(rank, world), rank=rank, world_size=world,
+                                timeout=datetime.timedelta(seconds=timeout_s), **kwargs)
     return rank, world, local
+
+
+# optional `(rank, world) -> store` used instead of the env:// rendezvous (see scripts/elastic.py)
+_STORE_FACTORY: list = [None]
+
+
+def agent_store_in_use() -> bool:
+    """True under ``torchrun``: the launcher's agent hosts the store, all ranks are clients."""
+    return os.environ.get("TORCHELASTIC_USE_AGENT_STORE", "").lower() == "true"
+
+
+def fresh_prefix_store(rank: int, world: int, prefix: str, rendezvous_timeout_s: float = 600.0) -> Any:
+    """A key-value store for a group that is formed a second time in the life of a job: the TCP
+    store at ``MASTER_ADDR:MASTER_PORT`` (hosted by rank 0 unless the launcher's agent hosts it)
+    seen through ``prefix``, returned once all ``world`` ranks have signed in.  Forming a group
+    waits for the other ranks' addresses only as long as a collective would, and a rank that
+    survived a failure can be that late by itself; the sign-in waits ``rendezvous_timeout_s``."""
+    import time
+
+    store = dist.TCPStore(
+        os.environ.get("MASTER_ADDR", "127.0.0.1"), int(os.environ["MASTER_PORT"]), world,
+        is_master=(rank == 0 and not agent_store_in_use()),
+        timeout=datetime.timedelta(seconds=rendezvous_timeout_s), wait_for_workers=False)
+    store = dist.PrefixStore(prefix, store)
+    store.add("arrived", 1)
+    deadline = time.monotonic() + rendezvous_timeout_s
+    while int(store.add("arrived", 0)) < world:
+        if time.monotonic() > deadline:
+            raise TimeoutError(f"{prefix}: only {int(store.add('arrived', 0))} of {world} ranks reached "
+                               f"the rendezvous within {rendezvous_timeout_s:.0f} s")
+        time.sleep(0.05)
+    return store
+
+
+def set_rendezvous_store_factory(factory) -> None:
+    _STORE_FACTORY[0] = factory
 
 
 # mesh of the running job: components that are constructed far from the recipe (the rollout

@@ -78,7 +78,8 @@ def setup_run(cfg: Any) -> RunContext:
     resume = load_training_checkpoint_from_config(cfg)
     prepare_model_config_for_training_resume(cfg, resume, strict=tc.resume_strict)
     native = str(cfg_path(cfg, "distributed.backend", "ray")) == "native"
-    rank, world, local = init_distributed() if native else (0, 1, 0)
+    rank, world, local = init_distributed(
+        timeout_s=float(cfg_path(cfg, "distributed.timeout_s", 1800.0) or 1800.0)) if native else (0, 1, 0)
     if torch.cuda.is_available():
         device = torch.device("cuda", local if native else torch.cuda.current_device())
     else:
@@ -294,36 +295,45 @@ async def run_online_recipe(ctx: RunContext, parts: RecipeParts, reward_fn: Any,
         mesh.barrier()
 
     metrics = None
-    for epoch in range(start, end):
-        picked = sample_prompt_indices(rng, num_examples=len(examples),
-                                       rollout_batch_size=tc.rollout_batch_size)
-        reset = getattr(reward_fn, "reset_components", None)
-        if callable(reset):
-            reset()
-        step_clock = _StepClock(ctx.device)
-        metrics = await trainer.step([examples[i] for i in picked])
-        step_ms = step_clock.stop(mesh)
-        if mesh.is_main:
-            _append_perf(out_dir / "perf.jsonl", epoch, step_ms, trainer, mesh)
-        if mesh.is_main and epoch % tc.log_freq == 0:
-            comp = _component_means(reward_fn, reward_names)
-            logger.info("Epoch %d | loss=%.4f kl=%.4f reward=%.4f+/-%.4f grad_norm=%.4f "
-                        "adv_sat=%.3f adv_zero=%.3f | %s", epoch, metrics.loss,
-                        metrics.kl_penalty, metrics.reward_mean, metrics.reward_std,
-                        metrics.grad_norm, metrics.adv_saturation, metrics.adv_zero_rate,
-                        " ".join(f"{n}={comp[n]:.3f}" for n in reward_names))
-            with open(csv_path, "a") as fh:
-                fh.write(row_fn(epoch, metrics)
-                         + "".join(f",{comp[n]:.4f}" for n in reward_names) + "\n")
-        if on_epoch_end is not None:
-            on_epoch_end(epoch, metrics, trainer)
-        if tc.save_freq > 0 and (epoch + 1 - parts.first_epoch) % tc.save_freq == 0:
-            checkpoint(f"checkpoint-{epoch + 1}", epoch + 1)
-    if bool(cfg_path(cfg, "trainer.save_final", True)):
-        checkpoint("checkpoint-final", end)
-        logger.info("Training complete. Final checkpoint: %s", out_dir / "checkpoint-final")
-    else:
-        logger.info("Training complete (trainer.save_final=false: no final checkpoint written)")
+    try:
+        for epoch in range(start, end):
+            picked = sample_prompt_indices(rng, num_examples=len(examples),
+                                           rollout_batch_size=tc.rollout_batch_size)
+            reset = getattr(reward_fn, "reset_components", None)
+            if callable(reset):
+                reset()
+            step_clock = _StepClock(ctx.device)
+            metrics = await trainer.step([examples[i] for i in picked])
+            step_ms = step_clock.stop(mesh)
+            if mesh.is_main:
+                _append_perf(out_dir / "perf.jsonl", epoch, step_ms, trainer, mesh)
+            if mesh.is_main and epoch % tc.log_freq == 0:
+                comp = _component_means(reward_fn, reward_names)
+                logger.info("Epoch %d | loss=%.4f kl=%.4f reward=%.4f+/-%.4f grad_norm=%.4f "
+                            "adv_sat=%.3f adv_zero=%.3f | %s", epoch, metrics.loss,
+                            metrics.kl_penalty, metrics.reward_mean, metrics.reward_std,
+                            metrics.grad_norm, metrics.adv_saturation, metrics.adv_zero_rate,
+                            " ".join(f"{n}={comp[n]:.3f}" for n in reward_names))
+                with open(csv_path, "a") as fh:
+                    fh.write(row_fn(epoch, metrics)
+                             + "".join(f",{comp[n]:.4f}" for n in reward_names) + "\n")
+            if on_epoch_end is not None:
+                on_epoch_end(epoch, metrics, trainer)
+            if tc.save_freq > 0 and (epoch + 1 - parts.first_epoch) % tc.save_freq == 0:
+                checkpoint(f"checkpoint-{epoch + 1}", epoch + 1)
+        if bool(cfg_path(cfg, "trainer.save_final", True)):
+            checkpoint("checkpoint-final", end)
+            logger.info("Training complete. Final checkpoint: %s", out_dir / "checkpoint-final")
+        else:
+            logger.info("Training complete (trainer.save_final=false: no final checkpoint written)")
+    except BaseException:
+        # the step that failed has announced itself to the peers; stop this rank's heartbeats so
+        # that whoever restarts the job (the launcher, or scripts/elastic.py in this process)
+        # finds no thread writing into a store that is about to go away
+        live = getattr(trainer, "liveness", None)
+        if live is not None:
+            live.stop()
+        raise
     shutdown = getattr(collector, "shutdown", None)
     if callable(shutdown):
         await shutdown()

@@ -81,7 +81,8 @@ def train_wan_2_1_dpo(cfg: Any) -> Any:
     resume = load_training_checkpoint_from_config(cfg)
     prepare_model_config_for_training_resume(cfg, resume, strict=tc.resume_strict)
     native = str(cfg_path(cfg, "distributed.backend", "ray")) == "native"
-    rank, world, local = init_distributed() if native else (0, 1, 0)
+    rank, world, local = init_distributed(
+        timeout_s=float(cfg_path(cfg, "distributed.timeout_s", 1800.0) or 1800.0)) if native else (0, 1, 0)
     device = torch.device("cuda", local) if torch.cuda.is_available() else torch.device("cpu")
     mesh = ProcessMesh.build() if native else ProcessMesh()
     precision = str(require(cfg, "actor.mixed_precision"))

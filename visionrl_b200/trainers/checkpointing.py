@@ -14,6 +14,7 @@ assembled state dicts, so a checkpoint written by N ranks loads on any other N.
 from __future__ import annotations
 
 import json
+import os
 import logging
 import re
 from dataclasses import dataclass
@@ -232,7 +233,11 @@ def save_training_checkpoint(checkpoint_dir: str | Path, *, trainer: Any, bundle
         "model": {"trainable_modules": export_trainable_state(bundle)},
         "progress": dict(progress), "rng": rng_state or capture_rng_state(),
     }
-    torch.save(payload, path / TRAINING_CHECKPOINT_NAME)
+    # written under a temporary name and renamed, and the meta file is written last: a checkpoint
+    # directory that has its meta file is complete, whatever interrupted the run
+    partial = path / (TRAINING_CHECKPOINT_NAME + ".partial")
+    torch.save(payload, partial)
+    os.replace(partial, path / TRAINING_CHECKPOINT_NAME)
     for name, module in (export_modules or {}).items():
         if not callable(getattr(module, "save_pretrained", None)):
             raise TypeError(f"export module {name!r} does not expose save_pretrained()")
@@ -263,8 +268,48 @@ def load_training_checkpoint(path: str | Path) -> TrainingCheckpoint:
     return TrainingCheckpoint(file.parent, file, payload, read_checkpoint_meta(file.parent))
 
 
+AUTO_RESUME = "auto"
+
+
+def latest_checkpoint(output_dir: str | Path) -> Path | None:
+    """The complete checkpoint directory below ``output_dir`` that is furthest along, or ``None``.
+
+    Complete means that both the payload and the meta file are there (the meta file is written
+    last).  Directories are ranked by the ``next_epoch`` recorded in their meta file, the newer
+    file winning a tie (``checkpoint-3`` and ``checkpoint-final`` of a three-epoch run)."""
+    root = Path(output_dir).expanduser()
+    if not root.is_dir():
+        return None
+    best: tuple[int, float, Path] | None = None
+    for child in root.iterdir():
+        payload, meta_file = child / TRAINING_CHECKPOINT_NAME, child / CHECKPOINT_META_NAME
+        if not (child.is_dir() and payload.is_file() and meta_file.is_file()):
+            continue
+        try:
+            meta = json.loads(meta_file.read_text())
+            progress = int(meta["next_epoch"])
+        except (OSError, ValueError, KeyError, TypeError):
+            continue
+        key = (progress, payload.stat().st_mtime, child)
+        if best is None or key[:2] > best[:2]:
+            best = key
+    return None if best is None else best[2]
+
+
 def load_training_checkpoint_from_config(cfg: Any) -> TrainingCheckpoint | None:
+    """``trainer.resume_from`` names a checkpoint directory (or file); ``auto`` means the latest
+    complete checkpoint below ``trainer.output_dir`` and a fresh start when there is none — the
+    setting under which a relaunched job (``torchrun --max-restarts``, or the restart loop of
+    ``visionrl_b200.scripts.elastic``) carries on where the failed one stopped."""
     resume = str(cfg_path(cfg, "trainer.resume_from", "") or "").strip()
+    if resume.lower() == AUTO_RESUME:
+        found = latest_checkpoint(str(cfg_path(cfg, "trainer.output_dir", "") or "."))
+        if found is None:
+            logger.info("trainer.resume_from=auto: no complete checkpoint below %s, starting fresh",
+                        cfg_path(cfg, "trainer.output_dir", "."))
+            return None
+        logger.info("trainer.resume_from=auto: resuming from %s", found)
+        return load_training_checkpoint(found)
     return load_training_checkpoint(resume) if resume else None
 
 
@@ -333,7 +378,8 @@ def sample_prompt_indices(rng: torch.Generator, *, num_examples: int,
 __all__ = [
     "CHECKPOINT_META_NAME", "CHECKPOINT_SCHEMA_VERSION", "LORA_WEIGHTS_NAME",
     "TRAINING_CHECKPOINT_NAME", "TrainingCheckpoint", "capture_rng_state",
-    "export_trainable_state", "join_trainable_state_gathers", "infer_next_epoch", "load_trainable_state",
+    "AUTO_RESUME", "export_trainable_state", "join_trainable_state_gathers", "infer_next_epoch",
+    "latest_checkpoint", "load_trainable_state",
     "load_training_checkpoint", "load_training_checkpoint_from_config", "prepare_metrics_csv",
     "prepare_model_config_for_training_resume", "read_checkpoint_meta", "restore_rng_state",
     "restore_training_checkpoint", "sample_prompt_indices", "save_resolved_config",

@@ -430,6 +430,10 @@ class OnlineTrainer(Trainer):
             live.check()
             live.beat(self.state.step)
         try:
+            if os.environ.get("VRL_FAULT_INJECT"):
+                from visionrl_b200.parallel.liveness import maybe_inject_fault
+
+                maybe_inject_fault(live.rank if live is not None else 0, self.state.step)
             return await self._step(prompts)
         except BaseException as exc:
             if live is not None:
