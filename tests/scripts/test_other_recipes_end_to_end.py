@@ -103,3 +103,50 @@ def test_wan_diffusion_dpo_recipe_trains_on_cpu(tmp_path):
     assert float(first[header.index("model_diff")]) == pytest.approx(float(first[header.index("ref_diff")]), abs=1e-6)
     assert float(first[header.index("grad_norm")]) > 0
     assert (out / "checkpoint-final" / "checkpoint.pt").exists()
+
+
+COSMOS_TINY = TINY_VIDEO_ARCH + TINY_VIT_REWARD + [
+    "model.random_init=true", "+model.dtype=float32", "model.lora.rank=4", "model.lora.alpha=8",
+    "sampling.num_steps=3", "rollout.n=2", "rollout.rollout_batch_size=1", "rollout.sample_batch_size=2",
+    "trainer.total_epochs=1", "trainer.save_freq=0", "reward.components.aesthetic=0.0",
+    "reward.kwargs.vit_scalar.num_frames=2"]
+
+
+@pytest.mark.timeout(600)
+def test_cosmos_sanity_gates_adapter_export_and_eval_only_comparison(tmp_path):
+    out = tmp_path / "cosmos"
+    # epoch 0 replays its own rollout: ratio 1, nothing clipped, so the default gates let it pass
+    _train(load_config("experiment/cosmos_predict2_2b_grpo", overrides=COSMOS_TINY + [
+        f"trainer.output_dir={out}", "eval.sanity_gates.enable=true"]))
+    export = out / "checkpoint-final" / "lora_weights"
+    assert (export / "adapter_model.safetensors").exists()
+    config = json.loads((export / "adapter_config.json").read_text())
+    assert config["peft_type"] == "LORA" and config["r"] == 4 and config["lora_alpha"] == 8.0
+    assert any(name.endswith("self_attn.qkv") for name in config["target_modules"])
+
+    # a gate that cannot be met stops the run after epoch 0 and says which metric tripped it
+    with pytest.raises(RuntimeError, match="epoch-0 sanity gate: approx_kl"):
+        _train(load_config("experiment/cosmos_predict2_2b_grpo", overrides=COSMOS_TINY + [
+            f"trainer.output_dir={tmp_path / 'gated'}", "eval.sanity_gates.enable=true",
+            "eval.sanity_gates.approx_kl_threshold=-1.0"]))
+
+    # eval-only needs an adapter to evaluate
+    prompts = tmp_path / "eval_prompts.txt"
+    prompts.write_text("a fox\na boat\n")
+    eval_overrides = COSMOS_TINY + [f"trainer.output_dir={out}", "eval.eval_only=true",
+                                    f"eval.prompts_file={prompts}", "eval.seeds=2"]
+    with pytest.raises(ValueError, match="model.lora.path"):
+        _train(load_config("experiment/cosmos_predict2_2b_grpo", overrides=eval_overrides))
+
+    _train(load_config("experiment/cosmos_predict2_2b_grpo",
+                       overrides=eval_overrides + [f"model.lora.path={export}"]))
+    rows = list(csv.DictReader((out / "eval_only" / "eval_results.csv").open()))
+    assert [(r["prompt"], r["seed"]) for r in rows] == [("a fox", "0"), ("a fox", "1"), ("a boat", "0"), ("a boat", "1")]
+    assert all(abs(float(r["lora_score"]) - float(r["base_score"]) - float(r["delta"])) < 2e-4 for r in rows)
+    frames = sorted(p.name for p in (out / "eval_only").glob("*.png"))
+    assert len(frames) == 8 and sum(n.startswith("lora_prompt_") for n in frames) == 4
+    # the base pass really ran without the adapter: the trained adapter moves the reward a little
+    hist = (out / "eval_only" / "eval_results.csv").read_text()
+    assert hist.count("\n") == 5
+    # no metrics row was added: nothing was trained
+    assert len((out / "metrics.csv").read_text().splitlines()) == 2

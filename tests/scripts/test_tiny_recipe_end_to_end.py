@@ -48,6 +48,9 @@ def test_tiny_dit_grpo_trains_checkpoints_and_resumes(tmp_path, caplog):
                for p in perf)
     for name in ("checkpoint-1", "checkpoint-final"):
         assert (out / name / "checkpoint.pt").exists() and (out / name / "checkpoint_meta.json").exists()
+        # the adapters are also exported by themselves, loadable through model.lora.path
+        assert (out / name / "lora_weights" / "adapter_model.safetensors").exists()
+        assert (out / name / "lora_weights" / "adapter_config.json").exists()
     meta = json.loads((out / "checkpoint-final" / "checkpoint_meta.json").read_text())
     assert meta["family"] == "sd3_5" and meta["next_epoch"] == 2 and meta["schema_version"] == 1
     payload = torch.load(out / "checkpoint-final" / "checkpoint.pt", map_location="cpu", weights_only=False)

@@ -156,14 +156,9 @@ class NativeFlowPolicy(DiffusionPolicy):
             self.load_lora_weights(spec.lora_path)
 
     def load_lora_weights(self, path: str) -> None:
-        import os
+        from visionrl_b200.models.nn.layers import load_lora_adapter
 
-        from safetensors.torch import load_file
-
-        state = load_file(os.path.join(path, "adapter_model.safetensors"))
-        missing = self.transformer.load_state_dict(state, strict=False)
-        if missing.unexpected_keys:
-            raise ValueError(f"unexpected LoRA keys: {missing.unexpected_keys[:4]}")
+        load_lora_adapter(self.transformer, path)
 
     def enable_full_finetune(self) -> None:
         self.transformer.requires_grad_(True)

@@ -186,6 +186,26 @@ def adapters_disabled(module: nn.Module):
             m.adapter_enabled = flag
 
 
+@contextlib.contextmanager
+def adapters_zeroed(module: nn.Module):
+    """Inside the block every adapter's ``B`` factor is zero, so the network IS its base model —
+    also for a copy of it that receives these tensors through a weight push — and afterwards the
+    trained values are back.  (``adapters_disabled`` only flips a flag of this module object.)"""
+    layers = list(iter_lora_layers(module))
+    if not layers:
+        raise RuntimeError("adapters_zeroed() called on a model without LoRA adapters")
+    saved = [m.lora_B.detach().clone() for m in layers]
+    with torch.no_grad():
+        for m in layers:
+            m.lora_B.zero_()
+    try:
+        yield
+    finally:
+        with torch.no_grad():
+            for m, b in zip(layers, saved):
+                m.lora_B.copy_(b)
+
+
 def apply_lora(module: nn.Module, rank: int, alpha: float, target_modules, init="gaussian",
                freeze_base: bool = True) -> list[str]:
     """Attach adapters to every :class:`LoRALinear` whose qualified name ends with a target
@@ -208,8 +228,77 @@ def apply_lora(module: nn.Module, rank: int, alpha: float, target_modules, init=
     return hit
 
 
+ADAPTER_WEIGHTS_NAME = "adapter_model.safetensors"
+ADAPTER_CONFIG_NAME = "adapter_config.json"
+
+
+def lora_state_dict(module: nn.Module) -> dict[str, torch.Tensor]:
+    """``<layer>.lora_A`` / ``<layer>.lora_B`` of every adapter under ``module``, on the CPU, under
+    the names ``module.load_state_dict`` knows them by.  Adapters are never sharded, so reading them
+    is local to the rank."""
+    out: dict[str, torch.Tensor] = {}
+    for name, m in module.named_modules():
+        if isinstance(m, LoRALinear) and m.has_adapter:
+            prefix = f"{name}." if name else ""
+            out[prefix + "lora_A"] = m.lora_A.detach().to("cpu").contiguous()
+            out[prefix + "lora_B"] = m.lora_B.detach().to("cpu").contiguous()
+    return out
+
+
+def save_lora_adapter(module: nn.Module, directory) -> dict:
+    """Write the adapters of ``module`` as ``adapter_model.safetensors`` + ``adapter_config.json``
+    (the two files of the ``lora_weights/`` export a training checkpoint carries, reference
+    ``vrl/trainers/checkpointing.py``); returns the config that was written."""
+    import json
+    import os
+
+    from safetensors.torch import save_file
+
+    layers = [(n, m) for n, m in module.named_modules() if isinstance(m, LoRALinear) and m.has_adapter]
+    if not layers:
+        raise RuntimeError("save_pretrained() called on a model without LoRA adapters")
+    os.makedirs(directory, exist_ok=True)
+    ranks = sorted({int(m.lora_A.shape[0]) for _, m in layers})
+    config = {"peft_type": "LORA", "r": ranks[0] if len(ranks) == 1 else ranks,
+              "lora_alpha": float(layers[0][1].lora_scale) * int(layers[0][1].lora_A.shape[0]),
+              "target_modules": [n for n, _ in layers], "bias": "none",
+              "base_model_class": type(module).__name__}
+    save_file(lora_state_dict(module), os.path.join(directory, ADAPTER_WEIGHTS_NAME))
+    with open(os.path.join(directory, ADAPTER_CONFIG_NAME), "w") as fh:
+        json.dump(config, fh, indent=2, sort_keys=True)
+        fh.write("\n")
+    return config
+
+
+def load_lora_adapter(module: nn.Module, directory) -> list[str]:
+    """Load an export written by :func:`save_lora_adapter` into the adapters ``module`` already
+    has.  Every tensor of the file must have a place of the same shape and every adapter of the
+    module must be in the file; returns the keys that were loaded."""
+    import os
+
+    from safetensors.torch import load_file
+
+    state = load_file(os.path.join(str(directory), ADAPTER_WEIGHTS_NAME))
+    have = lora_state_dict(module)
+    unexpected = sorted(set(state) - set(have))
+    missing = sorted(set(have) - set(state))
+    if unexpected:
+        raise ValueError(f"unexpected LoRA keys: {unexpected[:4]}")
+    if missing:
+        raise ValueError(f"adapter file lacks LoRA keys: {missing[:4]}")
+    for key, value in state.items():
+        if tuple(value.shape) != tuple(have[key].shape):
+            raise ValueError(f"LoRA tensor {key}: file has {tuple(value.shape)}, model has {tuple(have[key].shape)}")
+    params = dict(module.named_parameters())
+    with torch.no_grad():
+        for key, value in state.items():
+            params[key].copy_(value.to(params[key].device, params[key].dtype))
+    return sorted(state)
+
+
 class AdapterMixin:
-    """Gives a network ``disable_adapter()`` / ``has_adapters`` over its LoRA layers."""
+    """Gives a network ``disable_adapter()`` / ``has_adapters`` over its LoRA layers and the
+    adapter export / import of a checkpoint's ``lora_weights/`` directory."""
 
     def disable_adapter(self):
         return adapters_disabled(self)
@@ -217,6 +306,12 @@ class AdapterMixin:
     @property
     def has_adapters(self) -> bool:
         return any(True for _ in iter_lora_layers(self))
+
+    def save_pretrained(self, directory) -> dict:
+        return save_lora_adapter(self, directory)
+
+    def load_adapter(self, directory) -> list[str]:
+        return load_lora_adapter(self, directory)
 
 
 class RMSNorm(nn.Module):

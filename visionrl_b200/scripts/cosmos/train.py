@@ -38,7 +38,16 @@ def save_eval_frames(videos: torch.Tensor, out_dir: Path, tag: str) -> list[Path
 
 
 async def _eval_only(ctx, parts, reward_fn, cfg) -> dict[str, Any]:
-    """Paired adapter-vs-base comparison on the eval prompts (same seeds for both)."""
+    """Paired adapter-vs-base comparison on the eval prompts, the same seeds for both, no training
+    (reference: ``vrl/scripts/cosmos/train.py:445-557``).  Writes ``eval_only/eval_results.csv``
+    (``prompt, seed, lora_score, base_score, delta``) and the middle frame of every video.
+
+    The rollout workers hold their own copy of the policy, so the base pass does not flip a flag
+    on the trainer's module: it zeroes the adapters' ``B`` factors, pushes that state to the
+    workers, evaluates, then restores and pushes the trained state again."""
+    import csv
+
+    from visionrl_b200.models.nn.layers import adapters_zeroed
     from visionrl_b200.trainers.data import load_prompt_manifest
 
     lora_path = str(cfg_path(cfg, "model.lora.path", "") or "")
@@ -48,21 +57,43 @@ async def _eval_only(ctx, parts, reward_fn, cfg) -> dict[str, Any]:
     prompts = [e.prompt for e in load_prompt_manifest(str(cfg.eval.prompts_file))]
     seeds = int(cfg.eval.seeds)
     policy = parts.bundle.policy
-    results: dict[str, list[float]] = {"adapter": [], "base": []}
-    out_dir = Path(ctx.trainer_config.output_dir) / "eval"
-    for p_idx, prompt in enumerate(prompts):
-        for seed in range(seeds):
-            batch = await collector.collect([prompt], group_size=1, seed=seed)
-            results["adapter"].append(float(batch.rewards.mean()))
-            save_eval_frames(batch.videos, out_dir, f"adapter_p{p_idx}_s{seed}")
-            with policy.disable_adapter():
-                base = await collector.collect([prompt], group_size=1, seed=seed)
-            results["base"].append(float(base.rewards.mean()))
-            save_eval_frames(base.videos, out_dir, f"base_p{p_idx}_s{seed}")
+    out_dir = Path(ctx.trainer_config.output_dir) / "eval_only"
+    out_dir.mkdir(parents=True, exist_ok=True)
+
+    async def sweep(tag: str) -> list[float]:
+        scores = []
+        for p_idx, prompt in enumerate(prompts):
+            for seed in range(seeds):
+                with torch.no_grad():
+                    batch = await collector.collect([prompt], group_size=1, seed=seed)
+                score = float(batch.rewards[0])
+                scores.append(score)
+                if batch.videos is not None:
+                    save_eval_frames(batch.videos[:1], out_dir,
+                                     f"{tag}_prompt_{p_idx}_seed_{seed}_score_{score:.2f}")
+        return scores
+
+    await trainer.push_rollout_weights()
+    lora_scores = await sweep("lora")
+    with adapters_zeroed(policy.transformer):
+        await trainer.push_rollout_weights()
+        base_scores = await sweep("base")
+    await trainer.push_rollout_weights()
+
+    keys = [(p, s) for p in prompts for s in range(seeds)]
+    with open(out_dir / "eval_results.csv", "w", newline="") as fh:
+        writer = csv.DictWriter(fh, fieldnames=["prompt", "seed", "lora_score", "base_score", "delta"])
+        writer.writeheader()
+        for (prompt, seed), lo, ba in zip(keys, lora_scores, base_scores):
+            writer.writerow({"prompt": prompt, "seed": seed, "lora_score": f"{lo:.4f}",
+                             "base_score": f"{ba:.4f}", "delta": f"{lo - ba:.4f}"})
     mean = lambda xs: sum(xs) / max(len(xs), 1)  # noqa: E731
-    logger.info("eval-only: adapter=%.4f base=%.4f over %d samples", mean(results["adapter"]),
-                mean(results["base"]), len(results["adapter"]))
-    return results
+    logger.info("Eval-only results: lora=%.4f base=%.4f delta=%.4f | %s", mean(lora_scores),
+                mean(base_scores), mean(lora_scores) - mean(base_scores), out_dir / "eval_results.csv")
+    shutdown = getattr(collector, "shutdown", None)
+    if callable(shutdown):
+        await shutdown()
+    return {"adapter": lora_scores, "base": base_scores}
 
 
 async def train_cosmos_predict2_grpo(cfg: Any) -> Any:

@@ -218,6 +218,12 @@ class OnlineTrainer(Trainer):
         await self.weight_syncer.push(self._sync_payload())
         self._rollout_weights_initialized = True
 
+    async def push_rollout_weights(self) -> None:
+        """Send the current trainable state to the rollout workers now (a no-op without a syncer)."""
+        if self.weight_syncer is not None:
+            await self.weight_syncer.push(self._sync_payload())
+            self._rollout_weights_initialized = True
+
     # -- optimisation helpers ------------------------------------------------------------
     def _sync_payload(self) -> dict:
         """What a weight push carries: the trainable set when the policy can name it (adapters
