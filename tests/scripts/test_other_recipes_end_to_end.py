@@ -58,6 +58,12 @@ def test_cosmos_video_recipe_trains_on_cpu(tmp_path):
     assert float(rows[0][header.index("grad_norm")]) > 0
     meta = json.loads((out / "checkpoint-final" / "checkpoint_meta.json").read_text())
     assert meta["family"] == "cosmos" and meta["next_epoch"] == 2
+    # every periodic checkpoint carries one middle-frame sample per evaluation prompt (here the
+    # first four training prompts, the held-out file of the config does not exist); the final one none
+    for name in ("checkpoint-1", "checkpoint-2"):
+        frames = sorted(p.name for p in (out / name / "eval_samples").glob("*.png"))
+        assert len(frames) == 4 and all(f.startswith(f"prompt_{i}_score_") for i, f in enumerate(frames))
+    assert not (out / "checkpoint-final" / "eval_samples").exists()
     payload = torch.load(out / "checkpoint-final" / "checkpoint.pt", map_location="cpu", weights_only=False)
     trained = payload["model"]["trainable_modules"]
     assert trained and all(any("lora" in k for k in sd) for sd in trained.values())

@@ -15,6 +15,7 @@ sharded runtime, and only rank 0 writes logs, CSV rows and checkpoints.
 from __future__ import annotations
 
 import contextlib
+import inspect
 import logging
 import os
 from dataclasses import dataclass, field
@@ -239,7 +240,11 @@ def capture_trainer():
 
 async def run_online_recipe(ctx: RunContext, parts: RecipeParts, reward_fn: Any,
                             reward_names: list[str], *,
-                            on_epoch_end: Callable[[int, Any, Any], Any] | None = None) -> Any:
+                            on_epoch_end: Callable[[int, Any, Any], Any] | None = None,
+                            on_checkpoint: Callable[[Path, int, Any, Any], Any] | None = None) -> Any:
+    """The epoch loop every online recipe shares.  ``on_epoch_end(epoch, metrics, trainer)`` runs
+    after each step on every rank; ``on_checkpoint(directory, completed_epochs, trainer, collector)``
+    runs on every rank after each periodic checkpoint (not the final one) and may be a coroutine."""
     from visionrl_b200.trainers.data import load_prompt_manifest
 
     cfg, tc, bundle, mesh = ctx.cfg, ctx.trainer_config, parts.bundle, ctx.mesh
@@ -321,6 +326,10 @@ async def run_online_recipe(ctx: RunContext, parts: RecipeParts, reward_fn: Any,
                 on_epoch_end(epoch, metrics, trainer)
             if tc.save_freq > 0 and (epoch + 1 - parts.first_epoch) % tc.save_freq == 0:
                 checkpoint(f"checkpoint-{epoch + 1}", epoch + 1)
+                if on_checkpoint is not None:
+                    pending = on_checkpoint(out_dir / f"checkpoint-{epoch + 1}", epoch + 1, trainer, collector)
+                    if inspect.isawaitable(pending):
+                        await pending
         if bool(cfg_path(cfg, "trainer.save_final", True)):
             checkpoint("checkpoint-final", end)
             logger.info("Training complete. Final checkpoint: %s", out_dir / "checkpoint-final")

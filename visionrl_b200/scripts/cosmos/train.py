@@ -23,7 +23,8 @@ logger = logging.getLogger(__name__)
 
 
 def save_eval_frames(videos: torch.Tensor, out_dir: Path, tag: str) -> list[Path]:
-    """Middle frame of every ``[3, T, H, W]`` video in ``[0, 1]`` → ``<tag>_<i>.png``."""
+    """Middle frame of every ``[3, T, H, W]`` video in ``[0, 1]`` → ``<tag>.png`` for a single
+    video, ``<tag>_<i>.png`` for several."""
     from PIL import Image
 
     out_dir.mkdir(parents=True, exist_ok=True)
@@ -31,7 +32,7 @@ def save_eval_frames(videos: torch.Tensor, out_dir: Path, tag: str) -> list[Path
     for i, video in enumerate(videos):
         frame = video[:, video.shape[1] // 2] if video.ndim == 4 else video
         arr = (frame.clamp(0, 1) * 255).round().to(torch.uint8).permute(1, 2, 0).cpu().numpy()
-        path = out_dir / f"{tag}_{i:03d}.png"
+        path = out_dir / (f"{tag}.png" if len(videos) == 1 else f"{tag}_{i:03d}.png")
         Image.fromarray(arr).save(path)
         paths.append(path)
     return paths
@@ -132,4 +133,36 @@ async def train_cosmos_predict2_grpo(cfg: Any) -> Any:
                 f"epoch-0 sanity gate: approx_kl={metrics.approx_kl:.4f} exceeds "
                 f"{float(gates.approx_kl_threshold)}")
 
-    return await run_online_recipe(ctx, parts, reward_fn, list(weights), on_epoch_end=on_epoch_end)
+    async def on_checkpoint(directory: Path, completed: int, trainer: Any, collector: Any) -> None:
+        """One sample per evaluation prompt (seed = its index) beside every periodic checkpoint:
+        ``<checkpoint>/eval_samples/prompt_<i>_score_<reward>.png``.  The prompts come from
+        ``eval.prompts_file`` when that file exists, else the first four training prompts
+        (reference: ``vrl/scripts/cosmos/train.py:210-219,369-398``)."""
+        prompts = _eval_prompts(cfg)
+        await trainer.push_rollout_weights()
+        scores = []
+        for i, prompt in enumerate(prompts):
+            with torch.no_grad():
+                batch = await collector.collect([prompt], group_size=1, seed=i)
+            score = float(batch.rewards[0])
+            scores.append(score)
+            if batch.videos is not None and ctx.mesh.is_main:
+                save_eval_frames(batch.videos[:1], directory / "eval_samples", f"prompt_{i}_score_{score:.2f}")
+        if ctx.mesh.is_main:
+            logger.info("Checkpoint %d | eval_reward=%.4f (%s) | saved to %s", completed,
+                        sum(scores) / max(len(scores), 1), ", ".join(f"{s:.2f}" for s in scores), directory)
+
+    dump = bool(cfg_path(cfg, "eval.samples_at_checkpoints", True))
+    return await run_online_recipe(ctx, parts, reward_fn, list(weights), on_epoch_end=on_epoch_end,
+                                   on_checkpoint=on_checkpoint if dump else None)
+
+
+def _eval_prompts(cfg: Any) -> list[str]:
+    from visionrl_b200.trainers.data import load_prompt_manifest
+
+    held_out = str(cfg_path(cfg, "eval.prompts_file", "") or "")
+    if held_out and Path(held_out).exists():
+        prompts = [e.prompt for e in load_prompt_manifest(held_out)]
+        if prompts:
+            return prompts
+    return [e.prompt for e in load_prompt_manifest(str(cfg.data.manifest))[:4]]
