@@ -156,3 +156,74 @@ def test_cosmos_sanity_gates_adapter_export_and_eval_only_comparison(tmp_path):
     assert hist.count("\n") == 5
     # no metrics row was added: nothing was trained
     assert len((out / "metrics.csv").read_text().splitlines()) == 2
+
+
+@pytest.mark.timeout(600)
+def test_sd3_ocr_recipe_with_an_engine_named_in_the_config(tmp_path):
+    """The OCR reward reads generated images through whatever engine ``reward.kwargs.ocr.engine``
+    names (none ships offline).  The rollout runs on the in-process worker of the Ray-style
+    backend, which holds its own build of the policy: the first replay must still reproduce the
+    rollout's log-probabilities exactly, so nothing is clipped and the KL estimate is zero."""
+    from tests.rewards import ocr_engines
+
+    ocr_engines.CALLS.clear()
+    out = tmp_path / "ocr"
+    _train(load_config("experiment/sd3_5_ocr_grpo", overrides=TINY_VIT_REWARD[3:] + [
+        "model.random_init=true", "model.arch.num_layers=2", "model.arch.hidden_size=64", "model.arch.num_heads=2",
+        "model.arch.context_dim=32", "model.arch.pooled_dim=32", "model.arch.in_channels=4", "+model.dtype=float32",
+        "model.lora.rank=4", "model.lora.alpha=8", "sampling.height=32", "sampling.width=32",
+        "sampling.max_sequence_length=8", "sampling.num_steps=3", "actor.bf16=false", "rollout.n=2",
+        "rollout.rollout_batch_size=2", "rollout.sample_batch_size=2", "trainer.total_epochs=1",
+        "trainer.save_freq=0", f"trainer.output_dir={out}",
+        "reward.kwargs.ocr.engine=tests.rewards.ocr_engines:reads_amber"]))
+    header, rows = _rows(out)
+    assert header[-1] == "r_ocr" and len(rows) == 1
+    row = dict(zip(header, rows[0]))
+    assert float(row["clip_fraction"]) == 0.0 and float(row["approx_kl"]) < 1e-9
+    assert 0.0 <= float(row["r_ocr"]) <= 1.0 and float(row["reward_mean"]) == pytest.approx(float(row["r_ocr"]), abs=1e-4)
+    # one frame per generated image went through the engine: 2 prompts x 2 samples, 32 x 32 RGB
+    assert len(ocr_engines.CALLS) == 4 and set(ocr_engines.CALLS) == {(32, 32, 3)}
+
+
+@pytest.mark.timeout(600)
+def test_wan_multi_reward_recipe_mixes_its_components(tmp_path):
+    out = tmp_path / "multi"
+    _train(load_config("experiment/wan_2_1_1_3b_multi_reward_grpo", overrides=TINY_VIDEO_ARCH + [
+        "model.random_init=true", "model.dtype=float32", "model.lora.rank=4", "model.lora.alpha=8",
+        "model.arch.in_channels=4", "sampling.num_steps=3", "rollout.n=2", "rollout.rollout_batch_size=2",
+        "rollout.sample_batch_size=2", "trainer.total_epochs=1", "trainer.save_freq=0",
+        f"trainer.output_dir={out}", "reward.kwargs.aesthetic.model_name=random:vit_tiny",
+        "reward.kwargs.clipscore.model_name=random:vit_tiny", "data.manifest=synthetic:8:0",
+        "distributed.rollout.gpus_per_worker=0"]))
+    header, rows = _rows(out)
+    # the zero-weight OCR slot of the config is dropped; the other two are logged one column each
+    assert header[-2:] == ["r_aesthetic", "r_clipscore"]
+    row = dict(zip(header, rows[0]))
+    mixed = 0.5 * float(row["r_aesthetic"]) + 0.5 * float(row["r_clipscore"])
+    assert float(row["reward_mean"]) == pytest.approx(mixed, abs=2e-4)
+    assert float(row["clip_fraction"]) == 0.0 and float(row["grad_norm"]) > 0
+
+
+@pytest.mark.timeout(600)
+def test_janus_ocr_recipe_runs_through_its_own_entry_point(tmp_path):
+    from tests.rewards import ocr_engines
+
+    ocr_engines.CALLS.clear()
+    out = tmp_path / "janus_ocr"
+    cfg = load_config("experiment/janus_pro_1b_ocr_grpo", overrides=[
+        "model.random_init=true", "model.arch.num_layers=2", "model.arch.hidden_size=64", "model.arch.num_heads=2",
+        "model.arch.ffn_dim=128", "model.arch.vocab_size=128", "model.arch.image_vocab_size=96",
+        "model.arch.codebook_dim=8", "+model.arch.vq_base=16", "+model.arch.vq_mults=[1,2]",
+        "+model.arch.vq_blocks=1", "model.dtype=float32", "model.lora.rank=4", "model.lora.alpha=8",
+        "model.int4_decode=false", "sampling.image_token_num=9", "sampling.image_size=32",
+        "rollout.n_samples_per_prompt=2", "rollout.rollout_batch_size=2", "rollout.max_text_length=8",
+        "actor.bf16=false", "trainer.total_epochs=1", "trainer.save_freq=0", f"trainer.output_dir={out}",
+        "reward.kwargs.ocr.engine=tests.rewards.ocr_engines:reads_amber", "data.manifest=synthetic:8:0",
+        "distributed.rollout.gpus_per_worker=0"])
+    assert cfg.trainer.entrypoint.endswith(":train_janus_pro_ocr_grpo")
+    _train(cfg)
+    header, rows = _rows(out)
+    row = dict(zip(header, rows[0]))
+    assert header[-1] == "r_ocr" and float(row["clip_fraction"]) == 0.0 and float(row["approx_kl"]) < 1e-9
+    assert len(ocr_engines.CALLS) == 4
+    assert (out / "checkpoint-final" / "lora_weights" / "adapter_model.safetensors").exists()

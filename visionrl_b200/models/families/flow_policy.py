@@ -11,6 +11,7 @@ seeded per request.
 
 from __future__ import annotations
 
+import contextlib
 import math
 import random
 import sys
@@ -52,6 +53,22 @@ def resolve_dtype(value: Any) -> torch.dtype:
     if key not in table:
         raise ValueError(f"unknown dtype {value!r}")
     return table[key]
+
+
+@contextlib.contextmanager
+def seeded_construction(seed: int, device: Any = None):
+    """Inside the block the default random generators (CPU, and ``device`` when it is a GPU) are
+    seeded with ``seed``; afterwards they are where they were.  Building a network inside it makes
+    every weight a function of ``seed`` alone: the trainer's copy, a rollout worker's copy and
+    every rank's copy come out identical, whatever was drawn before."""
+    devices = []
+    if device is not None:
+        dev = torch.device(device)
+        if dev.type == "cuda":
+            devices = [dev.index if dev.index is not None else torch.cuda.current_device()]
+    with torch.random.fork_rng(devices=devices):
+        torch.manual_seed(int(seed))
+        yield
 
 
 def seeded_init(module: nn.Module, seed: int) -> None:
@@ -109,11 +126,14 @@ class NativeFlowPolicy(DiffusionPolicy):
         device = torch.device(spec.device)
         seed = int(native.get("init_seed", 0))
         # large networks are constructed where they will live (fp32 there, cast afterwards)
-        with torch.device(device if device.type == "cuda" else "cpu"):
-            transformer, decoder, text = cls._build_modules(arch, native)
-        if native.get("random_init", True):
-            seeded_init(transformer, seed)
-        else:
+        # (seeded_init scales its draws by the spread of the weights it replaces, so the
+        # construction itself has to be seeded as well; the decoder is only ever constructed)
+        with seeded_construction(seed, device):
+            with torch.device(device if device.type == "cuda" else "cpu"):
+                transformer, decoder, text = cls._build_modules(arch, native)
+            if native.get("random_init", True):
+                seeded_init(transformer, seed)
+        if not native.get("random_init", True):
             cls._load_native_checkpoint(transformer, spec.model_name_or_path)
         transformer.to(device=device, dtype=dtype)
         if decoder is not None:

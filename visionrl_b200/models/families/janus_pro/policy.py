@@ -26,7 +26,7 @@ import torch
 from torch import nn
 
 from visionrl_b200.models.ar import ARStepResult
-from visionrl_b200.models.families.flow_policy import resolve_dtype, seeded_init
+from visionrl_b200.models.families.flow_policy import resolve_dtype, seeded_construction, seeded_init
 from visionrl_b200.models.nn.layers import Linear, adapters_disabled, apply_lora, iter_lora_layers
 from visionrl_b200.models.nn.llama import KVCache, LlamaConfig, LlamaDecoder
 from visionrl_b200.models.nn.vision import HashTokenizer, VQDecoder
@@ -135,21 +135,23 @@ class JanusProPolicy(nn.Module):
         dtype = resolve_dtype(self.config.dtype)
         dev = torch.device(device)
         if network is None:
-            network = JanusNetwork(arch)
-            if self.config.random_init:
-                seeded_init(network, self.config.init_seed)
-            else:
+            with seeded_construction(self.config.init_seed, dev):
+                network = JanusNetwork(arch)
+                if self.config.random_init:
+                    seeded_init(network, self.config.init_seed)
+            if not self.config.random_init:
                 self._load_checkpoint(network, self.config.model_path)
         self.policy = network.to(device=dev, dtype=dtype)
         if vq_model is None:
             grid = max(1, self.config.image_size // self.config.patch_size)
             del grid
-            vq_model = VQDecoder(int(arch.get("image_vocab_size", 16384)),
-                                 int(arch.get("codebook_dim", 8)),
-                                 int(arch.get("vq_base", 128)),
-                                 tuple(arch.get("vq_mults", (1, 1, 2, 2, 4))),
-                                 int(arch.get("vq_blocks", 2)))
-            seeded_init(vq_model, self.config.init_seed + 1)
+            with seeded_construction(self.config.init_seed + 1, dev):
+                vq_model = VQDecoder(int(arch.get("image_vocab_size", 16384)),
+                                     int(arch.get("codebook_dim", 8)),
+                                     int(arch.get("vq_base", 128)),
+                                     tuple(arch.get("vq_mults", (1, 1, 2, 2, 4))),
+                                     int(arch.get("vq_blocks", 2)))
+                seeded_init(vq_model, self.config.init_seed + 1)
         vq_dtype = dtype if dev.type == "cuda" else torch.float32
         object.__setattr__(self, "_vq", vq_model.to(device=dev, dtype=vq_dtype).eval()
                            .requires_grad_(False))

@@ -18,7 +18,7 @@ import torch
 from torch import nn
 
 from visionrl_b200.models.ar import ARStepResult
-from visionrl_b200.models.families.flow_policy import resolve_dtype, seeded_init
+from visionrl_b200.models.families.flow_policy import resolve_dtype, seeded_construction, seeded_init
 from visionrl_b200.models.families.nextstep_1.flow_step import (
     flow_logprob_at, flow_sample_with_logprob,
 )
@@ -137,21 +137,23 @@ class NextStep1Policy(nn.Module):
         dtype = resolve_dtype(self.config.dtype)
         dev = torch.device(device)
         if network is None:
-            network = NextStepNetwork(arch)
             if not self.config.random_init:
                 raise FileNotFoundError(
                     "checkpoint-backed NextStep loading expects weights in the native key layout; "
                     "set model.random_init=true for seeded random weights")
-            seeded_init(network, self.config.init_seed)
+            with seeded_construction(self.config.init_seed, dev):
+                network = NextStepNetwork(arch)
+                seeded_init(network, self.config.init_seed)
         self.policy = network.to(device=dev, dtype=dtype)
         self.token_dim = int(self.policy.image_head.input_dim)
         if vae is None:
             patch = int(arch.get("token_patch", 2))
             channels = self.token_dim // (patch * patch)
-            vae = LatentDecoder2D(channels, int(arch.get("vae_base", 64)),
-                                  tuple(arch.get("vae_mults", (1, 2, 4))),
-                                  int(arch.get("vae_blocks", 1)), 1.0, 0.0)
-            seeded_init(vae, self.config.init_seed + 1)
+            with seeded_construction(self.config.init_seed + 1, dev):
+                vae = LatentDecoder2D(channels, int(arch.get("vae_base", 64)),
+                                      tuple(arch.get("vae_mults", (1, 2, 4))),
+                                      int(arch.get("vae_blocks", 1)), 1.0, 0.0)
+                seeded_init(vae, self.config.init_seed + 1)
         object.__setattr__(self, "_vae", vae.to(device=dev, dtype=dtype if dev.type == "cuda"
                                                 else torch.float32).eval().requires_grad_(False))
         self.tokenizer = HashTokenizer(self.policy.language_model.cfg.vocab_size)

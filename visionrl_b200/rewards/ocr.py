@@ -52,6 +52,18 @@ def _safe_filename_fragment(text: str, limit: int = 32) -> str:
     return re.sub(r"[^A-Za-z0-9_-]+", "_", text)[:limit] or "target"
 
 
+def _import_engine(path: str) -> Callable[[Any], str]:
+    import importlib
+
+    module, _, name = path.partition(":")
+    if not module or not name:
+        raise ValueError(f"OCR engine {path!r}: expected 'package.module:function'")
+    engine = getattr(importlib.import_module(module), name, None)
+    if not callable(engine):
+        raise ValueError(f"OCR engine {path!r} does not name a callable")
+    return engine
+
+
 def _default_engine() -> Callable[[Any], str]:
     try:
         from paddleocr import PaddleOCR
@@ -86,9 +98,11 @@ class OCRReward(RewardFunction):
     frame_interval: int = 4
 
     def __init__(self, device: str = "cuda", debug_dir: str | None = None,
-                 engine: Callable[[Any], str] | None = None) -> None:
+                 engine: Callable[[Any], str] | str | None = None) -> None:
         self._device = device
-        self._engine = engine
+        # a callable frame -> text, or its import path ("package.module:function") so that a YAML
+        # config can name one (``reward.kwargs.ocr.engine``)
+        self._engine = _import_engine(engine) if isinstance(engine, str) and engine else engine
         self._debug_dir = Path(debug_dir) if debug_dir else None
         self._debug_counter = 0
         if self._debug_dir is not None:

@@ -14,7 +14,7 @@ from typing import Any
 
 import torch
 
-from visionrl_b200.models.families.flow_policy import seeded_init
+from visionrl_b200.models.families.flow_policy import seeded_construction, seeded_init
 from visionrl_b200.models.nn.vision import ViTScorer
 
 _PRESET_OF = {
@@ -37,10 +37,12 @@ def build_image_tower(model_name: str, device: Any, dtype: torch.dtype | None = 
         random_init = True
     else:
         preset = _PRESET_OF.get(model_name, "vit_l14")
-    tower = ViTScorer.from_preset(preset)
-    if random_init:
-        seeded_init(tower, seed + 7919)
-    else:
+    # construction seeded too: every rank and every process scores with the same tower
+    with seeded_construction(seed + 7919):
+        tower = ViTScorer.from_preset(preset)
+        if random_init:
+            seeded_init(tower, seed + 7919)
+    if not random_init:
         file = os.path.join(model_name, "tower.safetensors")
         if not os.path.exists(file):
             raise FileNotFoundError(

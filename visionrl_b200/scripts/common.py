@@ -54,6 +54,8 @@ class RecipeParts:
     csv_columns: str = CSV_HEAD
     csv_row: Callable[[int, Any], str] | None = None
     first_epoch: int = 0                    # NextStep counts steps from 1
+    adapter_module: Any = None              # the module whose adapters a checkpoint exports to
+                                            # lora_weights/ (default: the first trainable module)
     extra: dict[str, Any] = field(default_factory=dict)
 
 
@@ -277,7 +279,8 @@ async def run_online_recipe(ctx: RunContext, parts: RecipeParts, reward_fn: Any,
                 tc.total_epochs, len(examples), tc.n)
     uses_lora = bool(cfg_path(cfg, "model.use_lora", False))
     export = None
-    trainable = next(iter(bundle.trainable_modules.values()))
+    trainable = parts.adapter_module if parts.adapter_module is not None \
+        else next(iter(bundle.trainable_modules.values()))
     if uses_lora and hasattr(trainable, "save_pretrained"):
         export = {LORA_WEIGHTS_NAME: trainable}
     row_fn = parts.csv_row or default_csv_row

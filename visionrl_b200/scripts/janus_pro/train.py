@@ -58,7 +58,8 @@ async def _train_janus_pro(cfg: Any) -> Any:
         family="janus_pro", bundle=bundle, collector_config=collector_config,
         evaluator=TokenLogProbEvaluator(mask_key=algo_cfg.mask_key), algorithm=TokenGRPO(algo_cfg),
         ref_model=policy if need_ref else None, stat_tracker=tracker,
-        csv_columns=JANUS_CSV_HEAD, csv_row=_janus_csv_row)
+        csv_columns=JANUS_CSV_HEAD, csv_row=_janus_csv_row,
+        adapter_module=policy.language_model)
     return await run_online_recipe(ctx, parts, reward_fn, list(weights))
 
 

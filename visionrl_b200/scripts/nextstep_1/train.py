@@ -44,5 +44,6 @@ async def train_nextstep_1_ocr_grpo(cfg: Any) -> Any:
         family="nextstep_1", bundle=bundle, collector_config=collector_config,
         evaluator=ContinuousTokenLogProbEvaluator(mask_key=algo_cfg.mask_key),
         algorithm=TokenGRPO(algo_cfg), ref_model=policy if need_ref else None,
-        stat_tracker=tracker, csv_columns=NEXTSTEP_CSV_HEAD, first_epoch=1)
+        stat_tracker=tracker, csv_columns=NEXTSTEP_CSV_HEAD, first_epoch=1,
+        adapter_module=policy.language_model)
     return await run_online_recipe(ctx, parts, reward_fn, list(weights))
