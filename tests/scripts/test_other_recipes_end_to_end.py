@@ -227,3 +227,49 @@ def test_janus_ocr_recipe_runs_through_its_own_entry_point(tmp_path):
     assert header[-1] == "r_ocr" and float(row["clip_fraction"]) == 0.0 and float(row["approx_kl"]) < 1e-9
     assert len(ocr_engines.CALLS) == 4
     assert (out / "checkpoint-final" / "lora_weights" / "adapter_model.safetensors").exists()
+
+
+@pytest.mark.timeout(600)
+def test_wan_dpo_recipe_on_a_local_dataset_in_the_pickapic_schema(tmp_path):
+    """The pixel path of the DPO recipe: a parquet directory with the Pick-a-Pic columns
+    (``jpg_0``, ``jpg_1``, ``label_0``, ``caption``) is read through ``datasets``, ties are dropped,
+    images are resized / cropped / normalised, encoded by the frozen encoder and trained on."""
+    datasets = pytest.importorskip("datasets")
+    pytest.importorskip("torchvision")
+    import io
+
+    import numpy as np
+    from PIL import Image
+
+    from visionrl_b200.trainers.pickapic import load_pickapic
+
+    rng = np.random.default_rng(0)
+
+    def jpg():
+        buf = io.BytesIO()
+        Image.fromarray(rng.integers(0, 255, (40, 48, 3), dtype=np.uint8)).save(buf, format="JPEG")
+        return buf.getvalue()
+
+    root = tmp_path / "pairs"
+    root.mkdir()
+    datasets.Dataset.from_dict({"jpg_0": [jpg() for _ in range(6)], "jpg_1": [jpg() for _ in range(6)],
+                                "label_0": [1, 0, 0.5, 1, 0, 1],
+                                "caption": [f"caption {i}" for i in range(6)]}).to_parquet(str(root / "train.parquet"))
+    pairs = load_pickapic(dataset_name=str(root), resolution=32, no_hflip=True)
+    assert len(pairs) == 5                                                # the tie is gone
+    item = pairs[1]                                                       # label_0 == 0: the second image won
+    assert item["pixel_values"].shape == (6, 32, 32) and item["caption"] == "caption 1"
+    assert float(item["pixel_values"].min()) >= -1.0 and float(item["pixel_values"].max()) <= 1.0
+
+    out = tmp_path / "dpo_pixels"
+    _train(load_config("experiment/wan_2_1_1_3b_dpo", overrides=[
+        o for o in TINY_VIDEO_ARCH if "num_frames" not in o] + [
+        "model.random_init=true", "model.dtype=float32", "model.lora.rank=4", "model.lora.alpha=8",
+        "actor.mixed_precision=no", "sampling.num_steps=4", "trainer.max_train_steps=3",
+        "trainer.checkpointing_steps=2", "trainer.log_interval=1", f"trainer.output_dir={out}",
+        f"data.dataset_name={root}", "data.dataloader_num_workers=0"]))
+    header, rows = _rows(out)
+    assert [r[0] for r in rows] == ["1", "2", "3"]
+    assert all(_finite(header, r, ("loss", "raw_model_loss", "grad_norm")) for r in rows)
+    assert float(rows[0][header.index("loss")]) == pytest.approx(math.log(2.0), abs=1e-5)
+    assert sorted(p.name for p in out.glob("checkpoint-*")) == ["checkpoint-2", "checkpoint-final"]
