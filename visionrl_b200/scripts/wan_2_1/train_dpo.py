@@ -119,7 +119,14 @@ def train_wan_2_1_dpo(cfg: Any) -> Any:
         grad_sync = ShardedGradSync(mesh, collectives=str(cfg_path(cfg, "distributed.collectives",
                                                                    "fused")))
     ref_model = None if bool(cfg.model.use_lora) else _frozen_copy(policy)
-    trainer = OfflineDPOTrainer(policy, ref_model, wan_forward, bundle.scheduler, encode_pixels,
+    noise_scheduler = bundle.scheduler
+    if dpo_cfg.prediction_type in ("epsilon", "v_prediction"):
+        # the flow schedule has no variance-preserving forward process; these targets get one
+        from visionrl_b200.models.nn.scheduler import DDPMNoiseScheduler
+
+        noise_scheduler = DDPMNoiseScheduler(prediction_type=dpo_cfg.prediction_type)
+        noise_scheduler.set_timesteps(noise_scheduler.num_train_timesteps, device=device)
+    trainer = OfflineDPOTrainer(policy, ref_model, wan_forward, noise_scheduler, encode_pixels,
                                 encode_text, dpo_cfg, device=device, grad_sync=grad_sync)
     if grad_sync is not None:
         grad_sync.prepare(trainer._optimizer)
