@@ -116,3 +116,34 @@ def test_wan_official_policy_samples_with_both_flow_solvers(wan):
     assert (dpm - fine).abs().mean() < 0.2 * fine.abs().mean()
     assert max(used) >= 500.0 > min(used)                      # both experts were consulted
     assert len(policy._prompt_cache) == 1                      # one prompt, encoded once
+
+
+def test_official_wan_variant_is_selectable_from_the_config_and_rolls_out():
+    """``model.backend: official`` builds the two-expert variant: the second expert is a different
+    network, the boundary comes from the config, the executor drives it like any other policy, and
+    asking it for adapters is refused (it is rollout-only)."""
+    from visionrl_b200.models.families.wan_2_1.builder import build_wan_2_1_runtime_bundle_from_cfg
+    from visionrl_b200.models.families.wan_2_1.executor import Wan_2_1PipelineExecutor
+    from visionrl_b200.models.families.wan_2_1.official_policy import WanT2VOfficialPolicy
+
+    cfg = load_config("experiment/wan_2_1_1_3b_grpo",
+                      overrides=TINY_WAN + ["model.backend=official", "+model.arch.boundary=0.5"])
+    bundle = build_wan_2_1_runtime_bundle_from_cfg(cfg, "cpu", torch.float32)
+    policy = bundle.policy
+    assert isinstance(policy, WanT2VOfficialPolicy) and bundle.backend_kind == "official"
+    assert policy.boundary == 0.5 and policy._low_noise is not None
+    high = dict(policy.transformer.named_parameters())
+    low = dict(policy._low_noise.named_parameters())
+    assert any(not torch.equal(high[k], low[k]) for k in high) and not any(p.requires_grad for p in low.values())
+    req = _request("wan_2_1", "t2v", ["a"], 2)
+    out = Wan_2_1PipelineExecutor(policy, sample_batch_size=2).forward(
+        req, GenerationIdFactory().build_sample_specs(req))
+    assert out.error is None and out.rollout_trajectory_data.rollout_log_probs.shape == (2, STEPS)
+    with pytest.raises(NotImplementedError):
+        build_wan_2_1_runtime_bundle_from_cfg(
+            load_config("experiment/wan_2_1_1_3b_grpo", overrides=[o for o in TINY_WAN if "use_lora" not in o]
+                        + ["model.backend=official"]), "cpu", torch.float32)
+    with pytest.raises(NotImplementedError, match="no adapter for backend"):
+        build_wan_2_1_runtime_bundle_from_cfg(
+            load_config("experiment/wan_2_1_1_3b_grpo", overrides=TINY_WAN + ["model.backend=vendor"]),
+            "cpu", torch.float32)

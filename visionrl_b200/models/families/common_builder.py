@@ -46,7 +46,7 @@ def extract_diffusion_runtime_spec(cfg: Any, device: Any, weight_dtype: Any, *,
         native["shift"] = float(model.shift)
     return RuntimeBuildSpec(
         model_name_or_path=str(_get(model, "path", "")), device=device, dtype=weight_dtype,
-        backend_preference=("native",), task_variant=task_variant,
+        backend_preference=(str(_get(model, "backend", "native") or "native"),), task_variant=task_variant,
         use_lora=bool(model.use_lora), lora_path=lora_path, lora_config=lora_cfg,
         scheduler_config={"num_steps": int(cfg.sampling.num_steps)},
         native_backend_config=native, extra=extra,

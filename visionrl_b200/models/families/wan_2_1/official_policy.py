@@ -30,6 +30,27 @@ class WanT2VOfficialPolicy(WanT2VDiffusersPolicy):
         object.__setattr__(self, "_low_noise", None)
         self._prompt_cache: dict[str, dict[str, Any]] = {}
 
+    @classmethod
+    def from_spec(cls, spec: Any) -> "WanT2VOfficialPolicy":
+        """``model.backend: official`` builds this variant: ``model.arch.boundary`` sets the switch
+        point and, unless ``model.arch.two_experts`` is false, the low-noise expert is attached
+        (with random init: a second network drawn from ``init_seed + 1``)."""
+        policy = super().from_spec(spec)
+        native = dict(spec.native_backend_config or {})
+        arch = dict(native.get("arch") or {})
+        policy.boundary = float(arch.get("boundary", policy.boundary))
+        if bool(arch.get("two_experts", True)):
+            expert = None
+            if native.get("random_init", True):
+                from visionrl_b200.models.families.flow_policy import seeded_construction, seeded_init
+
+                seed = int(native.get("init_seed", 0)) + 1
+                with seeded_construction(seed, policy.device):
+                    expert = copy.deepcopy(policy.transformer)
+                    seeded_init(expert, seed)
+            policy.attach_low_noise_expert(expert)
+        return policy
+
     def attach_low_noise_expert(self, module: torch.nn.Module | None = None) -> None:
         expert = module if module is not None else copy.deepcopy(self.transformer)
         object.__setattr__(self, "_low_noise", expert.requires_grad_(False).eval())
