@@ -89,19 +89,44 @@ TINY_JANUS = [
 ]
 
 
+TINY_COSMOS = [
+    "model.random_init=true", "model.arch.num_layers=2", "model.arch.hidden_size=64", "model.arch.num_heads=2",
+    "model.arch.ffn_dim=128", "model.arch.text_dim=32", "model.arch.freq_dim=32", "+model.dtype=float32",
+    "model.lora.rank=4", "model.lora.alpha=8", "sampling.num_frames=5", "sampling.height=32", "sampling.width=32",
+    "sampling.max_sequence_length=8", "sampling.num_steps=3", "actor.bf16=false", "rollout.n=2",
+    "rollout.rollout_batch_size=2", "rollout.sample_batch_size=2", "reward.components.aesthetic=0.0",
+    "reward.components.vit_scalar=1.0", "reward.kwargs.vit_scalar.preset=vit_tiny", "reward.kwargs.vit_scalar.seed=0",
+    "reward.kwargs.vit_scalar.num_frames=2", "data.manifest=synthetic:8:0", "distributed.rollout.gpus_per_worker=0",
+]
+TINY_NEXTSTEP = [
+    "model.random_init=true", "model.arch.num_layers=2", "model.arch.hidden_size=64", "model.arch.num_heads=2",
+    "model.arch.ffn_dim=128", "model.arch.vocab_size=128", "model.arch.token_dim=16", "model.arch.head_hidden=32",
+    "model.arch.head_layers=2", "+model.arch.token_patch=2", "+model.arch.vae_base=8", "+model.arch.vae_mults=[1,2]",
+    "+model.arch.vae_blocks=1", "model.dtype=float32", "model.lora.rank=4", "model.lora.alpha=8",
+    "sampling.image_size=16", "sampling.image_token_num=4", "sampling.num_flow_steps=3",
+    "rollout.n_samples_per_prompt=2", "rollout.rollout_batch_size=2", "rollout.max_text_length=8", "actor.bf16=false",
+    "reward.components.ocr=0.0", "reward.components.vit_scalar=1.0", "reward.kwargs.vit_scalar.preset=vit_tiny",
+    "reward.kwargs.vit_scalar.seed=0", "reward.kwargs.vit_scalar.num_frames=1", "data.manifest=synthetic:8:0",
+    "distributed.rollout.gpus_per_worker=0",
+]
+
+
 @pytest.mark.timeout(600)
-@pytest.mark.parametrize("experiment,overrides,samples", [
+@pytest.mark.parametrize("experiment,overrides,samples,epochs", [
     ("experiment/tiny_dit_grpo", ["sampling.num_steps=3", "rollout.n=2", "rollout.rollout_batch_size=2",
-                                  "rollout.sample_batch_size=2", "distributed.param_sharding=full"], 4),
-    ("experiment/janus_pro_1b_shape_grpo", TINY_JANUS, 8),
+                                  "rollout.sample_batch_size=2", "distributed.param_sharding=full"], 4, ["0", "1"]),
+    ("experiment/janus_pro_1b_shape_grpo", TINY_JANUS, 8, ["0", "1"]),
+    ("experiment/cosmos_predict2_2b_grpo", TINY_COSMOS, 4, ["0", "1"]),
+    ("experiment/nextstep_1_ocr_grpo", TINY_NEXTSTEP, 4, ["1", "2"]),        # this recipe counts steps from 1
 ])
-def test_recipes_train_checkpoint_and_resume_on_two_data_parallel_cpu_ranks(tmp_path, experiment, overrides, samples):
+def test_recipes_train_checkpoint_and_resume_on_two_data_parallel_cpu_ranks(tmp_path, experiment, overrides, samples,
+                                                                            epochs):
     import math
 
     res = _run(_workers.recipe_runs_on_cpu_ranks, 2, experiment, overrides, str(tmp_path / "run"), _free_port(),
                timeout=500)
     rows, perf = res["rows"], res["perf"]
-    assert [r[0] for r in rows[1:]] == ["0", "1"]
+    assert [r[0] for r in rows[1:]] == epochs
     assert all(math.isfinite(float(v)) for r in rows[1:] for v in r[1:6])
     assert [p["n_ranks"] for p in perf] == [2, 2] and perf[0]["samples"] == samples
 
