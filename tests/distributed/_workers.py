@@ -598,3 +598,35 @@ def recipe_restarts_in_place_after_a_rank_raises(rank, world, port, out_dir, sec
         out.put({"rows": list(csv.reader((root / "metrics.csv").open())), "restarts": restarts,
                  "attempts": attempts, "checkpoints": sorted(p.name for p in root.glob("checkpoint-*")),
                  "resume_configs": len(list(root.glob("resume_config_*.yaml")))})
+
+
+def dpo_recipe_runs_on_cpu_ranks(rank, world, port, overrides, out_dir, resume_port, out):
+    """The preference recipe on ``world`` gloo ranks: three steps with a checkpoint after the second,
+    then a resumed run up to step five; rank 0 reports the CSV rows and the checkpoints."""
+    import asyncio
+    import csv
+    import inspect
+    import pathlib
+
+    from visionrl_b200.config.loader import load_config
+    from visionrl_b200.scripts.train import run_config
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank))
+    base = list(overrides) + [f"trainer.output_dir={out_dir}", "trainer.checkpointing_steps=2", "trainer.log_interval=1",
+                              "+distributed.backend=native", "+distributed.collectives=nccl"]
+
+    def train(extra):
+        result = run_config(load_config("experiment/wan_2_1_1_3b_shape_dpo", overrides=base + extra))
+        if inspect.isawaitable(result):
+            asyncio.new_event_loop().run_until_complete(result)
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+    train(["trainer.max_train_steps=3"])
+    os.environ["MASTER_PORT"] = str(resume_port)
+    train(["trainer.max_train_steps=5", "trainer.resume_from=auto"])
+    if rank == 0:
+        root = pathlib.Path(out_dir)
+        out.put({"rows": list(csv.reader((root / "metrics.csv").open())),
+                 "checkpoints": sorted(p.name for p in root.glob("checkpoint-*"))})

@@ -187,3 +187,22 @@ def test_recipe_restarts_in_place_from_the_latest_checkpoint_after_a_rank_raises
     assert [r[0] for r in res["rows"][1:]] == ["0", "1", "2"]
     assert res["checkpoints"] == ["checkpoint-1", "checkpoint-2", "checkpoint-3", "checkpoint-final"]
     assert res["resume_configs"] == 1
+
+
+@pytest.mark.timeout(600)
+def test_preference_recipe_trains_and_resumes_on_two_cpu_ranks(tmp_path):
+    import math
+
+    overrides = ["model.arch.num_layers=2", "model.arch.hidden_size=64", "model.arch.num_heads=2",
+                 "model.arch.ffn_dim=128", "model.arch.text_dim=32", "model.arch.freq_dim=32", "model.dtype=float32",
+                 "sampling.num_frames=5", "sampling.height=32", "sampling.width=32", "sampling.max_sequence_length=8",
+                 "sampling.num_steps=4", "actor.bf16=false", "data.synthetic.num_pairs=8"]
+    res = _run(_workers.dpo_recipe_runs_on_cpu_ranks, 2, overrides, str(tmp_path / "run"), _free_port(), timeout=500)
+    header, rows = res["rows"][0], res["rows"][1:]
+    # three steps, then the resumed run picks up the latest checkpoint and adds steps four and five
+    assert [r[0] for r in rows] == ["1", "2", "3", "4", "5"]
+    assert res["checkpoints"] == ["checkpoint-2", "checkpoint-4", "checkpoint-final"]
+    assert float(rows[0][header.index("loss")]) == pytest.approx(math.log(2.0), abs=1e-5)
+    # the learning rate is scaled by the number of ranks (actor.scale_lr)
+    assert float(rows[0][header.index("lr")]) == pytest.approx(2.0e-8)
+    assert all(math.isfinite(float(r[header.index("grad_norm")])) for r in rows)
