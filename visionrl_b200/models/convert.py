@@ -1,0 +1,135 @@
+"""Checkpoints in the Hugging Face LLaMA layout → the native key layout.
+
+The native decoder (``visionrl_b200/models/nn/llama.py``) differs from the Hugging Face one in
+three ways a converter has to undo:
+
+* q, k and v are one fused projection whose output is ``[q | k | v]``, and gate and up are one
+  fused projection ``[gate | up]``;
+* rotary embedding rotates ADJACENT pairs ``(2i, 2i+1)`` of a head, the Hugging Face code
+  rotates the pair ``(i, i + Dh/2)``; the rows of the q and k projections are therefore
+  permuted per head so that HF row ``i`` becomes native row ``2i`` and HF row ``i + Dh/2`` becomes
+  native row ``2i + 1`` (q·k products are unchanged because both get the same permutation);
+* names: ``input_layernorm`` → ``attn_norm``, ``post_attention_layernorm`` → ``mlp_norm``,
+  ``self_attn.o_proj`` → ``attn.out``, ``mlp.down_proj`` → ``down``.
+
+``llama_from_hf`` is checked against the ``transformers`` implementation in the tests (same
+hidden states from the same weights).  ``janus_from_hf`` wraps it with the generation-side
+modules of a Janus-Pro checkpoint under the key names of the public Janus code
+(``gen_embed``, ``gen_aligner.layers.{0,2}``, ``gen_head.output_mlp_projector``,
+``gen_head.vision_head``); no such checkpoint can be fetched here, so that part is exercised on
+the key mapping only.
+
+    python -m visionrl_b200.models.convert janus <hf_dir> <out_dir> --num-heads 16
+"""
+
+from __future__ import annotations
+
+import argparse
+import os
+from typing import Mapping
+
+import torch
+
+_TRUNK_PREFIXES = ("language_model.model.", "model.", "")
+
+
+def _interleave_rotary_rows(weight: torch.Tensor, num_heads: int) -> torch.Tensor:
+    """Rows of a ``[H*Dh, K]`` q or k projection from half-split to adjacent-pair rotary order."""
+    out_features, k = weight.shape
+    dh = out_features // num_heads
+    if dh * num_heads != out_features or dh % 2:
+        raise ValueError(f"projection with {out_features} rows does not split into {num_heads} even heads")
+    w = weight.view(num_heads, 2, dh // 2, k)              # [head, half, i, K]
+    return w.transpose(1, 2).reshape(out_features, k).contiguous()   # [head, i, half, K]
+
+
+def _strip_trunk_prefix(state: Mapping[str, torch.Tensor]) -> dict[str, torch.Tensor]:
+    for prefix in _TRUNK_PREFIXES:
+        probe = prefix + "layers.0.self_attn.q_proj.weight"
+        if probe in state:
+            return {k[len(prefix):]: v for k, v in state.items() if k.startswith(prefix)}
+    raise KeyError("no LLaMA trunk found (looked for layers.0.self_attn.q_proj.weight under "
+                   "'language_model.model.', 'model.' and no prefix)")
+
+
+def llama_from_hf(state: Mapping[str, torch.Tensor], num_heads: int) -> dict[str, torch.Tensor]:
+    """State dict of ``LlamaDecoder`` from a Hugging Face ``LlamaModel`` / ``LlamaForCausalLM``
+    state dict (multi-head attention: as many key/value heads as query heads)."""
+    hf = _strip_trunk_prefix(state)
+    out: dict[str, torch.Tensor] = {"embed_tokens.weight": hf["embed_tokens.weight"], "norm.weight": hf["norm.weight"]}
+    layer = 0
+    while f"layers.{layer}.self_attn.q_proj.weight" in hf:
+        p = f"layers.{layer}."
+        q, k, v = (hf[p + f"self_attn.{n}_proj.weight"] for n in "qkv")
+        if k.shape != q.shape or v.shape != q.shape:
+            raise ValueError(f"layer {layer}: grouped-query attention ({tuple(k.shape)} keys for "
+                             f"{tuple(q.shape)} queries) has no native counterpart")
+        for bias in ("self_attn.q_proj.bias", "mlp.gate_proj.bias"):
+            if p + bias in hf:
+                raise ValueError(f"layer {layer}: projection biases have no native counterpart")
+        out[p + "attn.qkv.weight"] = torch.cat([_interleave_rotary_rows(q, num_heads),
+                                                _interleave_rotary_rows(k, num_heads), v], dim=0)
+        out[p + "attn.out.weight"] = hf[p + "self_attn.o_proj.weight"]
+        out[p + "gate_up.weight"] = torch.cat([hf[p + "mlp.gate_proj.weight"], hf[p + "mlp.up_proj.weight"]], dim=0)
+        out[p + "down.weight"] = hf[p + "mlp.down_proj.weight"]
+        out[p + "attn_norm.weight"] = hf[p + "input_layernorm.weight"]
+        out[p + "mlp_norm.weight"] = hf[p + "post_attention_layernorm.weight"]
+        layer += 1
+    if layer == 0:
+        raise KeyError("the state dict has no decoder layers")
+    return {k: v.contiguous() for k, v in out.items()}
+
+
+_JANUS_SIDE = {
+    "gen_embed.weight": "gen_embed.weight",
+    "gen_aligner.layers.0.weight": "gen_aligner.fc1.weight", "gen_aligner.layers.0.bias": "gen_aligner.fc1.bias",
+    "gen_aligner.layers.2.weight": "gen_aligner.fc2.weight", "gen_aligner.layers.2.bias": "gen_aligner.fc2.bias",
+    "gen_head.output_mlp_projector.weight": "gen_head.fc1.weight",
+    "gen_head.output_mlp_projector.bias": "gen_head.fc1.bias",
+    "gen_head.vision_head.weight": "gen_head.fc2.weight", "gen_head.vision_head.bias": "gen_head.fc2.bias",
+}
+
+
+def janus_from_hf(state: Mapping[str, torch.Tensor], num_heads: int) -> dict[str, torch.Tensor]:
+    """State dict of ``JanusNetwork`` (trunk + generation embedding, aligner and head) from a
+    Janus-Pro checkpoint; understanding-side modules (vision tower, ``lm_head``) are dropped."""
+    out = {f"language_model.{k}": v for k, v in llama_from_hf(state, num_heads).items()}
+    missing = [k for k in _JANUS_SIDE if k not in state]
+    if missing:
+        raise KeyError(f"Janus checkpoint lacks {missing[:3]}")
+    out.update({native: state[src].contiguous() for src, native in _JANUS_SIDE.items()})
+    return out
+
+
+def _load_dir(path: str) -> dict[str, torch.Tensor]:
+    from safetensors.torch import load_file
+
+    files = sorted(f for f in os.listdir(path) if f.endswith(".safetensors"))
+    if not files:
+        raise FileNotFoundError(f"no .safetensors files in {path}")
+    state: dict[str, torch.Tensor] = {}
+    for name in files:
+        state.update(load_file(os.path.join(path, name)))
+    return state
+
+
+def main(argv: list[str] | None = None) -> int:
+    from safetensors.torch import save_file
+
+    parser = argparse.ArgumentParser(description="Convert a Hugging Face LLaMA-layout checkpoint "
+                                                 "directory to the native key layout.")
+    parser.add_argument("kind", choices=["llama", "janus"])
+    parser.add_argument("source", help="directory with *.safetensors in the Hugging Face layout")
+    parser.add_argument("target", help="directory to write (janus.safetensors / llama.safetensors)")
+    parser.add_argument("--num-heads", type=int, required=True)
+    args = parser.parse_args(argv)
+    state = _load_dir(args.source)
+    native = (janus_from_hf if args.kind == "janus" else llama_from_hf)(state, args.num_heads)
+    os.makedirs(args.target, exist_ok=True)
+    save_file(native, os.path.join(args.target, f"{args.kind}.safetensors"))
+    print(f"wrote {len(native)} tensors to {os.path.join(args.target, args.kind + '.safetensors')}")
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
