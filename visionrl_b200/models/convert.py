@@ -19,7 +19,11 @@ modules of a Janus-Pro checkpoint under the key names of the public Janus code
 ``gen_head.vision_head``); no such checkpoint can be fetched here, so that part is exercised on
 the key mapping only.
 
+``clip_vision_from_hf`` does the same for the image tower of a CLIP checkpoint (the reward
+towers), checked against ``transformers.CLIPVisionModelWithProjection`` in the tests.
+
     python -m visionrl_b200.models.convert janus <hf_dir> <out_dir> --num-heads 16
+    python -m visionrl_b200.models.convert clip_vision <hf_dir> <out_dir>
 """
 
 from __future__ import annotations
@@ -101,6 +105,85 @@ def janus_from_hf(state: Mapping[str, torch.Tensor], num_heads: int) -> dict[str
     return out
 
 
+def clip_vision_from_hf(state: Mapping[str, torch.Tensor]) -> dict[str, torch.Tensor]:
+    """State dict of ``ViTScorer`` (without its scalar head) from a Hugging Face
+    ``CLIPVisionModelWithProjection`` / ``CLIPModel`` state dict: the strided patch convolution
+    becomes a product over flattened ``(channel, row, column)`` patches, q/k/v are fused, the class
+    token and the position table get their leading batch dimensions."""
+    vm = "vision_model."
+    if vm + "embeddings.class_embedding" not in state:
+        raise KeyError("no CLIP vision tower found (vision_model.embeddings.class_embedding)")
+    if "visual_projection.weight" not in state:
+        raise KeyError("the checkpoint has no visual_projection (a tower without projection head)")
+    conv = state[vm + "embeddings.patch_embedding.weight"]
+    out: dict[str, torch.Tensor] = {
+        "patch_embed.weight": conv.reshape(conv.shape[0], -1),
+        "cls": state[vm + "embeddings.class_embedding"].reshape(1, 1, -1),
+        "pos": state[vm + "embeddings.position_embedding.weight"].unsqueeze(0),
+        "proj.weight": state["visual_projection.weight"],
+    }
+    for src, dst in (("pre_layrnorm", "pre_norm"), ("post_layernorm", "post_norm")):
+        for leaf in ("weight", "bias"):
+            out[f"{dst}.{leaf}"] = state[f"{vm}{src}.{leaf}"]
+    layer = _clip_blocks(state, vm, out)
+    if layer == 0:
+        raise KeyError("the CLIP vision tower has no encoder layers")
+    return {k: v.contiguous() for k, v in out.items()}
+
+
+def _clip_blocks(state: Mapping[str, torch.Tensor], prefix: str, out: dict[str, torch.Tensor]) -> int:
+    layer = 0
+    while f"{prefix}encoder.layers.{layer}.self_attn.q_proj.weight" in state:
+        p, q = f"{prefix}encoder.layers.{layer}.", f"blocks.{layer}."
+        for leaf in ("weight", "bias"):
+            out[q + f"qkv.{leaf}"] = torch.cat([state[p + f"self_attn.{n}_proj.{leaf}"] for n in "qkv"], dim=0)
+            out[q + f"out.{leaf}"] = state[p + f"self_attn.out_proj.{leaf}"]
+            out[q + f"n1.{leaf}"] = state[p + f"layer_norm1.{leaf}"]
+            out[q + f"n2.{leaf}"] = state[p + f"layer_norm2.{leaf}"]
+            out[q + f"mlp.fc1.{leaf}"] = state[p + f"mlp.fc1.{leaf}"]
+            out[q + f"mlp.fc2.{leaf}"] = state[p + f"mlp.fc2.{leaf}"]
+        layer += 1
+    return layer
+
+
+def clip_text_from_hf(state: Mapping[str, torch.Tensor]) -> dict[str, torch.Tensor]:
+    """State dict of ``CLIPTextTower`` from a Hugging Face ``CLIPModel`` /
+    ``CLIPTextModelWithProjection`` state dict."""
+    tm = "text_model."
+    if tm + "embeddings.token_embedding.weight" not in state or "text_projection.weight" not in state:
+        raise KeyError("no CLIP text tower with projection found (text_model.embeddings.token_embedding.weight, "
+                       "text_projection.weight)")
+    out: dict[str, torch.Tensor] = {
+        "token_embed.weight": state[tm + "embeddings.token_embedding.weight"],
+        "pos": state[tm + "embeddings.position_embedding.weight"],
+        "final_norm.weight": state[tm + "final_layer_norm.weight"],
+        "final_norm.bias": state[tm + "final_layer_norm.bias"],
+        "proj.weight": state["text_projection.weight"],
+    }
+    if _clip_blocks(state, tm, out) == 0:
+        raise KeyError("the CLIP text tower has no encoder layers")
+    return {k: v.contiguous() for k, v in out.items()}
+
+
+def clip_text_shape(state: Mapping[str, torch.Tensor]) -> dict[str, int]:
+    """``CLIPTextTower`` constructor arguments read off a converted text tower state dict."""
+    layers = 1 + max(int(k.split(".")[1]) for k in state if k.startswith("blocks."))
+    vocab, dim = (int(v) for v in state["token_embed.weight"].shape)
+    return {"layers": layers, "dim": dim, "mlp": int(state["blocks.0.mlp.fc1.weight"].shape[0]), "vocab": vocab,
+            "context": int(state["pos"].shape[0]), "out_dim": int(state["proj.weight"].shape[0])}
+
+
+def clip_vision_shape(state: Mapping[str, torch.Tensor]) -> dict[str, int]:
+    """``ViTScorer`` constructor arguments read off a converted (native) tower state dict; the
+    head count is not recorded in the weights and has to come from the checkpoint's config."""
+    dim = int(state["cls"].shape[-1])
+    layers = 1 + max(int(k.split(".")[1]) for k in state if k.startswith("blocks."))
+    patch = int(round((state["patch_embed.weight"].shape[1] / 3) ** 0.5))
+    grid = int(round((state["pos"].shape[1] - 1) ** 0.5))
+    return {"layers": layers, "dim": dim, "mlp": int(state["blocks.0.mlp.fc1.weight"].shape[0]),
+            "patch": patch, "image": patch * grid, "out_dim": int(state["proj.weight"].shape[0])}
+
+
 def _load_dir(path: str) -> dict[str, torch.Tensor]:
     from safetensors.torch import load_file
 
@@ -118,16 +201,22 @@ def main(argv: list[str] | None = None) -> int:
 
     parser = argparse.ArgumentParser(description="Convert a Hugging Face LLaMA-layout checkpoint "
                                                  "directory to the native key layout.")
-    parser.add_argument("kind", choices=["llama", "janus"])
+    parser.add_argument("kind", choices=["llama", "janus", "clip_vision"])
     parser.add_argument("source", help="directory with *.safetensors in the Hugging Face layout")
     parser.add_argument("target", help="directory to write (janus.safetensors / llama.safetensors)")
-    parser.add_argument("--num-heads", type=int, required=True)
+    parser.add_argument("--num-heads", type=int, default=0, help="attention heads (llama, janus)")
     args = parser.parse_args(argv)
     state = _load_dir(args.source)
-    native = (janus_from_hf if args.kind == "janus" else llama_from_hf)(state, args.num_heads)
+    if args.kind == "clip_vision":
+        native, name = clip_vision_from_hf(state), "tower"
+    else:
+        if args.num_heads <= 0:
+            parser.error("--num-heads is required for llama and janus")
+        native = (janus_from_hf if args.kind == "janus" else llama_from_hf)(state, args.num_heads)
+        name = args.kind
     os.makedirs(args.target, exist_ok=True)
-    save_file(native, os.path.join(args.target, f"{args.kind}.safetensors"))
-    print(f"wrote {len(native)} tensors to {os.path.join(args.target, args.kind + '.safetensors')}")
+    save_file(native, os.path.join(args.target, f"{name}.safetensors"))
+    print(f"wrote {len(native)} tensors to {os.path.join(args.target, name + '.safetensors')}")
     return 0
 
 

@@ -122,19 +122,35 @@ class VQDecoder(nn.Module):
         return self.decoder(z)
 
 
+VIT_ACTIVATIONS = ("gelu_tanh", "quick_gelu", "gelu")
+
+
 class ViTBlock(nn.Module):
-    def __init__(self, dim: int, heads: int, mlp: int):
+    """Pre-norm transformer block.  ``act``: ``gelu_tanh`` (fused into the first MLP product;
+    what the seeded random towers use), ``quick_gelu`` (``x * sigmoid(1.702 x)``, the OpenAI CLIP
+    checkpoints) or ``gelu`` (exact, the OpenCLIP ones)."""
+
+    def __init__(self, dim: int, heads: int, mlp: int, act: str = "gelu_tanh", causal: bool = False):
         super().__init__()
-        self.heads = heads
+        if act not in VIT_ACTIVATIONS:
+            raise ValueError(f"unknown ViT activation {act!r}; expected one of {VIT_ACTIVATIONS}")
+        self.heads, self.act, self.causal = heads, act, causal
         self.n1, self.n2 = LayerNorm(dim), LayerNorm(dim)
         self.qkv, self.out = Linear(dim, 3 * dim), Linear(dim, dim)
         self.mlp = MLP(dim, mlp, act="gelu_tanh")
 
+    def _mlp(self, x):
+        if self.act == "gelu_tanh":
+            return self.mlp(x)
+        h = self.mlp.fc1(x)
+        h = h * torch.sigmoid(1.702 * h) if self.act == "quick_gelu" else F.gelu(h)
+        return self.mlp.fc2(h)
+
     def forward(self, x):
         q, k, v = self.qkv(self.n1(x)).chunk(3, dim=-1)
-        o = sdpa(*(split_heads(t.contiguous(), self.heads) for t in (q, k, v)))
+        o = sdpa(*(split_heads(t.contiguous(), self.heads) for t in (q, k, v)), causal=self.causal)
         x = x + self.out(merge_heads(o))
-        return x + self.mlp(self.n2(x))
+        return x + self._mlp(self.n2(x))
 
 
 class ViTScorer(nn.Module):
@@ -150,23 +166,24 @@ class ViTScorer(nn.Module):
         "vit_tiny": dict(layers=2, dim=32, heads=2, mlp=64, patch=8, image=32, out_dim=16),
     }
 
-    def __init__(self, layers=24, dim=1024, heads=16, mlp=4096, patch=14, image=224, out_dim=768):
+    def __init__(self, layers=24, dim=1024, heads=16, mlp=4096, patch=14, image=224, out_dim=768,
+                 act: str = "gelu_tanh"):
         super().__init__()
-        self.patch, self.image = patch, image
+        self.patch, self.image, self.act = patch, image, act
         n = (image // patch) ** 2
         self.patch_embed = Linear(3 * patch * patch, dim, bias=False)
         self.cls = nn.Parameter(torch.zeros(1, 1, dim))
         self.pos = nn.Parameter(torch.randn(1, n + 1, dim) * 0.02)
         self.pre_norm, self.post_norm = LayerNorm(dim), LayerNorm(dim)
-        self.blocks = nn.ModuleList(ViTBlock(dim, heads, mlp) for _ in range(layers))
+        self.blocks = nn.ModuleList(ViTBlock(dim, heads, mlp, act) for _ in range(layers))
         self.proj = Linear(dim, out_dim, bias=False)
         self.score_head = Linear(out_dim, 1)
         self.register_buffer("mean", torch.tensor([0.4815, 0.4578, 0.4082]).view(1, 3, 1, 1))
         self.register_buffer("std", torch.tensor([0.2686, 0.2613, 0.2758]).view(1, 3, 1, 1))
 
     @classmethod
-    def from_preset(cls, name: str) -> "ViTScorer":
-        return cls(**cls.PRESETS[name])
+    def from_preset(cls, name: str, act: str = "gelu_tanh") -> "ViTScorer":
+        return cls(**cls.PRESETS[name], act=act)
 
     def features(self, images01):
         """``images01[B,3,H,W]`` in ``[0,1]`` → L2-normalised features ``[B, out_dim]``."""
@@ -187,6 +204,39 @@ class ViTScorer(nn.Module):
 
     def forward(self, images01):
         return self.score_head(self.features(images01).to(self.score_head.weight.dtype)).float().squeeze(-1)
+
+
+class CLIPTextTower(nn.Module):
+    """Text side of a CLIP checkpoint: token + position embeddings, causal pre-norm blocks, final
+    norm, the state at the end-of-text token projected into the joint space and L2-normalised.
+    ``eos_token_id=None`` takes the position of the largest token id of each row (end-of-text is
+    the last entry of the CLIP vocabulary), otherwise the first occurrence of that id."""
+
+    def __init__(self, layers=12, dim=768, heads=12, mlp=3072, vocab=49408, context=77, out_dim=768,
+                 act: str = "quick_gelu", eos_token_id: int | None = None):
+        super().__init__()
+        self.context, self.eos_token_id = context, eos_token_id
+        self.token_embed = nn.Embedding(vocab, dim)
+        self.pos = nn.Parameter(torch.randn(context, dim) * 0.01)
+        self.blocks = nn.ModuleList(ViTBlock(dim, heads, mlp, act, causal=True) for _ in range(layers))
+        self.final_norm = LayerNorm(dim)
+        self.proj = Linear(dim, out_dim, bias=False)
+
+    def features(self, input_ids: torch.Tensor) -> torch.Tensor:
+        b, s = input_ids.shape
+        if s > self.context:
+            raise ValueError(f"{s} tokens exceed the tower's context of {self.context}")
+        dtype = self.proj.weight.dtype
+        x = (self.token_embed(input_ids) + self.pos[:s]).to(dtype)
+        for blk in self.blocks:
+            x = blk(x)
+        x = self.final_norm(x)
+        if self.eos_token_id is None:
+            last = input_ids.argmax(dim=-1)
+        else:
+            last = (input_ids == self.eos_token_id).int().argmax(dim=-1)
+        feat = self.proj(x[torch.arange(b, device=x.device), last]).float()
+        return feat / feat.norm(dim=-1, keepdim=True).clamp_min(1e-6)
 
 
 def _seed_from_text(text: str, salt: str = "") -> int:
