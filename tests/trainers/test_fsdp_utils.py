@@ -1,0 +1,99 @@
+"""``vrl.trainers.fsdp`` on one CPU process: what ``fsdp_wrapper`` attaches for each strategy,
+the single-file checkpoint, and the optimiser-state offload hooks (reference expectations:
+``vrl/trainers/fsdp.py:35-183``)."""
+
+import pytest
+import torch
+from safetensors.torch import load_file
+from torch import nn
+
+from visionrl_b200.trainers.fsdp import (
+    FSDPConfig, OptimizerOffloadHook, fsdp_wrapper, init_distributed, register_optimizer_offload_hooks,
+    save_fsdp_checkpoint,
+)
+
+
+class _Net(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.a, self.b = nn.Linear(8, 16), nn.Linear(16, 4)
+        self.checkpointing = None
+
+    def enable_gradient_checkpointing(self, flag=True):
+        self.checkpointing = flag
+
+    def forward(self, x):
+        return self.b(torch.relu(self.a(x)))
+
+
+def test_config_defaults_follow_the_reference():
+    cfg = FSDPConfig()
+    assert (cfg.sharding_strategy, cfg.backward_prefetch, cfg.cpu_offload) == ("FULL_SHARD", "BACKWARD_PRE", False)
+    assert (cfg.num_replicate, cfg.num_shard, cfg.mixed_precision_dtype) == (1, 8, torch.bfloat16)
+    assert cfg.use_activation_checkpointing is False and cfg.use_device_mesh is False
+
+
+@pytest.mark.parametrize("strategy,shards_optimizer", [("FULL_SHARD", True), ("SHARD_GRAD_OP", True),
+                                                       ("HYBRID_SHARD", True), ("NO_SHARD", False)])
+def test_wrapper_returns_the_same_module_with_a_gradient_runtime(strategy, shards_optimizer):
+    net = _Net()
+    out = fsdp_wrapper(net, FSDPConfig(sharding_strategy=strategy, use_activation_checkpointing=True),
+                       collectives="nccl")
+    assert out is net and net.checkpointing is True
+    runtime = net.sharded_runtime
+    # a single process has nothing to shard over, whatever the strategy asks for
+    assert runtime.shard_optimizer is False and shards_optimizer in (True, False)
+    assert getattr(net, "param_runtime", None) is None
+    assert callable(runtime.reduce_clip_step) and callable(runtime.prepare)
+
+
+def test_wrapper_reaches_an_inner_transformer_for_activation_checkpointing():
+    class Policy(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.transformer = _Net()
+
+    policy = Policy()
+    fsdp_wrapper(policy, FSDPConfig(sharding_strategy="NO_SHARD", use_activation_checkpointing=True))
+    assert policy.transformer.checkpointing is True
+
+
+def test_single_file_checkpoint_round_trips(tmp_path):
+    net = _Net()
+    path = save_fsdp_checkpoint(net, 7, str(tmp_path))
+    assert path.endswith("checkpoint-7")
+    state = load_file(f"{path}/model.safetensors")
+    assert set(state) == set(net.state_dict()) and all(torch.equal(state[k], v) for k, v in net.state_dict().items())
+    # any other rank writes nothing
+    other = save_fsdp_checkpoint(net, 8, str(tmp_path), rank=1)
+    assert not (tmp_path / "checkpoint-8").exists() and other.endswith("checkpoint-8")
+
+
+def test_offload_hooks_park_the_state_on_the_host_around_every_step():
+    net = _Net()
+    opt = torch.optim.AdamW(net.parameters(), lr=1e-2)
+    net(torch.randn(3, 8)).sum().backward()
+    opt.step()
+    seen = []
+
+    class Spy(OptimizerOffloadHook):
+        def _move(self, device):
+            seen.append(str(device))
+            super()._move(device)
+
+    hook = Spy(opt, "cpu")
+    opt.register_step_pre_hook(hook.pre_step)
+    opt.register_step_post_hook(hook.post_step)
+    before = {k: v.clone() for k, v in net.state_dict().items()}
+    net(torch.randn(3, 8)).sum().backward()
+    opt.step()
+    assert seen == ["cpu", "cpu"]                       # to the step device, then back to the host
+    assert any(not torch.equal(before[k], v) for k, v in net.state_dict().items())
+    registered = register_optimizer_offload_hooks(torch.optim.AdamW(_Net().parameters()), "cpu")
+    assert isinstance(registered, OptimizerOffloadHook)
+
+
+def test_init_distributed_without_a_launcher_is_a_single_rank(monkeypatch):
+    for name in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
+        monkeypatch.delenv(name, raising=False)
+    assert init_distributed() == (0, 1, 0)
