@@ -184,6 +184,35 @@ def clip_vision_shape(state: Mapping[str, torch.Tensor]) -> dict[str, int]:
             "patch": patch, "image": patch * grid, "out_dim": int(state["proj.weight"].shape[0])}
 
 
+def t5_encoder_from_hf(state: Mapping[str, torch.Tensor]) -> dict[str, torch.Tensor]:
+    """State dict of ``T5Encoder`` from a Hugging Face ``T5EncoderModel`` / ``UMT5EncoderModel``
+    state dict (gated or plain feed-forward, shared or per-layer position bias)."""
+    if "encoder.block.0.layer.0.SelfAttention.q.weight" not in state:
+        raise KeyError("no T5 encoder found (encoder.block.0.layer.0.SelfAttention.q.weight)")
+    embed = state.get("shared.weight", state.get("encoder.embed_tokens.weight"))
+    if embed is None:
+        raise KeyError("the T5 checkpoint has no token embedding (shared.weight)")
+    out: dict[str, torch.Tensor] = {"embed.weight": embed, "final_norm.weight": state["encoder.final_layer_norm.weight"]}
+    layer = 0
+    while f"encoder.block.{layer}.layer.0.SelfAttention.q.weight" in state:
+        p, q = f"encoder.block.{layer}.layer.", f"blocks.{layer}."
+        for n in "qkvo":
+            out[q + f"{n}.weight"] = state[p + f"0.SelfAttention.{n}.weight"]
+        bias = p + "0.SelfAttention.relative_attention_bias.weight"
+        if bias in state:
+            out[q + "rel_bias.weight"] = state[bias]
+        out[q + "attn_norm.weight"] = state[p + "0.layer_norm.weight"]
+        out[q + "ff_norm.weight"] = state[p + "1.layer_norm.weight"]
+        if p + "1.DenseReluDense.wi_0.weight" in state:
+            out[q + "wi_0.weight"] = state[p + "1.DenseReluDense.wi_0.weight"]
+            out[q + "wi_1.weight"] = state[p + "1.DenseReluDense.wi_1.weight"]
+        else:
+            out[q + "wi_0.weight"] = state[p + "1.DenseReluDense.wi.weight"]
+        out[q + "wo.weight"] = state[p + "1.DenseReluDense.wo.weight"]
+        layer += 1
+    return {k: v.contiguous() for k, v in out.items()}
+
+
 def _load_dir(path: str) -> dict[str, torch.Tensor]:
     from safetensors.torch import load_file
 
