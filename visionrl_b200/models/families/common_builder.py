@@ -44,6 +44,10 @@ def extract_diffusion_runtime_spec(cfg: Any, device: Any, weight_dtype: Any, *,
     }
     if _get(model, "shift") is not None:
         native["shift"] = float(model.shift)
+    text_encoder = _get(model, "text_encoder")
+    if text_encoder is not None and _get(text_encoder, "path"):
+        # a local pipeline directory (text_encoder*/ + tokenizer*/): real prompt conditioning
+        native["text_encoder_path"] = str(_get(text_encoder, "path"))
     return RuntimeBuildSpec(
         model_name_or_path=str(_get(model, "path", "")), device=device, dtype=weight_dtype,
         backend_preference=(str(_get(model, "backend", "native") or "native"),), task_variant=task_variant,

@@ -37,6 +37,17 @@ class CosmosPredict2Policy(NativeFlowPolicy):
         self.sequence_parallel = None
 
     @classmethod
+    def _build_prompt_encoder(cls, path: str, arch: dict[str, Any], device):
+        from visionrl_b200.models.nn.prompt_encoders import UMT5PromptEncoder
+
+        encoder = UMT5PromptEncoder.from_directory(path, device)
+        width = int(WanConfig.from_dict(arch).text_dim)
+        if encoder.context_dim != width:
+            raise ValueError(f"the text encoder is {encoder.context_dim} wide, the transformer expects "
+                             f"{width} (model.arch.text_dim)")
+        return encoder
+
+    @classmethod
     def _build_modules(cls, arch: dict[str, Any], native: dict[str, Any]):
         arch = dict(arch)
         arch["extra_in_channels"] = 1

@@ -135,6 +135,8 @@ class NativeFlowPolicy(DiffusionPolicy):
                 seeded_init(transformer, seed)
         if not native.get("random_init", True):
             cls._load_native_checkpoint(transformer, spec.model_name_or_path)
+        if native.get("text_encoder_path"):
+            text = cls._build_prompt_encoder(str(native["text_encoder_path"]), arch, device)
         transformer.to(device=device, dtype=dtype)
         if decoder is not None:
             decoder.to(device=device, dtype=dtype if device.type == "cuda" else torch.float32)
@@ -162,6 +164,12 @@ class NativeFlowPolicy(DiffusionPolicy):
     @classmethod
     def _build_modules(cls, arch: dict[str, Any], native: dict[str, Any]):
         raise NotImplementedError
+
+    @classmethod
+    def _build_prompt_encoder(cls, path: str, arch: dict[str, Any], device: torch.device):
+        """The real text side from a local pipeline directory (``model.text_encoder.path``),
+        replacing the seeded stand-in ``_build_modules`` returned."""
+        raise NotImplementedError(f"{cls.__name__} has no checkpoint-backed prompt encoder")
 
     def _call_transformer(self, latents, timesteps, embeds, pooled, state):
         raise NotImplementedError

@@ -30,11 +30,29 @@ class SD3_5Policy(NativeFlowPolicy):
                                       int(dec.get("blocks", 2)))
         return transformer, decoder, SyntheticTextEncoder(cfg.context_dim, cfg.pooled_dim)
 
+    @classmethod
+    def _build_prompt_encoder(cls, path: str, arch: dict[str, Any], device):
+        from visionrl_b200.models.nn.prompt_encoders import SD3PromptEncoder
+
+        cfg = MMDiTConfig.from_dict(arch)
+        encoder = SD3PromptEncoder.from_directory(path, cfg.context_dim, device)
+        if encoder.pooled_dim != cfg.pooled_dim:
+            raise ValueError(f"the CLIP towers pool to {encoder.pooled_dim} values, the transformer expects "
+                             f"{cfg.pooled_dim} (model.arch.pooled_dim)")
+        return encoder
+
     def _context_tokens(self, max_sequence_length: int) -> int:
         # two 77-token CLIP segments are concatenated in front of the T5 tokens; a
         # fixed ``context_len`` in the arch overrides it (tiny models)
         fixed = self.arch.get("context_len")
-        return int(fixed) if fixed else max_sequence_length
+        if fixed:
+            return int(fixed)
+        from visionrl_b200.models.nn.prompt_encoders import CLIP_TOKENS, SD3PromptEncoder
+
+        if isinstance(self._frozen.text, SD3PromptEncoder):
+            # the public pipeline's meaning: CLIP tokens first, then max_sequence_length T5 tokens
+            return CLIP_TOKENS + max_sequence_length
+        return max_sequence_length
 
     def _call_transformer(self, latents, timesteps, embeds, pooled, state):
         return self.transformer(latents, timesteps, embeds, pooled)

@@ -24,6 +24,17 @@ class WanT2VDiffusersPolicy(NativeFlowPolicy):
         self.sequence_parallel = None     # set by parallel.ulysses.attach_sequence_parallel
 
     @classmethod
+    def _build_prompt_encoder(cls, path: str, arch: dict[str, Any], device):
+        from visionrl_b200.models.nn.prompt_encoders import UMT5PromptEncoder
+
+        encoder = UMT5PromptEncoder.from_directory(path, device)
+        width = int(WanConfig.from_dict(arch).text_dim)
+        if encoder.context_dim != width:
+            raise ValueError(f"the text encoder is {encoder.context_dim} wide, the transformer expects "
+                             f"{width} (model.arch.text_dim)")
+        return encoder
+
+    @classmethod
     def _build_modules(cls, arch: dict[str, Any], native: dict[str, Any]):
         cfg = WanConfig.from_dict(arch)
         dec = dict(native.get("decoder") or {})

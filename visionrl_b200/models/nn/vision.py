@@ -222,20 +222,29 @@ class CLIPTextTower(nn.Module):
         self.final_norm = LayerNorm(dim)
         self.proj = Linear(dim, out_dim, bias=False)
 
-    def features(self, input_ids: torch.Tensor) -> torch.Tensor:
+    def encode(self, input_ids: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+        """``(penultimate, pooled)``: the output of the second-to-last block ``[B, S, dim]`` (what
+        diffusion pipelines condition on) and the projected end-of-text state ``[B, out_dim]``,
+        not normalised."""
         b, s = input_ids.shape
         if s > self.context:
             raise ValueError(f"{s} tokens exceed the tower's context of {self.context}")
         dtype = self.proj.weight.dtype
         x = (self.token_embed(input_ids) + self.pos[:s]).to(dtype)
-        for blk in self.blocks:
+        penultimate = x
+        for i, blk in enumerate(self.blocks):
+            if i == len(self.blocks) - 1:
+                penultimate = x
             x = blk(x)
         x = self.final_norm(x)
         if self.eos_token_id is None:
             last = input_ids.argmax(dim=-1)
         else:
             last = (input_ids == self.eos_token_id).int().argmax(dim=-1)
-        feat = self.proj(x[torch.arange(b, device=x.device), last]).float()
+        return penultimate, self.proj(x[torch.arange(b, device=x.device), last])
+
+    def features(self, input_ids: torch.Tensor) -> torch.Tensor:
+        feat = self.encode(input_ids)[1].float()
         return feat / feat.norm(dim=-1, keepdim=True).clamp_min(1e-6)
 
 
