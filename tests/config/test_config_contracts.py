@@ -80,3 +80,40 @@ def test_dpo_accepts_an_explicit_null_sample_cap_but_needs_a_step_budget():
     del cfg.trainer["max_train_steps"]
     with pytest.raises(ValueError, match=r"trainer\.max_train_steps"):
         validate_training_config(cfg)
+
+
+EXPECTED_PATHS = {
+    "cosmos_predict2_2b_grpo": ("datasets/drawbench/train_192.txt", "outputs/cosmos_pred2_2b_grpo"),
+    "janus_pro_1b_grpo": ("datasets/janus/prompts.txt", "outputs/janus_pro_1b_grpo"),
+    "janus_pro_1b_ocr_grpo": ("datasets/ocr/train.txt", "outputs/janus_pro_1b_ocr_grpo"),
+    "nextstep_1_ocr_grpo": ("datasets/ocr/train.txt", "outputs/nextstep_1_ocr_grpo"),
+    "sd3_5_ocr_grpo": ("datasets/ocr/train.txt", "outputs/sd3_5_ocr_grpo"),
+    "wan_2_1_14b_grpo": ("datasets/wan/prompts.txt", "outputs/wan_14b_grpo"),
+    "wan_2_1_1_3b_dpo": (None, "outputs/wan_1_3b_dpo"),
+    "wan_2_1_1_3b_grpo": ("datasets/wan/prompts.txt", "outputs/wan_1_3b_grpo"),
+    "wan_2_1_1_3b_multi_reward_grpo": ("datasets/wan/prompts.txt", "outputs/wan_1_3b_multi_reward_grpo"),
+    "wan_2_1_1_3b_ocr_grpo": ("datasets/ocr/train.txt", "outputs/wan_1_3b_ocr_grpo"),
+}
+
+
+@pytest.mark.parametrize("name", sorted(EXPECTED_PATHS))
+def test_experiments_name_the_manifest_and_output_directory_of_their_recipe(name):
+    cfg = load_config(f"experiment/{name}")
+    manifest, out = EXPECTED_PATHS[name]
+    data = cfg.get("data")
+    assert (data.get("manifest") if data is not None else None) == manifest
+    assert cfg.trainer.output_dir == out
+
+
+def test_every_experiment_has_a_plain_output_directory_and_a_textual_manifest():
+    import re
+    from pathlib import Path
+
+    from visionrl_b200.config.loader import CONFIGS_ROOT
+
+    for file in sorted(Path(CONFIGS_ROOT, "experiment").glob("*.yaml")):
+        cfg = load_config(f"experiment/{file.stem}")
+        assert re.fullmatch(r"outputs/\w+", str(cfg.trainer.output_dir)), file.stem
+        manifest = cfg.get("data").get("manifest") if cfg.get("data") is not None else None
+        assert manifest is None or (isinstance(manifest, str) and re.fullmatch(r"(synthetic:\d+(:\d+)?|[\w./-]+\.(txt|jsonl))",
+                                                                               manifest)), (file.stem, manifest)
