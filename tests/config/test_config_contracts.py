@@ -117,3 +117,25 @@ def test_every_experiment_has_a_plain_output_directory_and_a_textual_manifest():
         manifest = cfg.get("data").get("manifest") if cfg.get("data") is not None else None
         assert manifest is None or (isinstance(manifest, str) and re.fullmatch(r"(synthetic:\d+(:\d+)?|[\w./-]+\.(txt|jsonl))",
                                                                                manifest)), (file.stem, manifest)
+
+
+def test_shipped_manifests_exist_and_parse():
+    from pathlib import Path
+
+    from visionrl_b200.config.loader import CONFIGS_ROOT
+    from visionrl_b200.trainers.data import load_prompt_manifest
+
+    repo = Path(CONFIGS_ROOT).parent
+    not_shipped = {"datasets/drawbench/train_192.txt"}            # a published prompt set, see datasets/README.md
+    seen = set()
+    for file in sorted(Path(CONFIGS_ROOT, "experiment").glob("*.yaml")):
+        data = load_config(f"experiment/{file.stem}").get("data")
+        manifest = data.get("manifest") if data is not None else None
+        if manifest is None or manifest.startswith("synthetic:") or manifest in not_shipped:
+            continue
+        seen.add(manifest)
+        examples = load_prompt_manifest(repo / manifest)
+        assert len(examples) >= 32 and all(e.prompt for e in examples), manifest
+        if "/ocr/" in manifest:
+            assert all(e.target_text and e.target_text in e.prompt for e in examples)
+    assert seen == {"datasets/ocr/train.txt", "datasets/wan/prompts.txt", "datasets/janus/prompts.txt"}
