@@ -64,19 +64,22 @@ def test_hsdp_gloo_world4_matches_replicated():
 
 
 @pytest.mark.timeout(600)
-@pytest.mark.parametrize("sp", [2, 1])
-def test_wan_recipe_on_two_cpu_ranks_sharded_with_and_without_sequence_parallelism(tmp_path, sp):
-    """Public entry point, two gloo ranks: DP=1 x SP=2 and DP=2 x SP=1, block weights sharded over both;
-    train one epoch, checkpoint (rank 0 writes, every rank joins the gathers), resume for another."""
+@pytest.mark.parametrize("world,sp", [(2, 2), (2, 1), (4, 2)])
+def test_wan_recipe_on_cpu_ranks_sharded_with_and_without_sequence_parallelism(tmp_path, world, sp):
+    """Public entry point on gloo ranks: DP=1 x SP=2, DP=2 x SP=1 and DP=2 x SP=2, block weights sharded
+    over all ranks; train one epoch, checkpoint (rank 0 writes, every rank joins the gathers), resume for
+    another.  The first replay reproduces the rollout on every mesh: nothing is clipped."""
     import math
 
-    res = _run(_workers.wan_recipe_runs_sharded_and_sequence_parallel, 2, sp, str(tmp_path / f"run_sp{sp}"),
+    res = _run(_workers.wan_recipe_runs_sharded_and_sequence_parallel, world, sp, str(tmp_path / f"run_sp{sp}"),
                _free_port(), timeout=500)
     rows, perf = res["rows"], res["perf"]
     assert rows[0][0] == "epoch" and [r[0] for r in rows[1:]] == ["0", "1"]     # one epoch, then one more after resume
     assert all(math.isfinite(float(v)) for r in rows[1:] for v in r[1:10])
-    assert len(perf) == 2 and all(p["n_ranks"] == 2 and p["step_ms"] > 0 for p in perf)
-    assert perf[0]["samples"] == 2 * max(1, 2 // sp)                 # group of 2 per prompt, one prompt per DP rank
+    assert len(perf) == 2 and all(p["n_ranks"] == world and p["step_ms"] > 0 for p in perf)
+    assert perf[0]["samples"] == 2 * max(1, world // sp)             # group of 2 per prompt, one prompt per DP rank
+    first = dict(zip(rows[0], rows[1]))
+    assert float(first["clip_fraction"]) == 0.0 and float(first["approx_kl"]) < 1e-9
 
 
 TINY_JANUS = [
