@@ -1,25 +1,16 @@
 """Launcher / worker / executor names of the reference's Ray layer
 (``vrl/distributed/ray/__init__.py:22-39``), served by in-process workers."""
 
-from visionrl_b200.distributed.ray.placement.group import (
-    RolloutPlacementGroup as RayPlacement, create_rollout_placement_group,
-)
+from visionrl_b200.distributed.ray.placement.group import RayPlacement, create_rollout_placement_group
 from visionrl_b200.distributed.ray.rollout.executor import DistributedRolloutExecutor
-from visionrl_b200.distributed.ray.rollout.launcher import RayRolloutLauncher
+from visionrl_b200.distributed.ray.rollout.launcher import RayRolloutLauncher, launch_ray_rollout_runtime
 from visionrl_b200.distributed.ray.rollout.planner import DeviceAssignment, DistributedExecutionPlanner
 from visionrl_b200.distributed.ray.rollout.runtime import RayDistributedRuntime
 from visionrl_b200.distributed.ray.rollout.types import RayChunkResult, RayWorkerHandle
-from visionrl_b200.distributed.ray.rollout.weight_sync import RayRolloutWeightSync
+from visionrl_b200.distributed.ray.rollout.weight_sync import RayRolloutWeightSync, RolloutWeightSync
 from visionrl_b200.distributed.ray.rollout.worker import RayRolloutWorker
 from visionrl_b200.distributed.ray.train.actor import RayTrainActor
 from visionrl_b200.distributed.ray.train.group import RayTrainGroup, RayTrainRankSpec
-
-RolloutWeightSync = RayRolloutWeightSync
-
-
-def launch_ray_rollout_runtime(config, runtime_spec, gatherer):
-    return RayRolloutLauncher().launch(config, runtime_spec, gatherer)
-
 
 __all__ = [
     "DeviceAssignment", "DistributedExecutionPlanner", "DistributedRolloutExecutor",

@@ -30,6 +30,10 @@ class RolloutPlacementGroup:
         self.bundles = []
 
 
+# the name the reference's launcher and tests use for the placement record
+RayPlacement = RolloutPlacementGroup
+
+
 def create_rollout_placement_group(num_workers: int, *, gpus_per_worker: float = 1.0,
                                    cpus_per_worker: float = 1.0,
                                    strategy: str = "SPREAD") -> RolloutPlacementGroup:

@@ -13,3 +13,9 @@ def ip_sort_key(ip: str) -> tuple:
 
 def bundle_sort_key(ip: str, gpu_id: int | None, index: int) -> tuple:
     return (ip_sort_key(ip), -1 if gpu_id is None else int(gpu_id), int(index))
+
+
+def sort_node_gpu_key(item: tuple) -> tuple:
+    """The same ordering for an ``(index, node, gpu_id)`` triple, the form placement code sorts."""
+    index, node, gpu_id = item
+    return bundle_sort_key(str(node), None if gpu_id is None or int(gpu_id) < 0 else int(gpu_id), int(index))

@@ -49,4 +49,10 @@ class RayRolloutLauncher:
         return RayDistributedRuntime(executor, handles, sync, pg, spec.policy_version)
 
 
-__all__ = ["RayRolloutLauncher"]
+def launch_ray_rollout_runtime(config: Any, runtime_spec: Any, gatherer: Any, **_ignored: Any) -> RayDistributedRuntime:
+    """Function form of :meth:`RayRolloutLauncher.launch`.  ``init_ray`` / ``ray_init_kwargs`` of the
+    reference's signature are accepted and ignored: the workers live in this process."""
+    return RayRolloutLauncher().launch(config, runtime_spec, gatherer)
+
+
+__all__ = ["RayRolloutLauncher", "launch_ray_rollout_runtime"]

@@ -4,9 +4,15 @@
 from __future__ import annotations
 
 import asyncio
-from typing import Any
+from typing import Any, Protocol
 
 from visionrl_b200.distributed.ray.rollout.types import RayWorkerHandle
+
+
+class RolloutWeightSync(Protocol):
+    """What a runtime needs from its weight channel: push a trainable state with its version."""
+
+    async def push_to_rollout_workers(self, state_ref: Any, policy_version: int) -> None: ...
 
 
 class RayRolloutWeightSync:
@@ -28,4 +34,4 @@ class RayRolloutWeightSync:
             await asyncio.to_thread(require_ray().get, refs)
 
 
-__all__ = ["RayRolloutWeightSync"]
+__all__ = ["RayRolloutWeightSync", "RolloutWeightSync"]

@@ -155,4 +155,6 @@ class CosmosPredict2Policy(NativeFlowPolicy):
         return self.forward(state, timestep_idx)
 
 
-__all__ = ["CosmosPredict2Policy", "CosmosSamplingState"]
+CosmosPredict2SamplingState = CosmosSamplingState
+
+__all__ = ["CosmosPredict2Policy", "CosmosPredict2SamplingState", "CosmosSamplingState"]

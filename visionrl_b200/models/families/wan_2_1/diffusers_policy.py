@@ -54,4 +54,6 @@ class WanT2VDiffusersPolicy(NativeFlowPolicy):
         return self.transformer(latents, timesteps, embeds, sp=self.sequence_parallel)
 
 
-__all__ = ["WanSamplingState", "WanT2VDiffusersPolicy"]
+WanT2VSamplingState = WanSamplingState
+
+__all__ = ["WanSamplingState", "WanT2VDiffusersPolicy", "WanT2VSamplingState"]

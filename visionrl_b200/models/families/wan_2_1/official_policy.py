@@ -18,7 +18,7 @@ from typing import Any
 
 import torch
 
-from visionrl_b200.models.families.wan_2_1.diffusers_policy import WanT2VDiffusersPolicy
+from visionrl_b200.models.families.wan_2_1.diffusers_policy import WanSamplingState, WanT2VDiffusersPolicy
 
 
 class WanT2VOfficialPolicy(WanT2VDiffusersPolicy):
@@ -119,4 +119,6 @@ class WanT2VOfficialPolicy(WanT2VDiffusersPolicy):
         raise NotImplementedError("the two-expert Wan variant is rollout-only (no replay path)")
 
 
-__all__ = ["WanT2VOfficialPolicy"]
+WanT2VOfficialSamplingState = WanSamplingState
+
+__all__ = ["WanT2VOfficialPolicy", "WanT2VOfficialSamplingState"]
