@@ -209,3 +209,41 @@ def test_run_awaitable_works_with_and_without_a_running_loop():
 
     with pytest.raises(KeyError):
         asyncio.new_event_loop().run_until_complete(inside_boom())
+
+
+def test_placement_record_and_call_shapes_of_the_reference():
+    from visionrl_b200.distributed.ray.placement import RayPlacement, create_rollout_placement_group, sort_node_gpu_key
+    from visionrl_b200.rollouts.runtime.config import RolloutBackendConfig
+
+    cfg = RolloutBackendConfig.from_cfg({"backend": "ray", "num_workers": 3, "gpus_per_worker": 0, "cpus_per_worker": 2,
+                                         "placement_strategy": "PACK"})
+    placement = create_rollout_placement_group(cfg)
+    assert isinstance(placement, RayPlacement) and placement.strategy == "PACK"
+    assert placement.ordered_bundle_indices == [0, 1, 2] and placement.placement_group is not None
+    assert all(b.resources == {"CPU": 2.0} for b in placement.bundles)
+    assert create_rollout_placement_group(config=2, gpus_per_worker=0).ordered_bundle_indices == [0, 1]
+    placement.remove()
+    assert placement.placement_group is None and placement.ordered_bundle_indices == []
+    # (index, node, gpu): by node address, then GPU, then index; names that are not addresses sort after
+    items = [(0, "10.0.0.9", 1), (1, "10.0.0.10", 0), (2, "10.0.0.9", 0), (3, "nodeb", 0)]
+    assert [i for i, _, _ in sorted(items, key=sort_node_gpu_key)] == [2, 0, 1, 3]
+
+
+def test_runtime_launcher_and_train_group_take_the_reference_keywords():
+    from visionrl_b200.distributed.ray import (
+        RayDistributedRuntime, RayRolloutLauncher, RayTrainGroup, RayTrainRankSpec, RolloutWeightSync,
+    )
+
+    class _Executor:
+        async def execute(self, request):
+            return request
+
+    runtime = RayDistributedRuntime(_Executor(), weight_sync=None, owned_workers=[], placement_group=None)
+    assert runtime.workers == [] and runtime.current_policy_version is None
+    launcher = RayRolloutLauncher(init_ray=False, ray_init_kwargs={"num_cpus": 2})
+    assert launcher.init_ray is False and launcher.ray_init_kwargs == {"num_cpus": 2}
+    spec = RayTrainRankSpec(rank=1, local_rank=1, world_size=2, node_id="n0", gpu_ids=(1,))
+    assert (spec.rank, spec.local_rank, spec.world_size, spec.node_id) == (1, 1, 2, "n0")
+    group = RayTrainGroup(["first", "second"])
+    assert group.primary() == "first"
+    assert hasattr(RolloutWeightSync, "push_to_rollout_workers")

@@ -140,3 +140,33 @@ def test_aesthetic_head_weights_are_resolved_from_path_env_or_assets(tmp_path, m
     except Exception:      # noqa: BLE001 - the image tower needs weights that are not available offline
         return
     assert torch.allclose(reward._mlp.layers[0].weight, torch.full_like(reward._mlp.layers[0].weight, 0.01))
+
+
+def test_reward_constructors_take_the_reference_argument_order(tmp_path):
+    """Positional calls written against the reference keep working: ``(device, dtype, model_name)``
+    for the aesthetic and preference scorers, ``(device, model_name)`` for CLIP-score,
+    ``(url, timeout)`` for the remote one, ``(device, debug_dir)`` for OCR."""
+    from visionrl_b200.rewards.aesthetic import AestheticReward
+    from visionrl_b200.rewards.clip import CLIPScoreReward
+    from visionrl_b200.rewards.ocr import OCRReward
+    from visionrl_b200.rewards.pickscore import PickScoreReward
+    from visionrl_b200.rewards.remote import RemoteReward
+    from visionrl_b200.rewards.vision_tower import tower_dtype
+
+    aesthetic = AestheticReward("cpu", "float32", "random:vit_tiny")
+    assert (aesthetic._device, aesthetic._dtype, aesthetic.model_name) == ("cpu", "float32", "random:vit_tiny")
+    clip = CLIPScoreReward("cpu", "random:vit_tiny")
+    assert clip.model_name == "random:vit_tiny" and clip._dtype is None
+    pick = PickScoreReward("cpu", "bfloat16", "some/processor", "random:vit_tiny")
+    assert (pick._dtype, pick.processor_name, pick.model_name) == ("bfloat16", "some/processor", "random:vit_tiny")
+    assert RemoteReward("http://x/score", 5.0).timeout_s == 5.0 and RemoteReward("http://x/score").timeout_s == 60.0
+    ocr = OCRReward("cpu", str(tmp_path / "dbg"))
+    assert ocr._debug_dir == tmp_path / "dbg" and ocr._debug_dir.is_dir()
+    # the dtype string is honoured by the tower that gets built
+    score = aesthetic.score_tensor_batch(torch.rand(1, 3, 32, 32), ["p"]) if hasattr(aesthetic, "score_tensor_batch") else None
+    assert aesthetic._tower is None or aesthetic._tower.proj.weight.dtype == torch.float32
+    del score
+    assert tower_dtype("bf16", torch.device("cpu")) == torch.bfloat16
+    assert tower_dtype(None, torch.device("cpu")) == torch.float32
+    with pytest.raises(ValueError):
+        tower_dtype("int8", torch.device("cpu"))

@@ -58,14 +58,38 @@ def test_wrapper_reaches_an_inner_transformer_for_activation_checkpointing():
     assert policy.transformer.checkpointing is True
 
 
+def test_sharding_units_follow_the_layer_classes_and_skip_ignored_modules():
+    from visionrl_b200.trainers.fsdp import sharding_units
+
+    class Block(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.fc = nn.Linear(4, 4)
+
+    class Model(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.blocks = nn.ModuleList(Block() for _ in range(3))
+            self.frozen = nn.ModuleList(Block() for _ in range(2))
+
+    model = Model()
+    assert sharding_units(model) is None                                   # the model's own block list
+    assert len(sharding_units(model, lambda: [Block])) == 5
+    kept = sharding_units(model, lambda: [Block], ignored_modules=[model.frozen])
+    assert len(kept) == 3 and all(any(k is b for b in model.blocks) for k in kept)
+    assert len(sharding_units(model, None, ignored_modules=[model.blocks[0]])) == 2
+    # the reference's positional call shape
+    assert fsdp_wrapper(model, FSDPConfig(sharding_strategy="NO_SHARD"), lambda: [Block], [model.frozen]) is model
+
+
 def test_single_file_checkpoint_round_trips(tmp_path):
     net = _Net()
-    path = save_fsdp_checkpoint(net, 7, str(tmp_path))
+    path = save_fsdp_checkpoint(str(tmp_path), net, 7)
     assert path.endswith("checkpoint-7")
     state = load_file(f"{path}/model.safetensors")
     assert set(state) == set(net.state_dict()) and all(torch.equal(state[k], v) for k, v in net.state_dict().items())
     # any other rank writes nothing
-    other = save_fsdp_checkpoint(net, 8, str(tmp_path), rank=1)
+    other = save_fsdp_checkpoint(str(tmp_path), net, 8, 1)
     assert not (tmp_path / "checkpoint-8").exists() and other.endswith("checkpoint-8")
 
 

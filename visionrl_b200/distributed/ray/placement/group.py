@@ -29,14 +29,36 @@ class RolloutPlacementGroup:
         self.handle = None
         self.bundles = []
 
+    # the two fields of the reference's ``RayPlacement`` record, as views of this one
+    @property
+    def placement_group(self) -> Any:
+        return self.handle
+
+    @property
+    def ordered_bundle_indices(self) -> list[int]:
+        return [b.index for b in self.bundles]
+
 
 # the name the reference's launcher and tests use for the placement record
 RayPlacement = RolloutPlacementGroup
 
 
-def create_rollout_placement_group(num_workers: int, *, gpus_per_worker: float = 1.0,
-                                   cpus_per_worker: float = 1.0,
-                                   strategy: str = "SPREAD") -> RolloutPlacementGroup:
+def create_rollout_placement_group(config: Any, *, gpus_per_worker: float | None = None,
+                                   cpus_per_worker: float | None = None,
+                                   strategy: str | None = None) -> RolloutPlacementGroup:
+    """One bundle per worker, in stable (node, GPU, index) order.  ``config`` is a rollout backend
+    config carrying ``num_workers``, ``gpus_per_worker``, ``cpus_per_worker`` and
+    ``placement_strategy`` (the reference's call shape), or just the worker count."""
+    num_workers = config
+    if not isinstance(config, int):
+        pick = (lambda k, d: config.get(k, d)) if isinstance(config, dict) else (lambda k, d: getattr(config, k, d))
+        num_workers = int(pick("num_workers", 1))
+        gpus_per_worker = float(pick("gpus_per_worker", 1.0)) if gpus_per_worker is None else gpus_per_worker
+        cpus_per_worker = float(pick("cpus_per_worker", 1.0)) if cpus_per_worker is None else cpus_per_worker
+        strategy = str(pick("placement_strategy", "SPREAD")) if strategy is None else strategy
+    gpus_per_worker = 1.0 if gpus_per_worker is None else gpus_per_worker
+    cpus_per_worker = 1.0 if cpus_per_worker is None else cpus_per_worker
+    strategy = "SPREAD" if strategy is None else strategy
     if num_workers < 1:
         raise ValueError("num_workers must be >= 1")
     ip = current_node_ip()

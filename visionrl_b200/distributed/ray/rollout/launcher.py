@@ -21,6 +21,10 @@ from visionrl_b200.rollouts.runtime.config import RolloutBackendConfig
 class RayRolloutLauncher:
     worker_cls = RayRolloutWorker
 
+    def __init__(self, init_ray: bool = True, ray_init_kwargs: dict[str, Any] | None = None) -> None:
+        # kept for the reference's constructor; nothing is initialised, the workers are in-process
+        self.init_ray, self.ray_init_kwargs = bool(init_ray), dict(ray_init_kwargs or {})
+
     def launch(self, config: Any, runtime_spec: Any, gatherer: Any) -> RayDistributedRuntime:
         cfg = RolloutBackendConfig.from_cfg(config)
         spec = GenerationRuntimeSpec.from_value(runtime_spec)
@@ -49,10 +53,10 @@ class RayRolloutLauncher:
         return RayDistributedRuntime(executor, handles, sync, pg, spec.policy_version)
 
 
-def launch_ray_rollout_runtime(config: Any, runtime_spec: Any, gatherer: Any, **_ignored: Any) -> RayDistributedRuntime:
-    """Function form of :meth:`RayRolloutLauncher.launch`.  ``init_ray`` / ``ray_init_kwargs`` of the
-    reference's signature are accepted and ignored: the workers live in this process."""
-    return RayRolloutLauncher().launch(config, runtime_spec, gatherer)
+def launch_ray_rollout_runtime(config: Any, runtime_spec: Any, gatherer: Any, *, init_ray: bool = True,
+                               ray_init_kwargs: dict[str, Any] | None = None) -> RayDistributedRuntime:
+    """Function form of :meth:`RayRolloutLauncher.launch`."""
+    return RayRolloutLauncher(init_ray, ray_init_kwargs).launch(config, runtime_spec, gatherer)
 
 
 __all__ = ["RayRolloutLauncher", "launch_ray_rollout_runtime"]

@@ -12,10 +12,13 @@ from visionrl_b200.engine.core.types import GenerationRequest, OutputBatch
 
 
 class RayDistributedRuntime:
-    def __init__(self, executor: DistributedRolloutExecutor, workers: list[RayWorkerHandle],
+    def __init__(self, executor: DistributedRolloutExecutor, workers: list[RayWorkerHandle] | None = None,
                  weight_sync: RayRolloutWeightSync | None = None, placement_group: Any | None = None,
-                 policy_version: int | None = None) -> None:
-        self.executor, self.workers, self.weight_sync = executor, list(workers), weight_sync
+                 policy_version: int | None = None, *,
+                 owned_workers: list[RayWorkerHandle] | None = None) -> None:
+        # ``owned_workers`` is the reference's keyword for the workers this runtime shuts down
+        workers = owned_workers if workers is None else workers
+        self.executor, self.workers, self.weight_sync = executor, list(workers or []), weight_sync
         self.placement_group = placement_group
         self.current_policy_version = policy_version
 

@@ -11,8 +11,12 @@ from visionrl_b200.distributed.ray.train.actor import RayTrainActor
 
 @dataclass(frozen=True, slots=True)
 class RayTrainRankSpec:
+    """Where one rank of a train group runs."""
+
     rank: int
-    world_size: int
+    local_rank: int = 0
+    world_size: int = 1
+    node_id: str = ""
     gpu_ids: tuple[int, ...] = ()
     env: dict[str, str] = field(default_factory=dict)
 
@@ -31,8 +35,11 @@ class RayTrainGroup:
         for a in self.actors:
             a.setup(train_config)
 
+    def primary(self) -> Any:
+        return self.actors[0]
+
     def train_step(self, prompt_batch: list[Any]) -> Any:
-        return self.actors[0].train_step(prompt_batch)
+        return self.primary().train_step(prompt_batch)
 
     def metadata(self) -> list[dict[str, Any]]:
         return [a.metadata() for a in self.actors]

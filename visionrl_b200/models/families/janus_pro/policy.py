@@ -54,6 +54,13 @@ class JanusProConfig:
     init_seed: int = 0
     int4_decode: bool = False
     arch: dict = field(default_factory=dict)
+    # fields of the reference's config, accepted so that code and YAML written for it construct
+    # this one: the native model has no remote code and no understanding-side vision encoder
+    trust_remote_code: bool = True
+    device: str | None = None
+    freeze_vision_encoder: bool = True
+    freeze_aligner: bool = True                 # False: the generation aligner trains with the trunk
+    vq_latent_channels: int | None = None       # overrides arch["codebook_dim"] when set
 
 
 @dataclass
@@ -132,7 +139,13 @@ class JanusProPolicy(nn.Module):
         super().__init__()
         self.config = config or JanusProConfig()
         arch = dict(self.config.arch)
+        if self.config.vq_latent_channels is not None:
+            if int(self.config.vq_latent_channels) <= 0:
+                raise ValueError("vq_latent_channels must be positive")
+            arch["codebook_dim"] = int(self.config.vq_latent_channels)
         dtype = resolve_dtype(self.config.dtype)
+        if self.config.device is not None and str(device) == "cpu":
+            device = self.config.device          # the reference names the device in the config
         dev = torch.device(device)
         if network is None:
             with seeded_construction(self.config.init_seed, dev):
@@ -158,7 +171,10 @@ class JanusProPolicy(nn.Module):
         self.tokenizer = HashTokenizer(self.policy.language_model.cfg.vocab_size)
         # the codebook fed back into the trunk is the VQ codebook; it and the aligner / head
         # stay frozen, only the trunk (or its adapters) trains
-        for module in (self.policy.gen_embed, self.policy.gen_aligner, self.policy.gen_head):
+        frozen = [self.policy.gen_embed, self.policy.gen_head]
+        if self.config.freeze_aligner:
+            frozen.append(self.policy.gen_aligner)
+        for module in frozen:
             module.requires_grad_(False)
         self.policy.language_model.embed_tokens.requires_grad_(False)
         if self.config.use_lora:

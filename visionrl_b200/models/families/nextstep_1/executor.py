@@ -39,6 +39,14 @@ class NextStep1ARChunkResult(PipelineChunkResult):
     context: dict[str, Any]
     peak_memory_mb: float | None = None
 
+    @property
+    def images_for_reward(self) -> torch.Tensor:
+        """What reward models see of this chunk: ``[0, 1]`` pixels when the request asked for the
+        rescale (``context["rescale_to_unit"]``, the default), else the decoder's own range."""
+        if self.context.get("rescale_to_unit", True):
+            return ((self.output + 1.0) * 0.5).clamp(0.0, 1.0)
+        return self.output
+
 
 def _pack(request, sample_specs, fields, context, steps, micro_batches, peak) -> OutputBatch:
     extra = {k: fields[k] for k in _ROW_FIELDS if k != "output"}

@@ -50,6 +50,11 @@ class NextStep1Config:
     random_init: bool = True
     init_seed: int = 0
     arch: dict = field(default_factory=dict)
+    # fields of the reference's config, accepted so that code and YAML written for it construct this one
+    device: str | None = None
+    token_dim: int | None = None                # overrides arch["token_dim"] when set
+    freeze_vae: bool = True                     # the decoder is always frozen here
+    gradient_checkpointing: bool = False        # recompute the trunk's blocks in backward
 
 
 class FlowHeadBlock(nn.Module):
@@ -134,7 +139,11 @@ class NextStep1Policy(nn.Module):
         super().__init__()
         self.config = config or NextStep1Config()
         arch = dict(self.config.arch)
+        if self.config.token_dim is not None:
+            arch["token_dim"] = int(self.config.token_dim)
         dtype = resolve_dtype(self.config.dtype)
+        if self.config.device is not None and str(device) == "cpu":
+            device = self.config.device          # the reference names the device in the config
         dev = torch.device(device)
         if network is None:
             if not self.config.random_init:
@@ -145,6 +154,8 @@ class NextStep1Policy(nn.Module):
                 network = NextStepNetwork(arch)
                 seeded_init(network, self.config.init_seed)
         self.policy = network.to(device=dev, dtype=dtype)
+        if self.config.gradient_checkpointing:
+            self.policy.language_model.gradient_checkpointing = True
         self.token_dim = int(self.policy.image_head.input_dim)
         if vae is None:
             patch = int(arch.get("token_patch", 2))

@@ -847,9 +847,11 @@ def find_units(model: nn.Module) -> list[nn.Module]:
 
 
 def shard_model(model: nn.Module, mesh: Any, device: torch.device, collectives: str = "fused",
-                ring: int = 2, rollout_replica: bool = False) -> ShardedParamRuntime | None:
-    """Shard the block weights of ``model`` in place; ``None`` when nothing qualifies."""
-    units = find_units(model)
+                ring: int = 2, rollout_replica: bool = False,
+                units: list[nn.Module] | None = None) -> ShardedParamRuntime | None:
+    """Shard the block weights of ``model`` in place; ``None`` when nothing qualifies.  ``units``
+    names the blocks explicitly (default: :func:`find_units`)."""
+    units = find_units(model) if units is None else list(units)
     if not units:
         return None
     first = next((p for p in units[0].parameters() if p.dim() == 2), None)

@@ -53,9 +53,11 @@ def resolve_mlp_weights(explicit: str | None = None) -> Path | None:
 class AestheticReward(RewardFunction):
     frame_fractions = (0.25, 0.5, 0.75)
 
-    def __init__(self, device: str = "cuda", model_name: str = "openai/clip-vit-large-patch14",
+    def __init__(self, device: str = "cuda", dtype: str | None = None,
+                 model_name: str = "openai/clip-vit-large-patch14",
                  random_init: bool = False, mlp_path: str | None = None) -> None:
-        self._device = device
+        # positional order of the reference: (device, dtype, model_name); dtype None = bf16 on a GPU
+        self._device, self._dtype = device, dtype
         self.model_name, self.random_init, self.mlp_path = model_name, random_init, mlp_path
         self._tower = None
         self._mlp: AestheticMLP | None = None
@@ -63,7 +65,7 @@ class AestheticReward(RewardFunction):
     def _ensure_loaded(self) -> None:
         if self._tower is not None:
             return
-        self._tower = build_image_tower(self.model_name, self._device, random_init=self.random_init)
+        self._tower = build_image_tower(self.model_name, self._device, self._dtype, random_init=self.random_init)
         width = self._tower.proj.out_features
         mlp = AestheticMLP(width)
         weights = None if self.random_init else resolve_mlp_weights(self.mlp_path)

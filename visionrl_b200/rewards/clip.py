@@ -19,22 +19,22 @@ class CLIPScoreReward(RewardFunction):
     divisor = 30.0
 
     def __init__(self, device: str = "cuda", model_name: str = "openai/clip-vit-large-patch14",
-                 random_init: bool = False) -> None:
-        self._device = device
+                 random_init: bool = False, dtype: str | None = None) -> None:
+        self._device, self._dtype = device, dtype
         self.model_name, self.random_init = model_name, random_init
         self._tower = None
         self._text: SyntheticTextEncoder | None = None
 
     def _ensure_loaded(self) -> None:
         if self._tower is None:
-            self._tower = build_image_tower(self.model_name, self._device,
+            self._tower = build_image_tower(self.model_name, self._device, self._dtype,
                                             random_init=self.random_init)
             self._text = SyntheticTextEncoder(self._tower.proj.out_features, 0, salt="clip-text")
             self._text_tower = None
             if not self.random_init and not self.model_name.startswith("random:"):
                 # a local checkpoint directory with its text tower and tokenizer files scores
                 # prompts with the real text side and the checkpoint's own logit scale
-                real = build_text_tower(self.model_name, self._device)
+                real = build_text_tower(self.model_name, self._device, self._dtype)
                 if real is not None:
                     self._text_tower, self._tokenizer, self.logit_scale = real
 

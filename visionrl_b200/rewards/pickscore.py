@@ -10,8 +10,8 @@ class PickScoreReward(CLIPScoreReward):
     logit_scale = 100.0
     divisor = 26.0
 
-    def __init__(self, device: str = "cuda",
+    def __init__(self, device: str = "cuda", dtype: str | None = None,
                  processor_name: str = "laion/CLIP-ViT-H-14-laion2B-s32B-b79K",
                  model_name: str = "yuvalkirstain/PickScore_v1", random_init: bool = False) -> None:
-        super().__init__(device=device, model_name=model_name, random_init=random_init)
+        super().__init__(device=device, dtype=dtype, model_name=model_name, random_init=random_init)
         self.processor_name = processor_name

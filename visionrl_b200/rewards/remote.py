@@ -10,9 +10,11 @@ from visionrl_b200.rewards.base import RewardFunction
 
 
 class RemoteReward(RewardFunction):
-    def __init__(self, url: str, reward_name: str = "default", timeout_s: float = 60.0,
-                 session: Any | None = None) -> None:
-        self.url, self.reward_name, self.timeout_s = url, reward_name, timeout_s
+    def __init__(self, url: str, timeout: float | None = None, reward_name: str = "default",
+                 timeout_s: float = 60.0, session: Any | None = None) -> None:
+        # ``timeout`` (seconds) is the reference's name and position for the request time limit
+        self.url, self.reward_name = url, reward_name
+        self.timeout_s = float(timeout) if timeout is not None else float(timeout_s)
         self._session = session
 
     def _payload(self, rollout: Rollout) -> dict[str, Any]:

@@ -71,7 +71,7 @@ def _local_tower(directory: str) -> ViTScorer:
     return tower
 
 
-def build_text_tower(directory: str, device: Any, dtype: torch.dtype | None = None):
+def build_text_tower(directory: str, device: Any, dtype: Any = None):
     """``(CLIPTextTower, tokenizer, logit_scale)`` from a local Hugging Face CLIP checkpoint
     directory, or ``None`` when the directory does not hold a text tower and tokenizer files
     (``vocab.json`` + ``merges.txt``, read by ``transformers.CLIPTokenizer``)."""
@@ -110,19 +110,32 @@ def build_text_tower(directory: str, device: Any, dtype: torch.dtype | None = No
 
     tokenizer = CLIPTokenizer.from_pretrained(directory)
     device = torch.device(device)
-    if dtype is None:
-        dtype = torch.bfloat16 if device.type == "cuda" else torch.float32
+    dtype = tower_dtype(dtype, device)
     tower = CLIPTextTower(heads=heads, act=act, eos_token_id=eos, **shape)
     tower.load_state_dict(state, strict=True)
     scale = float(math.exp(float(raw["logit_scale"]))) if "logit_scale" in raw else 100.0
     return tower.to(device=device, dtype=dtype).eval().requires_grad_(False), tokenizer, scale
 
 
-def build_image_tower(model_name: str, device: Any, dtype: torch.dtype | None = None,
+def tower_dtype(dtype: Any, device: torch.device) -> torch.dtype:
+    """``None`` → bf16 on a GPU, fp32 on the host; otherwise a ``torch.dtype`` or its name
+    (``"float32"``, ``"bfloat16"``, ``"bf16"``, ``"float16"``, ``"fp16"``)."""
+    if dtype is None:
+        return torch.bfloat16 if device.type == "cuda" else torch.float32
+    if isinstance(dtype, torch.dtype):
+        return dtype
+    names = {"float32": torch.float32, "fp32": torch.float32, "bfloat16": torch.bfloat16, "bf16": torch.bfloat16,
+             "float16": torch.float16, "fp16": torch.float16, "half": torch.float16}
+    key = str(dtype).replace("torch.", "").lower()
+    if key not in names:
+        raise ValueError(f"unknown reward tower dtype {dtype!r}")
+    return names[key]
+
+
+def build_image_tower(model_name: str, device: Any, dtype: Any = None,
                       random_init: bool = False) -> ViTScorer:
     device = torch.device(device)
-    if dtype is None:
-        dtype = torch.bfloat16 if device.type == "cuda" else torch.float32
+    dtype = tower_dtype(dtype, device)
     seed = 0
     if model_name.startswith("random:"):
         parts = model_name.split(":")

@@ -37,17 +37,20 @@ class FSDPConfig:
     use_device_mesh: bool = False
 
 
-def fsdp_wrapper(model: nn.Module, config: FSDPConfig | None = None, *,
+def fsdp_wrapper(model: nn.Module, fsdp_config: FSDPConfig | None = None,
+                 get_transformer_layer_cls: Any = None, ignored_modules: list[nn.Module] | None = None, *,
                  mesh: ProcessMesh | None = None, collectives: str = "fused") -> nn.Module:
     """Prepare ``model`` for sharded training and return it (same object).
 
-    The returned module carries ``model.sharded_runtime`` — the object trainers pass as
-    ``grad_sync`` so that gradient reduction, clipping and the sharded AdamW update run
-    as one fused step.
+    Arguments as in the reference (``vrl/trainers/fsdp.py:49-54``): ``get_transformer_layer_cls()``
+    returns the block classes whose instances are the sharding units (default: the model's
+    ``blocks`` / ``layers`` list), ``ignored_modules`` are left whole.  The returned module carries
+    ``model.sharded_runtime`` — the object trainers pass as ``grad_sync`` so that gradient
+    reduction, clipping and the sharded AdamW update run as one fused step.
     """
     from visionrl_b200.parallel.sharded import ShardedGradSync
 
-    config = config or FSDPConfig()
+    config = fsdp_config or FSDPConfig()
     if mesh is None:
         hybrid = config.sharding_strategy == "HYBRID_SHARD" and config.num_replicate > 1
         mesh = ProcessMesh.build(replicate=config.num_replicate if hybrid else 1)
@@ -65,23 +68,47 @@ def fsdp_wrapper(model: nn.Module, config: FSDPConfig | None = None, *,
 
         first = next(model.parameters(), None)
         device = first.device if first is not None else torch.device("cpu")
-        param_runtime = shard_model(model, mesh, device, collectives=collectives)
+        param_runtime = shard_model(model, mesh, device, collectives=collectives,
+                                    units=sharding_units(model, get_transformer_layer_cls, ignored_modules))
         model.param_runtime = param_runtime
     model.sharded_runtime = ShardedGradSync(mesh, shard_optimizer=shard, collectives=collectives,
                                             param_runtime=param_runtime)
     return model
 
 
-def save_fsdp_checkpoint(model: nn.Module, step: int, output_dir: str, rank: int | None = None) -> str:
+def sharding_units(model: nn.Module, get_transformer_layer_cls: Any = None,
+                   ignored_modules: list[nn.Module] | None = None) -> list[nn.Module] | None:
+    """The blocks to shard: instances of the classes ``get_transformer_layer_cls()`` returns (or the
+    model's own block list when no classes are named: ``None``), minus everything inside an ignored
+    module."""
+    from visionrl_b200.parallel.fsdp import find_units
+
+    ignored = {id(m) for root in (ignored_modules or []) for m in root.modules()}
+    if get_transformer_layer_cls is None:
+        if not ignored:
+            return None
+        units = find_units(model)
+    else:
+        classes = tuple(get_transformer_layer_cls() if callable(get_transformer_layer_cls)
+                        else get_transformer_layer_cls)
+        units = [m for m in model.modules() if isinstance(m, classes)] if classes else []
+    return [u for u in units if id(u) not in ignored]
+
+
+def save_fsdp_checkpoint(save_dir: str, model: nn.Module, global_step: int, rank: int | None = None) -> str:
+    """Rank 0 writes the full state dict to ``<save_dir>/checkpoint-<global_step>/model.safetensors``
+    (every rank takes part in gathering sharded weights), then all ranks meet at a barrier.  Argument
+    order as in the reference (``vrl/trainers/fsdp.py:106-111``); returns the directory."""
     if rank is None:
         rank = dist.get_rank() if dist_ready() else 0
-    path = os.path.join(output_dir, f"checkpoint-{step}")
+    path = os.path.join(save_dir, f"checkpoint-{global_step}")
+    state = model.state_dict()
     if rank == 0:
         from safetensors.torch import save_file
 
         os.makedirs(path, exist_ok=True)
-        state = {k: v.detach().cpu().contiguous() for k, v in model.state_dict().items()}
-        save_file(state, os.path.join(path, "model.safetensors"))
+        save_file({k: v.detach().cpu().contiguous() for k, v in state.items()}, os.path.join(path, "model.safetensors"))
+    del state
     if dist_ready():
         dist.barrier()
     return path
@@ -126,4 +153,4 @@ def init_distributed(backend: str | None = None) -> tuple[int, int, int]:
 
 
 __all__ = ["FSDPConfig", "OptimizerOffloadHook", "fsdp_wrapper", "init_distributed",
-           "register_optimizer_offload_hooks", "save_fsdp_checkpoint"]
+           "register_optimizer_offload_hooks", "save_fsdp_checkpoint", "sharding_units"]

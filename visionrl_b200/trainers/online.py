@@ -54,8 +54,9 @@ class PhaseTimer:
     timer itself is enabled, so a timeline profiler shows the step's structure without the
     synchronisation that exact phase times need."""
 
-    def __init__(self, enabled: bool = False) -> None:
+    def __init__(self, enabled: bool = False, sync: bool = True) -> None:
         self.enabled = enabled
+        self.sync = bool(sync) and torch.cuda.is_available()
         self.times: dict[str, float] = {}
         self.events: list[tuple[str, float, float]] = []
         self._nvtx = _nvtx_wanted()
@@ -68,13 +69,13 @@ class PhaseTimer:
             if not self.enabled:
                 yield
                 return
-            if torch.cuda.is_available():
+            if self.sync:
                 torch.cuda.synchronize()
             t0, w0 = time.perf_counter(), time.time()
             try:
                 yield
             finally:
-                if torch.cuda.is_available():
+                if self.sync:
                     torch.cuda.synchronize()
                 dt = time.perf_counter() - t0
                 self.times[name] = self.times.get(name, 0.0) + dt
