@@ -94,30 +94,35 @@ def test_single_file_checkpoint_round_trips(tmp_path):
 
 
 def test_offload_hooks_park_the_state_on_the_host_around_every_step():
-    net = _Net()
-    opt = torch.optim.AdamW(net.parameters(), lr=1e-2)
-    net(torch.randn(3, 8)).sum().backward()
-    opt.step()
-    seen = []
+    torch.manual_seed(0)
+    net, twin = _Net(), _Net()
+    twin.load_state_dict(net.state_dict())
+    opt, twin_opt = torch.optim.AdamW(net.parameters(), lr=1e-2), torch.optim.AdamW(twin.parameters(), lr=1e-2)
 
-    class Spy(OptimizerOffloadHook):
-        def _move(self, device):
-            seen.append(str(device))
-            super()._move(device)
+    def step(x):
+        for model, optimiser in ((net, opt), (twin, twin_opt)):
+            optimiser.zero_grad()
+            model(x).sum().backward()
+            optimiser.step()
 
-    hook = Spy(opt, "cpu")
-    opt.register_step_pre_hook(hook.pre_step)
-    opt.register_step_post_hook(hook.post_step)
-    before = {k: v.clone() for k, v in net.state_dict().items()}
-    net(torch.randn(3, 8)).sum().backward()
-    opt.step()
-    assert seen == ["cpu", "cpu"]                       # to the step device, then back to the host
-    assert any(not torch.equal(before[k], v) for k, v in net.state_dict().items())
-    registered = register_optimizer_offload_hooks(torch.optim.AdamW(_Net().parameters()), "cpu")
-    assert isinstance(registered, OptimizerOffloadHook)
+    step(torch.randn(3, 8))
+    handles, hook = register_optimizer_offload_hooks(opt)
+    assert len(handles) == 2 and isinstance(hook, OptimizerOffloadHook)
+    weight = net.a.weight
+    # between steps the moments live in the hook's host copies and the optimiser holds placeholders
+    assert opt.state[weight]["exp_avg"].numel() == 0 and hook.cpu_states[weight]["exp_avg"].shape == weight.shape
+    assert opt.state[weight]["step"].numel() == 1                     # the step counter stays where it is
+    step(torch.randn(3, 8))
+    step(torch.randn(3, 8))
+    # every step saw the full state: bit for bit the run without offloading
+    assert all(torch.equal(a, b) for a, b in zip(net.parameters(), twin.parameters()))
+    assert opt.state[weight]["exp_avg"].numel() == 0 and weight in hook.cpu_states
+    assert torch.equal(hook.cpu_states[weight]["exp_avg"], twin_opt.state[twin.a.weight]["exp_avg"])
+    for h in handles:
+        h.remove()
 
 
 def test_init_distributed_without_a_launcher_is_a_single_rank(monkeypatch):
     for name in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
         monkeypatch.delenv(name, raising=False)
-    assert init_distributed() == (0, 1, 0)
+    assert init_distributed() == (False, 0, 1, 0)

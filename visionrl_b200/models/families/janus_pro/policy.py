@@ -458,7 +458,8 @@ class JanusProPolicy(nn.Module):
         return int(self._vq.quantize.embedding.weight.shape[-1])
 
     @torch.no_grad()
-    def decode_image_tokens(self, token_ids: torch.Tensor, image_size: int | None = None):
+    def decode_image_tokens(self, image_token_ids: torch.Tensor, image_size: int | None = None):
+        token_ids = image_token_ids
         b, n = token_ids.shape
         side = int(round(n ** 0.5))
         if side * side != n:

@@ -218,10 +218,11 @@ class NextStep1Policy(nn.Module):
 
     # -- sampling -----------------------------------------------------------------------------
     @torch.no_grad()
-    def init_ar_state(self, cond_inputs_embeds, uncond_inputs_embeds, cond_attention_mask,
-                      uncond_attention_mask, *, cfg_scale=None, num_flow_steps=None,
-                      noise_level=None, image_token_num=None,
+    def init_ar_state(self, prompt_embeds, uncond_embeds, prompt_mask, uncond_mask, *, cfg_scale=None,
+                      num_flow_steps=None, noise_level=None, image_token_num=None,
                       generator: torch.Generator | None = None) -> NextStep1ARState:
+        cond_inputs_embeds, uncond_inputs_embeds = prompt_embeds, uncond_embeds
+        cond_attention_mask, uncond_attention_mask = prompt_mask, uncond_mask
         c = self.config
         n_img = int(image_token_num or c.image_token_num)
         b, l_text = cond_attention_mask.shape
@@ -301,10 +302,11 @@ class NextStep1Policy(nn.Module):
         return state.tokens, state.log_probs, state.saved_noise
 
     # -- replay -----------------------------------------------------------------------------------
-    def recompute_logprobs(self, prompt_embeds, prompt_mask, uncond_embeds, uncond_mask, tokens,
+    def recompute_logprobs(self, prompt_embeds, uncond_embeds, prompt_mask, uncond_mask, tokens,
                            saved_noise, *, cfg_scale: float, num_flow_steps: int,
                            noise_level: float) -> torch.Tensor:
-        """``[B, L]`` log-probs of recorded ``tokens`` with the rollout's ``x_0`` (exact replay)."""
+        """``[B, L]`` log-probs of recorded ``tokens`` with the rollout's ``x_0`` (exact replay).
+        Argument order as in the reference: both embeddings, then both masks."""
         b, l_img, d = tokens.shape
         l_text = prompt_mask.shape[1]
         lm = self.policy.language_model
@@ -332,10 +334,11 @@ class NextStep1Policy(nn.Module):
         ids = (obs[:, 0] if obs.ndim == 3 else obs).to(self.device)
         ctx = batch.context
         lp = self.recompute_logprobs(
-            self.embed_text(ids), batch.extras["prompt_attention_mask"].to(self.device),
-            self.embed_text(batch.extras["uncond_input_ids"].to(self.device)),
-            batch.extras["uncond_attention_mask"].to(self.device), batch.actions.to(self.device),
-            batch.extras["saved_noise"].to(self.device), cfg_scale=float(ctx["cfg_scale"]),
+            prompt_embeds=self.embed_text(ids),
+            uncond_embeds=self.embed_text(batch.extras["uncond_input_ids"].to(self.device)),
+            prompt_mask=batch.extras["prompt_attention_mask"].to(self.device),
+            uncond_mask=batch.extras["uncond_attention_mask"].to(self.device), tokens=batch.actions.to(self.device),
+            saved_noise=batch.extras["saved_noise"].to(self.device), cfg_scale=float(ctx["cfg_scale"]),
             num_flow_steps=int(ctx["num_flow_steps"]), noise_level=float(ctx["noise_level"]))
         return {"log_probs": lp, "target_tokens": batch.actions}
 

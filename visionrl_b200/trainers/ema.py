@@ -63,7 +63,8 @@ class EMAModuleWrapper:
     def state_dict(self) -> dict:
         return {"decay": self.decay, "ema_parameters": [e.detach().cpu() for e in self.ema_parameters]}
 
-    def load_state_dict(self, state: dict) -> None:
+    def load_state_dict(self, state_dict: dict) -> None:
+        state = state_dict
         self.decay = state.get("decay", self.decay)
         loaded = state["ema_parameters"]
         if len(loaded) != len(self.ema_parameters):

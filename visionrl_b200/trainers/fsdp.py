@@ -115,41 +115,71 @@ def save_fsdp_checkpoint(save_dir: str, model: nn.Module, global_step: int, rank
 
 
 class OptimizerOffloadHook:
-    """Keeps optimiser state in host memory between steps: a pre-step hook brings it to
-    the device, a post-step hook returns it."""
+    """Keeps optimiser state in host memory between steps: the pre-step hook brings every state
+    tensor back to its parameter's device, the post-step hook parks it on the host again
+    (reference: ``vrl/trainers/fsdp.py:131-160``).  The flat moment buffers of
+    ``visionrl_b200.ops.optim.FusedAdamW`` are handled the same way."""
 
-    def __init__(self, optimizer: torch.optim.Optimizer, device: torch.device | str = "cuda"):
-        self.optimizer = optimizer
-        self.device = torch.device(device)
+    def __init__(self) -> None:
+        self.cpu_states: dict[Any, dict[str, torch.Tensor]] = {}
 
-    def _move(self, device: torch.device) -> None:
-        for state in self.optimizer.state.values():
-            for k, v in state.items():
-                if isinstance(v, torch.Tensor):
-                    state[k] = v.to(device, non_blocking=True)
-        for entry in getattr(self.optimizer, "_flat", []):
-            for k in ("exp_avg", "exp_avg_sq"):
-                entry[k] = entry[k].to(device, non_blocking=True)
+    @staticmethod
+    def _flat_entries(optimizer: Any) -> list:
+        return list(getattr(optimizer, "_flat", []) or [])
 
-    def pre_step(self, *_: Any) -> None:
-        self._move(self.device)
+    def pre_step_hook(self, optimizer: Any, args: Any = None, kwargs: Any = None) -> None:
+        for group in optimizer.param_groups:
+            for param in group["params"]:
+                parked = self.cpu_states.pop(param, None)
+                if parked and param in optimizer.state:
+                    for key, tensor in parked.items():
+                        optimizer.state[param][key] = tensor.to(param.device, non_blocking=True)
+        for i, entry in enumerate(self._flat_entries(optimizer)):
+            parked = self.cpu_states.pop(("flat", i), None)
+            if parked:
+                for key, tensor in parked.items():
+                    entry[key] = tensor.to(entry["param"].device, non_blocking=True)
 
-    def post_step(self, *_: Any) -> None:
-        self._move(torch.device("cpu"))
+    def post_step_hook(self, optimizer: Any, args: Any = None, kwargs: Any = None) -> None:
+        for group in optimizer.param_groups:
+            for param in group["params"]:
+                state = optimizer.state.get(param)
+                if not state:
+                    continue
+                parked = {}
+                for key, value in state.items():
+                    if isinstance(value, torch.Tensor) and value.numel() > 1:
+                        parked[key] = value.to("cpu", non_blocking=True)
+                        state[key] = torch.empty(0, device=param.device, dtype=value.dtype)
+                if parked:
+                    self.cpu_states[param] = parked
+        for i, entry in enumerate(self._flat_entries(optimizer)):
+            parked = {}
+            for key in ("exp_avg", "exp_avg_sq"):
+                value = entry.get(key)
+                if isinstance(value, torch.Tensor) and value.numel():
+                    parked[key] = value.to("cpu", non_blocking=True)
+                    entry[key] = torch.empty(0, device=value.device, dtype=value.dtype)
+            if parked:
+                self.cpu_states[("flat", i)] = parked
 
 
-def register_optimizer_offload_hooks(optimizer: torch.optim.Optimizer,
-                                     device: torch.device | str = "cuda") -> OptimizerOffloadHook:
-    hook = OptimizerOffloadHook(optimizer, device)
-    optimizer.register_step_pre_hook(hook.pre_step)
-    optimizer.register_step_post_hook(hook.post_step)
-    hook.post_step()
-    return hook
+def register_optimizer_offload_hooks(optimizer: torch.optim.Optimizer) -> tuple[list[Any], OptimizerOffloadHook]:
+    """Register the two hooks; returns ``([pre_handle, post_handle], hook)`` as the reference does.
+    State that already exists is parked at once."""
+    hook = OptimizerOffloadHook()
+    handles = [optimizer.register_step_pre_hook(hook.pre_step_hook),
+               optimizer.register_step_post_hook(hook.post_step_hook)]
+    hook.post_step_hook(optimizer)
+    return handles, hook
 
 
-def init_distributed(backend: str | None = None) -> tuple[int, int, int]:
-    """``env://`` rendezvous (NCCL on GPUs, gloo otherwise) → ``(rank, world, local_rank)``."""
-    return _init_distributed(backend)
+def init_distributed(backend: str | None = None) -> tuple[bool, int, int, int]:
+    """``env://`` rendezvous (NCCL on GPUs, gloo otherwise) →
+    ``(is_distributed, rank, world_size, local_rank)``; ``(False, 0, 1, 0)`` without a launcher
+    (reference: ``vrl/trainers/fsdp.py:172-183``)."""
+    rank, world, local = _init_distributed(backend)
+    return dist_ready(), rank, world, local
 
 
 __all__ = ["FSDPConfig", "OptimizerOffloadHook", "fsdp_wrapper", "init_distributed",
