@@ -48,8 +48,10 @@ def _normalized_edit_distance(a: str, b: str) -> float:
     return _edit_distance(a, b) / max(len(a), len(b), 1)
 
 
-def _safe_filename_fragment(text: str, limit: int = 32) -> str:
-    return re.sub(r"[^A-Za-z0-9_-]+", "_", text)[:limit] or "target"
+def _safe_filename_fragment(text: str, max_len: int = 24) -> str:
+    """Letters and digits of ``text`` joined by single underscores, at most ``max_len`` characters;
+    ``"empty"`` when nothing is left."""
+    return re.sub(r"[^A-Za-z0-9]+", "_", text).strip("_")[:max_len] or "empty"
 
 
 def _import_engine(path: str) -> Callable[[Any], str]:
