@@ -146,3 +146,46 @@ def test_resolved_config_written_and_resume_copy_kept(tmp_path):
     assert (tmp_path / "resolved_config.yaml").exists()
     ck.save_resolved_config(cfg, tmp_path, resumed=True)
     assert len(list(tmp_path.glob("resume_config_*.yaml"))) == 1
+
+
+def test_a_checkpoint_written_by_the_reference_implementation_restores_here(tmp_path):
+    """``tests/golden/reference_checkpoint`` was written by the reference's own
+    ``save_training_checkpoint`` (a 2x2 linear layer seeded with 0, optimiser and averaged state, the
+    prompt generator seeded with 123 and advanced by one permutation of five).  It must load, restore
+    and continue here exactly as there; and a checkpoint written here carries the same meta file."""
+    import json
+    import os
+    import types
+
+    from torch import nn
+
+    from visionrl_b200.trainers import checkpointing as ck
+
+    golden = os.path.join(os.path.dirname(os.path.dirname(__file__)), "golden", "reference_checkpoint")
+    loaded = ck.load_training_checkpoint(golden)
+    assert loaded.meta["next_epoch"] == 4 and loaded.meta["family"] == "sd3_5" and loaded.meta["schema_version"] == 1
+
+    class Trainer:
+        def load_state_dict(self, state, strict=True):
+            self.loaded = state
+
+        def state_dict(self):
+            return self.loaded
+
+    trainer, net = Trainer(), nn.Linear(2, 2)
+    bundle = types.SimpleNamespace(trainable_modules={"transformer": net}, metadata={"family": "sd3_5"})
+    ck.restore_training_checkpoint(loaded, trainer=trainer, bundle=bundle, strict=True)
+    torch.manual_seed(0)
+    assert torch.equal(net.weight, nn.Linear(2, 2).weight)
+    assert sorted(trainer.loaded) == ["ema", "global_step", "optimizer", "step", "total_loss", "total_reward"]
+    assert float(trainer.loaded["optimizer"]["state"][0]["exp_avg_sq"][0, 0]) == 2.0
+    generator = torch.Generator().manual_seed(0)
+    ck.restore_rng_state(loaded.payload["rng"], prompt_generator=generator)
+    assert torch.randperm(5, generator=generator).tolist() == [0, 3, 2, 4, 1]
+
+    # written here from the restored pieces: the same meta file, key for key
+    ck.save_training_checkpoint(tmp_path / "again", trainer=trainer, bundle=bundle, family="sd3_5",
+                                progress={"completed_epoch": 4, "next_epoch": 4, "global_step": 7})
+    ours = json.loads((tmp_path / "again" / "checkpoint_meta.json").read_text())
+    theirs = json.loads(open(os.path.join(golden, "checkpoint_meta.json")).read())
+    assert ours == theirs
