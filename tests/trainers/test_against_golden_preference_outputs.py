@@ -1,0 +1,28 @@
+"""``OfflineDPOTrainer.step`` against recorded outputs of the reference's trainer for the runs of
+``golden_preference_cases.compute`` (108 values: metrics of three steps in four set-ups, the
+timesteps handed to the model, the weights after training, the step counter)."""
+
+import os
+
+import pytest
+import torch
+
+from tests.trainers.golden_preference_cases import compute
+
+GOLDEN = torch.load(os.path.join(os.path.dirname(os.path.dirname(__file__)), "golden", "preference_trainer_outputs.pt"))
+
+
+@pytest.fixture(scope="module")
+def outputs():
+    return compute()
+
+
+def test_every_recorded_value_is_computed(outputs):
+    assert set(outputs) == set(GOLDEN) and len(GOLDEN) > 100
+
+
+@pytest.mark.parametrize("key", sorted(GOLDEN))
+def test_value_matches_the_recorded_one(outputs, key):
+    got, want = outputs[key].detach().float(), GOLDEN[key].float()
+    assert got.shape == want.shape, (got.shape, want.shape)
+    assert torch.allclose(got, want, atol=1e-5, rtol=1e-5), (key, float((got - want).abs().max()))
