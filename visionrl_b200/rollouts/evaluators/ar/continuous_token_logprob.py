@@ -43,7 +43,7 @@ class ContinuousTokenLogProbEvaluator:
                     ref_lp = self._log_probs(model, batch)
         aux = {self.mask_key: batch.extras[self.mask_key]} if self.mask_key in batch.extras else {}
         return SignalBatch(log_prob=new_lp, ref_log_prob=ref_lp, entropy=None,
-                           dist_family="gaussian_token", aux=aux)
+                           dist_family="continuous_flow", aux=aux)
 
 
 __all__ = ["ContinuousTokenLogProbEvaluator"]
