@@ -34,7 +34,7 @@ def extract_diffusion_runtime_spec(cfg: Any, device: Any, weight_dtype: Any, *,
     if compile_cfg is not None and _get(compile_cfg, "enable"):
         extra["torch_compile"] = {"enable": True, "mode": _get(compile_cfg, "mode", "default")}
     ref_image = _get(model, "reference_image")
-    if ref_image is not None:
+    if ref_image:
         extra["reference_image"] = ref_image
     native = {
         "arch": to_container(_get(model, "arch") or {}),

@@ -18,7 +18,7 @@ _CAPS = {"supports_stepwise": True, "supports_cfg": True, "supports_batched_deco
 
 
 def extract_cosmos_predict2_runtime_spec(cfg: Any, device: Any, weight_dtype: Any) -> RuntimeBuildSpec:
-    return extract_diffusion_runtime_spec(cfg, device, weight_dtype, task_variant="v2w")
+    return extract_diffusion_runtime_spec(cfg, device, weight_dtype, task_variant="video2world")
 
 
 def build_cosmos_predict2_runtime_bundle(spec: RuntimeBuildSpec) -> RuntimeBundle:

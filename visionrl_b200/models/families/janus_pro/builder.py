@@ -31,18 +31,28 @@ def extract_janus_pro_runtime_spec(cfg: Any, device: Any, weight_dtype: Any) -> 
         },
         "freeze_vq": bool(cfg_path(cfg, "model.freeze_vq", True)),
     }
+    # the same facts in the two places the reference's spec carries them (sampling defaults under
+    # ``scheduler_config``, freeze switches under ``extra``), so a spec written either way builds
+    sampling = native["sampling"]
     return RuntimeBuildSpec(
         model_name_or_path=str(model.path), device=device,
         dtype=cfg_path(cfg, "model.dtype", None) or weight_dtype, backend_preference=("native",),
         task_variant="ar_t2i", use_lora=bool(model.use_lora), lora_config=lora_cfg,
-        native_backend_config=native)
+        scheduler_config={"cfg_weight": sampling["cfg_weight"], "image_token_num": sampling["image_token_num"],
+                          "temperature": sampling["temperature"]},
+        native_backend_config=native,
+        extra={"freeze_vq": native["freeze_vq"],
+               "freeze_vision_encoder": bool(cfg_path(cfg, "model.freeze_vision_encoder", True)),
+               "freeze_aligner": bool(cfg_path(cfg, "model.freeze_aligner", True))})
 
 
 def _janus_config_from_runtime_spec(spec: RuntimeBuildSpec):
     from visionrl_b200.models.families.janus_pro.policy import JanusProConfig
 
     native = dict(spec.native_backend_config or {})
-    sampling = dict(native.get("sampling") or {})
+    extra = dict(spec.extra or {})
+    sampling = {**dict(spec.scheduler_config or {}), **dict(native.get("sampling") or {})}
+    native.setdefault("freeze_vq", extra.get("freeze_vq", True))
     lora = dict(spec.lora_config or {})
     dtype = str(spec.dtype).removeprefix("torch.")
     image_size = int(sampling.get("image_size", 384))
@@ -58,7 +68,9 @@ def _janus_config_from_runtime_spec(spec: RuntimeBuildSpec):
         image_size=image_size, patch_size=max(1, image_size // side),
         freeze_vq=bool(native.get("freeze_vq", True)), random_init=bool(native.get("random_init", True)),
         init_seed=int(native.get("init_seed", 0)), int4_decode=bool(native.get("int4_decode", False)),
-        arch=dict(native.get("arch") or {}))
+        arch=dict(native.get("arch") or {}),
+        freeze_vision_encoder=bool(extra.get("freeze_vision_encoder", True)),
+        freeze_aligner=bool(extra.get("freeze_aligner", True)))
 
 
 def build_janus_pro_runtime_bundle(spec: RuntimeBuildSpec) -> RuntimeBundle:

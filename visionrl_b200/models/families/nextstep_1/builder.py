@@ -32,18 +32,25 @@ def extract_nextstep_1_runtime_spec(cfg: Any, device: Any, weight_dtype: Any) ->
             "image_size": int(cfg.sampling.image_size),
         },
     }
+    # the same facts in the two places the reference's spec carries them
     return RuntimeBuildSpec(
         model_name_or_path=str(model.path), device=device,
         dtype=cfg_path(cfg, "model.dtype", None) or weight_dtype, backend_preference=("native",),
         task_variant="ar_t2i", use_lora=bool(model.use_lora), lora_config=lora_cfg,
-        native_backend_config=native)
+        scheduler_config=dict(native["sampling"]), native_backend_config=native,
+        extra={"vae_path": native["vae_path"], "freeze_image_head": native["freeze_image_head"],
+               "freeze_vae": bool(cfg_path(cfg, "model.freeze_vae", True)),
+               "gradient_checkpointing": bool(cfg_path(cfg, "actor.gradient_checkpointing", False))})
 
 
 def _nextstep_1_config_from_runtime_spec(spec: RuntimeBuildSpec):
     from visionrl_b200.models.families.nextstep_1.policy import NextStep1Config
 
     native = dict(spec.native_backend_config or {})
-    sampling = dict(native.get("sampling") or {})
+    extra = dict(spec.extra or {})
+    sampling = {**dict(spec.scheduler_config or {}), **dict(native.get("sampling") or {})}
+    native.setdefault("vae_path", extra.get("vae_path", ""))
+    native.setdefault("freeze_image_head", extra.get("freeze_image_head", False))
     lora = dict(spec.lora_config or {})
     return NextStep1Config(
         model_path=spec.model_name_or_path, vae_path=str(native.get("vae_path", "")),
@@ -58,7 +65,8 @@ def _nextstep_1_config_from_runtime_spec(spec: RuntimeBuildSpec):
         image_size=int(sampling.get("image_size", 256)),
         freeze_image_head=bool(native.get("freeze_image_head", False)),
         random_init=bool(native.get("random_init", True)), init_seed=int(native.get("init_seed", 0)),
-        arch=dict(native.get("arch") or {}))
+        arch=dict(native.get("arch") or {}), freeze_vae=bool(extra.get("freeze_vae", True)),
+        gradient_checkpointing=bool(extra.get("gradient_checkpointing", False)))
 
 
 def build_nextstep_1_runtime_bundle(spec: RuntimeBuildSpec) -> RuntimeBundle:
