@@ -1,5 +1,5 @@
 """Cosmos video-to-world executor: threads the reference image (constructor default, or
-``request.metadata["reference_image"]`` when present) into ``prepare_sampling``
+``request.metadata["reference_image"]`` when present) into ``encode_prompt`` and ``prepare_sampling``
 (reference: ``vrl/models/families/cosmos/executor.py:17-116``)."""
 
 from __future__ import annotations
@@ -22,6 +22,18 @@ class CosmosPipelineExecutor(DiffusionPipelineExecutorBase):
         self.default_sample_batch_size = max(1, int(sample_batch_size))
         self.reference_image = reference_image
 
+    def _reference_image(self, generation_request: Any) -> Any:
+        override = (generation_request.metadata or {}).get("reference_image")
+        return override if override is not None else self.reference_image
+
+    def encode_prompt_for_chunk(self, *, generation_request, video_request, spec, chunk):
+        # the reference image reaches the encoder as well as the sampler preparation
+        return self.model.encode_prompt(
+            chunk.prompt, video_request.negative_prompt or None,
+            max_sequence_length=spec.base.max_sequence_length,
+            guidance_scale=spec.base.guidance_scale, request=video_request,
+            reference_image=self._reference_image(generation_request))
+
     def build_chunk_encoded(self, *, encoded, generation_request, video_request, spec, chunk):
         del generation_request, video_request, spec
         return {k: repeat_tensor_batch(encoded[k], chunk.sample_count)
@@ -29,9 +41,7 @@ class CosmosPipelineExecutor(DiffusionPipelineExecutorBase):
 
     def build_prepare_kwargs(self, *, encoded, generation_request, video_request, spec, chunk):
         del encoded, video_request, spec, chunk
-        override = (generation_request.metadata or {}).get("reference_image")
-        image = override if override is not None else self.reference_image
-        return {"reference_image": image}
+        return {"reference_image": self._reference_image(generation_request)}
 
 
 __all__ = ["CosmosPipelineExecutor"]

@@ -133,8 +133,10 @@ class JanusProPipelineExecutor(ARPipelineExecutorBase):
                   seed_offset: int) -> tuple[dict[str, torch.Tensor], dict[str, Any], int]:
         spec = self.parse_spec(request)
         s = request.sampling
-        cfg_weight = float(s.get("cfg_weight", self.model.config.cfg_weight))
-        temperature = float(s.get("temperature", self.model.config.temperature))
+        # request values win; a policy without a config object gets the published defaults
+        config = getattr(self.model, "config", None)
+        cfg_weight = float(s.get("cfg_weight", getattr(config, "cfg_weight", 5.0)))
+        temperature = float(s.get("temperature", getattr(config, "temperature", 1.0)))
         generator = None
         if spec.seed is not None:
             generator = torch.Generator(device="cpu").manual_seed(int(spec.seed) + seed_offset)

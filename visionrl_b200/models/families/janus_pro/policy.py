@@ -34,6 +34,13 @@ from visionrl_b200.ops import logprob as logprob_ops
 from visionrl_b200.ops import sampling as sampling_ops
 
 
+# the published model's image-token geometry (defaults of the config below)
+JANUS_IMAGE_TOKEN_NUM = 576
+JANUS_IMAGE_VOCAB_SIZE = 16384
+JANUS_IMAGE_PATCH_SIZE = 16
+JANUS_IMAGE_PIXEL_SIZE = 384
+
+
 @dataclass
 class JanusProConfig:
     model_path: str = "deepseek-community/Janus-Pro-1B"

@@ -120,12 +120,11 @@ class NextStep1PipelineExecutor(ARPipelineExecutorBase):
     def _run_rows(self, request: GenerationRequest, prompts: list[str], sample_ids: list[str],
                   seed_offset: int):
         spec = self.parse_spec(request)
-        s, cfg = request.sampling, self.model.config
-        rollout_meta = (request.metadata or {}).get("rollout_metadata", {}) or {}
-        del rollout_meta
-        kwargs = dict(cfg_scale=float(s.get("cfg_scale", cfg.cfg_scale)),
-                      num_flow_steps=int(s.get("num_flow_steps", cfg.num_flow_steps)),
-                      noise_level=float(s.get("noise_level", cfg.noise_level)),
+        # request values win; a policy without a config object gets the published defaults
+        s, cfg = request.sampling, getattr(self.model, "config", None)
+        kwargs = dict(cfg_scale=float(s.get("cfg_scale", getattr(cfg, "cfg_scale", 4.5))),
+                      num_flow_steps=int(s.get("num_flow_steps", getattr(cfg, "num_flow_steps", 20))),
+                      noise_level=float(s.get("noise_level", getattr(cfg, "noise_level", 1.0))),
                       image_token_num=spec.image_token_num)
         if spec.seed is not None:
             kwargs["generator"] = torch.Generator(device="cpu").manual_seed(int(spec.seed) + seed_offset)

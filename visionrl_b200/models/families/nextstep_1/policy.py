@@ -30,6 +30,12 @@ from visionrl_b200.models.nn.vision import HashTokenizer, LatentDecoder2D
 from visionrl_b200.ops import norm as norm_ops
 
 
+# the published model's continuous-token geometry (defaults of the config below)
+NEXTSTEP_DEFAULT_TOKEN_NUM = 1024
+NEXTSTEP_DEFAULT_TOKEN_DIM = 64
+NEXTSTEP_DEFAULT_PIXEL_SIZE = 256
+
+
 @dataclass
 class NextStep1Config:
     model_path: str = "stepfun-ai/NextStep-1.1"

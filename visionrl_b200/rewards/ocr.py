@@ -114,6 +114,17 @@ class OCRReward(RewardFunction):
         if self._engine is None:
             self._engine = _default_engine()
 
+    def _read(self, frame: Any) -> str:
+        """Text of one frame.  The engine is a callable ``frame -> text``, or an object with the
+        ``ocr(frame, cls=False)`` method of PaddleOCR (lines of ``[box, (text, confidence)]``)."""
+        engine = self._engine
+        if callable(engine):
+            return str(engine(frame))
+        result = engine.ocr(frame, cls=False)
+        if result and result[0]:
+            return "".join(line[1][0] if line[1][1] > 0 else "" for line in result[0])
+        return ""
+
     def _frames(self, output: Any) -> tuple[list, bool]:
         import numpy as np
         import torch
@@ -139,7 +150,7 @@ class OCRReward(RewardFunction):
         positive: list[float] = []
         best = (0.0, None, "")
         for frame in frames:
-            seen_raw = self._engine(frame)
+            seen_raw = self._read(frame)
             seen = _normalize_ocr_text(seen_raw)
             dist = 0 if single and target in seen else _edit_distance(seen, target)
             reward = 1.0 - min(dist, len(target)) / len(target)

@@ -17,9 +17,9 @@ from visionrl_b200.engine import RolloutBackend
 from visionrl_b200.rollouts.runtime.config import RolloutBackendConfig, cfg_path
 
 DRIVER_CUDA_OWNERSHIP_ERROR = (
-    "Driver loaded rollout policy on CUDA. Keep the driver's copy on cpu so rollout workers "
-    "own the CUDA copies, or set distributed.rollout.allow_driver_gpu_overlap=true for an "
-    "explicitly colocated run."
+    "Driver loaded rollout policy on CUDA. With the Ray-style backend set model.device=cpu so that the "
+    "rollout workers own the CUDA copies, or set distributed.rollout.allow_driver_gpu_overlap=true "
+    "for an explicitly colocated run."
 )
 
 
