@@ -47,9 +47,11 @@ def compute() -> dict:
     from vrl.rollouts.evaluators import SignalBatch
     for gs in (False, True):
         algo = GRPO(GRPOConfig(global_std=gs, adv_clip_max=1.5))
-        rewards = R(12); groups = torch.tensor([0, 0, 0, 0, 1, 1, 1, 1, 2, 2, 2, 2])
+        rewards = R(12)
+        groups = torch.tensor([0, 0, 0, 0, 1, 1, 1, 1, 2, 2, 2, 2])
         res[f"grpo/adv/{gs}"] = algo.compute_advantages_from_tensors(rewards, groups)
-    same = torch.ones(4); res["grpo/adv/zero_std"] = GRPO(GRPOConfig()).compute_advantages_from_tensors(same, torch.zeros(4, dtype=torch.long))
+    same = torch.ones(4)
+    res["grpo/adv/zero_std"] = GRPO(GRPOConfig()).compute_advantages_from_tensors(same, torch.zeros(4, dtype=torch.long))
     import inspect
     fields = set(inspect.signature(SignalBatch).parameters)
     def sig(**kw):
@@ -59,7 +61,8 @@ def compute() -> dict:
             algo = GRPO(GRPOConfig(eps_clip=0.2, init_kl_coef=kl, flow_kl_use_dt=use_dt))
             new_lp, old_lp, adv = R(8), R(8), R(8)
             mean, ref_mean = R(8, 4, 6, 6), R(8, 4, 6, 6)
-            std = torch.rand(8, 1, 1, 1, generator=g) + 0.1; dt = -(torch.rand(8, 1, 1, 1, generator=g) + 0.1)
+            std = torch.rand(8, 1, 1, 1, generator=g) + 0.1
+            dt = -(torch.rand(8, 1, 1, 1, generator=g) + 0.1)
             s = sig(log_prob=new_lp, prev_sample_mean=mean, ref_prev_sample_mean=ref_mean if kl > 0 else None, std_dev_t=std, dt=dt, ref_log_prob=R(8) if kl > 0 else None, aux={}, dist_family="flow_matching")
             loss, m = algo.compute_signal_loss(s, adv, old_lp)
             res[f"grpo/loss/{kl}/{use_dt}"] = loss.detach()
@@ -84,8 +87,10 @@ def compute() -> dict:
     for gs in (False, True):
         tr = PerPromptStatTracker(global_std=gs)
         prompts = ["a", "a", "b", "b", "b", "c"]
-        r1 = np.array([1.0, 2.0, 0.5, 0.7, 0.9, 3.0]); r2 = np.array([0.0, 1.0, 0.1, 0.2, 0.3, 2.0])
-        res[f"stat/{gs}/1"] = torch.tensor(tr.update(prompts, r1)); res[f"stat/{gs}/2"] = torch.tensor(tr.update(prompts, r2))
+        r1 = np.array([1.0, 2.0, 0.5, 0.7, 0.9, 3.0])
+        r2 = np.array([0.0, 1.0, 0.1, 0.2, 0.3, 2.0])
+        res[f"stat/{gs}/1"] = torch.tensor(tr.update(prompts, r1))
+        res[f"stat/{gs}/2"] = torch.tensor(tr.update(prompts, r2))
         res[f"stat/{gs}/stats"] = torch.tensor([float(x) for x in tr.get_stats()])
 
     # --- flow-matching SDE step
@@ -122,6 +127,7 @@ def compute() -> dict:
         def __len__(self): return 37
     for rank in (0, 1):
         smp = DistributedKRepeatSampler(DS(), batch_size=6, k=3, num_replicas=2, rank=rank, seed=7)
-        it = iter(smp); smp.set_epoch(2) if hasattr(smp, "set_epoch") else None
+        it = iter(smp)
+        smp.set_epoch(2) if hasattr(smp, "set_epoch") else None
         res[f"sampler/{rank}"] = torch.tensor([list(next(it)) for _ in range(2)])
     return res
