@@ -74,8 +74,8 @@ def test_rotary_row_permutation_and_refusals():
         convert.llama_from_hf({"embed_tokens.weight": torch.zeros(1)}, 2)
     hf = transformers.LlamaModel(transformers.LlamaConfig(
         vocab_size=32, hidden_size=32, intermediate_size=48, num_hidden_layers=1, num_attention_heads=4,
-        num_key_value_heads=2)).state_dict()
-    with pytest.raises(ValueError, match="grouped-query"):
+        num_key_value_heads=2, mlp_bias=True)).state_dict()
+    with pytest.raises(ValueError, match="no native counterpart"):
         convert.llama_from_hf(hf, 4)
 
 
@@ -106,3 +106,38 @@ def test_janus_mapping_covers_the_generation_side_and_loads_strictly(pair, tmp_p
     assert torch.equal(net.gen_head.fc2.weight, state["gen_head.vision_head.weight"])
     with pytest.raises(KeyError, match="lacks"):
         convert.janus_from_hf({k: v for k, v in state.items() if not k.startswith("gen_head")}, HEADS)
+
+
+def test_grouped_query_trunk_with_projection_bias_matches_transformers():
+    """A Qwen2-style trunk (two key/value heads for four query heads, bias on q / k / v): converted
+    weights give the same hidden states, full sequence and token by token through the cache."""
+    torch.manual_seed(0)
+    hf_cfg = transformers.Qwen2Config(vocab_size=VOCAB, hidden_size=HIDDEN, intermediate_size=FFN,
+                                      num_hidden_layers=LAYERS, num_attention_heads=HEADS, num_key_value_heads=2,
+                                      rms_norm_eps=1e-6, rope_theta=10000.0, max_position_embeddings=64)
+    hf = transformers.Qwen2Model(hf_cfg).eval()
+    with torch.no_grad():
+        for name, p in hf.named_parameters():
+            if name.endswith("_proj.bias"):
+                p.normal_(std=0.5)                       # zero-initialised by default: make it matter
+    native = LlamaDecoder(LlamaConfig(num_layers=LAYERS, hidden_size=HIDDEN, num_heads=HEADS, ffn_dim=FFN,
+                                      vocab_size=VOCAB, rope_theta=10000.0, rms_eps=1e-6, max_positions=64,
+                                      num_kv_heads=2, qkv_bias=True)).eval()
+    state = convert.llama_from_hf(hf.state_dict(), HEADS)
+    assert state["layers.0.attn.qkv.weight"].shape == ((HEADS + 2 * 2) * (HIDDEN // HEADS), HIDDEN)
+    native.load_state_dict(state, strict=True)
+    assert not native.layers[0].attn.plain_layout
+    ids = torch.randint(0, VOCAB, (2, 9))
+    with torch.no_grad():
+        want = hf(input_ids=ids).last_hidden_state
+        got = native(native.embed_tokens(ids))
+        assert torch.allclose(got, want, atol=3e-5), float((got - want).abs().max())
+        cache = native.new_cache(2, 16)
+        prefix = native(native.embed_tokens(ids[:, :6]), cache=cache)
+        assert torch.allclose(prefix, want[:, :6], atol=3e-5)
+        for t in range(6, 9):
+            step = native.decode_step_at(native.embed_tokens(ids[:, t]), cache, torch.tensor([t]))
+            cache.length = t + 1
+            assert torch.allclose(step, want[:, t], atol=5e-5), t
+    with pytest.raises(ValueError, match="multiple of num_kv_heads"):
+        LlamaDecoder(LlamaConfig(num_layers=1, hidden_size=64, num_heads=4, ffn_dim=64, vocab_size=8, num_kv_heads=3))

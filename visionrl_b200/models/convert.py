@@ -57,22 +57,29 @@ def _strip_trunk_prefix(state: Mapping[str, torch.Tensor]) -> dict[str, torch.Te
 
 
 def llama_from_hf(state: Mapping[str, torch.Tensor], num_heads: int) -> dict[str, torch.Tensor]:
-    """State dict of ``LlamaDecoder`` from a Hugging Face ``LlamaModel`` / ``LlamaForCausalLM``
-    state dict (multi-head attention: as many key/value heads as query heads)."""
+    """State dict of ``LlamaDecoder`` from a Hugging Face ``LlamaModel`` / ``LlamaForCausalLM`` /
+    ``Qwen2Model`` state dict: multi-head or grouped-query attention (build the decoder with
+    ``num_kv_heads``), with or without the q/k/v bias (``qkv_bias``)."""
     hf = _strip_trunk_prefix(state)
     out: dict[str, torch.Tensor] = {"embed_tokens.weight": hf["embed_tokens.weight"], "norm.weight": hf["norm.weight"]}
     layer = 0
     while f"layers.{layer}.self_attn.q_proj.weight" in hf:
         p = f"layers.{layer}."
         q, k, v = (hf[p + f"self_attn.{n}_proj.weight"] for n in "qkv")
-        if k.shape != q.shape or v.shape != q.shape:
-            raise ValueError(f"layer {layer}: grouped-query attention ({tuple(k.shape)} keys for "
-                             f"{tuple(q.shape)} queries) has no native counterpart")
-        for bias in ("self_attn.q_proj.bias", "mlp.gate_proj.bias"):
+        head_dim = q.shape[0] // num_heads
+        kv_heads = k.shape[0] // head_dim          # fewer than num_heads: grouped-query attention
+        if k.shape != v.shape or kv_heads * head_dim != k.shape[0] or num_heads % max(kv_heads, 1):
+            raise ValueError(f"layer {layer}: key/value projections of {tuple(k.shape)} / {tuple(v.shape)} rows "
+                             f"do not form whole heads of {head_dim}")
+        for bias in ("self_attn.o_proj.bias", "mlp.gate_proj.bias", "mlp.down_proj.bias"):
             if p + bias in hf:
-                raise ValueError(f"layer {layer}: projection biases have no native counterpart")
+                raise ValueError(f"layer {layer}: a bias on {bias.rsplit('.', 1)[0]} has no native counterpart")
         out[p + "attn.qkv.weight"] = torch.cat([_interleave_rotary_rows(q, num_heads),
-                                                _interleave_rotary_rows(k, num_heads), v], dim=0)
+                                                _interleave_rotary_rows(k, kv_heads), v], dim=0)
+        if p + "self_attn.q_proj.bias" in hf:      # Qwen2-style trunks: bias on q, k and v only
+            qb, kb, vb = (hf[p + f"self_attn.{n}_proj.bias"] for n in "qkv")
+            out[p + "attn.qkv.bias"] = torch.cat([_interleave_rotary_rows(qb.unsqueeze(1), num_heads).squeeze(1),
+                                                  _interleave_rotary_rows(kb.unsqueeze(1), kv_heads).squeeze(1), vb])
         out[p + "attn.out.weight"] = hf[p + "self_attn.o_proj.weight"]
         out[p + "gate_up.weight"] = torch.cat([hf[p + "mlp.gate_proj.weight"], hf[p + "mlp.up_proj.weight"]], dim=0)
         out[p + "down.weight"] = hf[p + "mlp.down_proj.weight"]

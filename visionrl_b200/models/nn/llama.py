@@ -35,6 +35,8 @@ class LlamaConfig:
     rope_theta: float = 10000.0
     rms_eps: float = 1e-6
     max_positions: int = 4096
+    num_kv_heads: int | None = None     # fewer key/value heads than query heads (grouped-query attention)
+    qkv_bias: bool = False              # bias on the fused q/k/v projection (Qwen2-style trunks)
 
     @classmethod
     def from_dict(cls, d: dict) -> "LlamaConfig":
@@ -69,15 +71,34 @@ class LlamaAttention(nn.Module):
     def __init__(self, cfg: LlamaConfig):
         super().__init__()
         self.heads, self.head_dim = cfg.num_heads, cfg.hidden_size // cfg.num_heads
-        self.qkv = LoRALinear(cfg.hidden_size, 3 * cfg.hidden_size, bias=False)
+        self.kv_heads = int(cfg.num_kv_heads or cfg.num_heads)
+        if self.heads % self.kv_heads:
+            raise ValueError(f"num_heads={self.heads} is not a multiple of num_kv_heads={self.kv_heads}")
+        self.qkv = LoRALinear(cfg.hidden_size, (self.heads + 2 * self.kv_heads) * self.head_dim,
+                              bias=bool(cfg.qkv_bias))
         self.out = LoRALinear(cfg.hidden_size, cfg.hidden_size, bias=False)
         self.qkv.lora_aliases = ("q_proj", "k_proj", "v_proj")
         self.out.lora_aliases = ("o_proj",)
 
+    @property
+    def plain_layout(self) -> bool:
+        """Equal head counts and no bias: the layout the fused decode kernels are written for."""
+        return self.kv_heads == self.heads and self.qkv.bias is None
+
     def _split(self, x):
         b, s, _ = x.shape
-        q, k, v = x.view(b, s, 3, self.heads, self.head_dim).unbind(2)
-        return (t.transpose(1, 2) for t in (q, k, v))
+        if self.kv_heads == self.heads:
+            q, k, v = x.view(b, s, 3, self.heads, self.head_dim).unbind(2)
+            return (t.transpose(1, 2) for t in (q, k, v))
+        # grouped-query attention: [q | k | v] with fewer k/v heads; every k/v head serves a run of
+        # consecutive query heads and is repeated here, so everything downstream (rotary embedding,
+        # the cache, the attention calls) sees equal head counts
+        hd, group = self.head_dim, self.heads // self.kv_heads
+        q, k, v = x.split((self.heads * hd, self.kv_heads * hd, self.kv_heads * hd), dim=-1)
+        q = q.view(b, s, self.heads, hd).transpose(1, 2)
+        k = k.view(b, s, self.kv_heads, hd).transpose(1, 2).repeat_interleave(group, dim=1)
+        v = v.view(b, s, self.kv_heads, hd).transpose(1, 2).repeat_interleave(group, dim=1)
+        return iter((q, k, v))
 
 
 class LlamaLayer(nn.Module):
@@ -206,6 +227,7 @@ class LlamaDecoder(AdapterMixin, nn.Module):
         from visionrl_b200.ops import _ext
 
         return (embeds.is_cuda and embeds.dtype == torch.bfloat16 and embeds.dim() == 2
+                and self.layers[0].attn.plain_layout
                 and not torch.is_grad_enabled() and self.head_dim == 128
                 and self.cfg.hidden_size % 8 == 0 and self.cfg.ffn_dim % 8 == 0
                 and _ext.kernels_enabled() and _ext.has("decode_qkv_rope_append"))
