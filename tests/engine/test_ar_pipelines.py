@@ -119,7 +119,10 @@ def test_nextstep_rows_tokens_noise_and_replay_context(nextstep):
     assert out.extra["log_probs"].shape == (8, 4) and torch.isfinite(out.extra["log_probs"]).all()
     for key in ("prompt_input_ids", "prompt_attention_mask", "uncond_input_ids", "uncond_attention_mask"):
         assert out.extra[key].shape[0] == 8
-    assert out.rollout_trajectory_data is None                      # no DiT trajectory for AR families
+    # no DiT trajectory for a continuous-token rollout; the record carries the log-probabilities only
+    traj = out.rollout_trajectory_data
+    assert traj.dit_trajectory is None and traj.denoising_env is None
+    assert torch.equal(traj.rollout_log_probs, out.extra["log_probs"])
     ctx = out.extra["context"]
     assert (ctx["cfg_scale"], ctx["num_flow_steps"], ctx["noise_level"]) == (2.0, 3, 0.8)
     assert (out.metrics.num_prompts, out.metrics.num_samples, out.metrics.num_steps) == (2, 8, 4)

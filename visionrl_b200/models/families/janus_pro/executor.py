@@ -93,18 +93,29 @@ class JanusProPipelineExecutor(ARPipelineExecutorBase):
     def _format_t2i_prompt(prompt: str) -> str:
         return f"<｜User｜>: {prompt}\n\n<｜Assistant｜>:<begin_of_image>"
 
-    def _tokenize_prompts(self, prompts: list[str], max_length: int):
+    def _encode_texts(self, texts: list[str], max_length: int):
+        """Token ids and mask from the policy's own tokenizer, or — for a policy that carries a
+        chat processor with a Hugging Face tokenizer instead (the reference's policy contract) —
+        from that."""
         device = self.model.device
-        tok = self.model.tokenizer
-        cond_ids, cond_mask = tok.batch_encode([self._format_t2i_prompt(p) for p in prompts],
-                                               max_length, device)
-        unc_ids, unc_mask = tok.batch_encode([self._format_t2i_prompt("")] * len(prompts),
-                                             max_length, device)
-        return self.align_pair(cond_ids, cond_mask, unc_ids, unc_mask,
-                               pad_id=getattr(tok, "pad_id", 0))
+        tok = getattr(self.model, "tokenizer", None)
+        if tok is not None and hasattr(tok, "batch_encode"):
+            return (*tok.batch_encode(list(texts), max_length, device), getattr(tok, "pad_id", 0))
+        processor = self.model.processor
+        hf = getattr(processor, "tokenizer", processor)
+        enc = hf(list(texts), return_tensors="pt", padding="max_length", truncation=True, max_length=max_length)
+        return enc["input_ids"].to(device), enc["attention_mask"].to(device), int(getattr(hf, "pad_token_id", 0) or 0)
+
+    def _tokenize_prompts(self, prompts: list[str], max_length: int):
+        cond_ids, cond_mask, pad = self._encode_texts([self._format_t2i_prompt(p) for p in prompts], max_length)
+        unc_ids, unc_mask, _ = self._encode_texts([self._format_t2i_prompt("")] * len(prompts), max_length)
+        return self.align_pair(cond_ids, cond_mask, unc_ids, unc_mask, pad_id=pad)
 
     def _embed(self, token_ids: torch.Tensor) -> torch.Tensor:
-        return self.model.embed_text(token_ids)
+        embed = getattr(self.model, "embed_text", None)
+        if callable(embed):
+            return embed(token_ids)
+        return self.model.language_model.get_input_embeddings()(token_ids)
 
     # -- sampling -----------------------------------------------------------------------
     def _sample_with_ar_scheduler(self, *, request: GenerationRequest, sample_ids: list[str],
@@ -115,7 +126,7 @@ class JanusProPipelineExecutor(ARPipelineExecutorBase):
         scheduler = ARTokenScheduler(max_batch_size=max(1, int(batch_size)))
         scheduler.add_many([
             ActiveSequence(request_id=request.request_id, sample_id=sid, family=self.family,
-                           task=self.task, tokenizer_key="janus", dtype=str(self.model.dtype),
+                           task=self.task, tokenizer_key="janus", dtype=str(getattr(self.model, "dtype", "float32")),
                            max_new_tokens=state.image_token_num, metadata={"row_index": row})
             for row, sid in enumerate(sample_ids)
         ])

@@ -15,7 +15,8 @@ from visionrl_b200.engine.ar import (
 )
 from visionrl_b200.engine.core.protocols import PipelineChunkResult
 from visionrl_b200.engine.core.types import (
-    GenerationMetrics, GenerationRequest, GenerationSampleSpec, OutputBatch, WorkloadSignature,
+    GenerationMetrics, GenerationRequest, GenerationSampleSpec, OutputBatch, RolloutTrajectoryData,
+    WorkloadSignature,
 )
 from visionrl_b200.engine.microbatching import MicroBatchPlan
 
@@ -58,7 +59,8 @@ def _pack(request, sample_specs, fields, context, steps, micro_batches, peak) ->
     return OutputBatch(
         request_id=request.request_id, family=request.family, task=request.task,
         prompts=list(request.prompts), sample_specs=list(sample_specs), output=fields["output"],
-        rollout_trajectory_data=None, extra=extra,
+        # continuous tokens have no denoising trajectory; the log-probabilities are carried here too
+        rollout_trajectory_data=RolloutTrajectoryData(rollout_log_probs=fields["log_probs"]), extra=extra,
         metrics=GenerationMetrics(num_prompts=len(request.prompts), num_samples=len(sample_specs),
                                   num_steps=steps, micro_batches=micro_batches, peak_memory_mb=peak),
         peak_memory_mb=peak or 0.0)
@@ -88,14 +90,27 @@ class NextStep1PipelineExecutor(ARPipelineExecutorBase):
     def workload_signature(self, request: GenerationRequest) -> WorkloadSignature:
         return WorkloadSignature.from_request(request)
 
+    def _encode_texts(self, texts: list[str], max_length: int):
+        """Token ids and mask from the policy's own tokenizer, or — for a policy that carries a
+        Hugging Face style ``processor`` instead (the reference's policy contract) — from that."""
+        device = self.model.device
+        tok = getattr(self.model, "tokenizer", None)
+        if tok is not None and hasattr(tok, "batch_encode"):
+            return (*tok.batch_encode(list(texts), max_length, device), getattr(tok, "pad_id", 0))
+        enc = self.model.processor(list(texts), return_tensors="pt", padding="max_length", truncation=True,
+                                   max_length=max_length)
+        return enc["input_ids"].to(device), enc["attention_mask"].to(device), 0
+
     def _tokenize_prompts(self, prompts: list[str], max_length: int):
-        tok, device = self.model.tokenizer, self.model.device
-        c_ids, c_mask = tok.batch_encode(list(prompts), max_length, device)
-        u_ids, u_mask = tok.batch_encode([""] * len(prompts), max_length, device)
-        return self.align_pair(c_ids, c_mask, u_ids, u_mask, pad_id=getattr(tok, "pad_id", 0))
+        c_ids, c_mask, pad = self._encode_texts(list(prompts), max_length)
+        u_ids, u_mask, _ = self._encode_texts([""] * len(prompts), max_length)
+        return self.align_pair(c_ids, c_mask, u_ids, u_mask, pad_id=pad)
 
     def _embed(self, token_ids: torch.Tensor) -> torch.Tensor:
-        return self.model.embed_text(token_ids)
+        embed = getattr(self.model, "embed_text", None)
+        if callable(embed):
+            return embed(token_ids)
+        return self.model.language_model.get_input_embeddings()(token_ids)
 
     def _sample_with_ar_scheduler(self, *, request, sample_ids, cond_embeds, uncond_embeds,
                                   prompt_mask, uncond_mask, sample_kwargs, batch_size: int):
@@ -104,7 +119,7 @@ class NextStep1PipelineExecutor(ARPipelineExecutorBase):
         scheduler = ARTokenScheduler(max_batch_size=max(1, int(batch_size)))
         scheduler.add_many([
             ActiveSequence(request_id=request.request_id, sample_id=sid, family=self.family,
-                           task=self.task, tokenizer_key="nextstep", dtype=str(self.model.dtype),
+                           task=self.task, tokenizer_key="nextstep", dtype=str(getattr(self.model, "dtype", "float32")),
                            max_new_tokens=state.image_token_num, metadata={"row_index": row})
             for row, sid in enumerate(sample_ids)])
         while len(scheduler):
@@ -130,12 +145,12 @@ class NextStep1PipelineExecutor(ARPipelineExecutorBase):
             kwargs["generator"] = torch.Generator(device="cpu").manual_seed(int(spec.seed) + seed_offset)
         c_ids, c_mask, u_ids, u_mask = self._tokenize_prompts(prompts, spec.max_text_length)
         if spec.use_ar_scheduler:
-            tokens, log_probs, noise = self._sample_with_ar_scheduler(
+            tokens, noise, log_probs = self._sample_with_ar_scheduler(
                 request=request, sample_ids=sample_ids, cond_embeds=self._embed(c_ids),
                 uncond_embeds=self._embed(u_ids), prompt_mask=c_mask, uncond_mask=u_mask,
                 sample_kwargs=kwargs, batch_size=int(s.get("ar_scheduler_batch_size", len(prompts))))
         else:
-            tokens, log_probs, noise = self.model.sample_image_tokens(
+            tokens, noise, log_probs = self.model.sample_image_tokens(
                 self._embed(c_ids), self._embed(u_ids), c_mask, u_mask, **kwargs)
         images = self.model.decode_image_tokens(tokens, image_size=spec.image_size)
         fields = {"output": images, "tokens": tokens, "log_probs": log_probs, "saved_noise": noise,

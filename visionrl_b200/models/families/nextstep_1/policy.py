@@ -305,7 +305,8 @@ class NextStep1Policy(nn.Module):
                             replay_extras={"saved_noise": state.saved_noise[idx, position]})
 
     def finalize_ar_state(self, state: NextStep1ARState):
-        return state.tokens, state.log_probs, state.saved_noise
+        """``(tokens, saved_noise, log_probs)`` — the order of the reference's 3-tuple."""
+        return state.tokens, state.saved_noise, state.log_probs
 
     # -- replay -----------------------------------------------------------------------------------
     def recompute_logprobs(self, prompt_embeds, uncond_embeds, prompt_mask, uncond_mask, tokens,
