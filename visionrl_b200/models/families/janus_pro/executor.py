@@ -117,6 +117,15 @@ class JanusProPipelineExecutor(ARPipelineExecutorBase):
             return embed(token_ids)
         return self.model.language_model.get_input_embeddings()(token_ids)
 
+    def _takes_generator(self) -> bool:
+        import inspect
+
+        try:
+            params = inspect.signature(self.model.sample_image_tokens).parameters
+        except (TypeError, ValueError):
+            return True
+        return "generator" in params or any(p.kind == p.VAR_KEYWORD for p in params.values())
+
     # -- sampling -----------------------------------------------------------------------
     def _sample_with_ar_scheduler(self, *, request: GenerationRequest, sample_ids: list[str],
                                   cond_embeds, uncond_embeds, prompt_mask, uncond_mask,
@@ -127,7 +136,7 @@ class JanusProPipelineExecutor(ARPipelineExecutorBase):
         scheduler.add_many([
             ActiveSequence(request_id=request.request_id, sample_id=sid, family=self.family,
                            task=self.task, tokenizer_key="janus", dtype=str(getattr(self.model, "dtype", "float32")),
-                           max_new_tokens=state.image_token_num, metadata={"row_index": row})
+                           max_new_tokens=int(sample_kwargs["image_token_num"]), metadata={"row_index": row})
             for row, sid in enumerate(sample_ids)
         ])
         while len(scheduler):
@@ -152,8 +161,12 @@ class JanusProPipelineExecutor(ARPipelineExecutorBase):
         if spec.seed is not None:
             generator = torch.Generator(device="cpu").manual_seed(int(spec.seed) + seed_offset)
         cond_ids, cond_mask, unc_ids, unc_mask = self._tokenize_prompts(prompts, spec.max_text_length)
-        kwargs = dict(cfg_weight=cfg_weight, temperature=temperature,
-                      image_token_num=spec.image_token_num, generator=generator)
+        kwargs = dict(cfg_weight=cfg_weight, temperature=temperature, image_token_num=spec.image_token_num)
+        if generator is not None and self._takes_generator():
+            kwargs["generator"] = generator
+        elif generator is not None:
+            # a policy that draws from the default generator (the reference's contract): seed that
+            torch.manual_seed(int(spec.seed) + seed_offset)
         if spec.use_ar_scheduler:
             tokens, log_probs = self._sample_with_ar_scheduler(
                 request=request, sample_ids=sample_ids, cond_embeds=self._embed(cond_ids),

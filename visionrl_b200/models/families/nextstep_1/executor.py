@@ -120,7 +120,7 @@ class NextStep1PipelineExecutor(ARPipelineExecutorBase):
         scheduler.add_many([
             ActiveSequence(request_id=request.request_id, sample_id=sid, family=self.family,
                            task=self.task, tokenizer_key="nextstep", dtype=str(getattr(self.model, "dtype", "float32")),
-                           max_new_tokens=state.image_token_num, metadata={"row_index": row})
+                           max_new_tokens=int(sample_kwargs["image_token_num"]), metadata={"row_index": row})
             for row, sid in enumerate(sample_ids)])
         while len(scheduler):
             batch = scheduler.pop_batch()
