@@ -42,10 +42,12 @@ def compute() -> dict:
     flat(res, "expand", expand_prompt_major_prompts(req))
     for i, (ps, ss, sc) in enumerate(((0, 0, 2), (0, 2, 1), (2, 1, 2))):
         ch = MicroBatchPlan(prompt_index=ps, prompt=req.prompts[ps], sample_start=ss, sample_count=sc)
-        validate_chunk(req, ch); res[f"seedoff{i}"] = torch.tensor(float(chunk_seed_offset(req, ch)))
+        validate_chunk(req, ch)
+        res[f"seedoff{i}"] = torch.tensor(float(chunk_seed_offset(req, ch)))
     for bad in ((5, 0, 1), (0, 2, 2), (0, 0, 0)):
         try:
-            validate_chunk(req, MicroBatchPlan(prompt_index=bad[0], prompt="x", sample_start=bad[1], sample_count=bad[2])); res[f"bad{bad}"] = torch.tensor(0.0)
+            validate_chunk(req, MicroBatchPlan(prompt_index=bad[0], prompt="x", sample_start=bad[1], sample_count=bad[2]))
+            res[f"bad{bad}"] = torch.tensor(0.0)
         except Exception as e: res[f"bad{bad}"] = torch.tensor(1.0)
     a, am = torch.randint(0, 9, (2, 5), generator=g), torch.ones(2, 5, dtype=torch.long)
     b, bm = torch.randint(0, 9, (2, 3), generator=g), torch.ones(2, 3, dtype=torch.long)
@@ -70,12 +72,16 @@ def compute() -> dict:
     loop = asyncio.new_event_loop()
     ctx = RolloutPackContext(metadata={}, device=torch.device("cpu"), kl_reward=0.0, rescale_to_unit=True)
     pk = ARDiscreteRolloutPacker()
-    flat(res, "disc.reward_outputs", pk.reward_outputs(ob, ctx)); flat(res, "disc.reward_prompts", pk.reward_prompts(ob, ctx))
+    flat(res, "disc.reward_outputs", pk.reward_outputs(ob, ctx))
+    flat(res, "disc.reward_prompts", pk.reward_prompts(ob, ctx))
     batch = loop.run_until_complete(pk.pack(ob, torch.arange(4.0), ctx))
     flat(res, "disc.batch", {"obs": batch.observations, "act": batch.actions, "rew": batch.rewards, "done": batch.dones.float(), "gid": batch.group_ids.float(), "extras": batch.extras, "ctx": batch.context, "videos": batch.videos, "prompts": batch.prompts})
     class TokPolicy(nn.Module):
         def __init__(self):
-            super().__init__(); torch.manual_seed(1); self.emb = nn.Embedding(50, 50); self.adapter = True
+            super().__init__()
+            torch.manual_seed(1)
+            self.emb = nn.Embedding(50, 50)
+            self.adapter = True
         def replay_forward(self, batch, timestep_idx=0):
             ids = batch.actions
             logits = self.emb(ids) * (1.0 if self.adapter else 0.5)
@@ -85,7 +91,8 @@ def compute() -> dict:
             self.adapter = False
             try: yield
             finally: self.adapter = True
-        has_adapters = True; uses_lora = True
+        has_adapters = True
+        uses_lora = True
     pol = TokPolicy()
     for need_ref in (False, True):
         try:
@@ -105,7 +112,9 @@ def compute() -> dict:
     flat(res, "cont.batch", {"obs": batch2.observations, "act": batch2.actions, "rew": batch2.rewards, "gid": batch2.group_ids.float(), "extras": batch2.extras, "ctx": batch2.context, "videos": batch2.videos})
     class ContPolicy(nn.Module):
         def __init__(self):
-            super().__init__(); self.w = nn.Parameter(torch.tensor(0.3)); self.adapter = True
+            super().__init__()
+            self.w = nn.Parameter(torch.tensor(0.3))
+            self.adapter = True
         def replay_forward(self, batch, timestep_idx=0):
             lp = -(batch.actions.float() ** 2).sum(-1) * (self.w if self.adapter else self.w.detach() * 0.5)
             return {"log_probs": lp, "target_tokens": batch.actions}
@@ -114,7 +123,8 @@ def compute() -> dict:
             self.adapter = False
             try: yield
             finally: self.adapter = True
-        has_adapters = True; uses_lora = True
+        has_adapters = True
+        uses_lora = True
     cp = ContPolicy()
     for need_ref in (False, True):
         try:

@@ -39,7 +39,8 @@ def compute() -> dict:
         if chunk.sample_count > 2: raise RuntimeError("CUDA out of memory. Tried to allocate 2.00 GiB")
         return (chunk.prompt_index, chunk.sample_start, chunk.sample_count)
     chunks = [MicroBatchPlan(prompt_index=0, prompt="a", sample_start=0, sample_count=7), MicroBatchPlan(prompt_index=1, prompt="b", sample_start=0, sample_count=2)]
-    rec("oom/results", run_microbatches_with_oom_retry(chunks, run)); rec("oom/calls", calls)
+    rec("oom/results", run_microbatches_with_oom_retry(chunks, run))
+    rec("oom/calls", calls)
     try:
         run_microbatches_with_oom_retry([MicroBatchPlan(prompt_index=0, prompt="a", sample_start=0, sample_count=1)], lambda c: (_ for _ in ()).throw(RuntimeError("CUDA out of memory")))
         rec("oom/single", "no error")
@@ -47,7 +48,8 @@ def compute() -> dict:
     try:
         run_microbatches_with_oom_retry(chunks, lambda c: (_ for _ in ()).throw(RuntimeError("shape mismatch")))
     except Exception as e: rec("oom/other", [type(e).__name__, str(e)])
-    a, b = chunks[0].split(); rec("split", [(a.sample_start, a.sample_count), (b.sample_start, b.sample_count)])
+    a, b = chunks[0].split()
+    rec("split", [(a.sample_start, a.sample_count), (b.sample_start, b.sample_count)])
     # --- sample specs
     r = GenerationRequest(request_id="req-1", family="f", task="t", prompts=["x", "y"], samples_per_prompt=3, sampling={"seed": 9})
     specs = GenerationIdFactory().build_sample_specs(r)
@@ -64,7 +66,9 @@ def compute() -> dict:
             if request.metadata.get("boom"): raise ValueError("executor failed: boom")
             return OutputBatch(request_id=request.request_id, family="f", task="t", prompts=list(request.prompts), sample_specs=list(sample_specs),
                                output=torch.zeros(len(sample_specs), 1), rollout_trajectory_data=None, extra={}, metrics=GenerationMetrics())
-    reg = FamilyPipelineRegistry(); ex = Ex(); reg.register(ex)
+    reg = FamilyPipelineRegistry()
+    ex = Ex()
+    reg.register(ex)
     w = GenerationWorker(reg)
     ok = w.execute([r])[r.request_id]
     rec("worker/ok", {"error": ok.error, "n": len(ok.sample_specs), "rid": ok.request_id})
@@ -83,8 +87,11 @@ def compute() -> dict:
         for step in range(1, 7):
             with torch.no_grad():
                 for p in lin.parameters(): p.add_(0.1)
-            ema.step(list(lin.parameters()), step); decays.append(ema.get_current_decay(step)); snaps.append([float(t.sum()) for t in ema.ema_parameters])
-        rec(f"ema/{kw['decay']}/decays", decays); rec(f"ema/{kw['decay']}/sums", snaps)
+            ema.step(list(lin.parameters()), step)
+            decays.append(ema.get_current_decay(step))
+            snaps.append([float(t.sum()) for t in ema.ema_parameters])
+        rec(f"ema/{kw['decay']}/decays", decays)
+        rec(f"ema/{kw['decay']}/sums", snaps)
         ema.copy_ema_to(list(lin.parameters()), store_temp=False)
         rec(f"ema/{kw['decay']}/swapped_in", [float(p.detach().sum()) for p in lin.parameters()])
         rec(f"ema/{kw['decay']}/state_keys", sorted(ema.state_dict()))
@@ -101,7 +108,8 @@ def compute() -> dict:
         rec("multi/score", loop.run_until_complete(mr.score(ro("abc"))))
         rec("multi/batch", loop.run_until_complete(mr.score_batch([ro("a"), ro("bb"), ro("ccc")])))
         rec("multi/components", {k: list(v) for k, v in mr.last_components.items()} if hasattr(mr, "last_components") else None)
-        mr.reset_components(); rec("multi/after_reset", {k: list(v) for k, v in mr.last_components.items()} if hasattr(mr, "last_components") else None)
+        mr.reset_components()
+        rec("multi/after_reset", {k: list(v) for k, v in mr.last_components.items()} if hasattr(mr, "last_components") else None)
     except Exception as e:
         rec("multi/error", [type(e).__name__, str(e)[:200]])
     # --- stack_batches

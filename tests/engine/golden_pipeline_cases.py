@@ -24,8 +24,10 @@ from vrl.rollouts.packers.diffusion import DiffusionRolloutPacker
 T = 4
 class Sched:
     def __init__(self):
-        s = torch.linspace(1.0, 1.0 / 1000, T, dtype=torch.float64); s = 3.0 * s / (1 + 2.0 * s)
-        self.timesteps = (s * 1000).float(); self.sigmas = torch.cat([s, s.new_zeros(1)]).float()
+        s = torch.linspace(1.0, 1.0 / 1000, T, dtype=torch.float64)
+        s = 3.0 * s / (1 + 2.0 * s)
+        self.timesteps = (s * 1000).float()
+        self.sigmas = torch.cat([s, s.new_zeros(1)]).float()
     def index_for_timestep(self, t): return int(torch.argmin((self.timesteps - float(t)).abs()))
     def indices_for_timesteps(self, ts):
         ts = torch.as_tensor(ts, dtype=torch.float32).reshape(-1)
@@ -33,12 +35,17 @@ class Sched:
     def set_timesteps(self, n, device=None): pass
 @dataclass
 class State:
-    latents: torch.Tensor; timesteps: torch.Tensor; scheduler: Any; prompt_embeds: torch.Tensor
+    latents: torch.Tensor
+    timesteps: torch.Tensor
+    scheduler: Any
+    prompt_embeds: torch.Tensor
     extra: dict = field(default_factory=dict)
 class Policy(torch.nn.Module):
     device = torch.device("cpu")
     def __init__(self):
-        super().__init__(); self.w = torch.nn.Parameter(torch.tensor(0.1)); self.adapter = True
+        super().__init__()
+        self.w = torch.nn.Parameter(torch.tensor(0.1))
+        self.adapter = True
     def encode_prompt(self, prompt, negative_prompt=None, **kw):
         plist = [prompt] if isinstance(prompt, str) else list(prompt)
         return {"prompt_embeds": torch.stack([torch.full((3, 2), float(sum(ord(c) for c in p) % 7)) for p in plist])}
@@ -65,10 +72,12 @@ class Policy(torch.nn.Module):
         try: yield
         finally: self.adapter = True
 class Ex(DiffusionPipelineExecutorBase):
-    family, task = "sd3_5", "t2i"; default_sample_batch_size = 4
+    family, task = "sd3_5", "t2i"
+    default_sample_batch_size = 4
     def __init__(self, policy): self.model = policy
 def req(prompts, n, **s):
-    base = {"num_steps": T, "guidance_scale": 4.5, "height": 32, "width": 32, "noise_level": 0.7, "sample_batch_size": 2, "seed": 5}; base.update(s)
+    base = {"num_steps": T, "guidance_scale": 4.5, "height": 32, "width": 32, "noise_level": 0.7, "sample_batch_size": 2, "seed": 5}
+    base.update(s)
     return GenerationRequest(request_id="req", family="sd3_5", task="t2i", prompts=prompts, samples_per_prompt=n, sampling=base)
 def flat(res, prefix, obj, depth=0):
     if torch.is_tensor(obj): res[prefix] = obj.detach().float().clone()
@@ -80,7 +89,8 @@ def flat(res, prefix, obj, depth=0):
 
 def compute() -> dict:
     res = {}
-    pol = Policy(); ex = Ex(pol)
+    pol = Policy()
+    ex = Ex(pol)
     cases = {"base": dict(), "kl": dict(return_kl=True), "cps": dict(sde_type="cps", noise_level=1.0), "window": dict(sde_window_size=2, sde_window_range=[0, 3]),
              "same": dict(same_latent=True), "nlow": dict(noise_level=0.3, sample_batch_size=3)}
     loop = asyncio.new_event_loop()
@@ -88,13 +98,19 @@ def compute() -> dict:
         random.seed(11)
         r = req(["a cat", "b dog"], 3, **extra)
         o = ex.forward(r, GenerationIdFactory().build_sample_specs(r))
-        flat(res, f"{name}/out", o.output); flat(res, f"{name}/traj", o.rollout_trajectory_data); flat(res, f"{name}/extra", o.extra if hasattr(o, "extra") else {})
+        flat(res, f"{name}/out", o.output)
+        flat(res, f"{name}/traj", o.rollout_trajectory_data)
+        flat(res, f"{name}/extra", o.extra if hasattr(o, "extra") else {})
         res[f"{name}/specs"] = torch.tensor([[s.prompt_index, s.sample_index] for s in o.sample_specs]).float()
         res[f"{name}/micro"] = torch.tensor(float(o.metrics.micro_batches))
         ctx = RolloutPackContext(metadata={}, device=torch.device("cpu"), kl_reward=0.01 if name == "kl" else 0.0, rescale_to_unit=False)
         batch = loop.run_until_complete(DiffusionRolloutPacker(error_prefix="Stub").pack(o, torch.arange(6.0), ctx))
-        flat(res, f"{name}/batch.obs", batch.observations); flat(res, f"{name}/batch.act", batch.actions); flat(res, f"{name}/batch.rew", batch.rewards)
-        flat(res, f"{name}/batch.gid", batch.group_ids.float()); flat(res, f"{name}/batch.extras", batch.extras); flat(res, f"{name}/batch.ctx", batch.context)
+        flat(res, f"{name}/batch.obs", batch.observations)
+        flat(res, f"{name}/batch.act", batch.actions)
+        flat(res, f"{name}/batch.rew", batch.rewards)
+        flat(res, f"{name}/batch.gid", batch.group_ids.float())
+        flat(res, f"{name}/batch.extras", batch.extras)
+        flat(res, f"{name}/batch.ctx", batch.context)
         ev = FlowMatchingEvaluator(Sched(), noise_level=float(r.sampling["noise_level"]), sde_type=r.sampling.get("sde_type", "sde"))
         for j in range(T):
             sgn = ev.evaluate(pol, batch, j, ref_model=pol, signal_request=SignalRequest(need_ref=True, need_kl_intermediates=True))

@@ -58,13 +58,15 @@ def run(case):
     torch.manual_seed(0)
     model = nn.Sequential(nn.Linear(3, 4), nn.Tanh(), nn.Linear(4, 1))
     kw = dict(n=2, rollout_batch_size=4, bf16=False, timestep_fraction=0.5, ppo_epochs=2, max_norm=1.0)
-    ema_cls = getattr(T, "EMAConfig"); optim_cls = getattr(T, "OptimConfig", None)
+    ema_cls = getattr(T, "EMAConfig")
+    optim_cls = getattr(T, "OptimConfig", None)
     cfg = TrainerConfig(**kw, ema=ema_cls(enable=True, decay=0.9, update_interval=1))
     cfg.optim.lr = 1e-2
     token = case == "token"
     if token:
         algo = TokenGRPO(TokenGRPOConfig(eps_clip=0.2, init_kl_coef=0.05, kl_estimator="k3"))
-        ref = nn.Sequential(nn.Linear(3, 4), nn.Tanh(), nn.Linear(4, 1)); ref.load_state_dict(model.state_dict())
+        ref = nn.Sequential(nn.Linear(3, 4), nn.Tanh(), nn.Linear(4, 1))
+        ref.load_state_dict(model.state_dict())
         for p in ref.parameters(): p.requires_grad_(False)
         cfg.timestep_fraction = 1.0
     else:
