@@ -25,7 +25,7 @@ from typing import Any, Iterator
 import torch
 from torch import nn
 
-from visionrl_b200.models.ar import ARStepResult
+from visionrl_b200.models.ar import ARStepResult, AutoregressivePolicy
 from visionrl_b200.models.families.flow_policy import resolve_dtype, seeded_construction, seeded_init
 from visionrl_b200.models.nn.layers import Linear, adapters_disabled, apply_lora, iter_lora_layers
 from visionrl_b200.models.nn.llama import KVCache, LlamaConfig, LlamaDecoder
@@ -132,18 +132,35 @@ class JanusNetwork(nn.Module):
         return head(hh).float()
 
 
-def image_token_logits_from_hidden(network: JanusNetwork, hidden: torch.Tensor) -> torch.Tensor:
-    """Image-vocabulary logits from trunk hidden states (always through ``gen_head``)."""
-    return network.image_logits(hidden)
+def image_token_logits_from_hidden(network: Any, hidden: torch.Tensor) -> torch.Tensor:
+    """Image-vocabulary logits from trunk hidden states (always through ``gen_head``).
+    ``network`` is a :class:`JanusNetwork` or an external multi-modality model with ``gen_head``."""
+    if hasattr(network, "image_logits"):
+        return network.image_logits(hidden)
+    return network.gen_head(hidden)
 
 
-class JanusProPolicy(nn.Module):
+class JanusProPolicy(nn.Module, AutoregressivePolicy):
     family = "janus_pro"
     model_family = "janus_pro"
 
+    def __new__(cls, config: JanusProConfig | None = None, *args: Any, mmgpt: Any | None = None,
+                **kwargs: Any):
+        # an already loaded external model is served by the wrapper class of ``wrapped.py``
+        if mmgpt is not None and cls is JanusProPolicy:
+            from visionrl_b200.models.families.janus_pro.wrapped import WrappedJanusProPolicy
+
+            return super().__new__(WrappedJanusProPolicy)
+        return super().__new__(cls)
+
     def __init__(self, config: JanusProConfig | None = None, *, network: JanusNetwork | None = None,
-                 vq_model: nn.Module | None = None, device: Any = "cpu") -> None:
+                 vq_model: nn.Module | None = None, device: Any = "cpu", mmgpt: Any | None = None,
+                 processor: Any | None = None) -> None:
         super().__init__()
+        if mmgpt is not None:
+            raise TypeError("an external `mmgpt` is served by WrappedJanusProPolicy")
+        if processor is not None:
+            self.processor = processor
         self.config = config or JanusProConfig()
         arch = dict(self.config.arch)
         if self.config.vq_latent_channels is not None:
@@ -253,6 +270,7 @@ class JanusProPolicy(nn.Module):
     def has_adapters(self) -> bool:
         return any(True for _ in iter_lora_layers(self.policy.language_model))
 
+    @property
     def has_lora_adapter(self) -> bool:
         return self.has_adapters
 
