@@ -156,3 +156,64 @@ def test_codebook_width_comes_from_the_override_or_the_live_table():
     del policy.vq_model.quantize
     with pytest.raises(RuntimeError, match="vq_latent_channels"):
         policy.decode_image_tokens(torch.zeros(1, 4, dtype=torch.long))
+
+
+# ------------------------------------------------------------------ through the pipeline executor
+class _Tokenizer:
+    """Callable with the Hugging Face tokenizer interface the executor uses: fixed-length ids from
+    character codes, left as zeros (the pad id) beyond the text."""
+
+    pad_token_id = 0
+
+    def __call__(self, texts, return_tensors="pt", padding="max_length", truncation=True, max_length=8):
+        ids = torch.zeros(len(texts), max_length, dtype=torch.long)
+        mask = torch.zeros(len(texts), max_length, dtype=torch.long)
+        for row, text in enumerate(texts):
+            codes = [1 + (ord(ch) % (VOCAB - 1)) for ch in text][-max_length:]
+            ids[row, : len(codes)] = torch.tensor(codes)
+            mask[row, : len(codes)] = 1
+        return {"input_ids": ids, "attention_mask": mask}
+
+
+def _executor():
+    from visionrl_b200.models.families.janus_pro.executor import JanusProPipelineExecutor
+
+    torch.manual_seed(0)
+    config = JanusProConfig(use_lora=True, lora_rank=4, lora_alpha=8, image_token_num=4)
+    policy = JanusProPolicy(config, mmgpt=_External().eval(), processor=SimpleNamespace(tokenizer=_Tokenizer()))
+    return JanusProPipelineExecutor(policy)
+
+
+def _request(**sampling):
+    from visionrl_b200.engine.core.types import GenerationRequest
+
+    base = {"cfg_weight": 2.0, "temperature": 1.0, "image_token_num": 4, "image_size": 32,
+            "max_text_length": 24, "seed": 5}
+    base.update(sampling)
+    return GenerationRequest(request_id="w", family="janus_pro", task="ar_t2i", prompts=["a cat", "two dogs"],
+                             samples_per_prompt=2, sampling=base)
+
+
+def test_executor_serves_the_wrapped_policy_on_both_sampling_paths():
+    from visionrl_b200.engine.core.worker import GenerationIdFactory
+
+    executor = _executor()
+
+    def run(request):
+        return executor.forward(request, GenerationIdFactory().build_sample_specs(request))
+
+    whole = run(_request())
+    assert whole.output.shape == (4, 3, 32, 32)
+    assert whole.extra["token_ids"].shape == (4, 4) and bool((whole.extra["token_log_probs"] <= 0).all())
+    assert torch.equal(run(_request()).extra["token_ids"], whole.extra["token_ids"])
+    parts = run(_request(use_ar_scheduler=True, ar_scheduler_batch_size=3))
+    assert torch.equal(parts.extra["token_ids"], whole.extra["token_ids"])
+    torch.testing.assert_close(parts.extra["token_log_probs"], whole.extra["token_log_probs"],
+                               atol=2e-5, rtol=1e-5)
+    # the rollout's log-probabilities are what the training-time replay recomputes
+    batch = SimpleNamespace(observations=whole.extra["prompt_input_ids"].unsqueeze(1),
+                            actions=whole.extra["token_ids"],
+                            extras={"prompt_attention_mask": whole.extra["prompt_attention_mask"]})
+    out = executor.model.replay_forward(batch)
+    replayed = torch.log_softmax(out["logits"].float(), -1).gather(-1, whole.extra["token_ids"][..., None])[..., 0]
+    torch.testing.assert_close(replayed, whole.extra["token_log_probs"], atol=2e-5, rtol=1e-5)
